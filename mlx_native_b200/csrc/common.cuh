@@ -1,0 +1,95 @@
+// Shared declarations for the sm_100a kernels of the GGML block-quantized matmul path.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mlxn {
+
+// GGML type codes (same numbering as mlxn_ggml_type in include/mlxn_b200.h).
+enum : int { GT_F32 = 0, GT_F16 = 1, GT_Q4_0 = 2, GT_Q8_0 = 3, GT_Q4_K = 4, GT_Q5_K = 5, GT_Q6_K = 6, GT_I16 = 7 };
+
+// Block geometry (upstream src/shaders/quantized_matmul_ggml.metal:49-67).
+template <int T> struct BlockTraits;
+template <> struct BlockTraits<GT_Q4_0> { static constexpr int QK = 32, BYTES = 18; };
+template <> struct BlockTraits<GT_Q8_0> { static constexpr int QK = 32, BYTES = 34; };
+template <> struct BlockTraits<GT_Q6_K> { static constexpr int QK = 256, BYTES = 210; };
+
+__host__ __device__ inline uint32_t ggml_qk(int t) {
+    switch (t) {
+    case GT_F32: case GT_F16: case GT_I16: return 1;
+    case GT_Q4_0: case GT_Q8_0: return 32;
+    default: return 256;
+    }
+}
+__host__ __device__ inline uint32_t ggml_block_bytes(int t) {
+    switch (t) {
+    case GT_F32: return 4;
+    case GT_F16: case GT_I16: return 2;
+    case GT_Q4_0: return 18;
+    case GT_Q8_0: return 34;
+    case GT_Q4_K: return 144;
+    case GT_Q5_K: return 176;
+    default: return 210;
+    }
+}
+
+// Device status word written by kernels whose bounded waits gave up.  0 = ok.
+enum : uint32_t { ST_OK = 0, ST_WAIT_FULL_TIMEOUT = 1, ST_WAIT_EMPTY_TIMEOUT = 2, ST_WAIT_MMA_TIMEOUT = 3,
+                  ST_WAIT_TMEM_TIMEOUT = 4, ST_BAD_ARGUMENT = 5 };
+
+// Arguments shared by the mat-vec kernels (dense and expert-routed).
+struct QmvArgs {
+    const uint8_t *w;       // weight blocks; expert e starts at w + e*expert_stride
+    const float *x;         // activations [n_x_rows, k]
+    float *y;               // outputs [n_out_rows, n]
+    const uint32_t *ids;    // expert id per output row group (nullptr for the dense form)
+    uint32_t n, k;          // weight rows, reduction length
+    uint32_t m;             // dense: activation rows sharing the weights; routed: 1
+    uint32_t nprob;         // dense: 1; routed: n_tokens*top_k independent mat-vecs
+    uint32_t top_k;         // routed: activation row of problem p is p / top_k
+    uint32_t n_experts;
+    uint64_t expert_stride; // bytes
+    uint32_t *status;       // device status word
+};
+
+// Arguments of the mat-mat kernels (dense and grouped-by-expert).
+struct QmmArgs {
+    const uint8_t *w;
+    const float *x;          // [m, k] (dense) or [n_tokens, k] (routed)
+    float *y;                // [m, n] or [n_tokens*top_k, n]
+    uint32_t m, n, k;
+    // routed form (hids == nullptr for dense)
+    const uint32_t *htpe;    // [n_experts] rows routed to each expert
+    const int32_t *hids;     // [n_experts, hids_stride] entries token*top_k+slot
+    uint32_t hids_stride;
+    uint32_t top_k;
+    uint32_t n_experts;
+    uint32_t total_rows;     // n_tokens*top_k
+    uint64_t expert_stride;
+    const uint32_t *tiles;   // optional compact tile list built by the bucketing kernel
+    uint32_t *status;
+};
+
+// ---- small device helpers ---------------------------------------------------------------------
+__device__ __forceinline__ float half_bits_to_float(uint32_t h16) {
+    return __half2float(__ushort_as_half((unsigned short)h16));
+}
+
+// 2-byte-aligned little-endian loads (GGML blocks are only 2-byte aligned).
+__device__ __forceinline__ uint32_t ld_u16(const uint8_t *p) { return *reinterpret_cast<const uint16_t *>(p); }
+__device__ __forceinline__ uint32_t ld_u32_2(const uint8_t *p) {
+    const uint16_t *q = reinterpret_cast<const uint16_t *>(p);
+    return (uint32_t)q[0] | ((uint32_t)q[1] << 16);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Exact dequantisation of one element group, shared by the simple mat-vec and the mat-mat staging.
+// Q4_0: value = d*(nibble-8); Q8_0: d*q; Q6_K: (d*scale)*q  (all exact in f32).
+
+}  // namespace mlxn

@@ -1,0 +1,160 @@
+// Routing and glue kernels around the expert-routed matmul.
+//
+//   moe_map0           replaces kernel_mul_mm_id_map0_ne20_{1,8} (src/shaders/quantized_matmul_id_mm.metal:242-301):
+//                      per-expert count `htpe[e]` and list `hids[e, :]` of token*top_k+slot entries in
+//                      ascending token order (stable), for any top_k.
+//   moe_softmax_topk   replaces moe_softmax_topk_f32 (src/shaders/moe_softmax_topk.metal:27-148).
+//   silu_mul           replaces silu_mul_f32 (src/shaders/silu_mul.metal:17-30).
+//   moe_weighted_reduce replaces moe_weighted_reduce_f32 (src/shaders/moe_weighted_reduce.metal:33-66).
+#include "common.cuh"
+
+namespace mlxn {
+
+// One warp per expert.  The warp walks the tokens 32 at a time; each lane evaluates the upstream
+// selector for its token (sum of (slot+1) over slots whose id, truncated to 16 bits, equals the
+// expert), and a ballot + popcount prefix gives every selected token its position, so the list
+// order is the scan order.  grid ceil(n_experts/8), 256 threads.
+__global__ void __launch_bounds__(256) moe_map0_kernel(const uint32_t *ids, uint32_t n_tokens, uint32_t top_k,
+                                                       uint32_t n_experts, uint32_t hids_stride, uint32_t *htpe,
+                                                       int32_t *hids) {
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t e = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (e >= n_experts) return;
+    int32_t *row = hids + (size_t)e * hids_stride;
+    uint32_t n_all = 0;
+    for (uint32_t t0 = 0; t0 < n_tokens; t0 += 32) {
+        const uint32_t t = t0 + lane;
+        int sel = 0;
+        if (t < n_tokens) {
+            const uint32_t *p = ids + (size_t)t * top_k;
+            for (uint32_t s = 0; s < top_k; s++) sel += ((p[s] & 0xFFFFu) == (e & 0xFFFFu)) ? (int)(s + 1) : 0;
+        }
+        const uint32_t hit = __ballot_sync(0xffffffffu, sel > 0);
+        if (sel > 0) {
+            const uint32_t pos = n_all + __popc(hit & ((1u << lane) - 1u));
+            if (pos < hids_stride) row[pos] = (int32_t)(t * top_k) + sel - 1;
+        }
+        n_all += __popc(hit);
+    }
+    if (lane == 0) htpe[e] = n_all;
+}
+
+cudaError_t launch_moe_map0(const uint32_t *ids, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts,
+                            uint32_t hids_stride, uint32_t *htpe, int32_t *hids, cudaStream_t st) {
+    moe_map0_kernel<<<(n_experts + 7) / 8, 256, 0, st>>>(ids, n_tokens, top_k, n_experts, hids_stride, htpe, hids);
+    return cudaGetLastError();
+}
+
+// One CTA of tg = min(n_experts, 128) threads per token, same reduction trees as upstream so that
+// the probabilities (and therefore the selected ids) match its arithmetic.
+// dynamic shared memory: (2*tg + n_experts) floats.
+__global__ void moe_softmax_topk_kernel(const float *logits, uint32_t n_tokens, uint32_t n_experts, uint32_t top_k,
+                                        uint32_t *out_ids, float *out_w) {
+    extern __shared__ float sh[];
+    const uint32_t tg = blockDim.x, tid = threadIdx.x, tok = blockIdx.x;
+    if (tok >= n_tokens) return;
+    float *tg_max = sh, *tg_sum = sh + tg, *prob = sh + 2 * tg;
+    const float *lg = logits + (size_t)tok * n_experts;
+    float mx = -INFINITY;
+    for (uint32_t e = tid; e < n_experts; e += tg) {
+        const float v = lg[e];
+        if (v > mx) mx = v;
+    }
+    tg_max[tid] = mx;
+    __syncthreads();
+    for (uint32_t stride = tg / 2; stride > 0; stride >>= 1) {
+        if (tid < stride && tg_max[tid + stride] > tg_max[tid]) tg_max[tid] = tg_max[tid + stride];
+        __syncthreads();
+    }
+    const float gmax = tg_max[0];
+    float ls = 0.0f;
+    for (uint32_t e = tid; e < n_experts; e += tg) {
+        const float ev = expf(lg[e] - gmax);
+        prob[e] = ev;
+        ls += ev;
+    }
+    tg_sum[tid] = ls;
+    __syncthreads();
+    for (uint32_t stride = tg / 2; stride > 0; stride >>= 1) {
+        if (tid < stride) tg_sum[tid] += tg_sum[tid + stride];
+        __syncthreads();
+    }
+    const float gsum = tg_sum[0];
+    for (uint32_t e = tid; e < n_experts; e += tg) prob[e] = prob[e] / gsum;
+    __syncthreads();
+    if (tid == 0) {
+        float vals[64];
+        uint32_t idxs[64];
+        for (uint32_t k = 0; k < top_k; k++) {
+            vals[k] = -INFINITY;
+            idxs[k] = 0;
+        }
+        for (uint32_t e = 0; e < n_experts; e++) {
+            const float p = prob[e];
+            if (p <= vals[top_k - 1]) continue;
+            uint32_t ins = top_k - 1;
+            while (ins > 0 && p > vals[ins - 1]) ins--;
+            for (uint32_t k = top_k - 1; k > ins; k--) {
+                vals[k] = vals[k - 1];
+                idxs[k] = idxs[k - 1];
+            }
+            vals[ins] = p;
+            idxs[ins] = e;
+        }
+        float ts = 0.0f;
+        for (uint32_t k = 0; k < top_k; k++) ts += vals[k];
+        const float inv = ts > 1e-9f ? 1.0f / ts : 1.0f;
+        for (uint32_t k = 0; k < top_k; k++) {
+            out_ids[(size_t)tok * top_k + k] = idxs[k];
+            out_w[(size_t)tok * top_k + k] = vals[k] * inv;
+        }
+    }
+}
+
+cudaError_t launch_moe_softmax_topk(const float *logits, uint32_t n_tokens, uint32_t n_experts, uint32_t top_k,
+                                    uint32_t *out_ids, float *out_w, cudaStream_t st) {
+    const uint32_t tg = n_experts < 128 ? n_experts : 128;
+    const size_t smem = (2 * (size_t)tg + n_experts) * sizeof(float);
+    moe_softmax_topk_kernel<<<n_tokens, tg, smem, st>>>(logits, n_tokens, n_experts, top_k, out_ids, out_w);
+    return cudaGetLastError();
+}
+
+__global__ void silu_mul_kernel(const float *gate, const float *up, float *out, uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g = gate[i];
+    out[i] = g / (1.0f + expf(-g)) * up[i];
+}
+
+cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint32_t n, cudaStream_t st) {
+    silu_mul_kernel<<<(n + 255) / 256, 256, 0, st>>>(gate, up, out, n);
+    return cudaGetLastError();
+}
+
+__global__ void moe_weighted_reduce_kernel(const float *w, const float *y, const float *sh_logit, const float *y_shared,
+                                           const float *residual, float *out, uint32_t n_tokens, uint32_t top_k,
+                                           uint32_t h) {
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
+    if (c >= h || t >= n_tokens) return;
+    float acc = 0.0f;
+    for (uint32_t k = 0; k < top_k; k++) {
+        const size_t slot = (size_t)t * top_k + k;
+        acc += w[slot] * y[slot * h + c];
+    }
+    if (y_shared) {
+        const float gate = sh_logit ? 1.0f / (1.0f + expf(-sh_logit[t])) : 1.0f;
+        acc += gate * y_shared[(size_t)t * h + c];
+    }
+    if (residual) acc += residual[(size_t)t * h + c];
+    out[(size_t)t * h + c] = acc;
+}
+
+cudaError_t launch_moe_weighted_reduce(const float *w, const float *y, const float *sh_logit, const float *y_shared,
+                                       const float *residual, float *out, uint32_t n_tokens, uint32_t top_k, uint32_t h,
+                                       cudaStream_t st) {
+    dim3 grid((h + 255) / 256, n_tokens);
+    moe_weighted_reduce_kernel<<<grid, 256, 0, st>>>(w, y, sh_logit, y_shared, residual, out, n_tokens, top_k, h);
+    return cudaGetLastError();
+}
+
+}  // namespace mlxn

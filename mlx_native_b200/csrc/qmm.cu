@@ -1,0 +1,628 @@
+// Mat-mat kernels for GGML Q4_0 / Q8_0 / Q6_K weights (prefill path, m > 8), dense and grouped by expert.
+//
+// Replaces upstream kernel_mul_mm_*_tensor_f32 (src/shaders/quantized_matmul_mm_tensor.metal:170-343),
+// kernel_mul_mm_id_*_tensor_f32 (src/shaders/quantized_matmul_id_mm_tensor.metal:165-341) and the
+// simdgroup variants beside them.  Operand semantics are those of the upstream tensor path: weights
+// are dequantised in f32 and rounded once to f16, activations are rounded f32 -> f16, products are
+// accumulated in f32.
+//
+//   qmm_tc    tcgen05 kernel.  Per CTA one output tile of 128 weight rows x NT activation rows.
+//             Activations are packed once per call into f16 tiles already in the tensor core's
+//             K-major 128-byte-swizzled shared-memory layout (pack_x), so the GEMM fetches them with
+//             one bulk async copy per 64-wide K chunk.  Raw weight blocks are bulk-copied into a
+//             staging ring, eight warps dequantise them into the swizzled f16 A tile, one thread
+//             issues tcgen05.mma (M=128, N=NT, K=16) accumulating in tensor memory, and the same
+//             eight warps read the accumulator back with tcgen05.ld and store y.
+//   qmm_simt  plain CUDA-core tile kernel with the same operand rounding; used for shapes the
+//             tcgen05 kernel does not take and as an on-device cross-check.
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace mlxn {
+
+// =================================================================================================
+// element-wise dequantisation helpers
+// =================================================================================================
+// Exact value of element `e` of a weight row stored as raw GGML blocks (global memory).
+template <int T> __device__ __forceinline__ float dequant_elem(const uint8_t *row, uint32_t e) {
+    if constexpr (T == GT_Q4_0) {
+        const uint8_t *blk = row + 18u * (e >> 5);
+        const uint32_t i = e & 31u;
+        const uint32_t byte = blk[2 + (i & 15u)];
+        const int nib = (i < 16) ? (int)(byte & 15u) : (int)(byte >> 4);
+        return half_bits_to_float(ld_u16(blk)) * (float)(nib - 8);
+    } else if constexpr (T == GT_Q8_0) {
+        const uint8_t *blk = row + 34u * (e >> 5);
+        return half_bits_to_float(ld_u16(blk)) * (float)(int)(int8_t)blk[2 + (e & 31u)];
+    } else {
+        const uint8_t *blk = row + 210u * (e >> 8);
+        const uint32_t r = e & 255u, h = r >> 7, g = (r & 127u) >> 5, l = r & 31u;
+        const uint32_t qlb = blk[64 * h + 32 * (g & 1u) + l];
+        const uint32_t nib = (g < 2) ? (qlb & 15u) : (qlb >> 4);
+        const uint32_t hb = (blk[128 + 32 * h + l] >> (2 * g)) & 3u;
+        const int q = (int)(nib | (hb << 4)) - 32;
+        const float sc = (float)(int)(int8_t)blk[192 + 8 * h + (l >> 4) + 2 * g];
+        return half_bits_to_float(ld_u16(blk + 208)) * sc * (float)q;
+    }
+}
+
+__device__ __forceinline__ float round_f16(float v) { return __half2float(__float2half_rn(v)); }
+
+// =================================================================================================
+// qmm_simt: 64 x 64 output tile, K step 32, 256 threads, 4 x 4 outputs per thread
+// =================================================================================================
+// grid (ceil(rows/64), ceil(n/64), n_experts or 1)
+template <int T>
+__global__ void __launch_bounds__(256) qmm_simt_kernel(const QmmArgs a) {
+    __shared__ float Ws[32][64 + 1];
+    __shared__ float Xs[32][64 + 1];
+    __shared__ int32_t orow[64];  // output row of each tile row, -1 if none
+    __shared__ int32_t xrow[64];  // activation row of each tile row
+    const uint32_t tid = threadIdx.x;
+    const uint32_t r1 = blockIdx.x * 64, r0 = blockIdx.y * 64, e = blockIdx.z;
+    const uint8_t *w = a.w;
+    uint32_t nrows = a.m;
+    if (a.hids) {
+        nrows = a.htpe[e];
+        if (r1 >= nrows) return;
+        w += (size_t)e * a.expert_stride;
+    }
+    if (tid < 64) {
+        int32_t o = -1, xr = 0;
+        if (r1 + tid < nrows) {
+            if (a.hids) {
+                const int32_t id = a.hids[(size_t)e * a.hids_stride + r1 + tid];
+                if (id >= 0 && (uint32_t)id < a.total_rows) {
+                    o = id;
+                    xr = id / (int32_t)a.top_k;
+                }
+            } else {
+                o = (int32_t)(r1 + tid);
+                xr = o;
+            }
+        }
+        orow[tid] = o;
+        xrow[tid] = xr;
+    }
+    __syncthreads();
+    const size_t row_bytes = (size_t)(a.k / BlockTraits<T>::QK) * BlockTraits<T>::BYTES;
+    const uint32_t tx = tid & 15, ty = tid >> 4;  // tx: weight-row quad, ty: activation-row quad
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
+    for (uint32_t k0 = 0; k0 < a.k; k0 += 32) {
+        for (uint32_t idx = tid; idx < 64 * 32; idx += 256) {
+            const uint32_t rr = idx >> 5, kk = idx & 31u;
+            float wv = 0.0f, xv = 0.0f;
+            if (k0 + kk < a.k) {
+                if (r0 + rr < a.n) wv = round_f16(dequant_elem<T>(w + (size_t)(r0 + rr) * row_bytes, k0 + kk));
+                if (orow[rr] >= 0) xv = round_f16(a.x[(size_t)xrow[rr] * a.k + k0 + kk]);
+            }
+            Ws[kk][rr] = wv;
+            Xs[kk][rr] = xv;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < 32; kk++) {
+            float wv[4], xv[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                wv[i] = Ws[kk][tx * 4 + i];
+                xv[i] = Xs[kk][ty * 4 + i];
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int32_t o = orow[ty * 4 + i];
+        if (o < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const uint32_t col = r0 + tx * 4 + j;
+            if (col < a.n) a.y[(size_t)o * a.n + col] = acc[i][j];
+        }
+    }
+}
+
+// =================================================================================================
+// routed tile list + activation packing for qmm_tc
+// =================================================================================================
+// Scratch header written by build_tiles: [0] = number of tiles, [1..] = (expert, row-tile) pairs.
+__global__ void build_tiles_kernel(const uint32_t *htpe, uint32_t n_experts, uint32_t nt, uint32_t max_tiles,
+                                   uint32_t *tiles) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    uint32_t n = 0;
+    for (uint32_t e = 0; e < n_experts; e++) {
+        const uint32_t cnt = htpe[e];
+        for (uint32_t mt = 0; mt * nt < cnt && n < max_tiles; mt++) {
+            tiles[1 + 2 * n] = e;
+            tiles[2 + 2 * n] = mt;
+            n++;
+        }
+    }
+    tiles[0] = n;
+}
+
+// Packs activation rows into f16 tiles of NT rows x 64 columns laid out exactly as the tensor core
+// reads a K-major 128-byte-swizzled operand: row r, 16-byte chunk j (8 halves) of a tile lives at
+// (r/8)*1024 + (r%8)*128 + ((j ^ (r%8)) * 16).  Tile (t, kc) starts at ((t*nchunks + kc) * NT*128) bytes.
+// grid (nchunks, ntile_bound); 256 threads.
+template <int NT>
+__global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *xpack, uint32_t nchunks) {
+    const uint32_t kc = blockIdx.x, t = blockIdx.y;
+    uint32_t e = 0, mt = t, nrows = a.m;
+    if (a.hids) {
+        if (t >= a.tiles[0]) return;
+        e = a.tiles[1 + 2 * t];
+        mt = a.tiles[2 + 2 * t];
+        nrows = a.htpe[e];
+    }
+    uint8_t *tile = xpack + ((size_t)t * nchunks + kc) * (size_t)(NT * 128);
+    for (uint32_t q = threadIdx.x; q < NT * 8; q += 256) {
+        const uint32_t r = q >> 3, j = q & 7u;
+        const uint32_t row = mt * NT + r;
+        const uint32_t k0 = kc * 64 + 8 * j;
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (row < nrows && k0 < a.k) {
+            int64_t src = row;
+            if (a.hids) {
+                const int32_t id = a.hids[(size_t)e * a.hids_stride + row];
+                src = (id >= 0 && (uint32_t)id < a.total_rows) ? id / (int32_t)a.top_k : -1;
+            }
+            if (src >= 0) {
+                const float *xp = a.x + (size_t)src * a.k + k0;
+                float v[8];
+                if (k0 + 8 <= a.k && (((uintptr_t)xp) & 15u) == 0) {
+                    const float4 lo = __ldg(reinterpret_cast<const float4 *>(xp));
+                    const float4 hi = __ldg(reinterpret_cast<const float4 *>(xp) + 1);
+                    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+                    v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) v[i] = (k0 + i < a.k) ? xp[i] : 0.0f;
+                }
+                __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+                __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
+                out.x = *reinterpret_cast<uint32_t *>(&h0);
+                out.y = *reinterpret_cast<uint32_t *>(&h1);
+                out.z = *reinterpret_cast<uint32_t *>(&h2);
+                out.w = *reinterpret_cast<uint32_t *>(&h3);
+            }
+        }
+        *reinterpret_cast<uint4 *>(tile + (r >> 3) * 1024 + (r & 7u) * 128 + ((j ^ (r & 7u)) << 4)) = out;
+    }
+}
+
+// =================================================================================================
+// qmm_tc
+// =================================================================================================
+constexpr int kTcDequantWarps = 8;
+constexpr int kTcThreads = (kTcDequantWarps + 2) * 32;  // + producer warp + MMA warp
+constexpr int kTcRowsW = 128;                           // weight rows per tile (UMMA M)
+
+template <int T> struct TcTraits;
+template <> struct TcTraits<GT_Q4_0> { static constexpr int KR = 128; };  // raw-stage K extent
+template <> struct TcTraits<GT_Q8_0> { static constexpr int KR = 128; };
+template <> struct TcTraits<GT_Q6_K> { static constexpr int KR = 256; };
+
+__device__ __forceinline__ uint32_t lds32s(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds16s(uint32_t addr) {
+    uint32_t v;
+    asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ int lds_s8s(uint32_t addr) {
+    int v;
+    asm volatile("{ .reg .s16 t; ld.shared.s8 t, [%1]; cvt.s32.s16 %0, t; }" : "=r"(v) : "r"(addr));
+    return v;
+}
+// two logical 32-bit words at a 2-byte-aligned shared address
+__device__ __forceinline__ void lds_words2(uint32_t addr, uint32_t &w0, uint32_t &w1) {
+    const uint32_t al = addr & ~3u, sh = (addr & 2u) * 8u;
+    const uint32_t a = lds32s(al), b = lds32s(al + 4), c = lds32s(al + 8);
+    w0 = __funnelshift_rc(a, b, sh);
+    w1 = __funnelshift_rc(b, c, sh);
+}
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+
+// Eight consecutive elements [e, e+8) of one weight row segment in shared memory -> eight f16 values
+// (exact product rounded once to nearest even, as the upstream f32-then-cast staging does).
+template <int T> __device__ __forceinline__ uint4 dequant8(uint32_t seg, uint32_t e) {
+    uint4 out;
+    if constexpr (T == GT_Q4_0) {
+        const uint32_t o = seg + 18u * (e >> 5);
+        const uint32_t c8 = (e & 31u) >> 3;
+        const __half dh = __ushort_as_half((unsigned short)lds16s(o));
+        const __half2 d2 = __half2half2(dh);
+        uint32_t w0, w1;
+        lds_words2(o + 2 + 8 * (c8 & 1u), w0, w1);
+        if (c8 & 2u) {
+            w0 >>= 4;
+            w1 >>= 4;
+        }
+        w0 &= 0x0F0F0F0Fu;
+        w1 &= 0x0F0F0F0Fu;
+        const __half2 off = __float2half2_rn(1032.0f);  // 1024 + 8
+        out.x = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w0, 0x64646464u, 0x4140)), off), d2));
+        out.y = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w0, 0x64646464u, 0x4342)), off), d2));
+        out.z = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w1, 0x64646464u, 0x4140)), off), d2));
+        out.w = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w1, 0x64646464u, 0x4342)), off), d2));
+    } else if constexpr (T == GT_Q8_0) {
+        const uint32_t o = seg + 34u * (e >> 5);
+        const __half dh = __ushort_as_half((unsigned short)lds16s(o));
+        const __half2 d2 = __half2half2(dh);
+        uint32_t w0, w1;
+        lds_words2(o + 2 + (e & 31u), w0, w1);
+        w0 ^= 0x80808080u;
+        w1 ^= 0x80808080u;
+        const __half2 off = __float2half2_rn(1152.0f);  // 1024 + 128
+        out.x = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w0, 0x64646464u, 0x4140)), off), d2));
+        out.y = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w0, 0x64646464u, 0x4342)), off), d2));
+        out.z = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w1, 0x64646464u, 0x4140)), off), d2));
+        out.w = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w1, 0x64646464u, 0x4342)), off), d2));
+    } else {
+        const uint32_t o = seg + 210u * (e >> 8);
+        const uint32_t r = e & 255u, h = r >> 7, g = (r & 127u) >> 5, l = r & 31u;
+        uint32_t a0, a1, h0, h1;
+        lds_words2(o + 64 * h + 32 * (g & 1u) + l, a0, a1);
+        lds_words2(o + 128 + 32 * h + l, h0, h1);
+        if (g & 2u) {
+            a0 >>= 4;
+            a1 >>= 4;
+        }
+        const uint32_t u0 = (a0 & 0x0F0F0F0Fu) | (((h0 >> (2 * g)) & 0x03030303u) << 4);
+        const uint32_t u1 = (a1 & 0x0F0F0F0Fu) | (((h1 >> (2 * g)) & 0x03030303u) << 4);
+        const float ds = half_bits_to_float(lds16s(o + 208)) * (float)lds_s8s(o + 192 + 8 * h + (l >> 4) + 2 * g);
+        const float c = -160.0f * ds;  // exact: ds has <= 18 significant bits
+        // 128 + u spliced into an f32 mantissa; fma(128+u, ds, -160 ds) = ds*(u-32) exactly
+        const float f0 = fmaf(__uint_as_float(__byte_perm(u0, 0x43000000u, 0x7044)), ds, c);
+        const float f1 = fmaf(__uint_as_float(__byte_perm(u0, 0x43000000u, 0x7144)), ds, c);
+        const float f2 = fmaf(__uint_as_float(__byte_perm(u0, 0x43000000u, 0x7244)), ds, c);
+        const float f3 = fmaf(__uint_as_float(__byte_perm(u0, 0x43000000u, 0x7344)), ds, c);
+        const float f4 = fmaf(__uint_as_float(__byte_perm(u1, 0x43000000u, 0x7044)), ds, c);
+        const float f5 = fmaf(__uint_as_float(__byte_perm(u1, 0x43000000u, 0x7144)), ds, c);
+        const float f6 = fmaf(__uint_as_float(__byte_perm(u1, 0x43000000u, 0x7244)), ds, c);
+        const float f7 = fmaf(__uint_as_float(__byte_perm(u1, 0x43000000u, 0x7344)), ds, c);
+        out.x = h2_as_u32(__floats2half2_rn(f0, f1));
+        out.y = h2_as_u32(__floats2half2_rn(f2, f3));
+        out.z = h2_as_u32(__floats2half2_rn(f4, f5));
+        out.w = h2_as_u32(__floats2half2_rn(f6, f7));
+    }
+    return out;
+}
+
+struct TcCfg {
+    uint32_t nchunks;     // ceil(k / 64)
+    uint32_t stages;      // f16 operand ring depth
+    uint32_t seg_stride;  // bytes reserved per raw row segment
+    uint32_t a_off, b_off, raw_off;
+};
+
+// grid (ceil(n/128), tile count bound); kTcThreads threads; 1 CTA per SM (dynamic shared memory ~200 KiB).
+template <int T, int NT>
+__global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, const TcCfg c, const uint8_t *xpack) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES, KR = TcTraits<T>::KR;
+    constexpr int CPR = KR / 64;     // 64-wide chunks per raw stage
+    constexpr int kMaxS = 6;
+    __shared__ __align__(8) uint64_t a_full[kMaxS], b_full[kMaxS], ab_empty[kMaxS];
+    __shared__ __align__(8) uint64_t raw_full[2], raw_empty[2], acc_full;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile uint32_t abort_flag;
+    __shared__ int32_t orow[NT];
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t wt = blockIdx.x;              // weight-row tile
+    const uint32_t tt = blockIdx.y;              // token tile (dense) or tile-list index (routed)
+    uint32_t e = 0, mt = tt, nrows = a.m;
+    if (a.hids) {
+        if (tt >= a.tiles[0]) return;            // uniform for the whole CTA
+        e = a.tiles[1 + 2 * tt];
+        mt = a.tiles[2 + 2 * tt];
+        nrows = a.htpe[e];
+    }
+    const uint8_t *wbase = a.w + (size_t)e * a.expert_stride;
+    const uint32_t row_bytes = (a.k / QK) * BB;
+    const uint32_t n0 = wt * kTcRowsW;
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (uint32_t s = 0; s < c.stages; s++) {
+            mbar_init(&a_full[s], kTcDequantWarps);
+            mbar_init(&b_full[s], 1);
+            mbar_init(&ab_empty[s], 1);
+        }
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&raw_full[s], 1);
+            mbar_init(&raw_empty[s], kTcDequantWarps);
+        }
+        mbar_init(&acc_full, 1);
+        mbar_init_fence();
+    }
+    for (uint32_t i = tid; i < NT; i += kTcThreads) {
+        int32_t o = -1;
+        const uint32_t row = mt * NT + i;
+        if (row < nrows) {
+            if (a.hids) {
+                const int32_t id = a.hids[(size_t)e * a.hids_stride + row];
+                if (id >= 0 && (uint32_t)id < a.total_rows) o = id;
+            } else {
+                o = (int32_t)row;
+            }
+        }
+        orow[i] = o;
+    }
+    if (warp == kTcDequantWarps + 1) {  // MMA warp owns tensor memory
+        tmem_alloc(&tmem_base_s, NT);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_d = tmem_base_s;
+    const uint32_t smem_base = smem_u32(smem);
+    const uint32_t a_bytes = kTcRowsW * 128, b_bytes = NT * 128;
+    const uint32_t raw_stage_bytes = kTcRowsW * c.seg_stride;
+    const uint32_t nraw = (c.nchunks + CPR - 1) / CPR;
+
+    if (warp == kTcDequantWarps) {
+        // ======================= producer warp: bulk copies =======================
+        auto issue_raw = [&](uint32_t r) {
+            const uint32_t rs = r & 1u;
+            if (!mbar_wait(&raw_empty[rs], ((r >> 1) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) return false;
+            const uint32_t k0 = r * KR;
+            const uint32_t kb = min((uint32_t)KR, a.k - k0);
+            const uint32_t seg_bytes = (kb / QK) * BB;
+            const uint32_t rows = min((uint32_t)kTcRowsW, a.n - n0);
+            uint32_t total = 0;
+            for (uint32_t rr = lane; rr < rows; rr += 32) {
+                const uint8_t *src = wbase + (size_t)(n0 + rr) * row_bytes + (size_t)(k0 / QK) * BB;
+                total += ((uint32_t)((uintptr_t)src & 15u) + seg_bytes + 15u) & ~15u;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+            if (lane == 0) mbar_expect_tx(&raw_full[rs], total);
+            __syncwarp();
+            for (uint32_t rr = lane; rr < rows; rr += 32) {
+                const uint8_t *src = wbase + (size_t)(n0 + rr) * row_bytes + (size_t)(k0 / QK) * BB;
+                const uint32_t pre = (uint32_t)((uintptr_t)src & 15u);
+                bulk_g2s(smem + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride, src - pre,
+                         (pre + seg_bytes + 15u) & ~15u, &raw_full[rs]);
+            }
+            return true;
+        };
+        bool ok = issue_raw(0);
+        for (uint32_t kc = 0; ok && kc < c.nchunks; kc++) {
+            if (kc % CPR == 0 && kc / CPR + 1 < nraw) ok = issue_raw(kc / CPR + 1);
+            if (!ok) break;
+            const uint32_t s = kc % c.stages;
+            if (!mbar_wait(&ab_empty[s], ((kc / c.stages) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) break;
+            if (lane == 0) {
+                mbar_expect_tx(&b_full[s], b_bytes);
+                bulk_g2s(smem + c.b_off + s * b_bytes, xpack + ((size_t)tt * c.nchunks + kc) * (size_t)b_bytes, b_bytes,
+                         &b_full[s]);
+            }
+        }
+    } else if (warp == kTcDequantWarps + 1) {
+        // ======================= MMA warp: one thread issues tcgen05.mma =======================
+        constexpr uint32_t idesc = umma_idesc_f16(kTcRowsW, NT);
+        for (uint32_t kc = 0; kc < c.nchunks; kc++) {
+            const uint32_t s = kc % c.stages, ph = (kc / c.stages) & 1u;
+            if (!mbar_wait(&a_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT)) break;
+            if (!mbar_wait(&b_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT)) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint64_t ad = umma_desc_k_sw128(smem_base + c.a_off + s * a_bytes);
+                const uint64_t bd = umma_desc_k_sw128(smem_base + c.b_off + s * b_bytes);
+#pragma unroll
+                for (uint32_t kk = 0; kk < 4; kk++)
+                    umma_f16_ss(tmem_d, ad + 2 * kk, bd + 2 * kk, idesc, (kc | kk) != 0 ? 1u : 0u);
+                umma_commit(&ab_empty[s]);
+                if (kc + 1 == c.nchunks) umma_commit(&acc_full);
+            }
+            __syncwarp();
+        }
+    } else {
+        // ======================= dequantise warps, then epilogue =======================
+        for (uint32_t kc = 0; kc < c.nchunks; kc++) {
+            const uint32_t s = kc % c.stages;
+            const uint32_t r = kc / CPR, rs = r & 1u;
+            if (kc % CPR == 0 &&
+                !mbar_wait(&raw_full[rs], (r >> 1) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT))
+                break;
+            if (!mbar_wait(&ab_empty[s], ((kc / c.stages) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) break;
+            const uint32_t kvalid = min(64u, a.k - kc * 64);  // elements of this chunk inside K
+            const uint32_t raw = smem_base + c.raw_off + rs * raw_stage_bytes;
+            uint8_t *atile = smem + c.a_off + s * a_bytes;
+#pragma unroll
+            for (int i = 0; i < (kTcRowsW * 8) / (kTcDequantWarps * 32); i++) {
+                const uint32_t q = tid + i * (kTcDequantWarps * 32);
+                const uint32_t rr = q >> 3, j = q & 7u;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (8 * j < kvalid && n0 + rr < a.n) {
+                    const uint8_t *src = wbase + (size_t)(n0 + rr) * row_bytes + (size_t)((r * KR) / QK) * BB;
+                    const uint32_t seg = raw + rr * c.seg_stride + (uint32_t)((uintptr_t)src & 15u);
+                    v = dequant8<T>(seg, (kc % CPR) * 64 + 8 * j);
+                }
+                *reinterpret_cast<uint4 *>(atile + (rr >> 3) * 1024 + (rr & 7u) * 128 + ((j ^ (rr & 7u)) << 4)) = v;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&a_full[s]);
+                if (kc % CPR == CPR - 1 || kc + 1 == c.nchunks) mbar_arrive(&raw_empty[rs]);
+            }
+        }
+        // ---- epilogue: TMEM -> registers -> y ----
+        if (!abort_flag && mbar_wait(&acc_full, 0, &abort_flag, a.status, ST_WAIT_MMA_TIMEOUT)) {
+            tc_fence_after();
+            const uint32_t q4 = warp & 3u;           // tensor-memory lane quarter this warp may read
+            const uint32_t chalf = warp >> 2;        // column half
+            const uint32_t wrow = n0 + q4 * 32 + lane;
+            constexpr uint32_t kColsPerWarp = NT / 2;
+#pragma unroll 1
+            for (uint32_t c0 = 0; c0 < kColsPerWarp; c0 += 32) {
+                uint32_t v[32];
+                const uint32_t col = chalf * kColsPerWarp + c0;
+                tmem_ld_32x32(tmem_d + ((q4 * 32) << 16) + col, v);
+                tmem_ld_wait();
+                if (wrow < a.n) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int32_t o = orow[col + j];
+                        if (o >= 0) a.y[(size_t)o * a.n + wrow] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+        }
+    }
+    if (abort_flag) {  // let copies in flight land before the CTA's shared memory is released
+        for (int i = 0; i < 200; i++) __nanosleep(5000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kTcDequantWarps + 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_d, NT);
+    }
+}
+
+// =================================================================================================
+// host-side launchers
+// =================================================================================================
+static inline uint32_t round_up_u(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+// Bytes of scratch the tcgen05 path needs for one call (tile list + packed activations).
+size_t qmm_tc_scratch_bytes(const QmmArgs &a, uint32_t nt, bool routed) {
+    const uint32_t nchunks = (a.k + 63) / 64;
+    size_t tiles;
+    size_t header = 0;
+    if (routed) {
+        tiles = (size_t)a.total_rows / nt + a.n_experts;
+        if (tiles > a.total_rows) tiles = a.total_rows;
+        if (tiles == 0) tiles = 1;
+        header = ((1 + 2 * tiles) * 4 + 1023) / 1024 * 1024;
+    } else {
+        tiles = (a.m + nt - 1) / nt;
+    }
+    return header + tiles * nchunks * (size_t)nt * 128;
+}
+
+uint32_t qmm_tc_pick_nt(uint32_t rows_per_group, bool routed) {
+    if (routed) return 64;
+    return rows_per_group <= 64 ? 64 : rows_per_group <= 128 ? 128 : 256;
+}
+
+bool qmm_tc_supported(const QmmArgs &a) {
+    if (a.k % 32 != 0 || a.k < 32) return false;
+    if (((uintptr_t)a.w & 1u) || (a.expert_stride & 1u)) return false;
+    return true;
+}
+
+template <int T, int NT>
+static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaStream_t st, int *launches) {
+    constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES, KR = TcTraits<T>::KR;
+    TcCfg c{};
+    c.nchunks = (a.k + 63) / 64;
+    c.seg_stride = round_up_u((KR / QK) * BB + 15, 16) + 16;
+    const uint32_t a_bytes = kTcRowsW * 128, b_bytes = NT * 128;
+    const uint32_t raw_bytes = 2 * kTcRowsW * c.seg_stride;
+    const uint32_t limit = 220 * 1024;
+    uint32_t stages = (limit - raw_bytes) / (a_bytes + b_bytes);
+    if (stages > 6) stages = 6;
+    if (stages < 2) return cudaErrorInvalidConfiguration;
+    c.stages = stages;
+    c.a_off = 0;
+    c.b_off = stages * a_bytes;
+    c.raw_off = c.b_off + stages * b_bytes;
+    const size_t smem = (size_t)c.raw_off + raw_bytes;
+
+    size_t tiles;
+    uint8_t *xpack = scratch;
+    if (routed) {
+        tiles = (size_t)a.total_rows / NT + a.n_experts;
+        if (tiles > a.total_rows) tiles = a.total_rows;
+        if (tiles == 0) tiles = 1;
+        const size_t header = ((1 + 2 * tiles) * 4 + 1023) / 1024 * 1024;
+        uint32_t *tl = reinterpret_cast<uint32_t *>(scratch);
+        build_tiles_kernel<<<1, 32, 0, st>>>(a.htpe, a.n_experts, NT, (uint32_t)tiles, tl);
+        (*launches)++;
+        a.tiles = tl;
+        xpack = scratch + header;
+    } else {
+        tiles = (a.m + NT - 1) / NT;
+        a.tiles = nullptr;
+    }
+    {
+        dim3 grid(c.nchunks, (unsigned)tiles);
+        pack_x_kernel<NT><<<grid, 256, 0, st>>>(a, xpack, c.nchunks);
+        (*launches)++;
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(qmm_tc_kernel<T, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set[dev] = true;
+    }
+    dim3 grid((a.n + kTcRowsW - 1) / kTcRowsW, (unsigned)tiles);
+    qmm_tc_kernel<T, NT><<<grid, kTcThreads, smem, st>>>(a, c, xpack);
+    (*launches)++;
+    return cudaGetLastError();
+}
+
+template <int T> static cudaError_t launch_tc_t(const QmmArgs &a, bool routed, uint32_t nt, uint8_t *scratch, cudaStream_t st,
+                                                int *launches) {
+    switch (nt) {
+    case 64: return launch_tc_tn<T, 64>(a, routed, scratch, st, launches);
+    case 128: return launch_tc_tn<T, 128>(a, routed, scratch, st, launches);
+    case 256: return launch_tc_tn<T, 256>(a, routed, scratch, st, launches);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+// tcgen05 mat-mat.  `scratch` must hold qmm_tc_scratch_bytes(a, nt, routed) bytes, 1024-byte aligned.
+cudaError_t launch_qmm_tc(int ggml_type, const QmmArgs &a, bool routed, uint32_t nt, uint8_t *scratch, cudaStream_t st,
+                          int *launches) {
+    switch (ggml_type) {
+    case GT_Q4_0: return launch_tc_t<GT_Q4_0>(a, routed, nt, scratch, st, launches);
+    case GT_Q8_0: return launch_tc_t<GT_Q8_0>(a, routed, nt, scratch, st, launches);
+    case GT_Q6_K: return launch_tc_t<GT_Q6_K>(a, routed, nt, scratch, st, launches);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+template <int T> static cudaError_t launch_simt_t(const QmmArgs &a, bool routed, uint32_t max_rows, cudaStream_t st) {
+    dim3 grid((max_rows + 63) / 64, (a.n + 63) / 64, routed ? a.n_experts : 1);
+    qmm_simt_kernel<T><<<grid, 256, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+// CUDA-core mat-mat.  max_rows: a.m (dense) or the largest possible rows per expert (routed).
+cudaError_t launch_qmm_simt(int ggml_type, const QmmArgs &a, bool routed, uint32_t max_rows, cudaStream_t st) {
+    switch (ggml_type) {
+    case GT_Q4_0: return launch_simt_t<GT_Q4_0>(a, routed, max_rows, st);
+    case GT_Q8_0: return launch_simt_t<GT_Q8_0>(a, routed, max_rows, st);
+    case GT_Q6_K: return launch_simt_t<GT_Q6_K>(a, routed, max_rows, st);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace mlxn

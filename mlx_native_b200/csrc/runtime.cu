@@ -1,0 +1,1172 @@
+// CUDA runtime layer and C ABI of the library: device, buffers (HBM + lazily created pinned host
+// shadow), power-of-two buffer pool, kernel-name registry, stream-backed command encoder with CUDA
+// graph capture, global counters, and the host-side dispatchers of the quantized matmul path.
+// The dispatchers mirror upstream src/ops/quantized_matmul_ggml.rs and
+// src/ops/quantized_matmul_id_ggml.rs: same validation order, same messages, same routing rules.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "../../include/mlxn_b200.h"
+#include "common.cuh"
+
+namespace mlxn {
+cudaError_t launch_qmv(int ggml_type, const QmvArgs &a, bool want_stream, int sm_count, cudaStream_t st,
+                       const char **kname);
+cudaError_t launch_qmm_tc(int ggml_type, const QmmArgs &a, bool routed, uint32_t nt, uint8_t *scratch, cudaStream_t st,
+                          int *launches);
+cudaError_t launch_qmm_simt(int ggml_type, const QmmArgs &a, bool routed, uint32_t max_rows, cudaStream_t st);
+size_t qmm_tc_scratch_bytes(const QmmArgs &a, uint32_t nt, bool routed);
+uint32_t qmm_tc_pick_nt(uint32_t rows_per_group, bool routed);
+bool qmm_tc_supported(const QmmArgs &a);
+cudaError_t launch_moe_map0(const uint32_t *ids, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts,
+                            uint32_t hids_stride, uint32_t *htpe, int32_t *hids, cudaStream_t st);
+cudaError_t launch_moe_softmax_topk(const float *logits, uint32_t n_tokens, uint32_t n_experts, uint32_t top_k,
+                                    uint32_t *out_ids, float *out_w, cudaStream_t st);
+cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint32_t n, cudaStream_t st);
+cudaError_t launch_moe_weighted_reduce(const float *w, const float *y, const float *sh_logit, const float *y_shared,
+                                       const float *residual, float *out, uint32_t n_tokens, uint32_t top_k, uint32_t h,
+                                       cudaStream_t st);
+}  // namespace mlxn
+
+using namespace mlxn;
+
+// ------------------------------------------------------------------------------------------------
+// errors, counters, options
+// ------------------------------------------------------------------------------------------------
+static thread_local std::string g_last_error;
+static thread_local const char *g_last_kernel = "";
+
+static int fail(int status, const char *fmt, ...) {
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return status;
+}
+static int cuda_fail(cudaError_t e, const char *what) {
+    return fail(MLXN_COMMAND_BUFFER_ERROR, "Command buffer error: %s: %s", what, cudaGetErrorString(e));
+}
+#define CUDA_TRY(expr, what)                          \
+    do {                                              \
+        cudaError_t _e = (expr);                      \
+        if (_e != cudaSuccess) return cuda_fail(_e, what); \
+    } while (0)
+
+static std::atomic<uint64_t> g_dispatch{0}, g_sync{0}, g_cmd_buf{0}, g_barrier{0}, g_launches{0};
+
+static std::atomic<int> g_opt_qmv{-1}, g_opt_qmm{-1};  // -1 unset, 0 simple/simt, 1 stream/tc
+static bool opt_qmv_stream() {
+    int v = g_opt_qmv.load();
+    if (v < 0) {
+        const char *e = getenv("MLXN_QMV");
+        v = (e && strcmp(e, "simple") == 0) ? 0 : 1;
+        g_opt_qmv = v;
+    }
+    return v == 1;
+}
+static bool opt_qmm_tc() {
+    int v = g_opt_qmm.load();
+    if (v < 0) {
+        const char *e = getenv("MLXN_QMM");
+        v = (e && strcmp(e, "simt") == 0) ? 0 : 1;
+        g_opt_qmm = v;
+    }
+    return v == 1;
+}
+
+// ------------------------------------------------------------------------------------------------
+// handle types
+// ------------------------------------------------------------------------------------------------
+struct mlxn_device {
+    int ordinal;
+    int sm_count;
+    std::string name;
+};
+
+struct Storage {
+    std::atomic<int> refs{1};
+    int ordinal = 0;
+    void *dptr = nullptr;
+    size_t bytes = 0;
+    bool owned = true;
+    void *host = nullptr;      // pinned shadow, created on first host_map
+    bool host_newer = false;   // shadow holds data not yet uploaded
+    bool dev_newer = false;    // HBM holds data not yet reflected in the shadow
+    cudaStream_t last_stream = nullptr;  // stream of the last operation that touched the storage
+    bool has_last = false;
+    std::mutex mu;
+};
+
+static void storage_release(Storage *s) {
+    if (s->refs.fetch_sub(1) == 1) {
+        int prev = 0;
+        cudaGetDevice(&prev);
+        cudaSetDevice(s->ordinal);
+        if (s->owned && s->dptr) cudaFree(s->dptr);
+        if (s->host) cudaFreeHost(s->host);
+        cudaSetDevice(prev);
+        delete s;
+    }
+}
+
+struct mlxn_buffer {
+    std::atomic<int> refs{1};
+    Storage *st = nullptr;
+    size_t offset = 0;
+    size_t len = 0;
+    int dtype = MLXN_U8;
+    std::vector<size_t> shape;
+    uint8_t *dev() const { return static_cast<uint8_t *>(st->dptr) + offset; }
+};
+
+struct mlxn_pool {
+    std::map<size_t, std::vector<Storage *>> free_list;
+    std::vector<std::pair<size_t, Storage *>> in_use;
+};
+
+struct mlxn_registry {
+    std::set<std::string> cached;
+};
+
+struct mlxn_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t launches = 0;  // kernels recorded in the graph
+    uint64_t dispatches = 0;
+};
+
+struct mlxn_encoder {
+    mlxn_device *dev = nullptr;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev_start = nullptr, ev_end = nullptr;
+    bool started = false, committed = false, capturing = false;
+    uint64_t cap_launch0 = 0, cap_dispatch0 = 0;
+    std::vector<mlxn_buffer *> retained;
+    uint8_t *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    std::vector<void *> retired;  // outgrown scratch buffers, freed after the next wait
+    uint32_t *status_dev = nullptr;
+    uint32_t *status_host = nullptr;  // pinned
+};
+
+// ------------------------------------------------------------------------------------------------
+// small helpers
+// ------------------------------------------------------------------------------------------------
+extern "C" const char *mlxn_last_error_message(void) { return g_last_error.c_str(); }
+extern "C" int mlxn_status_is_transient(int status) { return status == MLXN_COMMAND_BUFFER_ERROR; }
+extern "C" const char *mlxn_last_kernel_name(void) { return g_last_kernel; }
+
+extern "C" size_t mlxn_dtype_size(int dtype) {
+    switch (dtype) {
+    case MLXN_F32: case MLXN_U32: case MLXN_I32: return 4;
+    case MLXN_F16: case MLXN_BF16: case MLXN_U16: return 2;
+    case MLXN_U8: return 1;
+    default: return 0;
+    }
+}
+extern "C" const char *mlxn_dtype_name(int dtype) {
+    static const char *names[] = {"f32", "f16", "bf16", "u8", "u16", "u32", "i32"};
+    return (dtype >= 0 && dtype <= MLXN_I32) ? names[dtype] : "?";
+}
+extern "C" uint32_t mlxn_ggml_block_values(int t) { return (t >= 0 && t <= MLXN_GGML_I16) ? ggml_qk(t) : 0; }
+extern "C" uint32_t mlxn_ggml_block_bytes(int t) { return (t >= 0 && t <= MLXN_GGML_I16) ? ggml_block_bytes(t) : 0; }
+static const char *ggml_name(int t) {
+    static const char *names[] = {"F32", "F16", "Q4_0", "Q8_0", "Q4_K", "Q5_K", "Q6_K", "I16"};
+    return (t >= 0 && t <= MLXN_GGML_I16) ? names[t] : "?";
+}
+
+extern "C" uint32_t mlxn_mm_id_routing_threshold(void) {
+    static std::once_flag once;
+    static uint32_t cached = MLXN_MM_ID_ROUTING_THRESHOLD;
+    std::call_once(once, [] {
+        const char *e = getenv("HF2Q_MM_ID_ROUTING_THRESHOLD");
+        if (e && *e) {
+            char *end = nullptr;
+            unsigned long v = strtoul(e, &end, 10);
+            if (end && *end == 0 && v <= 0xFFFFFFFFul) {
+                cached = (uint32_t)v;
+                if (getenv("MLX_LOG_TENSOR_PROBE"))
+                    fprintf(stderr, "[mlx-native] mm_id_routing_threshold: OVERRIDE via HF2Q_MM_ID_ROUTING_THRESHOLD=%u (default %u)\n",
+                            cached, MLXN_MM_ID_ROUTING_THRESHOLD);
+            }
+        }
+    });
+    return cached;
+}
+
+extern "C" int mlxn_set_option(const char *key, const char *value) {
+    if (!key || !value) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: option key/value must not be null");
+    if (strcmp(key, "qmv") == 0) {
+        if (strcmp(value, "stream") == 0) g_opt_qmv = 1;
+        else if (strcmp(value, "simple") == 0) g_opt_qmv = 0;
+        else return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: qmv must be 'stream' or 'simple'");
+        return MLXN_OK;
+    }
+    if (strcmp(key, "qmm") == 0) {
+        if (strcmp(value, "tc") == 0) g_opt_qmm = 1;
+        else if (strcmp(value, "simt") == 0) g_opt_qmm = 0;
+        else return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: qmm must be 'tc' or 'simt'");
+        return MLXN_OK;
+    }
+    return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: unknown option '%s'", key);
+}
+
+extern "C" uint64_t mlxn_dispatch_count(void) { return g_dispatch.load(); }
+extern "C" uint64_t mlxn_sync_count(void) { return g_sync.load(); }
+extern "C" uint64_t mlxn_cmd_buf_count(void) { return g_cmd_buf.load(); }
+extern "C" uint64_t mlxn_barrier_count(void) { return g_barrier.load(); }
+extern "C" uint64_t mlxn_kernel_launch_count(void) { return g_launches.load(); }
+extern "C" void mlxn_reset_counters(void) {
+    g_dispatch = 0;
+    g_sync = 0;
+    g_cmd_buf = 0;
+    g_barrier = 0;
+    g_launches = 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// device
+// ------------------------------------------------------------------------------------------------
+extern "C" int mlxn_device_create(int ordinal, mlxn_device **out) {
+    if (!out) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: out must not be null");
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(MLXN_DEVICE_NOT_FOUND, "No CUDA GPU device found — an NVIDIA B200 (sm_100a) is required");
+    }
+    if (ordinal < 0) {
+        if (cudaGetDevice(&ordinal) != cudaSuccess) ordinal = 0;
+    }
+    if (ordinal >= count) return fail(MLXN_DEVICE_NOT_FOUND, "No CUDA GPU device with ordinal %d (found %d)", ordinal, count);
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, ordinal) != cudaSuccess)
+        return fail(MLXN_DEVICE_NOT_FOUND, "No CUDA GPU device found — cannot query device %d", ordinal);
+    if (prop.major != 10)
+        return fail(MLXN_DEVICE_NOT_FOUND, "Device %d (%s, sm_%d%d) is not a Blackwell sm_100 GPU; this library is built for sm_100a only",
+                    ordinal, prop.name, prop.major, prop.minor);
+    cudaSetDevice(ordinal);
+    auto *d = new mlxn_device{ordinal, prop.multiProcessorCount, prop.name};
+    if (getenv("MLX_NATIVE_LOG_INIT")) fprintf(stderr, "[mlx-native] device %d: %s, %d SMs\n", ordinal, prop.name, prop.multiProcessorCount);
+    *out = d;
+    return MLXN_OK;
+}
+extern "C" void mlxn_device_destroy(mlxn_device *dev) { delete dev; }
+extern "C" const char *mlxn_device_name(const mlxn_device *dev) { return dev ? dev->name.c_str() : ""; }
+extern "C" int mlxn_device_ordinal(const mlxn_device *dev) { return dev ? dev->ordinal : -1; }
+extern "C" int mlxn_device_sm_count(const mlxn_device *dev) { return dev ? dev->sm_count : 0; }
+
+// ------------------------------------------------------------------------------------------------
+// buffers
+// ------------------------------------------------------------------------------------------------
+static mlxn_buffer *make_buffer(Storage *st, size_t offset, size_t len, int dtype, const size_t *shape, size_t rank) {
+    auto *b = new mlxn_buffer();
+    b->st = st;
+    b->offset = offset;
+    b->len = len;
+    b->dtype = dtype;
+    if (shape) b->shape.assign(shape, shape + rank);
+    return b;
+}
+
+static int alloc_storage(mlxn_device *dev, size_t byte_len, bool zero, Storage **out) {
+    cudaSetDevice(dev->ordinal);
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, byte_len);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(MLXN_BUFFER_ALLOCATION_ERROR, "Failed to allocate device buffer of %zu bytes", byte_len);
+    }
+    if (zero) {
+        e = cudaMemset(p, 0, byte_len);
+        if (e != cudaSuccess) {
+            cudaFree(p);
+            return cuda_fail(e, "zero-fill");
+        }
+    }
+    auto *s = new Storage();
+    s->ordinal = dev->ordinal;
+    s->dptr = p;
+    s->bytes = byte_len;
+    *out = s;
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_buffer_alloc(mlxn_device *dev, size_t byte_len, int dtype, const size_t *shape, size_t rank,
+                                 mlxn_buffer **out) {
+    if (!dev || !out) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: device and out must not be null");
+    if (byte_len == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: Buffer byte length must be > 0");
+    if (mlxn_dtype_size(dtype) == 0) return fail(MLXN_UNSUPPORTED_DTYPE, "Unsupported dtype: %d", dtype);
+    Storage *s = nullptr;
+    int rc = alloc_storage(dev, byte_len, true, &s);
+    if (rc) return rc;
+    *out = make_buffer(s, 0, byte_len, dtype, shape, rank);
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_buffer_wrap(mlxn_device *dev, void *device_ptr, size_t byte_len, int dtype, const size_t *shape,
+                                size_t rank, mlxn_buffer **out) {
+    if (!dev || !out || !device_ptr) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: device, pointer and out must not be null");
+    if (byte_len == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: Buffer byte length must be > 0");
+    if (mlxn_dtype_size(dtype) == 0) return fail(MLXN_UNSUPPORTED_DTYPE, "Unsupported dtype: %d", dtype);
+    auto *s = new Storage();
+    s->ordinal = dev->ordinal;
+    s->dptr = device_ptr;
+    s->bytes = byte_len;
+    s->owned = false;
+    *out = make_buffer(s, 0, byte_len, dtype, shape, rank);
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_buffer_slice_view(mlxn_buffer *buf, uint64_t byte_offset, size_t n_elements, mlxn_buffer **out) {
+    if (!buf || !out) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: buffer and out must not be null");
+    const size_t bytes = n_elements * mlxn_dtype_size(buf->dtype);
+    if (byte_offset > buf->len || bytes > buf->len - byte_offset)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: slice_view [%llu, +%zu) exceeds buffer of %zu bytes",
+                    (unsigned long long)byte_offset, bytes, buf->len);
+    buf->st->refs.fetch_add(1);
+    size_t shp = n_elements;
+    *out = make_buffer(buf->st, buf->offset + (size_t)byte_offset, bytes, buf->dtype, &shp, 1);
+    return MLXN_OK;
+}
+
+extern "C" void mlxn_buffer_retain(mlxn_buffer *buf) {
+    if (buf) buf->refs.fetch_add(1);
+}
+extern "C" void mlxn_buffer_release(mlxn_buffer *buf) {
+    if (!buf) return;
+    if (buf->refs.fetch_sub(1) == 1) {
+        storage_release(buf->st);
+        delete buf;
+    }
+}
+extern "C" int mlxn_buffer_dtype(const mlxn_buffer *buf) { return buf->dtype; }
+extern "C" size_t mlxn_buffer_rank(const mlxn_buffer *buf) { return buf->shape.size(); }
+extern "C" size_t mlxn_buffer_shape(const mlxn_buffer *buf, size_t axis) { return axis < buf->shape.size() ? buf->shape[axis] : 0; }
+extern "C" size_t mlxn_buffer_byte_len(const mlxn_buffer *buf) { return buf->len; }
+extern "C" size_t mlxn_buffer_element_count(const mlxn_buffer *buf) { return buf->len / mlxn_dtype_size(buf->dtype); }
+extern "C" uint64_t mlxn_buffer_byte_offset(const mlxn_buffer *buf) { return buf->offset; }
+extern "C" void *mlxn_buffer_device_ptr(const mlxn_buffer *buf) { return buf->dev(); }
+
+// wait for whatever touched the storage last (device work or an upload still reading the shadow)
+static int storage_quiesce(Storage *s) {
+    if (s->has_last) {
+        CUDA_TRY(cudaStreamSynchronize(s->last_stream), "stream synchronize");
+        s->has_last = false;
+    }
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_buffer_host_map(mlxn_buffer *buf, int write, void **host_ptr) {
+    if (!buf || !host_ptr) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: buffer and host_ptr must not be null");
+    Storage *s = buf->st;
+    std::lock_guard<std::mutex> lk(s->mu);
+    cudaSetDevice(s->ordinal);
+    int rc = storage_quiesce(s);
+    if (rc) return rc;
+    if (!s->host) {
+        CUDA_TRY(cudaHostAlloc(&s->host, s->bytes, cudaHostAllocDefault), "pinned host allocation");
+        s->dev_newer = true;  // HBM holds the (zero-filled or wrapped) contents
+    }
+    if (s->dev_newer) {
+        CUDA_TRY(cudaMemcpy(s->host, s->dptr, s->bytes, cudaMemcpyDeviceToHost), "device-to-host copy");
+        s->dev_newer = false;
+    }
+    if (write) s->host_newer = true;
+    *host_ptr = static_cast<uint8_t *>(s->host) + buf->offset;
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_buffer_upload(mlxn_buffer *buf, const void *src, size_t byte_len, size_t dst_offset) {
+    if (!buf || !src) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: buffer and src must not be null");
+    if (dst_offset > buf->len || byte_len > buf->len - dst_offset)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: upload of %zu bytes at %zu exceeds buffer of %zu bytes", byte_len, dst_offset, buf->len);
+    Storage *s = buf->st;
+    std::lock_guard<std::mutex> lk(s->mu);
+    cudaSetDevice(s->ordinal);
+    int rc = storage_quiesce(s);
+    if (rc) return rc;
+    if (s->host_newer) {  // flush pending shadow writes first so they are not lost
+        CUDA_TRY(cudaMemcpy(s->dptr, s->host, s->bytes, cudaMemcpyHostToDevice), "host-to-device copy");
+        s->host_newer = false;
+    }
+    CUDA_TRY(cudaMemcpy(buf->dev() + dst_offset, src, byte_len, cudaMemcpyHostToDevice), "host-to-device copy");
+    if (s->host) s->dev_newer = true;
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_buffer_download(mlxn_buffer *buf, void *dst, size_t byte_len, size_t src_offset) {
+    if (!buf || !dst) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: buffer and dst must not be null");
+    if (src_offset > buf->len || byte_len > buf->len - src_offset)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: download of %zu bytes at %zu exceeds buffer of %zu bytes", byte_len, src_offset, buf->len);
+    Storage *s = buf->st;
+    std::lock_guard<std::mutex> lk(s->mu);
+    cudaSetDevice(s->ordinal);
+    int rc = storage_quiesce(s);
+    if (rc) return rc;
+    if (s->host_newer) {
+        CUDA_TRY(cudaMemcpy(s->dptr, s->host, s->bytes, cudaMemcpyHostToDevice), "host-to-device copy");
+        s->host_newer = false;
+    }
+    CUDA_TRY(cudaMemcpy(dst, buf->dev() + src_offset, byte_len, cudaMemcpyDeviceToHost), "device-to-host copy");
+    return MLXN_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// pool
+// ------------------------------------------------------------------------------------------------
+static size_t bucket_size(size_t n) {
+    size_t b = 1;
+    while (b < n) b <<= 1;
+    return b;
+}
+extern "C" int mlxn_pool_create(mlxn_pool **out) {
+    if (!out) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: out must not be null");
+    *out = new mlxn_pool();
+    return MLXN_OK;
+}
+extern "C" void mlxn_pool_clear(mlxn_pool *pool) {
+    if (!pool) return;
+    for (auto &kv : pool->free_list)
+        for (Storage *s : kv.second) storage_release(s);
+    pool->free_list.clear();
+}
+extern "C" void mlxn_pool_destroy(mlxn_pool *pool) {
+    if (!pool) return;
+    mlxn_pool_clear(pool);
+    for (auto &p : pool->in_use) storage_release(p.second);
+    delete pool;
+}
+extern "C" int mlxn_pool_alloc(mlxn_pool *pool, mlxn_device *dev, size_t byte_len, int dtype, const size_t *shape,
+                               size_t rank, mlxn_buffer **out) {
+    if (!pool || !dev || !out) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: pool, device and out must not be null");
+    if (byte_len == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: Buffer byte length must be > 0");
+    if (mlxn_dtype_size(dtype) == 0) return fail(MLXN_UNSUPPORTED_DTYPE, "Unsupported dtype: %d", dtype);
+    const size_t bucket = bucket_size(byte_len);
+    Storage *s = nullptr;
+    auto it = pool->free_list.find(bucket);
+    if (it != pool->free_list.end() && !it->second.empty()) {
+        s = it->second.back();
+        it->second.pop_back();
+    } else {
+        int rc = alloc_storage(dev, bucket, true, &s);
+        if (rc) return rc;
+    }
+    s->refs.fetch_add(1);  // the pool's own reference (returned to the free list by reset)
+    pool->in_use.emplace_back(bucket, s);
+    *out = make_buffer(s, 0, bucket, dtype, shape, rank);
+    return MLXN_OK;
+}
+extern "C" int mlxn_pool_release(mlxn_pool *pool, mlxn_buffer *buf) {
+    if (!pool || !buf) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: pool and buffer must not be null");
+    const size_t bucket = bucket_size(buf->st->bytes);
+    buf->st->refs.fetch_add(1);
+    pool->free_list[bucket].push_back(buf->st);
+    mlxn_buffer_release(buf);
+    return MLXN_OK;
+}
+extern "C" void mlxn_pool_reset(mlxn_pool *pool) {
+    if (!pool) return;
+    for (auto &p : pool->in_use) pool->free_list[p.first].push_back(p.second);
+    pool->in_use.clear();
+}
+extern "C" int mlxn_pool_register_existing(mlxn_pool *pool, mlxn_device *dev, mlxn_buffer *buf) {
+    if (!pool || !dev || !buf) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: pool, device and buffer must not be null");
+    if (buf->st->ordinal != dev->ordinal)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: MlxBufferPool cannot register a buffer from a different device");
+    return MLXN_OK;  // residency sets have no CUDA counterpart: device memory is always resident
+}
+extern "C" size_t mlxn_pool_free_count(const mlxn_pool *pool) {
+    size_t n = 0;
+    for (auto &kv : pool->free_list) n += kv.second.size();
+    return n;
+}
+extern "C" size_t mlxn_pool_free_bytes(const mlxn_pool *pool) {
+    size_t n = 0;
+    for (auto &kv : pool->free_list) n += kv.first * kv.second.size();
+    return n;
+}
+extern "C" size_t mlxn_pool_in_use_count(const mlxn_pool *pool) { return pool->in_use.size(); }
+
+// ------------------------------------------------------------------------------------------------
+// registry
+// ------------------------------------------------------------------------------------------------
+static const char *const kKernelNames[] = {
+    "kernel_mul_mv_q4_0_f32", "kernel_mul_mv_q8_0_f32", "kernel_mul_mv_q6_K_f32",
+    "kernel_mul_mm_q4_0_f32", "kernel_mul_mm_q8_0_f32", "kernel_mul_mm_q6_K_f32",
+    "kernel_mul_mm_q4_0_tensor_f32", "kernel_mul_mm_q8_0_tensor_f32", "kernel_mul_mm_q6_K_tensor_f32",
+    "kernel_mul_mv_id_q4_0_f32", "kernel_mul_mv_id_q8_0_f32", "kernel_mul_mv_id_q6_K_f32",
+    "kernel_mul_mm_id_map0_ne20_1", "kernel_mul_mm_id_map0_ne20_8",
+    "kernel_mul_mm_id_q4_0_f32", "kernel_mul_mm_id_q8_0_f32", "kernel_mul_mm_id_q6_K_f32",
+    "kernel_mul_mm_id_q4_0_tensor_f32", "kernel_mul_mm_id_q8_0_tensor_f32", "kernel_mul_mm_id_q6_K_tensor_f32",
+    "moe_softmax_topk_f32", "moe_weighted_reduce_f32", "silu_mul_f32",
+};
+static bool known_kernel(const char *name) {
+    for (const char *k : kKernelNames)
+        if (strcmp(k, name) == 0) return true;
+    return false;
+}
+extern "C" int mlxn_registry_create(mlxn_registry **out) {
+    if (!out) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: out must not be null");
+    *out = new mlxn_registry();
+    return MLXN_OK;
+}
+extern "C" void mlxn_registry_destroy(mlxn_registry *reg) { delete reg; }
+extern "C" int mlxn_registry_get_pipeline(mlxn_registry *reg, mlxn_device *dev, const char *name) {
+    if (!reg || !name) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: registry and name must not be null");
+    (void)dev;
+    if (!known_kernel(name)) return fail(MLXN_KERNEL_NOT_FOUND, "Kernel not found: %s", name);
+    reg->cached.insert(name);
+    return MLXN_OK;
+}
+extern "C" int mlxn_registry_is_cached(const mlxn_registry *reg, const char *name) {
+    return reg && name && reg->cached.count(name) ? 1 : 0;
+}
+extern "C" size_t mlxn_registry_cached_count(const mlxn_registry *reg) { return reg ? reg->cached.size() : 0; }
+extern "C" size_t mlxn_registry_source_count(const mlxn_registry *) { return sizeof(kKernelNames) / sizeof(kKernelNames[0]); }
+
+static int touch_kernel(mlxn_registry *reg, mlxn_device *dev, const char *name) {
+    if (!reg) return MLXN_OK;
+    return mlxn_registry_get_pipeline(reg, dev, name);
+}
+
+// ------------------------------------------------------------------------------------------------
+// encoder
+// ------------------------------------------------------------------------------------------------
+extern "C" int mlxn_encoder_create(mlxn_device *dev, mlxn_encoder **out) {
+    if (!dev || !out) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: device and out must not be null");
+    cudaSetDevice(dev->ordinal);
+    auto *e = new mlxn_encoder();
+    e->dev = dev;
+    cudaError_t err = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking);
+    if (err == cudaSuccess) err = cudaEventCreate(&e->ev_start);
+    if (err == cudaSuccess) err = cudaEventCreate(&e->ev_end);
+    if (err == cudaSuccess) err = cudaMalloc((void **)&e->status_dev, 4);
+    if (err == cudaSuccess) err = cudaMemset(e->status_dev, 0, 4);
+    if (err == cudaSuccess) err = cudaHostAlloc((void **)&e->status_host, 4, cudaHostAllocDefault);
+    if (err != cudaSuccess) {
+        if (e->stream) cudaStreamDestroy(e->stream);
+        if (e->ev_start) cudaEventDestroy(e->ev_start);
+        if (e->ev_end) cudaEventDestroy(e->ev_end);
+        if (e->status_dev) cudaFree(e->status_dev);
+        delete e;
+        return cuda_fail(err, "encoder creation");
+    }
+    *e->status_host = 0;
+    g_cmd_buf.fetch_add(1);
+    *out = e;
+    return MLXN_OK;
+}
+
+static void encoder_release_retained(mlxn_encoder *e) {
+    for (mlxn_buffer *b : e->retained) mlxn_buffer_release(b);
+    e->retained.clear();
+    for (void *p : e->retired) cudaFree(p);
+    e->retired.clear();
+}
+
+extern "C" void mlxn_encoder_destroy(mlxn_encoder *enc) {
+    if (!enc) return;
+    cudaSetDevice(enc->dev->ordinal);
+    cudaStreamSynchronize(enc->stream);
+    encoder_release_retained(enc);
+    if (enc->scratch) cudaFree(enc->scratch);
+    cudaFree(enc->status_dev);
+    cudaFreeHost(enc->status_host);
+    cudaEventDestroy(enc->ev_start);
+    cudaEventDestroy(enc->ev_end);
+    cudaStreamDestroy(enc->stream);
+    delete enc;
+}
+
+extern "C" void *mlxn_encoder_stream(mlxn_encoder *enc) { return enc ? (void *)enc->stream : nullptr; }
+
+extern "C" int mlxn_encoder_memory_barrier(mlxn_encoder *enc) {
+    if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
+    g_barrier.fetch_add(1);  // one stream per encoder: operations already run in encode order
+    return MLXN_OK;
+}
+
+static int encoder_begin_work(mlxn_encoder *e) {
+    cudaSetDevice(e->dev->ordinal);
+    if (!e->started && !e->capturing) {
+        CUDA_TRY(cudaEventRecord(e->ev_start, e->stream), "event record");
+        e->started = true;
+        e->committed = false;
+    }
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_encoder_commit(mlxn_encoder *enc) {
+    if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
+    if (enc->capturing) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: commit while a capture is open");
+    cudaSetDevice(enc->dev->ordinal);
+    if (!enc->started) {
+        CUDA_TRY(cudaEventRecord(enc->ev_start, enc->stream), "event record");
+        enc->started = true;
+    }
+    CUDA_TRY(cudaMemcpyAsync(enc->status_host, enc->status_dev, 4, cudaMemcpyDeviceToHost, enc->stream), "status copy");
+    CUDA_TRY(cudaEventRecord(enc->ev_end, enc->stream), "event record");
+    enc->committed = true;
+    return MLXN_OK;
+}
+
+static const char *status_text(uint32_t s) {
+    switch (s) {
+    case ST_WAIT_FULL_TIMEOUT: return "a kernel gave up waiting for data to arrive in shared memory";
+    case ST_WAIT_EMPTY_TIMEOUT: return "a kernel gave up waiting for a pipeline stage to be released";
+    case ST_WAIT_MMA_TIMEOUT: return "a kernel gave up waiting for the tensor cores";
+    case ST_WAIT_TMEM_TIMEOUT: return "a kernel gave up waiting for tensor memory";
+    default: return "a kernel reported an error";
+    }
+}
+
+extern "C" int mlxn_encoder_wait_until_completed(mlxn_encoder *enc) {
+    if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
+    cudaSetDevice(enc->dev->ordinal);
+    g_sync.fetch_add(1);
+    cudaError_t e = enc->committed ? cudaEventSynchronize(enc->ev_end) : cudaStreamSynchronize(enc->stream);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    encoder_release_retained(enc);
+    enc->started = false;
+    if (e != cudaSuccess) return cuda_fail(e, "GPU execution");
+    if (enc->committed && *enc->status_host != 0) {
+        const uint32_t s = *enc->status_host;
+        *enc->status_host = 0;
+        cudaMemsetAsync(enc->status_dev, 0, 4, enc->stream);
+        return fail(MLXN_COMMAND_BUFFER_ERROR, "Command buffer error: %s (status %u)", status_text(s), s);
+    }
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_encoder_commit_and_wait(mlxn_encoder *enc) {
+    int rc = mlxn_encoder_commit(enc);
+    if (rc) return rc;
+    return mlxn_encoder_wait_until_completed(enc);
+}
+
+extern "C" int mlxn_encoder_commit_wait_with_gpu_time(mlxn_encoder *enc, double *gpu_seconds) {
+    int rc = mlxn_encoder_commit(enc);
+    if (rc) return rc;
+    rc = mlxn_encoder_wait_until_completed(enc);
+    if (rc) return rc;
+    float ms = 0.0f;
+    CUDA_TRY(cudaEventElapsedTime(&ms, enc->ev_start, enc->ev_end), "event elapsed time");
+    if (gpu_seconds) *gpu_seconds = (double)ms * 1e-3;
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_encoder_begin_capture(mlxn_encoder *enc) {
+    if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
+    if (enc->capturing) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: a capture is already open");
+    cudaSetDevice(enc->dev->ordinal);
+    CUDA_TRY(cudaStreamBeginCapture(enc->stream, cudaStreamCaptureModeRelaxed), "begin capture");
+    enc->capturing = true;
+    enc->cap_launch0 = g_launches.load();
+    enc->cap_dispatch0 = g_dispatch.load();
+    return MLXN_OK;
+}
+extern "C" int mlxn_encoder_end_capture(mlxn_encoder *enc, mlxn_graph **out) {
+    if (!enc || !out) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder and out must not be null");
+    if (!enc->capturing) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: no capture is open");
+    cudaSetDevice(enc->dev->ordinal);
+    enc->capturing = false;
+    auto *g = new mlxn_graph();
+    cudaError_t e = cudaStreamEndCapture(enc->stream, &g->graph);
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
+    if (e != cudaSuccess) {
+        if (g->graph) cudaGraphDestroy(g->graph);
+        delete g;
+        return cuda_fail(e, "end capture");
+    }
+    g->launches = g_launches.load() - enc->cap_launch0;
+    g->dispatches = g_dispatch.load() - enc->cap_dispatch0;
+    // recording is not running: take the recorded work back out of the global counters
+    g_launches.fetch_sub(g->launches);
+    g_dispatch.fetch_sub(g->dispatches);
+    *out = g;
+    return MLXN_OK;
+}
+extern "C" int mlxn_graph_launch(mlxn_graph *graph, mlxn_encoder *enc) {
+    if (!graph || !enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: graph and encoder must not be null");
+    int rc = encoder_begin_work(enc);
+    if (rc) return rc;
+    CUDA_TRY(cudaGraphLaunch(graph->exec, enc->stream), "graph launch");
+    g_launches.fetch_add(graph->launches);
+    g_dispatch.fetch_add(graph->dispatches);
+    return MLXN_OK;
+}
+extern "C" void mlxn_graph_destroy(mlxn_graph *graph) {
+    if (!graph) return;
+    if (graph->exec) cudaGraphExecDestroy(graph->exec);
+    if (graph->graph) cudaGraphDestroy(graph->graph);
+    delete graph;
+}
+
+// Grows the encoder's scratch arena (kept for its lifetime; an outgrown arena is freed at the next wait).
+static int encoder_scratch(mlxn_encoder *e, size_t bytes, uint8_t **out) {
+    if (bytes > e->scratch_bytes) {
+        const size_t want = bucket_size(bytes < (1u << 20) ? (1u << 20) : bytes);
+        void *p = nullptr;
+        cudaError_t err = cudaMalloc(&p, want);
+        if (err != cudaSuccess) {
+            cudaGetLastError();
+            return fail(MLXN_BUFFER_ALLOCATION_ERROR, "Failed to allocate device buffer of %zu bytes", want);
+        }
+        if (e->scratch) e->retired.push_back(e->scratch);
+        e->scratch = static_cast<uint8_t *>(p);
+        e->scratch_bytes = want;
+    }
+    *out = e->scratch;
+    return MLXN_OK;
+}
+
+// Binds a buffer to the encoder: uploads a newer host shadow on the encoder's stream, records the
+// stream as the storage's last user, and keeps the buffer alive until the encoder's next wait.
+static int bind(mlxn_encoder *e, mlxn_buffer *b, bool is_output) {
+    Storage *s = b->st;
+    std::lock_guard<std::mutex> lk(s->mu);
+    if (s->ordinal != e->dev->ordinal)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: buffer lives on device %d, encoder on device %d", s->ordinal, e->dev->ordinal);
+    if (s->has_last && s->last_stream != e->stream) {
+        CUDA_TRY(cudaStreamSynchronize(s->last_stream), "stream synchronize");
+    }
+    if (s->host_newer) {
+        CUDA_TRY(cudaMemcpyAsync(s->dptr, s->host, s->bytes, cudaMemcpyHostToDevice, e->stream), "host-to-device copy");
+        s->host_newer = false;
+    }
+    if (is_output && s->host) s->dev_newer = true;
+    s->last_stream = e->stream;
+    s->has_last = true;
+    b->refs.fetch_add(1);
+    e->retained.push_back(b);
+    return MLXN_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// quantized_matmul_ggml
+// ------------------------------------------------------------------------------------------------
+static const char *mv_kernel_name(int t) {
+    return t == GT_Q4_0 ? "kernel_mul_mv_q4_0_f32" : t == GT_Q8_0 ? "kernel_mul_mv_q8_0_f32" : "kernel_mul_mv_q6_K_f32";
+}
+static const char *mm_kernel_name(int t) {
+    return t == GT_Q4_0 ? "kernel_mul_mm_q4_0_tensor_f32" : t == GT_Q8_0 ? "kernel_mul_mm_q8_0_tensor_f32" : "kernel_mul_mm_q6_K_tensor_f32";
+}
+static const char *mv_id_kernel_name(int t) {
+    return t == GT_Q4_0 ? "kernel_mul_mv_id_q4_0_f32" : t == GT_Q8_0 ? "kernel_mul_mv_id_q8_0_f32" : "kernel_mul_mv_id_q6_K_f32";
+}
+static const char *mm_id_kernel_name(int t) {
+    return t == GT_Q4_0 ? "kernel_mul_mm_id_q4_0_tensor_f32" : t == GT_Q8_0 ? "kernel_mul_mm_id_q8_0_tensor_f32" : "kernel_mul_mm_id_q6_K_tensor_f32";
+}
+
+static int check_handles(mlxn_encoder *enc, mlxn_device *dev, std::initializer_list<const void *> ptrs) {
+    if (!enc || !dev) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder and device must not be null");
+    for (const void *p : ptrs)
+        if (!p) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: buffers and params must not be null");
+    return MLXN_OK;
+}
+
+static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input, mlxn_buffer *weight,
+                       mlxn_buffer *output, const mlxn_qmm_params *p) {
+    int rc = touch_kernel(reg, dev, mv_kernel_name((int)p->ggml_type));
+    if (rc) return rc;
+    if ((rc = encoder_begin_work(enc))) return rc;
+    if ((rc = bind(enc, input, false)) || (rc = bind(enc, weight, false)) || (rc = bind(enc, output, true))) return rc;
+    const bool stream = opt_qmv_stream();
+    // rows are processed in groups of at most 8 (the reference launches one grid row per input row)
+    for (uint32_t m0 = 0; m0 < p->m; m0 += 8) {
+        QmvArgs a{};
+        a.w = weight->dev();
+        a.x = reinterpret_cast<const float *>(input->dev()) + (size_t)m0 * p->k;
+        a.y = reinterpret_cast<float *>(output->dev()) + (size_t)m0 * p->n;
+        a.ids = nullptr;
+        a.n = p->n;
+        a.k = p->k;
+        a.m = (p->m - m0) < 8 ? (p->m - m0) : 8;
+        a.nprob = 1;
+        a.top_k = 1;
+        a.n_experts = 1;
+        a.expert_stride = 0;
+        a.status = enc->status_dev;
+        CUDA_TRY(launch_qmv((int)p->ggml_type, a, stream, dev->sm_count, enc->stream, &g_last_kernel), "mat-vec launch");
+        g_launches.fetch_add(1);
+    }
+    g_dispatch.fetch_add(1);
+    return MLXN_OK;
+}
+
+static int dispatch_mm(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input, mlxn_buffer *weight,
+                       mlxn_buffer *output, const mlxn_qmm_params *p) {
+    int rc = touch_kernel(reg, dev, mm_kernel_name((int)p->ggml_type));
+    if (rc) return rc;
+    if ((rc = encoder_begin_work(enc))) return rc;
+    if ((rc = bind(enc, input, false)) || (rc = bind(enc, weight, false)) || (rc = bind(enc, output, true))) return rc;
+    QmmArgs a{};
+    a.w = weight->dev();
+    a.x = reinterpret_cast<const float *>(input->dev());
+    a.y = reinterpret_cast<float *>(output->dev());
+    a.m = p->m;
+    a.n = p->n;
+    a.k = p->k;
+    a.top_k = 1;
+    a.n_experts = 1;
+    a.total_rows = p->m;
+    a.status = enc->status_dev;
+    if (opt_qmm_tc() && qmm_tc_supported(a)) {
+        const uint32_t nt = qmm_tc_pick_nt(p->m, false);
+        uint8_t *scratch = nullptr;
+        if ((rc = encoder_scratch(enc, qmm_tc_scratch_bytes(a, nt, false), &scratch))) return rc;
+        int launches = 0;
+        CUDA_TRY(launch_qmm_tc((int)p->ggml_type, a, false, nt, scratch, enc->stream, &launches), "mat-mat launch");
+        g_launches.fetch_add(launches);
+        g_last_kernel = "qmm_tc";
+    } else {
+        CUDA_TRY(launch_qmm_simt((int)p->ggml_type, a, false, p->m, enc->stream), "mat-mat launch");
+        g_launches.fetch_add(1);
+        g_last_kernel = "qmm_simt";
+    }
+    g_dispatch.fetch_add(1);
+    return MLXN_OK;
+}
+
+static int validate_dense(const char *who_types, mlxn_buffer *input, mlxn_buffer *weight, mlxn_buffer *output,
+                          const mlxn_qmm_params *p, bool allow_q4k) {
+    const int t = (int)p->ggml_type;
+    const bool ok_type = t == GT_Q4_0 || t == GT_Q8_0 || t == GT_Q6_K || (allow_q4k && t == GT_Q4_K);
+    if (!ok_type) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s does not support %s%s", who_types, ggml_name(t),
+                              allow_q4k ? " — use a different dispatch path" : "");
+    if (p->m == 0 || p->k == 0 || p->n == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: M, K, and N must all be > 0");
+    const uint32_t qk = ggml_qk(t);
+    if (p->k % qk != 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: K (%u) must be divisible by block QK (%u)", p->k, qk);
+    if (!input || !weight || !output) return MLXN_OK;
+    const size_t expected_w = (size_t)p->n * (p->k / qk) * ggml_block_bytes(t);
+    if (weight->len < expected_w)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: Weight buffer too small: expected %zu bytes for %s [%ux%u], got %zu",
+                    expected_w, ggml_name(t), p->n, p->k, weight->len);
+    const size_t expected_in = (size_t)p->m * p->k * 4;
+    if (input->len < expected_in)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: Input buffer too small: expected %zu bytes for [%ux%u] f32, got %zu",
+                    expected_in, p->m, p->k, input->len);
+    const size_t expected_out = (size_t)p->m * p->n * 4;
+    if (output->len < expected_out)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: Output buffer too small: expected %zu bytes for [%ux%u] f32, got %zu",
+                    expected_out, p->m, p->n, output->len);
+    return MLXN_OK;
+}
+
+static int check_alignment(mlxn_buffer *input, mlxn_buffer *weight, mlxn_buffer *output) {
+    if ((uintptr_t)weight->dev() & 1u)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: weight data must be 2-byte aligned (GGML blocks hold f16 scales)");
+    if (((uintptr_t)input->dev() & 3u) || ((uintptr_t)output->dev() & 3u))
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: f32 buffers must be 4-byte aligned");
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_quantized_matmul_ggml(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
+                                          mlxn_buffer *weight, mlxn_buffer *output, const mlxn_qmm_params *params) {
+    int rc = check_handles(enc, dev, {input, weight, output, params});
+    if (rc) return rc;
+    if ((rc = validate_dense("quantized_matmul_ggml", input, weight, output, params, true))) return rc;
+    if ((int)params->ggml_type == GT_Q4_K)
+        return fail(MLXN_KERNEL_NOT_FOUND, "Kernel not found: kernel_mul_mv_q4_K_f32 (Q4_K is not built into this library yet)");
+    if ((rc = check_alignment(input, weight, output))) return rc;
+    if (params->m > MLXN_MM_ROUTING_THRESHOLD && params->k >= 32)
+        return dispatch_mm(enc, reg, dev, input, weight, output, params);
+    return dispatch_mv(enc, reg, dev, input, weight, output, params);
+}
+
+extern "C" int mlxn_dispatch_mm_for_test(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
+                                         mlxn_buffer *weight, mlxn_buffer *output, const mlxn_qmm_params *params) {
+    int rc = check_handles(enc, dev, {input, weight, output, params});
+    if (rc) return rc;
+    if ((rc = validate_dense("dispatch_mm_for_test", input, weight, output, params, false))) return rc;
+    if ((rc = check_alignment(input, weight, output))) return rc;
+    return dispatch_mm(enc, reg, dev, input, weight, output, params);
+}
+
+// ------------------------------------------------------------------------------------------------
+// quantized_matmul_id_ggml
+// ------------------------------------------------------------------------------------------------
+static int validate_id(const char *who, mlxn_buffer *input, mlxn_buffer *weight, mlxn_buffer *ids, mlxn_buffer *output,
+                       const mlxn_qmm_id_params *p) {
+    const int t = (int)p->ggml_type;
+    if (p->n_tokens == 0 || p->k == 0 || p->n == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: n_tokens, K, and N must all be > 0", who);
+    if (p->top_k == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: top_k must be > 0", who);
+    if (p->n_experts == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: n_experts must be > 0", who);
+    if (t < 0 || t > MLXN_GGML_I16) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: unknown ggml_type %d", who, t);
+    const uint32_t qk = ggml_qk(t);
+    if (p->k % qk != 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: K (%u) must be divisible by block QK (%u)", who, p->k, qk);
+    const size_t expected_in = (size_t)p->n_tokens * p->k * 4;
+    if (input->len < expected_in)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: input buffer too small: expected %zu bytes for [%u x %u] f32, got %zu",
+                    who, expected_in, p->n_tokens, p->k, input->len);
+    const size_t per_expert = (size_t)p->n * (p->k / qk) * ggml_block_bytes(t);
+    if (p->expert_stride < per_expert)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: expert_stride (%llu) < per_expert_bytes (%zu)", who,
+                    (unsigned long long)p->expert_stride, per_expert);
+    const size_t total_w = per_expert * p->n_experts;
+    if (weight->len < total_w)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: weight buffer too small: expected %zu bytes for %u experts, got %zu",
+                    who, total_w, p->n_experts, weight->len);
+    // this build also reads expert e at e*expert_stride, so the strided extent must be inside the buffer
+    if (weight->len < (size_t)(p->n_experts - 1) * p->expert_stride + per_expert)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: weight buffer too small for %u experts at expert_stride %llu: got %zu bytes",
+                    who, p->n_experts, (unsigned long long)p->expert_stride, weight->len);
+    const size_t total_rows = (size_t)p->n_tokens * p->top_k;
+    if (ids->len < total_rows * 4)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: ids buffer too small: expected %zu bytes for [%u * %u] u32, got %zu",
+                    who, total_rows * 4, p->n_tokens, p->top_k, ids->len);
+    const size_t expected_out = total_rows * p->n * 4;
+    if (output->len < expected_out)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: output buffer too small: expected %zu bytes for [%zu x %u] f32, got %zu",
+                    who, expected_out, total_rows, p->n, output->len);
+    if (t != GT_Q4_0 && t != GT_Q8_0 && t != GT_Q6_K)
+        return fail(MLXN_KERNEL_NOT_FOUND, "Kernel not found: expert-routed kernels for %s are not built into this library yet", ggml_name(t));
+    if (total_rows > 0x7FFFFFFFull / 1) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: n_tokens * top_k is too large", who);
+    return MLXN_OK;
+}
+
+static int dispatch_id_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input, mlxn_buffer *weight,
+                          mlxn_buffer *ids, mlxn_buffer *output, const mlxn_qmm_id_params *p) {
+    int rc = touch_kernel(reg, dev, mv_id_kernel_name((int)p->ggml_type));
+    if (rc) return rc;
+    if ((rc = encoder_begin_work(enc))) return rc;
+    if ((rc = bind(enc, input, false)) || (rc = bind(enc, weight, false)) || (rc = bind(enc, ids, false)) ||
+        (rc = bind(enc, output, true)))
+        return rc;
+    QmvArgs a{};
+    a.w = weight->dev();
+    a.x = reinterpret_cast<const float *>(input->dev());
+    a.y = reinterpret_cast<float *>(output->dev());
+    a.ids = reinterpret_cast<const uint32_t *>(ids->dev());
+    a.n = p->n;
+    a.k = p->k;
+    a.m = 1;
+    a.nprob = p->n_tokens * p->top_k;
+    a.top_k = p->top_k;
+    a.n_experts = p->n_experts;
+    a.expert_stride = p->expert_stride;
+    a.status = enc->status_dev;
+    CUDA_TRY(launch_qmv((int)p->ggml_type, a, opt_qmv_stream(), dev->sm_count, enc->stream, &g_last_kernel), "mat-vec launch");
+    g_launches.fetch_add(1);
+    g_dispatch.fetch_add(1);
+    return MLXN_OK;
+}
+
+// two-stage route: bucket (token, slot) pairs by expert, then the grouped mat-mat
+static int dispatch_id_mm_stages(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
+                                 mlxn_buffer *weight, mlxn_buffer *ids, mlxn_buffer *output, uint32_t *htpe, int32_t *hids,
+                                 uint32_t hids_stride, size_t scratch_used, const mlxn_qmm_id_params *p) {
+    int rc = touch_kernel(reg, dev, p->top_k == 1 ? "kernel_mul_mm_id_map0_ne20_1" : "kernel_mul_mm_id_map0_ne20_8");
+    if (rc) return rc;
+    if ((rc = touch_kernel(reg, dev, mm_id_kernel_name((int)p->ggml_type)))) return rc;
+    CUDA_TRY(launch_moe_map0(reinterpret_cast<const uint32_t *>(ids->dev()), p->n_tokens, p->top_k, p->n_experts,
+                             hids_stride, htpe, hids, enc->stream),
+             "map0 launch");
+    g_launches.fetch_add(1);
+    g_dispatch.fetch_add(1);
+    g_barrier.fetch_add(1);  // upstream's RAW fence between map0 and mm_id (stream order provides it here)
+    QmmArgs a{};
+    a.w = weight->dev();
+    a.x = reinterpret_cast<const float *>(input->dev());
+    a.y = reinterpret_cast<float *>(output->dev());
+    a.m = p->n_tokens;
+    a.n = p->n;
+    a.k = p->k;
+    a.htpe = htpe;
+    a.hids = hids;
+    a.hids_stride = hids_stride;
+    a.top_k = p->top_k;
+    a.n_experts = p->n_experts;
+    a.total_rows = p->n_tokens * p->top_k;
+    a.expert_stride = p->expert_stride;
+    a.status = enc->status_dev;
+    if (opt_qmm_tc() && qmm_tc_supported(a)) {
+        const uint32_t nt = qmm_tc_pick_nt(p->n_tokens, true);
+        uint8_t *scratch = nullptr;
+        const size_t need = qmm_tc_scratch_bytes(a, nt, true);
+        if ((rc = encoder_scratch(enc, scratch_used + need, &scratch))) return rc;
+        int launches = 0;
+        CUDA_TRY(launch_qmm_tc((int)p->ggml_type, a, true, nt, scratch + scratch_used, enc->stream, &launches), "mat-mat launch");
+        g_launches.fetch_add(launches);
+        g_last_kernel = "qmm_tc_id";
+    } else {
+        CUDA_TRY(launch_qmm_simt((int)p->ggml_type, a, true, p->n_tokens, enc->stream), "mat-mat launch");
+        g_launches.fetch_add(1);
+        g_last_kernel = "qmm_simt_id";
+    }
+    g_dispatch.fetch_add(1);
+    return MLXN_OK;
+}
+
+static bool id_routes_to_mm(const mlxn_qmm_id_params *p) {
+    return p->n_tokens > mlxn_mm_id_routing_threshold() && (p->top_k == 1 || p->top_k == 8) && p->k >= 32 &&
+           (int)p->ggml_type != GT_Q5_K;
+}
+
+extern "C" size_t mlxn_id_mm_htpe_bytes(const mlxn_qmm_id_params *p) { return p ? (size_t)p->n_experts * 4 : 0; }
+extern "C" size_t mlxn_id_mm_hids_bytes(const mlxn_qmm_id_params *p) { return p ? (size_t)p->n_experts * p->n_tokens * 4 : 0; }
+
+extern "C" int mlxn_quantized_matmul_id_ggml(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
+                                             mlxn_buffer *weight, mlxn_buffer *ids, mlxn_buffer *output,
+                                             const mlxn_qmm_id_params *params) {
+    int rc = check_handles(enc, dev, {input, weight, ids, output, params});
+    if (rc) return rc;
+    if ((rc = validate_id("quantized_matmul_id_ggml", input, weight, ids, output, params))) return rc;
+    if ((rc = check_alignment(input, weight, output))) return rc;
+    if (!id_routes_to_mm(params)) return dispatch_id_mv(enc, reg, dev, input, weight, ids, output, params);
+    if ((rc = encoder_begin_work(enc))) return rc;
+    if ((rc = bind(enc, input, false)) || (rc = bind(enc, weight, false)) || (rc = bind(enc, ids, false)) ||
+        (rc = bind(enc, output, true)))
+        return rc;
+    // routing scratch comes out of the encoder's arena instead of two fresh allocations per call
+    const size_t htpe_b = (mlxn_id_mm_htpe_bytes(params) + 1023) / 1024 * 1024;
+    const size_t hids_b = (mlxn_id_mm_hids_bytes(params) + 1023) / 1024 * 1024;
+    QmmArgs probe{};
+    probe.k = params->k;
+    probe.n_experts = params->n_experts;
+    probe.total_rows = params->n_tokens * params->top_k;
+    const size_t tc_b = qmm_tc_scratch_bytes(probe, qmm_tc_pick_nt(params->n_tokens, true), true);
+    uint8_t *scratch = nullptr;
+    if ((rc = encoder_scratch(enc, htpe_b + hids_b + tc_b, &scratch))) return rc;
+    return dispatch_id_mm_stages(enc, reg, dev, input, weight, ids, output, reinterpret_cast<uint32_t *>(scratch),
+                                 reinterpret_cast<int32_t *>(scratch + htpe_b), params->n_tokens, htpe_b + hids_b, params);
+}
+
+static int check_scratch_buffers(mlxn_buffer *htpe, mlxn_buffer *hids, const mlxn_qmm_id_params *p) {
+    if (htpe->len < mlxn_id_mm_htpe_bytes(p))
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: htpe buffer too small: expected %zu bytes, got %zu", mlxn_id_mm_htpe_bytes(p), htpe->len);
+    if (hids->len < mlxn_id_mm_hids_bytes(p))
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: hids buffer too small: expected %zu bytes, got %zu", mlxn_id_mm_hids_bytes(p), hids->len);
+    if (((uintptr_t)htpe->dev() & 3u) || ((uintptr_t)hids->dev() & 3u))
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: scratch buffers must be 4-byte aligned");
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_quantized_matmul_id_ggml_pooled(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev,
+                                                    mlxn_buffer *input, mlxn_buffer *weight, mlxn_buffer *ids,
+                                                    mlxn_buffer *output, mlxn_buffer *htpe, mlxn_buffer *hids,
+                                                    uint32_t n_experts_cap, uint32_t n_tokens_cap,
+                                                    const mlxn_qmm_id_params *params) {
+    int rc = check_handles(enc, dev, {input, weight, ids, output, htpe, hids, params});
+    if (rc) return rc;
+    if ((rc = validate_id("quantized_matmul_id_ggml_pooled", input, weight, ids, output, params))) return rc;
+    if ((rc = check_alignment(input, weight, output))) return rc;
+    if (!id_routes_to_mm(params)) return dispatch_id_mv(enc, reg, dev, input, weight, ids, output, params);
+    if (params->n_experts > n_experts_cap)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: IdMmScratch: n_experts (%u) > cap (%u)", params->n_experts, n_experts_cap);
+    if (params->n_tokens > n_tokens_cap)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: IdMmScratch: n_tokens (%u) > cap (%u)", params->n_tokens, n_tokens_cap);
+    if ((rc = check_scratch_buffers(htpe, hids, params))) return rc;
+    if ((rc = encoder_begin_work(enc))) return rc;
+    if ((rc = bind(enc, input, false)) || (rc = bind(enc, weight, false)) || (rc = bind(enc, ids, false)) ||
+        (rc = bind(enc, output, true)) || (rc = bind(enc, htpe, true)) || (rc = bind(enc, hids, true)))
+        return rc;
+    return dispatch_id_mm_stages(enc, reg, dev, input, weight, ids, output, reinterpret_cast<uint32_t *>(htpe->dev()),
+                                 reinterpret_cast<int32_t *>(hids->dev()), params->n_tokens, 0, params);
+}
+
+extern "C" int mlxn_dispatch_id_mm_for_test(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
+                                            mlxn_buffer *weight, mlxn_buffer *ids, mlxn_buffer *htpe, mlxn_buffer *hids,
+                                            mlxn_buffer *output, const mlxn_qmm_id_params *params) {
+    int rc = check_handles(enc, dev, {input, weight, ids, output, htpe, hids, params});
+    if (rc) return rc;
+    if ((rc = validate_id("dispatch_id_mm_for_test", input, weight, ids, output, params))) return rc;
+    if ((rc = check_alignment(input, weight, output))) return rc;
+    if ((rc = check_scratch_buffers(htpe, hids, params))) return rc;
+    if ((rc = encoder_begin_work(enc))) return rc;
+    if ((rc = bind(enc, input, false)) || (rc = bind(enc, weight, false)) || (rc = bind(enc, ids, false)) ||
+        (rc = bind(enc, output, true)) || (rc = bind(enc, htpe, true)) || (rc = bind(enc, hids, true)))
+        return rc;
+    return dispatch_id_mm_stages(enc, reg, dev, input, weight, ids, output, reinterpret_cast<uint32_t *>(htpe->dev()),
+                                 reinterpret_cast<int32_t *>(hids->dev()), params->n_tokens, 0, params);
+}
+
+// ------------------------------------------------------------------------------------------------
+// MoE glue
+// ------------------------------------------------------------------------------------------------
+extern "C" int mlxn_moe_softmax_topk(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *logits,
+                                     mlxn_buffer *out_ids, mlxn_buffer *out_weights, uint32_t n_tokens,
+                                     uint32_t n_experts, uint32_t top_k) {
+    int rc = check_handles(enc, dev, {logits, out_ids, out_weights});
+    if (rc) return rc;
+    if (n_tokens == 0 || n_experts == 0 || top_k == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_softmax_topk: n_tokens, n_experts and top_k must all be > 0");
+    if (top_k > n_experts) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_softmax_topk: top_k (%u) > n_experts (%u)", top_k, n_experts);
+    if (top_k > 64) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_softmax_topk: top_k (%u) > 64", top_k);
+    if (n_experts > 8192) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_softmax_topk: n_experts (%u) > 8192", n_experts);
+    if (logits->len < (size_t)n_tokens * n_experts * 4 || out_ids->len < (size_t)n_tokens * top_k * 4 ||
+        out_weights->len < (size_t)n_tokens * top_k * 4)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_softmax_topk: a buffer is too small");
+    if ((rc = touch_kernel(reg, dev, "moe_softmax_topk_f32"))) return rc;
+    if ((rc = encoder_begin_work(enc))) return rc;
+    if ((rc = bind(enc, logits, false)) || (rc = bind(enc, out_ids, true)) || (rc = bind(enc, out_weights, true))) return rc;
+    CUDA_TRY(launch_moe_softmax_topk(reinterpret_cast<const float *>(logits->dev()), n_tokens, n_experts, top_k,
+                                     reinterpret_cast<uint32_t *>(out_ids->dev()), reinterpret_cast<float *>(out_weights->dev()),
+                                     enc->stream),
+             "moe_softmax_topk launch");
+    g_launches.fetch_add(1);
+    g_dispatch.fetch_add(1);
+    g_last_kernel = "moe_softmax_topk";
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_silu_mul(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *gate, mlxn_buffer *up,
+                             mlxn_buffer *out, uint32_t n) {
+    int rc = check_handles(enc, dev, {gate, up, out});
+    if (rc) return rc;
+    if (n == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: silu_mul: n must be > 0");
+    if (gate->len < (size_t)n * 4 || up->len < (size_t)n * 4 || out->len < (size_t)n * 4)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: silu_mul: a buffer is too small for %u f32 elements", n);
+    if ((rc = touch_kernel(reg, dev, "silu_mul_f32"))) return rc;
+    if ((rc = encoder_begin_work(enc))) return rc;
+    if ((rc = bind(enc, gate, false)) || (rc = bind(enc, up, false)) || (rc = bind(enc, out, true))) return rc;
+    CUDA_TRY(launch_silu_mul(reinterpret_cast<const float *>(gate->dev()), reinterpret_cast<const float *>(up->dev()),
+                             reinterpret_cast<float *>(out->dev()), n, enc->stream),
+             "silu_mul launch");
+    g_launches.fetch_add(1);
+    g_dispatch.fetch_add(1);
+    g_last_kernel = "silu_mul";
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_moe_weighted_reduce(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *expert_w,
+                                        mlxn_buffer *y_expert, mlxn_buffer *sh_logit, mlxn_buffer *y_shared,
+                                        mlxn_buffer *residual, mlxn_buffer *out, uint32_t n_tokens, uint32_t top_k,
+                                        uint32_t h) {
+    int rc = check_handles(enc, dev, {expert_w, y_expert, out});
+    if (rc) return rc;
+    if (n_tokens == 0 || top_k == 0 || h == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_weighted_reduce: n_tokens, top_k and h must all be > 0");
+    if (expert_w->len < (size_t)n_tokens * top_k * 4 || y_expert->len < (size_t)n_tokens * top_k * h * 4 ||
+        out->len < (size_t)n_tokens * h * 4 || (y_shared && y_shared->len < (size_t)n_tokens * h * 4) ||
+        (sh_logit && sh_logit->len < (size_t)n_tokens * 4) || (residual && residual->len < (size_t)n_tokens * h * 4))
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_weighted_reduce: a buffer is too small");
+    if ((rc = touch_kernel(reg, dev, "moe_weighted_reduce_f32"))) return rc;
+    if ((rc = encoder_begin_work(enc))) return rc;
+    if ((rc = bind(enc, expert_w, false)) || (rc = bind(enc, y_expert, false)) || (rc = bind(enc, out, true))) return rc;
+    if (sh_logit && (rc = bind(enc, sh_logit, false))) return rc;
+    if (y_shared && (rc = bind(enc, y_shared, false))) return rc;
+    if (residual && (rc = bind(enc, residual, false))) return rc;
+    CUDA_TRY(launch_moe_weighted_reduce(reinterpret_cast<const float *>(expert_w->dev()),
+                                        reinterpret_cast<const float *>(y_expert->dev()),
+                                        sh_logit ? reinterpret_cast<const float *>(sh_logit->dev()) : nullptr,
+                                        y_shared ? reinterpret_cast<const float *>(y_shared->dev()) : nullptr,
+                                        residual ? reinterpret_cast<const float *>(residual->dev()) : nullptr,
+                                        reinterpret_cast<float *>(out->dev()), n_tokens, top_k, h, enc->stream),
+             "moe_weighted_reduce launch");
+    g_launches.fetch_add(1);
+    g_dispatch.fetch_add(1);
+    g_last_kernel = "moe_weighted_reduce";
+    return MLXN_OK;
+}

@@ -1,0 +1,178 @@
+"""Parity of the mat-vec path (m <= 8) with the CPU oracle, through the C ABI.
+Mirrors upstream tests/test_quantized_matmul_ggml.rs and adds the shapes and edge cases of the B200 kernels."""
+import numpy as np
+import pytest
+
+import mlx_native_b200 as mx
+from oracle import oracle as orc
+from tests.gpu_util import MV_TOL, TYPES, Ctx, lcg_weights, norm_err, normal_acts, normal_weights
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    return Ctx()
+
+
+@pytest.fixture(params=["stream", "simple"])
+def variant(request):
+    mx.set_option("qmv", request.param)
+    yield request.param
+    mx.set_option("qmv", "stream")
+
+
+def check(ctx, tname, wq, x, n, k, abs_tol=None, tol=MV_TOL):
+    gtype, otype = TYPES[tname]
+    y = ctx.matmul(gtype, wq, x, n, k)
+    y_ref, ad = orc.qmatmul(otype, wq, x, n, k, nthreads=8)
+    err = norm_err(y, y_ref, ad)
+    assert err <= tol, f"{tname} n={n} k={k} m={x.shape[0]}: normalised error {err:.3e} > {tol}"
+    if abs_tol is not None:
+        assert np.max(np.abs(y - y_ref)) <= abs_tol
+    return y
+
+
+# ---- upstream known-value ramps (tests/test_quantized_matmul_ggml.rs:539-577, :651-686, :759-789)
+@pytest.mark.parametrize("tname", ["Q4_0", "Q8_0", "Q6_K"])
+def test_known_values(ctx, variant, tname):
+    if tname == "Q4_0":
+        n, k, tol = 8, 32, 1e-4
+        wf = np.array([[(r * 0.1) * ((c - 16.0) / 16.0) for c in range(k)] for r in range(n)], np.float32)
+    elif tname == "Q8_0":
+        n, k, tol = 8, 32, 1e-4
+        wf = np.array([[(r + 1.0) * (c - 16.0) / 32.0 for c in range(k)] for r in range(n)], np.float32)
+    else:
+        n, k, tol = 2, 256, 1e-3
+        wf = np.array([[(r + 1.0) * (c - 128.0) / 256.0 for c in range(k)] for r in range(n)], np.float32)
+    wq = orc.quantize(TYPES[tname][1], wf)
+    check(ctx, tname, wq, np.ones((1, k), np.float32), n, k, abs_tol=tol)
+
+
+# ---- upstream seeded random cases (:585-586, :694-695, :797-798)
+@pytest.mark.parametrize("tname,sw,sx,n,k,tol", [("Q4_0", 42, 123, 32, 256, 1e-3), ("Q8_0", 55, 66, 32, 256, 1e-3),
+                                                 ("Q6_K", 99, 100, 16, 256, 1e-2)])
+def test_random(ctx, variant, tname, sw, sx, n, k, tol):
+    wq = lcg_weights(sw, n, k, TYPES[tname][1])
+    check(ctx, tname, wq, orc.lcg_f32(sx, k)[None], n, k, abs_tol=tol)
+
+
+# ---- upstream production shape 4096 x 4096, m = 1 (:619-620, :727-728, :824-825)
+@pytest.mark.parametrize("tname,sw,sx,tol", [("Q4_0", 1, 2, 0.5), ("Q8_0", 77, 88, 0.1), ("Q6_K", 200, 201, 1.0)])
+def test_production_shape(ctx, variant, tname, sw, sx, tol):
+    n = k = 4096
+    wq = lcg_weights(sw, n, k, TYPES[tname][1])
+    check(ctx, tname, wq, orc.lcg_f32(sx, k)[None], n, k, abs_tol=tol)
+    assert mx.last_kernel_name() == ("qmv_stream" if variant == "stream" else "qmv_simple")
+
+
+# ---- the benchmark's first configuration: Q4_0, m=1, 4096 x 4096, N(0,0.02) weights, GGML quantizer, seed 0
+def test_config_q4_0_4096(ctx, variant):
+    wq = normal_weights(0, 4096, 4096, orc.Q4_0)
+    check(ctx, "Q4_0", wq, normal_acts(0, 1, 4096), 4096, 4096)
+
+
+# ---- decode sweep shapes, every m in 1..8 on one shape and m in {1,2,4,8} on the others
+@pytest.mark.parametrize("tname", ["Q4_0", "Q8_0", "Q6_K"])
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_all_m(ctx, variant, tname, m):
+    n, k = 1024, 4096
+    wq = normal_weights(3, n, k, TYPES[tname][1])
+    check(ctx, tname, wq, normal_acts(m, m, k), n, k)
+
+
+@pytest.mark.parametrize("tname", ["Q8_0", "Q6_K"])
+@pytest.mark.parametrize("n,k", [(4096, 4096), (12288, 4096), (4096, 12288)])
+@pytest.mark.parametrize("m", [1, 8])
+def test_decode_sweep_shapes(ctx, tname, n, k, m):
+    mx.set_option("qmv", "stream")
+    wq = normal_weights(11, n, k, TYPES[tname][1])
+    y = check(ctx, tname, wq, normal_acts(5, m, k), n, k)
+    assert mx.last_kernel_name() == "qmv_stream"
+    # a row's result does not depend on how many rows share the weights (up to summation order)
+    if m == 8:
+        x3 = normal_acts(5, 8, k)[3:4]
+        y1 = ctx.matmul(TYPES[tname][0], wq, x3, n, k)
+        _, ad = orc.qmatmul(TYPES[tname][1], wq, x3, n, k, nthreads=8)
+        assert norm_err(y1, y[3:4], ad) <= MV_TOL
+
+
+# ---- edge cases: ragged n, short and odd k, k-slicing, misaligned weight views
+@pytest.mark.parametrize("tname,n,k,m", [
+    ("Q4_0", 5, 32, 1), ("Q4_0", 13, 96, 3), ("Q8_0", 1, 64, 8), ("Q8_0", 7, 256, 2), ("Q6_K", 3, 256, 1),
+    ("Q6_K", 2049, 768, 1), ("Q6_K", 66, 5120, 2), ("Q4_0", 1027, 2048, 8), ("Q8_0", 130, 12288, 8),
+    ("Q6_K", 37, 12288, 4), ("Q4_0", 4, 256, 1), ("Q8_0", 149, 512, 5),
+])
+def test_edge_shapes(ctx, variant, tname, n, k, m):
+    wq = normal_weights(n * 31 + k, n, k, TYPES[tname][1])
+    check(ctx, tname, wq, normal_acts(n, m, k), n, k)
+
+
+@pytest.mark.parametrize("tname", ["Q4_0", "Q8_0", "Q6_K"])
+@pytest.mark.parametrize("offset", [2, 6, 18])
+def test_weight_view_offsets(ctx, variant, tname, offset):
+    """Weights that start at a 2-byte-aligned (not 16-byte-aligned) address inside a larger buffer."""
+    gtype, otype = TYPES[tname]
+    n, k = 64, 1024
+    wq = normal_weights(5, n, k, otype)
+    big = np.zeros(wq.size + 64, np.uint8)
+    big[offset:offset + wq.size] = wq
+    base = ctx.buf(big, mx.DType.U8)
+    view = base.slice_view(offset, wq.size)
+    x = normal_acts(1, 2, k)
+    y = ctx.matmul(gtype, wq, x, n, k, weight_buf=view)
+    y_ref, ad = orc.qmatmul(otype, wq, x, n, k)
+    assert norm_err(y, y_ref, ad) <= MV_TOL
+
+
+def test_zero_weights_and_zero_scale(ctx, variant):
+    n, k = 16, 512
+    for tname in ("Q4_0", "Q8_0", "Q6_K"):
+        gtype, otype = TYPES[tname]
+        wq = orc.quantize(otype, np.zeros((n, k), np.float32))
+        y = ctx.matmul(gtype, wq, normal_acts(0, 2, k), n, k)
+        assert np.all(y == 0)
+
+
+def test_stream_equals_simple_closely(ctx):
+    """The two mat-vec kernels agree to within summation-order rounding."""
+    n, k = 512, 4096
+    for tname in ("Q4_0", "Q8_0", "Q6_K"):
+        gtype, otype = TYPES[tname]
+        wq = normal_weights(9, n, k, otype)
+        x = normal_acts(9, 4, k)
+        mx.set_option("qmv", "stream")
+        a = ctx.matmul(gtype, wq, x, n, k)
+        mx.set_option("qmv", "simple")
+        b = ctx.matmul(gtype, wq, x, n, k)
+        mx.set_option("qmv", "stream")
+        _, ad = orc.qmatmul(otype, wq, x, n, k, nthreads=8)
+        assert norm_err(a, b, ad) <= MV_TOL
+
+
+# ---- error behaviour (src/ops/quantized_matmul_ggml.rs:283-334)
+def test_errors(ctx):
+    d = ctx.device
+    enc = d.command_encoder()
+    x = d.alloc_buffer(4 * 64, mx.DType.F32, [1, 64])
+    w = d.alloc_buffer(18 * 2 * 8, mx.DType.U8)
+    y = d.alloc_buffer(4 * 8, mx.DType.F32, [1, 8])
+    P = mx.GgmlQuantizedMatmulParams
+    with pytest.raises(mx.InvalidArgument, match="does not support F32"):
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, x, w, y, P(1, 8, 64, mx.GgmlType.F32))
+    with pytest.raises(mx.InvalidArgument, match="M, K, and N must all be > 0"):
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, x, w, y, P(0, 8, 64, mx.GgmlType.Q4_0))
+    with pytest.raises(mx.InvalidArgument, match=r"K \(48\) must be divisible by block QK \(32\)"):
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, x, w, y, P(1, 8, 48, mx.GgmlType.Q4_0))
+    with pytest.raises(mx.InvalidArgument, match="Weight buffer too small: expected 576 bytes"):
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, x, w, y, P(1, 16, 64, mx.GgmlType.Q4_0))
+    with pytest.raises(mx.InvalidArgument, match="Input buffer too small"):
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, x, w, y, P(2, 8, 64, mx.GgmlType.Q4_0))
+    small_y = d.alloc_buffer(4 * 4, mx.DType.F32)
+    with pytest.raises(mx.InvalidArgument, match="Output buffer too small"):
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, x, w, small_y, P(1, 8, 64, mx.GgmlType.Q4_0))
+    # over-sized buffers are accepted, as upstream
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, x, w, y, P(1, 4, 64, mx.GgmlType.Q4_0))
+    enc.commit_and_wait()
+    with pytest.raises(mx.InvalidArgument):
+        d.alloc_buffer(0, mx.DType.F32)

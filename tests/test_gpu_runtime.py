@@ -1,0 +1,138 @@
+"""Device / buffer / pool / encoder behaviour on a GPU (upstream src/lib.rs:211-308, tests/test_graph.rs)."""
+import numpy as np
+import pytest
+
+import mlx_native_b200 as mx
+from oracle import oracle as orc
+from tests.gpu_util import TYPES, Ctx, normal_acts, normal_weights
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    return Ctx()
+
+
+def test_device_and_buffers(ctx):
+    d = ctx.device
+    assert "B200" in d.name() or d.sm_count() > 0
+    b = d.alloc_buffer(4096, mx.DType.F32, [32, 32])
+    assert b.dtype() == mx.DType.F32 and b.shape() == [32, 32] and b.byte_len() == 4096 and b.element_count() == 1024
+    assert np.all(b.as_slice(np.float32) == 0)          # new buffers are zero-filled
+    b.as_mut_slice(np.float32)[:] = np.arange(1024, dtype=np.float32)
+    assert np.array_equal(b.download(np.float32), np.arange(1024, dtype=np.float32))
+    v = b.slice_view(1024, 16)
+    assert v.byte_offset() == 1024 and v.byte_len() == 64
+    assert np.array_equal(v.as_slice(np.float32), np.arange(256, 272, dtype=np.float32))
+    c = b.clone()
+    del b
+    assert c.as_slice(np.float32)[5] == 5.0             # storage lives as long as any handle
+    with pytest.raises(mx.InvalidArgument):
+        c.slice_view(4000, 100)
+
+
+def test_pool_reuse(ctx):
+    d = ctx.device
+    pool = mx.MlxBufferPool()
+    a = pool.alloc(d, 3000, mx.DType.U8)
+    assert a.byte_len() == 4096 and pool.in_use_count() == 1 and pool.free_count() == 0
+    ptr = a.contents_ptr()
+    del a
+    pool.reset()
+    assert pool.free_count() == 1 and pool.free_bytes() == 4096 and pool.in_use_count() == 0
+    b = pool.alloc(d, 4000, mx.DType.F32)
+    assert b.contents_ptr() == ptr and pool.free_count() == 0
+    pool.release(b)
+    assert pool.free_count() == 1
+    pool.clear()
+    assert pool.free_count() == 0
+    pool.register_existing(d, d.alloc_buffer(16, mx.DType.U8))
+
+
+def test_session_equals_direct_dispatch_and_counters(ctx):
+    d = ctx.device
+    gtype, otype = TYPES["Q8_0"]
+    n, k, m = 256, 1024, 2
+    wq = normal_weights(1, n, k, otype)
+    x = normal_acts(1, m, k)
+    direct = ctx.matmul(gtype, wq, x, n, k)
+    mx.reset_counters()
+    ex = mx.GraphExecutor.new(d)
+    s = ex.begin()
+    inp, w = ctx.buf(x, mx.DType.F32), ctx.buf(wq, mx.DType.U8)
+    out = d.alloc_buffer(m * n * 4, mx.DType.F32)
+    s.quantized_matmul_ggml(ctx.registry, d, inp, w, out, mx.GgmlQuantizedMatmulParams(m, n, k, gtype))
+    s.barrier()
+    t = s.finish_with_gpu_time()
+    assert np.array_equal(out.as_slice(np.float32).reshape(m, n), direct)
+    assert mx.dispatch_count() == 1 and mx.kernel_launch_count() == 1 and mx.barrier_count() == 1
+    assert mx.sync_count() == 1 and mx.cmd_buf_count() == 1 and 0 < t < 1.0
+    # dropping an encoder without committing is safe
+    s2 = ex.begin()
+    s2.quantized_matmul_ggml(ctx.registry, d, inp, w, out, mx.GgmlQuantizedMatmulParams(m, n, k, gtype))
+    del s2
+
+
+def test_buffer_dropped_after_encode_stays_alive(ctx):
+    d = ctx.device
+    gtype, otype = TYPES["Q4_0"]
+    n, k = 512, 2048
+    wq = normal_weights(2, n, k, otype)
+    x = normal_acts(2, 1, k)
+    want = ctx.matmul(gtype, wq, x, n, k)
+    enc = d.command_encoder()
+    inp, w = ctx.buf(x, mx.DType.F32), ctx.buf(wq, mx.DType.U8)
+    out = d.alloc_buffer(n * 4, mx.DType.F32)
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, inp, w, out, mx.GgmlQuantizedMatmulParams(1, n, k, gtype))
+    del inp, w                                   # the encoder holds them until the wait returns
+    enc.commit()
+    enc.wait_until_completed()
+    assert np.array_equal(out.as_slice(np.float32), want[0])
+
+
+def test_capture_and_replay(ctx):
+    d = ctx.device
+    gtype, otype = TYPES["Q6_K"]
+    n, k = 1024, 4096
+    wq = normal_weights(3, n, k, otype)
+    w = ctx.buf(wq, mx.DType.U8)
+    inp = ctx.buf(normal_acts(3, 1, k), mx.DType.F32)
+    out = d.alloc_buffer(n * 4, mx.DType.F32)
+    p = mx.GgmlQuantizedMatmulParams(1, n, k, gtype)
+    enc = d.command_encoder()
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, inp, w, out, p)   # uploads happen outside the capture
+    enc.commit_and_wait()
+    first = out.as_slice(np.float32).copy()
+    mx.reset_counters()
+    enc.begin_capture()
+    for _ in range(4):
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, inp, w, out, p)
+    graph = enc.end_capture()
+    assert mx.kernel_launch_count() == 0         # recording does not run anything
+    graph.launch(enc)
+    graph.launch(enc)
+    enc.commit_and_wait()
+    assert mx.kernel_launch_count() == 8 and mx.dispatch_count() == 8
+    assert np.array_equal(out.as_slice(np.float32), first)
+
+
+def test_wrap_external_device_memory(ctx):
+    torch = pytest.importorskip("torch")
+    d = ctx.device
+    gtype, otype = TYPES["Q8_0"]
+    n, k = 128, 512
+    wq = normal_weights(4, n, k, otype)
+    x = normal_acts(4, 1, k)
+    tw = torch.from_numpy(wq).cuda()
+    tx = torch.from_numpy(x).cuda()
+    ty = torch.zeros(n, dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    enc = d.command_encoder()
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, d.wrap_device_memory(tx.data_ptr(), x.nbytes, mx.DType.F32),
+                             d.wrap_device_memory(tw.data_ptr(), wq.nbytes, mx.DType.U8),
+                             d.wrap_device_memory(ty.data_ptr(), n * 4, mx.DType.F32),
+                             mx.GgmlQuantizedMatmulParams(1, n, k, gtype))
+    enc.commit_and_wait()
+    y_ref, _ = orc.qmatmul(otype, wq, x, n, k)
+    assert np.allclose(ty.cpu().numpy(), y_ref[0], rtol=1e-4, atol=1e-5)
