@@ -315,7 +315,9 @@ struct TcCfg {
 // grid (ceil(n/128), tile count bound); kTcThreads threads; 1 CTA per SM (dynamic shared memory ~200 KiB).
 template <int T, int NT>
 __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, const TcCfg c, const uint8_t *xpack) {
-    extern __shared__ __align__(1024) uint8_t smem[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // tensor-core operand tiles need 1024-byte alignment (128-byte swizzle atoms): align by hand
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES, KR = TcTraits<T>::KR;
     constexpr int CPR = KR / 64;     // 64-wide chunks per raw stage
     constexpr int kMaxS = 6;
@@ -549,7 +551,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     c.a_off = 0;
     c.b_off = stages * a_bytes;
     c.raw_off = c.b_off + stages * b_bytes;
-    const size_t smem = (size_t)c.raw_off + raw_bytes;
+    const size_t smem = (size_t)c.raw_off + raw_bytes + 1024;  // + slack for manual 1024-byte alignment
 
     size_t tiles;
     uint8_t *xpack = scratch;
@@ -574,13 +576,14 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    static bool attr_set[64] = {};
+    static size_t attr_smem[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(qmm_tc_kernel<T, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (smem > attr_smem[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(qmm_tc_kernel<T, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
+        attr_smem[dev] = smem;
     }
     dim3 grid((a.n + kTcRowsW - 1) / kTcRowsW, (unsigned)tiles);
     qmm_tc_kernel<T, NT><<<grid, kTcThreads, smem, st>>>(a, c, xpack);

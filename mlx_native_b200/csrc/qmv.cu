@@ -515,6 +515,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1) qmv_stream_kernel(const Qmv
                 more_issue = wi.next(a, c);
             }
         }
+        if (abort_flag) {  // let copies in flight land before the CTA's shared memory is released
+            for (int i = 0; i < 200; i++) __nanosleep(5000);
+        }
         return;
     }
 
@@ -688,13 +691,14 @@ static bool stream_config(const QmvArgs &a, int sm_count, size_t smem_limit, Str
 
 template <int T, int M> static cudaError_t launch_stream_tm(const QmvArgs &a, const StreamCfg &c, uint32_t grid, size_t smem,
                                                             cudaStream_t st) {
-    static bool attr_set[64] = {};
+    static size_t attr_smem[64] = {};  // largest dynamic shared-memory size enabled so far, per device
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(qmv_stream_kernel<T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (smem > attr_smem[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(qmv_stream_kernel<T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
+        attr_smem[dev] = smem;
     }
     qmv_stream_kernel<T, M><<<grid, kStreamThreads, smem, st>>>(a, c);
     return cudaGetLastError();

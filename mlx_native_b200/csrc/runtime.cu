@@ -56,6 +56,7 @@ static int fail(int status, const char *fmt, ...) {
     return status;
 }
 static int cuda_fail(cudaError_t e, const char *what) {
+    cudaGetLastError();  // clear the runtime's sticky "last error" so later launches are not blamed for it
     return fail(MLXN_COMMAND_BUFFER_ERROR, "Command buffer error: %s: %s", what, cudaGetErrorString(e));
 }
 #define CUDA_TRY(expr, what)                          \
@@ -571,7 +572,14 @@ extern "C" int mlxn_encoder_create(mlxn_device *dev, mlxn_encoder **out) {
 }
 
 static void encoder_release_retained(mlxn_encoder *e) {
-    for (mlxn_buffer *b : e->retained) mlxn_buffer_release(b);
+    // called once the stream is idle: storages whose last user was this stream no longer need a wait
+    for (mlxn_buffer *b : e->retained) {
+        {
+            std::lock_guard<std::mutex> lk(b->st->mu);
+            if (b->st->has_last && b->st->last_stream == e->stream) b->st->has_last = false;
+        }
+        mlxn_buffer_release(b);
+    }
     e->retained.clear();
     for (void *p : e->retired) cudaFree(p);
     e->retired.clear();
