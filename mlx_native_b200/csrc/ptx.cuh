@@ -41,7 +41,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     for (uint32_t i = 0; i < kWaitSpinLimit; i++) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort) return false;
-        if (i > 64) __nanosleep(i > 4096 ? 256 : 32);
+        __nanosleep(i > 4096 ? 256 : 20);  // back off at once: polling steals issue slots from working warps
     }
     *abort = 1;
     if (status) atomicCAS(status, 0u, code);

@@ -205,7 +205,8 @@ __global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *x
 // =================================================================================================
 // qmm_tc
 // =================================================================================================
-constexpr int kTcDequantWarps = 8;
+constexpr int kTcDequantWarps = 16;  // two sets of 8: set s dequantises the K chunks with kc % 2 == s
+constexpr int kTcSetWarps = 8;
 constexpr int kTcThreads = (kTcDequantWarps + 2) * 32;  // + producer warp + MMA warp
 constexpr int kTcRowsW = 128;                           // weight rows per tile (UMMA M)
 
@@ -305,6 +306,92 @@ template <int T> __device__ __forceinline__ uint4 dequant8(uint32_t seg, uint32_
     return out;
 }
 
+
+// NWORDS logical 32-bit words at a 2-byte-aligned shared address
+template <int NWORDS> __device__ __forceinline__ void lds_words_n(uint32_t addr, uint32_t (&out)[NWORDS]) {
+    const uint32_t al = addr & ~3u, sh = (addr & 2u) * 8u;
+    uint32_t prev = lds32s(al);
+#pragma unroll
+    for (int j = 0; j < NWORDS; j++) {
+        const uint32_t nxt = lds32s(al + 4 * (j + 1));
+        out[j] = __funnelshift_rc(prev, nxt, sh);
+        prev = nxt;
+    }
+}
+// four bytes (each < 128 after the caller's masking) -> two half2 of (1024 + byte)
+__device__ __forceinline__ void bytes_to_h2(uint32_t w, __half2 &lo, __half2 &hi) {
+    lo = u32_as_h2(__byte_perm(w, 0x64646464u, 0x4140));
+    hi = u32_as_h2(__byte_perm(w, 0x64646464u, 0x4342));
+}
+
+// Thirty-two consecutive elements [e, e+32) (e a multiple of 32) of one weight row segment in shared
+// memory -> four 16-byte groups of eight f16 values, each the exact product rounded once (RNE).
+template <int T> __device__ __forceinline__ void dequant32(uint32_t seg, uint32_t e, uint4 (&out)[4]) {
+    if constexpr (T == GT_Q4_0) {
+        const uint32_t o = seg + 18u * (e >> 5);
+        const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)lds16s(o)));
+        const __half2 off = __float2half2_rn(1032.0f);  // 1024 + 8
+        uint32_t q[4];
+        lds_words_n<4>(o + 2, q);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {  // j = 0,1: low nibbles of bytes 0-7, 8-15; j = 2,3: high nibbles
+            const uint32_t w0 = ((j & 2) ? (q[2 * (j & 1)] >> 4) : q[2 * (j & 1)]) & 0x0F0F0F0Fu;
+            const uint32_t w1 = ((j & 2) ? (q[2 * (j & 1) + 1] >> 4) : q[2 * (j & 1) + 1]) & 0x0F0F0F0Fu;
+            __half2 a, b, cc, dd;
+            bytes_to_h2(w0, a, b);
+            bytes_to_h2(w1, cc, dd);
+            out[j].x = h2_as_u32(__hmul2(__hsub2(a, off), d2));
+            out[j].y = h2_as_u32(__hmul2(__hsub2(b, off), d2));
+            out[j].z = h2_as_u32(__hmul2(__hsub2(cc, off), d2));
+            out[j].w = h2_as_u32(__hmul2(__hsub2(dd, off), d2));
+        }
+    } else if constexpr (T == GT_Q8_0) {
+        const uint32_t o = seg + 34u * (e >> 5);
+        const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)lds16s(o)));
+        const __half2 off = __float2half2_rn(1152.0f);  // 1024 + 128
+        uint32_t q[8];
+        lds_words_n<8>(o + 2, q);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            __half2 a, b, cc, dd;
+            bytes_to_h2(q[2 * j] ^ 0x80808080u, a, b);
+            bytes_to_h2(q[2 * j + 1] ^ 0x80808080u, cc, dd);
+            out[j].x = h2_as_u32(__hmul2(__hsub2(a, off), d2));
+            out[j].y = h2_as_u32(__hmul2(__hsub2(b, off), d2));
+            out[j].z = h2_as_u32(__hmul2(__hsub2(cc, off), d2));
+            out[j].w = h2_as_u32(__hmul2(__hsub2(dd, off), d2));
+        }
+    } else {
+        const uint32_t o = seg + 210u * (e >> 8);
+        const uint32_t r = e & 255u, h = r >> 7, g = (r & 127u) >> 5;
+        uint32_t A[8], H[8];
+        lds_words_n<8>(o + 64 * h + 32 * (g & 1u), A);
+        lds_words_n<8>(o + 128 + 32 * h, H);
+        const float d = half_bits_to_float(lds16s(o + 208));
+        const float ds0 = d * (float)lds_s8s(o + 192 + 8 * h + 2 * g);
+        const float ds1 = d * (float)lds_s8s(o + 192 + 8 * h + 2 * g + 1);
+        const uint32_t hsh = 2 * g, ash = (g & 2u) ? 4u : 0u;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float ds = j < 2 ? ds0 : ds1;
+            const float c = -160.0f * ds;  // exact: ds has <= 18 significant bits
+            uint32_t res[4];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const uint32_t u = ((A[2 * j + i] >> ash) & 0x0F0F0F0Fu) | (((H[2 * j + i] >> hsh) & 0x03030303u) << 4);
+                // 128 + u spliced into an f32 mantissa; fma(128+u, ds, -160 ds) = ds*(u-32) exactly
+                const float f0 = fmaf(__uint_as_float(__byte_perm(u, 0x43000000u, 0x7044)), ds, c);
+                const float f1 = fmaf(__uint_as_float(__byte_perm(u, 0x43000000u, 0x7144)), ds, c);
+                const float f2 = fmaf(__uint_as_float(__byte_perm(u, 0x43000000u, 0x7244)), ds, c);
+                const float f3 = fmaf(__uint_as_float(__byte_perm(u, 0x43000000u, 0x7344)), ds, c);
+                res[2 * i] = h2_as_u32(__floats2half2_rn(f0, f1));
+                res[2 * i + 1] = h2_as_u32(__floats2half2_rn(f2, f3));
+            }
+            out[j] = make_uint4(res[0], res[1], res[2], res[3]);
+        }
+    }
+}
+
 struct TcCfg {
     uint32_t nchunks;     // ceil(k / 64)
     uint32_t stages;      // f16 operand ring depth
@@ -344,12 +431,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     if (tid == 0) {
         abort_flag = 0;
         for (uint32_t s = 0; s < c.stages; s++) {
-            mbar_init(&a_full[s], kTcDequantWarps);
+            mbar_init(&a_full[s], kTcSetWarps);
             mbar_init(&b_full[s], 1);
             mbar_init(&ab_empty[s], 1);
         }
         for (int s = 0; s < 2; s++) {
-            mbar_init(&raw_full[s], 1);
+            mbar_init(&raw_full[s], kTcDequantWarps * 32);
             mbar_init(&raw_empty[s], kTcDequantWarps);
         }
         mbar_init(&acc_full, 1);
@@ -382,35 +469,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     const uint32_t nraw = (c.nchunks + CPR - 1) / CPR;
 
     if (warp == kTcDequantWarps) {
-        // ======================= producer warp: bulk copies =======================
-        auto issue_raw = [&](uint32_t r) {
-            const uint32_t rs = r & 1u;
-            if (!mbar_wait(&raw_empty[rs], ((r >> 1) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) return false;
-            const uint32_t k0 = r * KR;
-            const uint32_t kb = min((uint32_t)KR, a.k - k0);
-            const uint32_t seg_bytes = (kb / QK) * BB;
-            const uint32_t rows = min((uint32_t)kTcRowsW, a.n - n0);
-            uint32_t total = 0;
-            for (uint32_t rr = lane; rr < rows; rr += 32) {
-                const uint8_t *src = wbase + (size_t)(n0 + rr) * row_bytes + (size_t)(k0 / QK) * BB;
-                total += ((uint32_t)((uintptr_t)src & 15u) + seg_bytes + 15u) & ~15u;
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-            if (lane == 0) mbar_expect_tx(&raw_full[rs], total);
-            __syncwarp();
-            for (uint32_t rr = lane; rr < rows; rr += 32) {
-                const uint8_t *src = wbase + (size_t)(n0 + rr) * row_bytes + (size_t)(k0 / QK) * BB;
-                const uint32_t pre = (uint32_t)((uintptr_t)src & 15u);
-                bulk_g2s(smem + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride, src - pre,
-                         (pre + seg_bytes + 15u) & ~15u, &raw_full[rs]);
-            }
-            return true;
-        };
-        bool ok = issue_raw(0);
-        for (uint32_t kc = 0; ok && kc < c.nchunks; kc++) {
-            if (kc % CPR == 0 && kc / CPR + 1 < nraw) ok = issue_raw(kc / CPR + 1);
-            if (!ok) break;
+        // ======================= producer warp: bulk copies of the packed activation tiles =======================
+        for (uint32_t kc = 0; kc < c.nchunks; kc++) {
             const uint32_t s = kc % c.stages;
             if (!mbar_wait(&ab_empty[s], ((kc / c.stages) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) break;
             if (lane == 0) {
@@ -440,46 +500,87 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         }
     } else {
         // ======================= dequantise warps, then epilogue =======================
-        for (uint32_t kc = 0; kc < c.nchunks; kc++) {
-            const uint32_t s = kc % c.stages;
-            const uint32_t r = kc / CPR, rs = r & 1u;
-            if (kc % CPR == 0 &&
-                !mbar_wait(&raw_full[rs], (r >> 1) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT))
-                break;
-            if (!mbar_wait(&ab_empty[s], ((kc / c.stages) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) break;
-            const uint32_t kvalid = min(64u, a.k - kc * 64);  // elements of this chunk inside K
-            const uint32_t raw = smem_base + c.raw_off + rs * raw_stage_bytes;
-            uint8_t *atile = smem + c.a_off + s * a_bytes;
-#pragma unroll
-            for (int i = 0; i < (kTcRowsW * 8) / (kTcDequantWarps * 32); i++) {
-                const uint32_t q = tid + i * (kTcDequantWarps * 32);
-                const uint32_t rr = q >> 3, j = q & 7u;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (8 * j < kvalid && n0 + rr < a.n) {
-                    const uint8_t *src = wbase + (size_t)(n0 + rr) * row_bytes + (size_t)((r * KR) / QK) * BB;
-                    const uint32_t seg = raw + rr * c.seg_stride + (uint32_t)((uintptr_t)src & 15u);
-                    v = dequant8<T>(seg, (kc % CPR) * 64 + 8 * j);
+        // Thread t of a set owns weight row t/2 and the 32-element half t%2 of every K chunk of the set:
+        // one GGML block (Q4_0 / Q8_0) or one 32-run of a Q6_K super-block per chunk, i.e. four 16-byte
+        // groups of the swizzled A tile.
+        const uint32_t set = warp / kTcSetWarps;
+        const uint32_t t = tid - set * (kTcSetWarps * 32);
+        const uint32_t rr = t >> 1, half = t & 1u;
+        const bool row_ok = n0 + rr < a.n;
+        const uint32_t row_lo4 = (uint32_t)((uintptr_t)(wbase + (size_t)(n0 + rr) * row_bytes) & 15u);
+        const uint32_t a_row_off = (rr >> 3) * 1024 + (rr & 7u) * 128;
+        // Raw weight rows are short (72..272 bytes per stage and row), too short for one bulk copy each to be
+        // efficient, so all dequantising threads stream them as 16-byte cp.async chunks, one raw stage ahead
+        // of the one being dequantised.  Each row is fetched as the 16-byte aligned superset of its (only
+        // 2-byte aligned) segment; readers skip the lead-in bytes.
+        const uint32_t dq_tid = tid;  // 0 .. kTcDequantWarps*32-1
+        auto issue_raw = [&](uint32_t r) {
+            const uint32_t rs = r & 1u;
+            const uint32_t k0 = r * KR;
+            const uint32_t kb = min((uint32_t)KR, a.k - k0);
+            const uint32_t seg_bytes = (kb / QK) * BB;
+            const uint32_t rows = min((uint32_t)kTcRowsW, a.n - n0);
+            const uint32_t cmax = (seg_bytes + 30u) >> 4;  // most 16-byte chunks a row can need
+            const uint32_t dst0 = smem_base + c.raw_off + rs * raw_stage_bytes;
+            const uint8_t *g0 = wbase + (size_t)n0 * row_bytes + (size_t)(k0 / QK) * BB;
+            for (uint32_t idx = dq_tid; idx < rows * cmax; idx += kTcDequantWarps * 32) {
+                const uint32_t row = idx / cmax, cc = idx - row * cmax;
+                const uint8_t *src = g0 + (size_t)row * row_bytes;
+                const uint32_t pre_b = (uint32_t)((uintptr_t)src & 15u);
+                if (cc * 16u < pre_b + seg_bytes) {
+                    const uint8_t *gp = src - pre_b + cc * 16u;
+                    const uint32_t dp = dst0 + row * c.seg_stride + cc * 16u;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dp), "l"(gp) : "memory");
                 }
-                *reinterpret_cast<uint4 *>(atile + (rr >> 3) * 1024 + (rr & 7u) * 128 + ((j ^ (rr & 7u)) << 4)) = v;
             }
-            fence_proxy_async_smem();
+            // arrive on the stage's barrier once this thread's copies have landed (one arrival per thread)
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&raw_full[rs])) : "memory");
+        };
+        issue_raw(0);
+        bool ok = true;
+        for (uint32_t r = 0; ok && r < nraw; r++) {
+            const uint32_t rs = r & 1u;
+            if (r + 1 < nraw) {
+                // slot (r+1)&1 was last used by raw stage r-1: every warp must have released it
+                if (!mbar_wait(&raw_empty[(r + 1) & 1u], (((r + 1) >> 1) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) break;
+                issue_raw(r + 1);
+            }
+            if (!mbar_wait(&raw_full[rs], (r >> 1) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT)) break;
+            const uint32_t pre = (row_lo4 + ((r * KR) / QK) * BB) & 15u;
+            const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
+            for (uint32_t kc = r * CPR + set; kc < min((r + 1) * CPR, c.nchunks); kc += 2) {
+                const uint32_t s = kc % c.stages;
+                if (!mbar_wait(&ab_empty[s], ((kc / c.stages) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t kvalid = min(64u, a.k - kc * 64);  // elements of this chunk inside K
+                uint8_t *arow = smem + c.a_off + s * a_bytes + a_row_off;
+                uint4 v[4];
+                if (row_ok && 32 * half < kvalid) {
+                    dequant32<T>(seg, (kc % CPR) * 64 + 32 * half, v);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) v[j] = make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    *reinterpret_cast<uint4 *>(arow + (((4 * half + j) ^ (rr & 7u)) << 4)) = v[j];
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&a_full[s]);
+            }
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&a_full[s]);
-                if (kc % CPR == CPR - 1 || kc + 1 == c.nchunks) mbar_arrive(&raw_empty[rs]);
-            }
+            if (lane == 0) mbar_arrive(&raw_empty[rs]);  // this warp is done reading raw stage r
         }
         // ---- epilogue: TMEM -> registers -> y ----
         if (!abort_flag && mbar_wait(&acc_full, 0, &abort_flag, a.status, ST_WAIT_MMA_TIMEOUT)) {
             tc_fence_after();
             const uint32_t q4 = warp & 3u;           // tensor-memory lane quarter this warp may read
-            const uint32_t chalf = warp >> 2;        // column half
             const uint32_t wrow = n0 + q4 * 32 + lane;
-            constexpr uint32_t kColsPerWarp = NT / 2;
 #pragma unroll 1
-            for (uint32_t c0 = 0; c0 < kColsPerWarp; c0 += 32) {
+            for (uint32_t col = (warp >> 2) * 32; col < NT; col += (kTcDequantWarps / 4) * 32) {
                 uint32_t v[32];
-                const uint32_t col = chalf * kColsPerWarp + c0;
                 tmem_ld_32x32(tmem_d + ((q4 * 32) << 16) + col, v);
                 tmem_ld_wait();
                 if (wrow < a.n) {
@@ -524,9 +625,26 @@ size_t qmm_tc_scratch_bytes(const QmmArgs &a, uint32_t nt, bool routed) {
     return header + tiles * nchunks * (size_t)nt * 128;
 }
 
-uint32_t qmm_tc_pick_nt(uint32_t rows_per_group, bool routed) {
-    if (routed) return 64;
-    return rows_per_group <= 64 ? 64 : rows_per_group <= 128 ? 128 : 256;
+// Activation rows per tile.  Routed calls use 64 (few rows per expert).  Dense calls take the tile that
+// minimises waves x per-tile cost, where a tile costs about max(NT, 160) (tensor time vs the fixed
+// dequantisation of its 128 weight rows); ties go to the larger tile, which dequantises less in total.
+uint32_t qmm_tc_pick_nt(uint32_t rows, uint32_t n, int sm_count, bool routed) {
+    if (routed || rows <= 64) return 64;
+    const uint32_t cands[3] = {256, 128, 64};
+    uint32_t best = 256;
+    uint64_t best_cost = ~0ull;
+    const uint32_t wt = (n + kTcRowsW - 1) / kTcRowsW;
+    for (uint32_t nt : cands) {
+        if (nt / 2 >= rows && nt > 64) continue;  // more than half of the tile would be padding
+        const uint64_t tiles = (uint64_t)wt * ((rows + nt - 1) / nt);
+        const uint64_t waves = (tiles + sm_count - 1) / (uint64_t)sm_count;
+        const uint64_t cost = waves * (nt > 160 ? nt : 160);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best = nt;
+        }
+    }
+    return best;
 }
 
 bool qmm_tc_supported(const QmmArgs &a) {
@@ -541,6 +659,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     TcCfg c{};
     c.nchunks = (a.k + 63) / 64;
     c.seg_stride = round_up_u((KR / QK) * BB + 15, 16) + 16;
+    if ((c.seg_stride / 16) % 2 == 0) c.seg_stride += 16;  // odd multiple of 16 B: rows spread over the banks
     const uint32_t a_bytes = kTcRowsW * 128, b_bytes = NT * 128;
     const uint32_t raw_bytes = 2 * kTcRowsW * c.seg_stride;
     const uint32_t limit = 220 * 1024;

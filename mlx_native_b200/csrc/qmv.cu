@@ -139,10 +139,9 @@ __global__ void __launch_bounds__(256) qmv_simple_kernel(const QmvArgs a) {
 // =================================================================================================
 // qmv_stream
 // =================================================================================================
-constexpr int kConsumerWarps = 8;
-constexpr int kStreamThreads = (kConsumerWarps + 1) * 32;
+constexpr int kMaxWarps = 16;     // warps per CTA: 16 where the register budget allows (m <= 2), else 8
 constexpr int kRows = 4;         // weight rows per pipeline stage
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 16;
 
 struct StreamCfg {
     uint32_t ks;          // K-slice length in elements (multiple of 256)
@@ -417,15 +416,18 @@ __device__ __forceinline__ void task_q6_k(const uint32_t (&seg)[kRows], uint32_t
     }
 }
 
-template <int T, int M>
-__global__ void __launch_bounds__(kStreamThreads, 1) qmv_stream_kernel(const QmvArgs a, const StreamCfg c) {
+template <int T, int M, int NW>
+__global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a, const StreamCfg c) {
+    constexpr int kStreamThreads = NW * 32;
+    constexpr int kConsumerWarps = NW;
     extern __shared__ __align__(1024) uint8_t smem[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages];
-    __shared__ __align__(8) uint64_t empty_bar[kMaxStages];
+    __shared__ uint32_t done_cnt[kMaxStages];  // warps of the owning group that have finished with a slot
     __shared__ volatile uint32_t abort_flag;
 
     constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES;
     constexpr int E = StreamTraits<T>::E, SUB = StreamTraits<T>::SUB;
+    constexpr int V = kRows * M;
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t row_bytes = (a.k / QK) * BB;
     const uint32_t slice_bytes = (c.ks / QK) * BB;
@@ -435,7 +437,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1) qmv_stream_kernel(const Qmv
         abort_flag = 0;
         for (uint32_t s = 0; s < c.stages; s++) {
             mbar_init(&full_bar[s], 1);
-            mbar_init(&empty_bar[s], c.wpg);
+            done_cnt[s] = 0;
         }
         mbar_init_fence();
     }
@@ -444,108 +446,70 @@ __global__ void __launch_bounds__(kStreamThreads, 1) qmv_stream_kernel(const Qmv
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t xs = smem_base + c.xs_off;
     const uint32_t xsum = smem_base + c.xsum_off;
-    float *red = reinterpret_cast<float *>(smem + c.red_off);  // [stages][8 warps][kRows*M]
+    float *red = reinterpret_cast<float *>(smem + c.red_off);  // [stages][8 warps][V]
     const uint32_t stage_bytes = kRows * c.seg_stride;
 
-    if (warp == kConsumerWarps) {
-        // ======================= producer + finishing warp =======================
-        Walk wi, wd;  // issue cursor, done cursor
-        bool more_issue = wi.init(a, c);
-        bool more_done = more_issue;
-        wd = wi;
-        uint32_t it_issue = 0, it_done = 0;
+    // Every warp belongs to a group of c.wpg warps; group cg owns iterations it with it % ngrp == cg and,
+    // because c.stages is a multiple of ngrp, also the ring slots those iterations use.  Warp 0 of a group
+    // refills a slot (bulk copies of the next kRows row segments) as soon as the group has finished with it.
+    const uint32_t cg = warp / c.wpg, wig = warp % c.wpg;
+    const bool leader = wig == 0;
 
-        auto issue = [&](const Walk &w, uint32_t it) {
-            const uint32_t slot = it % c.stages;
-            bool valid;
-            const uint8_t *wb = problem_weights(a, w.p, valid);
-            const uint32_t row0 = w.g * kRows;
-            const uint32_t nrows = min((uint32_t)kRows, a.n - row0);
-            const uint32_t kb = min(c.ks, a.k - w.s * c.ks);            // elements in this slice
-            const uint32_t seg_bytes = (kb / QK) * BB;
-            if (lane == 0) {
-                uint32_t total = 0;
-                if (valid)
-                    for (uint32_t r = 0; r < nrows; r++) {
-                        const uint8_t *src = wb + (size_t)(row0 + r) * row_bytes + (size_t)w.s * slice_bytes;
-                        const uint32_t pre = (uint32_t)((uintptr_t)src & 15u);
-                        total += (pre + seg_bytes + 15u) & ~15u;
-                    }
-                if (total == 0) {
-                    mbar_arrive(&full_bar[slot]);
-                } else {
-                    mbar_expect_tx(&full_bar[slot], total);
-                    for (uint32_t r = 0; r < nrows; r++) {
-                        const uint8_t *src = wb + (size_t)(row0 + r) * row_bytes + (size_t)w.s * slice_bytes;
-                        const uint32_t pre = (uint32_t)((uintptr_t)src & 15u);
-                        bulk_g2s(smem + c.stage_off + slot * stage_bytes + r * c.seg_stride, src - pre,
-                                 (pre + seg_bytes + 15u) & ~15u, &full_bar[slot]);
-                    }
-                }
-            }
-        };
+    // lanes 0..kRows-1 of a group's leader warp each issue one row-segment copy of iteration `it`
+    auto issue = [&](const Walk &w, uint32_t it) {
+        const uint32_t slot = it % c.stages;
+        bool valid;
+        const uint8_t *wb = problem_weights(a, w.p, valid);
+        const uint32_t row0 = w.g * kRows;
+        const uint32_t nrows = min((uint32_t)kRows, a.n - row0);
+        const uint32_t kb = min(c.ks, a.k - w.s * c.ks);  // elements in this slice
+        const uint32_t seg_bytes = (kb / QK) * BB;
+        const uint8_t *src = wb + (size_t)(row0 + lane) * row_bytes + (size_t)w.s * slice_bytes;
+        const uint32_t pre = (uint32_t)((uintptr_t)src & 15u);
+        const uint32_t bytes = (valid && lane < nrows) ? ((pre + seg_bytes + 15u) & ~15u) : 0u;
+        uint32_t total = bytes;
+        total += __shfl_xor_sync(0xffffffffu, total, 1);
+        total += __shfl_xor_sync(0xffffffffu, total, 2);
+        if (lane == 0) {
+            if (total == 0) mbar_arrive(&full_bar[slot]);
+            else mbar_expect_tx(&full_bar[slot], total);
+        }
+        __syncwarp();
+        if (bytes) bulk_g2s(smem + c.stage_off + slot * stage_bytes + lane * c.seg_stride, src - pre, bytes, &full_bar[slot]);
+    };
 
-        // prime the ring
-        while (more_issue && it_issue < c.stages) {
-            issue(wi, it_issue);
-            it_issue++;
-            more_issue = wi.next(a, c);
-        }
-        while (more_done) {
-            const uint32_t slot = it_done % c.stages;
-            if (!mbar_wait(&empty_bar[slot], (it_done / c.stages) & 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) break;
-            // finish the reduction of this stage: lane (r, t) sums the wpg partials in warp order
-            const uint32_t row0 = wd.g * kRows;
-            if (lane < kRows * M) {
-                const uint32_t r = lane / M, t = lane % M;
-                if (row0 + r < a.n) {
-                    float s = 0.0f;
-                    for (uint32_t w8 = 0; w8 < c.wpg; w8++) s += red[(slot * kConsumerWarps + w8) * (kRows * M) + lane];
-                    float *yp = a.y + (a.ids ? (size_t)wd.p * a.n : (size_t)t * a.n) + row0 + r;
-                    if (wd.s == 0) *yp = s;
-                    else *yp += s;
-                }
-            }
-            __syncwarp();
-            it_done++;
-            more_done = wd.next(a, c);
-            if (more_issue) {
-                issue(wi, it_issue);
-                it_issue++;
-                more_issue = wi.next(a, c);
-            }
-        }
-        if (abort_flag) {  // let copies in flight land before the CTA's shared memory is released
-            for (int i = 0; i < 200; i++) __nanosleep(5000);
-        }
-        return;
+    Walk w, wi;  // compute cursor, issue cursor (c.stages iterations ahead)
+    bool more = w.init(a, c);
+    wi = w;
+    bool more_issue = more;
+    uint32_t it = 0, it_issue = 0;
+    // prime the ring: each group's leader issues the iterations it owns among the first c.stages
+    while (more_issue && it_issue < c.stages) {
+        if (leader && it_issue % ngrp == cg) issue(wi, it_issue);
+        it_issue++;
+        more_issue = wi.next(a, c);
     }
 
-    // ======================= consumer warps =======================
-    const uint32_t cg = warp / c.wpg, wig = warp % c.wpg;
-    Walk w;
-    bool more = w.init(a, c);
-    uint32_t it = 0;
     uint32_t cur_item = 0xFFFFFFFFu, cur_slice = 0xFFFFFFFFu;
     const uint32_t ks4 = c.ks >> 2;
     while (more) {
         if (w.item != cur_item || w.s != cur_slice) {
-            // ---- stage the activation slice (all consumer warps) ----
+            // ---- stage the activation slice (all warps) ----
             cur_item = w.item;
             cur_slice = w.s;
-            named_bar_sync(1, kConsumerWarps * 32);  // everyone is done with the previous slice
+            named_bar_sync(1, kStreamThreads);  // everyone is done with the previous slice
             const float *xg = a.x + (a.ids ? (size_t)(w.p / a.top_k) * a.k : 0);
             const uint32_t k0 = w.s * c.ks;
-            for (uint32_t idx = tid; idx < M * ks4; idx += kConsumerWarps * 32) {
+            for (uint32_t idx = tid; idx < M * ks4; idx += kStreamThreads) {
                 const uint32_t t = idx / ks4, f = idx % ks4;
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (k0 + 4 * f < a.k) v = __ldg(reinterpret_cast<const float4 *>(xg + (size_t)t * a.k + k0) + f);
                 *reinterpret_cast<float4 *>(smem + c.xs_off + (size_t)(t * ks4 + xswz<T>(f)) * 16) = v;
             }
-            named_bar_sync(1, kConsumerWarps * 32);
+            named_bar_sync(1, kStreamThreads);
             if constexpr (T != GT_Q8_0) {
                 const uint32_t nsub = c.ks / SUB;
-                for (uint32_t idx = tid; idx < M * nsub; idx += kConsumerWarps * 32) {
+                for (uint32_t idx = tid; idx < M * nsub; idx += kStreamThreads) {
                     const uint32_t t = idx / nsub, sb = idx % nsub;
                     float s = 0.0f;
 #pragma unroll
@@ -559,10 +523,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1) qmv_stream_kernel(const Qmv
                     }
                     reinterpret_cast<float *>(smem + c.xsum_off)[t * nsub + sb] = s;
                 }
-                named_bar_sync(1, kConsumerWarps * 32);
+                named_bar_sync(1, kStreamThreads);
             }
         }
-        if (it % ngrp == cg && !abort_flag) {
+        if (it % ngrp == cg) {
             const uint32_t slot = it % c.stages;
             bool valid;
             const uint8_t *wb = problem_weights(a, w.p, valid);
@@ -590,7 +554,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1) qmv_stream_kernel(const Qmv
                 }
             }
             // butterfly reduce-scatter across the warp: V values per lane -> lane L holds total number idx(L)
-            constexpr int V = kRows * M;
             constexpr int VP = V <= 4 ? 4 : V <= 8 ? 8 : V <= 16 ? 16 : 32;
             float v[VP];
 #pragma unroll
@@ -619,11 +582,45 @@ __global__ void __launch_bounds__(kStreamThreads, 1) qmv_stream_kernel(const Qmv
             }
             constexpr uint32_t kIdleMask = VP >= 32 ? 0u : (32u / VP) - 1u;  // lanes whose low bits are 0 write
             if ((lane & kIdleMask) == 0 && idx < V) red[(slot * kConsumerWarps + wig) * V + idx] = v[0];
+            // No warp waits for another: the last warp of the group to finish with this slot (counted in
+            // shared memory) adds up the group's partial sums, writes y and refills the slot.
             __syncwarp();
-            if (lane == 0) mbar_arrive(&empty_bar[slot]);
+            uint32_t last = 0;
+            if (lane == 0) {
+                __threadfence_block();
+                last = (atomicAdd(&done_cnt[slot], 1u) == c.wpg - 1u) ? 1u : 0u;
+                if (last) {
+                    done_cnt[slot] = 0;
+                    __threadfence_block();
+                }
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                if (lane < V) {
+                    const uint32_t r = lane / M, t = lane % M;
+                    if (row0 + r < a.n && landed) {
+                        float s = 0.0f;
+                        for (uint32_t w8 = 0; w8 < c.wpg; w8++)
+                            s += *reinterpret_cast<volatile float *>(&red[(slot * kConsumerWarps + w8) * V + lane]);
+                        float *yp = a.y + (a.ids ? (size_t)w.p * a.n : (size_t)t * a.n) + row0 + r;
+                        if (w.s == 0) *yp = s;
+                        else *yp += s;
+                    }
+                }
+                __syncwarp();
+                if (more_issue && !abort_flag) issue(wi, it_issue);  // iteration it + c.stages reuses this slot
+            }
+        }
+        // keep the issue cursor c.stages iterations ahead of the compute cursor
+        if (more_issue) {
+            it_issue++;
+            more_issue = wi.next(a, c);
         }
         it++;
         more = w.next(a, c);
+    }
+    if (abort_flag) {  // let copies in flight land before the CTA's shared memory is released
+        for (int i = 0; i < 200; i++) __nanosleep(5000);
     }
 }
 
@@ -633,7 +630,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1) qmv_stream_kernel(const Qmv
 static inline uint32_t round_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
 
 template <int T>
-static bool stream_config(const QmvArgs &a, int sm_count, size_t smem_limit, StreamCfg &c, uint32_t &grid, size_t &smem) {
+static bool stream_config(const QmvArgs &a, int sm_count, size_t smem_limit, uint32_t nw, StreamCfg &c, uint32_t &grid, size_t &smem) {
+    const uint32_t kConsumerWarps = nw;
     constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES;
     constexpr int E = StreamTraits<T>::E, SUB = StreamTraits<T>::SUB;
     if (a.k % 256 != 0 || a.k < 256) return false;
@@ -664,6 +662,9 @@ static bool stream_config(const QmvArgs &a, int sm_count, size_t smem_limit, Str
     uint32_t tasks = ks / E;
     uint32_t wpg = 1;
     while (wpg < kConsumerWarps && wpg * 32 < tasks) wpg *= 2;
+    const uint32_t ngrp = kConsumerWarps / wpg;
+    stages = stages / ngrp * ngrp;   // every group refills the ring slots it owns
+    if (stages < ngrp) return false;
     c.ks = ks;
     c.nslices = nslices;
     c.wpg = wpg;
@@ -689,18 +690,18 @@ static bool stream_config(const QmvArgs &a, int sm_count, size_t smem_limit, Str
     return grid > 0;
 }
 
-template <int T, int M> static cudaError_t launch_stream_tm(const QmvArgs &a, const StreamCfg &c, uint32_t grid, size_t smem,
+template <int T, int M, int NW> static cudaError_t launch_stream_tm(const QmvArgs &a, const StreamCfg &c, uint32_t grid, size_t smem,
                                                             cudaStream_t st) {
     static size_t attr_smem[64] = {};  // largest dynamic shared-memory size enabled so far, per device
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (smem > attr_smem[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(qmv_stream_kernel<T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(qmv_stream_kernel<T, M, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         attr_smem[dev] = smem;
     }
-    qmv_stream_kernel<T, M><<<grid, kStreamThreads, smem, st>>>(a, c);
+    qmv_stream_kernel<T, M, NW><<<grid, NW * 32, smem, st>>>(a, c);
     return cudaGetLastError();
 }
 
@@ -716,11 +717,12 @@ template <int T> static cudaError_t launch_t(const QmvArgs &a, bool want_stream,
     StreamCfg c{};
     uint32_t grid = 0;
     size_t smem = 0;
-    const bool stream = want_stream && stream_config<T>(a, sm_count, 227 * 1024 - 2048, c, grid, smem);
+    const uint32_t nw = a.m <= 2 ? 16 : 8;
+    const bool stream = want_stream && stream_config<T>(a, sm_count, 227 * 1024 - 2048, nw, c, grid, smem);
     *kname = stream ? "qmv_stream" : "qmv_simple";
 #define MLXN_CASE(MM)                                                                   \
     case MM:                                                                            \
-        return stream ? launch_stream_tm<T, MM>(a, c, grid, smem, st) : launch_simple_tm<T, MM>(a, st);
+        return stream ? launch_stream_tm<T, MM, (MM <= 2 ? 16 : 8)>(a, c, grid, smem, st) : launch_simple_tm<T, MM>(a, st);
     switch (a.m) {
         MLXN_CASE(1)
         MLXN_CASE(2)
