@@ -32,16 +32,37 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t *bar, uint32_t parity
     return ok;
 }
 
+// try_wait that lets the hardware suspend the thread for up to `ns` nanoseconds while the phase is pending,
+// so that a waiting warp does not compete for issue slots with the warps doing the work.
+__device__ __forceinline__ uint32_t mbar_try_wait_suspend(uint64_t *bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+        : "memory");
+    return ok;
+}
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
 // Bounded wait.  Returns false if the wait gave up (or another thread already raised `abort`).
 // `abort` is a CTA-shared word; `status` the device status word the host reads after the launch.
-constexpr uint32_t kWaitSpinLimit = 1u << 22;  // ~4M polls with back-off: far beyond any legitimate wait
+// A legitimate wait lasts microseconds; the limit is two seconds of wall time.
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort, uint32_t *status,
                                           uint32_t code) {
     if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < kWaitSpinLimit; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
         if (*abort) return false;
-        __nanosleep(i > 4096 ? 256 : 20);  // back off at once: polling steals issue slots from working warps
+        if (global_timer_ns() - t0 > kWaitLimitNs) break;
     }
     *abort = 1;
     if (status) atomicCAS(status, 0u, code);

@@ -392,6 +392,18 @@ template <int T> __device__ __forceinline__ void dequant32(uint32_t seg, uint32_
     }
 }
 
+// position in a ring of `stages` slots plus the phase bit of the slot's current use (no divisions)
+struct RingPos {
+    uint32_t s = 0, ph = 0;
+    __device__ __forceinline__ void adv(uint32_t n, uint32_t stages) {
+        s += n;
+        while (s >= stages) {
+            s -= stages;
+            ph ^= 1u;
+        }
+    }
+};
+
 struct TcCfg {
     uint32_t nchunks;     // ceil(k / 64)
     uint32_t stages;      // f16 operand ring depth
@@ -470,9 +482,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
 
     if (warp == kTcDequantWarps) {
         // ======================= producer warp: bulk copies of the packed activation tiles =======================
-        for (uint32_t kc = 0; kc < c.nchunks; kc++) {
-            const uint32_t s = kc % c.stages;
-            if (!mbar_wait(&ab_empty[s], ((kc / c.stages) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) break;
+        RingPos rp;
+        for (uint32_t kc = 0; kc < c.nchunks; kc++, rp.adv(1, c.stages)) {
+            const uint32_t s = rp.s;
+            if (!mbar_wait(&ab_empty[s], rp.ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) break;
             if (lane == 0) {
                 mbar_expect_tx(&b_full[s], b_bytes);
                 bulk_g2s(smem + c.b_off + s * b_bytes, xpack + ((size_t)tt * c.nchunks + kc) * (size_t)b_bytes, b_bytes,
@@ -482,8 +495,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     } else if (warp == kTcDequantWarps + 1) {
         // ======================= MMA warp: one thread issues tcgen05.mma =======================
         constexpr uint32_t idesc = umma_idesc_f16(kTcRowsW, NT);
-        for (uint32_t kc = 0; kc < c.nchunks; kc++) {
-            const uint32_t s = kc % c.stages, ph = (kc / c.stages) & 1u;
+        RingPos rp;
+        for (uint32_t kc = 0; kc < c.nchunks; kc++, rp.adv(1, c.stages)) {
+            const uint32_t s = rp.s, ph = rp.ph;
             if (!mbar_wait(&a_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT)) break;
             if (!mbar_wait(&b_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT)) break;
             tc_fence_after();
@@ -538,6 +552,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         };
         issue_raw(0);
         bool ok = true;
+        RingPos rp;
+        rp.adv(set, c.stages);  // this set's first chunk is kc = set
         for (uint32_t r = 0; ok && r < nraw; r++) {
             const uint32_t rs = r & 1u;
             if (r + 1 < nraw) {
@@ -548,9 +564,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             if (!mbar_wait(&raw_full[rs], (r >> 1) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT)) break;
             const uint32_t pre = (row_lo4 + ((r * KR) / QK) * BB) & 15u;
             const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
-            for (uint32_t kc = r * CPR + set; kc < min((r + 1) * CPR, c.nchunks); kc += 2) {
-                const uint32_t s = kc % c.stages;
-                if (!mbar_wait(&ab_empty[s], ((kc / c.stages) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) {
+            for (uint32_t kc = r * CPR + set; kc < min((r + 1) * CPR, c.nchunks); kc += 2, rp.adv(2, c.stages)) {
+                const uint32_t s = rp.s;
+                if (!mbar_wait(&ab_empty[s], rp.ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) {
                     ok = false;
                     break;
                 }
@@ -558,7 +574,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                 uint8_t *arow = smem + c.a_off + s * a_bytes + a_row_off;
                 uint4 v[4];
                 if (row_ok && 32 * half < kvalid) {
-                    dequant32<T>(seg, (kc % CPR) * 64 + 32 * half, v);
+                    dequant32<T>(seg, (kc - r * CPR) * 64 + 32 * half, v);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 4; j++) v[j] = make_uint4(0, 0, 0, 0);

@@ -146,8 +146,10 @@ constexpr int kMaxStages = 16;
 struct StreamCfg {
     uint32_t ks;          // K-slice length in elements (multiple of 256)
     uint32_t nslices;
-    uint32_t wpg;         // consumer warps cooperating on one stage (power of two, <= 8)
-    uint32_t stages;      // ring depth
+    uint32_t wpg;         // warps cooperating on one stage (power of two)
+    uint32_t lg_wpg;
+    uint32_t stages;      // ring depth (power of two, multiple of the number of warp groups)
+    uint32_t lg_stages;
     uint32_t seg_stride;  // shared-memory bytes reserved per row segment (multiple of 16)
     uint32_t cpp;         // CTAs per problem
     uint32_t xs_off, xsum_off, red_off, stage_off;  // byte offsets into dynamic shared memory
@@ -191,9 +193,8 @@ struct Walk {
         }
         return false;
     }
-    // advance to the next (slice, group); returns false at the end of the walk
-    __device__ __forceinline__ bool next(const QmvArgs &a, const StreamCfg &c) {
-        if (++g < g1) return true;
+    // move to the first group of the next slice (or of the next work item); false at the end of the walk
+    __device__ __forceinline__ bool next_slice(const QmvArgs &a, const StreamCfg &c) {
         if (++s < c.nslices) {
             g = g0;
             return true;
@@ -205,6 +206,18 @@ struct Walk {
             item += item_step;
         }
         return false;
+    }
+    // advance by n iterations; false if the walk ends first
+    __device__ __forceinline__ bool advance(uint32_t n, const QmvArgs &a, const StreamCfg &c) {
+        for (;;) {
+            const uint32_t rem = g1 - g;
+            if (n < rem) {
+                g += n;
+                return true;
+            }
+            n -= rem;
+            if (!next_slice(a, c)) return false;
+        }
     }
 };
 
@@ -452,12 +465,12 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
     // Every warp belongs to a group of c.wpg warps; group cg owns iterations it with it % ngrp == cg and,
     // because c.stages is a multiple of ngrp, also the ring slots those iterations use.  Warp 0 of a group
     // refills a slot (bulk copies of the next kRows row segments) as soon as the group has finished with it.
-    const uint32_t cg = warp / c.wpg, wig = warp % c.wpg;
+    const uint32_t cg = warp >> c.lg_wpg, wig = warp & (c.wpg - 1u);
     const bool leader = wig == 0;
 
     // lanes 0..kRows-1 of a group's leader warp each issue one row-segment copy of iteration `it`
     auto issue = [&](const Walk &w, uint32_t it) {
-        const uint32_t slot = it % c.stages;
+        const uint32_t slot = it & (c.stages - 1u);
         bool valid;
         const uint8_t *wb = problem_weights(a, w.p, valid);
         const uint32_t row0 = w.g * kRows;
@@ -478,30 +491,33 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
         if (bytes) bulk_g2s(smem + c.stage_off + slot * stage_bytes + lane * c.seg_stride, src - pre, bytes, &full_bar[slot]);
     };
 
-    Walk w, wi;  // compute cursor, issue cursor (c.stages iterations ahead)
+    Walk w;
     bool more = w.init(a, c);
-    wi = w;
-    bool more_issue = more;
-    uint32_t it = 0, it_issue = 0;
+    const uint32_t smask = c.stages - 1, gmask = ngrp - 1;
     // prime the ring: each group's leader issues the iterations it owns among the first c.stages
-    while (more_issue && it_issue < c.stages) {
-        if (leader && it_issue % ngrp == cg) issue(wi, it_issue);
-        it_issue++;
-        more_issue = wi.next(a, c);
+    if (more && leader) {
+        for (uint32_t i = cg; i < c.stages; i += ngrp) {
+            Walk t = w;
+            if (!t.advance(i, a, c)) break;
+            issue(t, i);
+        }
     }
 
-    uint32_t cur_item = 0xFFFFFFFFu, cur_slice = 0xFFFFFFFFu;
+    // Each warp steps through the whole walk slice by slice (every warp stages every activation slice) but
+    // jumps straight between the iterations its group owns: it, it + ngrp, ...
+    uint32_t it = 0;        // iteration number of the cursor position
+    uint32_t skip = cg;     // iterations between the cursor and this group's next own iteration
     const uint32_t ks4 = c.ks >> 2;
+    bool staged = false;
     while (more) {
-        if (w.item != cur_item || w.s != cur_slice) {
-            // ---- stage the activation slice (all warps) ----
-            cur_item = w.item;
-            cur_slice = w.s;
+        if (!staged) {
+            // ---- stage the activation slice of (w.item, w.s) (all warps) ----
+            staged = true;
             named_bar_sync(1, kStreamThreads);  // everyone is done with the previous slice
             const float *xg = a.x + (a.ids ? (size_t)(w.p / a.top_k) * a.k : 0);
             const uint32_t k0 = w.s * c.ks;
             for (uint32_t idx = tid; idx < M * ks4; idx += kStreamThreads) {
-                const uint32_t t = idx / ks4, f = idx % ks4;
+                const uint32_t t = idx / ks4, f = idx - t * ks4;
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (k0 + 4 * f < a.k) v = __ldg(reinterpret_cast<const float4 *>(xg + (size_t)t * a.k + k0) + f);
                 *reinterpret_cast<float4 *>(smem + c.xs_off + (size_t)(t * ks4 + xswz<T>(f)) * 16) = v;
@@ -510,7 +526,7 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
             if constexpr (T != GT_Q8_0) {
                 const uint32_t nsub = c.ks / SUB;
                 for (uint32_t idx = tid; idx < M * nsub; idx += kStreamThreads) {
-                    const uint32_t t = idx / nsub, sb = idx % nsub;
+                    const uint32_t t = idx / nsub, sb = idx - t * nsub;
                     float s = 0.0f;
 #pragma unroll
                     for (int q = 0; q < SUB / 4; q++) {
@@ -526,8 +542,19 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
                 named_bar_sync(1, kStreamThreads);
             }
         }
-        if (it % ngrp == cg) {
-            const uint32_t slot = it % c.stages;
+        const uint32_t rem = w.g1 - w.g;  // iterations left in this slice, cursor included
+        if (skip >= rem) {                // this group's next iteration lies beyond this slice
+            skip -= rem;
+            it += rem;
+            more = w.next_slice(a, c);
+            staged = false;
+            continue;
+        }
+        w.g += skip;
+        it += skip;
+        skip = ngrp;
+        {
+            const uint32_t slot = it & smask;
             bool valid;
             const uint8_t *wb = problem_weights(a, w.p, valid);
             const uint32_t row0 = w.g * kRows;
@@ -545,7 +572,7 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
             for (int r = 0; r < kRows; r++)
 #pragma unroll
                 for (int t = 0; t < M; t++) acc[r][t] = 0.0f;
-            const bool landed = !abort_flag && mbar_wait(&full_bar[slot], (it / c.stages) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
+            const bool landed = !abort_flag && mbar_wait(&full_bar[slot], (it >> c.lg_stages) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
             if (valid && landed) {
                 for (uint32_t task = wig * 32 + lane; task < ntasks; task += 32 * c.wpg) {
                     if constexpr (T == GT_Q4_0) task_q4_0<M>(seg, task, xs, xsum, c.ks, acc);
@@ -608,16 +635,12 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
                     }
                 }
                 __syncwarp();
-                if (more_issue && !abort_flag) issue(wi, it_issue);  // iteration it + c.stages reuses this slot
+                if (!abort_flag) {  // iteration it + c.stages reuses this slot
+                    Walk t = w;
+                    if (t.advance(c.stages, a, c)) issue(t, it + c.stages);
+                }
             }
         }
-        // keep the issue cursor c.stages iterations ahead of the compute cursor
-        if (more_issue) {
-            it_issue++;
-            more_issue = wi.next(a, c);
-        }
-        it++;
-        more = w.next(a, c);
     }
     if (abort_flag) {  // let copies in flight land before the CTA's shared memory is released
         for (int i = 0; i < 200; i++) __nanosleep(5000);
@@ -663,8 +686,17 @@ static bool stream_config(const QmvArgs &a, int sm_count, size_t smem_limit, uin
     uint32_t wpg = 1;
     while (wpg < kConsumerWarps && wpg * 32 < tasks) wpg *= 2;
     const uint32_t ngrp = kConsumerWarps / wpg;
-    stages = stages / ngrp * ngrp;   // every group refills the ring slots it owns
-    if (stages < ngrp) return false;
+    uint32_t p2 = 1, lg = 0;
+    while (p2 * 2 <= stages) {
+        p2 *= 2;
+        lg++;
+    }
+    stages = p2;                      // power of two: ring slot and phase come from masks and shifts
+    if (stages < ngrp || stages < 2) return false;   // every group refills the ring slots it owns
+    uint32_t lg_wpg = 0;
+    while ((1u << lg_wpg) < wpg) lg_wpg++;
+    c.lg_stages = lg;
+    c.lg_wpg = lg_wpg;
     c.ks = ks;
     c.nslices = nslices;
     c.wpg = wpg;
