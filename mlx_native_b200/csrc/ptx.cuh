@@ -55,14 +55,23 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // `abort` is a CTA-shared word; `status` the device status word the host reads after the launch.
 // A legitimate wait lasts microseconds; the limit is two seconds of wall time.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// `sleep_ns` > 0 spaces the polls out (for warps that are not on the critical path: each poll costs issue
+// slots that working warps could use).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort, uint32_t *status,
-                                          uint32_t code) {
+                                          uint32_t code, uint32_t sleep_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
-    for (;;) {
-        if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
-        if (*abort) return false;
-        if (global_timer_ns() - t0 > kWaitLimitNs) break;
+    for (uint32_t polls = 1;; polls++) {
+        if (sleep_ns == 0xFFFFFFFFu) {  // pure spin (lowest wake-up latency, costs issue slots)
+            if (mbar_try_wait(bar, parity)) return true;
+        } else {
+            if (sleep_ns) __nanosleep(sleep_ns);
+            if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
+        }
+        if ((polls & 63u) == 0) {
+            if (*abort) return false;
+            if (global_timer_ns() - t0 > kWaitLimitNs) break;
+        }
     }
     *abort = 1;
     if (status) atomicCAS(status, 0u, code);

@@ -17,6 +17,8 @@
 //             tcgen05 kernel does not take and as an on-device cross-check.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -211,7 +213,7 @@ constexpr int kTcThreads = (kTcDequantWarps + 2) * 32;  // + producer warp + MMA
 constexpr int kTcRowsW = 128;                           // weight rows per tile (UMMA M)
 
 template <int T> struct TcTraits;
-template <> struct TcTraits<GT_Q4_0> { static constexpr int KR = 128; };  // raw-stage K extent
+template <> struct TcTraits<GT_Q4_0> { static constexpr int KR = 256; };  // raw-stage K extent
 template <> struct TcTraits<GT_Q8_0> { static constexpr int KR = 128; };
 template <> struct TcTraits<GT_Q6_K> { static constexpr int KR = 256; };
 
@@ -409,6 +411,7 @@ struct TcCfg {
     uint32_t stages;      // f16 operand ring depth
     uint32_t seg_stride;  // bytes reserved per raw row segment
     uint32_t a_off, b_off, raw_off;
+    uint32_t debug;       // experiment switches: 1 = skip dequantisation, 2 = skip raw copies, 4 = skip MMA, 8 = skip B copies
 };
 
 // grid (ceil(n/128), tile count bound); kTcThreads threads; 1 CTA per SM (dynamic shared memory ~200 KiB).
@@ -448,7 +451,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             mbar_init(&ab_empty[s], 1);
         }
         for (int s = 0; s < 2; s++) {
-            mbar_init(&raw_full[s], kTcDequantWarps * 32);
+            mbar_init(&raw_full[s], kTcDequantWarps);
             mbar_init(&raw_empty[s], kTcDequantWarps);
         }
         mbar_init(&acc_full, 1);
@@ -479,14 +482,19 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     const uint32_t a_bytes = kTcRowsW * 128, b_bytes = NT * 128;
     const uint32_t raw_stage_bytes = kTcRowsW * c.seg_stride;
     const uint32_t nraw = (c.nchunks + CPR - 1) / CPR;
+    // wait styles: the single producer / MMA warps spin (they are the critical path and cost one warp's issue
+    // slots); the dequantising warps space their polls out
+    const uint32_t wmode_cr = (c.debug & 32u) ? 0u : 0xFFFFFFFFu;
+    const uint32_t wmode_dq = (c.debug & 16u) ? 0xFFFFFFFFu : 32u;
 
     if (warp == kTcDequantWarps) {
         // ======================= producer warp: bulk copies of the packed activation tiles =======================
         RingPos rp;
         for (uint32_t kc = 0; kc < c.nchunks; kc++, rp.adv(1, c.stages)) {
             const uint32_t s = rp.s;
-            if (!mbar_wait(&ab_empty[s], rp.ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) break;
-            if (lane == 0) {
+            if (!mbar_wait(&ab_empty[s], rp.ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_cr)) break;
+            if (lane == 0 && (c.debug & 8u)) mbar_arrive(&b_full[s]);
+            if (lane == 0 && !(c.debug & 8u)) {
                 mbar_expect_tx(&b_full[s], b_bytes);
                 bulk_g2s(smem + c.b_off + s * b_bytes, xpack + ((size_t)tt * c.nchunks + kc) * (size_t)b_bytes, b_bytes,
                          &b_full[s]);
@@ -494,23 +502,38 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         }
     } else if (warp == kTcDequantWarps + 1) {
         // ======================= MMA warp: one thread issues tcgen05.mma =======================
+        // The issuing thread is on the critical path of every K chunk, so its loop is kept minimal: running
+        // operand descriptors (advanced by one stage per chunk, rewound at the ring's end), four MMAs, one commit.
         constexpr uint32_t idesc = umma_idesc_f16(kTcRowsW, NT);
-        RingPos rp;
-        for (uint32_t kc = 0; kc < c.nchunks; kc++, rp.adv(1, c.stages)) {
-            const uint32_t s = rp.s, ph = rp.ph;
-            if (!mbar_wait(&a_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT)) break;
-            if (!mbar_wait(&b_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT)) break;
+        const uint64_t ad0 = umma_desc_k_sw128(smem_base + c.a_off);
+        const uint64_t bd0 = umma_desc_k_sw128(smem_base + c.b_off);
+        const uint64_t a_step = a_bytes >> 4, b_step = b_bytes >> 4;  // descriptor address field is in 16-byte units
+        uint64_t ad = ad0, bd = bd0;
+        uint32_t s = 0, ph = 0;
+        for (uint32_t kc = 0; kc < c.nchunks; kc++) {
+            if (!mbar_wait(&a_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
+            if (!mbar_wait(&b_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
             tc_fence_after();
             if (lane == 0) {
-                const uint64_t ad = umma_desc_k_sw128(smem_base + c.a_off + s * a_bytes);
-                const uint64_t bd = umma_desc_k_sw128(smem_base + c.b_off + s * b_bytes);
-#pragma unroll
-                for (uint32_t kk = 0; kk < 4; kk++)
-                    umma_f16_ss(tmem_d, ad + 2 * kk, bd + 2 * kk, idesc, (kc | kk) != 0 ? 1u : 0u);
-                umma_commit(&ab_empty[s]);
+                if (!(c.debug & 4u)) {
+                    umma_f16_ss(tmem_d, ad, bd, idesc, kc != 0 ? 1u : 0u);
+                    umma_f16_ss(tmem_d, ad + 2, bd + 2, idesc, 1u);
+                    umma_f16_ss(tmem_d, ad + 4, bd + 4, idesc, 1u);
+                    umma_f16_ss(tmem_d, ad + 6, bd + 6, idesc, 1u);
+                }
+                if (c.debug & 128u) mbar_arrive(&ab_empty[s]);
+                else umma_commit(&ab_empty[s]);
                 if (kc + 1 == c.nchunks) umma_commit(&acc_full);
             }
             __syncwarp();
+            ad += a_step;
+            bd += b_step;
+            if (++s == c.stages) {
+                s = 0;
+                ph ^= 1u;
+                ad = ad0;
+                bd = bd0;
+            }
         }
     } else {
         // ======================= dequantise warps, then epilogue =======================
@@ -527,30 +550,50 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         // efficient, so all dequantising threads stream them as 16-byte cp.async chunks, one raw stage ahead
         // of the one being dequantised.  Each row is fetched as the 16-byte aligned superset of its (only
         // 2-byte aligned) segment; readers skip the lead-in bytes.
-        const uint32_t dq_tid = tid;  // 0 .. kTcDequantWarps*32-1
+        // The (row, 16-byte chunk) pairs a thread copies are the same in every raw stage, so they are worked
+        // out once: per stage only the K offset moves.
+        constexpr int kRawSlots = 5;            // (128 rows x at most 19 chunks) / 512 threads, rounded up
+        constexpr uint32_t kSegFull = (KR / QK) * BB;
+        constexpr uint32_t kCmax = (kSegFull + 30u) >> 4;  // most 16-byte chunks a row segment can need
+        static_assert(kTcRowsW * kCmax <= kRawSlots * kTcDequantWarps * 32, "raw copy slots");
+        const uint32_t rows_here = min((uint32_t)kTcRowsW, a.n - n0);
+        const uint8_t *slot_src[kRawSlots];     // start of the thread's row (global)
+        uint32_t slot_dst[kRawSlots];           // row's place inside a raw stage + chunk offset (shared, relative)
+        uint32_t slot_cc[kRawSlots];            // chunk index within the row, 0xFFFFFFFF = unused
+#pragma unroll
+        for (int i = 0; i < kRawSlots; i++) {
+            const uint32_t idx = tid + i * (kTcDequantWarps * 32);
+            const uint32_t row = idx / kCmax, cc = idx - row * kCmax;
+            const bool used = row < rows_here;
+            slot_src[i] = wbase + (size_t)(n0 + (used ? row : 0)) * row_bytes;
+            slot_dst[i] = row * c.seg_stride + cc * 16u;
+            slot_cc[i] = used ? cc : 0xFFFFFFFFu;
+        }
         auto issue_raw = [&](uint32_t r) {
-            const uint32_t rs = r & 1u;
             const uint32_t k0 = r * KR;
-            const uint32_t kb = min((uint32_t)KR, a.k - k0);
-            const uint32_t seg_bytes = (kb / QK) * BB;
-            const uint32_t rows = min((uint32_t)kTcRowsW, a.n - n0);
-            const uint32_t cmax = (seg_bytes + 30u) >> 4;  // most 16-byte chunks a row can need
-            const uint32_t dst0 = smem_base + c.raw_off + rs * raw_stage_bytes;
-            const uint8_t *g0 = wbase + (size_t)n0 * row_bytes + (size_t)(k0 / QK) * BB;
-            for (uint32_t idx = dq_tid; idx < rows * cmax; idx += kTcDequantWarps * 32) {
-                const uint32_t row = idx / cmax, cc = idx - row * cmax;
-                const uint8_t *src = g0 + (size_t)row * row_bytes;
+            const uint32_t seg_bytes = (min((uint32_t)KR, a.k - k0) / QK) * BB;
+            const uint32_t koff = (k0 / QK) * BB;
+            const uint32_t dst0 = smem_base + c.raw_off + (r & 1u) * raw_stage_bytes;
+#pragma unroll
+            for (int i = 0; i < kRawSlots; i++) {
+                const uint8_t *src = slot_src[i] + koff;
                 const uint32_t pre_b = (uint32_t)((uintptr_t)src & 15u);
-                if (cc * 16u < pre_b + seg_bytes) {
-                    const uint8_t *gp = src - pre_b + cc * 16u;
-                    const uint32_t dp = dst0 + row * c.seg_stride + cc * 16u;
-                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dp), "l"(gp) : "memory");
-                }
+                if (slot_cc[i] != 0xFFFFFFFFu && slot_cc[i] * 16u < pre_b + seg_bytes && !(c.debug & 2u))
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + slot_dst[i]),
+                                 "l"(src - pre_b + slot_cc[i] * 16u)
+                                 : "memory");
             }
-            // arrive on the stage's barrier once this thread's copies have landed (one arrival per thread)
-            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&raw_full[rs])) : "memory");
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        // One barrier arrival per warp (not per thread: hundreds of arrivals on one mbarrier serialise):
+        // each lane waits for its own copies, the warp converges, lane 0 arrives.
+        auto publish_raw = [&](uint32_t r) {
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&raw_full[r & 1u]);
         };
         issue_raw(0);
+        publish_raw(0);
         bool ok = true;
         RingPos rp;
         rp.adv(set, c.stages);  // this set's first chunk is kc = set
@@ -558,22 +601,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             const uint32_t rs = r & 1u;
             if (r + 1 < nraw) {
                 // slot (r+1)&1 was last used by raw stage r-1: every warp must have released it
-                if (!mbar_wait(&raw_empty[(r + 1) & 1u], (((r + 1) >> 1) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) break;
+                if (!mbar_wait(&raw_empty[(r + 1) & 1u], (((r + 1) >> 1) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) break;
                 issue_raw(r + 1);
             }
-            if (!mbar_wait(&raw_full[rs], (r >> 1) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT)) break;
+            if (!mbar_wait(&raw_full[rs], (r >> 1) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_dq)) break;
             const uint32_t pre = (row_lo4 + ((r * KR) / QK) * BB) & 15u;
             const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
             for (uint32_t kc = r * CPR + set; kc < min((r + 1) * CPR, c.nchunks); kc += 2, rp.adv(2, c.stages)) {
                 const uint32_t s = rp.s;
-                if (!mbar_wait(&ab_empty[s], rp.ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT)) {
+                if (!mbar_wait(&ab_empty[s], rp.ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) {
                     ok = false;
                     break;
                 }
                 const uint32_t kvalid = min(64u, a.k - kc * 64);  // elements of this chunk inside K
                 uint8_t *arow = smem + c.a_off + s * a_bytes + a_row_off;
                 uint4 v[4];
-                if (row_ok && 32 * half < kvalid) {
+                if (row_ok && 32 * half < kvalid && !(c.debug & 1u)) {
                     dequant32<T>(seg, (kc - r * CPR) * 64 + 32 * half, v);
                 } else {
 #pragma unroll
@@ -582,15 +625,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
 #pragma unroll
                 for (int j = 0; j < 4; j++)
                     *reinterpret_cast<uint4 *>(arow + (((4 * half + j) ^ (rr & 7u)) << 4)) = v[j];
-                fence_proxy_async_smem();
+                if (!(c.debug & 64u)) fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&a_full[s]);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_empty[rs]);  // this warp is done reading raw stage r
+            if (r + 1 < nraw) publish_raw(r + 1);        // by now the copies issued before this stage have landed
         }
         // ---- epilogue: TMEM -> registers -> y ----
-        if (!abort_flag && mbar_wait(&acc_full, 0, &abort_flag, a.status, ST_WAIT_MMA_TIMEOUT)) {
+        if (!abort_flag && mbar_wait(&acc_full, 0, &abort_flag, a.status, ST_WAIT_MMA_TIMEOUT, 200)) {
             tc_fence_after();
             const uint32_t q4 = warp & 3u;           // tensor-memory lane quarter this warp may read
             const uint32_t wrow = n0 + q4 * 32 + lane;
@@ -673,6 +717,10 @@ template <int T, int NT>
 static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaStream_t st, int *launches) {
     constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES, KR = TcTraits<T>::KR;
     TcCfg c{};
+    {
+        const char *dbg = getenv("MLXN_TC_DEBUG");
+        c.debug = dbg ? (uint32_t)atoi(dbg) : 0u;
+    }
     c.nchunks = (a.k + 63) / 64;
     c.seg_stride = round_up_u((KR / QK) * BB + 15, 16) + 16;
     if ((c.seg_stride / 16) % 2 == 0) c.seg_stride += 16;  // odd multiple of 16 B: rows spread over the banks

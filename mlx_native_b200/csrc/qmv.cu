@@ -17,6 +17,8 @@
 // f32x2 FMAs, then applies scale*(S - offset*sum(x)); offset is 0 for Q8_0, 136 for Q4_0 and 160 for
 // Q6_K (the quants are spliced into an f32 mantissa under a 2^7 exponent, which costs one byte
 // permute per element instead of an integer-to-float conversion).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -153,6 +155,7 @@ struct StreamCfg {
     uint32_t seg_stride;  // shared-memory bytes reserved per row segment (multiple of 16)
     uint32_t cpp;         // CTAs per problem
     uint32_t xs_off, xsum_off, red_off, stage_off;  // byte offsets into dynamic shared memory
+    uint32_t debug;       // experiment switches: 1 = skip the arithmetic, 2 = skip the weight copies
 };
 
 template <int T> struct StreamTraits;
@@ -479,7 +482,7 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
         const uint32_t seg_bytes = (kb / QK) * BB;
         const uint8_t *src = wb + (size_t)(row0 + lane) * row_bytes + (size_t)w.s * slice_bytes;
         const uint32_t pre = (uint32_t)((uintptr_t)src & 15u);
-        const uint32_t bytes = (valid && lane < nrows) ? ((pre + seg_bytes + 15u) & ~15u) : 0u;
+        const uint32_t bytes = (valid && lane < nrows && !(c.debug & 2u)) ? ((pre + seg_bytes + 15u) & ~15u) : 0u;
         uint32_t total = bytes;
         total += __shfl_xor_sync(0xffffffffu, total, 1);
         total += __shfl_xor_sync(0xffffffffu, total, 2);
@@ -572,8 +575,8 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
             for (int r = 0; r < kRows; r++)
 #pragma unroll
                 for (int t = 0; t < M; t++) acc[r][t] = 0.0f;
-            const bool landed = !abort_flag && mbar_wait(&full_bar[slot], (it >> c.lg_stages) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT);
-            if (valid && landed) {
+            const bool landed = !abort_flag && mbar_wait(&full_bar[slot], (it >> c.lg_stages) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, 100);
+            if (valid && landed && !(c.debug & 1u)) {
                 for (uint32_t task = wig * 32 + lane; task < ntasks; task += 32 * c.wpg) {
                     if constexpr (T == GT_Q4_0) task_q4_0<M>(seg, task, xs, xsum, c.ks, acc);
                     else if constexpr (T == GT_Q8_0) task_q8_0<M>(seg, task, xs, xsum, c.ks, acc);
@@ -697,6 +700,10 @@ static bool stream_config(const QmvArgs &a, int sm_count, size_t smem_limit, uin
     while ((1u << lg_wpg) < wpg) lg_wpg++;
     c.lg_stages = lg;
     c.lg_wpg = lg_wpg;
+    {
+        const char *dbg = getenv("MLXN_MV_DEBUG");
+        c.debug = dbg ? (uint32_t)atoi(dbg) : 0u;
+    }
     c.ks = ks;
     c.nslices = nslices;
     c.wpg = wpg;
