@@ -1,0 +1,76 @@
+"""Small fixed workloads for profiler captures (a few hundred MB on the device, a handful of launches).
+
+  python -m mlx_native_b200.profile_case mv  [Q8_0|Q6_K|Q4_0] [m]   decode mat-vec, n=12288 k=4096, 4 weight copies (> L2)
+  python -m mlx_native_b200.profile_case mm  [Q4_0|Q6_K|Q8_0] [m]   prefill mat-mat, n=4096 k=4096, m=512 by default
+  python -m mlx_native_b200.profile_case moe [m]                    expert-routed gate projection, 128 experts, top-8
+
+Weights are random bytes with finite f16 scales: the kernels' timing and memory traffic do not depend on the values.
+"""
+from __future__ import annotations
+
+import sys
+
+import numpy as np
+
+import mlx_native_b200 as mx
+
+BLOCK = {"Q4_0": (mx.GgmlType.Q4_0, 32, 18, 0), "Q8_0": (mx.GgmlType.Q8_0, 32, 34, 0), "Q6_K": (mx.GgmlType.Q6_K, 256, 210, 208)}
+
+
+def random_blocks(rng, t: str, n: int, k: int) -> np.ndarray:
+    _, qk, bb, dpos = BLOCK[t]
+    raw = rng.integers(0, 256, size=(n * (k // qk), bb), dtype=np.uint8)
+    raw[:, dpos + 1] = (raw[:, dpos + 1] & 0x83) | 0x20   # f16 scale exponent in a small finite range
+    return raw.reshape(-1)
+
+
+def main(argv):
+    mode = argv[0] if argv else "mv"
+    dev = mx.MlxDevice.new(0)
+    reg = mx.KernelRegistry.new()
+    rng = np.random.default_rng(0)
+    enc = dev.command_encoder()
+    if mode == "moe":
+        m = int(argv[1]) if len(argv) > 1 else 512
+        E, top_k, hidden, ffn = 128, 8, 2048, 768
+        w = random_blocks(rng, "Q4_0", E * ffn, hidden)
+        wb = dev.alloc_buffer(w.size, mx.DType.U8)
+        wb.upload(w)
+        x = rng.standard_normal((m, hidden)).astype(np.float32)
+        xb = dev.alloc_buffer(x.nbytes, mx.DType.F32)
+        xb.upload(x)
+        ids = np.stack([rng.permutation(E)[:top_k] for _ in range(m)]).astype(np.uint32)
+        ib = dev.alloc_buffer(ids.nbytes, mx.DType.U32)
+        ib.upload(ids)
+        yb = dev.alloc_buffer(m * top_k * ffn * 4, mx.DType.F32)
+        p = mx.GgmlQuantizedMatmulIdParams(m, top_k, ffn, hidden, E, w.size // E, mx.GgmlType.Q4_0)
+        for _ in range(3):
+            mx.quantized_matmul_id_ggml(enc, reg, dev, xb, wb, ib, yb, p)
+        enc.commit_and_wait()
+        print("ok", mx.last_kernel_name())
+        return
+    t = argv[1] if len(argv) > 1 else ("Q8_0" if mode == "mv" else "Q4_0")
+    if mode == "mv":
+        n, k, m, copies = 12288, 4096, int(argv[2]) if len(argv) > 2 else 1, 4
+    else:
+        n, k, m, copies = 4096, 4096, int(argv[2]) if len(argv) > 2 else 512, 1
+    w = random_blocks(rng, t, n, k)
+    ws = []
+    for _ in range(copies):
+        b = dev.alloc_buffer(w.size, mx.DType.U8)
+        b.upload(w)
+        ws.append(b)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    xb = dev.alloc_buffer(x.nbytes, mx.DType.F32)
+    xb.upload(x)
+    yb = dev.alloc_buffer(m * n * 4, mx.DType.F32)
+    p = mx.GgmlQuantizedMatmulParams(m, n, k, BLOCK[t][0])
+    for _ in range(2):
+        for wbuf in ws:
+            mx.quantized_matmul_ggml(enc, reg, dev, xb, wbuf, yb, p)
+    enc.commit_and_wait()
+    print("ok", mx.last_kernel_name())
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])
