@@ -160,6 +160,7 @@ def run_ours(args, rank, world, local_rank):
     import torch
 
     import mlx_native_b200 as mx
+    from mlx_native_b200 import sharding
 
     torch.cuda.set_device(local_rank)
     dist = None
@@ -181,8 +182,7 @@ def run_ours(args, rank, world, local_rank):
         for (n, k) in SHAPES:
             wq = weights[(t, n, k)]
             n_loc = n // world
-            rb = wq.size // n
-            w_loc = wq[rank * n_loc * rb:(rank + 1) * n_loc * rb]
+            w_loc = sharding.shard_weight_bytes(wq, int(gt[t]), n, k, rank, world)
             for m in MS:
                 wbuf = dev.alloc_buffer(w_loc.size, mx.DType.U8)
                 wbuf.upload(w_loc)
@@ -191,7 +191,7 @@ def run_ours(args, rank, world, local_rank):
                 xbuf.upload(x)
                 if world > 1:
                     y_loc = torch.empty((m, n_loc), dtype=torch.float32, device="cuda")
-                    y_all = torch.empty((world, m, n_loc), dtype=torch.float32, device="cuda")
+                    y_all = torch.empty((world * m, n_loc), dtype=torch.float32, device="cuda")
                     ybuf = dev.wrap_device_memory(y_loc.data_ptr(), m * n_loc * 4, mx.DType.F32, [m, n_loc])
                 else:
                     y_loc = y_all = None
@@ -277,7 +277,7 @@ def run_ours(args, rank, world, local_rank):
         acc = 0.0
         for L in launches:
             if world > 1:
-                acc += float(L["y_all"][0, 0, 0].item())                      # device -> host read of the result
+                acc += float(L["y_all"][0, 0].item())                      # device -> host read of the result
             else:
                 acc += float(L["y"].as_slice(np.float32)[0])
         return acc
