@@ -230,6 +230,27 @@ int mlxn_moe_weighted_reduce(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device 
                              mlxn_buffer *residual, mlxn_buffer *out, uint32_t n_tokens, uint32_t top_k,
                              uint32_t h);
 
+/* ---- mat-mat without any allocation (no counterpart in the reference) ------------------------------
+ * For callers that cannot allocate device memory when they need the product: a serving process whose own
+ * allocator has claimed all of HBM, a latency-critical loop that must stay off the driver's allocation
+ * path, or a plug-in that only ever receives pointers.  Same result as mlxn_dispatch_mm_for_test (the
+ * tensor-core mat-mat at any m), but the packed f16 activations go into a fixed 16 MiB array compiled into
+ * the library instead of the encoder's arena, and inputs/outputs are plain device pointers on `cuda_stream`
+ * (a cudaStream_t; NULL = the default stream).  Nothing is allocated or freed, on the host or the device.
+ * Limits and rules:
+ *  - the packed activations, ceil(m/NT)*NT * ceil(k/64)*64 * 2 bytes, must fit in
+ *    mlxn_noalloc_scratch_limit() bytes (m*k up to about 8M elements); larger calls are refused with
+ *    MLXN_INVALID_ARGUMENT and a message naming both sizes;
+ *  - dense Q4_0 / Q8_0 / Q6_K only; K a multiple of 32;
+ *  - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *    current) — make that first call outside any stream capture;
+ *  - all calls on a device share the one array: two calls whose kernels overlap on the GPU (different
+ *    streams) race; the array keeps the last call's tiles, and every call rewrites all the tiles it reads;
+ *  - a kernel wait that gives up is not reported (there is no status word without an allocation). */
+size_t mlxn_noalloc_scratch_limit(void);
+int mlxn_quantized_matmul_ggml_mm_noalloc(void *cuda_stream, const void *input_dev, const void *weight_dev,
+                                          void *output_dev, const mlxn_qmm_params *params);
+
 /* ---- tuning and introspection (no upstream counterpart) -------------------------------------- */
 /* Selects kernel variants for experiments: key/value pairs such as "qmv=stream|simple",
  * "qmm=tc|simt".  Unknown keys are MLXN_INVALID_ARGUMENT.  The defaults are the fast paths. */

@@ -477,6 +477,21 @@ def dispatch_mm_for_test(encoder, registry, device, input, weight, output, param
                                                    _h(output), C.byref(params._c())))
 
 
+def noalloc_scratch_limit() -> int:
+    return int(_native.lib().mlxn_noalloc_scratch_limit())
+
+
+def quantized_matmul_ggml_mm_noalloc(cuda_stream: int, input_ptr: int, weight_ptr: int, output_ptr: int,
+                                     params: GgmlQuantizedMatmulParams) -> None:
+    """Tensor-core mat-mat on raw device pointers that allocates nothing (no counterpart upstream): for callers
+    that may not allocate device memory — an allocator that owns all of HBM, a loop that must avoid the driver's
+    allocation path, a plug-in that only gets pointers.  The packed activations live in a fixed 16 MiB array inside
+    the library, so m*k is limited (see noalloc_scratch_limit) and overlapping calls on one GPU race."""
+    _check(_native.lib().mlxn_quantized_matmul_ggml_mm_noalloc(C.c_void_p(cuda_stream), C.c_void_p(input_ptr),
+                                                               C.c_void_p(weight_ptr), C.c_void_p(output_ptr),
+                                                               C.byref(params._c())))
+
+
 def quantized_matmul_id_ggml(encoder, registry, device, input, weight, ids, output,
                              params: GgmlQuantizedMatmulIdParams) -> None:
     """src/ops/quantized_matmul_id_ggml.rs:163-276."""

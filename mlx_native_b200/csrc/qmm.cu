@@ -812,3 +812,105 @@ cudaError_t launch_qmm_simt(int ggml_type, const QmmArgs &a, bool routed, uint32
 }
 
 }  // namespace mlxn
+
+// =================================================================================================
+// mat-mat entry point that allocates nothing
+// =================================================================================================
+// Some callers may not allocate device memory at the moment they need a mat-mat: code running inside a
+// memory-budgeted serving process whose allocator owns every byte of HBM, a real-time loop that must not
+// hit the driver's allocation lock, or a plug-in that is only handed pointers.  For them the packed
+// activation tiles of the tensor-core path live in this fixed array instead of the encoder's arena.
+// Every GPU that loads the library carries the array until the process exits.
+#include <cstdio>
+#include <mutex>
+
+#include "../../include/mlxn_b200.h"
+
+int mlxn_detail_fail(int status, const char *msg);
+void mlxn_detail_count_launches(int launches);
+
+#define MLXN_NOALLOC_SCRATCH_BYTES (16u * 1024u * 1024u)
+static __device__ __align__(256) uint8_t g_noalloc_scratch[MLXN_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_noalloc_mu;
+uint8_t *g_noalloc_ptr[64] = {};  // device address of g_noalloc_scratch, per device ordinal
+int g_noalloc_sms[64] = {};
+}  // namespace
+
+extern "C" size_t mlxn_noalloc_scratch_limit(void) { return MLXN_NOALLOC_SCRATCH_BYTES; }
+
+extern "C" int mlxn_quantized_matmul_ggml_mm_noalloc(void *cuda_stream, const void *input_dev, const void *weight_dev,
+                                                     void *output_dev, const mlxn_qmm_params *params) {
+    using namespace mlxn;
+    if (!input_dev || !weight_dev || !output_dev || !params)
+        return mlxn_detail_fail(MLXN_INVALID_ARGUMENT, "Invalid argument: pointers and params must not be null");
+    const int t = (int)params->ggml_type;
+    if (t != GT_Q4_0 && t != GT_Q8_0 && t != GT_Q6_K)
+        return mlxn_detail_fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_mm_noalloc supports Q4_0, Q8_0 and Q6_K only");
+    if (params->m == 0 || params->k == 0 || params->n == 0)
+        return mlxn_detail_fail(MLXN_INVALID_ARGUMENT, "Invalid argument: M, K, and N must all be > 0");
+    if (params->k % ggml_qk(t) != 0 || params->k % 32 != 0)
+        return mlxn_detail_fail(MLXN_INVALID_ARGUMENT, "Invalid argument: K must be divisible by the block QK and by 32");
+    if (((uintptr_t)weight_dev & 1u) || ((uintptr_t)input_dev & 3u) || ((uintptr_t)output_dev & 3u))
+        return mlxn_detail_fail(MLXN_INVALID_ARGUMENT, "Invalid argument: weights must be 2-byte aligned, f32 buffers 4-byte aligned");
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+        return mlxn_detail_fail(MLXN_DEVICE_NOT_FOUND, "No usable current CUDA device for quantized_matmul_ggml_mm_noalloc");
+    uint8_t *scratch = nullptr;
+    int sms = 0;
+    {
+        // first call on this device (with the device current): look up where the array lives on it.
+        // The array's name is a host-side stand-in; only the address returned here may be given to a kernel.
+        std::lock_guard<std::mutex> lk(g_noalloc_mu);
+        if (!g_noalloc_ptr[dev]) {
+            void *p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess || !p) {
+                cudaGetLastError();
+                return mlxn_detail_fail(MLXN_COMMAND_BUFFER_ERROR, "Command buffer error: cudaGetSymbolAddress failed for the static scratch array");
+            }
+            int n = 0;
+            e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+            if (e != cudaSuccess || n <= 0) {
+                cudaGetLastError();
+                return mlxn_detail_fail(MLXN_COMMAND_BUFFER_ERROR, "Command buffer error: cannot query the SM count");
+            }
+            g_noalloc_sms[dev] = n;
+            g_noalloc_ptr[dev] = static_cast<uint8_t *>(p);
+        }
+        scratch = g_noalloc_ptr[dev];
+        sms = g_noalloc_sms[dev];
+    }
+    QmmArgs a{};
+    a.w = static_cast<const uint8_t *>(weight_dev);
+    a.x = static_cast<const float *>(input_dev);
+    a.y = static_cast<float *>(output_dev);
+    a.m = params->m;
+    a.n = params->n;
+    a.k = params->k;
+    a.top_k = 1;
+    a.n_experts = 1;
+    a.total_rows = params->m;
+    a.status = nullptr;  // no status word: a wait that gives up still ends the kernel, but is not reported
+    const uint32_t nt = qmm_tc_pick_nt(a.m, a.n, sms, false);
+    const size_t need = qmm_tc_scratch_bytes(a, nt, false);
+    if (need > MLXN_NOALLOC_SCRATCH_BYTES) {
+        char msg[256];
+        snprintf(msg, sizeof(msg),
+                 "Invalid argument: quantized_matmul_ggml_mm_noalloc needs %zu bytes of packed activations for m=%u k=%u, "
+                 "the static scratch holds %u (about m*k <= 8M elements); use quantized_matmul_ggml instead",
+                 need, a.m, a.k, MLXN_NOALLOC_SCRATCH_BYTES);
+        return mlxn_detail_fail(MLXN_INVALID_ARGUMENT, msg);
+    }
+    int launches = 0;
+    cudaError_t e = launch_qmm_tc(t, a, false, nt, scratch, static_cast<cudaStream_t>(cuda_stream), &launches);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        char msg[256];
+        snprintf(msg, sizeof(msg), "Command buffer error: mat-mat launch: %s", cudaGetErrorString(e));
+        return mlxn_detail_fail(MLXN_COMMAND_BUFFER_ERROR, msg);
+    }
+    mlxn_detail_count_launches(launches);
+    return MLXN_OK;
+}

@@ -65,7 +65,17 @@ static int cuda_fail(cudaError_t e, const char *what) {
         if (_e != cudaSuccess) return cuda_fail(_e, what); \
     } while (0)
 
+// error reporting for entry points that live in other translation units
+int mlxn_detail_fail(int status, const char *msg) { return fail(status, "%s", msg); }
+void mlxn_detail_count_launches(int launches);
+
 static std::atomic<uint64_t> g_dispatch{0}, g_sync{0}, g_cmd_buf{0}, g_barrier{0}, g_launches{0};
+
+void mlxn_detail_count_launches(int launches) {
+    g_launches.fetch_add((uint64_t)launches);
+    g_dispatch.fetch_add(1);
+    g_last_kernel = "qmm_tc";
+}
 
 static std::atomic<int> g_opt_qmv{-1}, g_opt_qmm{-1};  // -1 unset, 0 simple/simt, 1 stream/tc
 static bool opt_qmv_stream() {
