@@ -369,13 +369,19 @@ def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
     gt = {"Q4_0": mx.GgmlType.Q4_0, "Q6_K": mx.GgmlType.Q6_K}
 
     def timed(fn, reps=10, warm=3):
+        """Median device time of one replay of `fn` captured into a CUDA graph (launch gaps excluded)."""
         e = dev.command_encoder()
         for _ in range(warm):
             fn(e)
         e.commit_and_wait()
+        e.begin_capture()
+        fn(e)
+        g = e.end_capture()
+        g.launch(e)
+        e.commit_and_wait()
         ts = []
         for _ in range(reps):
-            fn(e)
+            g.launch(e)
             ts.append(e.commit_wait_with_gpu_time())
         return statistics.median(ts)
 

@@ -511,8 +511,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         uint64_t ad = ad0, bd = bd0;
         uint32_t s = 0, ph = 0;
         for (uint32_t kc = 0; kc < c.nchunks; kc++) {
+            const bool trace = (c.debug & 256u) && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && kc < 256;
+            long long t_a = 0, t_b = 0;
             if (!mbar_wait(&a_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
+            if (trace) t_a = clock64();
             if (!mbar_wait(&b_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
+            if (trace) t_b = clock64();
             tc_fence_after();
             if (lane == 0) {
                 if (!(c.debug & 4u)) {
@@ -524,6 +528,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                 if (c.debug & 128u) mbar_arrive(&ab_empty[s]);
                 else umma_commit(&ab_empty[s]);
                 if (kc + 1 == c.nchunks) umma_commit(&acc_full);
+                if (trace) {  // experiment only: the timeline overwrites the start of y
+                    long long *tr = reinterpret_cast<long long *>(a.y) + 3 * kc;
+                    tr[0] = t_a;
+                    tr[1] = t_b;
+                    tr[2] = clock64();
+                }
             }
             __syncwarp();
             ad += a_step;
@@ -643,7 +653,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_d + ((q4 * 32) << 16) + col, v);
                 tmem_ld_wait();
-                if (wrow < a.n) {
+                if (wrow < a.n && !(c.debug & 256u)) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int32_t o = orow[col + j];

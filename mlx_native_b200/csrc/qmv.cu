@@ -519,11 +519,28 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
             named_bar_sync(1, kStreamThreads);  // everyone is done with the previous slice
             const float *xg = a.x + (a.ids ? (size_t)(w.p / a.top_k) * a.k : 0);
             const uint32_t k0 = w.s * c.ks;
-            for (uint32_t idx = tid; idx < M * ks4; idx += kStreamThreads) {
-                const uint32_t t = idx / ks4, f = idx - t * ks4;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (k0 + 4 * f < a.k) v = __ldg(reinterpret_cast<const float4 *>(xg + (size_t)t * a.k + k0) + f);
-                *reinterpret_cast<float4 *>(smem + c.xs_off + (size_t)(t * ks4 + xswz<T>(f)) * 16) = v;
+            // loads are issued in batches of eight per thread before any is stored, so that the L2 latency is
+            // paid once per batch instead of once per element
+            constexpr int kBatch = 8;
+            for (uint32_t base = 0; base < M * ks4; base += kBatch * kStreamThreads) {
+                float4 v[kBatch];
+#pragma unroll
+                for (int u = 0; u < kBatch; u++) {
+                    const uint32_t idx = base + u * kStreamThreads + tid;
+                    v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (idx < M * ks4) {
+                        const uint32_t t = idx / ks4, f = idx - t * ks4;
+                        if (k0 + 4 * f < a.k) v[u] = __ldg(reinterpret_cast<const float4 *>(xg + (size_t)t * a.k + k0) + f);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < kBatch; u++) {
+                    const uint32_t idx = base + u * kStreamThreads + tid;
+                    if (idx < M * ks4) {
+                        const uint32_t t = idx / ks4, f = idx - t * ks4;
+                        *reinterpret_cast<float4 *>(smem + c.xs_off + (size_t)(t * ks4 + xswz<T>(f)) * 16) = v[u];
+                    }
+                }
             }
             named_bar_sync(1, kStreamThreads);
             if constexpr (T != GT_Q8_0) {
