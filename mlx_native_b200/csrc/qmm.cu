@@ -213,7 +213,7 @@ constexpr int kTcThreads = (kTcDequantWarps + 2) * 32;  // + producer warp + MMA
 constexpr int kTcRowsW = 128;                           // weight rows per tile (UMMA M)
 
 template <int T> struct TcTraits;
-template <> struct TcTraits<GT_Q4_0> { static constexpr int KR = 256; };  // raw-stage K extent
+template <> struct TcTraits<GT_Q4_0> { static constexpr int KR = 128; };  // raw-stage K extent
 template <> struct TcTraits<GT_Q8_0> { static constexpr int KR = 128; };
 template <> struct TcTraits<GT_Q6_K> { static constexpr int KR = 256; };
 
@@ -411,6 +411,7 @@ struct TcCfg {
     uint32_t stages;      // f16 operand ring depth
     uint32_t seg_stride;  // bytes reserved per raw row segment
     uint32_t a_off, b_off, raw_off;
+    uint32_t raw_slots;   // depth of the raw weight ring (2..6)
     uint32_t debug;       // experiment switches: 1 = skip dequantisation, 2 = skip raw copies, 4 = skip MMA, 8 = skip B copies
 };
 
@@ -424,7 +425,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     constexpr int CPR = KR / 64;     // 64-wide chunks per raw stage
     constexpr int kMaxS = 6;
     __shared__ __align__(8) uint64_t a_full[kMaxS], b_full[kMaxS], ab_empty[kMaxS];
-    __shared__ __align__(8) uint64_t raw_full[2], raw_empty[2], acc_full;
+    constexpr int kMaxRaw = 6;
+    __shared__ __align__(8) uint64_t raw_full[kMaxRaw], raw_empty[kMaxRaw], acc_full;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile uint32_t abort_flag;
     __shared__ int32_t orow[NT];
@@ -446,12 +448,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     if (tid == 0) {
         abort_flag = 0;
         for (uint32_t s = 0; s < c.stages; s++) {
-            mbar_init(&a_full[s], kTcSetWarps);
+            mbar_init(&a_full[s], kTcDequantWarps);
             mbar_init(&b_full[s], 1);
             mbar_init(&ab_empty[s], 1);
         }
-        for (int s = 0; s < 2; s++) {
-            mbar_init(&raw_full[s], kTcDequantWarps);
+        for (uint32_t s = 0; s < c.raw_slots; s++) {
+            mbar_init(&raw_full[s], kTcDequantWarps * 32);  // one asynchronous arrival per copying thread
             mbar_init(&raw_empty[s], kTcDequantWarps);
         }
         mbar_init(&acc_full, 1);
@@ -479,7 +481,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     tc_fence_after();
     const uint32_t tmem_d = tmem_base_s;
     const uint32_t smem_base = smem_u32(smem);
+    // a pipeline stage holds two 64-wide K chunks (two swizzle atoms side by side) of each operand
     const uint32_t a_bytes = kTcRowsW * 128, b_bytes = NT * 128;
+    const uint32_t a_stage = 2 * a_bytes, b_stage = 2 * b_bytes;
+    const uint32_t nst = (c.nchunks + 1) / 2;
     const uint32_t raw_stage_bytes = kTcRowsW * c.seg_stride;
     const uint32_t nraw = (c.nchunks + CPR - 1) / CPR;
     // wait styles: the single producer / MMA warps spin (they are the critical path and cost one warp's issue
@@ -490,13 +495,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     if (warp == kTcDequantWarps) {
         // ======================= producer warp: bulk copies of the packed activation tiles =======================
         RingPos rp;
-        for (uint32_t kc = 0; kc < c.nchunks; kc++, rp.adv(1, c.stages)) {
+        for (uint32_t st = 0; st < nst; st++, rp.adv(1, c.stages)) {
             const uint32_t s = rp.s;
             if (!mbar_wait(&ab_empty[s], rp.ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_cr)) break;
+            const uint32_t bytes = (2 * st + 1 < c.nchunks) ? b_stage : b_bytes;  // the two tiles are adjacent in xpack
             if (lane == 0 && (c.debug & 8u)) mbar_arrive(&b_full[s]);
             if (lane == 0 && !(c.debug & 8u)) {
-                mbar_expect_tx(&b_full[s], b_bytes);
-                bulk_g2s(smem + c.b_off + s * b_bytes, xpack + ((size_t)tt * c.nchunks + kc) * (size_t)b_bytes, b_bytes,
+                mbar_expect_tx(&b_full[s], bytes);
+                bulk_g2s(smem + c.b_off + s * b_stage, xpack + ((size_t)tt * c.nchunks + 2 * st) * (size_t)b_bytes, bytes,
                          &b_full[s]);
             }
         }
@@ -507,11 +513,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         constexpr uint32_t idesc = umma_idesc_f16(kTcRowsW, NT);
         const uint64_t ad0 = umma_desc_k_sw128(smem_base + c.a_off);
         const uint64_t bd0 = umma_desc_k_sw128(smem_base + c.b_off);
-        const uint64_t a_step = a_bytes >> 4, b_step = b_bytes >> 4;  // descriptor address field is in 16-byte units
+        const uint64_t a_step = a_stage >> 4, b_step = b_stage >> 4;  // descriptor address field is in 16-byte units
+        const uint64_t a_sub = a_bytes >> 4, b_sub = b_bytes >> 4;
         uint64_t ad = ad0, bd = bd0;
         uint32_t s = 0, ph = 0;
-        for (uint32_t kc = 0; kc < c.nchunks; kc++) {
-            const bool trace = (c.debug & 256u) && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && kc < 256;
+        for (uint32_t st = 0; st < nst; st++) {
+            const bool trace = (c.debug & 256u) && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && st < 256;
             long long t_a = 0, t_b = 0;
             if (!mbar_wait(&a_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
             if (trace) t_a = clock64();
@@ -520,16 +527,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             tc_fence_after();
             if (lane == 0) {
                 if (!(c.debug & 4u)) {
-                    umma_f16_ss(tmem_d, ad, bd, idesc, kc != 0 ? 1u : 0u);
+                    umma_f16_ss(tmem_d, ad, bd, idesc, st != 0 ? 1u : 0u);
                     umma_f16_ss(tmem_d, ad + 2, bd + 2, idesc, 1u);
                     umma_f16_ss(tmem_d, ad + 4, bd + 4, idesc, 1u);
                     umma_f16_ss(tmem_d, ad + 6, bd + 6, idesc, 1u);
+                    if (2 * st + 1 < c.nchunks) {
+                        umma_f16_ss(tmem_d, ad + a_sub, bd + b_sub, idesc, 1u);
+                        umma_f16_ss(tmem_d, ad + a_sub + 2, bd + b_sub + 2, idesc, 1u);
+                        umma_f16_ss(tmem_d, ad + a_sub + 4, bd + b_sub + 4, idesc, 1u);
+                        umma_f16_ss(tmem_d, ad + a_sub + 6, bd + b_sub + 6, idesc, 1u);
+                    }
                 }
                 if (c.debug & 128u) mbar_arrive(&ab_empty[s]);
                 else umma_commit(&ab_empty[s]);
-                if (kc + 1 == c.nchunks) umma_commit(&acc_full);
+                if (st + 1 == nst) umma_commit(&acc_full);
                 if (trace) {  // experiment only: the timeline overwrites the start of y
-                    long long *tr = reinterpret_cast<long long *>(a.y) + 3 * kc;
+                    long long *tr = reinterpret_cast<long long *>(a.y) + 3 * st;
                     tr[0] = t_a;
                     tr[1] = t_b;
                     tr[2] = clock64();
@@ -579,11 +592,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             slot_dst[i] = row * c.seg_stride + cc * 16u;
             slot_cc[i] = used ? cc : 0xFFFFFFFFu;
         }
-        auto issue_raw = [&](uint32_t r) {
+        auto issue_raw = [&](uint32_t r, uint32_t slot) {
             const uint32_t k0 = r * KR;
             const uint32_t seg_bytes = (min((uint32_t)KR, a.k - k0) / QK) * BB;
             const uint32_t koff = (k0 / QK) * BB;
-            const uint32_t dst0 = smem_base + c.raw_off + (r & 1u) * raw_stage_bytes;
+            const uint32_t dst0 = smem_base + c.raw_off + slot * raw_stage_bytes;
 #pragma unroll
             for (int i = 0; i < kRawSlots; i++) {
                 const uint8_t *src = slot_src[i] + koff;
@@ -593,38 +606,40 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                                  "l"(src - pre_b + slot_cc[i] * 16u)
                                  : "memory");
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
+            // the thread's arrival on the slot's barrier fires once its copies have landed; nobody blocks on it
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&raw_full[slot])) : "memory");
         };
-        // One barrier arrival per warp (not per thread: hundreds of arrivals on one mbarrier serialise):
-        // each lane waits for its own copies, the warp converges, lane 0 arrives.
-        auto publish_raw = [&](uint32_t r) {
-            asm volatile("cp.async.wait_all;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&raw_full[r & 1u]);
-        };
-        issue_raw(0);
-        publish_raw(0);
+        // raw ring: stage r lives in slot r % raw_slots and is requested raw_slots-1 stages before it is read
+        const uint32_t R = c.raw_slots, D = R - 1;
+        uint32_t islot = 0, iph = 0;   // slot / use-parity of the next stage to request
+        uint32_t rnext = 0;
+        for (; rnext < min(D, nraw); rnext++) {
+            issue_raw(rnext, islot);
+            if (++islot == R) { islot = 0; iph ^= 1u; }
+        }
         bool ok = true;
-        RingPos rp;
-        rp.adv(set, c.stages);  // this set's first chunk is kc = set
+        RingPos rp;  // stage of this set's next chunk: set s owns the half s of every stage
+        uint32_t rs = 0, rph = 0;      // slot / parity of the stage being read
         for (uint32_t r = 0; ok && r < nraw; r++) {
-            const uint32_t rs = r & 1u;
-            if (r + 1 < nraw) {
-                // slot (r+1)&1 was last used by raw stage r-1: every warp must have released it
-                if (!mbar_wait(&raw_empty[(r + 1) & 1u], (((r + 1) >> 1) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) break;
-                issue_raw(r + 1);
+            if (rnext < nraw) {
+                // the slot's previous tenant (stage rnext - R) must have been released by every warp
+                if (!mbar_wait(&raw_empty[islot], iph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) break;
+                issue_raw(rnext, islot);
+                rnext++;
+                if (++islot == R) { islot = 0; iph ^= 1u; }
             }
-            if (!mbar_wait(&raw_full[rs], (r >> 1) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_dq)) break;
+            if (!mbar_wait(&raw_full[rs], rph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_dq)) break;
             const uint32_t pre = (row_lo4 + ((r * KR) / QK) * BB) & 15u;
             const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
-            for (uint32_t kc = r * CPR + set; kc < min((r + 1) * CPR, c.nchunks); kc += 2, rp.adv(2, c.stages)) {
+            // an odd chunk count leaves the last stage half empty; set 1 still takes part in its hand-off
+            for (uint32_t kc = r * CPR + set; kc < min((r + 1) * CPR, 2 * nst); kc += 2, rp.adv(1, c.stages)) {
                 const uint32_t s = rp.s;
                 if (!mbar_wait(&ab_empty[s], rp.ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) {
                     ok = false;
                     break;
                 }
-                const uint32_t kvalid = min(64u, a.k - kc * 64);  // elements of this chunk inside K
-                uint8_t *arow = smem + c.a_off + s * a_bytes + a_row_off;
+                const uint32_t kvalid = kc < c.nchunks ? min(64u, a.k - kc * 64) : 0u;  // elements of this chunk inside K
+                uint8_t *arow = smem + c.a_off + s * a_stage + set * a_bytes + a_row_off;
                 uint4 v[4];
                 if (row_ok && 32 * half < kvalid && !(c.debug & 1u)) {
                     dequant32<T>(seg, (kc - r * CPR) * 64 + 32 * half, v);
@@ -641,7 +656,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_empty[rs]);  // this warp is done reading raw stage r
-            if (r + 1 < nraw) publish_raw(r + 1);        // by now the copies issued before this stage have landed
+            if (++rs == R) { rs = 0; rph ^= 1u; }
         }
         // ---- epilogue: TMEM -> registers -> y ----
         if (!abort_flag && mbar_wait(&acc_full, 0, &abort_flag, a.status, ST_WAIT_MMA_TIMEOUT, 200)) {
@@ -698,13 +713,16 @@ size_t qmm_tc_scratch_bytes(const QmmArgs &a, uint32_t nt, bool routed) {
 // Activation rows per tile.  Routed calls use 64 (few rows per expert).  Dense calls take the tile that
 // minimises waves x per-tile cost, where a tile costs about max(NT, 160) (tensor time vs the fixed
 // dequantisation of its 128 weight rows); ties go to the larger tile, which dequantises less in total.
-uint32_t qmm_tc_pick_nt(uint32_t rows, uint32_t n, int sm_count, bool routed) {
+uint32_t qmm_tc_pick_nt(int ggml_type, uint32_t rows, uint32_t n, int sm_count, bool routed) {
     if (routed || rows <= 64) return 64;
+    // shared memory: two stages of 256-row activation tiles only fit beside the small Q4_0 raw ring
+    const uint32_t cap = ggml_type == GT_Q4_0 ? 256u : 128u;
     const uint32_t cands[3] = {256, 128, 64};
-    uint32_t best = 256;
+    uint32_t best = cap;
     uint64_t best_cost = ~0ull;
     const uint32_t wt = (n + kTcRowsW - 1) / kTcRowsW;
     for (uint32_t nt : cands) {
+        if (nt > cap) continue;
         if (nt / 2 >= rows && nt > 64) continue;  // more than half of the tile would be padding
         const uint64_t tiles = (uint64_t)wt * ((rows + nt - 1) / nt);
         const uint64_t waves = (tiles + sm_count - 1) / (uint64_t)sm_count;
@@ -734,16 +752,29 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     c.nchunks = (a.k + 63) / 64;
     c.seg_stride = round_up_u((KR / QK) * BB + 15, 16) + 16;
     if ((c.seg_stride / 16) % 2 == 0) c.seg_stride += 16;  // odd multiple of 16 B: rows spread over the banks
-    const uint32_t a_bytes = kTcRowsW * 128, b_bytes = NT * 128;
-    const uint32_t raw_bytes = 2 * kTcRowsW * c.seg_stride;
-    const uint32_t limit = 220 * 1024;
-    uint32_t stages = (limit - raw_bytes) / (a_bytes + b_bytes);
-    if (stages > 6) stages = 6;
-    if (stages < 2) return cudaErrorInvalidConfiguration;
+    const uint32_t a_stage = 2 * kTcRowsW * 128, b_stage = 2 * NT * 128;  // two 64-wide K chunks per stage
+    const uint32_t raw_slot = kTcRowsW * c.seg_stride;
+    const uint32_t limit = 224 * 1024;
+    if (2 * raw_slot + 2 * (a_stage + b_stage) > limit) return cudaErrorInvalidConfiguration;
+    // two operand stages first (three when the tiles are small), the rest goes to the raw weight ring
+    uint32_t stages = NT <= 64 ? 3 : 2;
+    if (const char *e = getenv("MLXN_TC_STAGES")) {  // experiment switch
+        const uint32_t v = (uint32_t)atoi(e);
+        if (v >= 2 && v <= 6 && 2 * raw_slot + v * (a_stage + b_stage) <= limit) stages = v;
+    }
+    uint32_t raw_slots = (limit - stages * (a_stage + b_stage)) / raw_slot;
+    if (raw_slots > 6) raw_slots = 6;
+    if (const char *e = getenv("MLXN_TC_RAW")) {  // experiment switch
+        const uint32_t v = (uint32_t)atoi(e);
+        if (v >= 2 && v <= raw_slots) raw_slots = v;
+    }
+    if (raw_slots < 2) return cudaErrorInvalidConfiguration;
+    const uint32_t raw_bytes = raw_slots * raw_slot;
     c.stages = stages;
+    c.raw_slots = raw_slots;
     c.a_off = 0;
-    c.b_off = stages * a_bytes;
-    c.raw_off = c.b_off + stages * b_bytes;
+    c.b_off = stages * a_stage;
+    c.raw_off = c.b_off + stages * b_stage;
     const size_t smem = (size_t)c.raw_off + raw_bytes + 1024;  // + slack for manual 1024-byte alignment
 
     size_t tiles;
@@ -903,7 +934,7 @@ extern "C" int mlxn_quantized_matmul_ggml_mm_noalloc(void *cuda_stream, const vo
     a.n_experts = 1;
     a.total_rows = params->m;
     a.status = nullptr;  // no status word: a wait that gives up still ends the kernel, but is not reported
-    const uint32_t nt = qmm_tc_pick_nt(a.m, a.n, sms, false);
+    const uint32_t nt = qmm_tc_pick_nt(t, a.m, a.n, sms, false);
     const size_t need = qmm_tc_scratch_bytes(a, nt, false);
     if (need > MLXN_NOALLOC_SCRATCH_BYTES) {
         char msg[256];

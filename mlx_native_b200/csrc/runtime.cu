@@ -26,7 +26,7 @@ cudaError_t launch_qmm_tc(int ggml_type, const QmmArgs &a, bool routed, uint32_t
                           int *launches);
 cudaError_t launch_qmm_simt(int ggml_type, const QmmArgs &a, bool routed, uint32_t max_rows, cudaStream_t st);
 size_t qmm_tc_scratch_bytes(const QmmArgs &a, uint32_t nt, bool routed);
-uint32_t qmm_tc_pick_nt(uint32_t rows, uint32_t n, int sm_count, bool routed);
+uint32_t qmm_tc_pick_nt(int ggml_type, uint32_t rows, uint32_t n, int sm_count, bool routed);
 bool qmm_tc_supported(const QmmArgs &a);
 cudaError_t launch_moe_map0(const uint32_t *ids, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts,
                             uint32_t hids_stride, uint32_t *htpe, int32_t *hids, cudaStream_t st);
@@ -843,7 +843,7 @@ static int dispatch_mm(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
     a.total_rows = p->m;
     a.status = enc->status_dev;
     if (opt_qmm_tc() && qmm_tc_supported(a)) {
-        const uint32_t nt = qmm_tc_pick_nt(p->m, p->n, dev->sm_count, false);
+        const uint32_t nt = qmm_tc_pick_nt((int)p->ggml_type, p->m, p->n, dev->sm_count, false);
         uint8_t *scratch = nullptr;
         if ((rc = encoder_scratch(enc, qmm_tc_scratch_bytes(a, nt, false), &scratch))) return rc;
         int launches = 0;
@@ -1012,7 +1012,7 @@ static int dispatch_id_mm_stages(mlxn_encoder *enc, mlxn_registry *reg, mlxn_dev
     a.expert_stride = p->expert_stride;
     a.status = enc->status_dev;
     if (opt_qmm_tc() && qmm_tc_supported(a)) {
-        const uint32_t nt = qmm_tc_pick_nt(p->n_tokens, p->n, dev->sm_count, true);
+        const uint32_t nt = qmm_tc_pick_nt((int)p->ggml_type, p->n_tokens, p->n, dev->sm_count, true);
         uint8_t *scratch = nullptr;
         const size_t need = qmm_tc_scratch_bytes(a, nt, true);
         if ((rc = encoder_scratch(enc, scratch_used + need, &scratch))) return rc;
@@ -1056,7 +1056,7 @@ extern "C" int mlxn_quantized_matmul_id_ggml(mlxn_encoder *enc, mlxn_registry *r
     probe.k = params->k;
     probe.n_experts = params->n_experts;
     probe.total_rows = params->n_tokens * params->top_k;
-    const size_t tc_b = qmm_tc_scratch_bytes(probe, qmm_tc_pick_nt(params->n_tokens, params->n, dev->sm_count, true), true);
+    const size_t tc_b = qmm_tc_scratch_bytes(probe, qmm_tc_pick_nt((int)params->ggml_type, params->n_tokens, params->n, dev->sm_count, true), true);
     uint8_t *scratch = nullptr;
     if ((rc = encoder_scratch(enc, htpe_b + hids_b + tc_b, &scratch))) return rc;
     return dispatch_id_mm_stages(enc, reg, dev, input, weight, ids, output, reinterpret_cast<uint32_t *>(scratch),
