@@ -213,8 +213,8 @@ constexpr int kTcThreads = (kTcDequantWarps + 2) * 32;  // + producer warp + MMA
 constexpr int kTcRowsW = 128;                           // weight rows per tile (UMMA M)
 
 template <int T> struct TcTraits;
-template <> struct TcTraits<GT_Q4_0> { static constexpr int KR = 128; };  // raw-stage K extent
-template <> struct TcTraits<GT_Q8_0> { static constexpr int KR = 128; };
+template <> struct TcTraits<GT_Q4_0> { static constexpr int KR = 256; };  // raw-stage K extent
+template <> struct TcTraits<GT_Q8_0> { static constexpr int KR = 256; };
 template <> struct TcTraits<GT_Q6_K> { static constexpr int KR = 256; };
 
 __device__ __forceinline__ uint32_t lds32s(uint32_t addr) {
@@ -408,24 +408,35 @@ struct RingPos {
 
 struct TcCfg {
     uint32_t nchunks;     // ceil(k / 64)
-    uint32_t stages;      // f16 operand ring depth
+    uint32_t b_stages;    // depth of the activation ring, in 64-wide K chunks
     uint32_t seg_stride;  // bytes reserved per raw row segment
-    uint32_t a_off, b_off, raw_off;
+    uint32_t b_off, raw_off;
     uint32_t raw_slots;   // depth of the raw weight ring (2..6)
     uint32_t debug;       // experiment switches: 1 = skip dequantisation, 2 = skip raw copies, 4 = skip MMA, 8 = skip B copies
 };
 
-// grid (ceil(n/128), tile count bound); kTcThreads threads; 1 CTA per SM (dynamic shared memory ~200 KiB).
+constexpr int kTcAStages = 4;      // ring of dequantised weight stages held in tensor memory
+constexpr int kTcACols = 64;       // one stage: 128 K values as f16 pairs = 64 32-bit columns
+constexpr int kTcAColBase = 256;   // accumulator in columns [0, NT), weight ring in [256, 512)
+constexpr int kTcTmemCols = 512;
+
+// grid (ceil(n/128), tile count bound); kTcThreads threads; 1 CTA per SM.
+//
+// Data flow per CTA (one 128-row weight tile x one NT-row activation tile, all of K):
+//   raw GGML blocks  --cp.async-->  shared-memory ring  --dequantise (16 warps)-->  f16 pairs in registers
+//   --tcgen05.st-->  tensor-memory ring (A operand)  --tcgen05.mma, B = packed activations from the bulk-copy
+//   ring in shared memory-->  f32 accumulator in tensor memory  --tcgen05.ld-->  y.
+// The dequantised weights never touch shared memory: its bandwidth is the scarce resource here (the tensor
+// core already reads the whole activation tile from it for every MMA).
 template <int T, int NT>
 __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, const TcCfg c, const uint8_t *xpack) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // tensor-core operand tiles need 1024-byte alignment (128-byte swizzle atoms): align by hand
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES, KR = TcTraits<T>::KR;
-    constexpr int CPR = KR / 64;     // 64-wide chunks per raw stage
-    constexpr int kMaxS = 6;
-    __shared__ __align__(8) uint64_t a_full[kMaxS], b_full[kMaxS], ab_empty[kMaxS];
-    constexpr int kMaxRaw = 6;
+    constexpr int SPR = KR / 128;    // tensor-memory stages per raw stage
+    constexpr int kMaxB = 6, kMaxRaw = 6;
+    __shared__ __align__(8) uint64_t a_full[kTcAStages], stage_done[kTcAStages], b_full[kMaxB];
     __shared__ __align__(8) uint64_t raw_full[kMaxRaw], raw_empty[kMaxRaw], acc_full;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile uint32_t abort_flag;
@@ -447,11 +458,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
 
     if (tid == 0) {
         abort_flag = 0;
-        for (uint32_t s = 0; s < c.stages; s++) {
-            mbar_init(&a_full[s], kTcDequantWarps);
-            mbar_init(&b_full[s], 1);
-            mbar_init(&ab_empty[s], 1);
+        for (uint32_t s = 0; s < kTcAStages; s++) {
+            mbar_init(&a_full[s], kTcDequantWarps / 2);  // the eight warps of one set
+            mbar_init(&stage_done[s], 1);
         }
+        for (uint32_t s = 0; s < c.b_stages; s++) mbar_init(&b_full[s], 1);
         for (uint32_t s = 0; s < c.raw_slots; s++) {
             mbar_init(&raw_full[s], kTcDequantWarps * 32);  // one asynchronous arrival per copying thread
             mbar_init(&raw_empty[s], kTcDequantWarps);
@@ -473,7 +484,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         orow[i] = o;
     }
     if (warp == kTcDequantWarps + 1) {  // MMA warp owns tensor memory
-        tmem_alloc(&tmem_base_s, NT);
+        tmem_alloc(&tmem_base_s, kTcTmemCols);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -481,96 +492,93 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     tc_fence_after();
     const uint32_t tmem_d = tmem_base_s;
     const uint32_t smem_base = smem_u32(smem);
-    // a pipeline stage holds two 64-wide K chunks (two swizzle atoms side by side) of each operand
-    const uint32_t a_bytes = kTcRowsW * 128, b_bytes = NT * 128;
-    const uint32_t a_stage = 2 * a_bytes, b_stage = 2 * b_bytes;
-    const uint32_t nst = (c.nchunks + 1) / 2;
+    const uint32_t b_bytes = NT * 128;                 // one 64-wide K chunk of the activation tile
+    const uint32_t nst = (a.k + 127) / 128;            // tensor-memory stages over K
     const uint32_t raw_stage_bytes = kTcRowsW * c.seg_stride;
-    const uint32_t nraw = (c.nchunks + CPR - 1) / CPR;
+    const uint32_t nraw = (a.k + KR - 1) / KR;
     // wait styles: the single producer / MMA warps spin (they are the critical path and cost one warp's issue
     // slots); the dequantising warps space their polls out
     const uint32_t wmode_cr = (c.debug & 32u) ? 0u : 0xFFFFFFFFu;
-    const uint32_t wmode_dq = (c.debug & 16u) ? 0xFFFFFFFFu : 32u;
+    const uint32_t wmode_dq = (c.debug & 16u) ? 0xFFFFFFFFu : 0u;
 
     if (warp == kTcDequantWarps) {
         // ======================= producer warp: bulk copies of the packed activation tiles =======================
-        RingPos rp;
-        for (uint32_t st = 0; st < nst; st++, rp.adv(1, c.stages)) {
-            const uint32_t s = rp.s;
-            if (!mbar_wait(&ab_empty[s], rp.ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_cr)) break;
-            const uint32_t bytes = (2 * st + 1 < c.nchunks) ? b_stage : b_bytes;  // the two tiles are adjacent in xpack
-            if (lane == 0 && (c.debug & 8u)) mbar_arrive(&b_full[s]);
-            if (lane == 0 && !(c.debug & 8u)) {
-                mbar_expect_tx(&b_full[s], bytes);
-                bulk_g2s(smem + c.b_off + s * b_stage, xpack + ((size_t)tt * c.nchunks + 2 * st) * (size_t)b_bytes, bytes,
-                         &b_full[s]);
+        // Chunk kc reuses the slot of chunk kc - b_stages, which belonged to K stage (kc - b_stages) / 2: the
+        // slot is free once that stage's MMAs have completed (stage_done, the same barrier the dequantising
+        // warps wait on before they overwrite the stage's weights in tensor memory).
+        if (lane == 0) {
+            uint32_t s = 0;
+            for (uint32_t kc = 0; kc < c.nchunks; kc++) {
+                if (kc >= c.b_stages) {
+                    const uint32_t j = (kc - c.b_stages) >> 1;
+                    if (!mbar_wait(&stage_done[j & (kTcAStages - 1)], (j / kTcAStages) & 1u, &abort_flag, a.status,
+                                   ST_WAIT_EMPTY_TIMEOUT, wmode_cr))
+                        break;
+                }
+                if (c.debug & 8u) {
+                    mbar_arrive(&b_full[s]);
+                } else {
+                    mbar_expect_tx(&b_full[s], b_bytes);
+                    bulk_g2s(smem + c.b_off + s * b_bytes, xpack + ((size_t)tt * c.nchunks + kc) * (size_t)b_bytes, b_bytes,
+                             &b_full[s]);
+                }
+                if (++s == c.b_stages) s = 0;
             }
         }
     } else if (warp == kTcDequantWarps + 1) {
         // ======================= MMA warp: one thread issues tcgen05.mma =======================
-        // The issuing thread is on the critical path of every K chunk, so its loop is kept minimal: running
-        // operand descriptors (advanced by one stage per chunk, rewound at the ring's end), four MMAs, one commit.
-        constexpr uint32_t idesc = umma_idesc_f16(kTcRowsW, NT);
-        const uint64_t ad0 = umma_desc_k_sw128(smem_base + c.a_off);
-        const uint64_t bd0 = umma_desc_k_sw128(smem_base + c.b_off);
-        const uint64_t a_step = a_stage >> 4, b_step = b_stage >> 4;  // descriptor address field is in 16-byte units
-        const uint64_t a_sub = a_bytes >> 4, b_sub = b_bytes >> 4;
-        uint64_t ad = ad0, bd = bd0;
-        uint32_t s = 0, ph = 0;
-        for (uint32_t st = 0; st < nst; st++) {
-            const bool trace = (c.debug & 256u) && blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && st < 256;
-            long long t_a = 0, t_b = 0;
-            if (!mbar_wait(&a_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
-            if (trace) t_a = clock64();
-            if (!mbar_wait(&b_full[s], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
-            if (trace) t_b = clock64();
-            tc_fence_after();
-            if (lane == 0) {
-                if (!(c.debug & 4u)) {
-                    umma_f16_ss(tmem_d, ad, bd, idesc, st != 0 ? 1u : 0u);
-                    umma_f16_ss(tmem_d, ad + 2, bd + 2, idesc, 1u);
-                    umma_f16_ss(tmem_d, ad + 4, bd + 4, idesc, 1u);
-                    umma_f16_ss(tmem_d, ad + 6, bd + 6, idesc, 1u);
-                    if (2 * st + 1 < c.nchunks) {
-                        umma_f16_ss(tmem_d, ad + a_sub, bd + b_sub, idesc, 1u);
-                        umma_f16_ss(tmem_d, ad + a_sub + 2, bd + b_sub + 2, idesc, 1u);
-                        umma_f16_ss(tmem_d, ad + a_sub + 4, bd + b_sub + 4, idesc, 1u);
-                        umma_f16_ss(tmem_d, ad + a_sub + 6, bd + b_sub + 6, idesc, 1u);
+        // A lone thread runs at a fraction of an instruction per cycle, and every K stage passes through this
+        // loop, so it holds nothing but the waits, eight MMAs and one commit.
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_f16(kTcRowsW, NT);
+            const uint64_t bd0 = umma_desc_k_sw128(smem_base + c.b_off);
+            const uint64_t b_step = b_bytes >> 4;  // descriptor address field is in 16-byte units
+            const bool do_mma = !(c.debug & 4u);
+            uint64_t bd = bd0;
+            uint32_t sa = 0, aph = 0, sb = 0, bph = 0, kc = 0;
+            for (uint32_t st = 0; st < nst; st++) {
+                if (!mbar_wait(&a_full[sa], aph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
+                if (!mbar_wait(&b_full[sb], bph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
+                tc_fence_after();
+                const uint32_t a_col = tmem_d + kTcAColBase + sa * kTcACols;
+                if (do_mma) {
+                    umma_f16_ts(tmem_d, a_col, bd, idesc, st != 0 ? 1u : 0u);
+                    umma_f16_ts(tmem_d, a_col + 8, bd + 2, idesc, 1u);
+                    umma_f16_ts(tmem_d, a_col + 16, bd + 4, idesc, 1u);
+                    umma_f16_ts(tmem_d, a_col + 24, bd + 6, idesc, 1u);
+                }
+                bd += b_step;
+                if (++sb == c.b_stages) { sb = 0; bph ^= 1u; bd = bd0; }
+                if (++kc < c.nchunks) {
+                    if (!mbar_wait(&b_full[sb], bph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
+                    if (do_mma) {
+                        umma_f16_ts(tmem_d, a_col + 32, bd, idesc, 1u);
+                        umma_f16_ts(tmem_d, a_col + 40, bd + 2, idesc, 1u);
+                        umma_f16_ts(tmem_d, a_col + 48, bd + 4, idesc, 1u);
+                        umma_f16_ts(tmem_d, a_col + 56, bd + 6, idesc, 1u);
                     }
+                    bd += b_step;
+                    if (++sb == c.b_stages) { sb = 0; bph ^= 1u; bd = bd0; }
+                    ++kc;
                 }
-                if (c.debug & 128u) mbar_arrive(&ab_empty[s]);
-                else umma_commit(&ab_empty[s]);
+                umma_commit(&stage_done[sa]);  // frees the stage's weights and its two activation chunks
                 if (st + 1 == nst) umma_commit(&acc_full);
-                if (trace) {  // experiment only: the timeline overwrites the start of y
-                    long long *tr = reinterpret_cast<long long *>(a.y) + 3 * st;
-                    tr[0] = t_a;
-                    tr[1] = t_b;
-                    tr[2] = clock64();
-                }
-            }
-            __syncwarp();
-            ad += a_step;
-            bd += b_step;
-            if (++s == c.stages) {
-                s = 0;
-                ph ^= 1u;
-                ad = ad0;
-                bd = bd0;
+                if (++sa == kTcAStages) { sa = 0; aph ^= 1u; }
             }
         }
+        __syncwarp();
     } else {
         // ======================= dequantise warps, then epilogue =======================
-        // Thread t of a set owns weight row t/2 and the 32-element half t%2 of every K chunk of the set:
-        // one GGML block (Q4_0 / Q8_0) or one 32-run of a Q6_K super-block per chunk, i.e. four 16-byte
-        // groups of the swizzled A tile.
-        const uint32_t set = warp / kTcSetWarps;
-        const uint32_t t = tid - set * (kTcSetWarps * 32);
-        const uint32_t rr = t >> 1, half = t & 1u;
+        // The 16 warps form two sets of 8; set s fills the K stages st with st % 2 == s, so that a warp has two
+        // stage times for each of its turns.  Within a set, thread (warp w, lane l) owns weight row
+        // 32 (w % 4) + l of the tile -- the tensor-memory lane its warp may address -- and the 64-element half
+        // (w / 4) % 2 of the stage: thirty-two packed f16 pairs = one 32-column store.
+        const uint32_t q4 = warp & 3u, half = (warp >> 2) & 1u, set = warp >> 3;
+        const uint32_t rr = q4 * 32 + lane;
         const bool row_ok = n0 + rr < a.n;
         const uint32_t row_lo4 = (uint32_t)((uintptr_t)(wbase + (size_t)(n0 + rr) * row_bytes) & 15u);
-        const uint32_t a_row_off = (rr >> 3) * 1024 + (rr & 7u) * 128;
-        // Raw weight rows are short (72..272 bytes per stage and row), too short for one bulk copy each to be
-        // efficient, so all dequantising threads stream them as 16-byte cp.async chunks, one raw stage ahead
+        // Raw weight rows are short (144..272 bytes per stage and row), too short for one bulk copy each to be
+        // efficient, so all dequantising threads stream them as 16-byte cp.async chunks, a few raw stages ahead
         // of the one being dequantised.  Each row is fetched as the 16-byte aligned superset of its (only
         // 2-byte aligned) segment; readers skip the lead-in bytes.
         // The (row, 16-byte chunk) pairs a thread copies are the same in every raw stage, so they are worked
@@ -579,6 +587,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         constexpr uint32_t kSegFull = (KR / QK) * BB;
         constexpr uint32_t kCmax = (kSegFull + 30u) >> 4;  // most 16-byte chunks a row segment can need
         static_assert(kTcRowsW * kCmax <= kRawSlots * kTcDequantWarps * 32, "raw copy slots");
+        static_assert(KR == 256, "a raw stage feeds one K stage of each set");
         const uint32_t rows_here = min((uint32_t)kTcRowsW, a.n - n0);
         const uint8_t *slot_src[kRawSlots];     // start of the thread's row (global)
         uint32_t slot_dst[kRawSlots];           // row's place inside a raw stage + chunk offset (shared, relative)
@@ -617,10 +626,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             issue_raw(rnext, islot);
             if (++islot == R) { islot = 0; iph ^= 1u; }
         }
-        bool ok = true;
-        RingPos rp;  // stage of this set's next chunk: set s owns the half s of every stage
-        uint32_t rs = 0, rph = 0;      // slot / parity of the stage being read
-        for (uint32_t r = 0; ok && r < nraw; r++) {
+        uint32_t rs = 0, rph = 0;      // slot / parity of the raw stage being read
+        const uint32_t a_dst = tmem_d + ((q4 * 32) << 16) + kTcAColBase + 32 * half;
+        for (uint32_t r = 0; r < nraw; r++) {
             if (rnext < nraw) {
                 // the slot's previous tenant (stage rnext - R) must have been released by every warp
                 if (!mbar_wait(&raw_empty[islot], iph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) break;
@@ -629,42 +637,53 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                 if (++islot == R) { islot = 0; iph ^= 1u; }
             }
             if (!mbar_wait(&raw_full[rs], rph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_dq)) break;
-            const uint32_t pre = (row_lo4 + ((r * KR) / QK) * BB) & 15u;
-            const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
-            // an odd chunk count leaves the last stage half empty; set 1 still takes part in its hand-off
-            for (uint32_t kc = r * CPR + set; kc < min((r + 1) * CPR, 2 * nst); kc += 2, rp.adv(1, c.stages)) {
-                const uint32_t s = rp.s;
-                if (!mbar_wait(&ab_empty[s], rp.ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) {
-                    ok = false;
+            const uint32_t st = 2 * r + set;       // this set's K stage inside raw stage r
+            if (st < nst) {
+                const uint32_t sa = st & (kTcAStages - 1);
+                // the MMAs that read this stage's previous contents (K stage st - 4) have completed
+                if (st >= kTcAStages &&
+                    !mbar_wait(&stage_done[sa], ((st / kTcAStages) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT,
+                               wmode_dq))
                     break;
-                }
-                const uint32_t kvalid = kc < c.nchunks ? min(64u, a.k - kc * 64) : 0u;  // elements of this chunk inside K
-                uint8_t *arow = smem + c.a_off + s * a_stage + set * a_bytes + a_row_off;
-                uint4 v[4];
-                if (row_ok && 32 * half < kvalid && !(c.debug & 1u)) {
-                    dequant32<T>(seg, (kc - r * CPR) * 64 + 32 * half, v);
-                } else {
+                tc_fence_after();
+                const uint32_t pre = (row_lo4 + ((r * KR) / QK) * BB) & 15u;
+                const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
+                uint32_t regs[32];
 #pragma unroll
-                    for (int j = 0; j < 4; j++) v[j] = make_uint4(0, 0, 0, 0);
-                }
+                for (uint32_t hh = 0; hh < 2; hh++) {
+                    uint4 v[4];
+                    const uint32_t e0 = 128 * set + 64 * half + 32 * hh;  // element offset inside the raw stage
+                    if (row_ok && r * KR + e0 < a.k && !(c.debug & 1u)) {
+                        dequant32<T>(seg, e0, v);
+                    } else {
 #pragma unroll
-                for (int j = 0; j < 4; j++)
-                    *reinterpret_cast<uint4 *>(arow + (((4 * half + j) ^ (rr & 7u)) << 4)) = v[j];
-                if (!(c.debug & 64u)) fence_proxy_async_smem();
+                        for (int i = 0; i < 4; i++) v[i] = make_uint4(0, 0, 0, 0);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        regs[16 * hh + 4 * i + 0] = v[i].x;
+                        regs[16 * hh + 4 * i + 1] = v[i].y;
+                        regs[16 * hh + 4 * i + 2] = v[i].z;
+                        regs[16 * hh + 4 * i + 3] = v[i].w;
+                    }
+                }
+                tmem_st_32x32_x32(a_dst + sa * kTcACols, regs);
+                tmem_st_wait();
+                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&a_full[s]);
+                if (lane == 0) mbar_arrive(&a_full[sa]);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&raw_empty[rs]);  // this warp is done reading raw stage r
             if (++rs == R) { rs = 0; rph ^= 1u; }
         }
+        const uint32_t g = warp >> 2;
         // ---- epilogue: TMEM -> registers -> y ----
         if (!abort_flag && mbar_wait(&acc_full, 0, &abort_flag, a.status, ST_WAIT_MMA_TIMEOUT, 200)) {
             tc_fence_after();
-            const uint32_t q4 = warp & 3u;           // tensor-memory lane quarter this warp may read
-            const uint32_t wrow = n0 + q4 * 32 + lane;
+            const uint32_t wrow = n0 + rr;
 #pragma unroll 1
-            for (uint32_t col = (warp >> 2) * 32; col < NT; col += (kTcDequantWarps / 4) * 32) {
+            for (uint32_t col = g * 32; col < NT; col += (kTcDequantWarps / 4) * 32) {
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_d + ((q4 * 32) << 16) + col, v);
                 tmem_ld_wait();
@@ -685,7 +704,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     __syncthreads();
     if (warp == kTcDequantWarps + 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_d, NT);
+        tmem_dealloc(tmem_d, kTcTmemCols);
     }
 }
 
@@ -715,8 +734,8 @@ size_t qmm_tc_scratch_bytes(const QmmArgs &a, uint32_t nt, bool routed) {
 // dequantisation of its 128 weight rows); ties go to the larger tile, which dequantises less in total.
 uint32_t qmm_tc_pick_nt(int ggml_type, uint32_t rows, uint32_t n, int sm_count, bool routed) {
     if (routed || rows <= 64) return 64;
-    // shared memory: two stages of 256-row activation tiles only fit beside the small Q4_0 raw ring
-    const uint32_t cap = ggml_type == GT_Q4_0 ? 256u : 128u;
+    (void)ggml_type;
+    const uint32_t cap = 256u;
     const uint32_t cands[3] = {256, 128, 64};
     uint32_t best = cap;
     uint64_t best_cost = ~0ull;
@@ -752,29 +771,28 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     c.nchunks = (a.k + 63) / 64;
     c.seg_stride = round_up_u((KR / QK) * BB + 15, 16) + 16;
     if ((c.seg_stride / 16) % 2 == 0) c.seg_stride += 16;  // odd multiple of 16 B: rows spread over the banks
-    const uint32_t a_stage = 2 * kTcRowsW * 128, b_stage = 2 * NT * 128;  // two 64-wide K chunks per stage
+    const uint32_t b_bytes = NT * 128;  // one 64-wide K chunk of the activation tile
     const uint32_t raw_slot = kTcRowsW * c.seg_stride;
     const uint32_t limit = 224 * 1024;
-    if (2 * raw_slot + 2 * (a_stage + b_stage) > limit) return cudaErrorInvalidConfiguration;
-    // two operand stages first (three when the tiles are small), the rest goes to the raw weight ring
-    uint32_t stages = NT <= 64 ? 3 : 2;
+    // activation ring first (at least two raw slots kept back), the rest goes to the raw weight ring
+    uint32_t b_stages = (limit - 2 * raw_slot) / b_bytes;
+    if (b_stages > 6) b_stages = 6;
     if (const char *e = getenv("MLXN_TC_STAGES")) {  // experiment switch
         const uint32_t v = (uint32_t)atoi(e);
-        if (v >= 2 && v <= 6 && 2 * raw_slot + v * (a_stage + b_stage) <= limit) stages = v;
+        if (v >= 2 && v <= b_stages) b_stages = v;
     }
-    uint32_t raw_slots = (limit - stages * (a_stage + b_stage)) / raw_slot;
+    if (b_stages < 2) return cudaErrorInvalidConfiguration;
+    uint32_t raw_slots = (limit - b_stages * b_bytes) / raw_slot;
     if (raw_slots > 6) raw_slots = 6;
     if (const char *e = getenv("MLXN_TC_RAW")) {  // experiment switch
         const uint32_t v = (uint32_t)atoi(e);
         if (v >= 2 && v <= raw_slots) raw_slots = v;
     }
-    if (raw_slots < 2) return cudaErrorInvalidConfiguration;
     const uint32_t raw_bytes = raw_slots * raw_slot;
-    c.stages = stages;
+    c.b_stages = b_stages;
     c.raw_slots = raw_slots;
-    c.a_off = 0;
-    c.b_off = stages * a_stage;
-    c.raw_off = c.b_off + stages * b_stage;
+    c.b_off = 0;
+    c.raw_off = b_stages * b_bytes;
     const size_t smem = (size_t)c.raw_off + raw_bytes + 1024;  // + slack for manual 1024-byte alignment
 
     size_t tiles;
