@@ -22,6 +22,10 @@
 namespace mlxn {
 cudaError_t launch_qmv(int ggml_type, const QmvArgs &a, bool want_stream, int sm_count, cudaStream_t st,
                        const char **kname);
+bool qmv_tc_supported(int ggml_type, const QmvArgs &a);
+size_t qmv_tc_scratch_bytes(const QmvArgs &a);
+cudaError_t launch_qmv_tc(int ggml_type, const QmvArgs &a, uint8_t *scratch, uint32_t *flags, int sm_count, cudaStream_t st,
+                          int *launches);
 cudaError_t launch_qmm_tc(int ggml_type, const QmmArgs &a, bool routed, uint32_t nt, uint8_t *scratch, cudaStream_t st,
                           int *launches);
 cudaError_t launch_qmm_simt(int ggml_type, const QmmArgs &a, bool routed, uint32_t max_rows, cudaStream_t st);
@@ -77,16 +81,17 @@ void mlxn_detail_count_launches(int launches) {
     g_last_kernel = "qmm_tc";
 }
 
-static std::atomic<int> g_opt_qmv{-1}, g_opt_qmm{-1};  // -1 unset, 0 simple/simt, 1 stream/tc
-static bool opt_qmv_stream() {
+static std::atomic<int> g_opt_qmv{-1}, g_opt_qmm{-1};  // -1 unset; qmv: 0 simple, 1 stream, 2 tc; qmm: 0 simt, 1 tc
+static int opt_qmv() {
     int v = g_opt_qmv.load();
     if (v < 0) {
         const char *e = getenv("MLXN_QMV");
-        v = (e && strcmp(e, "simple") == 0) ? 0 : 1;
+        v = (e && strcmp(e, "simple") == 0) ? 0 : (e && strcmp(e, "stream") == 0) ? 1 : 2;
         g_opt_qmv = v;
     }
-    return v == 1;
+    return v;
 }
+static bool opt_qmv_stream() { return opt_qmv() >= 1; }
 static bool opt_qmm_tc() {
     int v = g_opt_qmm.load();
     if (v < 0) {
@@ -158,6 +163,7 @@ struct mlxn_graph {
     uint64_t dispatches = 0;
 };
 
+constexpr size_t kStatusBlockBytes = 8192;
 struct mlxn_encoder {
     mlxn_device *dev = nullptr;
     cudaStream_t stream = nullptr;
@@ -220,9 +226,10 @@ extern "C" uint32_t mlxn_mm_id_routing_threshold(void) {
 extern "C" int mlxn_set_option(const char *key, const char *value) {
     if (!key || !value) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: option key/value must not be null");
     if (strcmp(key, "qmv") == 0) {
-        if (strcmp(value, "stream") == 0) g_opt_qmv = 1;
+        if (strcmp(value, "tc") == 0) g_opt_qmv = 2;
+        else if (strcmp(value, "stream") == 0) g_opt_qmv = 1;
         else if (strcmp(value, "simple") == 0) g_opt_qmv = 0;
-        else return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: qmv must be 'stream' or 'simple'");
+        else return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: qmv must be 'tc', 'stream' or 'simple'");
         return MLXN_OK;
     }
     if (strcmp(key, "qmm") == 0) {
@@ -564,8 +571,9 @@ extern "C" int mlxn_encoder_create(mlxn_device *dev, mlxn_encoder **out) {
     cudaError_t err = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking);
     if (err == cudaSuccess) err = cudaEventCreate(&e->ev_start);
     if (err == cudaSuccess) err = cudaEventCreate(&e->ev_end);
-    if (err == cudaSuccess) err = cudaMalloc((void **)&e->status_dev, 4);
-    if (err == cudaSuccess) err = cudaMemset(e->status_dev, 0, 4);
+    // status word, then (256 bytes in) the zero-initialised flag words the tensor-core mat-vec's CTAs hand work over with
+    if (err == cudaSuccess) err = cudaMalloc((void **)&e->status_dev, kStatusBlockBytes);
+    if (err == cudaSuccess) err = cudaMemset(e->status_dev, 0, kStatusBlockBytes);
     if (err == cudaSuccess) err = cudaHostAlloc((void **)&e->status_host, 4, cudaHostAllocDefault);
     if (err != cudaSuccess) {
         if (e->stream) cudaStreamDestroy(e->stream);
@@ -663,7 +671,7 @@ extern "C" int mlxn_encoder_wait_until_completed(mlxn_encoder *enc) {
     if (enc->committed && *enc->status_host != 0) {
         const uint32_t s = *enc->status_host;
         *enc->status_host = 0;
-        cudaMemsetAsync(enc->status_dev, 0, 4, enc->stream);
+        cudaMemsetAsync(enc->status_dev, 0, kStatusBlockBytes, enc->stream);  // a kernel that gave up may have left its flag words set
         return fail(MLXN_COMMAND_BUFFER_ERROR, "Command buffer error: %s (status %u)", status_text(s), s);
     }
     return MLXN_OK;
@@ -818,6 +826,17 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
         a.n_experts = 1;
         a.expert_stride = 0;
         a.status = enc->status_dev;
+        if (opt_qmv() == 2 && qmv_tc_supported((int)p->ggml_type, a)) {
+            // tensor-core path: packed activations, block sums and split-K partial sums live in the encoder's arena
+            uint8_t *scratch = nullptr;
+            if ((rc = encoder_scratch(enc, qmv_tc_scratch_bytes(a), &scratch))) return rc;
+            int launches = 0;
+            CUDA_TRY(launch_qmv_tc((int)p->ggml_type, a, scratch, enc->status_dev + 64, dev->sm_count, enc->stream, &launches),
+                     "mat-vec launch");
+            g_launches.fetch_add((uint64_t)launches);
+            g_last_kernel = "qmv_tc";
+            continue;
+        }
         CUDA_TRY(launch_qmv((int)p->ggml_type, a, stream, dev->sm_count, enc->stream, &g_last_kernel), "mat-vec launch");
         g_launches.fetch_add(1);
     }
