@@ -217,19 +217,35 @@ __host__ __device__ inline uint32_t vt_range_begin(uint32_t c, uint32_t total, u
     return (uint32_t)(((uint64_t)c * total) / grid);
 }
 
-// One stage of a CTA's walk over its unit range: up to cu units of one tile.
-struct VtStage {
-    uint32_t tile, kun, cnt;
-    bool seg_end;   // the tile's segment (run of stages of this tile inside the CTA's range) ends with this stage
+// A CTA's walk over its unit range, one raw stage (up to cu units of one tile) at a time.  Every role of the
+// CTA walks the same sequence; the ring slot and its phase bit move along.  One division, at the start.
+struct VtWalk {
+    uint32_t u, u1, upt, cu, nslots;
+    uint32_t tile, kun, cnt;   // current stage: tile, first K unit inside the tile, units
+    uint32_t slot, ph;         // raw ring slot of the stage and the parity of this use of it
+    uint32_t sidx;
+    bool seg_end;              // the tile's segment (run of stages of this tile inside the CTA's range) ends with this stage
+    __device__ __forceinline__ void setup() {
+        cnt = min(cu, min(upt - kun, u1 - u));
+        seg_end = (kun + cnt == upt) || (u + cnt == u1);
+    }
+    __device__ __forceinline__ void init(uint32_t u0, uint32_t u1_, uint32_t upt_, uint32_t cu_, uint32_t nslots_) {
+        u = u0; u1 = u1_; upt = upt_; cu = cu_; nslots = nslots_;
+        tile = u0 / upt_;
+        kun = u0 - tile * upt_;
+        slot = 0; ph = 0; sidx = 0;
+        setup();
+    }
+    __device__ __forceinline__ bool done() const { return u >= u1; }
+    __device__ __forceinline__ void next() {
+        u += cnt;
+        kun += cnt;
+        if (kun == upt) { kun = 0; tile++; }
+        if (++slot == nslots) { slot = 0; ph ^= 1u; }
+        sidx++;
+        if (u < u1) setup();
+    }
 };
-__device__ __forceinline__ VtStage vt_stage_at(uint32_t u, uint32_t u1, uint32_t upt, uint32_t cu) {
-    VtStage s;
-    s.tile = u / upt;
-    s.kun = u - s.tile * upt;
-    s.cnt = min(cu, min(upt - s.kun, u1 - u));
-    s.seg_end = (s.kun + s.cnt == upt) || (u + s.cnt == u1);
-    return s;
-}
 
 // MP = activation row pairs carried (1, 2 or 4)
 template <int T, int MP>
@@ -269,7 +285,8 @@ __global__ void __launch_bounds__(kVtThreads, 1)
         for (int s = 0; s < 2; s++) mbar_init(&fin_all[s], kVtCvtWarps);
         mbar_init_fence();
         if (!(c.debug & 2u)) {
-            const VtStage st = vt_stage_at(u0, u1, c.upt, c.cu);
+            VtWalk st;
+            st.init(u0, u1, c.upt, c.cu, c.nslots);
             mbar_expect_tx(&raw_full[0], kVtRows * c.row_stride + st.cnt * (4 * 2048 + kVtAuxBytes));
             asm volatile(
                 "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -293,12 +310,10 @@ __global__ void __launch_bounds__(kVtThreads, 1)
 
     if (warp == kVtCvtWarps) {
         // ======================= producer warp: one tensor copy of weights per stage + the packed activations =======================
-        uint32_t sidx = 0;
-        for (uint32_t u = u0; u < u1; sidx++) {
-            const VtStage st = vt_stage_at(u, u1, c.upt, c.cu);
-            const uint32_t slot = sidx % c.nslots;
-            if (sidx >= c.nslots &&
-                !mbar_wait(&raw_empty[slot], ((sidx / c.nslots) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wspin))
+        VtWalk st;
+        for (st.init(u0, u1, c.upt, c.cu, c.nslots); !st.done(); st.next()) {
+            const uint32_t slot = st.slot, sidx = st.sidx;
+            if (sidx >= c.nslots && !mbar_wait(&raw_empty[slot], st.ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, 0u))
                 break;
             uint8_t *sl = smem + slot * c.slot_bytes;
             if (lane == 0) {
@@ -321,7 +336,6 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                 }
             }
             __syncwarp();
-            u += st.cnt;
         }
     } else if (warp > kVtCvtWarps) {
         // ======================= MMA warps: warp w2 serves groups w2 and w2 + 2 =======================
@@ -329,12 +343,12 @@ __global__ void __launch_bounds__(kVtThreads, 1)
         if (lane == 0) {
             const uint32_t w2 = warp - kVtCvtWarps - 1;
             constexpr uint32_t idesc = umma_idesc_f16(kVtRows, 16);
-            uint32_t sidx = 0, uc = 0;
+            uint32_t uc = 0;
             bool ok = true;
-            for (uint32_t u = u0; ok && u < u1; sidx++) {
-                const VtStage st = vt_stage_at(u, u1, c.upt, c.cu);
-                const uint32_t slot = sidx % c.nslots;
-                if (!mbar_wait(&raw_full[slot], (sidx / c.nslots) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wspin)) break;
+            VtWalk st;
+            for (st.init(u0, u1, c.upt, c.cu, c.nslots); ok && !st.done(); st.next()) {
+                const uint32_t slot = st.slot;
+                if (!mbar_wait(&raw_full[slot], st.ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wspin)) break;
                 const uint64_t bd0 = umma_desc_k_sw128(smem_base + slot * c.slot_bytes);
                 for (uint32_t ul = 0; ok && ul < st.cnt; ul++, uc++) {
                     const uint32_t p = uc & 1u, par = (uc >> 1) & 1u;
@@ -363,7 +377,6 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                     }
                 }
                 if (ok) umma_commit(&raw_empty[slot]);  // this warp's MMAs no longer read the stage's activation tiles
-                u += st.cnt;
             }
         }
         __syncwarp();
@@ -471,13 +484,13 @@ __global__ void __launch_bounds__(kVtThreads, 1)
             if (pv_seg_end) finalize();
         };
 
-        uint32_t sidx = 0, uc = 0;
-        for (uint32_t u = u0; ok && u < u1; sidx++) {
-            const VtStage st = vt_stage_at(u, u1, c.upt, c.cu);
-            const uint32_t slot = sidx % c.nslots;
-            if (!mbar_wait(&raw_full[slot], (sidx / c.nslots) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wdq)) break;
-            if (ktrace && sidx == 0) ktr[3] = clock64();
-            if (st.kun == 0 || u == u0) seg_ka = st.kun;
+        uint32_t uc = 0;
+        VtWalk st;
+        for (st.init(u0, u1, c.upt, c.cu, c.nslots); ok && !st.done(); st.next()) {
+            const uint32_t slot = st.slot;
+            if (!mbar_wait(&raw_full[slot], st.ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wdq)) break;
+            if (ktrace && st.sidx == 0) ktr[3] = clock64();
+            if (st.kun == 0 || st.sidx == 0) seg_ka = st.kun;
             const uint32_t sl_base = smem_base + slot * c.slot_bytes;
             for (uint32_t ul = 0; ok && ul < st.cnt; ul++, uc++) {
                 const uint32_t p = uc & 1u, sl = 2 * g + p;
@@ -512,7 +525,6 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                 pv_ka = seg_ka;
                 pv_kb = st.kun + st.cnt;
             }
-            u += st.cnt;
         }
         if (ktrace) ktr[4] = clock64();
         if (ok && pv) retire_prev();
