@@ -316,7 +316,7 @@ def run_ours(args, rank, world, local_rank):
                    "distinct weights per step, larger than L2", "launch": "CUDA graph replay" if world == 1 else
                    "direct launches + NCCL all-gather per mat-vec", "parallelism": f"n-shard x{world}"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": None, "peak_kind": f"{peak_kind} copy bandwidth", "kernel": "qmv_stream_kernel",
+                     "traffic": None, "peak_kind": f"{peak_kind} copy bandwidth", "kernel": "qmv_tc_kernel (3+ rows, 2 rows with k >= 8192) and qmv_stream_kernel (1-2 rows)",
                      "note": "achieved = (weight + activation + output bytes of the 32 launches) / event-timed step"},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s * 1e3},

@@ -252,8 +252,10 @@ int mlxn_quantized_matmul_ggml_mm_noalloc(void *cuda_stream, const void *input_d
                                           void *output_dev, const mlxn_qmm_params *params);
 
 /* ---- tuning and introspection (no upstream counterpart) -------------------------------------- */
-/* Selects kernel variants for experiments: key/value pairs such as "qmv=stream|simple",
- * "qmm=tc|simt".  Unknown keys are MLXN_INVALID_ARGUMENT.  The defaults are the fast paths. */
+/* Selects kernel variants for experiments: key/value pairs "qmv=auto|tc|stream|simple" (auto: the tensor-core
+ * mat-vec from three activation rows up, the streaming SIMT kernel below; tc forces the tensor-core kernel
+ * wherever it applies) and "qmm=tc|simt".  Unknown keys are MLXN_INVALID_ARGUMENT.  The defaults (auto, tc)
+ * are the fast paths. */
 int mlxn_set_option(const char *key, const char *value);
 /* Name of the kernel variant the last operation on this thread launched (for tests and profiles). */
 const char *mlxn_last_kernel_name(void);

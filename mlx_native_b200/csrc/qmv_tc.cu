@@ -21,8 +21,8 @@
 // shared by several CTAs is summed into y with f32 atomic adds (the packing kernel zeroes y first); two
 // partial sums add up the same in either order, three or more may differ in the last bit from run to run.
 //
-// Supported here: Q4_0 and Q8_0, dense form, k % 256 == 0, 16-byte aligned weight rows.  Everything else
-// takes the SIMT kernels.
+// Supported here: Q4_0, Q8_0 (k % 256 == 0) and Q6_K (k % 2048 == 0), dense form, 16-byte aligned weight rows.
+// Everything else takes the SIMT kernels.
 #include <cuda.h>  // CUtensorMap (types only; the encoder is fetched through the runtime, no libcuda link)
 
 #include <cstdio>
@@ -44,24 +44,39 @@ constexpr int kVtUnitK = 256;           // K elements per unit (8 blocks: a mult
 constexpr int kVtMaxSlots = 8;          // raw ring depth bound
 constexpr int kVtMaxCtas = 160;
 
+// UB: bytes of a K unit of one row.  SS: sub-steps a group runs per unit (a sub-step is what one thread converts
+// and stores at a time: 64 K = 2 blocks, or for Q6_K 32 K = 2 scale groups).  SG: elements per scale (= per
+// accumulator).  AUX: bytes of per-unit side data (sums of x per scale group [256/SG][8] f32, scales [2][8] f32).
 template <int T> struct VtTraits;
-template <> struct VtTraits<GT_Q4_0> { static constexpr int UB = 144, SUB = 36, OFFSET = 8; };
-template <> struct VtTraits<GT_Q8_0> { static constexpr int UB = 272, SUB = 68, OFFSET = 128; };
+template <> struct VtTraits<GT_Q4_0> { static constexpr int UB = 144, SUB = 36, OFFSET = 8, SS = 1, SG = 32, AUX = 320; };
+template <> struct VtTraits<GT_Q8_0> { static constexpr int UB = 272, SUB = 68, OFFSET = 128, SS = 1, SG = 32, AUX = 320; };
+template <> struct VtTraits<GT_Q6_K> { static constexpr int UB = 210, SUB = 0, OFFSET = 32, SS = 2, SG = 16, AUX = 576; };
+constexpr int kVtQ6Box = 240;  // bytes per row of a Q6_K stage: the 210-byte super-block and its lead-in, an odd multiple of 16
 
-// K permutation inside a 32-element block: packed position p (pair p/2 of tensor-memory column, half p%2)
-// holds element vt_perm(p) of the block.  It follows from the cheapest way to pull code pairs out of a
-// 32-bit word of the block (mask / shift, or byte select), and the activations are packed the same way.
-__host__ __device__ inline uint32_t vt_perm(int ggml_type, uint32_t p) {
+__host__ __device__ inline uint32_t vt_aux_bytes(int ggml_type) { return ggml_type == GT_Q6_K ? 576u : 320u; }
+
+// K permutation inside a unit: packed position P (tensor-memory column P/2, half P%2, in the order the
+// sub-steps are stored) holds element vt_src(P) of the unit.  It follows from the cheapest way to pull code
+// pairs out of a 32-bit word of the block (mask / shift, or byte select); the activations are packed the same way.
+__host__ __device__ inline uint32_t vt_src(int ggml_type, uint32_t P) {
+    if (ggml_type == GT_Q6_K) {
+        // sub-step ss = 4 n + 2 pairB + lh (32 positions): two scale groups (q1|q2 then q3|q4 of the same 16 l's)
+        const uint32_t ss = P >> 5, p = P & 31u;
+        const uint32_t n = ss >> 2, pair_b = (ss >> 1) & 1u, lh = ss & 1u;
+        const uint32_t grp = p >> 4, col = (p & 15u) >> 1, hl = p & 1u;
+        const uint32_t l = 16 * lh + 4 * (col >> 1) + (col & 1u) + 2 * hl;
+        return 128 * n + l + 32 * pair_b + 64 * grp;
+    }
+    const uint32_t blk = P >> 5, p = P & 31u;
     const uint32_t col = p >> 1, hl = p & 1u;
     if (ggml_type == GT_Q4_0) {
         // word i = bytes 4i..4i+3 (low nibbles: elements 4i..4i+3, high nibbles: 16+4i..); four pairs per word
         const uint32_t i = col >> 2, j = col & 3u;
-        const uint32_t base = 4 * i + ((j & 1u) ? 16u : 0u) + ((j & 2u) ? 1u : 0u);
-        return base + 2 * hl;
+        return 32 * blk + 4 * i + ((j & 1u) ? 16u : 0u) + ((j & 2u) ? 1u : 0u) + 2 * hl;
     }
     // Q8_0: word i = elements 4i..4i+3; pairs (b0, b2) and (b1, b3)
     const uint32_t i = col >> 1, j = col & 1u;
-    return 4 * i + j + 2 * hl;
+    return 32 * blk + 4 * i + j + 2 * hl;
 }
 
 struct VtCfg {
@@ -75,12 +90,11 @@ struct VtCfg {
     uint32_t debug;
 };
 
-constexpr int kVtAuxBytes = 320;  // per K unit: block sums [8 blocks][8 rows] f32, then scales [2 halves][8 rows] f32
 constexpr int kVtMaxUnits = 1024; // K units per row the flag words cover (k <= 262144)
 
 struct VtScratch {
     uint8_t *xpack;      // [k/64][16 rows][128 B] f16 hi/lo tiles, 128-byte swizzled
-    uint8_t *aux;        // [k/256][kVtAuxBytes]
+    uint8_t *aux;        // [k/256][aux bytes of the format]
 };
 
 __device__ __forceinline__ uint32_t pack_h2(__half lo, __half hi) {
@@ -98,12 +112,11 @@ __device__ __forceinline__ uint32_t pack_h2(__half lo, __half hi) {
 __device__ __forceinline__ void vt_pack_half(const float *xr, uint32_t ku, uint32_t t, uint32_t h, uint32_t lane, int ggml_type,
                                              const VtScratch &s) {
     const uint32_t p0 = 128 * h + 4 * lane;            // first of the lane's 4 packed positions inside the unit
-    const uint32_t blk = p0 >> 5;                       // block of the unit (8 lanes per block)
     float v[4];
     float amax = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        v[i] = xr[(size_t)ku * kVtUnitK + blk * 32 + vt_perm(ggml_type, (p0 & 31u) + i)];
+        v[i] = xr[(size_t)ku * kVtUnitK + vt_src(ggml_type, p0 + i)];
         amax = fmaxf(amax, fabsf(v[i]));
     }
     for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -128,12 +141,18 @@ __device__ __forceinline__ void vt_pack_half(const float *xr, uint32_t ku, uint3
     uint8_t *tile = s.xpack + ((size_t)ku * 4 + chunk) * 2048 + t * 128 + ((j ^ t) << 4) + (q & 7u) * 2;
     *reinterpret_cast<uint2 *>(tile) = make_uint2(pack_h2(hi[0], hi[1]), pack_h2(hi[2], hi[3]));          // row t
     *reinterpret_cast<uint2 *>(tile + 1024) = make_uint2(pack_h2(lo[0], lo[1]), pack_h2(lo[2], lo[3]));   // row 8 + t
+    // sums per scale group: 32 positions (8 lanes) for Q4_0 / Q8_0, 16 positions (4 lanes) for Q6_K
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-    float *aux = reinterpret_cast<float *>(s.aux + (size_t)ku * kVtAuxBytes);
-    if ((lane & 7u) == 0) aux[blk * 8 + t] = sum;
-    if (lane == 0) aux[64 + h * 8 + t] = inv;
+    float *aux = reinterpret_cast<float *>(s.aux + (size_t)ku * vt_aux_bytes(ggml_type));
+    if (ggml_type == GT_Q6_K) {
+        if ((lane & 3u) == 0) aux[(p0 >> 4) * 8 + t] = sum;
+        if (lane == 0) aux[128 + h * 8 + t] = inv;
+    } else {
+        sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if ((lane & 7u) == 0) aux[(p0 >> 5) * 8 + t] = sum;
+        if (lane == 0) aux[64 + h * 8 + t] = inv;
+    }
 }
 
 // grid = K units, 512 threads: warp w packs activation row w / 2, half w % 2 of the CTA's unit; all threads zero
@@ -203,6 +222,64 @@ template <int T, int S4> __device__ __forceinline__ void vt_extract(uint32_t uni
     }
 }
 
+// Q6_K: one sub-step = the 16 l's [16 lh, 16 lh + 16) of half n of the super-block, for the quant pair
+// (q1, q3) or (q2, q4): two scale groups of 16 codes -> 16 packed pairs.  The super-block starts PRE bytes
+// into the row's 16-byte aligned stage (PRE = 2 (unit index % 8), the same for every row, so it is a
+// compile-time constant of the variant); every field offset below is PRE plus a multiple of 16.
+__device__ __forceinline__ int lds_s8(uint32_t addr) {
+    int v;
+    asm volatile("{ .reg .s16 t; ld.shared.s8 t, [%1]; cvt.s32.s16 %0, t; }" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(addr));
+    return v;
+}
+// four words that start PRE bytes into the 16-byte aligned address `a16`
+template <int PRE> __device__ __forceinline__ void lds_field16(uint32_t a16, uint32_t (&w)[4]) {
+    uint32_t W[8];
+    lds128(a16, W[0], W[1], W[2], W[3]);
+    if constexpr (PRE != 0) lds128(a16 + 16, W[4], W[5], W[6], W[7]);
+    constexpr int wo = PRE >> 2;
+#pragma unroll
+    for (int i = 0; i < 4; i++) w[i] = (PRE & 2) ? __funnelshift_r(W[wo + i], W[wo + i + 1], 16) : W[wo + i];
+}
+template <int PRE>
+__device__ __forceinline__ void vt_extract_q6k(uint32_t stage_row, uint32_t n, uint32_t g, uint32_t (&r)[16], float &d0, float &d1) {
+    const uint32_t pair_b = g >> 1, lh = g & 1u;
+    uint32_t ql[4], qh[4];
+    lds_field16<PRE>(stage_row + 64 * n + 32 * pair_b + 16 * lh, ql);
+    lds_field16<PRE>(stage_row + 128 + 32 * n + 16 * lh, qh);
+    const uint32_t sc_addr = stage_row + PRE + 192 + 8 * n + lh + 2 * pair_b;
+    const float d = half_bits_to_float(lds_u16(stage_row + PRE + 208));
+    d0 = d * (float)lds_s8(sc_addr);
+    d1 = d * (float)lds_s8(sc_addr + 4);
+    const uint32_t s_up = pair_b ? 2u : 4u, s_dn = pair_b ? 2u : 0u;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const uint32_t first = (ql[i] & 0x0F0F0F0Fu) | ((qh[i] << s_up) & 0x30303030u);
+        const uint32_t second = ((ql[i] >> 4) & 0x0F0F0F0Fu) | ((qh[i] >> s_dn) & 0x30303030u);
+        r[2 * i + 0] = __byte_perm(first, 0u, 0x4240);
+        r[2 * i + 1] = __byte_perm(first, 0u, 0x4341);
+        r[8 + 2 * i + 0] = __byte_perm(second, 0u, 0x4240);
+        r[8 + 2 * i + 1] = __byte_perm(second, 0u, 0x4341);
+    }
+}
+__device__ __forceinline__ void vt_extract_q6k_p(uint32_t p8, uint32_t stage_row, uint32_t n, uint32_t g, uint32_t (&r)[16],
+                                                 float &d0, float &d1) {
+    switch (p8) {  // uniform over the CTA
+    case 0: vt_extract_q6k<0>(stage_row, n, g, r, d0, d1); break;
+    case 1: vt_extract_q6k<2>(stage_row, n, g, r, d0, d1); break;
+    case 2: vt_extract_q6k<4>(stage_row, n, g, r, d0, d1); break;
+    case 3: vt_extract_q6k<6>(stage_row, n, g, r, d0, d1); break;
+    case 4: vt_extract_q6k<8>(stage_row, n, g, r, d0, d1); break;
+    case 5: vt_extract_q6k<10>(stage_row, n, g, r, d0, d1); break;
+    case 6: vt_extract_q6k<12>(stage_row, n, g, r, d0, d1); break;
+    default: vt_extract_q6k<14>(stage_row, n, g, r, d0, d1); break;
+    }
+}
+
 template <int T> __device__ __forceinline__ void vt_extract_g(uint32_t g, uint32_t unit, uint32_t (&r)[32], float &d0, float &d1) {
     switch (g) {  // uniform per warp
     case 0: vt_extract<T, 0>(unit, r, d0, d1); break;
@@ -253,8 +330,10 @@ __global__ void __launch_bounds__(kVtThreads, 1)
     qmv_tc_kernel(const QmvArgs a, const VtCfg c, const VtScratch sc, const __grid_constant__ CUtensorMap wmap) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    constexpr int UB = VtTraits<T>::UB;
+    constexpr int UB = VtTraits<T>::UB, SS = VtTraits<T>::SS, AUX = VtTraits<T>::AUX;
     constexpr float kOff = (float)VtTraits<T>::OFFSET;
+    // byte coordinate of a unit's tensor copy inside the row: Q6_K units start at the 16-byte boundary below them
+    auto unit_x = [](uint32_t kun) -> uint32_t { return T == GT_Q6_K ? ((kun * UB) & ~15u) >> 2 : kun * (UB / 4); };
     __shared__ __align__(8) uint64_t raw_full[kVtMaxSlots], raw_empty[kVtMaxSlots];
     __shared__ __align__(8) uint64_t a_full[2 * kVtGroups], d_full[2 * kVtGroups];
     __shared__ uint32_t tmem_base_s;
@@ -268,7 +347,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
     long long *ktr = reinterpret_cast<long long *>(a.y) + 2048;  // experiment: kernel-level timeline of CTA 0 / warp 0
     const bool ktrace = (c.debug & 256u) && cta == 0 && tid == 0;
     const uint32_t u0 = vt_range_begin(cta, c.total_units, grid), u1 = vt_range_begin(cta + 1, c.total_units, grid);
-    const uint32_t row_bytes = (a.k / 32) * BlockTraits<T>::BYTES;
+    const uint32_t row_bytes = (a.k / BlockTraits<T>::QK) * BlockTraits<T>::BYTES;
 
     if (warp == kVtCvtWarps && lane == 0) {
         // the producer's lane sets the barriers up and has the first weight stage on its way before the rest
@@ -287,10 +366,10 @@ __global__ void __launch_bounds__(kVtThreads, 1)
         if (!(c.debug & 2u)) {
             VtWalk st;
             st.init(u0, u1, c.upt, c.cu, c.nslots);
-            mbar_expect_tx(&raw_full[0], kVtRows * c.row_stride + st.cnt * (4 * 2048 + kVtAuxBytes));
+            mbar_expect_tx(&raw_full[0], kVtRows * c.row_stride + st.cnt * (4 * 2048 + AUX));
             asm volatile(
                 "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                ::"r"(smem_u32(smem + c.raw_off)), "l"(&wmap), "r"(st.kun * (UB / 4)), "r"(st.tile * kVtRows),
+                ::"r"(smem_u32(smem + c.raw_off)), "l"(&wmap), "r"(unit_x(st.kun)), "r"(st.tile * kVtRows),
                   "r"(smem_u32(&raw_full[0]))
                 : "memory");
         }
@@ -323,16 +402,16 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                     // one tensor copy brings the stage's 128 rows (rows past n arrive as zeros); the box is always
                     // cu units wide, a stage that uses fewer just ignores the rest (reads past a row's end are zeros too)
                     if (sidx != 0) {  // stage 0's weights were requested during set-up
-                        mbar_expect_tx(&raw_full[slot], kVtRows * c.row_stride + st.cnt * (4 * 2048 + kVtAuxBytes));
+                        mbar_expect_tx(&raw_full[slot], kVtRows * c.row_stride + st.cnt * (4 * 2048 + AUX));
                         asm volatile(
                             "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                            ::"r"(smem_u32(sl + c.raw_off)), "l"(&wmap), "r"(st.kun * (UB / 4)), "r"(st.tile * kVtRows),
+                            ::"r"(smem_u32(sl + c.raw_off)), "l"(&wmap), "r"(unit_x(st.kun)), "r"(st.tile * kVtRows),
                               "r"(smem_u32(&raw_full[slot]))
                             : "memory");
                     }
                     if (sidx == 0) asm volatile("griddepcontrol.wait;" ::: "memory");  // the packed activations come from the kernel before
                     bulk_g2s(sl, sc.xpack + (size_t)st.kun * 4 * 2048, st.cnt * 4 * 2048, &raw_full[slot]);
-                    bulk_g2s(sl + c.xs_off, sc.aux + (size_t)st.kun * kVtAuxBytes, st.cnt * kVtAuxBytes, &raw_full[slot]);
+                    bulk_g2s(sl + c.xs_off, sc.aux + (size_t)st.kun * AUX, st.cnt * AUX, &raw_full[slot]);
                 }
             }
             __syncwarp();
@@ -350,30 +429,42 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                 const uint32_t slot = st.slot;
                 if (!mbar_wait(&raw_full[slot], st.ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wspin)) break;
                 const uint64_t bd0 = umma_desc_k_sw128(smem_base + slot * c.slot_bytes);
-                for (uint32_t ul = 0; ok && ul < st.cnt; ul++, uc++) {
-                    const uint32_t p = uc & 1u, par = (uc >> 1) & 1u;
+                for (uint32_t ul = 0; ok && ul < st.cnt; ul++) {
 #pragma unroll
-                    for (uint32_t h = 0; h < 2; h++) {
-                        const uint32_t g = w2 + 2 * h, sl = 2 * g + p;
-                        const bool tr = (c.debug & 256u) && cta == 0 && w2 == 0 && uc < 40;
-                        long long *tp = reinterpret_cast<long long *>(a.y) + 8 * (2 * uc + h);
-                        if (tr) tp[0] = clock64();
-                        if (!mbar_wait(&a_full[sl], par, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wspin)) {
-                            ok = false;
-                            break;
+                    for (uint32_t n = 0; n < (uint32_t)SS; n++, uc++) {   // uc counts sub-steps per group
+                        const uint32_t p = uc & 1u, par = (uc >> 1) & 1u;
+#pragma unroll
+                        for (uint32_t h = 0; h < 2; h++) {
+                            const uint32_t g = w2 + 2 * h, sl = 2 * g + p;
+                            const bool tr = (c.debug & 256u) && cta == 0 && w2 == 0 && uc < 40;
+                            long long *tp = reinterpret_cast<long long *>(a.y) + 8 * (2 * uc + h);
+                            if (tr) tp[0] = clock64();
+                            if (!mbar_wait(&a_full[sl], par, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wspin)) {
+                                ok = false;
+                                break;
+                            }
+                            if (tr) tp[1] = clock64();
+                            tc_fence_after();
+                            const uint32_t acol = tmem + sl * kVtSlotCols, dcol = acol + 32;
+                            if (!(c.debug & 4u)) {
+                                if constexpr (T == GT_Q6_K) {
+                                    // sub-step ss = 4 n + g: 32 K = half of 64-wide chunk ss / 2; one MMA per scale group
+                                    const uint32_t ss = 4 * n + g;
+                                    const uint64_t bd = bd0 + (uint64_t)((ul * 4 + (ss >> 1)) * (2048 >> 4) + (ss & 1u) * 4);
+                                    umma_f16_ts(dcol, acol, bd, idesc, 0u);
+                                    umma_f16_ts(dcol + 16, acol + 8, bd + 2, idesc, 0u);
+                                } else {
+                                    const uint64_t bd = bd0 + (uint64_t)((ul * 4 + g) * (2048 >> 4));
+                                    umma_f16_ts(dcol, acol, bd, idesc, 0u);
+                                    umma_f16_ts(dcol, acol + 8, bd + 2, idesc, 1u);
+                                    umma_f16_ts(dcol + 16, acol + 16, bd + 4, idesc, 0u);
+                                    umma_f16_ts(dcol + 16, acol + 24, bd + 6, idesc, 1u);
+                                }
+                            }
+                            umma_commit(&d_full[sl]);
+                            if (tr) tp[2] = clock64();
                         }
-                        if (tr) tp[1] = clock64();
-                        tc_fence_after();
-                        const uint32_t acol = tmem + sl * kVtSlotCols, dcol = acol + 32;
-                        const uint64_t bd = bd0 + (uint64_t)((ul * 4 + g) * (2048 >> 4));
-                        if (!(c.debug & 4u)) {
-                            umma_f16_ts(dcol, acol, bd, idesc, 0u);
-                            umma_f16_ts(dcol, acol + 8, bd + 2, idesc, 1u);
-                            umma_f16_ts(dcol + 16, acol + 16, bd + 4, idesc, 0u);
-                            umma_f16_ts(dcol + 16, acol + 24, bd + 6, idesc, 1u);
-                        }
-                        umma_commit(&d_full[sl]);
-                        if (tr) tp[2] = clock64();
+                        if (!ok) break;
                     }
                 }
                 if (ok) umma_commit(&raw_empty[slot]);  // this warp's MMAs no longer read the stage's activation tiles
@@ -492,38 +583,51 @@ __global__ void __launch_bounds__(kVtThreads, 1)
             if (ktrace && st.sidx == 0) ktr[3] = clock64();
             if (st.kun == 0 || st.sidx == 0) seg_ka = st.kun;
             const uint32_t sl_base = smem_base + slot * c.slot_bytes;
-            for (uint32_t ul = 0; ok && ul < st.cnt; ul++, uc++) {
-                const uint32_t p = uc & 1u, sl = 2 * g + p;
-                const bool tr = (c.debug & 256u) && cta == 0 && warp == 0 && lane == 0 && uc < 40;
-                long long *tp = reinterpret_cast<long long *>(a.y) + 1024 + 8 * uc;
-                if (tr) tp[0] = clock64();
-                uint32_t r[32];
-                float d0, d1;
-                vt_extract_g<T>(g, sl_base + c.raw_off + row * c.row_stride + ul * UB, r, d0, d1);
-                // the slot's previous contents were consumed: its accumulators were read back two units ago
-                if (tr) tp[1] = clock64();
-                tmem_st_32x32_x32(lane_base + sl * kVtSlotCols, r);
-                tmem_st_wait();
-                if (tr) tp[2] = clock64();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&a_full[sl]);
-                if (tr) tp[3] = clock64();
-                if (pv) retire_prev();
-                if (tr) tp[4] = clock64();
-                pv = true;
-                pv_sl = sl;
-                pv_par = (uc >> 1) & 1u;
-                pv_d0 = d0;
-                pv_d1 = d1;
-                pv_xs = sl_base + c.xs_off + ul * kVtAuxBytes + 2 * g * 32;
-                pv_ts = sl_base + c.xs_off + ul * kVtAuxBytes + 256 + (g >> 1) * 32;
-                pv_slot = slot;
-                pv_stage_end = ul + 1 == st.cnt;
-                pv_seg_end = pv_stage_end && st.seg_end;
-                pv_tile = st.tile;
-                pv_ka = seg_ka;
-                pv_kb = st.kun + st.cnt;
+            for (uint32_t ul = 0; ok && ul < st.cnt; ul++) {
+#pragma unroll
+                for (uint32_t n = 0; n < (uint32_t)SS; n++, uc++) {   // uc counts this group's sub-steps
+                    if (!ok) break;
+                    const uint32_t p = uc & 1u, sl = 2 * g + p;
+                    const bool tr = (c.debug & 256u) && cta == 0 && warp == 0 && lane == 0 && uc < 40;
+                    long long *tp = reinterpret_cast<long long *>(a.y) + 1024 + 8 * uc;
+                    if (tr) tp[0] = clock64();
+                    float d0, d1;
+                    // the slot's previous contents were consumed: its accumulators were read back two sub-steps ago
+                    if constexpr (T == GT_Q6_K) {
+                        uint32_t r[16];
+                        vt_extract_q6k_p((st.kun + ul) & 7u, sl_base + c.raw_off + row * c.row_stride, n, g, r, d0, d1);
+                        if (tr) tp[1] = clock64();
+                        tmem_st_32x32_x16(lane_base + sl * kVtSlotCols, r);
+                    } else {
+                        uint32_t r[32];
+                        vt_extract_g<T>(g, sl_base + c.raw_off + row * c.row_stride + ul * UB, r, d0, d1);
+                        if (tr) tp[1] = clock64();
+                        tmem_st_32x32_x32(lane_base + sl * kVtSlotCols, r);
+                    }
+                    tmem_st_wait();
+                    if (tr) tp[2] = clock64();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&a_full[sl]);
+                    if (tr) tp[3] = clock64();
+                    if (pv) retire_prev();
+                    if (tr) tp[4] = clock64();
+                    pv = true;
+                    pv_sl = sl;
+                    pv_par = (uc >> 1) & 1u;
+                    pv_d0 = d0;
+                    pv_d1 = d1;
+                    // sums of x for the sub-step's two scale groups, and the scale of its half of the unit
+                    const uint32_t ss = T == GT_Q6_K ? 4 * n + g : g;
+                    pv_xs = sl_base + c.xs_off + ul * AUX + 2 * ss * 32;
+                    pv_ts = sl_base + c.xs_off + ul * AUX + (AUX - 64) + (T == GT_Q6_K ? n : (g >> 1)) * 32;
+                    pv_slot = slot;
+                    pv_stage_end = ul + 1 == st.cnt && n + 1 == (uint32_t)SS;
+                    pv_seg_end = pv_stage_end && st.seg_end;
+                    pv_tile = st.tile;
+                    pv_ka = seg_ka;
+                    pv_kb = st.kun + st.cnt;
+                }
             }
         }
         if (ktrace) ktr[4] = clock64();
@@ -547,7 +651,8 @@ __global__ void __launch_bounds__(kVtThreads, 1)
 // ------------------------------------------------------------------------------------------------
 static bool vt_have_encoder();
 bool qmv_tc_supported(int ggml_type, const QmvArgs &a) {
-    if (ggml_type != GT_Q4_0 && ggml_type != GT_Q8_0) return false;
+    if (ggml_type != GT_Q4_0 && ggml_type != GT_Q8_0 && ggml_type != GT_Q6_K) return false;
+    if (ggml_type == GT_Q6_K && a.k % 2048 != 0) return false;  // rows of 210-byte super-blocks start on 16-byte boundaries
     if (a.ids || a.nprob != 1 || a.m < 1 || a.m > 8) return false;
     if (a.k % kVtUnitK != 0 || a.k == 0 || a.n == 0 || a.k / kVtUnitK > (uint32_t)kVtMaxUnits) return false;
     if ((uint64_t)a.m * a.n >= (1ull << 32)) return false;
@@ -559,7 +664,7 @@ static inline size_t vt_align(size_t v, size_t al) { return (v + al - 1) / al * 
 
 // Scratch layout: packed activation tiles | per-unit block sums and scales.
 size_t qmv_tc_scratch_bytes(const QmvArgs &a) {
-    return vt_align((size_t)(a.k / 64) * 2048, 1024) + vt_align((size_t)(a.k / kVtUnitK) * kVtAuxBytes, 1024);
+    return vt_align((size_t)(a.k / 64) * 2048, 1024) + vt_align((size_t)(a.k / kVtUnitK) * 576, 1024);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -621,11 +726,11 @@ static cudaError_t launch_vt_t(const QmvArgs &a, uint8_t *scratch, uint32_t *fla
     c.cu = T == GT_Q4_0 ? 3u : 1u;
     if (const char *e = getenv("MLXN_VT_CU")) {  // experiment switch
         const uint32_t v = (uint32_t)atoi(e);
-        if (v >= 1 && v <= 5 && v * UB / 4 <= 256) c.cu = v;
+        if (T != GT_Q6_K && v >= 1 && v <= 5 && v * UB / 4 <= 256) c.cu = v;
     }
-    c.row_stride = c.cu * UB;
+    c.row_stride = T == GT_Q6_K ? (uint32_t)kVtQ6Box : c.cu * UB;
     c.xs_off = c.cu * 4 * 2048;
-    c.raw_off = (uint32_t)vt_align(c.xs_off + c.cu * kVtAuxBytes, 128);
+    c.raw_off = (uint32_t)vt_align(c.xs_off + c.cu * VtTraits<T>::AUX, 128);
     c.slot_bytes = (uint32_t)vt_align(c.raw_off + (size_t)kVtRows * c.row_stride, 1024);
     const uint32_t limit = 208 * 1024;
     c.nslots = limit / c.slot_bytes;
@@ -650,12 +755,12 @@ static cudaError_t launch_vt_t(const QmvArgs &a, uint8_t *scratch, uint32_t *fla
     // the weight matrix as a 2-D tensor of 32-bit words: [n rows][row_bytes / 4], box = 128 rows x cu units
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return cudaErrorNotSupported;
-    const uint32_t row_bytes = (a.k / 32) * BlockTraits<T>::BYTES;
+    const uint32_t row_bytes = (a.k / BlockTraits<T>::QK) * BlockTraits<T>::BYTES;
     alignas(64) CUtensorMap wmap;
     {
         const cuuint64_t gdim[2] = {row_bytes / 4, a.n};
         const cuuint64_t gstride[1] = {row_bytes};
-        const cuuint32_t box[2] = {c.cu * UB / 4, (cuuint32_t)kVtRows};
+        const cuuint32_t box[2] = {c.row_stride / 4, (cuuint32_t)kVtRows};
         const cuuint32_t estr[2] = {1, 1};
         if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(a.w), gdim, gstride, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -677,6 +782,7 @@ cudaError_t launch_qmv_tc(int ggml_type, const QmvArgs &a, uint8_t *scratch, uin
     switch (ggml_type) {
     case GT_Q4_0: return launch_vt_t<GT_Q4_0>(a, scratch, flags, sm_count, st, launches);
     case GT_Q8_0: return launch_vt_t<GT_Q8_0>(a, scratch, flags, sm_count, st, launches);
+    case GT_Q6_K: return launch_vt_t<GT_Q6_K>(a, scratch, flags, sm_count, st, launches);
     default: return cudaErrorInvalidValue;
     }
 }

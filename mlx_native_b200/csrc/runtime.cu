@@ -81,12 +81,12 @@ void mlxn_detail_count_launches(int launches) {
     g_last_kernel = "qmm_tc";
 }
 
-static std::atomic<int> g_opt_qmv{-1}, g_opt_qmm{-1};  // -1 unset; qmv: 0 simple, 1 stream, 2 tc; qmm: 0 simt, 1 tc
+static std::atomic<int> g_opt_qmv{-1}, g_opt_qmm{-1};  // -1 unset; qmv: 0 simple, 1 stream, 2 tc, 3 auto; qmm: 0 simt, 1 tc
 static int opt_qmv() {
     int v = g_opt_qmv.load();
     if (v < 0) {
         const char *e = getenv("MLXN_QMV");
-        v = (e && strcmp(e, "simple") == 0) ? 0 : (e && strcmp(e, "stream") == 0) ? 1 : 2;
+        v = (e && strcmp(e, "simple") == 0) ? 0 : (e && strcmp(e, "stream") == 0) ? 1 : (e && strcmp(e, "tc") == 0) ? 2 : 3;
         g_opt_qmv = v;
     }
     return v;
@@ -226,10 +226,11 @@ extern "C" uint32_t mlxn_mm_id_routing_threshold(void) {
 extern "C" int mlxn_set_option(const char *key, const char *value) {
     if (!key || !value) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: option key/value must not be null");
     if (strcmp(key, "qmv") == 0) {
-        if (strcmp(value, "tc") == 0) g_opt_qmv = 2;
+        if (strcmp(value, "auto") == 0) g_opt_qmv = 3;
+        else if (strcmp(value, "tc") == 0) g_opt_qmv = 2;
         else if (strcmp(value, "stream") == 0) g_opt_qmv = 1;
         else if (strcmp(value, "simple") == 0) g_opt_qmv = 0;
-        else return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: qmv must be 'tc', 'stream' or 'simple'");
+        else return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: qmv must be 'auto', 'tc', 'stream' or 'simple'");
         return MLXN_OK;
     }
     if (strcmp(key, "qmm") == 0) {
@@ -826,7 +827,11 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
         a.n_experts = 1;
         a.expert_stride = 0;
         a.status = enc->status_dev;
-        if (opt_qmv() == 2 && qmv_tc_supported((int)p->ggml_type, a)) {
+        // The tensor-core kernel's time does not grow with the number of rows, the streaming SIMT kernel's does
+        // (it wins for one row, and for two rows unless K is long): "auto" picks by that measured crossover.
+        const int mode = opt_qmv();
+        const bool want_tc = mode == 2 || (mode == 3 && (a.m >= 3 || (a.m == 2 && a.k >= 8192)));
+        if (want_tc && qmv_tc_supported((int)p->ggml_type, a)) {
             // tensor-core path: packed activations, block sums and split-K partial sums live in the encoder's arena
             uint8_t *scratch = nullptr;
             if ((rc = encoder_scratch(enc, qmv_tc_scratch_bytes(a), &scratch))) return rc;

@@ -79,6 +79,8 @@ def test_no_cpu_fallback_without_a_gpu():
 def test_options_and_threshold_env():
     mx.set_option("qmv", "simple")
     mx.set_option("qmv", "stream")
+    mx.set_option("qmv", "tc")
+    mx.set_option("qmv", "auto")
     with pytest.raises(mx.InvalidArgument):
         mx.set_option("qmv", "cpu")
     with pytest.raises(mx.InvalidArgument):

@@ -15,11 +15,15 @@ def ctx():
     return Ctx()
 
 
-@pytest.fixture(params=["stream", "simple"])
+@pytest.fixture(params=["tc", "stream", "simple"])
 def variant(request):
+    # "tc" is the library default; shapes the tensor-core kernel does not take fall through to "stream"
     mx.set_option("qmv", request.param)
     yield request.param
-    mx.set_option("qmv", "stream")
+    mx.set_option("qmv", "auto")
+
+
+KERNEL_OF = {"tc": "qmv_tc", "stream": "qmv_stream", "simple": "qmv_simple"}
 
 
 def check(ctx, tname, wq, x, n, k, abs_tol=None, tol=MV_TOL):
@@ -63,7 +67,7 @@ def test_production_shape(ctx, variant, tname, sw, sx, tol):
     n = k = 4096
     wq = lcg_weights(sw, n, k, TYPES[tname][1])
     check(ctx, tname, wq, orc.lcg_f32(sx, k)[None], n, k, abs_tol=tol)
-    assert mx.last_kernel_name() == ("qmv_stream" if variant == "stream" else "qmv_simple")
+    assert mx.last_kernel_name() == KERNEL_OF[variant]
 
 
 # ---- the benchmark's first configuration: Q4_0, m=1, 4096 x 4096, N(0,0.02) weights, GGML quantizer, seed 0
@@ -84,11 +88,12 @@ def test_all_m(ctx, variant, tname, m):
 @pytest.mark.parametrize("tname", ["Q8_0", "Q6_K"])
 @pytest.mark.parametrize("n,k", [(4096, 4096), (12288, 4096), (4096, 12288)])
 @pytest.mark.parametrize("m", [1, 8])
-def test_decode_sweep_shapes(ctx, tname, n, k, m):
-    mx.set_option("qmv", "stream")
+@pytest.mark.parametrize("kernel", ["tc", "stream"])
+def test_decode_sweep_shapes(ctx, tname, n, k, m, kernel):
+    mx.set_option("qmv", kernel)
     wq = normal_weights(11, n, k, TYPES[tname][1])
     y = check(ctx, tname, wq, normal_acts(5, m, k), n, k)
-    assert mx.last_kernel_name() == "qmv_stream"
+    assert mx.last_kernel_name() == KERNEL_OF[kernel]
     # a row's result does not depend on how many rows share the weights (up to summation order)
     if m == 8:
         x3 = normal_acts(5, 8, k)[3:4]
@@ -134,8 +139,8 @@ def test_zero_weights_and_zero_scale(ctx, variant):
         assert np.all(y == 0)
 
 
-def test_stream_equals_simple_closely(ctx):
-    """The two mat-vec kernels agree to within summation-order rounding."""
+def test_kernels_agree_closely(ctx):
+    """The three mat-vec kernels agree to within summation-order rounding."""
     n, k = 512, 4096
     for tname in ("Q4_0", "Q8_0", "Q6_K"):
         gtype, otype = TYPES[tname]
@@ -145,9 +150,13 @@ def test_stream_equals_simple_closely(ctx):
         a = ctx.matmul(gtype, wq, x, n, k)
         mx.set_option("qmv", "simple")
         b = ctx.matmul(gtype, wq, x, n, k)
-        mx.set_option("qmv", "stream")
+        mx.set_option("qmv", "tc")
+        c = ctx.matmul(gtype, wq, x, n, k)
+        assert mx.last_kernel_name() == "qmv_tc"
         _, ad = orc.qmatmul(otype, wq, x, n, k, nthreads=8)
+        mx.set_option("qmv", "auto")
         assert norm_err(a, b, ad) <= MV_TOL
+        assert norm_err(a, c, ad) <= MV_TOL
 
 
 # ---- error behaviour (src/ops/quantized_matmul_ggml.rs:283-334)

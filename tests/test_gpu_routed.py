@@ -42,7 +42,7 @@ def test_id_vs_nonid_bit_exact(ctx, qmv, tname, n_tokens, n, k):
         y_ref, ad = orc.qmatmul_id(otype, stacked, stride, x, ids, top_k, n, k, n_experts)
         assert norm_err(y, y_ref, ad) <= MV_TOL
     finally:
-        mx.set_option("qmv", "stream")
+        mx.set_option("qmv", "auto")
 
 
 def test_id_expert_stride_with_padding(ctx):

@@ -9,6 +9,15 @@ from tests.gpu_util import TYPES, Ctx, normal_acts, normal_weights
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def single_launch_matvec():
+    """These tests count launches and compare runs bit for bit: they use the one-kernel, fixed-summation-order
+    mat-vec.  (The tensor-core mat-vec is two launches and adds split tiles up with atomics.)"""
+    mx.set_option("qmv", "stream")
+    yield
+    mx.set_option("qmv", "auto")
+
+
 @pytest.fixture(scope="module")
 def ctx():
     return Ctx()
