@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <utility>
+
 namespace mlxn {
 
 // GGML type codes (same numbering as mlxn_ggml_type in include/mlxn_b200.h).
@@ -51,6 +53,8 @@ struct QmvArgs {
     uint32_t n_experts;
     uint64_t expert_stride; // bytes
     uint32_t *status;       // device status word
+    uint32_t early_weights; // 1: no kernel of this process wrote the weights, so they may be fetched before the
+                            // kernels ahead in the stream have finished (see launch_overlapped)
 };
 
 // Arguments of the mat-mat kernels (dense and grouped-by-expert).
@@ -70,6 +74,32 @@ struct QmmArgs {
     const uint32_t *tiles;   // optional compact tile list built by the bucketing kernel
     uint32_t *status;
 };
+
+// ---- overlapped launches -------------------------------------------------------------------------
+// A kernel launched with launch_overlapped may be scheduled while the kernel ahead of it in the stream is still
+// running: its blocks set themselves up (barriers, tensor memory, the first weight copies) and then call
+// grid_dependency_wait(), which returns once every kernel ahead has completed and its writes are visible.
+// Nothing a predecessor may have written is read before that call.  allow_dependents() lets the *next*
+// overlapped launch start in the same way.  Launched after anything else (copies, ordinary kernels) it
+// behaves like an ordinary launch.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void allow_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                     Args &&...args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // ---- small device helpers ---------------------------------------------------------------------
 __device__ __forceinline__ float half_bits_to_float(uint32_t h16) {

@@ -496,7 +496,10 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
 
     Walk w;
     bool more = w.init(a, c);
-    const uint32_t smask = c.stages - 1, gmask = ngrp - 1;
+    const uint32_t smask = c.stages - 1;
+    // This kernel may have been scheduled while the one ahead of it in the stream is still running.  Weights
+    // that no kernel writes can be requested right away; everything else waits for the kernels ahead.
+    if (!a.early_weights) grid_dependency_wait();
     // prime the ring: each group's leader issues the iterations it owns among the first c.stages
     if (more && leader) {
         for (uint32_t i = cg; i < c.stages; i += ngrp) {
@@ -505,6 +508,8 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
             issue(t, i);
         }
     }
+    if (a.early_weights) grid_dependency_wait();
+    allow_dependents();
 
     // Each warp steps through the whole walk slice by slice (every warp stages every activation slice) but
     // jumps straight between the iterations its group owns: it, it + ngrp, ...
@@ -757,7 +762,8 @@ template <int T, int M, int NW> static cudaError_t launch_stream_tm(const QmvArg
         if (e != cudaSuccess) return e;
         attr_smem[dev] = smem;
     }
-    qmv_stream_kernel<T, M, NW><<<grid, NW * 32, smem, st>>>(a, c);
+    cudaError_t le = launch_overlapped(qmv_stream_kernel<T, M, NW>, dim3(grid), dim3(NW * 32), smem, st, a, c);
+    if (le != cudaSuccess) return le;
     return cudaGetLastError();
 }
 

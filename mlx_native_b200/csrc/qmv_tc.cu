@@ -159,7 +159,8 @@ __device__ __forceinline__ void vt_pack_half(const float *xr, uint32_t ku, uint3
 // a slice of y (tiles split between CTAs of the mat-vec kernel are summed into it with atomic adds).
 __global__ void __launch_bounds__(512) qmv_tc_pack_kernel(const float *x, float *y, uint32_t m, uint32_t n, uint32_t k,
                                                           int ggml_type, VtScratch s, uint32_t debug) {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // the mat-vec kernel may start its weight stream
+    grid_dependency_wait();  // x (and y, which is zeroed here) belong to the kernels ahead until they are done
+    allow_dependents();      // the mat-vec kernel may set itself up and start its weight stream
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t total = m * n, per = (total + gridDim.x - 1) / gridDim.x;
     const uint32_t lo = min(total, blockIdx.x * per), hi = min(total, lo + per);
@@ -383,6 +384,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
     tc_fence_after();
     const uint32_t tmem = tmem_base_s;
     const uint32_t smem_base = smem_u32(smem);
+    allow_dependents();  // the next overlapped launch in the stream (its blocks wait for this grid before reading anything)
     if (ktrace) { ktr[0] = t_entry; ktr[1] = clock64(); }
     const uint32_t wspin = 0xFFFFFFFFu;   // producer / MMA warps poll back to back
     const uint32_t wdq = (c.debug & 16u) ? 0xFFFFFFFFu : ((c.debug & 32u) ? 20u : 0u);  // convert warps: suspend / spin / short sleeps
@@ -409,7 +411,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                               "r"(smem_u32(&raw_full[slot]))
                             : "memory");
                     }
-                    if (sidx == 0) asm volatile("griddepcontrol.wait;" ::: "memory");  // the packed activations come from the kernel before
+                    if (sidx == 0) grid_dependency_wait();  // the packed activations come from the kernel before
                     bulk_g2s(sl, sc.xpack + (size_t)st.kun * 4 * 2048, st.cnt * 4 * 2048, &raw_full[slot]);
                     bulk_g2s(sl + c.xs_off, sc.aux + (size_t)st.kun * AUX, st.cnt * AUX, &raw_full[slot]);
                 }
@@ -418,7 +420,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
         }
     } else if (warp > kVtCvtWarps) {
         // ======================= MMA warps: warp w2 serves groups w2 and w2 + 2 =======================
-        asm volatile("griddepcontrol.wait;" ::: "memory");
+        grid_dependency_wait();
         if (lane == 0) {
             const uint32_t w2 = warp - kVtCvtWarps - 1;
             constexpr uint32_t idesc = umma_idesc_f16(kVtRows, 16);
@@ -475,7 +477,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
         // ======================= convert + readout warps =======================
         // Thread (warp w, lane l): group g = w / 4 owns sub-step g (64 K) of every K unit; the thread owns
         // weight row 32 (w % 4) + l of the tile, which is also the tensor-memory lane its warp may address.
-        asm volatile("griddepcontrol.wait;" ::: "memory");
+        grid_dependency_wait();
         if (ktrace) ktr[2] = clock64();
         const uint32_t q4 = warp & 3u, g = warp >> 2;
         const uint32_t row = q4 * 32 + lane;
@@ -697,17 +699,7 @@ static cudaError_t launch_vt(const QmvArgs &a, const VtCfg &c, const VtScratch &
         if (e != cudaSuccess) return e;
         attr_smem[dev] = smem;
     }
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kVtThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, qmv_tc_kernel<T, MP>, a, c, sc, wmap);
+    return launch_overlapped(qmv_tc_kernel<T, MP>, dim3(grid), dim3(kVtThreads), smem, st, a, c, sc, wmap);
 }
 
 template <int T>
@@ -767,9 +759,8 @@ static cudaError_t launch_vt_t(const QmvArgs &a, uint8_t *scratch, uint32_t *fla
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    qmv_tc_pack_kernel<<<c.upt, 512, 0, st>>>(a.x, a.y, a.m, a.n, a.k, T, sc, c.debug);
+    cudaError_t e = launch_overlapped(qmv_tc_pack_kernel, dim3(c.upt), dim3(512), 0, st, a.x, a.y, a.m, a.n, a.k, (int)T, sc, c.debug);
     (*launches)++;
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     (*launches)++;
     if (a.m <= 2) return launch_vt<T, 1>(a, c, sc, wmap, grid, smem, st);

@@ -122,6 +122,7 @@ struct Storage {
     bool dev_newer = false;    // HBM holds data not yet reflected in the shadow
     cudaStream_t last_stream = nullptr;  // stream of the last operation that touched the storage
     bool has_last = false;
+    bool kernel_written = false;  // some operation of this library has used the storage as an output
     std::mutex mu;
 };
 
@@ -775,6 +776,7 @@ static int bind(mlxn_encoder *e, mlxn_buffer *b, bool is_output) {
         s->host_newer = false;
     }
     if (is_output && s->host) s->dev_newer = true;
+    if (is_output) s->kernel_written = true;
     s->last_stream = e->stream;
     s->has_last = true;
     b->refs.fetch_add(1);
@@ -827,6 +829,7 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
         a.n_experts = 1;
         a.expert_stride = 0;
         a.status = enc->status_dev;
+        a.early_weights = weight->st->kernel_written ? 0u : 1u;
         // The tensor-core kernel's time does not grow with the number of rows, the streaming SIMT kernel's does
         // (it wins for one row, and for two rows unless K is long): "auto" picks by that measured crossover.
         const int mode = opt_qmv();
