@@ -155,19 +155,21 @@ __device__ __forceinline__ void vt_pack_half(const float *xr, uint32_t ku, uint3
     }
 }
 
-// grid = K units, 512 threads: warp w packs activation row w / 2, half w % 2 of the CTA's unit; all threads zero
-// a slice of y (tiles split between CTAs of the mat-vec kernel are summed into it with atomic adds).
-__global__ void __launch_bounds__(512) qmv_tc_pack_kernel(const float *x, float *y, uint32_t m, uint32_t n, uint32_t k,
+// grid = (K units, ceil(2 m / 4)), 128 threads (small enough to share an SM with a mat-vec CTA of the operation
+// ahead): each warp packs one (activation row, half) of the CTA's unit; all threads zero a slice of y (tiles
+// split between CTAs of the mat-vec kernel are summed into it with atomic adds).
+__global__ void __launch_bounds__(128) qmv_tc_pack_kernel(const float *x, float *y, uint32_t m, uint32_t n, uint32_t k,
                                                           int ggml_type, VtScratch s, uint32_t debug) {
     grid_dependency_wait();  // x (and y, which is zeroed here) belong to the kernels ahead until they are done
     allow_dependents();      // the mat-vec kernel may set itself up and start its weight stream
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t total = m * n, per = (total + gridDim.x - 1) / gridDim.x;
-    const uint32_t lo = min(total, blockIdx.x * per), hi = min(total, lo + per);
+    const uint32_t ncta = gridDim.x * gridDim.y, cta = blockIdx.y * gridDim.x + blockIdx.x;
+    const uint32_t total = m * n, per = (total + ncta - 1) / ncta;
+    const uint32_t lo = min(total, cta * per), hi = min(total, lo + per);
     if (!(debug & 256u))
         for (uint32_t i = lo + tid; i < hi; i += blockDim.x) y[i] = 0.f;
-    const uint32_t t = warp >> 1, h = warp & 1u;
-    if (t < m) vt_pack_half(x + (size_t)t * k, blockIdx.x, t, h, lane, ggml_type, s);
+    const uint32_t task = blockIdx.y * 4 + warp;
+    if (task < 2 * m) vt_pack_half(x + (size_t)(task >> 1) * k, blockIdx.x, task >> 1, task & 1u, lane, ggml_type, s);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -759,7 +761,7 @@ static cudaError_t launch_vt_t(const QmvArgs &a, uint8_t *scratch, uint32_t *fla
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    cudaError_t e = launch_overlapped(qmv_tc_pack_kernel, dim3(c.upt), dim3(512), 0, st, a.x, a.y, a.m, a.n, a.k, (int)T, sc, c.debug);
+    cudaError_t e = launch_overlapped(qmv_tc_pack_kernel, dim3(c.upt, (2 * a.m + 3) / 4), dim3(128), 0, st, a.x, a.y, a.m, a.n, a.k, (int)T, sc, c.debug);
     (*launches)++;
     if (e != cudaSuccess) return e;
     (*launches)++;

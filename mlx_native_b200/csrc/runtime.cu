@@ -165,15 +165,29 @@ struct mlxn_graph {
 };
 
 constexpr size_t kStatusBlockBytes = 8192;
+// The reference encodes with MTLDispatchTypeConcurrent: dispatches may overlap on the GPU unless a
+// memory_barrier() separates them (src/encoder.rs:837-853), and its tracked-dispatch mode inserts the barrier
+// itself when the buffers of a new dispatch conflict with the current group (src/graph.rs:1494-1530).  Here a
+// "concurrent group" is spread over kLanes CUDA streams: an operation whose buffers do not conflict with the
+// group goes to the next lane, so that its kernels start on each SM as the previous operation's CTAs leave it
+// (launch latency and the tail of the previous kernel are hidden); a conflict, or an explicit barrier, joins the
+// lanes first.  Lane 0 is the encoder's own stream; commits, captures and graph launches happen there.
+constexpr int kLanes = 2;
 struct mlxn_encoder {
     mlxn_device *dev = nullptr;
-    cudaStream_t stream = nullptr;
+    cudaStream_t lanes[kLanes] = {};
+    cudaStream_t stream = nullptr;   // lane of the operation being encoded (lanes[cur_lane])
+    int cur_lane = 0;
+    bool lane_busy[kLanes] = {};     // lane has work of the current group that lane 0 has not been made to wait for
+    cudaEvent_t ev_fork = nullptr, ev_join[kLanes] = {};
+    std::vector<const void *> grp_reads, grp_writes;  // storages the current group reads / writes
+    bool grp_open = false;           // ev_fork marks the start of the current group
     cudaEvent_t ev_start = nullptr, ev_end = nullptr;
     bool started = false, committed = false, capturing = false;
     uint64_t cap_launch0 = 0, cap_dispatch0 = 0;
     std::vector<mlxn_buffer *> retained;
-    uint8_t *scratch = nullptr;
-    size_t scratch_bytes = 0;
+    uint8_t *scratch_lane[kLanes] = {};
+    size_t scratch_lane_bytes[kLanes] = {};
     std::vector<void *> retired;  // outgrown scratch buffers, freed after the next wait
     uint32_t *status_dev = nullptr;
     uint32_t *status_host = nullptr;  // pinned
@@ -570,7 +584,13 @@ extern "C" int mlxn_encoder_create(mlxn_device *dev, mlxn_encoder **out) {
     cudaSetDevice(dev->ordinal);
     auto *e = new mlxn_encoder();
     e->dev = dev;
-    cudaError_t err = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking);
+    cudaError_t err = cudaSuccess;
+    for (int l = 0; l < kLanes && err == cudaSuccess; l++) {
+        err = cudaStreamCreateWithFlags(&e->lanes[l], cudaStreamNonBlocking);
+        if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->ev_join[l], cudaEventDisableTiming);
+    }
+    e->stream = e->lanes[0];
+    if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->ev_fork, cudaEventDisableTiming);
     if (err == cudaSuccess) err = cudaEventCreate(&e->ev_start);
     if (err == cudaSuccess) err = cudaEventCreate(&e->ev_end);
     // status word, then (256 bytes in) the zero-initialised flag words the tensor-core mat-vec's CTAs hand work over with
@@ -578,7 +598,11 @@ extern "C" int mlxn_encoder_create(mlxn_device *dev, mlxn_encoder **out) {
     if (err == cudaSuccess) err = cudaMemset(e->status_dev, 0, kStatusBlockBytes);
     if (err == cudaSuccess) err = cudaHostAlloc((void **)&e->status_host, 4, cudaHostAllocDefault);
     if (err != cudaSuccess) {
-        if (e->stream) cudaStreamDestroy(e->stream);
+        for (int l = 0; l < kLanes; l++) {
+            if (e->lanes[l]) cudaStreamDestroy(e->lanes[l]);
+            if (e->ev_join[l]) cudaEventDestroy(e->ev_join[l]);
+        }
+        if (e->ev_fork) cudaEventDestroy(e->ev_fork);
         if (e->ev_start) cudaEventDestroy(e->ev_start);
         if (e->ev_end) cudaEventDestroy(e->ev_end);
         if (e->status_dev) cudaFree(e->status_dev);
@@ -596,7 +620,9 @@ static void encoder_release_retained(mlxn_encoder *e) {
     for (mlxn_buffer *b : e->retained) {
         {
             std::lock_guard<std::mutex> lk(b->st->mu);
-            if (b->st->has_last && b->st->last_stream == e->stream) b->st->has_last = false;
+            bool mine = false;
+            for (int l = 0; l < kLanes; l++) mine = mine || b->st->last_stream == e->lanes[l];
+            if (b->st->has_last && mine) b->st->has_last = false;
         }
         mlxn_buffer_release(b);
     }
@@ -608,29 +634,52 @@ static void encoder_release_retained(mlxn_encoder *e) {
 extern "C" void mlxn_encoder_destroy(mlxn_encoder *enc) {
     if (!enc) return;
     cudaSetDevice(enc->dev->ordinal);
-    cudaStreamSynchronize(enc->stream);
+    for (int l = 0; l < kLanes; l++) cudaStreamSynchronize(enc->lanes[l]);
     encoder_release_retained(enc);
-    if (enc->scratch) cudaFree(enc->scratch);
+    for (int l = 0; l < kLanes; l++)
+        if (enc->scratch_lane[l]) cudaFree(enc->scratch_lane[l]);
     cudaFree(enc->status_dev);
     cudaFreeHost(enc->status_host);
     cudaEventDestroy(enc->ev_start);
     cudaEventDestroy(enc->ev_end);
-    cudaStreamDestroy(enc->stream);
+    cudaEventDestroy(enc->ev_fork);
+    for (int l = 0; l < kLanes; l++) {
+        cudaEventDestroy(enc->ev_join[l]);
+        cudaStreamDestroy(enc->lanes[l]);
+    }
     delete enc;
 }
 
-extern "C" void *mlxn_encoder_stream(mlxn_encoder *enc) { return enc ? (void *)enc->stream : nullptr; }
+extern "C" void *mlxn_encoder_stream(mlxn_encoder *enc) { return enc ? (void *)enc->lanes[0] : nullptr; }
+
+// Ends the current concurrent group: lane 0 waits for every other lane that has work of the group; the next
+// operation starts a new group on lane 0.
+static int encoder_join_lanes(mlxn_encoder *e) {
+    for (int l = 1; l < kLanes; l++) {
+        if (!e->lane_busy[l]) continue;
+        CUDA_TRY(cudaEventRecord(e->ev_join[l], e->lanes[l]), "event record");
+        CUDA_TRY(cudaStreamWaitEvent(e->lanes[0], e->ev_join[l], 0), "stream wait");
+        e->lane_busy[l] = false;
+    }
+    e->grp_reads.clear();
+    e->grp_writes.clear();
+    e->grp_open = false;
+    e->cur_lane = 0;
+    e->stream = e->lanes[0];
+    return MLXN_OK;
+}
 
 extern "C" int mlxn_encoder_memory_barrier(mlxn_encoder *enc) {
     if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
-    g_barrier.fetch_add(1);  // one stream per encoder: operations already run in encode order
-    return MLXN_OK;
+    g_barrier.fetch_add(1);
+    cudaSetDevice(enc->dev->ordinal);
+    return encoder_join_lanes(enc);
 }
 
 static int encoder_begin_work(mlxn_encoder *e) {
     cudaSetDevice(e->dev->ordinal);
     if (!e->started && !e->capturing) {
-        CUDA_TRY(cudaEventRecord(e->ev_start, e->stream), "event record");
+        CUDA_TRY(cudaEventRecord(e->ev_start, e->lanes[0]), "event record");
         e->started = true;
         e->committed = false;
     }
@@ -641,12 +690,14 @@ extern "C" int mlxn_encoder_commit(mlxn_encoder *enc) {
     if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
     if (enc->capturing) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: commit while a capture is open");
     cudaSetDevice(enc->dev->ordinal);
+    int jrc = encoder_join_lanes(enc);
+    if (jrc) return jrc;
     if (!enc->started) {
-        CUDA_TRY(cudaEventRecord(enc->ev_start, enc->stream), "event record");
+        CUDA_TRY(cudaEventRecord(enc->ev_start, enc->lanes[0]), "event record");
         enc->started = true;
     }
-    CUDA_TRY(cudaMemcpyAsync(enc->status_host, enc->status_dev, 4, cudaMemcpyDeviceToHost, enc->stream), "status copy");
-    CUDA_TRY(cudaEventRecord(enc->ev_end, enc->stream), "event record");
+    CUDA_TRY(cudaMemcpyAsync(enc->status_host, enc->status_dev, 4, cudaMemcpyDeviceToHost, enc->lanes[0]), "status copy");
+    CUDA_TRY(cudaEventRecord(enc->ev_end, enc->lanes[0]), "event record");
     enc->committed = true;
     return MLXN_OK;
 }
@@ -665,7 +716,12 @@ extern "C" int mlxn_encoder_wait_until_completed(mlxn_encoder *enc) {
     if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
     cudaSetDevice(enc->dev->ordinal);
     g_sync.fetch_add(1);
-    cudaError_t e = enc->committed ? cudaEventSynchronize(enc->ev_end) : cudaStreamSynchronize(enc->stream);
+    cudaError_t e = cudaSuccess;
+    if (enc->committed) {
+        e = cudaEventSynchronize(enc->ev_end);
+    } else {
+        for (int l = 0; l < kLanes && e == cudaSuccess; l++) e = cudaStreamSynchronize(enc->lanes[l]);
+    }
     if (e == cudaSuccess) e = cudaGetLastError();
     encoder_release_retained(enc);
     enc->started = false;
@@ -673,7 +729,7 @@ extern "C" int mlxn_encoder_wait_until_completed(mlxn_encoder *enc) {
     if (enc->committed && *enc->status_host != 0) {
         const uint32_t s = *enc->status_host;
         *enc->status_host = 0;
-        cudaMemsetAsync(enc->status_dev, 0, kStatusBlockBytes, enc->stream);  // a kernel that gave up may have left its flag words set
+        cudaMemsetAsync(enc->status_dev, 0, kStatusBlockBytes, enc->lanes[0]);
         return fail(MLXN_COMMAND_BUFFER_ERROR, "Command buffer error: %s (status %u)", status_text(s), s);
     }
     return MLXN_OK;
@@ -700,7 +756,9 @@ extern "C" int mlxn_encoder_begin_capture(mlxn_encoder *enc) {
     if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
     if (enc->capturing) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: a capture is already open");
     cudaSetDevice(enc->dev->ordinal);
-    CUDA_TRY(cudaStreamBeginCapture(enc->stream, cudaStreamCaptureModeRelaxed), "begin capture");
+    int jrc = encoder_join_lanes(enc);  // the capture starts from lane 0 alone; other lanes fork from inside it
+    if (jrc) return jrc;
+    CUDA_TRY(cudaStreamBeginCapture(enc->lanes[0], cudaStreamCaptureModeRelaxed), "begin capture");
     enc->capturing = true;
     enc->cap_launch0 = g_launches.load();
     enc->cap_dispatch0 = g_dispatch.load();
@@ -710,9 +768,11 @@ extern "C" int mlxn_encoder_end_capture(mlxn_encoder *enc, mlxn_graph **out) {
     if (!enc || !out) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder and out must not be null");
     if (!enc->capturing) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: no capture is open");
     cudaSetDevice(enc->dev->ordinal);
+    int jrc = encoder_join_lanes(enc);  // every forked lane rejoins lane 0 before the capture ends
     enc->capturing = false;
     auto *g = new mlxn_graph();
-    cudaError_t e = cudaStreamEndCapture(enc->stream, &g->graph);
+    cudaError_t e = cudaStreamEndCapture(enc->lanes[0], &g->graph);
+    if (jrc && e == cudaSuccess) e = cudaErrorUnknown;
     if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
     if (e != cudaSuccess) {
         if (g->graph) cudaGraphDestroy(g->graph);
@@ -731,7 +791,8 @@ extern "C" int mlxn_graph_launch(mlxn_graph *graph, mlxn_encoder *enc) {
     if (!graph || !enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: graph and encoder must not be null");
     int rc = encoder_begin_work(enc);
     if (rc) return rc;
-    CUDA_TRY(cudaGraphLaunch(graph->exec, enc->stream), "graph launch");
+    if ((rc = encoder_join_lanes(enc))) return rc;  // the graph's buffers are unknown here: it is its own group
+    CUDA_TRY(cudaGraphLaunch(graph->exec, enc->lanes[0]), "graph launch");
     g_launches.fetch_add(graph->launches);
     g_dispatch.fetch_add(graph->dispatches);
     return MLXN_OK;
@@ -745,7 +806,9 @@ extern "C" void mlxn_graph_destroy(mlxn_graph *graph) {
 
 // Grows the encoder's scratch arena (kept for its lifetime; an outgrown arena is freed at the next wait).
 static int encoder_scratch(mlxn_encoder *e, size_t bytes, uint8_t **out) {
-    if (bytes > e->scratch_bytes) {
+    uint8_t *&scratch = e->scratch_lane[e->cur_lane];  // operations on different lanes may run at the same time
+    size_t &scratch_bytes = e->scratch_lane_bytes[e->cur_lane];
+    if (bytes > scratch_bytes) {
         const size_t want = bucket_size(bytes < (1u << 20) ? (1u << 20) : bytes);
         void *p = nullptr;
         cudaError_t err = cudaMalloc(&p, want);
@@ -753,11 +816,11 @@ static int encoder_scratch(mlxn_encoder *e, size_t bytes, uint8_t **out) {
             cudaGetLastError();
             return fail(MLXN_BUFFER_ALLOCATION_ERROR, "Failed to allocate device buffer of %zu bytes", want);
         }
-        if (e->scratch) e->retired.push_back(e->scratch);
-        e->scratch = static_cast<uint8_t *>(p);
-        e->scratch_bytes = want;
+        if (scratch) e->retired.push_back(scratch);
+        scratch = static_cast<uint8_t *>(p);
+        scratch_bytes = want;
     }
-    *out = e->scratch;
+    *out = scratch;
     return MLXN_OK;
 }
 
@@ -768,7 +831,9 @@ static int bind(mlxn_encoder *e, mlxn_buffer *b, bool is_output) {
     std::lock_guard<std::mutex> lk(s->mu);
     if (s->ordinal != e->dev->ordinal)
         return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: buffer lives on device %d, encoder on device %d", s->ordinal, e->dev->ordinal);
-    if (s->has_last && s->last_stream != e->stream) {
+    bool own_lane = false;  // lanes of one encoder are ordered by its group logic, not by host-side waits
+    for (int l = 0; l < kLanes; l++) own_lane = own_lane || s->last_stream == e->lanes[l];
+    if (s->has_last && !own_lane) {
         CUDA_TRY(cudaStreamSynchronize(s->last_stream), "stream synchronize");
     }
     if (s->host_newer) {
@@ -781,6 +846,60 @@ static int bind(mlxn_encoder *e, mlxn_buffer *b, bool is_output) {
     s->has_last = true;
     b->refs.fetch_add(1);
     e->retained.push_back(b);
+    return MLXN_OK;
+}
+
+// Places an operation: decides whether it may join the current concurrent group (none of its buffers conflicts
+// with what the group reads and writes; an input whose host shadow still has to be uploaded counts as written),
+// picks its lane, and binds its buffers there.
+struct OpBuf {
+    mlxn_buffer *b;
+    bool out;
+};
+static int op_begin(mlxn_encoder *e, std::initializer_list<OpBuf> bufs) {
+    int rc = encoder_begin_work(e);
+    if (rc) return rc;
+    auto has = [](const std::vector<const void *> &v, const void *p) {
+        for (const void *q : v)
+            if (q == p) return true;
+        return false;
+    };
+    bool conflict = false;
+    for (const OpBuf &ob : bufs) {
+        if (!ob.b) continue;
+        Storage *st = ob.b->st;
+        bool writes = ob.out;
+        {
+            std::lock_guard<std::mutex> lk(st->mu);
+            writes = writes || st->host_newer;
+        }
+        if (writes) conflict = conflict || has(e->grp_reads, st) || has(e->grp_writes, st);
+        else conflict = conflict || has(e->grp_writes, st);
+    }
+    if (conflict && (rc = encoder_join_lanes(e))) return rc;
+    const bool first = e->grp_reads.empty() && e->grp_writes.empty();
+    const int lane = first ? 0 : (e->cur_lane + 1) % kLanes;
+    if (!e->grp_open) {
+        CUDA_TRY(cudaEventRecord(e->ev_fork, e->lanes[0]), "event record");  // everything before this group
+        e->grp_open = true;
+    }
+    if (lane != 0 && !e->lane_busy[lane]) {
+        CUDA_TRY(cudaStreamWaitEvent(e->lanes[lane], e->ev_fork, 0), "stream wait");
+        e->lane_busy[lane] = true;
+    }
+    e->cur_lane = lane;
+    e->stream = e->lanes[lane];
+    for (const OpBuf &ob : bufs) {
+        if (!ob.b) continue;
+        Storage *st = ob.b->st;
+        bool writes = ob.out;
+        {
+            std::lock_guard<std::mutex> lk(st->mu);
+            writes = writes || st->host_newer;
+        }
+        (writes ? e->grp_writes : e->grp_reads).push_back(st);
+        if ((rc = bind(e, ob.b, ob.out))) return rc;
+    }
     return MLXN_OK;
 }
 
@@ -811,8 +930,7 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
                        mlxn_buffer *output, const mlxn_qmm_params *p) {
     int rc = touch_kernel(reg, dev, mv_kernel_name((int)p->ggml_type));
     if (rc) return rc;
-    if ((rc = encoder_begin_work(enc))) return rc;
-    if ((rc = bind(enc, input, false)) || (rc = bind(enc, weight, false)) || (rc = bind(enc, output, true))) return rc;
+    if ((rc = op_begin(enc, {{input, false}, {weight, false}, {output, true}}))) return rc;
     const bool stream = opt_qmv_stream();
     // rows are processed in groups of at most 8 (the reference launches one grid row per input row)
     for (uint32_t m0 = 0; m0 < p->m; m0 += 8) {
@@ -831,9 +949,9 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
         a.status = enc->status_dev;
         a.early_weights = weight->st->kernel_written ? 0u : 1u;
         // The tensor-core kernel's time does not grow with the number of rows, the streaming SIMT kernel's does
-        // (it wins for one row, and for two rows unless K is long): "auto" picks by that measured crossover.
+        // (it wins for one row, and for two rows of Q6_K unless K is long): "auto" picks by that measured crossover.
         const int mode = opt_qmv();
-        const bool want_tc = mode == 2 || (mode == 3 && (a.m >= 3 || (a.m == 2 && a.k >= 8192)));
+        const bool want_tc = mode == 2 || (mode == 3 && (a.m >= 3 || (a.m == 2 && ((int)p->ggml_type != GT_Q6_K || a.k >= 8192))));
         if (want_tc && qmv_tc_supported((int)p->ggml_type, a)) {
             // tensor-core path: packed activations, block sums and split-K partial sums live in the encoder's arena
             uint8_t *scratch = nullptr;
@@ -856,8 +974,7 @@ static int dispatch_mm(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
                        mlxn_buffer *output, const mlxn_qmm_params *p) {
     int rc = touch_kernel(reg, dev, mm_kernel_name((int)p->ggml_type));
     if (rc) return rc;
-    if ((rc = encoder_begin_work(enc))) return rc;
-    if ((rc = bind(enc, input, false)) || (rc = bind(enc, weight, false)) || (rc = bind(enc, output, true))) return rc;
+    if ((rc = op_begin(enc, {{input, false}, {weight, false}, {output, true}}))) return rc;
     QmmArgs a{};
     a.w = weight->dev();
     a.x = reinterpret_cast<const float *>(input->dev());
@@ -987,10 +1104,7 @@ static int dispatch_id_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *de
                           mlxn_buffer *ids, mlxn_buffer *output, const mlxn_qmm_id_params *p) {
     int rc = touch_kernel(reg, dev, mv_id_kernel_name((int)p->ggml_type));
     if (rc) return rc;
-    if ((rc = encoder_begin_work(enc))) return rc;
-    if ((rc = bind(enc, input, false)) || (rc = bind(enc, weight, false)) || (rc = bind(enc, ids, false)) ||
-        (rc = bind(enc, output, true)))
-        return rc;
+    if ((rc = op_begin(enc, {{input, false}, {weight, false}, {ids, false}, {output, true}}))) return rc;
     QmvArgs a{};
     a.w = weight->dev();
     a.x = reinterpret_cast<const float *>(input->dev());
@@ -1072,10 +1186,7 @@ extern "C" int mlxn_quantized_matmul_id_ggml(mlxn_encoder *enc, mlxn_registry *r
     if ((rc = validate_id("quantized_matmul_id_ggml", input, weight, ids, output, params))) return rc;
     if ((rc = check_alignment(input, weight, output))) return rc;
     if (!id_routes_to_mm(params)) return dispatch_id_mv(enc, reg, dev, input, weight, ids, output, params);
-    if ((rc = encoder_begin_work(enc))) return rc;
-    if ((rc = bind(enc, input, false)) || (rc = bind(enc, weight, false)) || (rc = bind(enc, ids, false)) ||
-        (rc = bind(enc, output, true)))
-        return rc;
+    if ((rc = op_begin(enc, {{input, false}, {weight, false}, {ids, false}, {output, true}}))) return rc;
     // routing scratch comes out of the encoder's arena instead of two fresh allocations per call
     const size_t htpe_b = (mlxn_id_mm_htpe_bytes(params) + 1023) / 1024 * 1024;
     const size_t hids_b = (mlxn_id_mm_hids_bytes(params) + 1023) / 1024 * 1024;
@@ -1115,9 +1226,7 @@ extern "C" int mlxn_quantized_matmul_id_ggml_pooled(mlxn_encoder *enc, mlxn_regi
     if (params->n_tokens > n_tokens_cap)
         return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: IdMmScratch: n_tokens (%u) > cap (%u)", params->n_tokens, n_tokens_cap);
     if ((rc = check_scratch_buffers(htpe, hids, params))) return rc;
-    if ((rc = encoder_begin_work(enc))) return rc;
-    if ((rc = bind(enc, input, false)) || (rc = bind(enc, weight, false)) || (rc = bind(enc, ids, false)) ||
-        (rc = bind(enc, output, true)) || (rc = bind(enc, htpe, true)) || (rc = bind(enc, hids, true)))
+    if ((rc = op_begin(enc, {{input, false}, {weight, false}, {ids, false}, {output, true}, {htpe, true}, {hids, true}})))
         return rc;
     return dispatch_id_mm_stages(enc, reg, dev, input, weight, ids, output, reinterpret_cast<uint32_t *>(htpe->dev()),
                                  reinterpret_cast<int32_t *>(hids->dev()), params->n_tokens, 0, params);
@@ -1131,9 +1240,7 @@ extern "C" int mlxn_dispatch_id_mm_for_test(mlxn_encoder *enc, mlxn_registry *re
     if ((rc = validate_id("dispatch_id_mm_for_test", input, weight, ids, output, params))) return rc;
     if ((rc = check_alignment(input, weight, output))) return rc;
     if ((rc = check_scratch_buffers(htpe, hids, params))) return rc;
-    if ((rc = encoder_begin_work(enc))) return rc;
-    if ((rc = bind(enc, input, false)) || (rc = bind(enc, weight, false)) || (rc = bind(enc, ids, false)) ||
-        (rc = bind(enc, output, true)) || (rc = bind(enc, htpe, true)) || (rc = bind(enc, hids, true)))
+    if ((rc = op_begin(enc, {{input, false}, {weight, false}, {ids, false}, {output, true}, {htpe, true}, {hids, true}})))
         return rc;
     return dispatch_id_mm_stages(enc, reg, dev, input, weight, ids, output, reinterpret_cast<uint32_t *>(htpe->dev()),
                                  reinterpret_cast<int32_t *>(hids->dev()), params->n_tokens, 0, params);
@@ -1155,8 +1262,7 @@ extern "C" int mlxn_moe_softmax_topk(mlxn_encoder *enc, mlxn_registry *reg, mlxn
         out_weights->len < (size_t)n_tokens * top_k * 4)
         return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_softmax_topk: a buffer is too small");
     if ((rc = touch_kernel(reg, dev, "moe_softmax_topk_f32"))) return rc;
-    if ((rc = encoder_begin_work(enc))) return rc;
-    if ((rc = bind(enc, logits, false)) || (rc = bind(enc, out_ids, true)) || (rc = bind(enc, out_weights, true))) return rc;
+    if ((rc = op_begin(enc, {{logits, false}, {out_ids, true}, {out_weights, true}}))) return rc;
     CUDA_TRY(launch_moe_softmax_topk(reinterpret_cast<const float *>(logits->dev()), n_tokens, n_experts, top_k,
                                      reinterpret_cast<uint32_t *>(out_ids->dev()), reinterpret_cast<float *>(out_weights->dev()),
                                      enc->stream),
@@ -1175,8 +1281,7 @@ extern "C" int mlxn_silu_mul(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device 
     if (gate->len < (size_t)n * 4 || up->len < (size_t)n * 4 || out->len < (size_t)n * 4)
         return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: silu_mul: a buffer is too small for %u f32 elements", n);
     if ((rc = touch_kernel(reg, dev, "silu_mul_f32"))) return rc;
-    if ((rc = encoder_begin_work(enc))) return rc;
-    if ((rc = bind(enc, gate, false)) || (rc = bind(enc, up, false)) || (rc = bind(enc, out, true))) return rc;
+    if ((rc = op_begin(enc, {{gate, false}, {up, false}, {out, true}}))) return rc;
     CUDA_TRY(launch_silu_mul(reinterpret_cast<const float *>(gate->dev()), reinterpret_cast<const float *>(up->dev()),
                              reinterpret_cast<float *>(out->dev()), n, enc->stream),
              "silu_mul launch");
@@ -1198,11 +1303,9 @@ extern "C" int mlxn_moe_weighted_reduce(mlxn_encoder *enc, mlxn_registry *reg, m
         (sh_logit && sh_logit->len < (size_t)n_tokens * 4) || (residual && residual->len < (size_t)n_tokens * h * 4))
         return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_weighted_reduce: a buffer is too small");
     if ((rc = touch_kernel(reg, dev, "moe_weighted_reduce_f32"))) return rc;
-    if ((rc = encoder_begin_work(enc))) return rc;
-    if ((rc = bind(enc, expert_w, false)) || (rc = bind(enc, y_expert, false)) || (rc = bind(enc, out, true))) return rc;
-    if (sh_logit && (rc = bind(enc, sh_logit, false))) return rc;
-    if (y_shared && (rc = bind(enc, y_shared, false))) return rc;
-    if (residual && (rc = bind(enc, residual, false))) return rc;
+    if ((rc = op_begin(enc, {{expert_w, false}, {y_expert, false}, {out, true}, {sh_logit, false}, {y_shared, false},
+                             {residual, false}})))
+        return rc;
     CUDA_TRY(launch_moe_weighted_reduce(reinterpret_cast<const float *>(expert_w->dev()),
                                         reinterpret_cast<const float *>(y_expert->dev()),
                                         sh_logit ? reinterpret_cast<const float *>(sh_logit->dev()) : nullptr,
