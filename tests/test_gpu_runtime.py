@@ -4,7 +4,7 @@ import pytest
 
 import mlx_native_b200 as mx
 from oracle import oracle as orc
-from tests.gpu_util import TYPES, Ctx, normal_acts, normal_weights
+from tests.gpu_util import MV_TOL, TYPES, Ctx, norm_err, normal_acts, normal_weights
 
 pytestmark = pytest.mark.gpu
 
@@ -145,3 +145,52 @@ def test_wrap_external_device_memory(ctx):
     enc.commit_and_wait()
     y_ref, _ = orc.qmatmul(otype, wq, x, n, k)
     assert np.allclose(ty.cpu().numpy(), y_ref[0], rtol=1e-4, atol=1e-5)
+
+
+# ---- concurrent groups: operations without buffer conflicts may overlap (the reference dispatches concurrently
+# ---- and orders dependent dispatches with memory barriers, src/encoder.rs:837-853, src/graph.rs:1494-1530)
+@pytest.mark.parametrize("qmv", ["auto", "stream"])
+@pytest.mark.parametrize("captured", [False, True])
+def test_dependent_chain_and_independent_ops_in_one_encoder(ctx, qmv, captured):
+    mx.set_option("qmv", qmv)
+    d = ctx.device
+    gtype, otype = TYPES["Q8_0"]
+    m, k, n1, n2 = 4, 1024, 2048, 512
+    w1, w2, w3 = normal_weights(21, n1, k, otype), normal_weights(22, n2, n1, otype), normal_weights(23, n2, k, otype)
+    x = normal_acts(21, m, k)
+    xb, w1b, w2b, w3b = (ctx.buf(x, mx.DType.F32), ctx.buf(w1, mx.DType.U8), ctx.buf(w2, mx.DType.U8),
+                         ctx.buf(w3, mx.DType.U8))
+    y1 = d.alloc_buffer(m * n1 * 4, mx.DType.F32)
+    y2 = d.alloc_buffer(m * n2 * 4, mx.DType.F32)
+    y3 = d.alloc_buffer(m * n2 * 4, mx.DType.F32)
+    p1 = mx.GgmlQuantizedMatmulParams(m, n1, k, gtype)
+    p2 = mx.GgmlQuantizedMatmulParams(m, n2, n1, gtype)
+    p3 = mx.GgmlQuantizedMatmulParams(m, n2, k, gtype)
+    enc = d.command_encoder()
+
+    def encode():
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, w1b, y1, p1)   # y1 = x W1^T
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, w3b, y3, p3)   # independent of the first: other lane
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, y1, w2b, y2, p2)   # reads y1: ordered after the first
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, w3b, y3, p3)   # writes y3 again: ordered after the second
+
+    if captured:
+        encode()
+        enc.commit_and_wait()
+        enc.begin_capture()
+        encode()
+        g = enc.end_capture()
+        for _ in range(3):
+            g.launch(enc)
+        enc.commit_and_wait()
+    else:
+        for _ in range(3):
+            encode()
+        enc.commit_and_wait()
+    r1, ad1 = orc.qmatmul(otype, w1, x, n1, k, nthreads=8)
+    got1 = y1.as_slice(np.float32).reshape(m, n1)
+    assert norm_err(got1, r1, ad1) <= MV_TOL
+    r2, ad2 = orc.qmatmul(otype, w2, got1.copy(), n2, n1, nthreads=8)
+    assert norm_err(y2.as_slice(np.float32).reshape(m, n2), r2, ad2) <= MV_TOL
+    r3, ad3 = orc.qmatmul(otype, w3, x, n2, k, nthreads=8)
+    assert norm_err(y3.as_slice(np.float32).reshape(m, n2), r3, ad3) <= MV_TOL
