@@ -3,6 +3,8 @@
   python -m mlx_native_b200.profile_case mv  [Q8_0|Q6_K|Q4_0] [m]   decode mat-vec, n=12288 k=4096, 4 weight copies (> L2)
   python -m mlx_native_b200.profile_case mm  [Q4_0|Q6_K|Q8_0] [m]   prefill mat-mat, n=4096 k=4096, m=512 by default
   python -m mlx_native_b200.profile_case moe [m]                    expert-routed gate projection, 128 experts, top-8
+  python -m mlx_native_b200.profile_case cmp [types]                 tensor-core vs streaming mat-vec, microseconds per call
+                                                                     (CUDA-graph replay over rotating weight copies > L2)
 
 Weights are random bytes with finite f16 scales: the kernels' timing and memory traffic do not depend on the values.
 """
@@ -24,11 +26,59 @@ def random_blocks(rng, t: str, n: int, k: int) -> np.ndarray:
     return raw.reshape(-1)
 
 
+def compare_matvec_kernels(dev, reg, rng, types):
+    """Event-timed microseconds per mat-vec for both kernels, every decode shape and m in {1, 2, 4, 8}; each call
+    of a replayed graph has its own weight copy (more than L2 in total) and its own output buffer."""
+    shapes = [(4096, 4096), (1024, 4096), (12288, 4096), (4096, 12288)]
+
+    def timed(t, n, k, m, variant, reps=10):
+        _, qk, bb, _ = BLOCK[t]
+        wbytes = n * (k // qk) * bb
+        ncopies = int(max(4, min(48, (300e6 // wbytes) + 1)))
+        w = random_blocks(rng, t, n, k)
+        ws = []
+        for _ in range(ncopies):
+            b = dev.alloc_buffer(wbytes, mx.DType.U8)
+            b.upload(w)
+            ws.append(b)
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        xb = dev.alloc_buffer(x.nbytes, mx.DType.F32)
+        xb.upload(x)
+        ys = [dev.alloc_buffer(m * n * 4, mx.DType.F32) for _ in range(ncopies)]
+        p = mx.GgmlQuantizedMatmulParams(m, n, k, BLOCK[t][0])
+        mx.set_option("qmv", variant)
+        enc = dev.command_encoder()
+        for wb, yb in zip(ws[:2], ys[:2]):
+            mx.quantized_matmul_ggml(enc, reg, dev, xb, wb, yb, p)
+        enc.commit_and_wait()
+        enc.begin_capture()
+        for wb, yb in zip(ws, ys):
+            mx.quantized_matmul_ggml(enc, reg, dev, xb, wb, yb, p)
+        g = enc.end_capture()
+        for _ in range(2):
+            g.launch(enc)
+        enc.commit_and_wait()
+        for _ in range(reps):
+            g.launch(enc)
+        return enc.commit_wait_with_gpu_time() / (reps * ncopies) * 1e6
+
+    for t in types:
+        for (n, k) in shapes:
+            cells = []
+            for m in (1, 2, 4, 8):
+                cells.append(f"m={m}: tc {timed(t, n, k, m, 'tc'):6.2f} st {timed(t, n, k, m, 'stream'):6.2f}")
+            print(f"{t} {n:6d}x{k:<6d} " + " | ".join(cells), flush=True)
+    mx.set_option("qmv", "auto")
+
+
 def main(argv):
     mode = argv[0] if argv else "mv"
     dev = mx.MlxDevice.new(0)
     reg = mx.KernelRegistry.new()
     rng = np.random.default_rng(0)
+    if mode == "cmp":
+        compare_matvec_kernels(dev, reg, rng, (argv[1] if len(argv) > 1 else "Q8_0,Q6_K,Q4_0").split(","))
+        return
     enc = dev.command_encoder()
     if mode == "moe":
         m = int(argv[1]) if len(argv) > 1 else 512
