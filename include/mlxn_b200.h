@@ -251,6 +251,17 @@ size_t mlxn_noalloc_scratch_limit(void);
 int mlxn_quantized_matmul_ggml_mm_noalloc(void *cuda_stream, const void *input_dev, const void *weight_dev,
                                           void *output_dev, const mlxn_qmm_params *params);
 
+/* Row-sharded mat-vec for tensor parallelism (m <= 8; no upstream counterpart: upstream is single-GPU).  This
+ * rank holds params->n of the n_total weight rows, rows [col0, col0 + n) of the full matrix.  `output` is this
+ * rank's full result buffer, f32 [m, n_total]; the kernel stores its columns there AND at the same place in the
+ * other ranks' result buffers (`peer_outputs`: device addresses mapped into this process, e.g. CUDA IPC or
+ * symmetric memory; at most 7), so that every rank holds the whole result once all ranks' kernels have finished,
+ * without a collective launch.  The caller orders ranks (a barrier between this call and the first use of the
+ * full result, and between that use and the next call that writes the buffers). */
+int mlxn_quantized_matmul_ggml_sharded(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
+                                       mlxn_buffer *weight, mlxn_buffer *output, const mlxn_qmm_params *params,
+                                       uint32_t n_total, uint32_t col0, void *const *peer_outputs, uint32_t n_peers);
+
 /* ---- tuning and introspection (no upstream counterpart) -------------------------------------- */
 /* Selects kernel variants for experiments: key/value pairs "qmv=auto|tc|stream|simple" (auto: the tensor-core
  * mat-vec from three activation rows up, the streaming SIMT kernel below; tc forces the tensor-core kernel

@@ -89,6 +89,8 @@ SIGNATURES = {
     "mlxn_reset_counters": (None, []),
     "mlxn_kernel_launch_count": (u64, []),
     "mlxn_quantized_matmul_ggml": (i32, [vp, vp, vp, vp, vp, vp, C.POINTER(QmmParams)]),
+    "mlxn_quantized_matmul_ggml_sharded": (i32, [vp, vp, vp, vp, vp, vp, C.POINTER(QmmParams), C.c_uint32, C.c_uint32,
+                                                 C.POINTER(C.c_void_p), C.c_uint32]),
     "mlxn_dispatch_mm_for_test": (i32, [vp, vp, vp, vp, vp, vp, C.POINTER(QmmParams)]),
     "mlxn_quantized_matmul_id_ggml": (i32, [vp, vp, vp, vp, vp, vp, vp, C.POINTER(QmmIdParams)]),
     "mlxn_quantized_matmul_id_ggml_pooled": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32,

@@ -471,6 +471,21 @@ def quantized_matmul_ggml(encoder: CommandEncoder, registry: KernelRegistry | No
                                                     _h(output), C.byref(params._c())))
 
 
+def quantized_matmul_ggml_sharded(encoder: CommandEncoder, registry: KernelRegistry | None, device: MlxDevice,
+                                  input: MlxBuffer, weight: MlxBuffer, output: MlxBuffer,
+                                  params: GgmlQuantizedMatmulParams, n_total: int, col0: int,
+                                  peer_outputs: list[int] | tuple[int, ...] = ()) -> None:
+    """Row-sharded mat-vec (m <= 8) for tensor parallelism; no counterpart upstream (single GPU).  `weight` holds
+    params.n of the n_total rows (rows col0 .. col0 + n of the full matrix); `output` is this rank's full
+    [m, n_total] result buffer.  The kernel stores its columns there and at the same place in every buffer of
+    `peer_outputs` (device addresses of the other ranks' result buffers mapped into this process), so all ranks
+    hold the whole result once every rank's kernel has finished; ordering between ranks is the caller's."""
+    arr = (C.c_void_p * max(1, len(peer_outputs)))(*[C.c_void_p(p) for p in peer_outputs])
+    _check(_native.lib().mlxn_quantized_matmul_ggml_sharded(encoder._h, _h(registry), device._h, _h(input), _h(weight),
+                                                            _h(output), C.byref(params._c()), n_total, col0, arr,
+                                                            len(peer_outputs)))
+
+
 def dispatch_mm_for_test(encoder, registry, device, input, weight, output, params) -> None:
     """src/ops/quantized_matmul_ggml.rs:371-402."""
     _check(_native.lib().mlxn_dispatch_mm_for_test(encoder._h, _h(registry), device._h, _h(input), _h(weight),

@@ -55,7 +55,16 @@ struct QmvArgs {
     uint32_t *status;       // device status word
     uint32_t early_weights; // 1: no kernel of this process wrote the weights, so they may be fetched before the
                             // kernels ahead in the stream have finished (see launch_overlapped)
+    // Row-sharded form (dense only): this rank holds n of the n_total weight rows; output row t lives at
+    // y[t * y_ld + y_col0 ..] and every result is also stored to the same place in the other ranks' output
+    // buffers (peer memory), so that each rank ends up with the whole [m, n_total] result without a collective.
+    uint32_t y_ld;          // elements between output rows (0: n)
+    uint32_t y_col0;        // first output column of this rank
+    uint32_t n_peer;        // other ranks' buffers in y_peer
+    float *y_peer[7];
 };
+constexpr int kMaxPeers = 7;
+__host__ __device__ inline uint32_t qmv_ld(const QmvArgs &a) { return a.y_ld ? a.y_ld : a.n; }
 
 // Arguments of the mat-mat kernels (dense and grouped-by-expert).
 struct QmmArgs {

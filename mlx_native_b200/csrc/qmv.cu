@@ -134,7 +134,11 @@ __global__ void __launch_bounds__(256) qmv_simple_kernel(const QmvArgs a) {
 #pragma unroll
     for (int t = 0; t < M; t++) {
         const float s = warp_sum(acc[t]);
-        if (lane == 0) y[(size_t)t * a.n + row] = s;
+        if (lane == 0) {
+            const size_t off = a.ids ? (size_t)t * a.n + row : (size_t)t * qmv_ld(a) + a.y_col0 + row;
+            y[off] = s;
+            for (uint32_t pr = 0; pr < a.n_peer; pr++) a.y_peer[pr][off] = s;
+        }
     }
 }
 
@@ -654,9 +658,10 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
                         float s = 0.0f;
                         for (uint32_t w8 = 0; w8 < c.wpg; w8++)
                             s += *reinterpret_cast<volatile float *>(&red[(slot * kConsumerWarps + w8) * V + lane]);
-                        float *yp = a.y + (a.ids ? (size_t)w.p * a.n : (size_t)t * a.n) + row0 + r;
-                        if (w.s == 0) *yp = s;
-                        else *yp += s;
+                        const size_t off = (a.ids ? (size_t)w.p * a.n : (size_t)t * qmv_ld(a) + a.y_col0) + row0 + r;
+                        if (w.s != 0) s += a.y[off];   // later K slices add to what the earlier ones left (same thread)
+                        a.y[off] = s;
+                        for (uint32_t pr = 0; pr < a.n_peer; pr++) a.y_peer[pr][off] = s;
                     }
                 }
                 __syncwarp();

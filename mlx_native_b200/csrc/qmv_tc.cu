@@ -158,16 +158,24 @@ __device__ __forceinline__ void vt_pack_half(const float *xr, uint32_t ku, uint3
 // grid = (K units, ceil(2 m / 4)), 128 threads (small enough to share an SM with a mat-vec CTA of the operation
 // ahead): each warp packs one (activation row, half) of the CTA's unit; all threads zero a slice of y (tiles
 // split between CTAs of the mat-vec kernel are summed into it with atomic adds).
-__global__ void __launch_bounds__(128) qmv_tc_pack_kernel(const float *x, float *y, uint32_t m, uint32_t n, uint32_t k,
-                                                          int ggml_type, VtScratch s, uint32_t debug) {
+__global__ void __launch_bounds__(128) qmv_tc_pack_kernel(const QmvArgs a, int ggml_type, VtScratch s, uint32_t debug) {
+    const float *x = a.x;
+    const uint32_t m = a.m, n = a.n, k = a.k;
     grid_dependency_wait();  // x (and y, which is zeroed here) belong to the kernels ahead until they are done
     allow_dependents();      // the mat-vec kernel may set itself up and start its weight stream
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t ncta = gridDim.x * gridDim.y, cta = blockIdx.y * gridDim.x + blockIdx.x;
     const uint32_t total = m * n, per = (total + ncta - 1) / ncta;
     const uint32_t lo = min(total, cta * per), hi = min(total, lo + per);
-    if (!(debug & 256u))
-        for (uint32_t i = lo + tid; i < hi; i += blockDim.x) y[i] = 0.f;
+    if (!(debug & 256u)) {
+        const uint32_t ld = qmv_ld(a);
+        for (uint32_t i = lo + tid; i < hi; i += blockDim.x) {
+            const uint32_t t = i / n, col = i - t * n;
+            const size_t off = (size_t)t * ld + a.y_col0 + col;
+            a.y[off] = 0.f;
+            for (uint32_t pr = 0; pr < a.n_peer; pr++) a.y_peer[pr][off] = 0.f;
+        }
+    }
     const uint32_t task = blockIdx.y * 4 + warp;
     if (task < 2 * m) vt_pack_half(x + (size_t)(task >> 1) * k, blockIdx.x, task >> 1, task & 1u, lane, ggml_type, s);
 }
@@ -552,16 +560,24 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                     for (int i = 0; i < 2 * MP; i++) tot[i] += red[(gg * 2 * MP + i) * kVtRows + row];
                 const uint32_t grow = pv_tile * kVtRows + row;
                 const bool full = pv_ka == 0 && pv_kb == c.upt;
+                const size_t ycol = (size_t)a.y_col0 + grow;
+                const uint32_t ld = qmv_ld(a);
                 if (full) {
                     if (grow < a.n && !(c.debug & 256u))
 #pragma unroll
                         for (int i = 0; i < 2 * MP; i++)
-                            if ((uint32_t)i < a.m) a.y[(size_t)i * a.n + grow] = tot[i];
+                            if ((uint32_t)i < a.m) {
+                                a.y[(size_t)i * ld + ycol] = tot[i];
+                                for (uint32_t pr = 0; pr < a.n_peer; pr++) a.y_peer[pr][(size_t)i * ld + ycol] = tot[i];
+                            }
                 } else if (grow < a.n && !(c.debug & 256u)) {
                     // the tile's K range is shared with other CTAs: add into the rows the packing kernel zeroed
 #pragma unroll
                     for (int i = 0; i < 2 * MP; i++)
-                        if ((uint32_t)i < a.m) atomicAdd(&a.y[(size_t)i * a.n + grow], tot[i]);
+                        if ((uint32_t)i < a.m) {
+                            atomicAdd(&a.y[(size_t)i * ld + ycol], tot[i]);
+                            for (uint32_t pr = 0; pr < a.n_peer; pr++) atomicAdd(&a.y_peer[pr][(size_t)i * ld + ycol], tot[i]);
+                        }
                 }
             }
             if (!sync_bounded(&fin_all[1], fin_ph)) { ok = false; return; }
@@ -761,7 +777,7 @@ static cudaError_t launch_vt_t(const QmvArgs &a, uint8_t *scratch, uint32_t *fla
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
-    cudaError_t e = launch_overlapped(qmv_tc_pack_kernel, dim3(c.upt, (2 * a.m + 3) / 4), dim3(128), 0, st, a.x, a.y, a.m, a.n, a.k, (int)T, sc, c.debug);
+    cudaError_t e = launch_overlapped(qmv_tc_pack_kernel, dim3(c.upt, (2 * a.m + 3) / 4), dim3(128), 0, st, a, (int)T, sc, c.debug);
     (*launches)++;
     if (e != cudaSuccess) return e;
     (*launches)++;

@@ -926,8 +926,12 @@ static int check_handles(mlxn_encoder *enc, mlxn_device *dev, std::initializer_l
     return MLXN_OK;
 }
 
+struct ShardOut {            // row-sharded output: see QmvArgs
+    uint32_t y_ld = 0, y_col0 = 0, n_peer = 0;
+    float *peer[kMaxPeers] = {};
+};
 static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input, mlxn_buffer *weight,
-                       mlxn_buffer *output, const mlxn_qmm_params *p) {
+                       mlxn_buffer *output, const mlxn_qmm_params *p, const ShardOut *sh = nullptr) {
     int rc = touch_kernel(reg, dev, mv_kernel_name((int)p->ggml_type));
     if (rc) return rc;
     if ((rc = op_begin(enc, {{input, false}, {weight, false}, {output, true}}))) return rc;
@@ -937,7 +941,13 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
         QmvArgs a{};
         a.w = weight->dev();
         a.x = reinterpret_cast<const float *>(input->dev()) + (size_t)m0 * p->k;
-        a.y = reinterpret_cast<float *>(output->dev()) + (size_t)m0 * p->n;
+        a.y = reinterpret_cast<float *>(output->dev()) + (size_t)m0 * (sh ? sh->y_ld : p->n);
+        if (sh) {
+            a.y_ld = sh->y_ld;
+            a.y_col0 = sh->y_col0;
+            a.n_peer = sh->n_peer;
+            for (uint32_t i = 0; i < sh->n_peer; i++) a.y_peer[i] = sh->peer[i] + (size_t)m0 * sh->y_ld;
+        }
         a.ids = nullptr;
         a.n = p->n;
         a.k = p->k;
@@ -1047,6 +1057,39 @@ extern "C" int mlxn_quantized_matmul_ggml(mlxn_encoder *enc, mlxn_registry *reg,
     if (params->m > MLXN_MM_ROUTING_THRESHOLD && params->k >= 32)
         return dispatch_mm(enc, reg, dev, input, weight, output, params);
     return dispatch_mv(enc, reg, dev, input, weight, output, params);
+}
+
+extern "C" int mlxn_quantized_matmul_ggml_sharded(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
+                                                  mlxn_buffer *weight, mlxn_buffer *output, const mlxn_qmm_params *params,
+                                                  uint32_t n_total, uint32_t col0, void *const *peer_outputs, uint32_t n_peers) {
+    int rc = check_handles(enc, dev, {input, weight, output, params});
+    if (rc) return rc;
+    if (params->m == 0 || params->m > MLXN_MM_ROUTING_THRESHOLD)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_sharded: m (%u) must be in 1..%u", params->m,
+                    (unsigned)MLXN_MM_ROUTING_THRESHOLD);
+    if (n_peers > (uint32_t)kMaxPeers || (n_peers && !peer_outputs))
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_sharded: at most %d peer outputs", kMaxPeers);
+    if ((uint64_t)col0 + params->n > n_total)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_sharded: columns [%u, %u) exceed n_total (%u)", col0,
+                    col0 + params->n, n_total);
+    // the local problem is validated as usual, against a [m, n] view; the output buffer must hold [m, n_total]
+    if ((rc = validate_dense("quantized_matmul_ggml_sharded", input, weight, output, params, true))) return rc;
+    if (output->len < (size_t)params->m * n_total * 4)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_sharded: output buffer too small: expected %zu bytes for [%u x %u] f32, got %zu",
+                    (size_t)params->m * n_total * 4, params->m, n_total, output->len);
+    if ((int)params->ggml_type == GT_Q4_K)
+        return fail(MLXN_KERNEL_NOT_FOUND, "Kernel not found: kernel_mul_mv_q4_K_f32 (Q4_K is not built into this library yet)");
+    if ((rc = check_alignment(input, weight, output))) return rc;
+    ShardOut sh;
+    sh.y_ld = n_total;
+    sh.y_col0 = col0;
+    sh.n_peer = n_peers;
+    for (uint32_t i = 0; i < n_peers; i++) {
+        if (!peer_outputs[i] || ((uintptr_t)peer_outputs[i] & 3u))
+            return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_sharded: peer output %u is null or misaligned", i);
+        sh.peer[i] = static_cast<float *>(peer_outputs[i]);
+    }
+    return dispatch_mv(enc, reg, dev, input, weight, output, params, &sh);
 }
 
 extern "C" int mlxn_dispatch_mm_for_test(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
