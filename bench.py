@@ -12,8 +12,10 @@ written on the host, uploaded, results read back), `roofline` (mat-vec kernel vs
 mat-mat TFLOP/s and the MoE expert-routed tokens/s.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-For N > 1 launch with torch.distributed.run; weights are sharded along N (rows) and every mat-vec output is
-all-gathered over NCCL ("strong" scaling: the total work is fixed).
+For N > 1 launch with torch.distributed.run; weights are sharded along N (rows) and every rank's mat-vec kernels
+store their columns of the result straight into all ranks' result buffers (peer memory over NVLink, allocated as
+torch symmetric memory), with one cross-rank barrier per step ("strong" scaling: the total work is fixed).  If
+symmetric memory cannot be set up, every mat-vec output is all-gathered over NCCL instead.
 """
 from __future__ import annotations
 
@@ -176,6 +178,23 @@ def run_ours(args, rank, world, local_rank):
     weights = make_weights(TYPE_NAMES, SHAPES, seed=0)
     rng = np.random.default_rng(1)
 
+    # ---- N > 1: every rank's full-width result buffers live in symmetric memory, so that the other ranks' kernels
+    # ---- can store into them (peer stores over NVLink)
+    symm = None
+    if world > 1 and os.environ.get("MLXN_BENCH_NCCL_GATHER", "0") != "1":
+        try:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings only
+            import torch.distributed._symmetric_memory as symm_mem
+            total = sum(m * n for (n, k) in SHAPES for m in MS) * len(TYPE_NAMES)
+            symm_buf = symm_mem.empty(total, dtype=torch.float32, device=f"cuda:{local_rank}")
+            symm_hdl = symm_mem.rendezvous(symm_buf, dist.group.WORLD)
+            symm_buf.zero_()
+            symm = dict(buf=symm_buf, hdl=symm_hdl, ptrs=[int(p) for p in symm_hdl.buffer_ptrs], off=0)
+        except Exception as ex:  # fall back to NCCL all-gathers
+            if rank == 0:
+                print(f"# symmetric memory unavailable ({ex!r}); using NCCL all-gather per mat-vec", file=sys.stderr)
+            symm = None
+
     # ---- resident data: one weight buffer per launch (sharded by rows across ranks), activations, outputs
     launches = []
     for t in TYPE_NAMES:
@@ -189,16 +208,25 @@ def run_ours(args, rank, world, local_rank):
                 x = rng.standard_normal((m, k)).astype(np.float32)
                 xbuf = dev.alloc_buffer(x.nbytes, mx.DType.F32, [m, k])
                 xbuf.upload(x)
-                if world > 1:
+                y_loc = y_all = None
+                peers = None
+                if symm is not None:
+                    off = symm["off"]
+                    symm["off"] += m * n
+                    ybuf = dev.wrap_device_memory(symm["ptrs"][rank] + off * 4, m * n * 4, mx.DType.F32, [m, n])
+                    peers = [symm["ptrs"][r] + off * 4 for r in range(world) if r != rank]
+                    y_full = symm["buf"][off:off + m * n].view(m, n)
+                elif world > 1:
                     y_loc = torch.empty((m, n_loc), dtype=torch.float32, device="cuda")
                     y_all = torch.empty((world * m, n_loc), dtype=torch.float32, device="cuda")
                     ybuf = dev.wrap_device_memory(y_loc.data_ptr(), m * n_loc * 4, mx.DType.F32, [m, n_loc])
+                    y_full = None
                 else:
-                    y_loc = y_all = None
                     ybuf = dev.alloc_buffer(m * n_loc * 4, mx.DType.F32, [m, n_loc])
+                    y_full = None
                 launches.append(dict(t=t, n=n, k=k, m=m, n_loc=n_loc, w=wbuf, x=xbuf, y=ybuf, y_loc=y_loc, y_all=y_all,
-                                     x_host=x, params=mx.GgmlQuantizedMatmulParams(m, n_loc, k, gt[t])))
-    del weights
+                                     peers=peers, y_full=y_full, x_host=x,
+                                     params=mx.GgmlQuantizedMatmulParams(m, n_loc, k, gt[t])))
     step_weight_bytes = sum(weight_bytes(L["t"], L["n"], L["k"]) for L in launches)           # whole job
     step_algo_bytes = sum(weight_bytes(L["t"], L["n_loc"], L["k"]) + L["m"] * L["k"] * 4 + L["m"] * L["n_loc"] * 4
                           for L in launches)                                                 # this rank's kernels
@@ -206,26 +234,40 @@ def run_ours(args, rank, world, local_rank):
     enc = dev.command_encoder()
     ext_stream = torch.cuda.ExternalStream(enc.stream())
 
+    def encode_op(e, L):
+        if L["peers"] is not None:
+            mx.quantized_matmul_ggml_sharded(e, reg, dev, L["x"], L["w"], L["y"], L["params"], L["n"], rank * L["n_loc"],
+                                             L["peers"])
+        else:
+            mx.quantized_matmul_ggml(e, reg, dev, L["x"], L["w"], L["y"], L["params"])
+
     def encode_step():
         for L in launches:
-            mx.quantized_matmul_ggml(enc, reg, dev, L["x"], L["w"], L["y"], L["params"])
-            if world > 1:
+            encode_op(enc, L)
+            if world > 1 and symm is None:
                 with torch.cuda.stream(ext_stream):
                     dist.all_gather_into_tensor(L["y_all"], L["y_loc"])
 
     graph = None
-    if world == 1:
+    if world == 1 or symm is not None:
         encode_step()                      # first touch outside the capture
         enc.commit_and_wait()
         enc.begin_capture()
         encode_step()
         graph = enc.end_capture()
 
+    def rank_barrier_on_stream(stream):
+        """All ranks' kernels of the step have finished (their peer stores have landed) before anyone goes on."""
+        with torch.cuda.stream(stream):
+            symm["hdl"].barrier()
+
     def run_step():
         if graph is not None:
             graph.launch(enc)
         else:
             encode_step()
+        if symm is not None:
+            rank_barrier_on_stream(ext_stream)
 
     def barrier():
         if dist is not None:
@@ -236,7 +278,32 @@ def run_ours(args, rank, world, local_rank):
         run_step()
     enc.commit_and_wait()
     barrier()
+    if symm is not None:
+        # every rank must hold the same full results: compare with rank 0's copy (tensor-core mat-vecs add split
+        # tiles with atomics, so the copies may differ in the last bits, nothing more)
+        mine = symm["buf"].clone()
+        ref = mine.clone()
+        dist.broadcast(ref, src=0)
+        scale = float(ref.abs().max().item())
+        worst = float((mine - ref).abs().max().item())
+        if not (scale > 0 and worst <= 1e-4 * scale):
+            raise RuntimeError(f"rank {rank}: assembled results differ from rank 0's: max diff {worst}, scale {scale}")
+        # and the columns other ranks stored must be what this rank computes for them: spot-check one launch against
+        # an unsharded run of the same mat-vec on this GPU
+        L = launches[len(launches) // 2]
+        wfull = dev.alloc_buffer(weights[(L["t"], L["n"], L["k"])].size, mx.DType.U8)
+        wfull.upload(weights[(L["t"], L["n"], L["k"])])
+        ychk = dev.alloc_buffer(L["m"] * L["n"] * 4, mx.DType.F32, [L["m"], L["n"]])
+        e2 = dev.command_encoder()
+        mx.quantized_matmul_ggml(e2, reg, dev, L["x"], wfull, ychk, mx.GgmlQuantizedMatmulParams(L["m"], L["n"], L["k"], gt[L["t"]]))
+        e2.commit_and_wait()
+        want = torch.from_numpy(ychk.as_slice(np.float32).reshape(L["m"], L["n"]).copy()).cuda()
+        diff = float((L["y_full"] - want).abs().max().item())
+        if not diff <= 1e-4 * float(want.abs().max().item()):
+            raise RuntimeError(f"rank {rank}: sharded result differs from the unsharded mat-vec: {diff}")
+        del wfull, ychk
 
+    del weights
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -267,17 +334,24 @@ def run_ours(args, rank, world, local_rank):
 
     def e2e_step():
         e = dev.command_encoder()
+        e_stream = torch.cuda.ExternalStream(e.stream())
         for L in launches:
             L["x"].as_mut_slice(np.float32)[:] = L["x_host"].reshape(-1)      # host write -> upload at bind
-            mx.quantized_matmul_ggml(e, reg, dev, L["x"], L["w"], L["y"], L["params"])
-            if world > 1:
-                with torch.cuda.stream(torch.cuda.ExternalStream(e.stream())):
+            encode_op(e, L)
+            if world > 1 and symm is None:
+                with torch.cuda.stream(e_stream):
                     dist.all_gather_into_tensor(L["y_all"], L["y_loc"])
-        e.commit_and_wait()
+        e.commit()
+        if symm is not None:
+            rank_barrier_on_stream(e_stream)
+        e.wait_until_completed()
+        torch.cuda.synchronize()
         acc = 0.0
         for L in launches:
-            if world > 1:
-                acc += float(L["y_all"][0, 0].item())                      # device -> host read of the result
+            if symm is not None:
+                acc += float(L["y_full"][0, 0].item())                     # device -> host read of the result
+            elif world > 1:
+                acc += float(L["y_all"][0, 0].item())
             else:
                 acc += float(L["y"].as_slice(np.float32)[0])
         return acc
@@ -313,8 +387,11 @@ def run_ours(args, rank, world, local_rank):
         "config": {"workload": "decode mat-vec sweep: Qwen3-8B projections (4096->4096, 4096->1024, 4096->12288, "
                                "12288->4096) x {Q8_0,Q6_K} x m in {1,2,4,8}; 32 mat-vecs per step",
                    "weight_bytes_per_step": step_weight_bytes, "l2": "each launch has its own weight buffer: 915 MB of "
-                   "distinct weights per step, larger than L2", "launch": "CUDA graph replay" if world == 1 else
-                   "direct launches + NCCL all-gather per mat-vec", "parallelism": f"n-shard x{world}"},
+                   "distinct weights per step, larger than L2", "launch": "CUDA graph replay" if graph is not None else
+                   "direct launches + NCCL all-gather per mat-vec",
+                   "exchange": "none" if world == 1 else ("peer stores from the mat-vec kernels into every rank's result "
+                   "buffer (symmetric memory) + one cross-rank barrier per step" if symm is not None else
+                   "NCCL all-gather per mat-vec"), "parallelism": f"n-shard x{world}"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                      "traffic": None, "peak_kind": f"{peak_kind} copy bandwidth", "kernel": "qmv_tc_kernel (3+ rows, 2 rows with k >= 8192) and qmv_stream_kernel (1-2 rows)",
                      "note": "achieved = (weight + activation + output bytes of the 32 launches) / event-timed step"},

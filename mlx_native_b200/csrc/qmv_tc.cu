@@ -786,14 +786,37 @@ static cudaError_t launch_vt_t(const QmvArgs &a, uint8_t *scratch, uint32_t *fla
     return launch_vt<T, 4>(a, c, sc, wmap, grid, smem, st);
 }
 
+// Row-sharded form: copies this rank's columns of the result into the other ranks' result buffers.  The mat-vec
+// kernel adds split tiles up with atomics, which are slow on peer memory; a plain copy of the finished columns is not.
+__global__ void __launch_bounds__(256) qmv_publish_kernel(const QmvArgs a) {
+    grid_dependency_wait();  // the mat-vec kernel ahead has finished
+    allow_dependents();
+    const uint32_t total = a.m * a.n, ld = qmv_ld(a);
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const uint32_t t = i / a.n, col = i - t * a.n;
+        const size_t off = (size_t)t * ld + a.y_col0 + col;
+        const float v = a.y[off];
+        for (uint32_t pr = 0; pr < a.n_peer; pr++) a.y_peer[pr][off] = v;
+    }
+}
+
 cudaError_t launch_qmv_tc(int ggml_type, const QmvArgs &a, uint8_t *scratch, uint32_t *flags, int sm_count, cudaStream_t st,
                           int *launches) {
+    QmvArgs loc = a;
+    loc.n_peer = 0;  // the mat-vec itself writes this rank's buffer only
+    cudaError_t e;
     switch (ggml_type) {
-    case GT_Q4_0: return launch_vt_t<GT_Q4_0>(a, scratch, flags, sm_count, st, launches);
-    case GT_Q8_0: return launch_vt_t<GT_Q8_0>(a, scratch, flags, sm_count, st, launches);
-    case GT_Q6_K: return launch_vt_t<GT_Q6_K>(a, scratch, flags, sm_count, st, launches);
+    case GT_Q4_0: e = launch_vt_t<GT_Q4_0>(loc, scratch, flags, sm_count, st, launches); break;
+    case GT_Q8_0: e = launch_vt_t<GT_Q8_0>(loc, scratch, flags, sm_count, st, launches); break;
+    case GT_Q6_K: e = launch_vt_t<GT_Q6_K>(loc, scratch, flags, sm_count, st, launches); break;
     default: return cudaErrorInvalidValue;
     }
+    if (e != cudaSuccess || a.n_peer == 0) return e;
+    const uint32_t total = a.m * a.n;
+    uint32_t blocks = (total + 255) / 256;
+    if (blocks > 64) blocks = 64;
+    (*launches)++;
+    return launch_overlapped(qmv_publish_kernel, dim3(blocks), dim3(256), 0, st, a);
 }
 
 }  // namespace mlxn

@@ -164,6 +164,37 @@ struct mlxn_graph {
     uint64_t dispatches = 0;
 };
 
+// Scratch arenas outlive their encoder: short-lived encoders (one per command buffer, as upstream uses them) would
+// otherwise pay a cudaMalloc / cudaFree pair, which synchronises the device, for every mat-vec they encode.
+struct ScratchBlock {
+    int ordinal;
+    void *ptr;
+    size_t bytes;
+};
+static std::mutex g_scratch_mu;
+static std::vector<ScratchBlock> g_scratch_free;
+static void *scratch_take(int ordinal, size_t want, size_t *got) {
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    int best = -1;
+    for (int i = 0; i < (int)g_scratch_free.size(); i++)
+        if (g_scratch_free[i].ordinal == ordinal && g_scratch_free[i].bytes >= want &&
+            (best < 0 || g_scratch_free[i].bytes < g_scratch_free[best].bytes))
+            best = i;
+    if (best < 0) return nullptr;
+    void *p = g_scratch_free[best].ptr;
+    *got = g_scratch_free[best].bytes;
+    g_scratch_free.erase(g_scratch_free.begin() + best);
+    return p;
+}
+static void scratch_give(int ordinal, void *p, size_t bytes) {  // the caller has made sure no kernel still uses p
+    std::lock_guard<std::mutex> lk(g_scratch_mu);
+    if (g_scratch_free.size() >= 16) {
+        cudaFree(p);
+        return;
+    }
+    g_scratch_free.push_back({ordinal, p, bytes});
+}
+
 constexpr size_t kStatusBlockBytes = 8192;
 // The reference encodes with MTLDispatchTypeConcurrent: dispatches may overlap on the GPU unless a
 // memory_barrier() separates them (src/encoder.rs:837-853), and its tracked-dispatch mode inserts the barrier
@@ -175,6 +206,7 @@ constexpr size_t kStatusBlockBytes = 8192;
 constexpr int kLanes = 2;
 struct mlxn_encoder {
     mlxn_device *dev = nullptr;
+    int ordinal = 0;  // of dev (kept by value: an idle pooled encoder may outlive the device handle)
     cudaStream_t lanes[kLanes] = {};
     cudaStream_t stream = nullptr;   // lane of the operation being encoded (lanes[cur_lane])
     int cur_lane = 0;
@@ -188,7 +220,7 @@ struct mlxn_encoder {
     std::vector<mlxn_buffer *> retained;
     uint8_t *scratch_lane[kLanes] = {};
     size_t scratch_lane_bytes[kLanes] = {};
-    std::vector<void *> retired;  // outgrown scratch buffers, freed after the next wait
+    std::vector<std::pair<void *, size_t>> retired;  // outgrown scratch arenas, handed back after the next wait
     uint32_t *status_dev = nullptr;
     uint32_t *status_host = nullptr;  // pinned
 };
@@ -579,11 +611,29 @@ static int touch_kernel(mlxn_registry *reg, mlxn_device *dev, const char *name) 
 // ------------------------------------------------------------------------------------------------
 // encoder
 // ------------------------------------------------------------------------------------------------
+// Idle encoders (streams, events, status block, scratch arenas) are kept and handed out again: upstream makes
+// one encoder per command buffer, and creating streams and pinned memory for each would cost more than a mat-vec.
+static std::mutex g_enc_pool_mu;
+static std::vector<mlxn_encoder *> g_enc_pool;
+
 extern "C" int mlxn_encoder_create(mlxn_device *dev, mlxn_encoder **out) {
     if (!dev || !out) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: device and out must not be null");
     cudaSetDevice(dev->ordinal);
+    {
+        std::lock_guard<std::mutex> lk(g_enc_pool_mu);
+        for (size_t i = 0; i < g_enc_pool.size(); i++) {
+            if (g_enc_pool[i]->ordinal != dev->ordinal) continue;
+            mlxn_encoder *e = g_enc_pool[i];
+            g_enc_pool.erase(g_enc_pool.begin() + i);
+            e->dev = dev;
+            g_cmd_buf.fetch_add(1);
+            *out = e;
+            return MLXN_OK;
+        }
+    }
     auto *e = new mlxn_encoder();
     e->dev = dev;
+    e->ordinal = dev->ordinal;
     cudaError_t err = cudaSuccess;
     for (int l = 0; l < kLanes && err == cudaSuccess; l++) {
         err = cudaStreamCreateWithFlags(&e->lanes[l], cudaStreamNonBlocking);
@@ -627,17 +677,41 @@ static void encoder_release_retained(mlxn_encoder *e) {
         mlxn_buffer_release(b);
     }
     e->retained.clear();
-    for (void *p : e->retired) cudaFree(p);
+    for (auto &pr : e->retired) scratch_give(e->ordinal, pr.first, pr.second);
     e->retired.clear();
 }
 
 extern "C" void mlxn_encoder_destroy(mlxn_encoder *enc) {
     if (!enc) return;
-    cudaSetDevice(enc->dev->ordinal);
-    for (int l = 0; l < kLanes; l++) cudaStreamSynchronize(enc->lanes[l]);
+    cudaSetDevice(enc->ordinal);
+    cudaError_t serr = cudaSuccess;
+    for (int l = 0; l < kLanes; l++) {
+        cudaError_t e1 = cudaStreamSynchronize(enc->lanes[l]);
+        if (e1 != cudaSuccess) serr = e1;
+    }
     encoder_release_retained(enc);
+    if (serr == cudaSuccess && !enc->capturing) {
+        // clean and idle: keep it for the next mlxn_encoder_create on this device
+        enc->started = enc->committed = false;
+        enc->cur_lane = 0;
+        enc->stream = enc->lanes[0];
+        for (int l = 0; l < kLanes; l++) enc->lane_busy[l] = false;
+        enc->grp_reads.clear();
+        enc->grp_writes.clear();
+        enc->grp_open = false;
+        if (*enc->status_host != 0) {
+            *enc->status_host = 0;
+            cudaMemset(enc->status_dev, 0, kStatusBlockBytes);
+        }
+        std::lock_guard<std::mutex> lk(g_enc_pool_mu);
+        if (g_enc_pool.size() < 8) {
+            g_enc_pool.push_back(enc);
+            return;
+        }
+    }
+    (void)cudaGetLastError();
     for (int l = 0; l < kLanes; l++)
-        if (enc->scratch_lane[l]) cudaFree(enc->scratch_lane[l]);
+        if (enc->scratch_lane[l]) scratch_give(enc->ordinal, enc->scratch_lane[l], enc->scratch_lane_bytes[l]);
     cudaFree(enc->status_dev);
     cudaFreeHost(enc->status_host);
     cudaEventDestroy(enc->ev_start);
@@ -672,12 +746,12 @@ static int encoder_join_lanes(mlxn_encoder *e) {
 extern "C" int mlxn_encoder_memory_barrier(mlxn_encoder *enc) {
     if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
     g_barrier.fetch_add(1);
-    cudaSetDevice(enc->dev->ordinal);
+    cudaSetDevice(enc->ordinal);
     return encoder_join_lanes(enc);
 }
 
 static int encoder_begin_work(mlxn_encoder *e) {
-    cudaSetDevice(e->dev->ordinal);
+    cudaSetDevice(e->ordinal);
     if (!e->started && !e->capturing) {
         CUDA_TRY(cudaEventRecord(e->ev_start, e->lanes[0]), "event record");
         e->started = true;
@@ -689,7 +763,7 @@ static int encoder_begin_work(mlxn_encoder *e) {
 extern "C" int mlxn_encoder_commit(mlxn_encoder *enc) {
     if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
     if (enc->capturing) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: commit while a capture is open");
-    cudaSetDevice(enc->dev->ordinal);
+    cudaSetDevice(enc->ordinal);
     int jrc = encoder_join_lanes(enc);
     if (jrc) return jrc;
     if (!enc->started) {
@@ -714,7 +788,7 @@ static const char *status_text(uint32_t s) {
 
 extern "C" int mlxn_encoder_wait_until_completed(mlxn_encoder *enc) {
     if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
-    cudaSetDevice(enc->dev->ordinal);
+    cudaSetDevice(enc->ordinal);
     g_sync.fetch_add(1);
     cudaError_t e = cudaSuccess;
     if (enc->committed) {
@@ -755,7 +829,7 @@ extern "C" int mlxn_encoder_commit_wait_with_gpu_time(mlxn_encoder *enc, double 
 extern "C" int mlxn_encoder_begin_capture(mlxn_encoder *enc) {
     if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
     if (enc->capturing) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: a capture is already open");
-    cudaSetDevice(enc->dev->ordinal);
+    cudaSetDevice(enc->ordinal);
     int jrc = encoder_join_lanes(enc);  // the capture starts from lane 0 alone; other lanes fork from inside it
     if (jrc) return jrc;
     CUDA_TRY(cudaStreamBeginCapture(enc->lanes[0], cudaStreamCaptureModeRelaxed), "begin capture");
@@ -767,7 +841,7 @@ extern "C" int mlxn_encoder_begin_capture(mlxn_encoder *enc) {
 extern "C" int mlxn_encoder_end_capture(mlxn_encoder *enc, mlxn_graph **out) {
     if (!enc || !out) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder and out must not be null");
     if (!enc->capturing) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: no capture is open");
-    cudaSetDevice(enc->dev->ordinal);
+    cudaSetDevice(enc->ordinal);
     int jrc = encoder_join_lanes(enc);  // every forked lane rejoins lane 0 before the capture ends
     enc->capturing = false;
     auto *g = new mlxn_graph();
@@ -809,14 +883,16 @@ static int encoder_scratch(mlxn_encoder *e, size_t bytes, uint8_t **out) {
     uint8_t *&scratch = e->scratch_lane[e->cur_lane];  // operations on different lanes may run at the same time
     size_t &scratch_bytes = e->scratch_lane_bytes[e->cur_lane];
     if (bytes > scratch_bytes) {
-        const size_t want = bucket_size(bytes < (1u << 20) ? (1u << 20) : bytes);
-        void *p = nullptr;
-        cudaError_t err = cudaMalloc(&p, want);
-        if (err != cudaSuccess) {
-            cudaGetLastError();
-            return fail(MLXN_BUFFER_ALLOCATION_ERROR, "Failed to allocate device buffer of %zu bytes", want);
+        size_t want = bucket_size(bytes < (1u << 20) ? (1u << 20) : bytes);
+        void *p = scratch_take(e->ordinal, want, &want);
+        if (!p) {
+            cudaError_t err = cudaMalloc(&p, want);
+            if (err != cudaSuccess) {
+                cudaGetLastError();
+                return fail(MLXN_BUFFER_ALLOCATION_ERROR, "Failed to allocate device buffer of %zu bytes", want);
+            }
         }
-        if (scratch) e->retired.push_back(scratch);
+        if (scratch) e->retired.push_back({scratch, scratch_bytes});
         scratch = static_cast<uint8_t *>(p);
         scratch_bytes = want;
     }
@@ -829,8 +905,8 @@ static int encoder_scratch(mlxn_encoder *e, size_t bytes, uint8_t **out) {
 static int bind(mlxn_encoder *e, mlxn_buffer *b, bool is_output) {
     Storage *s = b->st;
     std::lock_guard<std::mutex> lk(s->mu);
-    if (s->ordinal != e->dev->ordinal)
-        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: buffer lives on device %d, encoder on device %d", s->ordinal, e->dev->ordinal);
+    if (s->ordinal != e->ordinal)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: buffer lives on device %d, encoder on device %d", s->ordinal, e->ordinal);
     bool own_lane = false;  // lanes of one encoder are ordered by its group logic, not by host-side waits
     for (int l = 0; l < kLanes; l++) own_lane = own_lane || s->last_stream == e->lanes[l];
     if (s->has_last && !own_lane) {
@@ -958,10 +1034,14 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
         a.expert_stride = 0;
         a.status = enc->status_dev;
         a.early_weights = weight->st->kernel_written ? 0u : 1u;
-        // The tensor-core kernel's time does not grow with the number of rows, the streaming SIMT kernel's does
-        // (it wins for one row, and for two rows of Q6_K unless K is long): "auto" picks by that measured crossover.
+        // The tensor-core kernel's time does not grow with the number of rows, the streaming SIMT kernel's does.
+        // Alone, the streaming kernel is a little faster for one row; in a sequence of mat-vecs the tensor-core
+        // kernel's calls overlap better, and the whole decode sweep is fastest with it everywhere ("auto").
         const int mode = opt_qmv();
-        const bool want_tc = mode == 2 || (mode == 3 && (a.m >= 3 || (a.m == 2 && ((int)p->ggml_type != GT_Q6_K || a.k >= 8192))));
+        static const int min_m = [] { const char *e = getenv("MLXN_QMV_TC_MIN_M"); return e ? atoi(e) : 1; }();         // experiment switches
+        static const int min_m_q6k = [] { const char *e = getenv("MLXN_QMV_TC_MIN_M_Q6K"); return e ? atoi(e) : 1; }();
+        const int need_m = (int)p->ggml_type == GT_Q6_K ? (a.k >= 8192 ? (min_m_q6k < 2 ? min_m_q6k : 2) : min_m_q6k) : min_m;
+        const bool want_tc = mode == 2 || (mode == 3 && (int)a.m >= need_m);
         if (want_tc && qmv_tc_supported((int)p->ggml_type, a)) {
             // tensor-core path: packed activations, block sums and split-K partial sums live in the encoder's arena
             uint8_t *scratch = nullptr;
