@@ -770,6 +770,18 @@ extern "C" int mlxn_encoder_commit(mlxn_encoder *enc) {
         CUDA_TRY(cudaEventRecord(enc->ev_start, enc->lanes[0]), "event record");
         enc->started = true;
     }
+    // Results the host has a view of are brought back as part of the command buffer (upstream's buffers are
+    // unified memory: after commit_and_wait the CPU simply sees them); large ones are fetched on demand instead.
+    for (mlxn_buffer *b : enc->retained) {
+        Storage *st = b->st;
+        std::lock_guard<std::mutex> lk(st->mu);
+        if (st->host && st->dev_newer && st->bytes <= (size_t)(4u << 20)) {
+            CUDA_TRY(cudaMemcpyAsync(st->host, st->dptr, st->bytes, cudaMemcpyDeviceToHost, enc->lanes[0]), "device-to-host copy");
+            st->dev_newer = false;
+            st->last_stream = enc->lanes[0];
+            st->has_last = true;
+        }
+    }
     CUDA_TRY(cudaMemcpyAsync(enc->status_host, enc->status_dev, 4, cudaMemcpyDeviceToHost, enc->lanes[0]), "status copy");
     CUDA_TRY(cudaEventRecord(enc->ev_end, enc->lanes[0]), "event record");
     enc->committed = true;
