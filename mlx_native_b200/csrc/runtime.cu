@@ -162,6 +162,9 @@ struct mlxn_graph {
     cudaGraphExec_t exec = nullptr;
     uint64_t launches = 0;  // kernels recorded in the graph
     uint64_t dispatches = 0;
+    // Host views and replays: the upload of an input whose host view was dirty at capture time is part of the
+    // graph (it reads the pinned shadow again at every replay); outputs become "newer on the device" at every replay.
+    std::vector<mlxn_buffer *> uploads, outputs;  // hold a reference each
 };
 
 // Scratch arenas outlive their encoder: short-lived encoders (one per command buffer, as upstream uses them) would
@@ -221,6 +224,7 @@ struct mlxn_encoder {
     uint8_t *scratch_lane[kLanes] = {};
     size_t scratch_lane_bytes[kLanes] = {};
     std::vector<std::pair<void *, size_t>> retired;  // outgrown scratch arenas, handed back after the next wait
+    std::vector<mlxn_buffer *> cap_uploads, cap_outputs;  // see mlxn_graph; filled while a capture is open
     uint32_t *status_dev = nullptr;
     uint32_t *status_host = nullptr;  // pinned
 };
@@ -863,8 +867,14 @@ extern "C" int mlxn_encoder_end_capture(mlxn_encoder *enc, mlxn_graph **out) {
     if (e != cudaSuccess) {
         if (g->graph) cudaGraphDestroy(g->graph);
         delete g;
+        for (mlxn_buffer *b : enc->cap_uploads) mlxn_buffer_release(b);
+        for (mlxn_buffer *b : enc->cap_outputs) mlxn_buffer_release(b);
+        enc->cap_uploads.clear();
+        enc->cap_outputs.clear();
         return cuda_fail(e, "end capture");
     }
+    g->uploads.swap(enc->cap_uploads);
+    g->outputs.swap(enc->cap_outputs);
     g->launches = g_launches.load() - enc->cap_launch0;
     g->dispatches = g_dispatch.load() - enc->cap_dispatch0;
     // recording is not running: take the recorded work back out of the global counters
@@ -879,12 +889,28 @@ extern "C" int mlxn_graph_launch(mlxn_graph *graph, mlxn_encoder *enc) {
     if (rc) return rc;
     if ((rc = encoder_join_lanes(enc))) return rc;  // the graph's buffers are unknown here: it is its own group
     CUDA_TRY(cudaGraphLaunch(graph->exec, enc->lanes[0]), "graph launch");
+    for (mlxn_buffer *b : graph->uploads) {
+        std::lock_guard<std::mutex> lk(b->st->mu);
+        b->st->host_newer = false;  // the replay has just read the shadow
+    }
+    for (mlxn_buffer *b : graph->outputs) {
+        {
+            std::lock_guard<std::mutex> lk(b->st->mu);
+            if (b->st->host) b->st->dev_newer = true;
+            b->st->last_stream = enc->lanes[0];
+            b->st->has_last = true;
+        }
+        b->refs.fetch_add(1);
+        enc->retained.push_back(b);  // kept alive, and fetched back at commit like any other result
+    }
     g_launches.fetch_add(graph->launches);
     g_dispatch.fetch_add(graph->dispatches);
     return MLXN_OK;
 }
 extern "C" void mlxn_graph_destroy(mlxn_graph *graph) {
     if (!graph) return;
+    for (mlxn_buffer *b : graph->uploads) mlxn_buffer_release(b);
+    for (mlxn_buffer *b : graph->outputs) mlxn_buffer_release(b);
     if (graph->exec) cudaGraphExecDestroy(graph->exec);
     if (graph->graph) cudaGraphDestroy(graph->graph);
     delete graph;
@@ -927,6 +953,14 @@ static int bind(mlxn_encoder *e, mlxn_buffer *b, bool is_output) {
     if (s->host_newer) {
         CUDA_TRY(cudaMemcpyAsync(s->dptr, s->host, s->bytes, cudaMemcpyHostToDevice, e->stream), "host-to-device copy");
         s->host_newer = false;
+        if (e->capturing) {
+            b->refs.fetch_add(1);
+            e->cap_uploads.push_back(b);
+        }
+    }
+    if (is_output && e->capturing) {
+        b->refs.fetch_add(1);
+        e->cap_outputs.push_back(b);
     }
     if (is_output && s->host) s->dev_newer = true;
     if (is_output) s->kernel_written = true;

@@ -194,3 +194,33 @@ def test_dependent_chain_and_independent_ops_in_one_encoder(ctx, qmv, captured):
     assert norm_err(y2.as_slice(np.float32).reshape(m, n2), r2, ad2) <= MV_TOL
     r3, ad3 = orc.qmatmul(otype, w3, x, n2, k, nthreads=8)
     assert norm_err(y3.as_slice(np.float32).reshape(m, n2), r3, ad3) <= MV_TOL
+
+
+def test_graph_replay_with_host_views(ctx):
+    """An input written through its host view before the capture is uploaded by the graph at every replay, and an
+    output with a host view is fetched back by the commit after each replay (unified-memory behaviour upstream)."""
+    d = ctx.device
+    gtype, otype = TYPES["Q8_0"]
+    n, k, m = 512, 1024, 2
+    wq = normal_weights(41, n, k, otype)
+    w = ctx.buf(wq, mx.DType.U8)
+    xb = d.alloc_buffer(m * k * 4, mx.DType.F32)
+    yb = d.alloc_buffer(m * n * 4, mx.DType.F32)
+    yb.as_slice(np.float32)                                  # give the output a host view
+    p = mx.GgmlQuantizedMatmulParams(m, n, k, gtype)
+    enc = d.command_encoder()
+    x0 = normal_acts(41, m, k)
+    xb.as_mut_slice(np.float32)[:] = x0.reshape(-1)
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, w, yb, p)
+    enc.commit_and_wait()
+    xb.as_mut_slice(np.float32)[:] = x0.reshape(-1)          # dirty again: the capture records the upload
+    enc.begin_capture()
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, w, yb, p)
+    g = enc.end_capture()
+    for seed in (42, 43, 44):
+        x = normal_acts(seed, m, k)
+        xb.as_mut_slice(np.float32)[:] = x.reshape(-1)
+        g.launch(enc)
+        enc.commit_and_wait()
+        y_ref, ad = orc.qmatmul(otype, wq, x, n, k, nthreads=8)
+        assert norm_err(yb.as_slice(np.float32).reshape(m, n), y_ref, ad) <= MV_TOL
