@@ -236,3 +236,38 @@ __device__ __forceinline__ void tmem_st_32x32_x32(uint32_t taddr, const uint32_t
         : "memory");
 }
 }  // namespace mlxn
+
+namespace mlxn {
+
+// ---- shared-memory loads by 32-bit shared address ---------------------------------------------------
+__device__ __forceinline__ void lds128(uint32_t addr, uint32_t &a, uint32_t &b, uint32_t &c, uint32_t &d) {
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
+}
+__device__ __forceinline__ void lds64(uint32_t addr, uint32_t &a, uint32_t &b) {
+    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(a), "=r"(b) : "r"(addr));
+}
+__device__ __forceinline__ int lds_s8(uint32_t addr) {
+    int v;
+    asm volatile("{ .reg .s16 t; ld.shared.s8 t, [%1]; cvt.s32.s16 %0, t; }" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(addr));
+    return v;
+}
+// NW words that start PRE bytes (even, < 16, compile time) into the 16-byte aligned shared address `a16`:
+// 16-byte loads (conflict-free when consecutive rows are an odd multiple of 16 bytes apart) + static funnel shifts.
+template <int PRE, int NW> __device__ __forceinline__ void lds_field(uint32_t a16, uint32_t (&w)[NW]) {
+    constexpr int kChunks = (PRE + 4 * NW + 15) / 16;
+    uint32_t W[4 * kChunks + 1];
+#pragma unroll
+    for (int i = 0; i < kChunks; i++) lds128(a16 + 16 * i, W[4 * i], W[4 * i + 1], W[4 * i + 2], W[4 * i + 3]);
+    W[4 * kChunks] = 0;
+    constexpr int wo = PRE >> 2;
+#pragma unroll
+    for (int i = 0; i < NW; i++) w[i] = (PRE & 2) ? __funnelshift_r(W[wo + i], W[wo + i + 1], 16) : W[wo + i];
+}
+template <int PRE> __device__ __forceinline__ void lds_field16(uint32_t a16, uint32_t (&w)[4]) { lds_field<PRE, 4>(a16, w); }
+
+}  // namespace mlxn

@@ -394,6 +394,108 @@ template <int T> __device__ __forceinline__ void dequant32(uint32_t seg, uint32_
     }
 }
 
+// ---- rows that start on 16-byte boundaries: 16-byte shared loads at compile-time offsets ----------------------
+// The generic routines above read the raw rows with 32-bit loads at 2-byte granular addresses; with rows an odd
+// multiple of 16 bytes apart those are 4-way bank-conflicted (two thirds of the kernel's shared-memory wavefronts).
+// When every weight row starts on a 16-byte boundary and the raw stage is a whole number of 16-byte units per row
+// (k % 256 == 0), each thread's 64 elements sit at a compile-time byte offset of the row's stage, so they can
+// be fetched with conflict-free 16-byte loads and static funnel shifts.
+__device__ __forceinline__ void q4_0_block_to_h(uint32_t dbits, const uint32_t (&q)[4], uint32_t *out /*16 words*/) {
+    const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits));
+    const __half2 off = __float2half2_rn(1032.0f);  // 1024 + 8
+#pragma unroll
+    for (int j = 0; j < 4; j++) {  // j = 0,1: low nibbles of bytes 0-7, 8-15; j = 2,3: high nibbles
+        const uint32_t w0 = ((j & 2) ? (q[2 * (j & 1)] >> 4) : q[2 * (j & 1)]) & 0x0F0F0F0Fu;
+        const uint32_t w1 = ((j & 2) ? (q[2 * (j & 1) + 1] >> 4) : q[2 * (j & 1) + 1]) & 0x0F0F0F0Fu;
+        __half2 a, b, cc, dd;
+        bytes_to_h2(w0, a, b);
+        bytes_to_h2(w1, cc, dd);
+        out[4 * j + 0] = h2_as_u32(__hmul2(__hsub2(a, off), d2));
+        out[4 * j + 1] = h2_as_u32(__hmul2(__hsub2(b, off), d2));
+        out[4 * j + 2] = h2_as_u32(__hmul2(__hsub2(cc, off), d2));
+        out[4 * j + 3] = h2_as_u32(__hmul2(__hsub2(dd, off), d2));
+    }
+}
+__device__ __forceinline__ void q8_0_block_to_h(uint32_t dbits, const uint32_t (&q)[8], uint32_t *out /*16 words*/) {
+    const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)dbits));
+    const __half2 off = __float2half2_rn(1152.0f);  // 1024 + 128
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        __half2 a, b;
+        bytes_to_h2(q[j] ^ 0x80808080u, a, b);
+        out[2 * j + 0] = h2_as_u32(__hmul2(__hsub2(a, off), d2));
+        out[2 * j + 1] = h2_as_u32(__hmul2(__hsub2(b, off), d2));
+    }
+}
+// Quarter S4 (64 elements = 2 blocks) of a row's 256-wide raw stage at the 16-byte aligned shared address `unit`.
+template <int T, int S4> __device__ __forceinline__ void dequant64_aligned(uint32_t unit, uint32_t (&r)[32]) {
+    constexpr int SUB = 2 * BlockTraits<T>::BYTES;   // bytes of two blocks
+    constexpr int c0 = (SUB * S4) >> 4;              // first 16-byte chunk touched
+    constexpr int wo = ((SUB * S4) & 15) >> 2;       // word offset inside it (SUB * S4 is a multiple of 4)
+    if constexpr (T == GT_Q4_0) {
+        uint32_t W[12];
+#pragma unroll
+        for (int i = 0; i < 3; i++) lds128(unit + 16 * (c0 + i), W[4 * i], W[4 * i + 1], W[4 * i + 2], W[4 * i + 3]);
+        uint32_t q0[4], q1[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            q0[i] = __funnelshift_r(W[wo + i], W[wo + i + 1], 16);  // block 0's codes start 2 bytes into a word
+            q1[i] = W[wo + 5 + i];                                  // block 1's are word aligned
+        }
+        q4_0_block_to_h(W[wo] & 0xFFFFu, q0, r);
+        q4_0_block_to_h(W[wo + 4] >> 16, q1, r + 16);
+    } else {
+        uint32_t W[20];
+#pragma unroll
+        for (int i = 0; i < 5; i++) lds128(unit + 16 * (c0 + i), W[4 * i], W[4 * i + 1], W[4 * i + 2], W[4 * i + 3]);
+        uint32_t q0[8], q1[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            q0[i] = __funnelshift_r(W[wo + i], W[wo + i + 1], 16);
+            q1[i] = W[wo + 9 + i];
+        }
+        q8_0_block_to_h(W[wo] & 0xFFFFu, q0, r);
+        q8_0_block_to_h(W[wo + 8] >> 16, q1, r + 16);
+    }
+}
+// Q6_K: the 32-element run (h, g) of the super-block that starts PRE bytes into the row's aligned stage.
+template <int PRE> __device__ __forceinline__ void dequant32_q6k_aligned(uint32_t stage_row, uint32_t h, uint32_t g, uint32_t *out) {
+    uint32_t A[8], H[8];
+    lds_field<PRE, 8>(stage_row + 64 * h + 32 * (g & 1u), A);
+    lds_field<PRE, 8>(stage_row + 128 + 32 * h, H);
+    const float d = half_bits_to_float(lds_u16(stage_row + PRE + 208));
+    const float ds0 = d * (float)lds_s8(stage_row + PRE + 192 + 8 * h + 2 * g);
+    const float ds1 = d * (float)lds_s8(stage_row + PRE + 192 + 8 * h + 2 * g + 1);
+    const uint32_t hsh = 2 * g, ash = (g & 2u) ? 4u : 0u;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float ds = j < 2 ? ds0 : ds1;
+        const float c = -160.0f * ds;  // exact: ds has <= 18 significant bits
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const uint32_t u = ((A[2 * j + i] >> ash) & 0x0F0F0F0Fu) | (((H[2 * j + i] >> hsh) & 0x03030303u) << 4);
+            const float f0 = fmaf(__uint_as_float(__byte_perm(u, 0x43000000u, 0x7044)), ds, c);
+            const float f1 = fmaf(__uint_as_float(__byte_perm(u, 0x43000000u, 0x7144)), ds, c);
+            const float f2 = fmaf(__uint_as_float(__byte_perm(u, 0x43000000u, 0x7244)), ds, c);
+            const float f3 = fmaf(__uint_as_float(__byte_perm(u, 0x43000000u, 0x7344)), ds, c);
+            out[4 * j + 2 * i] = h2_as_u32(__floats2half2_rn(f0, f1));
+            out[4 * j + 2 * i + 1] = h2_as_u32(__floats2half2_rn(f2, f3));
+        }
+    }
+}
+__device__ __forceinline__ void dequant32_q6k_aligned_p(uint32_t p8, uint32_t stage_row, uint32_t h, uint32_t g, uint32_t *out) {
+    switch (p8) {  // uniform over the CTA
+    case 0: dequant32_q6k_aligned<0>(stage_row, h, g, out); break;
+    case 1: dequant32_q6k_aligned<2>(stage_row, h, g, out); break;
+    case 2: dequant32_q6k_aligned<4>(stage_row, h, g, out); break;
+    case 3: dequant32_q6k_aligned<6>(stage_row, h, g, out); break;
+    case 4: dequant32_q6k_aligned<8>(stage_row, h, g, out); break;
+    case 5: dequant32_q6k_aligned<10>(stage_row, h, g, out); break;
+    case 6: dequant32_q6k_aligned<12>(stage_row, h, g, out); break;
+    default: dequant32_q6k_aligned<14>(stage_row, h, g, out); break;
+    }
+}
+
 // position in a ring of `stages` slots plus the phase bit of the slot's current use (no divisions)
 struct RingPos {
     uint32_t s = 0, ph = 0;
@@ -412,6 +514,7 @@ struct TcCfg {
     uint32_t seg_stride;  // bytes reserved per raw row segment
     uint32_t b_off, raw_off;
     uint32_t raw_slots;   // depth of the raw weight ring (2..6)
+    uint32_t aligned;     // every weight row starts on a 16-byte boundary and k % 256 == 0: static-offset 16-byte raw reads
     uint32_t debug;       // experiment switches: 1 = skip dequantisation, 2 = skip raw copies, 4 = skip MMA, 8 = skip B copies
 };
 
@@ -649,22 +752,37 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                 const uint32_t pre = (row_lo4 + ((r * KR) / QK) * BB) & 15u;
                 const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
                 uint32_t regs[32];
-#pragma unroll
-                for (uint32_t hh = 0; hh < 2; hh++) {
-                    uint4 v[4];
-                    const uint32_t e0 = 128 * set + 64 * half + 32 * hh;  // element offset inside the raw stage
-                    if (row_ok && r * KR + e0 < a.k && !(c.debug & 1u)) {
-                        dequant32<T>(seg, e0, v);
+                if (c.aligned && row_ok && !(c.debug & 1u)) {
+                    const uint32_t stage_row = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride;
+                    if constexpr (T == GT_Q6_K) {
+                        dequant32_q6k_aligned_p(r & 7u, stage_row, set, 2 * half, regs);
+                        dequant32_q6k_aligned_p(r & 7u, stage_row, set, 2 * half + 1, regs + 16);
                     } else {
-#pragma unroll
-                        for (int i = 0; i < 4; i++) v[i] = make_uint4(0, 0, 0, 0);
+                        switch (2 * set + half) {  // uniform per warp
+                        case 0: dequant64_aligned<T, 0>(stage_row, regs); break;
+                        case 1: dequant64_aligned<T, 1>(stage_row, regs); break;
+                        case 2: dequant64_aligned<T, 2>(stage_row, regs); break;
+                        default: dequant64_aligned<T, 3>(stage_row, regs); break;
+                        }
                     }
+                } else {
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        regs[16 * hh + 4 * i + 0] = v[i].x;
-                        regs[16 * hh + 4 * i + 1] = v[i].y;
-                        regs[16 * hh + 4 * i + 2] = v[i].z;
-                        regs[16 * hh + 4 * i + 3] = v[i].w;
+                    for (uint32_t hh = 0; hh < 2; hh++) {
+                        uint4 v[4];
+                        const uint32_t e0 = 128 * set + 64 * half + 32 * hh;  // element offset inside the raw stage
+                        if (row_ok && r * KR + e0 < a.k && !(c.debug & 1u)) {
+                            dequant32<T>(seg, e0, v);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; i++) v[i] = make_uint4(0, 0, 0, 0);
+                        }
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            regs[16 * hh + 4 * i + 0] = v[i].x;
+                            regs[16 * hh + 4 * i + 1] = v[i].y;
+                            regs[16 * hh + 4 * i + 2] = v[i].z;
+                            regs[16 * hh + 4 * i + 3] = v[i].w;
+                        }
                     }
                 }
                 tmem_st_32x32_x32(a_dst + sa * kTcACols, regs);
@@ -767,6 +885,11 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     {
         const char *dbg = getenv("MLXN_TC_DEBUG");
         c.debug = dbg ? (uint32_t)atoi(dbg) : 0u;
+    }
+    {
+        const uint32_t row_bytes = (a.k / QK) * BB;
+        c.aligned = ((((uintptr_t)a.w | a.expert_stride) & 15u) == 0 && row_bytes % 16 == 0 && a.k % 256 == 0) ? 1u : 0u;
+        if (getenv("MLXN_TC_NO_ALIGNED")) c.aligned = 0;  // experiment switch
     }
     c.nchunks = (a.k + 63) / 64;
     c.seg_stride = round_up_u((KR / QK) * BB + 15, 16) + 16;

@@ -254,11 +254,6 @@ __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
     asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ int lds_s8(uint32_t addr) {
-    int v;
-    asm volatile("{ .reg .s16 t; ld.shared.s8 t, [%1]; cvt.s32.s16 %0, t; }" : "=r"(v) : "r"(addr));
-    return v;
-}
 __device__ __forceinline__ void lds128(uint32_t addr, uint64_t &lo, uint64_t &hi) {
     asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(lo), "=l"(hi) : "r"(addr));
 }

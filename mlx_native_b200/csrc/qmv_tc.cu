@@ -183,13 +183,6 @@ __global__ void __launch_bounds__(128) qmv_tc_pack_kernel(const QmvArgs a, int g
 // ------------------------------------------------------------------------------------------------
 // code extraction: one sub-step (64 K elements = 2 blocks) of one weight row -> 32 packed f16 pairs
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void lds128(uint32_t addr, uint32_t &a, uint32_t &b, uint32_t &c, uint32_t &d) {
-    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
-}
-__device__ __forceinline__ void lds64(uint32_t addr, uint32_t &a, uint32_t &b) {
-    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2];" : "=r"(a), "=r"(b) : "r"(addr));
-}
-
 // `unit` = shared address of the row's 16-byte aligned K unit; S4 = which quarter of the unit (compile time,
 // so every byte offset below is static).  d0 / d1 receive the two blocks' scales.
 template <int T, int S4> __device__ __forceinline__ void vt_extract(uint32_t unit, uint32_t (&r)[32], float &d0, float &d1) {
@@ -237,25 +230,6 @@ template <int T, int S4> __device__ __forceinline__ void vt_extract(uint32_t uni
 // (q1, q3) or (q2, q4): two scale groups of 16 codes -> 16 packed pairs.  The super-block starts PRE bytes
 // into the row's 16-byte aligned stage (PRE = 2 (unit index % 8), the same for every row, so it is a
 // compile-time constant of the variant); every field offset below is PRE plus a multiple of 16.
-__device__ __forceinline__ int lds_s8(uint32_t addr) {
-    int v;
-    asm volatile("{ .reg .s16 t; ld.shared.s8 t, [%1]; cvt.s32.s16 %0, t; }" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
-    uint32_t v;
-    asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(addr));
-    return v;
-}
-// four words that start PRE bytes into the 16-byte aligned address `a16`
-template <int PRE> __device__ __forceinline__ void lds_field16(uint32_t a16, uint32_t (&w)[4]) {
-    uint32_t W[8];
-    lds128(a16, W[0], W[1], W[2], W[3]);
-    if constexpr (PRE != 0) lds128(a16 + 16, W[4], W[5], W[6], W[7]);
-    constexpr int wo = PRE >> 2;
-#pragma unroll
-    for (int i = 0; i < 4; i++) w[i] = (PRE & 2) ? __funnelshift_r(W[wo + i], W[wo + i + 1], 16) : W[wo + i];
-}
 template <int PRE>
 __device__ __forceinline__ void vt_extract_q6k(uint32_t stage_row, uint32_t n, uint32_t g, uint32_t (&r)[16], float &d0, float &d1) {
     const uint32_t pair_b = g >> 1, lh = g & 1u;
@@ -800,8 +774,10 @@ __global__ void __launch_bounds__(256) qmv_publish_kernel(const QmvArgs a) {
     }
 }
 
+// `pub_st` / `pub_ev`: for the row-sharded form, the copy to the peers runs on a stream of its own behind an event,
+// so that the operations that follow on `st` do not wait for stores to other GPUs to be acknowledged.
 cudaError_t launch_qmv_tc(int ggml_type, const QmvArgs &a, uint8_t *scratch, uint32_t *flags, int sm_count, cudaStream_t st,
-                          int *launches) {
+                          cudaStream_t pub_st, cudaEvent_t pub_ev, int *launches) {
     QmvArgs loc = a;
     loc.n_peer = 0;  // the mat-vec itself writes this rank's buffer only
     cudaError_t e;
@@ -816,7 +792,10 @@ cudaError_t launch_qmv_tc(int ggml_type, const QmvArgs &a, uint8_t *scratch, uin
     uint32_t blocks = (total + 255) / 256;
     if (blocks > 64) blocks = 64;
     (*launches)++;
-    return launch_overlapped(qmv_publish_kernel, dim3(blocks), dim3(256), 0, st, a);
+    if ((e = cudaEventRecord(pub_ev, st)) != cudaSuccess) return e;
+    if ((e = cudaStreamWaitEvent(pub_st, pub_ev, 0)) != cudaSuccess) return e;
+    qmv_publish_kernel<<<blocks, 256, 0, pub_st>>>(a);
+    return cudaGetLastError();
 }
 
 }  // namespace mlxn

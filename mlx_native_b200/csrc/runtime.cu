@@ -25,7 +25,7 @@ cudaError_t launch_qmv(int ggml_type, const QmvArgs &a, bool want_stream, int sm
 bool qmv_tc_supported(int ggml_type, const QmvArgs &a);
 size_t qmv_tc_scratch_bytes(const QmvArgs &a);
 cudaError_t launch_qmv_tc(int ggml_type, const QmvArgs &a, uint8_t *scratch, uint32_t *flags, int sm_count, cudaStream_t st,
-                          int *launches);
+                          cudaStream_t pub_st, cudaEvent_t pub_ev, int *launches);
 cudaError_t launch_qmm_tc(int ggml_type, const QmmArgs &a, bool routed, uint32_t nt, uint8_t *scratch, cudaStream_t st,
                           int *launches);
 cudaError_t launch_qmm_simt(int ggml_type, const QmmArgs &a, bool routed, uint32_t max_rows, cudaStream_t st);
@@ -215,6 +215,9 @@ struct mlxn_encoder {
     int cur_lane = 0;
     bool lane_busy[kLanes] = {};     // lane has work of the current group that lane 0 has not been made to wait for
     cudaEvent_t ev_fork = nullptr, ev_join[kLanes] = {};
+    cudaStream_t aux = nullptr;      // side work that nothing in the group waits for (copies of results to peer GPUs)
+    cudaEvent_t ev_aux = nullptr, ev_aux_join = nullptr;
+    bool aux_busy = false;
     std::vector<const void *> grp_reads, grp_writes;  // storages the current group reads / writes
     bool grp_open = false;           // ev_fork marks the start of the current group
     cudaEvent_t ev_start = nullptr, ev_end = nullptr;
@@ -644,6 +647,9 @@ extern "C" int mlxn_encoder_create(mlxn_device *dev, mlxn_encoder **out) {
         if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->ev_join[l], cudaEventDisableTiming);
     }
     e->stream = e->lanes[0];
+    if (err == cudaSuccess) err = cudaStreamCreateWithFlags(&e->aux, cudaStreamNonBlocking);
+    if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->ev_aux, cudaEventDisableTiming);
+    if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->ev_aux_join, cudaEventDisableTiming);
     if (err == cudaSuccess) err = cudaEventCreateWithFlags(&e->ev_fork, cudaEventDisableTiming);
     if (err == cudaSuccess) err = cudaEventCreate(&e->ev_start);
     if (err == cudaSuccess) err = cudaEventCreate(&e->ev_end);
@@ -657,6 +663,9 @@ extern "C" int mlxn_encoder_create(mlxn_device *dev, mlxn_encoder **out) {
             if (e->ev_join[l]) cudaEventDestroy(e->ev_join[l]);
         }
         if (e->ev_fork) cudaEventDestroy(e->ev_fork);
+        if (e->aux) cudaStreamDestroy(e->aux);
+        if (e->ev_aux) cudaEventDestroy(e->ev_aux);
+        if (e->ev_aux_join) cudaEventDestroy(e->ev_aux_join);
         if (e->ev_start) cudaEventDestroy(e->ev_start);
         if (e->ev_end) cudaEventDestroy(e->ev_end);
         if (e->status_dev) cudaFree(e->status_dev);
@@ -688,7 +697,7 @@ static void encoder_release_retained(mlxn_encoder *e) {
 extern "C" void mlxn_encoder_destroy(mlxn_encoder *enc) {
     if (!enc) return;
     cudaSetDevice(enc->ordinal);
-    cudaError_t serr = cudaSuccess;
+    cudaError_t serr = cudaStreamSynchronize(enc->aux);
     for (int l = 0; l < kLanes; l++) {
         cudaError_t e1 = cudaStreamSynchronize(enc->lanes[l]);
         if (e1 != cudaSuccess) serr = e1;
@@ -700,6 +709,7 @@ extern "C" void mlxn_encoder_destroy(mlxn_encoder *enc) {
         enc->cur_lane = 0;
         enc->stream = enc->lanes[0];
         for (int l = 0; l < kLanes; l++) enc->lane_busy[l] = false;
+        enc->aux_busy = false;
         enc->grp_reads.clear();
         enc->grp_writes.clear();
         enc->grp_open = false;
@@ -721,6 +731,9 @@ extern "C" void mlxn_encoder_destroy(mlxn_encoder *enc) {
     cudaEventDestroy(enc->ev_start);
     cudaEventDestroy(enc->ev_end);
     cudaEventDestroy(enc->ev_fork);
+    cudaEventDestroy(enc->ev_aux);
+    cudaEventDestroy(enc->ev_aux_join);
+    cudaStreamDestroy(enc->aux);
     for (int l = 0; l < kLanes; l++) {
         cudaEventDestroy(enc->ev_join[l]);
         cudaStreamDestroy(enc->lanes[l]);
@@ -738,6 +751,11 @@ static int encoder_join_lanes(mlxn_encoder *e) {
         CUDA_TRY(cudaEventRecord(e->ev_join[l], e->lanes[l]), "event record");
         CUDA_TRY(cudaStreamWaitEvent(e->lanes[0], e->ev_join[l], 0), "stream wait");
         e->lane_busy[l] = false;
+    }
+    if (e->aux_busy) {
+        CUDA_TRY(cudaEventRecord(e->ev_aux_join, e->aux), "event record");
+        CUDA_TRY(cudaStreamWaitEvent(e->lanes[0], e->ev_aux_join, 0), "stream wait");
+        e->aux_busy = false;
     }
     e->grp_reads.clear();
     e->grp_writes.clear();
@@ -810,6 +828,7 @@ extern "C" int mlxn_encoder_wait_until_completed(mlxn_encoder *enc) {
     if (enc->committed) {
         e = cudaEventSynchronize(enc->ev_end);
     } else {
+        e = cudaStreamSynchronize(enc->aux);
         for (int l = 0; l < kLanes && e == cudaSuccess; l++) e = cudaStreamSynchronize(enc->lanes[l]);
     }
     if (e == cudaSuccess) e = cudaGetLastError();
@@ -1093,8 +1112,10 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
             uint8_t *scratch = nullptr;
             if ((rc = encoder_scratch(enc, qmv_tc_scratch_bytes(a), &scratch))) return rc;
             int launches = 0;
-            CUDA_TRY(launch_qmv_tc((int)p->ggml_type, a, scratch, enc->status_dev + 64, dev->sm_count, enc->stream, &launches),
+            CUDA_TRY(launch_qmv_tc((int)p->ggml_type, a, scratch, enc->status_dev + 64, dev->sm_count, enc->stream, enc->aux,
+                                   enc->ev_aux, &launches),
                      "mat-vec launch");
+            if (a.n_peer) enc->aux_busy = true;
             g_launches.fetch_add((uint64_t)launches);
             g_last_kernel = "qmv_tc";
             continue;
