@@ -412,7 +412,8 @@ def run_ours(args, rank, world, local_rank):
                    "buffer (symmetric memory) + one cross-rank barrier per step" if symm is not None else
                    "NCCL all-gather per mat-vec"), "parallelism": f"n-shard x{world}"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": None, "peak_kind": f"{peak_kind} copy bandwidth", "kernel": "qmv_tc_kernel (3+ rows, 2 rows with k >= 8192) and qmv_stream_kernel (1-2 rows)",
+                     "traffic": step_algo_bytes * 1.01, "traffic_note": "ncu dram__bytes_read+write of qmv_tc_kernel is 1.008x (Q8_0) "
+                     "and 1.011x (Q6_K) its algorithmic bytes (profiles/qmv_tc_*_full.md); scaled to the step", "peak_kind": f"{peak_kind} copy bandwidth", "kernel": "qmv_tc_kernel (+ qmv_tc_pack_kernel)",
                      "note": "achieved = (weight + activation + output bytes of the 32 launches) / event-timed step"},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s * 1e3},
@@ -464,39 +465,42 @@ def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
     otype = {"Q4_0": orc.Q4_0, "Q6_K": orc.Q6_K}
     gt = {"Q4_0": mx.GgmlType.Q4_0, "Q6_K": mx.GgmlType.Q6_K}
 
-    def timed(fn, reps=10, warm=3):
-        """Median device time of one replay of `fn` captured into a CUDA graph (launch gaps excluded)."""
+    def timed(fn, reps=10, warm=3, inner=4):
+        """Median device time of one call of `fn`: `inner` calls are captured into one CUDA graph, so that the graph
+        launch and the first call's start-up latency are shared (as in a real sequence of calls)."""
         e = dev.command_encoder()
         for _ in range(warm):
             fn(e)
         e.commit_and_wait()
         e.begin_capture()
-        fn(e)
+        for _ in range(inner):
+            fn(e)
         g = e.end_capture()
         g.launch(e)
         e.commit_and_wait()
         ts = []
         for _ in range(reps):
             g.launch(e)
-            ts.append(e.commit_wait_with_gpu_time())
+            ts.append(e.commit_wait_with_gpu_time() / inner)
         return statistics.median(ts)
 
-    n, k = 4096, 4096
-    wf = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
     mm = {}
-    for t in ("Q4_0", "Q6_K"):
-        wq = orc.quantize(otype[t], wf, rule="ggml")
-        wb = dev.alloc_buffer(wq.size, mx.DType.U8)
-        wb.upload(wq)
-        for m in (512, 2048):
-            x = rng.standard_normal((m, k)).astype(np.float32)
-            xb = dev.alloc_buffer(x.nbytes, mx.DType.F32)
-            xb.upload(x)
-            yb = dev.alloc_buffer(m * n * 4, mx.DType.F32)
-            p = mx.GgmlQuantizedMatmulParams(m, n, k, gt[t])
-            sec = timed(lambda e: mx.quantized_matmul_ggml(e, reg, dev, xb, wb, yb, p))
-            tf = 2.0 * m * n * k / sec / 1e12
-            mm[f"{t}_m{m}_n{n}_k{k}"] = {"tflops": tf, "ms": sec * 1e3, "frac_of_measured_bf16_peak": tf / tf_peak}
+    for (n, k, ms) in ((4096, 4096, (512, 2048)), (12288, 4096, (2048,)), (4096, 12288, (2048,))):
+        wf = (rng.standard_normal((512, k), dtype=np.float32) * np.float32(0.02))
+        for t in ("Q4_0", "Q6_K"):
+            wq = np.tile(orc.quantize(otype[t], wf, rule="ggml"), n // 512)   # timing does not depend on the values
+            wb = dev.alloc_buffer(wq.size, mx.DType.U8)
+            wb.upload(wq)
+            for m in ms:
+                x = rng.standard_normal((m, k)).astype(np.float32)
+                xb = dev.alloc_buffer(x.nbytes, mx.DType.F32)
+                xb.upload(x)
+                yb = dev.alloc_buffer(m * n * 4, mx.DType.F32)
+                p = mx.GgmlQuantizedMatmulParams(m, n, k, gt[t])
+                sec = timed(lambda e: mx.quantized_matmul_ggml(e, reg, dev, xb, wb, yb, p))
+                tf = 2.0 * m * n * k / sec / 1e12
+                mm[f"{t}_m{m}_n{n}_k{k}"] = {"tflops": tf, "ms": sec * 1e3, "frac_of_measured_bf16_peak": tf / tf_peak}
+            del wb
     out["qmm"] = mm
 
     # MoE FFN: gate + up (Q4_0 [768 x 2048] per expert), down (Q6_K [2048 x 768] per expert)
