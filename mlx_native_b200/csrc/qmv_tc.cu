@@ -774,8 +774,9 @@ __global__ void __launch_bounds__(256) qmv_publish_kernel(const QmvArgs a) {
     }
 }
 
-// `pub_st` / `pub_ev`: for the row-sharded form, the copy to the peers runs on a stream of its own behind an event,
-// so that the operations that follow on `st` do not wait for stores to other GPUs to be acknowledged.
+// `pub_st` / `pub_ev` (optional): for the row-sharded form, run the copy to the peers on a stream of its own behind an
+// event instead of on `st`.  (Measured on two GPUs: slower than leaving it on `st`, where it is a programmatic
+// dependent of the mat-vec kernel; the runtime passes null.)
 cudaError_t launch_qmv_tc(int ggml_type, const QmvArgs &a, uint8_t *scratch, uint32_t *flags, int sm_count, cudaStream_t st,
                           cudaStream_t pub_st, cudaEvent_t pub_ev, int *launches) {
     QmvArgs loc = a;
@@ -792,6 +793,7 @@ cudaError_t launch_qmv_tc(int ggml_type, const QmvArgs &a, uint8_t *scratch, uin
     uint32_t blocks = (total + 255) / 256;
     if (blocks > 64) blocks = 64;
     (*launches)++;
+    if (!pub_st) return launch_overlapped(qmv_publish_kernel, dim3(blocks), dim3(256), 0, st, a);
     if ((e = cudaEventRecord(pub_ev, st)) != cudaSuccess) return e;
     if ((e = cudaStreamWaitEvent(pub_st, pub_ev, 0)) != cudaSuccess) return e;
     qmv_publish_kernel<<<blocks, 256, 0, pub_st>>>(a);

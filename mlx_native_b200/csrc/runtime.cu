@@ -1112,10 +1112,9 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
             uint8_t *scratch = nullptr;
             if ((rc = encoder_scratch(enc, qmv_tc_scratch_bytes(a), &scratch))) return rc;
             int launches = 0;
-            CUDA_TRY(launch_qmv_tc((int)p->ggml_type, a, scratch, enc->status_dev + 64, dev->sm_count, enc->stream, enc->aux,
-                                   enc->ev_aux, &launches),
+            CUDA_TRY(launch_qmv_tc((int)p->ggml_type, a, scratch, enc->status_dev + 64, dev->sm_count, enc->stream, nullptr,
+                                   nullptr, &launches),
                      "mat-vec launch");
-            if (a.n_peer) enc->aux_busy = true;
             g_launches.fetch_add((uint64_t)launches);
             g_last_kernel = "qmv_tc";
             continue;
