@@ -207,8 +207,7 @@ __global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *x
 // =================================================================================================
 // qmm_tc
 // =================================================================================================
-constexpr int kTcDequantWarps = 16;  // two sets of 8: set s dequantises the K chunks with kc % 2 == s
-constexpr int kTcSetWarps = 8;
+constexpr int kTcDequantWarps = 16;  // two sets of 8: set s dequantises the K stages with st % 2 == s
 constexpr int kTcThreads = (kTcDequantWarps + 2) * 32;  // + producer warp + MMA warp
 constexpr int kTcRowsW = 128;                           // weight rows per tile (UMMA M)
 
@@ -232,82 +231,8 @@ __device__ __forceinline__ int lds_s8s(uint32_t addr) {
     asm volatile("{ .reg .s16 t; ld.shared.s8 t, [%1]; cvt.s32.s16 %0, t; }" : "=r"(v) : "r"(addr));
     return v;
 }
-// two logical 32-bit words at a 2-byte-aligned shared address
-__device__ __forceinline__ void lds_words2(uint32_t addr, uint32_t &w0, uint32_t &w1) {
-    const uint32_t al = addr & ~3u, sh = (addr & 2u) * 8u;
-    const uint32_t a = lds32s(al), b = lds32s(al + 4), c = lds32s(al + 8);
-    w0 = __funnelshift_rc(a, b, sh);
-    w1 = __funnelshift_rc(b, c, sh);
-}
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
-
-// Eight consecutive elements [e, e+8) of one weight row segment in shared memory -> eight f16 values
-// (exact product rounded once to nearest even, as the upstream f32-then-cast staging does).
-template <int T> __device__ __forceinline__ uint4 dequant8(uint32_t seg, uint32_t e) {
-    uint4 out;
-    if constexpr (T == GT_Q4_0) {
-        const uint32_t o = seg + 18u * (e >> 5);
-        const uint32_t c8 = (e & 31u) >> 3;
-        const __half dh = __ushort_as_half((unsigned short)lds16s(o));
-        const __half2 d2 = __half2half2(dh);
-        uint32_t w0, w1;
-        lds_words2(o + 2 + 8 * (c8 & 1u), w0, w1);
-        if (c8 & 2u) {
-            w0 >>= 4;
-            w1 >>= 4;
-        }
-        w0 &= 0x0F0F0F0Fu;
-        w1 &= 0x0F0F0F0Fu;
-        const __half2 off = __float2half2_rn(1032.0f);  // 1024 + 8
-        out.x = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w0, 0x64646464u, 0x4140)), off), d2));
-        out.y = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w0, 0x64646464u, 0x4342)), off), d2));
-        out.z = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w1, 0x64646464u, 0x4140)), off), d2));
-        out.w = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w1, 0x64646464u, 0x4342)), off), d2));
-    } else if constexpr (T == GT_Q8_0) {
-        const uint32_t o = seg + 34u * (e >> 5);
-        const __half dh = __ushort_as_half((unsigned short)lds16s(o));
-        const __half2 d2 = __half2half2(dh);
-        uint32_t w0, w1;
-        lds_words2(o + 2 + (e & 31u), w0, w1);
-        w0 ^= 0x80808080u;
-        w1 ^= 0x80808080u;
-        const __half2 off = __float2half2_rn(1152.0f);  // 1024 + 128
-        out.x = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w0, 0x64646464u, 0x4140)), off), d2));
-        out.y = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w0, 0x64646464u, 0x4342)), off), d2));
-        out.z = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w1, 0x64646464u, 0x4140)), off), d2));
-        out.w = h2_as_u32(__hmul2(__hsub2(u32_as_h2(__byte_perm(w1, 0x64646464u, 0x4342)), off), d2));
-    } else {
-        const uint32_t o = seg + 210u * (e >> 8);
-        const uint32_t r = e & 255u, h = r >> 7, g = (r & 127u) >> 5, l = r & 31u;
-        uint32_t a0, a1, h0, h1;
-        lds_words2(o + 64 * h + 32 * (g & 1u) + l, a0, a1);
-        lds_words2(o + 128 + 32 * h + l, h0, h1);
-        if (g & 2u) {
-            a0 >>= 4;
-            a1 >>= 4;
-        }
-        const uint32_t u0 = (a0 & 0x0F0F0F0Fu) | (((h0 >> (2 * g)) & 0x03030303u) << 4);
-        const uint32_t u1 = (a1 & 0x0F0F0F0Fu) | (((h1 >> (2 * g)) & 0x03030303u) << 4);
-        const float ds = half_bits_to_float(lds16s(o + 208)) * (float)lds_s8s(o + 192 + 8 * h + (l >> 4) + 2 * g);
-        const float c = -160.0f * ds;  // exact: ds has <= 18 significant bits
-        // 128 + u spliced into an f32 mantissa; fma(128+u, ds, -160 ds) = ds*(u-32) exactly
-        const float f0 = fmaf(__uint_as_float(__byte_perm(u0, 0x43000000u, 0x7044)), ds, c);
-        const float f1 = fmaf(__uint_as_float(__byte_perm(u0, 0x43000000u, 0x7144)), ds, c);
-        const float f2 = fmaf(__uint_as_float(__byte_perm(u0, 0x43000000u, 0x7244)), ds, c);
-        const float f3 = fmaf(__uint_as_float(__byte_perm(u0, 0x43000000u, 0x7344)), ds, c);
-        const float f4 = fmaf(__uint_as_float(__byte_perm(u1, 0x43000000u, 0x7044)), ds, c);
-        const float f5 = fmaf(__uint_as_float(__byte_perm(u1, 0x43000000u, 0x7144)), ds, c);
-        const float f6 = fmaf(__uint_as_float(__byte_perm(u1, 0x43000000u, 0x7244)), ds, c);
-        const float f7 = fmaf(__uint_as_float(__byte_perm(u1, 0x43000000u, 0x7344)), ds, c);
-        out.x = h2_as_u32(__floats2half2_rn(f0, f1));
-        out.y = h2_as_u32(__floats2half2_rn(f2, f3));
-        out.z = h2_as_u32(__floats2half2_rn(f4, f5));
-        out.w = h2_as_u32(__floats2half2_rn(f6, f7));
-    }
-    return out;
-}
-
 
 // NWORDS logical 32-bit words at a 2-byte-aligned shared address
 template <int NWORDS> __device__ __forceinline__ void lds_words_n(uint32_t addr, uint32_t (&out)[NWORDS]) {
@@ -537,7 +462,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     // tensor-core operand tiles need 1024-byte alignment (128-byte swizzle atoms): align by hand
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES, KR = TcTraits<T>::KR;
-    constexpr int SPR = KR / 128;    // tensor-memory stages per raw stage
     constexpr int kMaxB = 6, kMaxRaw = 6;
     __shared__ __align__(8) uint64_t a_full[kTcAStages], stage_done[kTcAStages], b_full[kMaxB];
     __shared__ __align__(8) uint64_t raw_full[kMaxRaw], raw_empty[kMaxRaw], acc_full;

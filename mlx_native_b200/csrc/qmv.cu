@@ -145,7 +145,6 @@ __global__ void __launch_bounds__(256) qmv_simple_kernel(const QmvArgs a) {
 // =================================================================================================
 // qmv_stream
 // =================================================================================================
-constexpr int kMaxWarps = 16;     // warps per CTA: 16 where the register budget allows (m <= 2), else 8
 constexpr int kRows = 4;         // weight rows per pipeline stage
 constexpr int kMaxStages = 16;
 

@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(128) qmv_tc_pack_kernel(const QmvArgs a, int g
     const uint32_t ncta = gridDim.x * gridDim.y, cta = blockIdx.y * gridDim.x + blockIdx.x;
     const uint32_t total = m * n, per = (total + ncta - 1) / ncta;
     const uint32_t lo = min(total, cta * per), hi = min(total, lo + per);
-    if (!(debug & 256u)) {
+    {
         const uint32_t ld = qmv_ld(a);
         for (uint32_t i = lo + tid; i < hi; i += blockDim.x) {
             const uint32_t t = i / n, col = i - t * n;
@@ -328,9 +328,6 @@ __global__ void __launch_bounds__(kVtThreads, 1)
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t grid = gridDim.x, cta = blockIdx.x;
-    const long long t_entry = clock64();
-    long long *ktr = reinterpret_cast<long long *>(a.y) + 2048;  // experiment: kernel-level timeline of CTA 0 / warp 0
-    const bool ktrace = (c.debug & 256u) && cta == 0 && tid == 0;
     const uint32_t u0 = vt_range_begin(cta, c.total_units, grid), u1 = vt_range_begin(cta + 1, c.total_units, grid);
     const uint32_t row_bytes = (a.k / BlockTraits<T>::QK) * BlockTraits<T>::BYTES;
 
@@ -369,7 +366,6 @@ __global__ void __launch_bounds__(kVtThreads, 1)
     const uint32_t tmem = tmem_base_s;
     const uint32_t smem_base = smem_u32(smem);
     allow_dependents();  // the next overlapped launch in the stream (its blocks wait for this grid before reading anything)
-    if (ktrace) { ktr[0] = t_entry; ktr[1] = clock64(); }
     const uint32_t wspin = 0xFFFFFFFFu;   // producer / MMA warps poll back to back
     const uint32_t wdq = (c.debug & 16u) ? 0xFFFFFFFFu : ((c.debug & 32u) ? 20u : 0u);  // convert warps: suspend / spin / short sleeps
 
@@ -422,14 +418,10 @@ __global__ void __launch_bounds__(kVtThreads, 1)
 #pragma unroll
                         for (uint32_t h = 0; h < 2; h++) {
                             const uint32_t g = w2 + 2 * h, sl = 2 * g + p;
-                            const bool tr = (c.debug & 256u) && cta == 0 && w2 == 0 && uc < 40;
-                            long long *tp = reinterpret_cast<long long *>(a.y) + 8 * (2 * uc + h);
-                            if (tr) tp[0] = clock64();
                             if (!mbar_wait(&a_full[sl], par, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wspin)) {
                                 ok = false;
                                 break;
                             }
-                            if (tr) tp[1] = clock64();
                             tc_fence_after();
                             const uint32_t acol = tmem + sl * kVtSlotCols, dcol = acol + 32;
                             if (!(c.debug & 4u)) {
@@ -448,7 +440,6 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                                 }
                             }
                             umma_commit(&d_full[sl]);
-                            if (tr) tp[2] = clock64();
                         }
                         if (!ok) break;
                     }
@@ -462,7 +453,6 @@ __global__ void __launch_bounds__(kVtThreads, 1)
         // Thread (warp w, lane l): group g = w / 4 owns sub-step g (64 K) of every K unit; the thread owns
         // weight row 32 (w % 4) + l of the tile, which is also the tensor-memory lane its warp may address.
         grid_dependency_wait();
-        if (ktrace) ktr[2] = clock64();
         const uint32_t q4 = warp & 3u, g = warp >> 2;
         const uint32_t row = q4 * 32 + lane;
         const uint32_t lane_base = tmem + ((q4 * 32) << 16);
@@ -537,14 +527,14 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                 const size_t ycol = (size_t)a.y_col0 + grow;
                 const uint32_t ld = qmv_ld(a);
                 if (full) {
-                    if (grow < a.n && !(c.debug & 256u))
+                    if (grow < a.n)
 #pragma unroll
                         for (int i = 0; i < 2 * MP; i++)
                             if ((uint32_t)i < a.m) {
                                 a.y[(size_t)i * ld + ycol] = tot[i];
                                 for (uint32_t pr = 0; pr < a.n_peer; pr++) a.y_peer[pr][(size_t)i * ld + ycol] = tot[i];
                             }
-                } else if (grow < a.n && !(c.debug & 256u)) {
+                } else if (grow < a.n) {
                     // the tile's K range is shared with other CTAs: add into the rows the packing kernel zeroed
 #pragma unroll
                     for (int i = 0; i < 2 * MP; i++)
@@ -574,7 +564,6 @@ __global__ void __launch_bounds__(kVtThreads, 1)
         for (st.init(u0, u1, c.upt, c.cu, c.nslots); ok && !st.done(); st.next()) {
             const uint32_t slot = st.slot;
             if (!mbar_wait(&raw_full[slot], st.ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wdq)) break;
-            if (ktrace && st.sidx == 0) ktr[3] = clock64();
             if (st.kun == 0 || st.sidx == 0) seg_ka = st.kun;
             const uint32_t sl_base = smem_base + slot * c.slot_bytes;
             for (uint32_t ul = 0; ok && ul < st.cnt; ul++) {
@@ -582,30 +571,22 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                 for (uint32_t n = 0; n < (uint32_t)SS; n++, uc++) {   // uc counts this group's sub-steps
                     if (!ok) break;
                     const uint32_t p = uc & 1u, sl = 2 * g + p;
-                    const bool tr = (c.debug & 256u) && cta == 0 && warp == 0 && lane == 0 && uc < 40;
-                    long long *tp = reinterpret_cast<long long *>(a.y) + 1024 + 8 * uc;
-                    if (tr) tp[0] = clock64();
                     float d0, d1;
                     // the slot's previous contents were consumed: its accumulators were read back two sub-steps ago
                     if constexpr (T == GT_Q6_K) {
                         uint32_t r[16];
                         vt_extract_q6k_p((st.kun + ul) & 7u, sl_base + c.raw_off + row * c.row_stride, n, g, r, d0, d1);
-                        if (tr) tp[1] = clock64();
                         tmem_st_32x32_x16(lane_base + sl * kVtSlotCols, r);
                     } else {
                         uint32_t r[32];
                         vt_extract_g<T>(g, sl_base + c.raw_off + row * c.row_stride + ul * UB, r, d0, d1);
-                        if (tr) tp[1] = clock64();
                         tmem_st_32x32_x32(lane_base + sl * kVtSlotCols, r);
                     }
                     tmem_st_wait();
-                    if (tr) tp[2] = clock64();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&a_full[sl]);
-                    if (tr) tp[3] = clock64();
                     if (pv) retire_prev();
-                    if (tr) tp[4] = clock64();
                     pv = true;
                     pv_sl = sl;
                     pv_par = (uc >> 1) & 1u;
@@ -624,16 +605,13 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                 }
             }
         }
-        if (ktrace) ktr[4] = clock64();
         if (ok && pv) retire_prev();
-        if (ktrace) ktr[5] = clock64();
     }
     if (abort_flag) {  // let copies in flight land before the CTA's shared memory is released
         for (int i = 0; i < 200; i++) __nanosleep(5000);
     }
     tc_fence_before();
     __syncthreads();
-    if (ktrace) ktr[6] = clock64();
     if (warp == kVtCvtWarps + 1) {
         tc_fence_after();
         tmem_dealloc(tmem, kVtTmemCols);
