@@ -263,10 +263,10 @@ int mlxn_quantized_matmul_ggml_sharded(mlxn_encoder *enc, mlxn_registry *reg, ml
                                        uint32_t n_total, uint32_t col0, void *const *peer_outputs, uint32_t n_peers);
 
 /* ---- tuning and introspection (no upstream counterpart) -------------------------------------- */
-/* Selects kernel variants for experiments: key/value pairs "qmv=auto|tc|stream|simple" (auto: the tensor-core
- * mat-vec from three activation rows up, the streaming SIMT kernel below; tc forces the tensor-core kernel
- * wherever it applies) and "qmm=tc|simt".  Unknown keys are MLXN_INVALID_ARGUMENT.  The defaults (auto, tc)
- * are the fast paths. */
+/* Selects kernel variants for experiments: key/value pairs "qmv=auto|tc|stream|simple" (auto and tc: the
+ * tensor-core mat-vec wherever it applies, the streaming SIMT kernel elsewhere; stream / simple force the SIMT
+ * kernels, whose results are bit-reproducible) and "qmm=tc|simt".  Unknown keys are MLXN_INVALID_ARGUMENT.  The
+ * defaults (auto, tc) are the fast paths. */
 int mlxn_set_option(const char *key, const char *value);
 /* Name of the kernel variant the last operation on this thread launched (for tests and profiles). */
 const char *mlxn_last_kernel_name(void);

@@ -366,7 +366,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
     const uint32_t tmem = tmem_base_s;
     const uint32_t smem_base = smem_u32(smem);
     allow_dependents();  // the next overlapped launch in the stream (its blocks wait for this grid before reading anything)
-    const uint32_t wspin = 0xFFFFFFFFu;   // producer / MMA warps poll back to back
+    const uint32_t wspin = (c.debug & 64u) ? 0u : ((c.debug & 128u) ? 40u : 0xFFFFFFFFu);   // MMA warps poll back to back (experiments: suspend / sleep)
     const uint32_t wdq = (c.debug & 16u) ? 0xFFFFFFFFu : ((c.debug & 32u) ? 20u : 0u);  // convert warps: suspend / spin / short sleeps
 
     if (warp == kVtCvtWarps) {
