@@ -159,8 +159,13 @@ __global__ void build_tiles_kernel(const uint32_t *htpe, uint32_t n_experts, uin
 // (r/8)*1024 + (r%8)*128 + ((j ^ (r%8)) * 16).  Tile (t, kc) starts at ((t*nchunks + kc) * NT*128) bytes.
 // grid (nchunks, ntile_bound); 256 threads.
 template <int NT>
-__global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *xpack, uint32_t nchunks) {
+__global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *xpack, uint32_t nchunks, uint32_t zero_y) {
     const uint32_t kc = blockIdx.x, t = blockIdx.y;
+    if (zero_y) {  // split-K tiles add their halves into y with atomics (dense form only)
+        const size_t total = (size_t)a.m * a.n, ncta = (size_t)gridDim.x * gridDim.y, cta = (size_t)t * gridDim.x + kc;
+        const size_t per = (total + ncta - 1) / ncta, lo = cta * per, hi = lo + per < total ? lo + per : total;
+        for (size_t i = lo + threadIdx.x; i < hi; i += 256) a.y[i] = 0.f;
+    }
     uint32_t e = 0, mt = t, nrows = a.m;
     if (a.hids) {
         if (t >= a.tiles[0]) return;
@@ -520,9 +525,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     const uint32_t tmem_d = tmem_base_s;
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t b_bytes = NT * 128;                 // one 64-wide K chunk of the activation tile
-    const uint32_t nst = (a.k + 127) / 128;            // tensor-memory stages over K
     const uint32_t raw_stage_bytes = kTcRowsW * c.seg_stride;
-    const uint32_t nraw = (a.k + KR - 1) / KR;
+    // Split-K (gridDim.z = 2 when the tile grid alone would leave half of the SMs idle): this CTA takes the raw
+    // stages [r_lo, r_hi) of K and adds its part of the tile into y.  Everything below counts stages and chunks
+    // relative to r_lo; absolute positions are only needed for addresses.
+    const uint32_t nraw_all = (a.k + KR - 1) / KR;
+    const uint32_t r_lo = (uint32_t)(((uint64_t)blockIdx.z * nraw_all) / gridDim.z);
+    const uint32_t r_hi = (uint32_t)(((uint64_t)(blockIdx.z + 1) * nraw_all) / gridDim.z);
+    const uint32_t nraw = r_hi - r_lo;
+    const uint32_t st_lo = r_lo * (KR / 128), kc_lo = r_lo * (KR / 64);
+    const uint32_t nst = min((a.k + 127) / 128, r_hi * (KR / 128)) - st_lo;   // tensor-memory stages of this CTA
+    const uint32_t nck = min(c.nchunks, r_hi * (KR / 64)) - kc_lo;            // 64-wide chunks of this CTA
     // wait styles: the single producer / MMA warps spin (they are the critical path and cost one warp's issue
     // slots); the dequantising warps space their polls out
     const uint32_t wmode_cr = (c.debug & 32u) ? 0u : 0xFFFFFFFFu;
@@ -535,7 +548,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         // warps wait on before they overwrite the stage's weights in tensor memory).
         if (lane == 0) {
             uint32_t s = 0;
-            for (uint32_t kc = 0; kc < c.nchunks; kc++) {
+            for (uint32_t kc = 0; kc < nck; kc++) {
                 if (kc >= c.b_stages) {
                     const uint32_t j = (kc - c.b_stages) >> 1;
                     if (!mbar_wait(&stage_done[j & (kTcAStages - 1)], (j / kTcAStages) & 1u, &abort_flag, a.status,
@@ -546,7 +559,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                     mbar_arrive(&b_full[s]);
                 } else {
                     mbar_expect_tx(&b_full[s], b_bytes);
-                    bulk_g2s(smem + c.b_off + s * b_bytes, xpack + ((size_t)tt * c.nchunks + kc) * (size_t)b_bytes, b_bytes,
+                    bulk_g2s(smem + c.b_off + s * b_bytes, xpack + ((size_t)tt * c.nchunks + kc_lo + kc) * (size_t)b_bytes, b_bytes,
                              &b_full[s]);
                 }
                 if (++s == c.b_stages) s = 0;
@@ -576,7 +589,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                 }
                 bd += b_step;
                 if (++sb == c.b_stages) { sb = 0; bph ^= 1u; bd = bd0; }
-                if (++kc < c.nchunks) {
+                if (++kc < nck) {
                     if (!mbar_wait(&b_full[sb], bph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
                     if (do_mma) {
                         umma_f16_ts(tmem_d, a_col + 32, bd, idesc, 1u);
@@ -650,7 +663,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         uint32_t islot = 0, iph = 0;   // slot / use-parity of the next stage to request
         uint32_t rnext = 0;
         for (; rnext < min(D, nraw); rnext++) {
-            issue_raw(rnext, islot);
+            issue_raw(r_lo + rnext, islot);
             if (++islot == R) { islot = 0; iph ^= 1u; }
         }
         uint32_t rs = 0, rph = 0;      // slot / parity of the raw stage being read
@@ -659,7 +672,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             if (rnext < nraw) {
                 // the slot's previous tenant (stage rnext - R) must have been released by every warp
                 if (!mbar_wait(&raw_empty[islot], iph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) break;
-                issue_raw(rnext, islot);
+                issue_raw(r_lo + rnext, islot);
                 rnext++;
                 if (++islot == R) { islot = 0; iph ^= 1u; }
             }
@@ -673,14 +686,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                                wmode_dq))
                     break;
                 tc_fence_after();
-                const uint32_t pre = (row_lo4 + ((r * KR) / QK) * BB) & 15u;
+                const uint32_t r_abs = r_lo + r;
+                const uint32_t pre = (row_lo4 + ((r_abs * KR) / QK) * BB) & 15u;
                 const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
                 uint32_t regs[32];
                 if (c.aligned && row_ok && !(c.debug & 1u)) {
                     const uint32_t stage_row = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride;
                     if constexpr (T == GT_Q6_K) {
-                        dequant32_q6k_aligned_p(r & 7u, stage_row, set, 2 * half, regs);
-                        dequant32_q6k_aligned_p(r & 7u, stage_row, set, 2 * half + 1, regs + 16);
+                        dequant32_q6k_aligned_p(r_abs & 7u, stage_row, set, 2 * half, regs);
+                        dequant32_q6k_aligned_p(r_abs & 7u, stage_row, set, 2 * half + 1, regs + 16);
                     } else {
                         switch (2 * set + half) {  // uniform per warp
                         case 0: dequant64_aligned<T, 0>(stage_row, regs); break;
@@ -694,7 +708,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                     for (uint32_t hh = 0; hh < 2; hh++) {
                         uint4 v[4];
                         const uint32_t e0 = 128 * set + 64 * half + 32 * hh;  // element offset inside the raw stage
-                        if (row_ok && r * KR + e0 < a.k && !(c.debug & 1u)) {
+                        if (row_ok && r_abs * KR + e0 < a.k && !(c.debug & 1u)) {
                             dequant32<T>(seg, e0, v);
                         } else {
 #pragma unroll
@@ -733,7 +747,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int32_t o = orow[col + j];
-                        if (o >= 0) a.y[(size_t)o * a.n + wrow] = __uint_as_float(v[j]);
+                        if (o >= 0) {
+                            if (gridDim.z > 1) atomicAdd(&a.y[(size_t)o * a.n + wrow], __uint_as_float(v[j]));
+                            else a.y[(size_t)o * a.n + wrow] = __uint_as_float(v[j]);
+                        }
                     }
                 }
             }
@@ -754,6 +771,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
 // host-side launchers
 // =================================================================================================
 static inline uint32_t round_up_u(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+static int sm_count_of_device() {
+    static int sms[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return 148;
+    if (!sms[dev]) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    return sms[dev] ? sms[dev] : 148;
+}
 
 // Bytes of scratch the tcgen05 path needs for one call (tile list + packed activations).
 size_t qmm_tc_scratch_bytes(const QmmArgs &a, uint32_t nt, bool routed) {
@@ -774,6 +799,14 @@ size_t qmm_tc_scratch_bytes(const QmmArgs &a, uint32_t nt, bool routed) {
 // Activation rows per tile.  Routed calls use 64 (few rows per expert).  Dense calls take the tile that
 // minimises waves x per-tile cost, where a tile costs about max(NT, 160) (tensor time vs the fixed
 // dequantisation of its 128 weight rows); ties go to the larger tile, which dequantises less in total.
+// Split-K factor for a dense call: 2 when the tile grid alone would fill at most ~half of the SMs and K is long
+// enough to share (two halves added onto a zeroed y give the same sum in either order).
+uint32_t qmm_tc_ksplit(uint32_t nt, uint32_t rows, uint32_t n, uint32_t k, int sm_count, bool routed) {
+    if (routed || getenv("MLXN_TC_NO_SPLITK")) return 1;
+    const uint64_t tiles = (uint64_t)((n + kTcRowsW - 1) / kTcRowsW) * ((rows + nt - 1) / nt);
+    return (tiles * 2 <= (uint64_t)sm_count + sm_count / 8 && k >= 2048) ? 2u : 1u;
+}
+
 uint32_t qmm_tc_pick_nt(int ggml_type, uint32_t rows, uint32_t n, int sm_count, bool routed) {
     if (routed || rows <= 64) return 64;
     (void)ggml_type;
@@ -785,9 +818,11 @@ uint32_t qmm_tc_pick_nt(int ggml_type, uint32_t rows, uint32_t n, int sm_count, 
     for (uint32_t nt : cands) {
         if (nt > cap) continue;
         if (nt / 2 >= rows && nt > 64) continue;  // more than half of the tile would be padding
-        const uint64_t tiles = (uint64_t)wt * ((rows + nt - 1) / nt);
+        // (K is not known here: assume it is long enough to split when the grid is small)
+        const uint64_t ks = qmm_tc_ksplit(nt, rows, n, 4096, sm_count, false);
+        const uint64_t tiles = (uint64_t)wt * ((rows + nt - 1) / nt) * ks;
         const uint64_t waves = (tiles + sm_count - 1) / (uint64_t)sm_count;
-        const uint64_t cost = waves * (nt > 160 ? nt : 160);
+        const uint64_t cost = waves * (nt > 160 ? nt : 160) / ks;
         if (cost < best_cost) {
             best_cost = cost;
             best = nt;
@@ -842,6 +877,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     c.raw_off = b_stages * b_bytes;
     const size_t smem = (size_t)c.raw_off + raw_bytes + 1024;  // + slack for manual 1024-byte alignment
 
+    const uint32_t ksplit = qmm_tc_ksplit(NT, a.m, a.n, a.k, sm_count_of_device(), routed);
     size_t tiles;
     uint8_t *xpack = scratch;
     if (routed) {
@@ -860,7 +896,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     }
     {
         dim3 grid(c.nchunks, (unsigned)tiles);
-        pack_x_kernel<NT><<<grid, 256, 0, st>>>(a, xpack, c.nchunks);
+        pack_x_kernel<NT><<<grid, 256, 0, st>>>(a, xpack, c.nchunks, ksplit > 1 ? 1u : 0u);
         (*launches)++;
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
@@ -874,7 +910,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
         if (e != cudaSuccess) return e;
         attr_smem[dev] = smem;
     }
-    dim3 grid((a.n + kTcRowsW - 1) / kTcRowsW, (unsigned)tiles);
+    dim3 grid((a.n + kTcRowsW - 1) / kTcRowsW, (unsigned)tiles, ksplit);
     qmm_tc_kernel<T, NT><<<grid, kTcThreads, smem, st>>>(a, c, xpack);
     (*launches)++;
     return cudaGetLastError();
