@@ -103,16 +103,16 @@ class ClockSampler:
 
 
 def make_weights(t_names, shapes, seed=0):
-    """One seeded N(0, 0.02) weight set per (type, shape), quantized on the host."""
-    from oracle import oracle as orc  # host-side quantizer for synthetic data; not on the measured path
+    """One seeded N(0, 0.02) weight set per (type, shape), packed into GGML blocks on the host."""
+    from mlx_native_b200 import ggml_pack as gp
 
-    otype = {"Q4_0": orc.Q4_0, "Q8_0": orc.Q8_0, "Q6_K": orc.Q6_K}
+    otype = {"Q4_0": gp.Q4_0, "Q8_0": gp.Q8_0, "Q6_K": gp.Q6_K}
     out = {}
     rng = np.random.default_rng(seed)
     for (n, k) in shapes:
         wf = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
         for t in t_names:
-            out[(t, n, k)] = orc.quantize(otype[t], wf, rule="ggml")
+            out[(t, n, k)] = gp.pack(otype[t], wf)
     return out
 
 
@@ -458,11 +458,11 @@ def cpu_baseline():
 def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
     """Secondary figures: prefill mat-mat TFLOP/s (Q4_0 and Q6_K, m=512 and 2048, 4096x4096) and
     MoE expert-routed tokens/s (128 experts, top-8, hidden 2048, ffn 768, m=512 and m=1)."""
-    from oracle import oracle as orc
+    from mlx_native_b200 import ggml_pack as gp
 
     out = {}
     rng = np.random.default_rng(3)
-    otype = {"Q4_0": orc.Q4_0, "Q6_K": orc.Q6_K}
+    otype = {"Q4_0": gp.Q4_0, "Q6_K": gp.Q6_K}
     gt = {"Q4_0": mx.GgmlType.Q4_0, "Q6_K": mx.GgmlType.Q6_K}
 
     def timed(fn, reps=10, warm=3, inner=4):
@@ -488,7 +488,7 @@ def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
     for (n, k, ms) in ((4096, 4096, (512, 2048)), (12288, 4096, (2048,)), (4096, 12288, (2048,))):
         wf = (rng.standard_normal((512, k), dtype=np.float32) * np.float32(0.02))
         for t in ("Q4_0", "Q6_K"):
-            wq = np.tile(orc.quantize(otype[t], wf, rule="ggml"), n // 512)   # timing does not depend on the values
+            wq = np.tile(gp.pack(otype[t], wf), n // 512)   # timing does not depend on the values
             wb = dev.alloc_buffer(wq.size, mx.DType.U8)
             wb.upload(wq)
             for m in ms:
@@ -505,8 +505,8 @@ def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
 
     # MoE FFN: gate + up (Q4_0 [768 x 2048] per expert), down (Q6_K [2048 x 768] per expert)
     E, top_k, hidden, ffn = 128, 8, 2048, 768
-    w1 = orc.quantize(orc.Q4_0, (rng.standard_normal((ffn, hidden), dtype=np.float32) * np.float32(0.02)), rule="ggml")
-    w2 = orc.quantize(orc.Q6_K, (rng.standard_normal((hidden, ffn), dtype=np.float32) * np.float32(0.02)))
+    w1 = gp.pack(gp.Q4_0, (rng.standard_normal((ffn, hidden), dtype=np.float32) * np.float32(0.02)))
+    w2 = gp.pack(gp.Q6_K, (rng.standard_normal((hidden, ffn), dtype=np.float32) * np.float32(0.02)))
     wg = dev.alloc_buffer(w1.size * E, mx.DType.U8)
     wu = dev.alloc_buffer(w1.size * E, mx.DType.U8)
     wd = dev.alloc_buffer(w2.size * E, mx.DType.U8)

@@ -10,33 +10,66 @@
 
 namespace mlxn {
 
-// One warp per expert.  The warp walks the tokens 32 at a time; each lane evaluates the upstream
-// selector for its token (sum of (slot+1) over slots whose id, truncated to 16 bits, equals the
-// expert), and a ballot + popcount prefix gives every selected token its position, so the list
-// order is the scan order.  grid ceil(n_experts/8), 256 threads.
+// One warp per expert, eight experts per CTA.  The CTA stages the id table through shared memory a chunk of tokens at
+// a time (one coalesced pass, transposed to [slot][token] so that the scan reads without bank conflicts); each warp
+// then walks the chunk 32 tokens at a time: every lane evaluates the upstream selector for its token (sum of
+// (slot+1) over slots whose id, truncated to 16 bits, equals the expert), and a ballot + popcount prefix gives every
+// selected token its position, so the list order is the scan order.  grid ceil(n_experts/8), 256 threads.
+constexpr uint32_t kMap0Entries = 4096;   // id entries staged per chunk (16 KB + padding)
 __global__ void __launch_bounds__(256) moe_map0_kernel(const uint32_t *ids, uint32_t n_tokens, uint32_t top_k,
                                                        uint32_t n_experts, uint32_t hids_stride, uint32_t *htpe,
                                                        int32_t *hids) {
+    __shared__ uint16_t stage[kMap0Entries + 2 * 64 + 64];
     const uint32_t lane = threadIdx.x & 31;
     const uint32_t e = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (e >= n_experts) return;
-    int32_t *row = hids + (size_t)e * hids_stride;
+    const bool live = e < n_experts;
+    int32_t *row = hids + (size_t)(live ? e : 0) * hids_stride;
+    // tokens per chunk: a multiple of 32, at least 32 (top_k <= 64 keeps a chunk of 32 tokens within the stage)
+    uint32_t chunk = (kMap0Entries / top_k) & ~31u;
+    if (chunk < 32) chunk = 32;
+    const uint32_t pitch = chunk + 2;   // 16-bit entries: +2 moves each slot's row by one 32-bit bank
     uint32_t n_all = 0;
-    for (uint32_t t0 = 0; t0 < n_tokens; t0 += 32) {
-        const uint32_t t = t0 + lane;
-        int sel = 0;
-        if (t < n_tokens) {
-            const uint32_t *p = ids + (size_t)t * top_k;
-            for (uint32_t s = 0; s < top_k; s++) sel += ((p[s] & 0xFFFFu) == (e & 0xFFFFu)) ? (int)(s + 1) : 0;
+    if (top_k > 64) {   // a chunk of 32 tokens would not fit the stage: scan the table in place
+        if (!live) return;
+        for (uint32_t t0 = 0; t0 < n_tokens; t0 += 32) {
+            const uint32_t t = t0 + lane;
+            int sel = 0;
+            if (t < n_tokens)
+                for (uint32_t sl = 0; sl < top_k; sl++)
+                    sel += ((ids[(size_t)t * top_k + sl] & 0xFFFFu) == (e & 0xFFFFu)) ? (int)(sl + 1) : 0;
+            const uint32_t hit = __ballot_sync(0xffffffffu, sel > 0);
+            if (sel > 0) {
+                const uint32_t pos = n_all + __popc(hit & ((1u << lane) - 1u));
+                if (pos < hids_stride) row[pos] = (int32_t)(t * top_k) + sel - 1;
+            }
+            n_all += __popc(hit);
         }
-        const uint32_t hit = __ballot_sync(0xffffffffu, sel > 0);
-        if (sel > 0) {
-            const uint32_t pos = n_all + __popc(hit & ((1u << lane) - 1u));
-            if (pos < hids_stride) row[pos] = (int32_t)(t * top_k) + sel - 1;
-        }
-        n_all += __popc(hit);
+        if (lane == 0) htpe[e] = n_all;
+        return;
     }
-    if (lane == 0) htpe[e] = n_all;
+    for (uint32_t c0 = 0; c0 < n_tokens; c0 += chunk) {
+        const uint32_t ct = min(chunk, n_tokens - c0);
+        __syncthreads();   // the previous chunk has been scanned
+        for (uint32_t i = threadIdx.x; i < ct * top_k; i += 256) {
+            const uint32_t t = i / top_k, sl = i - t * top_k;
+            stage[sl * pitch + t] = (uint16_t)(ids[(size_t)c0 * top_k + i] & 0xFFFFu);
+        }
+        __syncthreads();
+        if (!live) continue;
+        for (uint32_t t0 = 0; t0 < ct; t0 += 32) {
+            const uint32_t t = t0 + lane;
+            int sel = 0;
+            if (t < ct)
+                for (uint32_t sl = 0; sl < top_k; sl++) sel += (stage[sl * pitch + t] == (uint16_t)(e & 0xFFFFu)) ? (int)(sl + 1) : 0;
+            const uint32_t hit = __ballot_sync(0xffffffffu, sel > 0);
+            if (sel > 0) {
+                const uint32_t pos = n_all + __popc(hit & ((1u << lane) - 1u));
+                if (pos < hids_stride) row[pos] = (int32_t)((c0 + t) * top_k) + sel - 1;
+            }
+            n_all += __popc(hit);
+        }
+    }
+    if (live && lane == 0) htpe[e] = n_all;
 }
 
 cudaError_t launch_moe_map0(const uint32_t *ids, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts,
@@ -47,7 +80,7 @@ cudaError_t launch_moe_map0(const uint32_t *ids, uint32_t n_tokens, uint32_t top
 
 // One CTA of tg = min(n_experts, 128) threads per token, same reduction trees as upstream so that
 // the probabilities (and therefore the selected ids) match its arithmetic.
-// dynamic shared memory: (2*tg + n_experts) floats.
+// dynamic shared memory: (2*tg + n_experts + 128) words.
 __global__ void moe_softmax_topk_kernel(const float *logits, uint32_t n_tokens, uint32_t n_experts, uint32_t top_k,
                                         uint32_t *out_ids, float *out_w) {
     extern __shared__ float sh[];
@@ -80,41 +113,69 @@ __global__ void moe_softmax_topk_kernel(const float *logits, uint32_t n_tokens, 
         __syncthreads();
     }
     const float gsum = tg_sum[0];
-    for (uint32_t e = tid; e < n_experts; e += tg) prob[e] = prob[e] / gsum;
-    __syncthreads();
-    if (tid == 0) {
-        float vals[64];
-        uint32_t idxs[64];
-        for (uint32_t k = 0; k < top_k; k++) {
-            vals[k] = -INFINITY;
-            idxs[k] = 0;
-        }
-        for (uint32_t e = 0; e < n_experts; e++) {
-            const float p = prob[e];
-            if (p <= vals[top_k - 1]) continue;
-            uint32_t ins = top_k - 1;
-            while (ins > 0 && p > vals[ins - 1]) ins--;
-            for (uint32_t k = top_k - 1; k > ins; k--) {
-                vals[k] = vals[k - 1];
-                idxs[k] = idxs[k - 1];
+    bool any_nan = false;
+    for (uint32_t e = tid; e < n_experts; e += tg) {
+        const float p = prob[e] / gsum;
+        prob[e] = p;
+        any_nan |= p != p;
+    }
+    // Selection.  Upstream keeps a sorted top-k list in one thread (insertion with strict comparisons: of two equal
+    // probabilities the lower expert index comes first).  The same list falls out of ranking every expert against
+    // all others in parallel: rank(e) = #{j : p_j > p_e, or p_j == p_e and j < e}; rank < top_k is its slot.
+    float *top_v = prob + n_experts;            // top_k <= 64 slots each
+    uint32_t *top_i = reinterpret_cast<uint32_t *>(prob + n_experts + 64);
+    if (__syncthreads_or(any_nan)) {
+        // NaN probabilities have no order; keep the one-thread insertion for that (garbage-in) case
+        if (tid == 0) {
+            for (uint32_t k = 0; k < top_k; k++) {
+                top_v[k] = -INFINITY;
+                top_i[k] = 0;
             }
-            vals[ins] = p;
-            idxs[ins] = e;
+            for (uint32_t e = 0; e < n_experts; e++) {
+                const float p = prob[e];
+                if (p <= top_v[top_k - 1]) continue;
+                uint32_t ins = top_k - 1;
+                while (ins > 0 && p > top_v[ins - 1]) ins--;
+                for (uint32_t k = top_k - 1; k > ins; k--) {
+                    top_v[k] = top_v[k - 1];
+                    top_i[k] = top_i[k - 1];
+                }
+                top_v[ins] = p;
+                top_i[ins] = e;
+            }
         }
-        float ts = 0.0f;
-        for (uint32_t k = 0; k < top_k; k++) ts += vals[k];
-        const float inv = ts > 1e-9f ? 1.0f / ts : 1.0f;
-        for (uint32_t k = 0; k < top_k; k++) {
-            out_ids[(size_t)tok * top_k + k] = idxs[k];
-            out_w[(size_t)tok * top_k + k] = vals[k] * inv;
+    } else {
+        for (uint32_t k = n_experts + tid; k < top_k; k += tg) {  // more slots than experts: the rest stay empty
+            top_v[k] = -INFINITY;
+            top_i[k] = 0;
         }
+        for (uint32_t e = tid; e < n_experts; e += tg) {
+            const float p = prob[e];
+            uint32_t rank = 0;
+            for (uint32_t j = 0; j < n_experts; j++) {
+                const float q = prob[j];
+                rank += (q > p || (q == p && j < e)) ? 1u : 0u;
+            }
+            if (rank < top_k) {
+                top_v[rank] = p;
+                top_i[rank] = e;
+            }
+        }
+    }
+    __syncthreads();
+    float ts = 0.0f;
+    for (uint32_t k = 0; k < top_k; k++) ts += top_v[k];   // slot order, as upstream sums them
+    const float inv = ts > 1e-9f ? 1.0f / ts : 1.0f;
+    for (uint32_t k = tid; k < top_k; k += tg) {
+        out_ids[(size_t)tok * top_k + k] = top_i[k];
+        out_w[(size_t)tok * top_k + k] = top_v[k] * inv;
     }
 }
 
 cudaError_t launch_moe_softmax_topk(const float *logits, uint32_t n_tokens, uint32_t n_experts, uint32_t top_k,
                                     uint32_t *out_ids, float *out_w, cudaStream_t st) {
     const uint32_t tg = n_experts < 128 ? n_experts : 128;
-    const size_t smem = (2 * (size_t)tg + n_experts) * sizeof(float);
+    const size_t smem = (2 * (size_t)tg + n_experts + 128) * sizeof(float);
     moe_softmax_topk_kernel<<<n_tokens, tg, smem, st>>>(logits, n_tokens, n_experts, top_k, out_ids, out_w);
     return cudaGetLastError();
 }

@@ -139,19 +139,38 @@ __global__ void __launch_bounds__(256) qmm_simt_kernel(const QmmArgs a) {
 // routed tile list + activation packing for qmm_tc
 // =================================================================================================
 // Scratch header written by build_tiles: [0] = number of tiles, [1..] = (expert, row-tile) pairs.
-__global__ void build_tiles_kernel(const uint32_t *htpe, uint32_t n_experts, uint32_t nt, uint32_t max_tiles,
-                                   uint32_t *tiles) {
-    if (threadIdx.x != 0 || blockIdx.x != 0) return;
-    uint32_t n = 0;
-    for (uint32_t e = 0; e < n_experts; e++) {
-        const uint32_t cnt = htpe[e];
-        for (uint32_t mt = 0; mt * nt < cnt && n < max_tiles; mt++) {
-            tiles[1 + 2 * n] = e;
-            tiles[2 + 2 * n] = mt;
-            n++;
+// One CTA of 256 threads: thread i takes expert base + i, a block-wide exclusive prefix sum of the experts' tile
+// counts gives each expert its place in the list (experts ascending, row tiles ascending inside an expert).
+__global__ void __launch_bounds__(256) build_tiles_kernel(const uint32_t *htpe, uint32_t n_experts, uint32_t nt,
+                                                          uint32_t max_tiles, uint32_t *tiles) {
+    __shared__ uint32_t warp_tot[8];
+    __shared__ uint32_t carry_s;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    if (tid == 0) carry_s = 0;
+    __syncthreads();
+    for (uint32_t base = 0; base < n_experts; base += 256) {
+        const uint32_t e = base + tid;
+        const uint32_t cnt = e < n_experts ? (htpe[e] + nt - 1) / nt : 0u;
+        uint32_t incl = cnt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t v = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= (uint32_t)d) incl += v;
         }
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        uint32_t before = carry_s;
+        for (uint32_t w = 0; w < warp; w++) before += warp_tot[w];
+        uint32_t pos = before + incl - cnt;
+        for (uint32_t mt = 0; mt < cnt && pos < max_tiles; mt++, pos++) {
+            tiles[1 + 2 * pos] = e;
+            tiles[2 + 2 * pos] = mt;
+        }
+        __syncthreads();
+        if (tid == 255) carry_s = before + incl;
+        __syncthreads();
     }
-    tiles[0] = n;
+    if (tid == 0) tiles[0] = carry_s < max_tiles ? carry_s : max_tiles;
 }
 
 // Packs activation rows into f16 tiles of NT rows x 64 columns laid out exactly as the tensor core
@@ -446,6 +465,9 @@ struct TcCfg {
     uint32_t raw_slots;   // depth of the raw weight ring (2..6)
     uint32_t aligned;     // every weight row starts on a 16-byte boundary and k % 256 == 0: static-offset 16-byte raw reads
     uint32_t debug;       // experiment switches: 1 = skip dequantisation, 2 = skip raw copies, 4 = skip MMA, 8 = skip B copies
+    uint32_t n_wt;        // weight-row tiles, ceil(n / 128)
+    uint32_t ntiles;      // activation tiles: the count (dense) or its bound (routed: the list's length is read on the device)
+    uint32_t ksplit;      // K split factor (1 or 2)
 };
 
 constexpr int kTcAStages = 4;      // ring of dequantised weight stages held in tensor memory
@@ -453,9 +475,9 @@ constexpr int kTcACols = 64;       // one stage: 128 K values as f16 pairs = 64 
 constexpr int kTcAColBase = 256;   // accumulator in columns [0, NT), weight ring in [256, 512)
 constexpr int kTcTmemCols = 512;
 
-// grid (ceil(n/128), tile count bound); kTcThreads threads; 1 CTA per SM.
+// grid = min(work items, SMs) persistent CTAs; kTcThreads threads; 1 CTA per SM.
 //
-// Data flow per CTA (one 128-row weight tile x one NT-row activation tile, all of K):
+// Data flow per work item (one 128-row weight tile x one NT-row activation tile, all of K or one K split):
 //   raw GGML blocks  --cp.async-->  shared-memory ring  --dequantise (16 warps)-->  f16 pairs in registers
 //   --tcgen05.st-->  tensor-memory ring (A operand)  --tcgen05.mma, B = packed activations from the bulk-copy
 //   ring in shared memory-->  f32 accumulator in tensor memory  --tcgen05.ld-->  y.
@@ -469,24 +491,46 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES, KR = TcTraits<T>::KR;
     constexpr int kMaxB = 6, kMaxRaw = 6;
     __shared__ __align__(8) uint64_t a_full[kTcAStages], stage_done[kTcAStages], b_full[kMaxB];
-    __shared__ __align__(8) uint64_t raw_full[kMaxRaw], raw_empty[kMaxRaw], acc_full;
+    __shared__ __align__(8) uint64_t raw_full[kMaxRaw], raw_empty[kMaxRaw], acc_full, acc_empty, orow_ready[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile uint32_t abort_flag;
-    __shared__ int32_t orow[NT];
+    __shared__ int32_t orow[2][NT];
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t wt = blockIdx.x;              // weight-row tile
-    const uint32_t tt = blockIdx.y;              // token tile (dense) or tile-list index (routed)
-    uint32_t e = 0, mt = tt, nrows = a.m;
-    if (a.hids) {
-        if (tt >= a.tiles[0]) return;            // uniform for the whole CTA
-        e = a.tiles[1 + 2 * tt];
-        mt = a.tiles[2 + 2 * tt];
-        nrows = a.htpe[e];
-    }
-    const uint8_t *wbase = a.w + (size_t)e * a.expert_stride;
     const uint32_t row_bytes = (a.k / QK) * BB;
-    const uint32_t n0 = wt * kTcRowsW;
+
+    // ---- work items: (weight-row tile, K split, token tile), weight tile fastest; CTA b takes items b, b + grid, ...
+    // Every role walks the same item sequence; ring slots and barrier phases run on across items, so the next
+    // item's weights are already on their way while this item's accumulator is read back.
+    const uint32_t n_tt = a.hids ? min(a.tiles[0], c.ntiles) : c.ntiles;   // uniform for the whole CTA
+    const uint32_t total_items = c.n_wt * c.ksplit * n_tt;
+    const uint32_t nraw_all = (a.k + KR - 1) / KR;
+    struct Item {
+        uint32_t tt, e, mt, n0, r_lo, nraw, nst, nck, kc_lo;
+        const uint8_t *wbase;
+    };
+    auto load_item = [&](uint32_t item) -> Item {
+        Item it;
+        const uint32_t wt = item % c.n_wt, rest = item / c.n_wt;
+        const uint32_t z = rest % c.ksplit;
+        it.tt = rest / c.ksplit;
+        it.e = 0;
+        it.mt = it.tt;
+        if (a.hids) {
+            it.e = a.tiles[1 + 2 * it.tt];
+            it.mt = a.tiles[2 + 2 * it.tt];
+        }
+        it.wbase = a.w + (size_t)it.e * a.expert_stride;
+        it.n0 = wt * kTcRowsW;
+        // split-K: this item takes the raw stages [r_lo, r_hi) of K and adds its part of the tile into y
+        it.r_lo = (uint32_t)(((uint64_t)z * nraw_all) / c.ksplit);
+        const uint32_t r_hi = (uint32_t)(((uint64_t)(z + 1) * nraw_all) / c.ksplit);
+        it.nraw = r_hi - it.r_lo;
+        it.kc_lo = it.r_lo * (KR / 64);
+        it.nst = min((a.k + 127) / 128, r_hi * (KR / 128)) - it.r_lo * (KR / 128);   // tensor-memory stages
+        it.nck = min(c.nchunks, r_hi * (KR / 64)) - it.kc_lo;                         // 64-wide activation chunks
+        return it;
+    };
 
     if (tid == 0) {
         abort_flag = 0;
@@ -500,20 +544,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             mbar_init(&raw_empty[s], kTcDequantWarps);
         }
         mbar_init(&acc_full, 1);
+        mbar_init(&acc_empty, kTcDequantWarps);
+        for (int s = 0; s < 2; s++) mbar_init(&orow_ready[s], kTcDequantWarps);
         mbar_init_fence();
-    }
-    for (uint32_t i = tid; i < NT; i += kTcThreads) {
-        int32_t o = -1;
-        const uint32_t row = mt * NT + i;
-        if (row < nrows) {
-            if (a.hids) {
-                const int32_t id = a.hids[(size_t)e * a.hids_stride + row];
-                if (id >= 0 && (uint32_t)id < a.total_rows) o = id;
-            } else {
-                o = (int32_t)row;
-            }
-        }
-        orow[i] = o;
     }
     if (warp == kTcDequantWarps + 1) {  // MMA warp owns tensor memory
         tmem_alloc(&tmem_base_s, kTcTmemCols);
@@ -526,16 +559,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     const uint32_t smem_base = smem_u32(smem);
     const uint32_t b_bytes = NT * 128;                 // one 64-wide K chunk of the activation tile
     const uint32_t raw_stage_bytes = kTcRowsW * c.seg_stride;
-    // Split-K (gridDim.z = 2 when the tile grid alone would leave half of the SMs idle): this CTA takes the raw
-    // stages [r_lo, r_hi) of K and adds its part of the tile into y.  Everything below counts stages and chunks
-    // relative to r_lo; absolute positions are only needed for addresses.
-    const uint32_t nraw_all = (a.k + KR - 1) / KR;
-    const uint32_t r_lo = (uint32_t)(((uint64_t)blockIdx.z * nraw_all) / gridDim.z);
-    const uint32_t r_hi = (uint32_t)(((uint64_t)(blockIdx.z + 1) * nraw_all) / gridDim.z);
-    const uint32_t nraw = r_hi - r_lo;
-    const uint32_t st_lo = r_lo * (KR / 128), kc_lo = r_lo * (KR / 64);
-    const uint32_t nst = min((a.k + 127) / 128, r_hi * (KR / 128)) - st_lo;   // tensor-memory stages of this CTA
-    const uint32_t nck = min(c.nchunks, r_hi * (KR / 64)) - kc_lo;            // 64-wide chunks of this CTA
     // wait styles: the single producer / MMA warps spin (they are the critical path and cost one warp's issue
     // slots); the dequantising warps space their polls out
     const uint32_t wmode_cr = (c.debug & 32u) ? 0u : 0xFFFFFFFFu;
@@ -543,26 +566,34 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
 
     if (warp == kTcDequantWarps) {
         // ======================= producer warp: bulk copies of the packed activation tiles =======================
-        // Chunk kc reuses the slot of chunk kc - b_stages, which belonged to K stage (kc - b_stages) / 2: the
-        // slot is free once that stage's MMAs have completed (stage_done, the same barrier the dequantising
-        // warps wait on before they overwrite the stage's weights in tensor memory).
+        // Every K stage owns two consecutive chunk slots of the ring (a K tail of 64 leaves its second one empty;
+        // the producer still arrives on it so that the slot's phase moves on).  Chunk slot G reuses the place of
+        // chunk slot G - b_stages, which belonged to K stage (G - b_stages) / 2: free once that stage's MMAs have
+        // completed (stage_done, the same barrier the dequantising warps wait on before they overwrite the stage's
+        // weights in tensor memory).  G and the stage numbers count on across items.
         if (lane == 0) {
-            uint32_t s = 0;
-            for (uint32_t kc = 0; kc < nck; kc++) {
-                if (kc >= c.b_stages) {
-                    const uint32_t j = (kc - c.b_stages) >> 1;
-                    if (!mbar_wait(&stage_done[j & (kTcAStages - 1)], (j / kTcAStages) & 1u, &abort_flag, a.status,
-                                   ST_WAIT_EMPTY_TIMEOUT, wmode_cr))
-                        break;
+            uint32_t s = 0, G = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+                const Item it = load_item(item);
+                for (uint32_t kc = 0; kc < 2 * it.nst; kc++, G++) {
+                    if (G >= c.b_stages) {
+                        const uint32_t j = (G - c.b_stages) >> 1;
+                        if (!mbar_wait(&stage_done[j & (kTcAStages - 1)], (j / kTcAStages) & 1u, &abort_flag, a.status,
+                                       ST_WAIT_EMPTY_TIMEOUT, wmode_cr)) {
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (kc >= it.nck || (c.debug & 8u)) {
+                        mbar_arrive(&b_full[s]);
+                    } else {
+                        mbar_expect_tx(&b_full[s], b_bytes);
+                        bulk_g2s(smem + c.b_off + s * b_bytes,
+                                 xpack + ((size_t)it.tt * c.nchunks + it.kc_lo + kc) * (size_t)b_bytes, b_bytes, &b_full[s]);
+                    }
+                    if (++s == c.b_stages) s = 0;
                 }
-                if (c.debug & 8u) {
-                    mbar_arrive(&b_full[s]);
-                } else {
-                    mbar_expect_tx(&b_full[s], b_bytes);
-                    bulk_g2s(smem + c.b_off + s * b_bytes, xpack + ((size_t)tt * c.nchunks + kc_lo + kc) * (size_t)b_bytes, b_bytes,
-                             &b_full[s]);
-                }
-                if (++s == c.b_stages) s = 0;
             }
         }
     } else if (warp == kTcDequantWarps + 1) {
@@ -575,35 +606,43 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             const uint64_t b_step = b_bytes >> 4;  // descriptor address field is in 16-byte units
             const bool do_mma = !(c.debug & 4u);
             uint64_t bd = bd0;
-            uint32_t sa = 0, aph = 0, sb = 0, bph = 0, kc = 0;
-            for (uint32_t st = 0; st < nst; st++) {
-                if (!mbar_wait(&a_full[sa], aph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
-                if (!mbar_wait(&b_full[sb], bph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
+            uint32_t sa = 0, aph = 0, sb = 0, bph = 0, nitem = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; ok && item < total_items; item += gridDim.x, nitem++) {
+                const Item it = load_item(item);
+                // the accumulator of the item before has been read back
+                if (nitem > 0 &&
+                    !mbar_wait(&acc_empty, (nitem - 1) & 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_cr))
+                    break;
                 tc_fence_after();
-                const uint32_t a_col = tmem_d + kTcAColBase + sa * kTcACols;
-                if (do_mma) {
-                    umma_f16_ts(tmem_d, a_col, bd, idesc, st != 0 ? 1u : 0u);
-                    umma_f16_ts(tmem_d, a_col + 8, bd + 2, idesc, 1u);
-                    umma_f16_ts(tmem_d, a_col + 16, bd + 4, idesc, 1u);
-                    umma_f16_ts(tmem_d, a_col + 24, bd + 6, idesc, 1u);
-                }
-                bd += b_step;
-                if (++sb == c.b_stages) { sb = 0; bph ^= 1u; bd = bd0; }
-                if (++kc < nck) {
-                    if (!mbar_wait(&b_full[sb], bph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) break;
+                for (uint32_t st = 0; st < it.nst; st++) {
+                    if (!mbar_wait(&a_full[sa], aph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) { ok = false; break; }
+                    if (!mbar_wait(&b_full[sb], bph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_col = tmem_d + kTcAColBase + sa * kTcACols;
                     if (do_mma) {
-                        umma_f16_ts(tmem_d, a_col + 32, bd, idesc, 1u);
-                        umma_f16_ts(tmem_d, a_col + 40, bd + 2, idesc, 1u);
-                        umma_f16_ts(tmem_d, a_col + 48, bd + 4, idesc, 1u);
-                        umma_f16_ts(tmem_d, a_col + 56, bd + 6, idesc, 1u);
+                        umma_f16_ts(tmem_d, a_col, bd, idesc, st != 0 ? 1u : 0u);
+                        umma_f16_ts(tmem_d, a_col + 8, bd + 2, idesc, 1u);
+                        umma_f16_ts(tmem_d, a_col + 16, bd + 4, idesc, 1u);
+                        umma_f16_ts(tmem_d, a_col + 24, bd + 6, idesc, 1u);
                     }
                     bd += b_step;
                     if (++sb == c.b_stages) { sb = 0; bph ^= 1u; bd = bd0; }
-                    ++kc;
+                    if (2 * st + 1 < it.nck) {
+                        if (!mbar_wait(&b_full[sb], bph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) { ok = false; break; }
+                        if (do_mma) {
+                            umma_f16_ts(tmem_d, a_col + 32, bd, idesc, 1u);
+                            umma_f16_ts(tmem_d, a_col + 40, bd + 2, idesc, 1u);
+                            umma_f16_ts(tmem_d, a_col + 48, bd + 4, idesc, 1u);
+                            umma_f16_ts(tmem_d, a_col + 56, bd + 6, idesc, 1u);
+                        }
+                    }
+                    bd += b_step;   // the stage's second chunk slot is passed over whether it held data or not
+                    if (++sb == c.b_stages) { sb = 0; bph ^= 1u; bd = bd0; }
+                    umma_commit(&stage_done[sa]);  // frees the stage's weights and its two activation chunks
+                    if (st + 1 == it.nst) umma_commit(&acc_full);
+                    if (++sa == kTcAStages) { sa = 0; aph ^= 1u; }
                 }
-                umma_commit(&stage_done[sa]);  // frees the stage's weights and its two activation chunks
-                if (st + 1 == nst) umma_commit(&acc_full);
-                if (++sa == kTcAStages) { sa = 0; aph ^= 1u; }
             }
         }
         __syncwarp();
@@ -615,32 +654,39 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         // (w / 4) % 2 of the stage: thirty-two packed f16 pairs = one 32-column store.
         const uint32_t q4 = warp & 3u, half = (warp >> 2) & 1u, set = warp >> 3;
         const uint32_t rr = q4 * 32 + lane;
-        const bool row_ok = n0 + rr < a.n;
-        const uint32_t row_lo4 = (uint32_t)((uintptr_t)(wbase + (size_t)(n0 + rr) * row_bytes) & 15u);
         // Raw weight rows are short (144..272 bytes per stage and row), too short for one bulk copy each to be
         // efficient, so all dequantising threads stream them as 16-byte cp.async chunks, a few raw stages ahead
         // of the one being dequantised.  Each row is fetched as the 16-byte aligned superset of its (only
         // 2-byte aligned) segment; readers skip the lead-in bytes.
-        // The (row, 16-byte chunk) pairs a thread copies are the same in every raw stage, so they are worked
-        // out once: per stage only the K offset moves.
+        // The (row, 16-byte chunk) pairs a thread copies are the same in every raw stage and every item; per item
+        // only the rows' base addresses change, per stage only the K offset.
         constexpr int kRawSlots = 5;            // (128 rows x at most 19 chunks) / 512 threads, rounded up
         constexpr uint32_t kSegFull = (KR / QK) * BB;
         constexpr uint32_t kCmax = (kSegFull + 30u) >> 4;  // most 16-byte chunks a row segment can need
         static_assert(kTcRowsW * kCmax <= kRawSlots * kTcDequantWarps * 32, "raw copy slots");
         static_assert(KR == 256, "a raw stage feeds one K stage of each set");
-        const uint32_t rows_here = min((uint32_t)kTcRowsW, a.n - n0);
-        const uint8_t *slot_src[kRawSlots];     // start of the thread's row (global)
+        const uint8_t *slot_src[kRawSlots];     // start of the thread's row (global), for the item being requested
         uint32_t slot_dst[kRawSlots];           // row's place inside a raw stage + chunk offset (shared, relative)
-        uint32_t slot_cc[kRawSlots];            // chunk index within the row, 0xFFFFFFFF = unused
+        uint32_t slot_cc[kRawSlots];            // chunk index within the row, 0xFFFFFFFF = unused in this item
+        // request cursor: runs ahead of the dequantisation, across item boundaries
+        uint32_t q_item = blockIdx.x, q_r = 0, q_nraw = 0, q_rlo = 0;
+        auto open_request_item = [&]() {
+            const Item it = load_item(q_item);
+            const uint32_t rows_here = min((uint32_t)kTcRowsW, a.n - it.n0);
 #pragma unroll
-        for (int i = 0; i < kRawSlots; i++) {
-            const uint32_t idx = tid + i * (kTcDequantWarps * 32);
-            const uint32_t row = idx / kCmax, cc = idx - row * kCmax;
-            const bool used = row < rows_here;
-            slot_src[i] = wbase + (size_t)(n0 + (used ? row : 0)) * row_bytes;
-            slot_dst[i] = row * c.seg_stride + cc * 16u;
-            slot_cc[i] = used ? cc : 0xFFFFFFFFu;
-        }
+            for (int i = 0; i < kRawSlots; i++) {
+                const uint32_t idx = tid + i * (kTcDequantWarps * 32);
+                const uint32_t row = idx / kCmax, cc = idx - row * kCmax;
+                const bool used = row < rows_here;
+                slot_src[i] = it.wbase + (size_t)(it.n0 + (used ? row : 0)) * row_bytes;
+                slot_dst[i] = row * c.seg_stride + cc * 16u;
+                slot_cc[i] = used ? cc : 0xFFFFFFFFu;
+            }
+            q_r = 0;
+            q_nraw = it.nraw;
+            q_rlo = it.r_lo;
+        };
+        if (q_item < total_items) open_request_item();
         auto issue_raw = [&](uint32_t r, uint32_t slot) {
             const uint32_t k0 = r * KR;
             const uint32_t seg_bytes = (min((uint32_t)KR, a.k - k0) / QK) * BB;
@@ -658,37 +704,75 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             // the thread's arrival on the slot's barrier fires once its copies have landed; nobody blocks on it
             asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&raw_full[slot])) : "memory");
         };
-        // raw ring: stage r lives in slot r % raw_slots and is requested raw_slots-1 stages before it is read
+        // raw ring: a stage is requested raw_slots-1 stages before it is read; slots and phases count on across items
         const uint32_t R = c.raw_slots, D = R - 1;
         uint32_t islot = 0, iph = 0;   // slot / use-parity of the next stage to request
-        uint32_t rnext = 0;
-        for (; rnext < min(D, nraw); rnext++) {
-            issue_raw(r_lo + rnext, islot);
-            if (++islot == R) { islot = 0; iph ^= 1u; }
-        }
+        uint32_t requested = 0, consumed = 0;
         uint32_t rs = 0, rph = 0;      // slot / parity of the raw stage being read
+        uint32_t J0 = 0;               // K stages of the items before this one (tensor-memory ring position)
+        uint32_t nitem = 0;
+        bool ok = true;
         const uint32_t a_dst = tmem_d + ((q4 * 32) << 16) + kTcAColBase + 32 * half;
-        for (uint32_t r = 0; r < nraw; r++) {
-            if (rnext < nraw) {
-                // the slot's previous tenant (stage rnext - R) must have been released by every warp
-                if (!mbar_wait(&raw_empty[islot], iph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) break;
-                issue_raw(r_lo + rnext, islot);
-                rnext++;
-                if (++islot == R) { islot = 0; iph ^= 1u; }
+        const uint32_t g = warp >> 2;
+        for (uint32_t item = blockIdx.x; ok && item < total_items; item += gridDim.x, nitem++) {
+            const Item it = load_item(item);
+            const uint32_t n0 = it.n0;
+            const bool row_ok = n0 + rr < a.n;
+            const uint32_t row_lo4 = (uint32_t)((uintptr_t)(it.wbase + (size_t)(n0 + rr) * row_bytes) & 15u);
+            // the item's output-row table (double-buffered: the one of the item before may still be in use by a
+            // warp that is behind); read again only in the epilogue
+            {
+                int32_t *tab = orow[nitem & 1u];
+                const uint32_t nrows = a.hids ? a.htpe[it.e] : a.m;
+                for (uint32_t i = tid; i < NT; i += kTcDequantWarps * 32) {
+                    int32_t o = -1;
+                    const uint32_t row = it.mt * NT + i;
+                    if (row < nrows) {
+                        if (a.hids) {
+                            const int32_t id = a.hids[(size_t)it.e * a.hids_stride + row];
+                            if (id >= 0 && (uint32_t)id < a.total_rows) o = id;
+                        } else {
+                            o = (int32_t)row;
+                        }
+                    }
+                    tab[i] = o;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&orow_ready[nitem & 1u]);
             }
-            if (!mbar_wait(&raw_full[rs], rph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_dq)) break;
-            const uint32_t st = 2 * r + set;       // this set's K stage inside raw stage r
-            if (st < nst) {
-                const uint32_t sa = st & (kTcAStages - 1);
-                // the MMAs that read this stage's previous contents (K stage st - 4) have completed
-                if (st >= kTcAStages &&
-                    !mbar_wait(&stage_done[sa], ((st / kTcAStages) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT,
-                               wmode_dq))
-                    break;
-                tc_fence_after();
-                const uint32_t r_abs = r_lo + r;
-                const uint32_t pre = (row_lo4 + ((r_abs * KR) / QK) * BB) & 15u;
-                const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
+            for (uint32_t r = 0; ok && r < it.nraw; r++) {
+                // keep D raw stages requested ahead of the one being read
+                while (q_item < total_items && requested - consumed < D + 1) {
+                    if (requested >= R &&
+                        !mbar_wait(&raw_empty[islot], iph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) {
+                        ok = false;
+                        break;
+                    }
+                    issue_raw(q_rlo + q_r, islot);
+                    requested++;
+                    if (++islot == R) { islot = 0; iph ^= 1u; }
+                    if (++q_r == q_nraw) {
+                        q_item += gridDim.x;
+                        if (q_item < total_items) open_request_item();
+                    }
+                }
+                if (!ok) break;
+                if (!mbar_wait(&raw_full[rs], rph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_dq)) { ok = false; break; }
+                const uint32_t st = 2 * r + set;       // this set's K stage inside raw stage r
+                if (st < it.nst) {
+                    const uint32_t J = J0 + st;        // its number in the CTA's whole run
+                    const uint32_t sa = J & (kTcAStages - 1);
+                    // the MMAs that read this ring place's previous contents (K stage J - 4) have completed
+                    if (J >= kTcAStages &&
+                        !mbar_wait(&stage_done[sa], ((J / kTcAStages) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT,
+                                   wmode_dq)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t r_abs = it.r_lo + r;
+                    const uint32_t pre = (row_lo4 + ((r_abs * KR) / QK) * BB) & 15u;
+                    const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
                 uint32_t regs[32];
                 if (c.aligned && row_ok && !(c.debug & 1u)) {
                     const uint32_t stage_row = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride;
@@ -723,20 +807,24 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                         }
                     }
                 }
-                tmem_st_32x32_x32(a_dst + sa * kTcACols, regs);
-                tmem_st_wait();
-                tc_fence_before();
+                    tmem_st_32x32_x32(a_dst + sa * kTcACols, regs);
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&a_full[sa]);
+                }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&a_full[sa]);
+                if (lane == 0) mbar_arrive(&raw_empty[rs]);  // this warp is done reading the raw stage
+                consumed++;
+                if (++rs == R) { rs = 0; rph ^= 1u; }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&raw_empty[rs]);  // this warp is done reading raw stage r
-            if (++rs == R) { rs = 0; rph ^= 1u; }
-        }
-        const uint32_t g = warp >> 2;
-        // ---- epilogue: TMEM -> registers -> y ----
-        if (!abort_flag && mbar_wait(&acc_full, 0, &abort_flag, a.status, ST_WAIT_MMA_TIMEOUT, 200)) {
+            if (!ok) break;
+            J0 += it.nst;
+            // ---- epilogue: TMEM -> registers -> y ----
+            if (!mbar_wait(&orow_ready[nitem & 1u], (nitem >> 1) & 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) break;
+            if (!mbar_wait(&acc_full, nitem & 1u, &abort_flag, a.status, ST_WAIT_MMA_TIMEOUT, wmode_dq)) break;
             tc_fence_after();
+            const int32_t *tab = orow[nitem & 1u];
             const uint32_t wrow = n0 + rr;
 #pragma unroll 1
             for (uint32_t col = g * 32; col < NT; col += (kTcDequantWarps / 4) * 32) {
@@ -746,14 +834,17 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                 if (wrow < a.n && !(c.debug & 256u)) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
-                        const int32_t o = orow[col + j];
+                        const int32_t o = tab[col + j];
                         if (o >= 0) {
-                            if (gridDim.z > 1) atomicAdd(&a.y[(size_t)o * a.n + wrow], __uint_as_float(v[j]));
+                            if (c.ksplit > 1) atomicAdd(&a.y[(size_t)o * a.n + wrow], __uint_as_float(v[j]));
                             else a.y[(size_t)o * a.n + wrow] = __uint_as_float(v[j]);
                         }
                     }
                 }
             }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty);   // the MMA warp may start the next item's accumulation
         }
     }
     if (abort_flag) {  // let copies in flight land before the CTA's shared memory is released
@@ -855,7 +946,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     if ((c.seg_stride / 16) % 2 == 0) c.seg_stride += 16;  // odd multiple of 16 B: rows spread over the banks
     const uint32_t b_bytes = NT * 128;  // one 64-wide K chunk of the activation tile
     const uint32_t raw_slot = kTcRowsW * c.seg_stride;
-    const uint32_t limit = 224 * 1024;
+    const uint32_t limit = 222 * 1024;  // + 1 KB alignment slack + ~3 KB of static shared memory <= 227 KB
     // activation ring first (at least two raw slots kept back), the rest goes to the raw weight ring
     uint32_t b_stages = (limit - 2 * raw_slot) / b_bytes;
     if (b_stages > 6) b_stages = 6;
@@ -886,7 +977,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
         if (tiles == 0) tiles = 1;
         const size_t header = ((1 + 2 * tiles) * 4 + 1023) / 1024 * 1024;
         uint32_t *tl = reinterpret_cast<uint32_t *>(scratch);
-        build_tiles_kernel<<<1, 32, 0, st>>>(a.htpe, a.n_experts, NT, (uint32_t)tiles, tl);
+        build_tiles_kernel<<<1, 256, 0, st>>>(a.htpe, a.n_experts, NT, (uint32_t)tiles, tl);
         (*launches)++;
         a.tiles = tl;
         xpack = scratch + header;
@@ -910,8 +1001,19 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
         if (e != cudaSuccess) return e;
         attr_smem[dev] = smem;
     }
-    dim3 grid((a.n + kTcRowsW - 1) / kTcRowsW, (unsigned)tiles, ksplit);
-    qmm_tc_kernel<T, NT><<<grid, kTcThreads, smem, st>>>(a, c, xpack);
+    c.n_wt = (a.n + kTcRowsW - 1) / kTcRowsW;
+    c.ntiles = (uint32_t)tiles;
+    c.ksplit = ksplit;
+    // persistent CTAs, one per SM, each walking its share of the (weight tile, K split, activation tile) items
+    const uint64_t items = (uint64_t)c.n_wt * tiles * ksplit;
+    uint32_t ctas = (uint32_t)sm_count_of_device();
+    if (const char *e = getenv("MLXN_TC_CTAS")) {  // experiment switch
+        const int v = atoi(e);
+        if (v >= 1 && v <= 4096) ctas = (uint32_t)v;
+    }
+    if (items < ctas) ctas = (uint32_t)items;
+    if (ctas == 0) return cudaSuccess;
+    qmm_tc_kernel<T, NT><<<ctas, kTcThreads, smem, st>>>(a, c, xpack);
     (*launches)++;
     return cudaGetLastError();
 }

@@ -3,6 +3,8 @@
   python -m mlx_native_b200.profile_case mv  [Q8_0|Q6_K|Q4_0] [m]   decode mat-vec, n=12288 k=4096, 4 weight copies (> L2)
   python -m mlx_native_b200.profile_case mm  [Q4_0|Q6_K|Q8_0] [m]   prefill mat-mat, n=4096 k=4096, m=512 by default
   python -m mlx_native_b200.profile_case moe [m]                    expert-routed gate projection, 128 experts, top-8
+  python -m mlx_native_b200.profile_case moe_layer [m] [reps]         whole MoE FFN layer (route, gate, up, SwiGLU, down, reduce),
+                                                                     128 experts, top-8, hidden 2048, ffn 768
   python -m mlx_native_b200.profile_case cmp [types]                 tensor-core vs streaming mat-vec, microseconds per call
                                                                      (CUDA-graph replay over rotating weight copies > L2)
 
@@ -80,6 +82,41 @@ def main(argv):
         compare_matvec_kernels(dev, reg, rng, (argv[1] if len(argv) > 1 else "Q8_0,Q6_K,Q4_0").split(","))
         return
     enc = dev.command_encoder()
+    if mode == "moe_layer":
+        T = int(argv[1]) if len(argv) > 1 else 512
+        reps = int(argv[2]) if len(argv) > 2 else 3
+        E, top_k, hidden, ffn = 128, 8, 2048, 768
+        bufs = {}
+        for name, t, rows, cols in (("gate", "Q4_0", E * ffn, hidden), ("up", "Q4_0", E * ffn, hidden), ("down", "Q6_K", E * hidden, ffn)):
+            w = random_blocks(rng, t, rows, cols)
+            bufs[name] = dev.alloc_buffer(w.size, mx.DType.U8)
+            bufs[name].upload(w)
+            bufs[name + "_stride"] = w.size // E
+        logits = rng.standard_normal((T, E)).astype(np.float32)
+        lg = dev.alloc_buffer(logits.nbytes, mx.DType.F32)
+        lg.upload(logits)
+        x = rng.standard_normal((T, hidden)).astype(np.float32)
+        xb = dev.alloc_buffer(x.nbytes, mx.DType.F32)
+        xb.upload(x)
+        ids = dev.alloc_buffer(T * top_k * 4, mx.DType.U32)
+        rw = dev.alloc_buffer(T * top_k * 4, mx.DType.F32)
+        yg = dev.alloc_buffer(T * top_k * ffn * 4, mx.DType.F32)
+        yu = dev.alloc_buffer(T * top_k * ffn * 4, mx.DType.F32)
+        act = dev.alloc_buffer(T * top_k * ffn * 4, mx.DType.F32)
+        yd = dev.alloc_buffer(T * top_k * hidden * 4, mx.DType.F32)
+        outb = dev.alloc_buffer(T * hidden * 4, mx.DType.F32)
+        pg = mx.GgmlQuantizedMatmulIdParams(T, top_k, ffn, hidden, E, bufs["gate_stride"], mx.GgmlType.Q4_0)
+        pd = mx.GgmlQuantizedMatmulIdParams(T * top_k, 1, hidden, ffn, E, bufs["down_stride"], mx.GgmlType.Q6_K)
+        for _ in range(reps):
+            mx.moe_softmax_topk(enc, reg, dev, lg, ids, rw, T, E, top_k)
+            mx.quantized_matmul_id_ggml(enc, reg, dev, xb, bufs["gate"], ids, yg, pg)
+            mx.quantized_matmul_id_ggml(enc, reg, dev, xb, bufs["up"], ids, yu, pg)
+            mx.silu_mul(enc, reg, dev, yg, yu, act, T * top_k * ffn)
+            mx.quantized_matmul_id_ggml(enc, reg, dev, act, bufs["down"], ids, yd, pd)
+            mx.moe_weighted_reduce(enc, reg, dev, rw, yd, outb, T, top_k, hidden)
+            enc.commit_and_wait()
+        print("ok", mx.last_kernel_name())
+        return
     if mode == "moe":
         m = int(argv[1]) if len(argv) > 1 else 512
         E, top_k, hidden, ffn = 128, 8, 2048, 768
