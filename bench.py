@@ -392,6 +392,12 @@ def run_ours(args, rank, world, local_rank):
         e2e_s = float(tt.item())
     e2e_value = step_weight_bytes / e2e_s / 1e9
 
+    sharded = None
+    if world > 1 and not args.no_extra:
+        try:
+            sharded = sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream)
+        except Exception as ex:  # the headline stands on its own
+            sharded = {"error": repr(ex)}
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -428,9 +434,135 @@ def run_ours(args, rank, world, local_rank):
                 line["extra"] = extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak)
             except Exception as ex:  # the headline stands on its own
                 line["extra"] = {"error": repr(ex)}
+    if sharded is not None:
+        line["extra"] = sharded
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+
+
+def sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream):
+    """Secondary multi-GPU figures, every rank taking part:
+    the expert-sharded MoE FFN layer (128 experts / world per rank, local routing filter, one all-reduce of the
+    [T, hidden] partial sums as the combine) and the N-sharded Q6_K lm_head mat-vec (151936 x 5120, m = 1, peer
+    stores into every rank's logits + one cross-rank barrier)."""
+    from mlx_native_b200 import sharding
+    from mlx_native_b200.profile_case import random_blocks
+
+    out = {}
+    rng = np.random.default_rng(11)          # same seed on every rank: replicated activations and logits
+
+    def timed(step, reps=10, warm=3):
+        for _ in range(warm):
+            step()
+        enc.commit_and_wait()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(ext_stream):
+            e0.record()
+        for _ in range(reps):
+            step()
+        with torch.cuda.stream(ext_stream):
+            e1.record()
+        enc.commit_and_wait()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps * 1e-3], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- expert-sharded MoE FFN layer
+    E, top_k, hidden, ffn = 128, 8, 2048, 768
+    lo, cnt = sharding.shard_experts(E, rank, world)
+    wrng = np.random.default_rng(100 + rank)
+    w = {}
+    for name, t, rows, cols in (("gate", "Q4_0", cnt * ffn, hidden), ("up", "Q4_0", cnt * ffn, hidden), ("down", "Q6_K", cnt * hidden, ffn)):
+        blk = random_blocks(wrng, t, rows, cols)
+        w[name] = dev.alloc_buffer(blk.size, mx.DType.U8)
+        w[name].upload(blk)
+        w[name + "_stride"] = blk.size // cnt
+    moe = {}
+    for T in (512, 1):
+        logits = rng.standard_normal((T, E)).astype(np.float32)
+        lg = dev.alloc_buffer(logits.nbytes, mx.DType.F32)
+        lg.upload(logits)
+        x = rng.standard_normal((T, hidden)).astype(np.float32)
+        xb = dev.alloc_buffer(x.nbytes, mx.DType.F32)
+        xb.upload(x)
+        pairs = T * top_k
+        ids = dev.alloc_buffer(pairs * 4, mx.DType.U32)
+        lids = dev.alloc_buffer(pairs * 4, mx.DType.U32)
+        rw = dev.alloc_buffer(pairs * 4, mx.DType.F32)
+        yg = dev.alloc_buffer(pairs * ffn * 4, mx.DType.F32)
+        yu = dev.alloc_buffer(pairs * ffn * 4, mx.DType.F32)
+        act = dev.alloc_buffer(pairs * ffn * 4, mx.DType.F32)
+        yd = dev.alloc_buffer(pairs * hidden * 4, mx.DType.F32)
+        out_t = torch.zeros((T, hidden), dtype=torch.float32, device="cuda")
+        outb = dev.wrap_device_memory(out_t.data_ptr(), T * hidden * 4, mx.DType.F32, [T, hidden])
+        pg = mx.GgmlQuantizedMatmulIdParams(T, top_k, ffn, hidden, cnt, w["gate_stride"], mx.GgmlType.Q4_0)
+        pd = mx.GgmlQuantizedMatmulIdParams(pairs, 1, hidden, ffn, cnt, w["down_stride"], mx.GgmlType.Q6_K)
+
+        def layer(e):
+            mx.moe_softmax_topk(e, reg, dev, lg, ids, rw, T, E, top_k)            # replicated routing
+            mx.moe_expert_shard_route(e, reg, dev, ids, lids, pairs, lo, cnt)     # dispatch = local filter
+            mx.quantized_matmul_id_ggml(e, reg, dev, xb, w["gate"], lids, yg, pg)
+            mx.quantized_matmul_id_ggml(e, reg, dev, xb, w["up"], lids, yu, pg)
+            mx.silu_mul(e, reg, dev, yg, yu, act, pairs * ffn)
+            mx.quantized_matmul_id_ggml(e, reg, dev, act, w["down"], lids, yd, pd)
+            mx.moe_weighted_reduce_local(e, reg, dev, rw, yd, lids, outb, T, top_k, hidden)
+
+        layer(enc)
+        enc.commit_and_wait()
+        enc.begin_capture()
+        layer(enc)
+        g = enc.end_capture()
+
+        def step():
+            g.launch(enc)
+            with torch.cuda.stream(ext_stream):
+                dist.all_reduce(out_t)                                             # combine
+
+        sec = timed(step)
+        if not bool(torch.isfinite(out_t).all().item()):
+            raise RuntimeError("expert-sharded MoE layer produced non-finite values")
+        moe[f"m{T}"] = {"tokens_per_s": T / sec, "ms_per_layer": sec * 1e3, "experts_per_rank": cnt,
+                        "combine": "NCCL all-reduce of the [T, hidden] partial sums"}
+    out["moe_ffn_layer_expert_sharded"] = moe
+
+    # ---- N-sharded lm_head, Q6_K 151936 x 5120, m = 1
+    n, k, m = 151936, 5120, 1
+    try:
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+
+        n_loc = n // world
+        blk = random_blocks(wrng, "Q6_K", n_loc, k)
+        wb = dev.alloc_buffer(blk.size, mx.DType.U8)
+        wb.upload(blk)
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        xb = dev.alloc_buffer(x.nbytes, mx.DType.F32, [m, k])
+        xb.upload(x)
+        buf = symm_mem.empty(m * n, dtype=torch.float32, device=f"cuda:{torch.cuda.current_device()}")
+        hdl = symm_mem.rendezvous(buf, dist.group.WORLD)
+        buf.zero_()
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        yb = dev.wrap_device_memory(ptrs[rank], m * n * 4, mx.DType.F32, [m, n])
+        peers = [ptrs[r] for r in range(world) if r != rank]
+        prm = mx.GgmlQuantizedMatmulParams(m, n_loc, k, mx.GgmlType.Q6_K)
+
+        def step():
+            mx.quantized_matmul_ggml_sharded(enc, reg, dev, xb, wb, yb, prm, n, rank * n_loc, peers)
+            with torch.cuda.stream(ext_stream):
+                hdl.barrier()
+
+        sec = timed(step)
+        nz = int((buf != 0).sum().item())
+        out["lm_head_q6k_m1_n_sharded"] = {"us": sec * 1e6, "weight_GBps_all_ranks": n * (k // 256) * 210 / sec / 1e9,
+                                           "logits_filled": nz, "of": m * n,
+                                           "exchange": "peer stores from the mat-vec kernel + one barrier"}
+    except Exception as ex:
+        out["lm_head_q6k_m1_n_sharded"] = {"error": repr(ex)}
+    return out
 
 
 def cpu_baseline():
@@ -546,6 +678,24 @@ def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
         moe[f"m{T}"] = {"tokens_per_s": T / sec, "ms_per_layer": sec * 1e3, "expert_weight_GBps": wbytes / sec / 1e9,
                         "frac_of_measured_hbm_peak": wbytes / sec / 1e9 / hbm_peak}
     out["moe_ffn_layer"] = moe
+
+    # lm_head: Q6_K 151936 x 5120 (638 MB), m = 1 (mat-vec, HBM-bound) and m = 256 (mat-mat)
+    from mlx_native_b200.profile_case import random_blocks
+    n, k = 151936, 5120
+    blk = random_blocks(rng, "Q6_K", n, k)
+    wb = dev.alloc_buffer(blk.size, mx.DType.U8)
+    wb.upload(blk)
+    lm = {}
+    for m in (1, 256):
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        xb = dev.alloc_buffer(x.nbytes, mx.DType.F32)
+        xb.upload(x)
+        yb = dev.alloc_buffer(m * n * 4, mx.DType.F32)
+        p = mx.GgmlQuantizedMatmulParams(m, n, k, mx.GgmlType.Q6_K)
+        sec = timed(lambda e: mx.quantized_matmul_ggml(e, reg, dev, xb, wb, yb, p), inner=2)
+        lm[f"m{m}"] = {"us": sec * 1e6, "weight_GBps": blk.size / sec / 1e9, "frac_of_measured_hbm_peak": blk.size / sec / 1e9 / hbm_peak,
+                       "tflops": 2.0 * m * n * k / sec / 1e12}
+    out["lm_head_q6k"] = lm
     return out
 
 

@@ -230,6 +230,19 @@ int mlxn_moe_weighted_reduce(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device 
                              mlxn_buffer *residual, mlxn_buffer *out, uint32_t n_tokens, uint32_t top_k,
                              uint32_t h);
 
+/* ---- expert-sharded MoE (no counterpart in the reference: it runs on one GPU) ------------------------
+ * Rank r of g holds the experts [r E/g, (r+1) E/g) (a contiguous byte range of the stacked expert weights at
+ * `expert_stride`).  Activations and the router's ids/weights are replicated, so "dispatch" is a local filter:
+ * mlxn_moe_expert_shard_route turns the global ids into local ones (id - expert_lo) and marks the pairs of
+ * other ranks' experts with 0xFFFFFFFF, which mlxn_quantized_matmul_id_ggml treats as "no expert" (n_experts
+ * in its params is the local count).  mlxn_moe_weighted_reduce_local sums this rank's pairs only; the ranks'
+ * partial results are then added up by one all-reduce (the combine step). */
+int mlxn_moe_expert_shard_route(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *ids,
+                                mlxn_buffer *local_ids, uint32_t n_pairs, uint32_t expert_lo, uint32_t expert_count);
+int mlxn_moe_weighted_reduce_local(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *expert_w,
+                                   mlxn_buffer *y_expert, mlxn_buffer *local_ids, mlxn_buffer *out, uint32_t n_tokens,
+                                   uint32_t top_k, uint32_t h);
+
 /* ---- mat-mat without any allocation (no counterpart in the reference) ------------------------------
  * For callers that cannot allocate device memory when they need the product: a serving process whose own
  * allocator has claimed all of HBM, a latency-critical loop that must stay off the driver's allocation

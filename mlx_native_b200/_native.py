@@ -101,6 +101,8 @@ SIGNATURES = {
     "mlxn_moe_softmax_topk": (i32, [vp, vp, vp, vp, vp, vp, u32, u32, u32]),
     "mlxn_silu_mul": (i32, [vp, vp, vp, vp, vp, vp, u32]),
     "mlxn_moe_weighted_reduce": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32]),
+    "mlxn_moe_weighted_reduce_local": (i32, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32]),
+    "mlxn_moe_expert_shard_route": (i32, [vp, vp, vp, vp, vp, u32, u32, u32]),
     "mlxn_noalloc_scratch_limit": (sz, []),
     "mlxn_quantized_matmul_ggml_mm_noalloc": (i32, [vp, vp, vp, vp, C.POINTER(QmmParams)]),
     "mlxn_set_option": (i32, [C.c_char_p, C.c_char_p]),

@@ -562,6 +562,20 @@ def moe_weighted_reduce(encoder, registry, device, expert_w, y_expert, out, n_to
                                                   h))
 
 
+def moe_expert_shard_route(encoder, registry, device, ids, local_ids, n_pairs, expert_lo, expert_count) -> None:
+    """Expert-sharded MoE (no upstream counterpart): global expert ids -> this rank's local ids, 0xFFFFFFFF for
+    pairs whose expert lives on another rank."""
+    _check(_native.lib().mlxn_moe_expert_shard_route(encoder._h, _h(registry), device._h, _h(ids), _h(local_ids),
+                                                     n_pairs, expert_lo, expert_count))
+
+
+def moe_weighted_reduce_local(encoder, registry, device, expert_w, y_expert, local_ids, out, n_tokens, top_k, h) -> None:
+    """Partial `moe_weighted_reduce` over the pairs routed to this rank's experts; an all-reduce over the ranks'
+    results completes the sum."""
+    _check(_native.lib().mlxn_moe_weighted_reduce_local(encoder._h, _h(registry), device._h, _h(expert_w), _h(y_expert),
+                                                        _h(local_ids), _h(out), n_tokens, top_k, h))
+
+
 # ---------------------------------------------------------------- graph executor / session (src/graph.rs:862-941, 1029-1732)
 class GraphSession:
     """A single-encoder session whose op methods delegate to the free functions (src/graph.rs:1135-1208)."""

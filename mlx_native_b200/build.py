@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmlxn_b200.so")
 SOURCES = ["runtime.cu", "qmv.cu", "qmv_tc.cu", "qmm.cu", "moe.cu"]
-HEADERS = ["common.cuh", "ptx.cuh", os.path.join("..", "..", "include", "mlxn_b200.h")]
+HEADERS = ["common.cuh", "ptx.cuh", "tensor_map.cuh", os.path.join("..", "..", "include", "mlxn_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC",
@@ -38,7 +38,7 @@ def needs_build() -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
         return LIB
-    flags = list(NVCC_FLAGS)
+    flags = list(NVCC_FLAGS) + os.environ.get("MLXN_NVCC_EXTRA", "").split()   # e.g. -DMLXN_TC_TRACE for experiments
     objs = []
     procs = []
     for s in SOURCES:

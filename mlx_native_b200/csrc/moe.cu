@@ -10,6 +10,8 @@
 
 namespace mlxn {
 
+constexpr uint32_t kNotLocal = 0xFFFFFFFFu;   // id of a (token, slot) pair whose expert lives on another rank
+
 // One warp per expert, eight experts per CTA.  The CTA stages the id table through shared memory a chunk of tokens at
 // a time (one coalesced pass, transposed to [slot][token] so that the scan reads without bank conflicts); each warp
 // then walks the chunk 32 tokens at a time: every lane evaluates the upstream selector for its token (sum of
@@ -180,26 +182,47 @@ cudaError_t launch_moe_softmax_topk(const float *logits, uint32_t n_tokens, uint
     return cudaGetLastError();
 }
 
+__device__ __forceinline__ float silu_mul_one(float g, float u) { return g / (1.0f + expf(-g)) * u; }
+
 __global__ void silu_mul_kernel(const float *gate, const float *up, float *out, uint32_t n) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const float g = gate[i];
-    out[i] = g / (1.0f + expf(-g)) * up[i];
+    out[i] = silu_mul_one(gate[i], up[i]);
+}
+
+// Four elements per thread with 16-byte accesses (all three arrays 16-byte aligned); grid-stride.
+__global__ void __launch_bounds__(256) silu_mul_vec4_kernel(const float4 *gate, const float4 *up, float4 *out, uint32_t n4) {
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += gridDim.x * blockDim.x) {
+        const float4 g = __ldg(gate + i), u = __ldg(up + i);
+        out[i] = make_float4(silu_mul_one(g.x, u.x), silu_mul_one(g.y, u.y), silu_mul_one(g.z, u.z), silu_mul_one(g.w, u.w));
+    }
 }
 
 cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint32_t n, cudaStream_t st) {
+    const uint32_t n4 = n / 4;
+    if (n4 && ((((uintptr_t)gate | (uintptr_t)up | (uintptr_t)out) & 15u) == 0)) {
+        uint32_t blocks = (n4 + 255) / 256;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        silu_mul_vec4_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const float4 *>(gate), reinterpret_cast<const float4 *>(up),
+                                                     reinterpret_cast<float4 *>(out), n4);
+        if (n % 4) silu_mul_kernel<<<1, 32, 0, st>>>(gate + 4 * n4, up + 4 * n4, out + 4 * n4, n % 4);
+        return cudaGetLastError();
+    }
     silu_mul_kernel<<<(n + 255) / 256, 256, 0, st>>>(gate, up, out, n);
     return cudaGetLastError();
 }
 
+// `local_ids` (optional, expert-sharded form): slots whose entry is kNotLocal belong to another rank's experts;
+// their rows of y were never written here and are not read.
 __global__ void moe_weighted_reduce_kernel(const float *w, const float *y, const float *sh_logit, const float *y_shared,
-                                           const float *residual, float *out, uint32_t n_tokens, uint32_t top_k,
-                                           uint32_t h) {
+                                           const float *residual, const uint32_t *local_ids, float *out,
+                                           uint32_t n_tokens, uint32_t top_k, uint32_t h) {
     const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x, t = blockIdx.y;
     if (c >= h || t >= n_tokens) return;
     float acc = 0.0f;
     for (uint32_t k = 0; k < top_k; k++) {
         const size_t slot = (size_t)t * top_k + k;
+        if (local_ids && local_ids[slot] == kNotLocal) continue;
         acc += w[slot] * y[slot * h + c];
     }
     if (y_shared) {
@@ -211,10 +234,27 @@ __global__ void moe_weighted_reduce_kernel(const float *w, const float *y, const
 }
 
 cudaError_t launch_moe_weighted_reduce(const float *w, const float *y, const float *sh_logit, const float *y_shared,
-                                       const float *residual, float *out, uint32_t n_tokens, uint32_t top_k, uint32_t h,
-                                       cudaStream_t st) {
+                                       const float *residual, const uint32_t *local_ids, float *out, uint32_t n_tokens,
+                                       uint32_t top_k, uint32_t h, cudaStream_t st) {
     dim3 grid((h + 255) / 256, n_tokens);
-    moe_weighted_reduce_kernel<<<grid, 256, 0, st>>>(w, y, sh_logit, y_shared, residual, out, n_tokens, top_k, h);
+    moe_weighted_reduce_kernel<<<grid, 256, 0, st>>>(w, y, sh_logit, y_shared, residual, local_ids, out, n_tokens, top_k, h);
+    return cudaGetLastError();
+}
+
+// Expert-sharded routing: this rank owns the experts [lo, lo + count).  Global ids become local ones (id - lo);
+// entries of other ranks' experts become kNotLocal, which every routed kernel treats as "no expert" (no tile is
+// built for it; the mat-vec form writes a zero row).
+__global__ void moe_expert_shard_route_kernel(const uint32_t *ids, uint32_t *local_ids, uint32_t n, uint32_t lo,
+                                              uint32_t count) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint32_t id = ids[i];
+    local_ids[i] = (id >= lo && id - lo < count) ? id - lo : kNotLocal;
+}
+
+cudaError_t launch_moe_expert_shard_route(const uint32_t *ids, uint32_t *local_ids, uint32_t n, uint32_t lo, uint32_t count,
+                                          cudaStream_t st) {
+    moe_expert_shard_route_kernel<<<(n + 255) / 256, 256, 0, st>>>(ids, local_ids, n, lo, count);
     return cudaGetLastError();
 }
 

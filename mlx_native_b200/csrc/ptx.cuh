@@ -60,7 +60,9 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort, uint32_t *status,
                                           uint32_t code, uint32_t sleep_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = global_timer_ns();
+    // The wall clock is only looked at every 64 polls, and for the first time after 64 polls: reading it costs
+    // hundreds of cycles, which a wait that is about to succeed must not pay.
+    uint64_t t0 = 0;
     for (uint32_t polls = 1;; polls++) {
         if (sleep_ns == 0xFFFFFFFFu) {  // pure spin (lowest wake-up latency, costs issue slots)
             if (mbar_try_wait(bar, parity)) return true;
@@ -70,7 +72,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
         }
         if ((polls & 63u) == 0) {
             if (*abort) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) break;
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) break;
         }
     }
     *abort = 1;

@@ -18,9 +18,11 @@
 #include <cuda_fp16.h>
 
 #include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "tensor_map.cuh"
 
 namespace mlxn {
 
@@ -232,7 +234,7 @@ __global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *x
 // qmm_tc
 // =================================================================================================
 constexpr int kTcDequantWarps = 16;  // two sets of 8: set s dequantises the K stages with st % 2 == s
-constexpr int kTcThreads = (kTcDequantWarps + 2) * 32;  // + producer warp + MMA warp
+constexpr int kTcThreads = (kTcDequantWarps + 4) * 32;  // + activation producer, MMA, weight producer, second MMA warp
 constexpr int kTcRowsW = 128;                           // weight rows per tile (UMMA M)
 
 template <int T> struct TcTraits;
@@ -468,6 +470,7 @@ struct TcCfg {
     uint32_t n_wt;        // weight-row tiles, ceil(n / 128)
     uint32_t ntiles;      // activation tiles: the count (dense) or its bound (routed: the list's length is read on the device)
     uint32_t ksplit;      // K split factor (1 or 2)
+    uint32_t raw_tma;     // raw weight stages arrive as one tensor copy each (needs `aligned`); otherwise 16-byte cp.async
 };
 
 constexpr int kTcAStages = 4;      // ring of dequantised weight stages held in tensor memory
@@ -484,19 +487,26 @@ constexpr int kTcTmemCols = 512;
 // The dequantised weights never touch shared memory: its bandwidth is the scarce resource here (the tensor
 // core already reads the whole activation tile from it for every MMA).
 template <int T, int NT>
-__global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, const TcCfg c, const uint8_t *xpack) {
+__global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, const TcCfg c, const uint8_t *xpack,
+                                                                const __grid_constant__ CUtensorMap wmap) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     // tensor-core operand tiles need 1024-byte alignment (128-byte swizzle atoms): align by hand
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES, KR = TcTraits<T>::KR;
     constexpr int kMaxB = 6, kMaxRaw = 6;
+    constexpr int kNumMma = NT <= 128 ? 2 : 1;   // issuing threads, each with its own accumulator
     __shared__ __align__(8) uint64_t a_full[kTcAStages], stage_done[kTcAStages], b_full[kMaxB];
     __shared__ __align__(8) uint64_t raw_full[kMaxRaw], raw_empty[kMaxRaw], acc_full, acc_empty, orow_ready[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile uint32_t abort_flag;
     __shared__ int32_t orow[2][NT];
 
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // Warps 0-3 are the four single-thread roles (one per scheduler partition, and the lowest warp numbers, so that
+    // they are served before the dequantising warps whenever both have an instruction ready: these threads are the
+    // critical path and lose hundreds of cycles per K stage otherwise); warps 4-19 dequantise.
+    constexpr uint32_t kWarpActs = 0, kWarpMma0 = 1, kWarpWeights = 2, kWarpMma1 = 3, kCtrlWarps = 4;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t tid = threadIdx.x - kCtrlWarps * 32;   // index among the dequantising threads (wraps for warps 0-3)
     const uint32_t row_bytes = (a.k / QK) * BB;
 
     // ---- work items: (weight-row tile, K split, token tile), weight tile fastest; CTA b takes items b, b + grid, ...
@@ -509,22 +519,40 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         uint32_t tt, e, mt, n0, r_lo, nraw, nst, nck, kc_lo;
         const uint8_t *wbase;
     };
+    // routed: the (expert, row tile) pairs of the CTA's first items, fetched once (a lookup per item would put a
+    // global-memory round trip in front of every role's start on the item)
+    constexpr uint32_t kMetaItems = 32;
+    __shared__ uint32_t meta[kMetaItems][2];
+    if (a.hids && threadIdx.x < kMetaItems) {
+        const uint32_t item = blockIdx.x + threadIdx.x * gridDim.x;
+        if (item < total_items) {
+            const uint32_t tt = item / (c.n_wt * c.ksplit);
+            meta[threadIdx.x][0] = a.tiles[1 + 2 * tt];
+            meta[threadIdx.x][1] = a.tiles[2 + 2 * tt];
+        }
+    }
     auto load_item = [&](uint32_t item) -> Item {
         Item it;
-        const uint32_t wt = item % c.n_wt, rest = item / c.n_wt;
-        const uint32_t z = rest % c.ksplit;
-        it.tt = rest / c.ksplit;
+        const uint32_t rest = item / c.n_wt, wt = item - rest * c.n_wt;
+        const uint32_t z = c.ksplit == 1 ? 0u : rest % c.ksplit;
+        it.tt = c.ksplit == 1 ? rest : rest / c.ksplit;
         it.e = 0;
         it.mt = it.tt;
         if (a.hids) {
-            it.e = a.tiles[1 + 2 * it.tt];
-            it.mt = a.tiles[2 + 2 * it.tt];
+            const uint32_t li = (item - blockIdx.x) / gridDim.x;   // the CTA's li-th item
+            if (li < kMetaItems) {
+                it.e = meta[li][0];
+                it.mt = meta[li][1];
+            } else {
+                it.e = a.tiles[1 + 2 * it.tt];
+                it.mt = a.tiles[2 + 2 * it.tt];
+            }
         }
         it.wbase = a.w + (size_t)it.e * a.expert_stride;
         it.n0 = wt * kTcRowsW;
         // split-K: this item takes the raw stages [r_lo, r_hi) of K and adds its part of the tile into y
-        it.r_lo = (uint32_t)(((uint64_t)z * nraw_all) / c.ksplit);
-        const uint32_t r_hi = (uint32_t)(((uint64_t)(z + 1) * nraw_all) / c.ksplit);
+        it.r_lo = c.ksplit == 1 ? 0u : (z * nraw_all) / c.ksplit;   // (ksplit <= 2 and nraw_all < 2^24: no overflow)
+        const uint32_t r_hi = c.ksplit == 1 ? nraw_all : ((z + 1) * nraw_all) / c.ksplit;
         it.nraw = r_hi - it.r_lo;
         it.kc_lo = it.r_lo * (KR / 64);
         it.nst = min((a.k + 127) / 128, r_hi * (KR / 128)) - it.r_lo * (KR / 128);   // tensor-memory stages
@@ -532,7 +560,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         return it;
     };
 
-    if (tid == 0) {
+    if (threadIdx.x == 0) {
         abort_flag = 0;
         for (uint32_t s = 0; s < kTcAStages; s++) {
             mbar_init(&a_full[s], kTcDequantWarps / 2);  // the eight warps of one set
@@ -540,15 +568,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         }
         for (uint32_t s = 0; s < c.b_stages; s++) mbar_init(&b_full[s], 1);
         for (uint32_t s = 0; s < c.raw_slots; s++) {
-            mbar_init(&raw_full[s], kTcDequantWarps * 32);  // one asynchronous arrival per copying thread
+            // one asynchronous arrival per copying thread, or the weight producer's single arrival with the byte count
+            mbar_init(&raw_full[s], c.raw_tma ? 1u : kTcDequantWarps * 32);
             mbar_init(&raw_empty[s], kTcDequantWarps);
         }
-        mbar_init(&acc_full, 1);
+        mbar_init(&acc_full, kNumMma);
         mbar_init(&acc_empty, kTcDequantWarps);
         for (int s = 0; s < 2; s++) mbar_init(&orow_ready[s], kTcDequantWarps);
         mbar_init_fence();
     }
-    if (warp == kTcDequantWarps + 1) {  // MMA warp owns tensor memory
+    if (warp == kWarpMma0) {  // the first MMA warp owns tensor memory
         tmem_alloc(&tmem_base_s, kTcTmemCols);
         tmem_relinquish();
     }
@@ -563,8 +592,22 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     // slots); the dequantising warps space their polls out
     const uint32_t wmode_cr = (c.debug & 32u) ? 0u : 0xFFFFFFFFu;
     const uint32_t wmode_dq = (c.debug & 16u) ? 0xFFFFFFFFu : 0u;
+#ifdef MLXN_TC_TRACE
+    // experiment: CTA 0 logs (event, clock) pairs into y (use with debug 256, which keeps the epilogue from writing y)
+    uint32_t trace_n = 0;
+    auto TRACE = [&](uint32_t role, uint32_t code, uint32_t x) {
+        if ((c.debug & 512u) && blockIdx.x == 0 && lane == 0 && trace_n < 500) {
+            uint32_t *t = reinterpret_cast<uint32_t *>(a.y) + role * 1024 + 2 * trace_n;
+            t[0] = (code << 16) | (x & 0xFFFFu);
+            t[1] = (uint32_t)clock64();
+            trace_n++;
+        }
+    };
+#else
+#define TRACE(role, code, x) ((void)0)
+#endif
 
-    if (warp == kTcDequantWarps) {
+    if (warp == kWarpActs) {
         // ======================= producer warp: bulk copies of the packed activation tiles =======================
         // Every K stage owns two consecutive chunk slots of the ring (a K tail of 64 leaves its second one empty;
         // the producer still arrives on it so that the slot's phase moves on).  Chunk slot G reuses the place of
@@ -596,53 +639,103 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                 }
             }
         }
-    } else if (warp == kTcDequantWarps + 1) {
-        // ======================= MMA warp: one thread issues tcgen05.mma =======================
-        // A lone thread runs at a fraction of an instruction per cycle, and every K stage passes through this
-        // loop, so it holds nothing but the waits, eight MMAs and one commit.
-        if (lane == 0) {
+    } else if (warp == kWarpWeights) {
+        // ======================= weight producer warp: one tensor copy per raw stage =======================
+        // The weights as a 3-D tensor of 32-bit words [expert][row][row_bytes / 4]; a raw stage is the box
+        // (1, 128 rows, seg_stride / 4 words) at the stage's K offset, rounded down to 16 bytes for Q6_K
+        // (210-byte super-blocks; readers skip the lead-in).  Rows past n arrive as zeros.  The copies run
+        // raw_slots - 1 stages ahead of the dequantisation, across item boundaries.
+        if (c.raw_tma && lane == 0) {
+            const uint32_t R = c.raw_slots;
+            uint32_t slot = 0, ph = 0, requested = 0;
+            bool ok = true;
+            for (uint32_t item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+                const Item it = load_item(item);
+                for (uint32_t r = 0; r < it.nraw; r++, requested++) {
+                    if (requested >= R &&
+                        !mbar_wait(&raw_empty[slot], ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_cr)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t kb = ((it.r_lo + r) * (KR / QK) * BB) & ~15u;   // byte offset of the stage in the row
+                    mbar_expect_tx(&raw_full[slot], raw_stage_bytes);
+                    asm volatile(
+                        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                        ::"r"(smem_base + c.raw_off + slot * raw_stage_bytes), "l"(&wmap), "r"(kb >> 2), "r"(it.n0), "r"(it.e),
+                          "r"(smem_u32(&raw_full[slot]))
+                        : "memory");
+                    if (++slot == R) { slot = 0; ph ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == kWarpMma0 || warp == kWarpMma1) {
+        // ======================= MMA warps: one thread each issues tcgen05.mma =======================
+        // A lone thread gets through one of these instructions (MMA, commit, barrier test) every 50-100 cycles, and
+        // a K stage costs about thirteen of them, which bounds a narrow tile (NT <= 128: the MMAs themselves are
+        // short) well before the tensor core does.  So narrow tiles use two issuing threads: thread w takes the K
+        // stages st with st % 2 == w and accumulates them in its own accumulator (columns [w NT, (w+1) NT)); the
+        // epilogue adds the two.  NT = 256 keeps one thread (tensor memory has no room for a second accumulator,
+        // and there the MMAs are long enough to hide the issue).
+        const uint32_t w = warp == kWarpMma0 ? 0u : 1u;
+        if (lane == 0 && w < (uint32_t)kNumMma) {
             constexpr uint32_t idesc = umma_idesc_f16(kTcRowsW, NT);
             const uint64_t bd0 = umma_desc_k_sw128(smem_base + c.b_off);
             const uint64_t b_step = b_bytes >> 4;  // descriptor address field is in 16-byte units
             const bool do_mma = !(c.debug & 4u);
-            uint64_t bd = bd0;
-            uint32_t sa = 0, aph = 0, sb = 0, bph = 0, nitem = 0;
+            const uint32_t d_col = tmem_d + w * NT;
+            uint32_t sa = 0, aph = 0, sb = 0, bph = 0, nitem = 0;   // ring positions of the stage being looked at
             bool ok = true;
             for (uint32_t item = blockIdx.x; ok && item < total_items; item += gridDim.x, nitem++) {
                 const Item it = load_item(item);
-                // the accumulator of the item before has been read back
+                // the accumulators of the item before have been read back
                 if (nitem > 0 &&
                     !mbar_wait(&acc_empty, (nitem - 1) & 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_cr))
                     break;
                 tc_fence_after();
+                TRACE(1 + 3 * w, 1, nitem);
+                bool issued = false;
                 for (uint32_t st = 0; st < it.nst; st++) {
-                    if (!mbar_wait(&a_full[sa], aph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) { ok = false; break; }
-                    if (!mbar_wait(&b_full[sb], bph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t a_col = tmem_d + kTcAColBase + sa * kTcACols;
-                    if (do_mma) {
-                        umma_f16_ts(tmem_d, a_col, bd, idesc, st != 0 ? 1u : 0u);
-                        umma_f16_ts(tmem_d, a_col + 8, bd + 2, idesc, 1u);
-                        umma_f16_ts(tmem_d, a_col + 16, bd + 4, idesc, 1u);
-                        umma_f16_ts(tmem_d, a_col + 24, bd + 6, idesc, 1u);
-                    }
-                    bd += b_step;
-                    if (++sb == c.b_stages) { sb = 0; bph ^= 1u; bd = bd0; }
-                    if (2 * st + 1 < it.nck) {
+                    if ((st & (uint32_t)(kNumMma - 1)) == w) {
+                        if (!mbar_wait(&a_full[sa], aph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) { ok = false; break; }
+                        TRACE(1 + 3 * w, 2, st);
                         if (!mbar_wait(&b_full[sb], bph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) { ok = false; break; }
+                        tc_fence_after();
+                        TRACE(1 + 3 * w, 4, st);
+                        const uint32_t a_col = tmem_d + kTcAColBase + sa * kTcACols;
+                        const uint64_t bd = bd0 + sb * b_step;
                         if (do_mma) {
-                            umma_f16_ts(tmem_d, a_col + 32, bd, idesc, 1u);
-                            umma_f16_ts(tmem_d, a_col + 40, bd + 2, idesc, 1u);
-                            umma_f16_ts(tmem_d, a_col + 48, bd + 4, idesc, 1u);
-                            umma_f16_ts(tmem_d, a_col + 56, bd + 6, idesc, 1u);
+                            umma_f16_ts(d_col, a_col, bd, idesc, issued ? 1u : 0u);
+                            umma_f16_ts(d_col, a_col + 8, bd + 2, idesc, 1u);
+                            umma_f16_ts(d_col, a_col + 16, bd + 4, idesc, 1u);
+                            umma_f16_ts(d_col, a_col + 24, bd + 6, idesc, 1u);
                         }
+                        issued = true;
+                        if (2 * st + 1 < it.nck) {
+                            const uint32_t sb1 = sb + 1 == c.b_stages ? 0u : sb + 1;
+                            const uint32_t bph1 = sb + 1 == c.b_stages ? bph ^ 1u : bph;
+                            if (!mbar_wait(&b_full[sb1], bph1, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_cr)) { ok = false; break; }
+                            const uint64_t bd1 = bd0 + sb1 * b_step;
+                            if (do_mma) {
+                                umma_f16_ts(d_col, a_col + 32, bd1, idesc, 1u);
+                                umma_f16_ts(d_col, a_col + 40, bd1 + 2, idesc, 1u);
+                                umma_f16_ts(d_col, a_col + 48, bd1 + 4, idesc, 1u);
+                                umma_f16_ts(d_col, a_col + 56, bd1 + 6, idesc, 1u);
+                            }
+                        }
+                        TRACE(1 + 3 * w, 5, st);
+                        umma_commit(&stage_done[sa]);  // frees the stage's weights and its two activation chunks
+                        TRACE(1 + 3 * w, 3, st);
                     }
-                    bd += b_step;   // the stage's second chunk slot is passed over whether it held data or not
-                    if (++sb == c.b_stages) { sb = 0; bph ^= 1u; bd = bd0; }
-                    umma_commit(&stage_done[sa]);  // frees the stage's weights and its two activation chunks
-                    if (st + 1 == it.nst) umma_commit(&acc_full);
+                    // on to the next stage's ring places (two activation chunk slots per stage, used or not)
+                    sb += 2;
+                    if (sb >= c.b_stages) { sb -= c.b_stages; bph ^= 1u; }
                     if (++sa == kTcAStages) { sa = 0; aph ^= 1u; }
                 }
+                if (!ok) break;
+                // this thread's share of the item is issued: its accumulator is complete when these MMAs are
+                if (issued) umma_commit(&acc_full);
+                else mbar_arrive(&acc_full);
             }
         }
         __syncwarp();
@@ -652,7 +745,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         // stage times for each of its turns.  Within a set, thread (warp w, lane l) owns weight row
         // 32 (w % 4) + l of the tile -- the tensor-memory lane its warp may address -- and the 64-element half
         // (w / 4) % 2 of the stage: thirty-two packed f16 pairs = one 32-column store.
-        const uint32_t q4 = warp & 3u, half = (warp >> 2) & 1u, set = warp >> 3;
+        const uint32_t dw = warp - kCtrlWarps;   // 0..15
+        const uint32_t q4 = dw & 3u, half = (dw >> 2) & 1u, set = dw >> 3;
         const uint32_t rr = q4 * 32 + lane;
         // Raw weight rows are short (144..272 bytes per stage and row), too short for one bulk copy each to be
         // efficient, so all dequantising threads stream them as 16-byte cp.async chunks, a few raw stages ahead
@@ -686,7 +780,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             q_nraw = it.nraw;
             q_rlo = it.r_lo;
         };
-        if (q_item < total_items) open_request_item();
+        if (!c.raw_tma && q_item < total_items) open_request_item();
         auto issue_raw = [&](uint32_t r, uint32_t slot) {
             const uint32_t k0 = r * KR;
             const uint32_t seg_bytes = (min((uint32_t)KR, a.k - k0) / QK) * BB;
@@ -713,36 +807,26 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         uint32_t nitem = 0;
         bool ok = true;
         const uint32_t a_dst = tmem_d + ((q4 * 32) << 16) + kTcAColBase + 32 * half;
-        const uint32_t g = warp >> 2;
+        const uint32_t g = dw >> 2;
         for (uint32_t item = blockIdx.x; ok && item < total_items; item += gridDim.x, nitem++) {
             const Item it = load_item(item);
             const uint32_t n0 = it.n0;
             const bool row_ok = n0 + rr < a.n;
             const uint32_t row_lo4 = (uint32_t)((uintptr_t)(it.wbase + (size_t)(n0 + rr) * row_bytes) & 15u);
-            // the item's output-row table (double-buffered: the one of the item before may still be in use by a
-            // warp that is behind); read again only in the epilogue
-            {
-                int32_t *tab = orow[nitem & 1u];
-                const uint32_t nrows = a.hids ? a.htpe[it.e] : a.m;
-                for (uint32_t i = tid; i < NT; i += kTcDequantWarps * 32) {
-                    int32_t o = -1;
-                    const uint32_t row = it.mt * NT + i;
-                    if (row < nrows) {
-                        if (a.hids) {
-                            const int32_t id = a.hids[(size_t)it.e * a.hids_stride + row];
-                            if (id >= 0 && (uint32_t)id < a.total_rows) o = id;
-                        } else {
-                            o = (int32_t)row;
-                        }
-                    }
-                    tab[i] = o;
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&orow_ready[nitem & 1u]);
+            // the item's output-row table: every thread fetches the entries it will publish now (the loads stay in
+            // flight behind the K loop) and stores them just before the epilogue
+            static_assert(NT <= kTcDequantWarps * 32, "one output-row entry per thread");
+            if (q4 == 0 && half == 0) TRACE(2 + set, 1, nitem);
+            uint32_t o_nrows = a.m;
+            int32_t o_id = -1;
+            const uint32_t o_row = it.mt * NT + tid;
+            if (a.hids && tid < NT) {
+                o_nrows = a.htpe[it.e];
+                if (o_row < a.hids_stride) o_id = a.hids[(size_t)it.e * a.hids_stride + o_row];
             }
             for (uint32_t r = 0; ok && r < it.nraw; r++) {
                 // keep D raw stages requested ahead of the one being read
-                while (q_item < total_items && requested - consumed < D + 1) {
+                while (!c.raw_tma && q_item < total_items && requested - consumed < D + 1) {
                     if (requested >= R &&
                         !mbar_wait(&raw_empty[islot], iph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) {
                         ok = false;
@@ -753,11 +837,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                     if (++islot == R) { islot = 0; iph ^= 1u; }
                     if (++q_r == q_nraw) {
                         q_item += gridDim.x;
-                        if (q_item < total_items) open_request_item();
+                        if (!c.raw_tma && q_item < total_items) open_request_item();
                     }
                 }
                 if (!ok) break;
                 if (!mbar_wait(&raw_full[rs], rph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, wmode_dq)) { ok = false; break; }
+                if (q4 == 0 && half == 0) TRACE(2 + set, 2, r);
                 const uint32_t st = 2 * r + set;       // this set's K stage inside raw stage r
                 if (st < it.nst) {
                     const uint32_t J = J0 + st;        // its number in the CTA's whole run
@@ -770,6 +855,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                         break;
                     }
                     tc_fence_after();
+                    if (q4 == 0 && half == 0) TRACE(2 + set, 3, r);
                     const uint32_t r_abs = it.r_lo + r;
                     const uint32_t pre = (row_lo4 + ((r_abs * KR) / QK) * BB) & 15u;
                     const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
@@ -807,11 +893,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                         }
                     }
                 }
+                    if (q4 == 0 && half == 0) TRACE(2 + set, 8, r);
                     tmem_st_32x32_x32(a_dst + sa * kTcACols, regs);
                     tmem_st_wait();
+                    if (q4 == 0 && half == 0) TRACE(2 + set, 9, r);
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&a_full[sa]);
+                    if (q4 == 0 && half == 0) TRACE(2 + set, 4, r);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&raw_empty[rs]);  // this warp is done reading the raw stage
@@ -821,15 +910,40 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             if (!ok) break;
             J0 += it.nst;
             // ---- epilogue: TMEM -> registers -> y ----
+            {   // double-buffered: the table of the item before may still be in use by a warp that is behind
+                int32_t *wtab = orow[nitem & 1u];
+                if (tid < NT) {
+                    int32_t o = -1;
+                    if (o_row < o_nrows) {
+                        if (a.hids) {
+                            if (o_id >= 0 && (uint32_t)o_id < a.total_rows) o = o_id;
+                        } else {
+                            o = (int32_t)o_row;
+                        }
+                    }
+                    wtab[tid] = o;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&orow_ready[nitem & 1u]);
+            }
             if (!mbar_wait(&orow_ready[nitem & 1u], (nitem >> 1) & 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) break;
+            if (q4 == 0 && half == 0) TRACE(2 + set, 5, nitem);
             if (!mbar_wait(&acc_full, nitem & 1u, &abort_flag, a.status, ST_WAIT_MMA_TIMEOUT, wmode_dq)) break;
             tc_fence_after();
+            if (q4 == 0 && half == 0) TRACE(2 + set, 6, nitem);
             const int32_t *tab = orow[nitem & 1u];
             const uint32_t wrow = n0 + rr;
 #pragma unroll 1
             for (uint32_t col = g * 32; col < NT; col += (kTcDequantWarps / 4) * 32) {
                 uint32_t v[32];
                 tmem_ld_32x32(tmem_d + ((q4 * 32) << 16) + col, v);
+                if (kNumMma == 2 && it.nst >= 2) {   // the odd K stages went into the second accumulator
+                    uint32_t v1[32];
+                    tmem_ld_32x32(tmem_d + ((q4 * 32) << 16) + NT + col, v1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v1[j]));
+                }
                 tmem_ld_wait();
                 if (wrow < a.n && !(c.debug & 256u)) {
 #pragma unroll
@@ -845,6 +959,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty);   // the MMA warp may start the next item's accumulation
+            if (q4 == 0 && half == 0) TRACE(2 + set, 7, nitem);
         }
     }
     if (abort_flag) {  // let copies in flight land before the CTA's shared memory is released
@@ -852,7 +967,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == kTcDequantWarps + 1) {
+    if (warp == kWarpMma0) {
         tc_fence_after();
         tmem_dealloc(tmem_d, kTcTmemCols);
     }
@@ -944,6 +1059,30 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     c.nchunks = (a.k + 63) / 64;
     c.seg_stride = round_up_u((KR / QK) * BB + 15, 16) + 16;
     if ((c.seg_stride / 16) % 2 == 0) c.seg_stride += 16;  // odd multiple of 16 B: rows spread over the banks
+    // Aligned weights arrive by tensor copies: one per raw stage instead of 16-byte copies from every thread.
+    // The box is the stage's bytes of 128 rows (Q6_K: 224 bytes cover 210 plus the lead-in; 240 keeps the row
+    // pitch an odd multiple of 16).  A 3-D map [expert][row][words]; dense calls are one expert.
+    alignas(64) CUtensorMap wmap;
+    memset(&wmap, 0, sizeof(wmap));
+    if (c.aligned && !getenv("MLXN_TC_NO_TMA")) {
+        EncodeTiledFn enc = encode_tiled_fn();
+        const uint32_t row_bytes = (a.k / QK) * BB;
+        const uint32_t box_bytes = T == GT_Q6_K ? 240u : (uint32_t)((KR / QK) * BB);
+        const uint32_t n_exp = routed ? a.n_experts : 1u;
+        const uint64_t estride = routed ? a.expert_stride : (uint64_t)a.n * row_bytes;
+        if (enc && n_exp >= 1 && (uint64_t)row_bytes * a.n <= estride) {
+            const cuuint64_t gdim[3] = {row_bytes / 4, a.n, n_exp};
+            const cuuint64_t gstride[2] = {row_bytes, estride};
+            const cuuint32_t box[3] = {box_bytes / 4, (cuuint32_t)kTcRowsW, 1};
+            const cuuint32_t estr[3] = {1, 1, 1};
+            if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t *>(a.w), gdim, gstride, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS) {
+                c.raw_tma = 1;
+                c.seg_stride = box_bytes;
+            }
+        }
+    }
     const uint32_t b_bytes = NT * 128;  // one 64-wide K chunk of the activation tile
     const uint32_t raw_slot = kTcRowsW * c.seg_stride;
     const uint32_t limit = 222 * 1024;  // + 1 KB alignment slack + ~3 KB of static shared memory <= 227 KB
@@ -1013,7 +1152,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     }
     if (items < ctas) ctas = (uint32_t)items;
     if (ctas == 0) return cudaSuccess;
-    qmm_tc_kernel<T, NT><<<ctas, kTcThreads, smem, st>>>(a, c, xpack);
+    qmm_tc_kernel<T, NT><<<ctas, kTcThreads, smem, st>>>(a, c, xpack, wmap);
     (*launches)++;
     return cudaGetLastError();
 }

@@ -23,7 +23,7 @@
 //
 // Supported here: Q4_0, Q8_0 (k % 256 == 0) and Q6_K (k % 2048 == 0), dense form, 16-byte aligned weight rows.
 // Everything else takes the SIMT kernels.
-#include <cuda.h>  // CUtensorMap (types only; the encoder is fetched through the runtime, no libcuda link)
+#include "tensor_map.cuh"  // CUtensorMap + the encoder, fetched through the runtime (no libcuda link)
 
 #include <cstdio>
 #include <cstdlib>
@@ -639,10 +639,7 @@ size_t qmv_tc_scratch_bytes(const QmvArgs &a) {
     return vt_align((size_t)(a.k / 64) * 2048, 1024) + vt_align((size_t)(a.k / kVtUnitK) * 576, 1024);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn encode_tiled_fn() {
+EncodeTiledFn encode_tiled_fn() {
     static EncodeTiledFn fn = [] {
         void *p = nullptr;
         cudaDriverEntryPointQueryResult q;

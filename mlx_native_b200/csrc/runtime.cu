@@ -38,8 +38,10 @@ cudaError_t launch_moe_softmax_topk(const float *logits, uint32_t n_tokens, uint
                                     uint32_t *out_ids, float *out_w, cudaStream_t st);
 cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint32_t n, cudaStream_t st);
 cudaError_t launch_moe_weighted_reduce(const float *w, const float *y, const float *sh_logit, const float *y_shared,
-                                       const float *residual, float *out, uint32_t n_tokens, uint32_t top_k, uint32_t h,
-                                       cudaStream_t st);
+                                       const float *residual, const uint32_t *local_ids, float *out, uint32_t n_tokens,
+                                       uint32_t top_k, uint32_t h, cudaStream_t st);
+cudaError_t launch_moe_expert_shard_route(const uint32_t *ids, uint32_t *local_ids, uint32_t n, uint32_t lo, uint32_t count,
+                                          cudaStream_t st);
 }  // namespace mlxn
 
 using namespace mlxn;
@@ -1480,30 +1482,69 @@ extern "C" int mlxn_silu_mul(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device 
     return MLXN_OK;
 }
 
-extern "C" int mlxn_moe_weighted_reduce(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *expert_w,
-                                        mlxn_buffer *y_expert, mlxn_buffer *sh_logit, mlxn_buffer *y_shared,
-                                        mlxn_buffer *residual, mlxn_buffer *out, uint32_t n_tokens, uint32_t top_k,
-                                        uint32_t h) {
+static int moe_weighted_reduce_impl(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *expert_w,
+                                   mlxn_buffer *y_expert, mlxn_buffer *sh_logit, mlxn_buffer *y_shared,
+                                   mlxn_buffer *residual, mlxn_buffer *local_ids, mlxn_buffer *out, uint32_t n_tokens,
+                                   uint32_t top_k, uint32_t h) {
     int rc = check_handles(enc, dev, {expert_w, y_expert, out});
     if (rc) return rc;
     if (n_tokens == 0 || top_k == 0 || h == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_weighted_reduce: n_tokens, top_k and h must all be > 0");
     if (expert_w->len < (size_t)n_tokens * top_k * 4 || y_expert->len < (size_t)n_tokens * top_k * h * 4 ||
         out->len < (size_t)n_tokens * h * 4 || (y_shared && y_shared->len < (size_t)n_tokens * h * 4) ||
-        (sh_logit && sh_logit->len < (size_t)n_tokens * 4) || (residual && residual->len < (size_t)n_tokens * h * 4))
+        (sh_logit && sh_logit->len < (size_t)n_tokens * 4) || (residual && residual->len < (size_t)n_tokens * h * 4) ||
+        (local_ids && local_ids->len < (size_t)n_tokens * top_k * 4))
         return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_weighted_reduce: a buffer is too small");
     if ((rc = touch_kernel(reg, dev, "moe_weighted_reduce_f32"))) return rc;
     if ((rc = op_begin(enc, {{expert_w, false}, {y_expert, false}, {out, true}, {sh_logit, false}, {y_shared, false},
-                             {residual, false}})))
+                             {residual, false}, {local_ids, false}})))
         return rc;
     CUDA_TRY(launch_moe_weighted_reduce(reinterpret_cast<const float *>(expert_w->dev()),
                                         reinterpret_cast<const float *>(y_expert->dev()),
                                         sh_logit ? reinterpret_cast<const float *>(sh_logit->dev()) : nullptr,
                                         y_shared ? reinterpret_cast<const float *>(y_shared->dev()) : nullptr,
                                         residual ? reinterpret_cast<const float *>(residual->dev()) : nullptr,
+                                        local_ids ? reinterpret_cast<const uint32_t *>(local_ids->dev()) : nullptr,
                                         reinterpret_cast<float *>(out->dev()), n_tokens, top_k, h, enc->stream),
              "moe_weighted_reduce launch");
     g_launches.fetch_add(1);
     g_dispatch.fetch_add(1);
     g_last_kernel = "moe_weighted_reduce";
+    return MLXN_OK;
+}
+
+extern "C" int mlxn_moe_weighted_reduce(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *expert_w,
+                                        mlxn_buffer *y_expert, mlxn_buffer *sh_logit, mlxn_buffer *y_shared,
+                                        mlxn_buffer *residual, mlxn_buffer *out, uint32_t n_tokens, uint32_t top_k,
+                                        uint32_t h) {
+    return moe_weighted_reduce_impl(enc, reg, dev, expert_w, y_expert, sh_logit, y_shared, residual, nullptr, out, n_tokens,
+                                    top_k, h);
+}
+
+// Expert-sharded form (no upstream counterpart): the partial sum over this rank's experts only.
+extern "C" int mlxn_moe_weighted_reduce_local(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *expert_w,
+                                              mlxn_buffer *y_expert, mlxn_buffer *local_ids, mlxn_buffer *out,
+                                              uint32_t n_tokens, uint32_t top_k, uint32_t h) {
+    if (!local_ids) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_weighted_reduce_local: local_ids is null");
+    return moe_weighted_reduce_impl(enc, reg, dev, expert_w, y_expert, nullptr, nullptr, nullptr, local_ids, out, n_tokens,
+                                    top_k, h);
+}
+
+extern "C" int mlxn_moe_expert_shard_route(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *ids,
+                                           mlxn_buffer *local_ids, uint32_t n_pairs, uint32_t expert_lo,
+                                           uint32_t expert_count) {
+    (void)reg;
+    int rc = check_handles(enc, dev, {ids, local_ids});
+    if (rc) return rc;
+    if (n_pairs == 0 || expert_count == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_expert_shard_route: n_pairs and expert_count must be > 0");
+    if (ids->len < (size_t)n_pairs * 4 || local_ids->len < (size_t)n_pairs * 4)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_expert_shard_route: a buffer is too small");
+    if ((rc = op_begin(enc, {{ids, false}, {local_ids, true}}))) return rc;
+    CUDA_TRY(launch_moe_expert_shard_route(reinterpret_cast<const uint32_t *>(ids->dev()),
+                                           reinterpret_cast<uint32_t *>(local_ids->dev()), n_pairs, expert_lo, expert_count,
+                                           enc->stream),
+             "moe_expert_shard_route launch");
+    g_launches.fetch_add(1);
+    g_dispatch.fetch_add(1);
+    g_last_kernel = "moe_expert_shard_route";
     return MLXN_OK;
 }

@@ -39,3 +39,31 @@ def assemble_gathered(gathered: np.ndarray) -> np.ndarray:
     """[g, m, n/g] -> [m, n]"""
     g, m, per = gathered.shape
     return np.ascontiguousarray(np.transpose(gathered, (1, 0, 2))).reshape(m, g * per)
+
+
+# ---------------------------------------------------------------------------------------------- expert sharding
+NOT_LOCAL = 0xFFFFFFFF  # id of a (token, slot) pair whose expert lives on another rank
+
+
+def shard_experts(n_experts: int, rank: int, world: int) -> tuple[int, int]:
+    """(first expert, count) of `rank`: contiguous blocks of n_experts / world experts."""
+    if n_experts % world:
+        raise ValueError(f"n_experts ({n_experts}) is not divisible by the number of ranks ({world})")
+    per = n_experts // world
+    return rank * per, per
+
+
+def shard_expert_bytes(wq: np.ndarray, expert_stride: int, n_experts: int, rank: int, world: int) -> np.ndarray:
+    """The stacked expert weights [n_experts][expert_stride bytes] of `rank`'s experts (one contiguous byte range)."""
+    lo, cnt = shard_experts(n_experts, rank, world)
+    flat = np.ascontiguousarray(wq, dtype=np.uint8).reshape(-1)
+    if flat.size < n_experts * expert_stride:
+        raise ValueError("weight buffer too small for [n_experts, expert_stride]")
+    return flat[lo * expert_stride:(lo + cnt) * expert_stride]
+
+
+def local_expert_ids(ids: np.ndarray, lo: int, count: int) -> np.ndarray:
+    """Host mirror of `moe_expert_shard_route`: global ids -> local ids, NOT_LOCAL for other ranks' experts."""
+    ids = np.asarray(ids, dtype=np.uint32)
+    mine = (ids >= lo) & (ids < lo + count)
+    return np.where(mine, ids - np.uint32(lo), np.uint32(NOT_LOCAL)).astype(np.uint32)

@@ -1,4 +1,6 @@
-"""One gloo rank of tests/test_sharding_gloo.py: python shard_worker.py rank world port ggml_type n k m out_dir"""
+"""One gloo rank of tests/test_sharding_gloo.py:
+  python shard_worker.py rank world port ggml_type n k m out_dir        row-sharded mat-vec + all-gather
+  python shard_worker.py rank world port moe T E top_k out_dir          expert-sharded MoE FFN layer + all-reduce"""
 import os
 import sys
 
@@ -35,6 +37,62 @@ def main(rank, world, port, ggml_type, n, k, m, out_dir):
 
 
 
+def main_moe(rank, world, port, T, E, top_k, out_dir):
+    """Every rank runs the oracle on the (token, slot) pairs routed to its experts only, with its slice of the
+    stacked expert weights and local ids; the all-reduce of the partial combines must give the one-rank layer."""
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+
+    from mlx_native_b200 import sharding
+    from oracle import oracle as orc
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    hidden, ffn = 256, 256
+    rng = np.random.default_rng(1)                       # same data on every rank
+    wg = orc.quantize(orc.Q4_0, (rng.standard_normal((E * ffn, hidden)) * 0.02).astype(np.float32), rule="ggml")
+    wu = orc.quantize(orc.Q4_0, (rng.standard_normal((E * ffn, hidden)) * 0.02).astype(np.float32), rule="ggml")
+    wd = orc.quantize(orc.Q6_K, (rng.standard_normal((E * hidden, ffn)) * 0.02).astype(np.float32))
+    x = rng.standard_normal((T, hidden)).astype(np.float32)
+    ids, rw = orc.moe_softmax_topk(rng.standard_normal((T, E)).astype(np.float32), top_k)
+    flat = ids.reshape(-1)
+
+    lo, cnt = sharding.shard_experts(E, rank, world)
+    lids = sharding.local_expert_ids(flat, lo, cnt)
+    mine = np.nonzero(lids != sharding.NOT_LOCAL)[0]
+    sg, su, sd = wg.size // E, wu.size // E, wd.size // E
+    wg_l = sharding.shard_expert_bytes(wg, sg, E, rank, world)
+    wu_l = sharding.shard_expert_bytes(wu, su, E, rank, world)
+    wd_l = sharding.shard_expert_bytes(wd, sd, E, rank, world)
+    yd = np.zeros((T * top_k, hidden), dtype=np.float32)
+    if mine.size:
+        xs = x[mine // top_k]
+        g, _ = orc.qmatmul_id(orc.Q4_0, wg_l, sg, xs, lids[mine], 1, ffn, hidden, cnt)
+        u, _ = orc.qmatmul_id(orc.Q4_0, wu_l, su, xs, lids[mine], 1, ffn, hidden, cnt)
+        dn, _ = orc.qmatmul_id(orc.Q6_K, wd_l, sd, orc.silu_mul(g, u), lids[mine], 1, hidden, ffn, cnt)
+        yd[mine] = dn
+    w_loc = np.where((lids != sharding.NOT_LOCAL).reshape(T, top_k), rw, np.float32(0.0)).astype(np.float32)
+    part = torch.from_numpy(orc.moe_weighted_reduce(yd, w_loc, T, top_k, hidden).copy())
+    dist.all_reduce(part)                                # the combine step
+    # every pair belongs to exactly one rank
+    owned = torch.from_numpy((lids != sharding.NOT_LOCAL).astype(np.int32))
+    dist.all_reduce(owned)
+    if rank == 0:
+        g, _ = orc.qmatmul_id(orc.Q4_0, wg, sg, x, flat, top_k, ffn, hidden, E)
+        u, _ = orc.qmatmul_id(orc.Q4_0, wu, su, x, flat, top_k, ffn, hidden, E)
+        dn, _ = orc.qmatmul_id(orc.Q6_K, wd, sd, orc.silu_mul(g, u), flat, 1, hidden, ffn, E)
+        want = orc.moe_weighted_reduce(dn, rw, T, top_k, hidden)
+        ok = bool((owned.numpy() == 1).all()) and float(np.max(np.abs(part.numpy() - want))) <= 1e-5 * float(np.abs(want).max())
+        np.save(os.path.join(out_dir, "ok.npy"), np.array([ok]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 if __name__ == "__main__":
     a = sys.argv[1:]
+    if a[3] == "moe":
+        main_moe(int(a[0]), int(a[1]), int(a[2]), int(a[4]), int(a[5]), int(a[6]), a[7])
+        sys.exit(0)
     main(int(a[0]), int(a[1]), int(a[2]), int(a[3]), int(a[4]), int(a[5]), int(a[6]), a[7])
