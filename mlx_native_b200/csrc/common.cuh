@@ -16,6 +16,18 @@ template <int T> struct BlockTraits;
 template <> struct BlockTraits<GT_Q4_0> { static constexpr int QK = 32, BYTES = 18; };
 template <> struct BlockTraits<GT_Q8_0> { static constexpr int QK = 32, BYTES = 34; };
 template <> struct BlockTraits<GT_Q6_K> { static constexpr int QK = 256, BYTES = 210; };
+template <> struct BlockTraits<GT_Q4_K> { static constexpr int QK = 256, BYTES = 144; };
+
+// Q4_K (src/gguf/mod.rs:440-452): the 6-bit (scale, min) pair of sub-block j from the block's 12 packed bytes.
+__host__ __device__ inline void q4k_scale_min(uint32_t j, const uint8_t *scales, uint32_t &sc, uint32_t &mn) {
+    if (j < 4) {
+        sc = scales[j] & 63u;
+        mn = scales[j + 4] & 63u;
+    } else {
+        sc = (scales[j + 4] & 0x0Fu) | ((uint32_t)(scales[j - 4] >> 6) << 4);
+        mn = (uint32_t)(scales[j + 4] >> 4) | ((uint32_t)(scales[j] >> 6) << 4);
+    }
+}
 
 __host__ __device__ inline uint32_t ggml_qk(int t) {
     switch (t) {

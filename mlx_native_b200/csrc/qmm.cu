@@ -40,6 +40,18 @@ template <int T> __device__ __forceinline__ float dequant_elem(const uint8_t *ro
     } else if constexpr (T == GT_Q8_0) {
         const uint8_t *blk = row + 34u * (e >> 5);
         return half_bits_to_float(ld_u16(blk)) * (float)(int)(int8_t)blk[2 + (e & 31u)];
+    } else if constexpr (T == GT_Q4_K) {
+        // f16 d, f16 dmin, scales[12], qs[128]; sub-block j = e / 32 of the super-block, byte (j / 2) * 32 + l,
+        // low nibble for even j (src/gguf/mod.rs:582-644).  (d sc) q - (dmin m), each step rounded in f32.
+        const uint8_t *blk = row + 144u * (e >> 8);
+        const uint32_t r = e & 255u, j = r >> 5, l = r & 31u;
+        uint32_t sc, mn;
+        q4k_scale_min(j, blk + 4, sc, mn);
+        const uint32_t byte = blk[16 + 32 * (j >> 1) + l];
+        const uint32_t q = (j & 1u) ? (byte >> 4) : (byte & 15u);
+        const float dj = __fmul_rn(half_bits_to_float(ld_u16(blk)), (float)sc);
+        const float mj = __fmul_rn(half_bits_to_float(ld_u16(blk + 2)), (float)mn);
+        return __fsub_rn(__fmul_rn(dj, (float)q), mj);
     } else {
         const uint8_t *blk = row + 210u * (e >> 8);
         const uint32_t r = e & 255u, h = r >> 7, g = (r & 127u) >> 5, l = r & 31u;
@@ -1190,6 +1202,7 @@ cudaError_t launch_qmm_simt(int ggml_type, const QmmArgs &a, bool routed, uint32
     case GT_Q4_0: return launch_simt_t<GT_Q4_0>(a, routed, max_rows, st);
     case GT_Q8_0: return launch_simt_t<GT_Q8_0>(a, routed, max_rows, st);
     case GT_Q6_K: return launch_simt_t<GT_Q6_K>(a, routed, max_rows, st);
+    case GT_Q4_K: return launch_simt_t<GT_Q4_K>(a, routed, max_rows, st);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -72,6 +72,37 @@ __device__ __forceinline__ void dot_row_simple(const uint8_t *wrow, const float 
                 }
             }
         }
+    } else if constexpr (T == GT_Q4_K) {
+        // task = 8 consecutive bytes of one pair of sub-blocks (low nibbles: sub-block 2p, high: 2p+1): 16 per block
+        const uint32_t ntask = (k / 256) * 16;
+        for (uint32_t tk = lane; tk < ntask; tk += 32) {
+            const uint32_t b = tk >> 4, p = (tk >> 2) & 3u, l0 = 8 * (tk & 3u);
+            const uint8_t *blk = wrow + 144u * b;
+            uint32_t sc1, m1, sc2, m2;
+            q4k_scale_min(2 * p, blk + 4, sc1, m1);
+            q4k_scale_min(2 * p + 1, blk + 4, sc2, m2);
+            const float d = half_bits_to_float(ld_u16(blk)), dmin = half_bits_to_float(ld_u16(blk + 2));
+            const float d1 = __fmul_rn(d, (float)sc1), min1 = __fmul_rn(dmin, (float)m1);
+            const float d2 = __fmul_rn(d, (float)sc2), min2 = __fmul_rn(dmin, (float)m2);
+            const uint8_t *q = blk + 16 + 32 * p + l0;
+            const float *xb = x + 256u * b + 64u * p + l0;
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) {
+                const uint32_t qq = ld_u16(q + i);
+                const float w0 = __fsub_rn(__fmul_rn(d1, (float)(qq & 15u)), min1);
+                const float w1 = __fsub_rn(__fmul_rn(d1, (float)((qq >> 8) & 15u)), min1);
+                const float w2 = __fsub_rn(__fmul_rn(d2, (float)((qq >> 4) & 15u)), min2);
+                const float w3 = __fsub_rn(__fmul_rn(d2, (float)(qq >> 12)), min2);
+#pragma unroll
+                for (int t = 0; t < M; t++) {
+                    const float *xt = xb + (size_t)t * k;
+                    acc[t] = fmaf(w0, __ldg(xt + i), acc[t]);
+                    acc[t] = fmaf(w1, __ldg(xt + i + 1), acc[t]);
+                    acc[t] = fmaf(w2, __ldg(xt + 32 + i), acc[t]);
+                    acc[t] = fmaf(w3, __ldg(xt + 32 + i + 1), acc[t]);
+                }
+            }
+        }
     } else {  // Q6_K: 16 strips of 4 (x4 groups) per block
         const uint32_t ntask = (k / 256) * 16;
         for (uint32_t tk = lane; tk < ntask; tk += 32) {
@@ -806,6 +837,20 @@ cudaError_t launch_qmv(int ggml_type, const QmvArgs &a, bool want_stream, int sm
     case GT_Q4_0: return launch_t<GT_Q4_0>(a, want_stream, sm_count, st, kname);
     case GT_Q8_0: return launch_t<GT_Q8_0>(a, want_stream, sm_count, st, kname);
     case GT_Q6_K: return launch_t<GT_Q6_K>(a, want_stream, sm_count, st, kname);
+    case GT_Q4_K: {   // the simple kernel only (no streaming or tensor-core form yet)
+        *kname = "qmv_simple";
+        switch (a.m) {
+        case 1: return launch_simple_tm<GT_Q4_K, 1>(a, st);
+        case 2: return launch_simple_tm<GT_Q4_K, 2>(a, st);
+        case 3: return launch_simple_tm<GT_Q4_K, 3>(a, st);
+        case 4: return launch_simple_tm<GT_Q4_K, 4>(a, st);
+        case 5: return launch_simple_tm<GT_Q4_K, 5>(a, st);
+        case 6: return launch_simple_tm<GT_Q4_K, 6>(a, st);
+        case 7: return launch_simple_tm<GT_Q4_K, 7>(a, st);
+        case 8: return launch_simple_tm<GT_Q4_K, 8>(a, st);
+        default: return cudaErrorInvalidValue;
+        }
+    }
     default: return cudaErrorInvalidValue;
     }
 }

@@ -586,6 +586,7 @@ static const char *const kKernelNames[] = {
     "kernel_mul_mm_id_map0_ne20_1", "kernel_mul_mm_id_map0_ne20_8",
     "kernel_mul_mm_id_q4_0_f32", "kernel_mul_mm_id_q8_0_f32", "kernel_mul_mm_id_q6_K_f32",
     "kernel_mul_mm_id_q4_0_tensor_f32", "kernel_mul_mm_id_q8_0_tensor_f32", "kernel_mul_mm_id_q6_K_tensor_f32",
+    "kernel_mul_mv_q4_K_f32", "kernel_mul_mv_id_q4_K_f32", "kernel_mul_mm_id_q4_K_f32", "kernel_mul_mm_id_q4_K_tensor_f32",
     "moe_softmax_topk_f32", "moe_weighted_reduce_f32", "silu_mul_f32",
 };
 static bool known_kernel(const char *name) {
@@ -1050,16 +1051,16 @@ static int op_begin(mlxn_encoder *e, std::initializer_list<OpBuf> bufs) {
 // quantized_matmul_ggml
 // ------------------------------------------------------------------------------------------------
 static const char *mv_kernel_name(int t) {
-    return t == GT_Q4_0 ? "kernel_mul_mv_q4_0_f32" : t == GT_Q8_0 ? "kernel_mul_mv_q8_0_f32" : "kernel_mul_mv_q6_K_f32";
+    return t == GT_Q4_0 ? "kernel_mul_mv_q4_0_f32" : t == GT_Q8_0 ? "kernel_mul_mv_q8_0_f32" : t == GT_Q4_K ? "kernel_mul_mv_q4_K_f32" : "kernel_mul_mv_q6_K_f32";
 }
 static const char *mm_kernel_name(int t) {
     return t == GT_Q4_0 ? "kernel_mul_mm_q4_0_tensor_f32" : t == GT_Q8_0 ? "kernel_mul_mm_q8_0_tensor_f32" : "kernel_mul_mm_q6_K_tensor_f32";
 }
 static const char *mv_id_kernel_name(int t) {
-    return t == GT_Q4_0 ? "kernel_mul_mv_id_q4_0_f32" : t == GT_Q8_0 ? "kernel_mul_mv_id_q8_0_f32" : "kernel_mul_mv_id_q6_K_f32";
+    return t == GT_Q4_0 ? "kernel_mul_mv_id_q4_0_f32" : t == GT_Q8_0 ? "kernel_mul_mv_id_q8_0_f32" : t == GT_Q4_K ? "kernel_mul_mv_id_q4_K_f32" : "kernel_mul_mv_id_q6_K_f32";
 }
 static const char *mm_id_kernel_name(int t) {
-    return t == GT_Q4_0 ? "kernel_mul_mm_id_q4_0_tensor_f32" : t == GT_Q8_0 ? "kernel_mul_mm_id_q8_0_tensor_f32" : "kernel_mul_mm_id_q6_K_tensor_f32";
+    return t == GT_Q4_0 ? "kernel_mul_mm_id_q4_0_tensor_f32" : t == GT_Q8_0 ? "kernel_mul_mm_id_q8_0_tensor_f32" : t == GT_Q4_K ? "kernel_mul_mm_id_q4_K_tensor_f32" : "kernel_mul_mm_id_q6_K_tensor_f32";
 }
 
 static int check_handles(mlxn_encoder *enc, mlxn_device *dev, std::initializer_list<const void *> ptrs) {
@@ -1199,10 +1200,10 @@ extern "C" int mlxn_quantized_matmul_ggml(mlxn_encoder *enc, mlxn_registry *reg,
     int rc = check_handles(enc, dev, {input, weight, output, params});
     if (rc) return rc;
     if ((rc = validate_dense("quantized_matmul_ggml", input, weight, output, params, true))) return rc;
-    if ((int)params->ggml_type == GT_Q4_K)
-        return fail(MLXN_KERNEL_NOT_FOUND, "Kernel not found: kernel_mul_mv_q4_K_f32 (Q4_K is not built into this library yet)");
     if ((rc = check_alignment(input, weight, output))) return rc;
-    if (params->m > MLXN_MM_ROUTING_THRESHOLD && params->k >= 32)
+    // Q4_K has no dense mat-mat upstream either: it takes the mat-vec route at any m
+    // (src/ops/quantized_matmul_ggml.rs:350-360)
+    if (params->m > MLXN_MM_ROUTING_THRESHOLD && params->k >= 32 && (int)params->ggml_type != GT_Q4_K)
         return dispatch_mm(enc, reg, dev, input, weight, output, params);
     return dispatch_mv(enc, reg, dev, input, weight, output, params);
 }
@@ -1225,8 +1226,6 @@ extern "C" int mlxn_quantized_matmul_ggml_sharded(mlxn_encoder *enc, mlxn_regist
     if (output->len < (size_t)params->m * n_total * 4)
         return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_sharded: output buffer too small: expected %zu bytes for [%u x %u] f32, got %zu",
                     (size_t)params->m * n_total * 4, params->m, n_total, output->len);
-    if ((int)params->ggml_type == GT_Q4_K)
-        return fail(MLXN_KERNEL_NOT_FOUND, "Kernel not found: kernel_mul_mv_q4_K_f32 (Q4_K is not built into this library yet)");
     if ((rc = check_alignment(input, weight, output))) return rc;
     ShardOut sh;
     sh.y_ld = n_total;
@@ -1285,7 +1284,7 @@ static int validate_id(const char *who, mlxn_buffer *input, mlxn_buffer *weight,
     if (output->len < expected_out)
         return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: output buffer too small: expected %zu bytes for [%zu x %u] f32, got %zu",
                     who, expected_out, total_rows, p->n, output->len);
-    if (t != GT_Q4_0 && t != GT_Q8_0 && t != GT_Q6_K)
+    if (t != GT_Q4_0 && t != GT_Q8_0 && t != GT_Q6_K && t != GT_Q4_K)
         return fail(MLXN_KERNEL_NOT_FOUND, "Kernel not found: expert-routed kernels for %s are not built into this library yet", ggml_name(t));
     if (total_rows > 0x7FFFFFFFull / 1) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: n_tokens * top_k is too large", who);
     return MLXN_OK;
@@ -1343,7 +1342,7 @@ static int dispatch_id_mm_stages(mlxn_encoder *enc, mlxn_registry *reg, mlxn_dev
     a.total_rows = p->n_tokens * p->top_k;
     a.expert_stride = p->expert_stride;
     a.status = enc->status_dev;
-    if (opt_qmm_tc() && qmm_tc_supported(a)) {
+    if (opt_qmm_tc() && qmm_tc_supported(a) && (int)p->ggml_type != GT_Q4_K) {   // Q4_K: CUDA-core tiles for now
         const uint32_t nt = qmm_tc_pick_nt((int)p->ggml_type, p->n_tokens, p->n, dev->sm_count, true);
         uint8_t *scratch = nullptr;
         const size_t need = qmm_tc_scratch_bytes(a, nt, true);

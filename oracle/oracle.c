@@ -33,6 +33,8 @@
  *   src/gguf/mod.rs:355-388, 395-425, 656-709    production dequantizers
  *   src/shaders/quantized_matmul_id_mm.metal:242-283  map0 bucketing
  *   src/shaders/moe_softmax_topk.metal:27-148    router softmax + top-k
+ *   src/gguf/mod.rs:440-452, 582-644             Q4_K scale/min unpacking and dequantize
+ *   tests/test_q4_k_kernels.rs:58-76, 108-180    Q4_K scale packing and the test packer
  *   src/shaders/moe_weighted_reduce.metal:33-66  weighted combine
  *   src/shaders/silu_mul.metal:17-30             SwiGLU
  *   src/shaders/quantized_matmul_mm_tensor.metal:92-158, 280-287  f16 operand rounding
@@ -49,6 +51,7 @@
 #define BYTES_Q4_0 18
 #define BYTES_Q8_0 34
 #define BYTES_Q6_K 210
+#define BYTES_Q4_K 144
 
 /* ggml_type codes shared with include/mlxn_b200.h */
 enum { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q8_0 = 3, T_Q4_K = 4, T_Q5_K = 5, T_Q6_K = 6, T_I16 = 7 };
@@ -182,14 +185,54 @@ void orc_dequant_q6_k(const uint8_t *data, size_t nblocks, float *out) {
     }
 }
 
-static int type_qk(int t) { return t == T_Q6_K ? QK_K : 32; }
-static int type_bytes(int t) { return t == T_Q4_0 ? BYTES_Q4_0 : t == T_Q8_0 ? BYTES_Q8_0 : BYTES_Q6_K; }
+/* src/gguf/mod.rs:440-452: the 6-bit (scale, min) pair of sub-block j from the 12 packed bytes. */
+void orc_q4k_scale_min(int j, const uint8_t *scales, uint8_t *sc, uint8_t *mn) {
+    if (j < 4) {
+        *sc = scales[j] & 63;
+        *mn = scales[j + 4] & 63;
+    } else {
+        *sc = (uint8_t)((scales[j + 4] & 0x0F) | ((scales[j - 4] >> 6) << 4));
+        *mn = (uint8_t)((scales[j + 4] >> 4) | ((scales[j] >> 6) << 4));
+    }
+}
+
+/* src/gguf/mod.rs:582-644; tests/test_q4_k_kernels.rs:206-233.  Block: f16 d, f16 dmin, scales[12], qs[128].
+ * Eight sub-blocks of 32; bytes [32p, 32p+32) of qs hold sub-block 2p in the low nibbles and 2p+1 in the
+ * high ones.  Value = (d * sc) * q - (dmin * m), each product and the difference rounded in f32. */
+void orc_dequant_q4_k(const uint8_t *data, size_t nblocks, float *out) {
+    for (size_t b = 0; b < nblocks; b++) {
+        const uint8_t *blk = data + b * BYTES_Q4_K;
+        const float d = orc_f16_to_f32(rd_u16(blk));
+        const float dmin = orc_f16_to_f32(rd_u16(blk + 2));
+        const uint8_t *scales = blk + 4, *qs = blk + 16;
+        float *o = out + b * QK_K;
+        for (int p = 0; p < 4; p++) {
+            uint8_t sc1, m1, sc2, m2;
+            orc_q4k_scale_min(2 * p, scales, &sc1, &m1);
+            orc_q4k_scale_min(2 * p + 1, scales, &sc2, &m2);
+            const float d1 = d * (float)sc1, min1 = dmin * (float)m1;
+            const float d2 = d * (float)sc2, min2 = dmin * (float)m2;
+            for (int l = 0; l < 32; l++) {
+                volatile float a = d1 * (float)(qs[32 * p + l] & 0x0F);   /* no fused multiply-subtract */
+                volatile float c = d2 * (float)(qs[32 * p + l] >> 4);
+                o[64 * p + l] = a - min1;
+                o[64 * p + 32 + l] = c - min2;
+            }
+        }
+    }
+}
+
+static int type_qk(int t) { return (t == T_Q6_K || t == T_Q4_K) ? QK_K : 32; }
+static int type_bytes(int t) {
+    return t == T_Q4_0 ? BYTES_Q4_0 : t == T_Q8_0 ? BYTES_Q8_0 : t == T_Q4_K ? BYTES_Q4_K : BYTES_Q6_K;
+}
 
 int orc_dequant(int ggml_type, const uint8_t *data, size_t nblocks, float *out) {
     switch (ggml_type) {
     case T_Q4_0: orc_dequant_q4_0(data, nblocks, out); return 0;
     case T_Q8_0: orc_dequant_q8_0(data, nblocks, out); return 0;
     case T_Q6_K: orc_dequant_q6_k(data, nblocks, out); return 0;
+    case T_Q4_K: orc_dequant_q4_k(data, nblocks, out); return 0;
     default: return -1;
     }
 }
@@ -317,6 +360,64 @@ void orc_pack_q6_k(const float *v, size_t n, uint8_t *out) {
     }
 }
 
+/* tests/test_q4_k_kernels.rs:58-76: packs eight 6-bit scales and mins into 12 bytes. */
+void orc_q4k_encode_scales(const uint8_t *sc, const uint8_t *mn, uint8_t *s) {
+    memset(s, 0, 12);
+    for (int j = 0; j < 4; j++) {
+        s[j] = sc[j] & 63;
+        s[j + 4] = mn[j] & 63;
+    }
+    for (int j = 4; j < 8; j++) {
+        s[j + 4] = (uint8_t)((sc[j] & 0x0F) | ((mn[j] & 0x0F) << 4));
+        s[j - 4] |= (uint8_t)((sc[j] >> 4) << 6);
+        s[j] |= (uint8_t)((mn[j] >> 4) << 6);
+    }
+}
+
+static float clampf(float v, float lo, float hi) { return v < lo ? lo : v > hi ? hi : v; }
+
+/* tests/test_q4_k_kernels.rs:108-180 (the upstream test packer, a uniform per-sub-block quantizer):
+ * shift = -min(values) if negative; d = max(values + shift) / (15*63) (1 if that max is 0); dmin = shift / 63
+ * (1 if shift is 0); per sub-block sc = round(max(sub + shift) / 15 / d), m = round(shift / dmin), both
+ * clamped to 0..63; q = round((v + dmin*m) / (d*sc)) clamped to 0..15. */
+void orc_pack_q4_k(const float *v, size_t n, uint8_t *out) {
+    for (size_t b = 0; b < n / 256; b++) {
+        const float *x = v + b * 256;
+        float gmin = 3.402823466e+38f;
+        for (int i = 0; i < 256; i++) gmin = fminf(gmin, x[i]);
+        const float shift = gmin < 0.0f ? -gmin : 0.0f;
+        float gmax = 0.0f;
+        for (int i = 0; i < 256; i++) gmax = fmaxf(gmax, x[i] + shift);
+        const float d = gmax > 0.0f ? gmax / (15.0f * 63.0f) : 1.0f;
+        const float dmin = shift > 0.0f ? shift / 63.0f : 1.0f;
+        const float id_d = 1.0f / d, id_dmin = 1.0f / dmin;
+        uint8_t sc[8], mn[8];
+        for (int s = 0; s < 8; s++) {
+            float smax = 0.0f;
+            for (int i = 0; i < 32; i++) smax = fmaxf(smax, x[32 * s + i] + shift);
+            sc[s] = (uint8_t)clampf(roundf((smax / 15.0f) * id_d), 0.0f, 63.0f);
+            mn[s] = (uint8_t)clampf(roundf(shift * id_dmin), 0.0f, 63.0f);
+        }
+        uint8_t q4[256];
+        for (int s = 0; s < 8; s++) {
+            const float sub_scale = d * (float)sc[s], sub_min = dmin * (float)mn[s];
+            const float inv = sub_scale != 0.0f ? 1.0f / sub_scale : 0.0f;
+            for (int i = 0; i < 32; i++)
+                q4[32 * s + i] = (uint8_t)clampf(roundf((x[32 * s + i] + sub_min) * inv), 0.0f, 15.0f);
+        }
+        uint8_t *o = out + b * BYTES_Q4_K;
+        const uint16_t dh = orc_f32_to_f16(d), mh = orc_f32_to_f16(dmin);
+        o[0] = (uint8_t)(dh & 0xFF);
+        o[1] = (uint8_t)(dh >> 8);
+        o[2] = (uint8_t)(mh & 0xFF);
+        o[3] = (uint8_t)(mh >> 8);
+        orc_q4k_encode_scales(sc, mn, o + 4);
+        for (int p = 0; p < 4; p++)
+            for (int l = 0; l < 32; l++)
+                o[16 + 32 * p + l] = (uint8_t)((q4[64 * p + l] & 0x0F) | ((q4[64 * p + 32 + l] & 0x0F) << 4));
+    }
+}
+
 /* quantizer: 0 = upstream test quantizer, 1 = GGML rule (differs for Q4_0 only). */
 int orc_quantize(int ggml_type, int rule, const float *v, size_t n, uint8_t *out) {
     switch (ggml_type) {
@@ -325,6 +426,7 @@ int orc_quantize(int ggml_type, int rule, const float *v, size_t n, uint8_t *out
         return 0;
     case T_Q8_0: orc_pack_q8_0(v, n, out); return 0;
     case T_Q6_K: orc_pack_q6_k(v, n, out); return 0;
+    case T_Q4_K: orc_pack_q4_k(v, n, out); return 0;
     default: return -1;
     }
 }
@@ -390,7 +492,7 @@ static void *mm_worker(void *arg) {
  * staging, quantized_matmul_mm_tensor.metal:92-158 and :280-287) and still accumulates in f32. */
 int orc_qmatmul(int ggml_type, const uint8_t *w, const float *x, int m, size_t n, size_t k,
                 size_t row0, size_t row1, float *y, double *absdot, int f16_operands, int nthreads) {
-    if (ggml_type != T_Q4_0 && ggml_type != T_Q8_0 && ggml_type != T_Q6_K) return -1;
+    if (ggml_type != T_Q4_0 && ggml_type != T_Q8_0 && ggml_type != T_Q6_K && ggml_type != T_Q4_K) return -1;
     if (k % (size_t)type_qk(ggml_type)) return -2;
     if (nthreads < 1) nthreads = 1;
     if (nthreads > 256) nthreads = 256;
