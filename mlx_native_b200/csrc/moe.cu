@@ -12,33 +12,32 @@ namespace mlxn {
 
 constexpr uint32_t kNotLocal = 0xFFFFFFFFu;   // id of a (token, slot) pair whose expert lives on another rank
 
-// One warp per expert, eight experts per CTA.  The CTA stages the id table through shared memory a chunk of tokens at
-// a time (one coalesced pass, transposed to [slot][token] so that the scan reads without bank conflicts); each warp
-// then walks the chunk 32 tokens at a time: every lane evaluates the upstream selector for its token (sum of
-// (slot+1) over slots whose id, truncated to 16 bits, equals the expert), and a ballot + popcount prefix gives every
-// selected token its position, so the list order is the scan order.  grid ceil(n_experts/8), 256 threads.
-constexpr uint32_t kMap0Entries = 4096;   // id entries staged per chunk (16 KB + padding)
+// One CTA of eight warps per expert.  The CTA stages the id table through shared memory a chunk of tokens at a time
+// (one coalesced pass, transposed to [slot][token] so that the scan reads without bank conflicts); warp w takes the
+// w-th eighth of the chunk's tokens.  Every lane evaluates the upstream selector for its token (sum of (slot+1) over
+// slots whose id, truncated to 16 bits, equals the expert); pass 1 counts each warp's hits, a prefix over the eight
+// counts gives each warp its first position, pass 2 writes the entries (ballot + popcount inside the warp), so the
+// list order is the scan order.  grid n_experts, 256 threads.
+constexpr uint32_t kMap0Entries = 4096;   // id entries staged per chunk (8 KB + padding)
 __global__ void __launch_bounds__(256) moe_map0_kernel(const uint32_t *ids, uint32_t n_tokens, uint32_t top_k,
                                                        uint32_t n_experts, uint32_t hids_stride, uint32_t *htpe,
                                                        int32_t *hids) {
     __shared__ uint16_t stage[kMap0Entries + 2 * 64 + 64];
-    const uint32_t lane = threadIdx.x & 31;
-    const uint32_t e = blockIdx.x * 8 + (threadIdx.x >> 5);
-    const bool live = e < n_experts;
-    int32_t *row = hids + (size_t)(live ? e : 0) * hids_stride;
-    // tokens per chunk: a multiple of 32, at least 32 (top_k <= 64 keeps a chunk of 32 tokens within the stage)
-    uint32_t chunk = (kMap0Entries / top_k) & ~31u;
-    if (chunk < 32) chunk = 32;
-    const uint32_t pitch = chunk + 2;   // 16-bit entries: +2 moves each slot's row by one 32-bit bank
-    uint32_t n_all = 0;
-    if (top_k > 64) {   // a chunk of 32 tokens would not fit the stage: scan the table in place
-        if (!live) return;
+    __shared__ uint32_t warp_hits[8];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t e = blockIdx.x;
+    if (e >= n_experts) return;
+    int32_t *row = hids + (size_t)e * hids_stride;
+    const uint16_t e16 = (uint16_t)(e & 0xFFFFu);
+    uint32_t n_all = 0;    // entries written so far (kept in step by every thread)
+    if (top_k > 64) {      // a chunk of 32 tokens would not fit the stage: one warp scans the table in place
+        if (warp != 0) return;
         for (uint32_t t0 = 0; t0 < n_tokens; t0 += 32) {
             const uint32_t t = t0 + lane;
             int sel = 0;
             if (t < n_tokens)
                 for (uint32_t sl = 0; sl < top_k; sl++)
-                    sel += ((ids[(size_t)t * top_k + sl] & 0xFFFFu) == (e & 0xFFFFu)) ? (int)(sl + 1) : 0;
+                    sel += ((ids[(size_t)t * top_k + sl] & 0xFFFFu) == e16) ? (int)(sl + 1) : 0;
             const uint32_t hit = __ballot_sync(0xffffffffu, sel > 0);
             if (sel > 0) {
                 const uint32_t pos = n_all + __popc(hit & ((1u << lane) - 1u));
@@ -49,34 +48,54 @@ __global__ void __launch_bounds__(256) moe_map0_kernel(const uint32_t *ids, uint
         if (lane == 0) htpe[e] = n_all;
         return;
     }
+    // tokens per chunk: a multiple of 256 when it fits (32 per warp and round), at least 32
+    uint32_t chunk = (kMap0Entries / top_k) & ~31u;
+    if (chunk < 32) chunk = 32;
+    const uint32_t pitch = chunk + 2;   // 16-bit entries: +2 moves each slot's row by one 32-bit bank
     for (uint32_t c0 = 0; c0 < n_tokens; c0 += chunk) {
         const uint32_t ct = min(chunk, n_tokens - c0);
-        __syncthreads();   // the previous chunk has been scanned
+        __syncthreads();   // the previous chunk has been scanned, warp_hits consumed
         for (uint32_t i = threadIdx.x; i < ct * top_k; i += 256) {
             const uint32_t t = i / top_k, sl = i - t * top_k;
             stage[sl * pitch + t] = (uint16_t)(ids[(size_t)c0 * top_k + i] & 0xFFFFu);
         }
         __syncthreads();
-        if (!live) continue;
-        for (uint32_t t0 = 0; t0 < ct; t0 += 32) {
-            const uint32_t t = t0 + lane;
+        // warp w scans the 32-token groups [g_lo, g_hi) of the chunk
+        const uint32_t groups = (ct + 31) / 32;
+        const uint32_t g_lo = warp * groups / 8, g_hi = (warp + 1) * groups / 8;
+        auto selector = [&](uint32_t t) -> int {
             int sel = 0;
             if (t < ct)
-                for (uint32_t sl = 0; sl < top_k; sl++) sel += (stage[sl * pitch + t] == (uint16_t)(e & 0xFFFFu)) ? (int)(sl + 1) : 0;
+                for (uint32_t sl = 0; sl < top_k; sl++) sel += (stage[sl * pitch + t] == e16) ? (int)(sl + 1) : 0;
+            return sel;
+        };
+        uint32_t mine = 0;
+        for (uint32_t g = g_lo; g < g_hi; g++) mine += __popc(__ballot_sync(0xffffffffu, selector(32 * g + lane) > 0));
+        if (lane == 0) warp_hits[warp] = mine;
+        __syncthreads();
+        uint32_t base = n_all, total = 0;
+        for (uint32_t w = 0; w < 8; w++) {
+            if (w < warp) base += warp_hits[w];
+            total += warp_hits[w];
+        }
+        for (uint32_t g = g_lo; g < g_hi; g++) {
+            const uint32_t t = 32 * g + lane;
+            const int sel = selector(t);
             const uint32_t hit = __ballot_sync(0xffffffffu, sel > 0);
             if (sel > 0) {
-                const uint32_t pos = n_all + __popc(hit & ((1u << lane) - 1u));
+                const uint32_t pos = base + __popc(hit & ((1u << lane) - 1u));
                 if (pos < hids_stride) row[pos] = (int32_t)((c0 + t) * top_k) + sel - 1;
             }
-            n_all += __popc(hit);
+            base += __popc(hit);
         }
+        n_all += total;
     }
-    if (live && lane == 0) htpe[e] = n_all;
+    if (threadIdx.x == 0) htpe[e] = n_all;
 }
 
 cudaError_t launch_moe_map0(const uint32_t *ids, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts,
                             uint32_t hids_stride, uint32_t *htpe, int32_t *hids, cudaStream_t st) {
-    moe_map0_kernel<<<(n_experts + 7) / 8, 256, 0, st>>>(ids, n_tokens, top_k, n_experts, hids_stride, htpe, hids);
+    moe_map0_kernel<<<n_experts, 256, 0, st>>>(ids, n_tokens, top_k, n_experts, hids_stride, htpe, hids);
     return cudaGetLastError();
 }
 
