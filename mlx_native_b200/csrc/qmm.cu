@@ -193,9 +193,11 @@ __global__ void __launch_bounds__(256) build_tiles_kernel(const uint32_t *htpe, 
 // grid (nchunks, ntile_bound); 256 threads.
 template <int NT>
 __global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *xpack, uint32_t nchunks, uint32_t zero_y) {
-    const uint32_t kc = blockIdx.x, t = blockIdx.y;
+    // grid (K-chunk lanes, tiles): CTA (c, t) packs the chunks c, c + gridDim.x, ... of tile t, so that the tile's
+    // routing lookups (a chain of dependent loads) are paid once per CTA, not once per chunk.
+    const uint32_t t = blockIdx.y;
     if (zero_y) {  // split-K tiles add their halves into y with atomics (dense form only)
-        const size_t total = (size_t)a.m * a.n, ncta = (size_t)gridDim.x * gridDim.y, cta = (size_t)t * gridDim.x + kc;
+        const size_t total = (size_t)a.m * a.n, ncta = (size_t)gridDim.x * gridDim.y, cta = (size_t)t * gridDim.x + blockIdx.x;
         const size_t per = (total + ncta - 1) / ncta, lo = cta * per, hi = lo + per < total ? lo + per : total;
         for (size_t i = lo + threadIdx.x; i < hi; i += 256) a.y[i] = 0.f;
     }
@@ -206,20 +208,33 @@ __global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *x
         mt = a.tiles[2 + 2 * t];
         nrows = a.htpe[e];
     }
-    uint8_t *tile = xpack + ((size_t)t * nchunks + kc) * (size_t)(NT * 128);
-    for (uint32_t q = threadIdx.x; q < NT * 8; q += 256) {
-        const uint32_t r = q >> 3, j = q & 7u;
+    constexpr int kPer = (NT * 8 + 255) / 256;   // (row, 16-byte column) pairs per thread: the same ones in every chunk
+    const float *src_row[kPer];
+#pragma unroll
+    for (int i = 0; i < kPer; i++) {
+        const uint32_t q = threadIdx.x + i * 256, r = q >> 3;
         const uint32_t row = mt * NT + r;
-        const uint32_t k0 = kc * 64 + 8 * j;
-        uint4 out = make_uint4(0, 0, 0, 0);
-        if (row < nrows && k0 < a.k) {
+        src_row[i] = nullptr;
+        if (q < NT * 8 && row < nrows) {
             int64_t src = row;
             if (a.hids) {
                 const int32_t id = a.hids[(size_t)e * a.hids_stride + row];
                 src = (id >= 0 && (uint32_t)id < a.total_rows) ? id / (int32_t)a.top_k : -1;
             }
-            if (src >= 0) {
-                const float *xp = a.x + (size_t)src * a.k + k0;
+            if (src >= 0) src_row[i] = a.x + (size_t)src * a.k;
+        }
+    }
+    for (uint32_t kc = blockIdx.x; kc < nchunks; kc += gridDim.x) {
+        uint8_t *tile = xpack + ((size_t)t * nchunks + kc) * (size_t)(NT * 128);
+#pragma unroll
+        for (int i = 0; i < kPer; i++) {
+            const uint32_t q = threadIdx.x + i * 256;
+            if (q >= NT * 8) break;
+            const uint32_t r = q >> 3, j = q & 7u;
+            const uint32_t k0 = kc * 64 + 8 * j;
+            uint4 out = make_uint4(0, 0, 0, 0);
+            if (src_row[i] && k0 < a.k) {
+                const float *xp = src_row[i] + k0;
                 float v[8];
                 if (k0 + 8 <= a.k && (((uintptr_t)xp) & 15u) == 0) {
                     const float4 lo = __ldg(reinterpret_cast<const float4 *>(xp));
@@ -228,7 +243,7 @@ __global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *x
                     v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 8; i++) v[i] = (k0 + i < a.k) ? xp[i] : 0.0f;
+                    for (int u = 0; u < 8; u++) v[u] = (k0 + u < a.k) ? xp[u] : 0.0f;
                 }
                 __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
                 __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
@@ -237,8 +252,8 @@ __global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *x
                 out.z = *reinterpret_cast<uint32_t *>(&h2);
                 out.w = *reinterpret_cast<uint32_t *>(&h3);
             }
+            *reinterpret_cast<uint4 *>(tile + (r >> 3) * 1024 + (r & 7u) * 128 + ((j ^ (r & 7u)) << 4)) = out;
         }
-        *reinterpret_cast<uint4 *>(tile + (r >> 3) * 1024 + (r & 7u) * 128 + ((j ^ (r & 7u)) << 4)) = out;
     }
 }
 
@@ -1137,7 +1152,10 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
         a.tiles = nullptr;
     }
     {
-        dim3 grid(c.nchunks, (unsigned)tiles);
+        // enough CTAs to fill the GPU a few times over, few enough that a tile's routing lookups are amortised
+        uint32_t lanes = c.nchunks;
+        while (lanes > 1 && (uint64_t)lanes * tiles > 2048) lanes = (lanes + 1) / 2;
+        dim3 grid(lanes, (unsigned)tiles);
         pack_x_kernel<NT><<<grid, 256, 0, st>>>(a, xpack, c.nchunks, ksplit > 1 ? 1u : 0u);
         (*launches)++;
         cudaError_t e = cudaGetLastError();
