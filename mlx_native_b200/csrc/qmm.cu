@@ -497,6 +497,7 @@ struct TcCfg {
     uint32_t n_wt;        // weight-row tiles, ceil(n / 128)
     uint32_t ntiles;      // activation tiles: the count (dense) or its bound (routed: the list's length is read on the device)
     uint32_t ksplit;      // K split factor (1 or 2)
+    uint32_t stage_off;   // byte offset of the two staged output tiles (narrow tiles only), 0 = write y straight from registers
     uint32_t raw_tma;     // raw weight stages arrive as one tensor copy each (needs `aligned`); otherwise 16-byte cp.async
 };
 
@@ -523,7 +524,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     constexpr int kMaxB = 6, kMaxRaw = 6;
     constexpr int kNumMma = NT <= 128 ? 2 : 1;   // issuing threads, each with its own accumulator
     __shared__ __align__(8) uint64_t a_full[kTcAStages], stage_done[kTcAStages], b_full[kMaxB];
-    __shared__ __align__(8) uint64_t raw_full[kMaxRaw], raw_empty[kMaxRaw], acc_full, acc_empty, orow_ready[2];
+    __shared__ __align__(8) uint64_t raw_full[kMaxRaw], raw_empty[kMaxRaw], acc_full, acc_empty, orow_ready[2], stage_ready[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile uint32_t abort_flag;
     __shared__ int32_t orow[2][NT];
@@ -601,7 +602,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         }
         mbar_init(&acc_full, kNumMma);
         mbar_init(&acc_empty, kTcDequantWarps);
-        for (int s = 0; s < 2; s++) mbar_init(&orow_ready[s], kTcDequantWarps);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&orow_ready[s], kTcDequantWarps);
+            mbar_init(&stage_ready[s], kTcDequantWarps);
+        }
         mbar_init_fence();
     }
     if (warp == kWarpMma0) {  // the first MMA warp owns tensor memory
@@ -960,6 +964,53 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             if (q4 == 0 && half == 0) TRACE(2 + set, 6, nitem);
             const int32_t *tab = orow[nitem & 1u];
             const uint32_t wrow = n0 + rr;
+            if (c.stage_off) {
+                // Staged read-back (narrow tiles): the accumulator goes to shared memory as [activation row][weight
+                // row], tensor memory is handed back to the MMA warps at once, and every warp then writes whole
+                // 512-byte output rows with 16-byte stores (the direct form below writes 128 bytes per instruction).
+                constexpr uint32_t kPitch = kTcRowsW + 4;   // floats per staged row
+                float *stg = reinterpret_cast<float *>(smem + c.stage_off) + (nitem & 1u) * (NT * kPitch);
+#pragma unroll 1
+                for (uint32_t col = g * 32; col < NT; col += (kTcDequantWarps / 4) * 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(tmem_d + ((q4 * 32) << 16) + col, v);
+                    if (kNumMma == 2 && it.nst >= 2) {
+                        uint32_t v1[32];
+                        tmem_ld_32x32(tmem_d + ((q4 * 32) << 16) + NT + col, v1);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v1[j]));
+                    }
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) stg[(col + j) * kPitch + rr] = __uint_as_float(v[j]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&acc_empty);                      // the MMA warps may start the next item
+                    mbar_arrive(&stage_ready[nitem & 1u]);        // this warp's part of the staged tile is written
+                }
+                if (!mbar_wait(&stage_ready[nitem & 1u], (nitem >> 1) & 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) break;
+                if (!(c.debug & 256u)) {
+                    const uint32_t c4 = n0 + 4 * lane;
+                    for (uint32_t r = dw; r < NT; r += kTcDequantWarps) {
+                        const int32_t o = tab[r];
+                        if (o < 0) continue;
+                        const float4 val = *reinterpret_cast<const float4 *>(stg + r * kPitch + 4 * lane);
+                        float *dst = a.y + (size_t)o * a.n + c4;
+                        if (c4 + 3 < a.n) {
+                            *reinterpret_cast<float4 *>(dst) = val;
+                        } else {
+                            if (c4 < a.n) dst[0] = val.x;
+                            if (c4 + 1 < a.n) dst[1] = val.y;
+                            if (c4 + 2 < a.n) dst[2] = val.z;
+                        }
+                    }
+                }
+                if (q4 == 0 && half == 0) TRACE(2 + set, 7, nitem);
+                continue;
+            }
 #pragma unroll 1
             for (uint32_t col = g * 32; col < NT; col += (kTcDequantWarps / 4) * 32) {
                 uint32_t v[32];
@@ -1112,7 +1163,12 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     }
     const uint32_t b_bytes = NT * 128;  // one 64-wide K chunk of the activation tile
     const uint32_t raw_slot = kTcRowsW * c.seg_stride;
-    const uint32_t limit = 222 * 1024;  // + 1 KB alignment slack + ~3 KB of static shared memory <= 227 KB
+    uint32_t limit = 222 * 1024;  // + 1 KB alignment slack + ~3 KB of static shared memory <= 227 KB
+    // narrow tiles stage their result in shared memory (two tiles of NT x 132 floats) and write whole output rows
+    const uint32_t stage_bytes = 2u * NT * (kTcRowsW + 4) * 4u;
+    const bool staged = NT == 64 && qmm_tc_ksplit(NT, a.m, a.n, a.k, sm_count_of_device(), routed) == 1 &&
+                        ((((uintptr_t)a.y) | ((uintptr_t)a.n * 4u)) & 15u) == 0 && !getenv("MLXN_TC_NO_STAGED_OUT");
+    if (staged) limit -= stage_bytes;
     // activation ring first (at least two raw slots kept back), the rest goes to the raw weight ring
     uint32_t b_stages = (limit - 2 * raw_slot) / b_bytes;
     if (b_stages > 6) b_stages = 6;
@@ -1132,7 +1188,8 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     c.raw_slots = raw_slots;
     c.b_off = 0;
     c.raw_off = b_stages * b_bytes;
-    const size_t smem = (size_t)c.raw_off + raw_bytes + 1024;  // + slack for manual 1024-byte alignment
+    if (staged) c.stage_off = c.raw_off + raw_bytes;
+    const size_t smem = (size_t)c.raw_off + raw_bytes + (staged ? stage_bytes : 0u) + 1024;  // + slack for manual 1024-byte alignment
 
     const uint32_t ksplit = qmm_tc_ksplit(NT, a.m, a.n, a.k, sm_count_of_device(), routed);
     size_t tiles;
