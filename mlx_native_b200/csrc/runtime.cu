@@ -167,6 +167,8 @@ struct mlxn_graph {
     // Host views and replays: the upload of an input whose host view was dirty at capture time is part of the
     // graph (it reads the pinned shadow again at every replay); outputs become "newer on the device" at every replay.
     std::vector<mlxn_buffer *> uploads, outputs;  // hold a reference each
+    std::vector<bool> fetched;                    // per output: the graph copies it back to its host shadow itself
+    std::vector<bool> covered;                    // per output: its storage is fetched by one of the graph's copies
 };
 
 // Scratch arenas outlive their encoder: short-lived encoders (one per command buffer, as upstream uses them) would
@@ -883,6 +885,29 @@ extern "C" int mlxn_encoder_end_capture(mlxn_encoder *enc, mlxn_graph **out) {
     int jrc = encoder_join_lanes(enc);  // every forked lane rejoins lane 0 before the capture ends
     enc->capturing = false;
     auto *g = new mlxn_graph();
+    // Results the host already has a view of are fetched back by the graph itself (copy nodes behind all the work),
+    // so that a replay costs no device-to-host call per result at commit time.
+    if (!jrc) {
+        for (mlxn_buffer *b : enc->cap_outputs) {
+            Storage *st = b->st;
+            std::lock_guard<std::mutex> lk(st->mu);
+            bool fetch = st->host && st->bytes <= (size_t)(4u << 20);
+            if (fetch) {
+                for (size_t i = 0; i < g->fetched.size(); i++)
+                    if (enc->cap_outputs[i]->st == st && g->fetched[i]) fetch = false;   // one copy per storage
+            }
+            if (fetch && cudaMemcpyAsync(st->host, st->dptr, st->bytes, cudaMemcpyDeviceToHost, enc->lanes[0]) != cudaSuccess) {
+                (void)cudaGetLastError();
+                fetch = false;
+            }
+            g->fetched.push_back(fetch);
+        }
+    }
+    g->fetched.resize(enc->cap_outputs.size(), false);
+    g->covered.assign(enc->cap_outputs.size(), false);
+    for (size_t i = 0; i < enc->cap_outputs.size(); i++)
+        for (size_t j = 0; j < enc->cap_outputs.size() && !g->covered[i]; j++)
+            if (g->fetched[j] && enc->cap_outputs[j]->st == enc->cap_outputs[i]->st) g->covered[i] = true;
     cudaError_t e = cudaStreamEndCapture(enc->lanes[0], &g->graph);
     if (jrc && e == cudaSuccess) e = cudaErrorUnknown;
     if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
@@ -915,10 +940,13 @@ extern "C" int mlxn_graph_launch(mlxn_graph *graph, mlxn_encoder *enc) {
         std::lock_guard<std::mutex> lk(b->st->mu);
         b->st->host_newer = false;  // the replay has just read the shadow
     }
-    for (mlxn_buffer *b : graph->outputs) {
+    for (size_t oi = 0; oi < graph->outputs.size(); oi++) {
+        mlxn_buffer *b = graph->outputs[oi];
         {
             std::lock_guard<std::mutex> lk(b->st->mu);
-            if (b->st->host) b->st->dev_newer = true;
+            // (a storage the graph fetches itself is current on the host once lane 0 has run the replay)
+            const bool fetched_by_graph = graph->covered[oi];
+            if (b->st->host) b->st->dev_newer = !fetched_by_graph;
             b->st->last_stream = enc->lanes[0];
             b->st->has_last = true;
         }
