@@ -5,7 +5,7 @@ import pytest
 
 import mlx_native_b200 as mx
 from oracle import oracle as orc
-from tests.gpu_util import TYPES, Ctx, normal_acts, normal_weights
+from tests.gpu_util import TYPES, Ctx, norm_err, normal_acts, normal_weights
 
 pytestmark = pytest.mark.gpu
 
@@ -122,3 +122,53 @@ def test_moe_ffn_layer(ctx, T):
     scale = np.abs(want).max()
     tol = 2e-3 if T > mx.mm_id_routing_threshold() else 2e-5
     assert np.max(np.abs(got - want)) <= tol * scale
+
+
+def test_moe_ffn_layer_full_size_sampled(ctx):
+    """The MoE configuration at its full size (128 experts, top-8, hidden 2048, ffn 768, T = 512: the persistent grouped
+    mat-mat with 768 / 2048 work items), checked on a sample of (token, slot) pairs against the oracle, stage by stage."""
+    d = ctx.device
+    E, top_k, hidden, ffn, T = 128, 8, 2048, 768, 512
+    g4, o4 = TYPES["Q4_0"]
+    g6, o6 = TYPES["Q6_K"]
+    # one seeded expert, rolled by a different amount per expert (distinct weights everywhere, quick to build)
+    base_g = normal_weights(21, ffn, hidden, o4).reshape(ffn, -1)
+    base_u = normal_weights(22, ffn, hidden, o4).reshape(ffn, -1)
+    base_d = normal_weights(23, hidden, ffn, o6).reshape(hidden, -1)
+    wg = np.concatenate([np.roll(base_g, e, axis=0) for e in range(E)]).reshape(-1)
+    wu = np.concatenate([np.roll(base_u, 3 * e, axis=0) for e in range(E)]).reshape(-1)
+    wd = np.concatenate([np.roll(base_d, 5 * e, axis=0) for e in range(E)]).reshape(-1)
+    x = normal_acts(24, T, hidden)
+    logits = np.random.default_rng(25).standard_normal((T, E)).astype(np.float32)
+    ids, rw = route(ctx, logits, top_k)
+    o_ids, o_rw = orc.moe_softmax_topk(logits, top_k)
+    assert np.array_equal(ids, o_ids)
+    flat = ids.reshape(-1)
+
+    yg, _ = ctx.matmul_id(g4, wg, wg.size // E, x, flat, top_k, ffn, hidden, E)
+    assert mx.last_kernel_name() == "qmm_tc_id"
+    yu, _ = ctx.matmul_id(g4, wu, wu.size // E, x, flat, top_k, ffn, hidden, E)
+    gb, ub = ctx.buf(yg, mx.DType.F32), ctx.buf(yu, mx.DType.F32)
+    act = d.alloc_buffer(yg.nbytes, mx.DType.F32)
+    enc = d.command_encoder()
+    mx.silu_mul(enc, ctx.registry, d, gb, ub, act, yg.size)
+    enc.commit_and_wait()
+    a = act.as_slice(np.float32).reshape(T * top_k, ffn).copy()
+    yd, _ = ctx.matmul_id(g6, wd, wd.size // E, a, flat, 1, hidden, ffn, E)
+    out = d.alloc_buffer(T * hidden * 4, mx.DType.F32)
+    enc = d.command_encoder()
+    mx.moe_weighted_reduce(enc, ctx.registry, d, ctx.buf(rw, mx.DType.F32), ctx.buf(yd, mx.DType.F32), out, T, top_k, hidden)
+    enc.commit_and_wait()
+    got = out.as_slice(np.float32).reshape(T, hidden)
+
+    # every output row was written (no NaN left from an unvisited tile) and a sample matches the oracle
+    assert np.isfinite(yg).all() and np.isfinite(yd).all() and np.isfinite(got).all()
+    pairs = np.random.default_rng(26).choice(T * top_k, size=96, replace=False)
+    sel_ids = flat[pairs]
+    rg, adg = orc.qmatmul_id(o4, wg, wg.size // E, x[pairs // top_k], sel_ids, 1, ffn, hidden, E, f16_operands=True, nthreads=8)
+    assert norm_err(yg[pairs], rg, adg) <= 2e-5          # against the f16-operand oracle
+    rd, add = orc.qmatmul_id(o6, wd, wd.size // E, a[pairs], sel_ids, 1, hidden, ffn, E, f16_operands=True, nthreads=8)
+    assert norm_err(yd[pairs], rd, add) <= 2e-5
+    toks = np.unique(pairs // top_k)[:16]
+    want = orc.moe_weighted_reduce(yd.reshape(T, top_k, hidden)[toks].reshape(-1, hidden), rw[toks], len(toks), top_k, hidden)
+    assert np.allclose(got[toks], want, rtol=1e-5, atol=1e-6)
