@@ -88,6 +88,8 @@ struct VtCfg {
     uint32_t slot_bytes;        // B tiles + block sums + raw rows, multiple of 1024
     uint32_t xs_off, raw_off;   // offsets inside a slot
     uint32_t debug;
+    uint32_t pairs;             // Q6_K rows of 16 n + 8 bytes: the tensor map's rows are pairs of weight rows (see launch_vt_t)
+    uint32_t row_bytes;
 };
 
 constexpr int kVtMaxUnits = 1024; // K units per row the flag words cover (k <= 262144)
@@ -319,6 +321,27 @@ __global__ void __launch_bounds__(kVtThreads, 1)
     constexpr float kOff = (float)VtTraits<T>::OFFSET;
     // byte coordinate of a unit's tensor copy inside the row: Q6_K units start at the 16-byte boundary below them
     auto unit_x = [](uint32_t kun) -> uint32_t { return T == GT_Q6_K ? ((kun * UB) & ~15u) >> 2 : kun * (UB / 4); };
+    // One tensor copy brings a stage's 128 rows.  Pair mode (Q6_K rows that are 8 bytes past a 16-byte boundary every
+    // other row): the map's rows are pairs of weight rows, so two copies of 64 map rows each bring the even weight
+    // rows (stage rows 0-63) and the odd ones (stage rows 64-127), each from the 16-byte boundary below its unit.
+    auto issue_weights = [&](uint32_t dst, uint32_t kun, uint32_t tile, uint32_t bar) {
+        if (T == GT_Q6_K && c.pairs) {
+            const uint32_t xe = ((kun * UB) & ~15u) >> 2, xo = ((c.row_bytes + kun * UB) & ~15u) >> 2;
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                ::"r"(dst), "l"(&wmap), "r"(xe), "r"(tile * (kVtRows / 2)), "r"(bar)
+                : "memory");
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                ::"r"(dst + (kVtRows / 2) * c.row_stride), "l"(&wmap), "r"(xo), "r"(tile * (kVtRows / 2)), "r"(bar)
+                : "memory");
+        } else {
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                ::"r"(dst), "l"(&wmap), "r"(unit_x(kun)), "r"(tile * kVtRows), "r"(bar)
+                : "memory");
+        }
+    };
     __shared__ __align__(8) uint64_t raw_full[kVtMaxSlots], raw_empty[kVtMaxSlots];
     __shared__ __align__(8) uint64_t a_full[2 * kVtGroups], d_full[2 * kVtGroups];
     __shared__ uint32_t tmem_base_s;
@@ -349,11 +372,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
             VtWalk st;
             st.init(u0, u1, c.upt, c.cu, c.nslots);
             mbar_expect_tx(&raw_full[0], kVtRows * c.row_stride + st.cnt * (4 * 2048 + AUX));
-            asm volatile(
-                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                ::"r"(smem_u32(smem + c.raw_off)), "l"(&wmap), "r"(unit_x(st.kun)), "r"(st.tile * kVtRows),
-                  "r"(smem_u32(&raw_full[0]))
-                : "memory");
+            issue_weights(smem_u32(smem + c.raw_off), st.kun, st.tile, smem_u32(&raw_full[0]));
         }
     }
     if (warp == kVtCvtWarps + 1) {
@@ -385,11 +404,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                     // cu units wide, a stage that uses fewer just ignores the rest (reads past a row's end are zeros too)
                     if (sidx != 0) {  // stage 0's weights were requested during set-up
                         mbar_expect_tx(&raw_full[slot], kVtRows * c.row_stride + st.cnt * (4 * 2048 + AUX));
-                        asm volatile(
-                            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                            ::"r"(smem_u32(sl + c.raw_off)), "l"(&wmap), "r"(unit_x(st.kun)), "r"(st.tile * kVtRows),
-                              "r"(smem_u32(&raw_full[slot]))
-                            : "memory");
+                        issue_weights(smem_u32(sl + c.raw_off), st.kun, st.tile, smem_u32(&raw_full[slot]));
                     }
                     if (sidx == 0) grid_dependency_wait();  // the packed activations come from the kernel before
                     bulk_g2s(sl, sc.xpack + (size_t)st.kun * 4 * 2048, st.cnt * 4 * 2048, &raw_full[slot]);
@@ -522,7 +537,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                 for (int gg = 0; gg < kVtGroups - 1; gg++)
 #pragma unroll
                     for (int i = 0; i < 2 * MP; i++) tot[i] += red[(gg * 2 * MP + i) * kVtRows + row];
-                const uint32_t grow = pv_tile * kVtRows + row;
+                const uint32_t grow = pv_tile * kVtRows + ((T == GT_Q6_K && c.pairs) ? (row < kVtRows / 2 ? 2 * row : 2 * (row - kVtRows / 2) + 1) : row);
                 const bool full = pv_ka == 0 && pv_kb == c.upt;
                 const size_t ycol = (size_t)a.y_col0 + grow;
                 const uint32_t ld = qmv_ld(a);
@@ -575,7 +590,10 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                     // the slot's previous contents were consumed: its accumulators were read back two sub-steps ago
                     if constexpr (T == GT_Q6_K) {
                         uint32_t r[16];
-                        vt_extract_q6k_p((st.kun + ul) & 7u, sl_base + c.raw_off + row * c.row_stride, n, g, r, d0, d1);
+                        // (pair mode: odd weight rows, stage rows 64-127 = lane quarters 2 and 3, start 8 bytes further
+                        //  into their 16-byte chunk: four steps on in the lead-in sequence)
+                        const uint32_t p8 = (st.kun + ul + ((c.pairs && q4 >= 2) ? 4u : 0u)) & 7u;
+                        vt_extract_q6k_p(p8, sl_base + c.raw_off + row * c.row_stride, n, g, r, d0, d1);
                         tmem_st_32x32_x16(lane_base + sl * kVtSlotCols, r);
                     } else {
                         uint32_t r[32];
@@ -624,7 +642,12 @@ __global__ void __launch_bounds__(kVtThreads, 1)
 static bool vt_have_encoder();
 bool qmv_tc_supported(int ggml_type, const QmvArgs &a) {
     if (ggml_type != GT_Q4_0 && ggml_type != GT_Q8_0 && ggml_type != GT_Q6_K) return false;
-    if (ggml_type == GT_Q6_K && a.k % 2048 != 0) return false;  // rows of 210-byte super-blocks start on 16-byte boundaries
+    if (ggml_type == GT_Q6_K) {
+        // rows of 210-byte super-blocks: every row on a 16-byte boundary (k % 2048 == 0), or every other row with the
+        // rows between 8 bytes past one (k % 2048 == 1024: pairs of rows become the tensor map's rows; n even)
+        const uint32_t rem = a.k % 2048;
+        if (!(rem == 0 || (rem == 1024 && a.n % 2 == 0 && !getenv("MLXN_VT_NO_PAIRS")))) return false;
+    }
     if (a.ids || a.nprob != 1 || a.m < 1 || a.m > 8) return false;
     if (a.k % kVtUnitK != 0 || a.k == 0 || a.n == 0 || a.k / kVtUnitK > (uint32_t)kVtMaxUnits) return false;
     if ((uint64_t)a.m * a.n >= (1ull << 32)) return false;
@@ -716,10 +739,12 @@ static cudaError_t launch_vt_t(const QmvArgs &a, uint8_t *scratch, uint32_t *fla
     if (!enc) return cudaErrorNotSupported;
     const uint32_t row_bytes = (a.k / BlockTraits<T>::QK) * BlockTraits<T>::BYTES;
     alignas(64) CUtensorMap wmap;
+    c.row_bytes = row_bytes;
+    c.pairs = (T == GT_Q6_K && row_bytes % 16 != 0) ? 1u : 0u;
     {
-        const cuuint64_t gdim[2] = {row_bytes / 4, a.n};
-        const cuuint64_t gstride[1] = {row_bytes};
-        const cuuint32_t box[2] = {c.row_stride / 4, (cuuint32_t)kVtRows};
+        const cuuint64_t gdim[2] = {c.pairs ? row_bytes / 2 : row_bytes / 4, c.pairs ? a.n / 2 : a.n};
+        const cuuint64_t gstride[1] = {c.pairs ? 2ull * row_bytes : row_bytes};
+        const cuuint32_t box[2] = {c.row_stride / 4, (cuuint32_t)(c.pairs ? kVtRows / 2 : kVtRows)};
         const cuuint32_t estr[2] = {1, 1};
         if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<uint8_t *>(a.w), gdim, gstride, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

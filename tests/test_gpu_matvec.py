@@ -185,3 +185,20 @@ def test_errors(ctx):
     enc.commit_and_wait()
     with pytest.raises(mx.InvalidArgument):
         d.alloc_buffer(0, mx.DType.F32)
+
+
+# ---- Q6_K rows of 16 j + 8 bytes (k % 2048 == 1024, e.g. the 5120-wide lm_head): the tensor-core kernel reads pairs
+# ---- of weight rows as one tensor-map row
+@pytest.mark.parametrize("n,k,m", [(2, 1024, 1), (66, 5120, 2), (128, 1024, 8), (130, 3072, 3), (1000, 5120, 1), (4748, 5120, 4)])
+def test_q6k_row_pairs(ctx, n, k, m):
+    mx.set_option("qmv", "tc")
+    try:
+        wq = normal_weights(n + k, n, k, orc.Q6_K)
+        check(ctx, "Q6_K", wq, normal_acts(m, m, k), n, k)
+        assert mx.last_kernel_name() == "qmv_tc"
+        # an odd row count cannot be paired: the streaming kernel takes it
+        wq = normal_weights(7, 33, 1024, orc.Q6_K)
+        check(ctx, "Q6_K", wq, normal_acts(m, m, 1024), 33, 1024)
+        assert mx.last_kernel_name() != "qmv_tc"
+    finally:
+        mx.set_option("qmv", "auto")
