@@ -196,6 +196,7 @@ __global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *x
     // grid (K-chunk lanes, tiles): CTA (c, t) packs the chunks c, c + gridDim.x, ... of tile t, so that the tile's
     // routing lookups (a chain of dependent loads) are paid once per CTA, not once per chunk.
     const uint32_t t = blockIdx.y;
+    allow_dependents();   // the mat-mat kernel behind may set itself up; it waits for this grid before it reads anything
     if (zero_y) {  // split-K tiles add their halves into y with atomics (dense form only)
         const size_t total = (size_t)a.m * a.n, ncta = (size_t)gridDim.x * gridDim.y, cta = (size_t)t * gridDim.x + blockIdx.x;
         const size_t per = (total + ncta - 1) / ncta, lo = cta * per, hi = lo + per < total ? lo + per : total;
@@ -537,6 +538,35 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     const uint32_t tid = threadIdx.x - kCtrlWarps * 32;   // index among the dequantising threads (wraps for warps 0-3)
     const uint32_t row_bytes = (a.k / QK) * BB;
 
+    // ---- set-up that needs nothing from the kernels ahead in the stream (it overlaps their tail: the kernel is
+    // ---- launched with programmatic stream serialisation), then the wait for them
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (uint32_t s = 0; s < kTcAStages; s++) {
+            mbar_init(&a_full[s], kTcDequantWarps / 2);  // the eight warps of one set
+            mbar_init(&stage_done[s], 1);
+        }
+        for (uint32_t s = 0; s < c.b_stages; s++) mbar_init(&b_full[s], 1);
+        for (uint32_t s = 0; s < c.raw_slots; s++) {
+            // one asynchronous arrival per copying thread, or the weight producer's single arrival with the byte count
+            mbar_init(&raw_full[s], c.raw_tma ? 1u : kTcDequantWarps * 32);
+            mbar_init(&raw_empty[s], kTcDequantWarps);
+        }
+        mbar_init(&acc_full, kNumMma);
+        mbar_init(&acc_empty, kTcDequantWarps);
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&orow_ready[s], kTcDequantWarps);
+            mbar_init(&stage_ready[s], kTcDequantWarps);
+        }
+        mbar_init_fence();
+    }
+    if (warp == kWarpMma0) {  // the first MMA warp owns tensor memory
+        tmem_alloc(&tmem_base_s, kTcTmemCols);
+        tmem_relinquish();
+    }
+    grid_dependency_wait();   // the packed activations, the tile list and (split-K) the zeroed y are complete
+    allow_dependents();
+
     // ---- work items: (weight-row tile, K split, token tile), weight tile fastest; CTA b takes items b, b + grid, ...
     // Every role walks the same item sequence; ring slots and barrier phases run on across items, so the next
     // item's weights are already on their way while this item's accumulator is read back.
@@ -588,30 +618,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
         return it;
     };
 
-    if (threadIdx.x == 0) {
-        abort_flag = 0;
-        for (uint32_t s = 0; s < kTcAStages; s++) {
-            mbar_init(&a_full[s], kTcDequantWarps / 2);  // the eight warps of one set
-            mbar_init(&stage_done[s], 1);
-        }
-        for (uint32_t s = 0; s < c.b_stages; s++) mbar_init(&b_full[s], 1);
-        for (uint32_t s = 0; s < c.raw_slots; s++) {
-            // one asynchronous arrival per copying thread, or the weight producer's single arrival with the byte count
-            mbar_init(&raw_full[s], c.raw_tma ? 1u : kTcDequantWarps * 32);
-            mbar_init(&raw_empty[s], kTcDequantWarps);
-        }
-        mbar_init(&acc_full, kNumMma);
-        mbar_init(&acc_empty, kTcDequantWarps);
-        for (int s = 0; s < 2; s++) {
-            mbar_init(&orow_ready[s], kTcDequantWarps);
-            mbar_init(&stage_ready[s], kTcDequantWarps);
-        }
-        mbar_init_fence();
-    }
-    if (warp == kWarpMma0) {  // the first MMA warp owns tensor memory
-        tmem_alloc(&tmem_base_s, kTcTmemCols);
-        tmem_relinquish();
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -1239,9 +1245,8 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     }
     if (items < ctas) ctas = (uint32_t)items;
     if (ctas == 0) return cudaSuccess;
-    qmm_tc_kernel<T, NT><<<ctas, kTcThreads, smem, st>>>(a, c, xpack, wmap);
     (*launches)++;
-    return cudaGetLastError();
+    return launch_overlapped(qmm_tc_kernel<T, NT>, dim3(ctas), dim3(kTcThreads), smem, st, a, c, xpack, wmap);
 }
 
 template <int T> static cudaError_t launch_tc_t(const QmmArgs &a, bool routed, uint32_t nt, uint8_t *scratch, cudaStream_t st,
