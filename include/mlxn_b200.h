@@ -119,6 +119,11 @@ int mlxn_pool_create(mlxn_pool **out);
 void mlxn_pool_destroy(mlxn_pool *pool);
 int mlxn_pool_alloc(mlxn_pool *pool, mlxn_device *dev, size_t byte_len, int dtype, const size_t *shape,
                     size_t rank, mlxn_buffer **out);                 /* :97-112 */
+/* alloc_batch (:114-135): `count` buffers in one call, all or nothing: on failure the buffers this call took go
+ * back to the pool and out[] holds no handle.  `shapes` concatenates the requests' shapes, ranks[i] entries each
+ * (both may be NULL: no shapes). */
+int mlxn_pool_alloc_batch(mlxn_pool *pool, mlxn_device *dev, size_t count, const size_t *byte_lens, const int *dtypes,
+                          const size_t *shapes, const size_t *ranks, mlxn_buffer **out);
 int mlxn_pool_release(mlxn_pool *pool, mlxn_buffer *buf);            /* :218-222 (consumes the handle) */
 void mlxn_pool_reset(mlxn_pool *pool);                               /* :248-252 */
 int mlxn_pool_register_existing(mlxn_pool *pool, mlxn_device *dev, mlxn_buffer *buf); /* :306-357 (no-op on CUDA) */
@@ -139,7 +144,13 @@ size_t mlxn_registry_cached_count(const mlxn_registry *reg);
 size_t mlxn_registry_source_count(const mlxn_registry *reg);
 
 /* ---- command encoder: CommandEncoder (src/encoder.rs) --------------------------------------
- * One CUDA stream per encoder: operations run in encode order, so memory_barrier only counts. */
+ * Upstream encodes with MTLDispatchTypeConcurrent: dispatches may overlap unless memory_barrier() separates them
+ * (src/encoder.rs:837-853), and its tracked mode inserts that barrier itself where the buffers of a new dispatch
+ * conflict with the running group (src/graph.rs:1494-1530).  The same holds here: an encoder owns two CUDA stream
+ * "lanes"; an operation none of whose buffers conflicts (read-after-write, write-after-read, write-after-write,
+ * or an input whose host view still has to be uploaded) with the operations encoded since the last barrier goes
+ * to the other lane and may overlap them; a conflict, memory_barrier(), commit, a capture boundary and
+ * mlxn_encoder_stream() join the lanes first.  Results are therefore those of encode order. */
 int mlxn_encoder_create(mlxn_device *dev, mlxn_encoder **out);       /* MlxDevice::command_encoder src/device.rs:86-88 */
 void mlxn_encoder_destroy(mlxn_encoder *enc);                        /* Drop: waits for submitted work */
 int mlxn_encoder_memory_barrier(mlxn_encoder *enc);                  /* src/encoder.rs:886-906 */
@@ -148,10 +159,25 @@ int mlxn_encoder_wait_until_completed(mlxn_encoder *enc);            /* src/enco
 int mlxn_encoder_commit_and_wait(mlxn_encoder *enc);                 /* src/encoder.rs:1852-1879 */
 /* commit_wait_with_gpu_time (src/encoder.rs:2001-2014): device time of the committed work in seconds. */
 int mlxn_encoder_commit_wait_with_gpu_time(mlxn_encoder *enc, double *gpu_seconds);
-/* The encoder's cudaStream_t, for callers that order their own work against it. */
+/* The encoder's cudaStream_t (lane 0), after it has been made to wait for the other lane: work the caller
+ * enqueues on it runs behind everything encoded so far.  NULL on failure. */
 void *mlxn_encoder_stream(mlxn_encoder *enc);
+/* commit_labeled / commit_and_wait_labeled (src/encoder.rs:1893-1935): as commit / commit_and_wait; with the
+ * environment variable MLX_PROFILE_CB=1 the command buffer's device time is printed to stderr under `label`
+ * when its wait returns (upstream's per-command-buffer profile, src/encoder.rs:1882-1935). */
+int mlxn_encoder_commit_labeled(mlxn_encoder *enc, const char *label);
+int mlxn_encoder_commit_and_wait_labeled(mlxn_encoder *enc, const char *label);
+/* The profile table (src/kernel_profile.rs): command buffers and device nanoseconds recorded under `label`. */
+int mlxn_profile_cb_get(const char *label, uint64_t *count, uint64_t *nanoseconds);
+void mlxn_profile_cb_reset(void);
 /* Replay support for launch-bound decode loops: everything encoded between begin and end is recorded
- * into a CUDA graph instead of being run; graph_launch replays it on the encoder's stream. */
+ * into a CUDA graph instead of being run; graph_launch replays it on the encoder's stream.
+ * Lifetimes: the graph keeps a reference to every buffer its operations bind, owns the scratch arenas its
+ * kernels use (eager work on the same encoder never shares or frees them) and shares the recording encoder's
+ * status block, so it stays valid after that encoder is destroyed; it replays only on the encoder that recorded
+ * it (or on the pooled successor that inherited its status block), other encoders get MLXN_INVALID_ARGUMENT.
+ * A host view of an input whose upload is part of the graph may be rewritten right after graph_launch: the
+ * write waits until the replay has read the view. */
 int mlxn_encoder_begin_capture(mlxn_encoder *enc);
 int mlxn_encoder_end_capture(mlxn_encoder *enc, mlxn_graph **out);
 int mlxn_graph_launch(mlxn_graph *graph, mlxn_encoder *enc);
@@ -276,11 +302,19 @@ int mlxn_quantized_matmul_ggml_sharded(mlxn_encoder *enc, mlxn_registry *reg, ml
                                        uint32_t n_total, uint32_t col0, void *const *peer_outputs, uint32_t n_peers);
 
 /* ---- tuning and introspection (no upstream counterpart) -------------------------------------- */
-/* Selects kernel variants for experiments: key/value pairs "qmv=auto|tc|stream|simple" (auto and tc: the
- * tensor-core mat-vec wherever it applies, the streaming SIMT kernel elsewhere; stream / simple force the SIMT
- * kernels, whose results are bit-reproducible) and "qmm=tc|simt".  Unknown keys are MLXN_INVALID_ARGUMENT.  The
- * defaults (auto, tc) are the fast paths. */
+/* Selects kernel variants for cross-checks: key/value pairs
+ *   "qmv" = auto | mma | tc | stream | simple   (auto: per shape and m, the fastest of the register-level tensor-core
+ *           kernel "mma" and the tensor-memory kernel "tc", the streaming SIMT kernel for shapes neither takes;
+ *           mma, stream and simple give bit-reproducible results, tc may differ in the last bit from run to run),
+ *   "qmm" = tc | simt,
+ *   "qmv_mma_ctas" = 1 | 2 (CTAs per SM of the mma kernel), "qmv_mma_tpw" = 0 | 1 | 2 | 4 (its row-group size; 0 = auto).
+ * Unknown keys are MLXN_INVALID_ARGUMENT.  The defaults are the fast paths. */
 int mlxn_set_option(const char *key, const char *value);
+/* Exercises the give-up path of the kernels' bounded waits: enqueues a one-CTA kernel that waits `limit_us`
+ * microseconds (1..100000) on a barrier nothing arrives at, records "wait for data timed out" in the encoder's
+ * status word and returns normally.  The next commit_and_wait reports MLXN_COMMAND_BUFFER_ERROR; the encoder and
+ * the device stay usable (src/encoder.rs:1867-1878 is the upstream path that surfaces a failed command buffer). */
+int mlxn_debug_wait_probe(mlxn_encoder *enc, uint32_t limit_us);
 /* Name of the kernel variant the last operation on this thread launched (for tests and profiles). */
 const char *mlxn_last_kernel_name(void);
 

@@ -57,6 +57,7 @@ SIGNATURES = {
     "mlxn_pool_create": (i32, [pvp]),
     "mlxn_pool_destroy": (None, [vp]),
     "mlxn_pool_alloc": (i32, [vp, vp, sz, i32, C.POINTER(sz), sz, pvp]),
+    "mlxn_pool_alloc_batch": (i32, [vp, vp, sz, C.POINTER(sz), C.POINTER(i32), C.POINTER(sz), C.POINTER(sz), pvp]),
     "mlxn_pool_release": (i32, [vp, vp]),
     "mlxn_pool_reset": (None, [vp]),
     "mlxn_pool_register_existing": (i32, [vp, vp, vp]),
@@ -78,6 +79,10 @@ SIGNATURES = {
     "mlxn_encoder_commit_and_wait": (i32, [vp]),
     "mlxn_encoder_commit_wait_with_gpu_time": (i32, [vp, C.POINTER(C.c_double)]),
     "mlxn_encoder_stream": (vp, [vp]),
+    "mlxn_encoder_commit_labeled": (i32, [vp, C.c_char_p]),
+    "mlxn_encoder_commit_and_wait_labeled": (i32, [vp, C.c_char_p]),
+    "mlxn_profile_cb_get": (i32, [C.c_char_p, C.POINTER(u64), C.POINTER(u64)]),
+    "mlxn_profile_cb_reset": (None, []),
     "mlxn_encoder_begin_capture": (i32, [vp]),
     "mlxn_encoder_end_capture": (i32, [vp, pvp]),
     "mlxn_graph_launch": (i32, [vp, vp]),
@@ -106,6 +111,7 @@ SIGNATURES = {
     "mlxn_noalloc_scratch_limit": (sz, []),
     "mlxn_quantized_matmul_ggml_mm_noalloc": (i32, [vp, vp, vp, vp, C.POINTER(QmmParams)]),
     "mlxn_set_option": (i32, [C.c_char_p, C.c_char_p]),
+    "mlxn_debug_wait_probe": (i32, [vp, u32]),
     "mlxn_last_kernel_name": (C.c_char_p, []),
 }
 

@@ -295,7 +295,18 @@ class MlxBufferPool:
         return MlxBuffer(out.value)
 
     def alloc_batch(self, device: MlxDevice, requests) -> list[MlxBuffer]:
-        return [self.alloc(device, *r) for r in requests]
+        """src/buffer_pool.rs:114-135: requests are (byte_len, dtype, shape) triples; all or nothing."""
+        reqs = list(requests)
+        n = len(reqs)
+        lens = (C.c_size_t * max(n, 1))(*[int(r[0]) for r in reqs])
+        dts = (C.c_int * max(n, 1))(*[int(r[1]) for r in reqs])
+        shapes = [list(r[2]) if len(r) > 2 and r[2] is not None else [] for r in reqs]
+        flat = [int(d) for sh in shapes for d in sh]
+        flat_arr = (C.c_size_t * max(len(flat), 1))(*flat)
+        ranks = (C.c_size_t * max(n, 1))(*[len(sh) for sh in shapes])
+        outs = (C.c_void_p * max(n, 1))()
+        _check(_native.lib().mlxn_pool_alloc_batch(self._h, device._h, n, lens, dts, flat_arr, ranks, outs))
+        return [MlxBuffer(outs[i]) for i in range(n)]
 
     def release(self, buffer: MlxBuffer) -> None:
         h, buffer._h = buffer._h, None
@@ -403,10 +414,16 @@ class CommandEncoder:
         _check(_native.lib().mlxn_encoder_commit_and_wait(self._h))
 
     def commit_and_wait_labeled(self, label: str) -> None:
-        self.commit_and_wait()
+        """src/encoder.rs:1893-1929: the label names an NVTX range; with MLX_PROFILE_CB=1 the command buffer's device
+        time is recorded under it (profile_cb_get)."""
+        _check(_native.lib().mlxn_encoder_commit_and_wait_labeled(self._h, label.encode()))
 
     def commit_labeled(self, label: str) -> None:
-        self.commit()
+        _check(_native.lib().mlxn_encoder_commit_labeled(self._h, label.encode()))
+
+    def debug_wait_probe(self, limit_us: int = 1000) -> None:
+        """Enqueues the kernel whose bounded wait runs out (see mlxn_debug_wait_probe)."""
+        _check(_native.lib().mlxn_debug_wait_probe(self._h, int(limit_us)))
 
     def commit_wait_with_gpu_time(self) -> float:
         t = C.c_double()
@@ -456,6 +473,17 @@ def set_option(key: str, value: str) -> None:
 
 def last_kernel_name() -> str:
     return _native.lib().mlxn_last_kernel_name().decode()
+
+
+def profile_cb_get(label: str) -> tuple[int, int]:
+    """(command buffers, device nanoseconds) recorded under `label` while MLX_PROFILE_CB=1 (src/kernel_profile.rs)."""
+    n, ns = C.c_uint64(), C.c_uint64()
+    _check(_native.lib().mlxn_profile_cb_get(label.encode(), C.byref(n), C.byref(ns)))
+    return int(n.value), int(ns.value)
+
+
+def profile_cb_reset() -> None:
+    _native.lib().mlxn_profile_cb_reset()
 
 
 # ---------------------------------------------------------------- the hot path
@@ -596,10 +624,13 @@ class GraphSession:
         self._barriers += 1
 
     def barrier_between(self, reads, writes) -> None:
+        """src/graph.rs:1494-1530.  The buffer lists are not needed: the encoder itself tracks which storages the
+        running group reads and writes and joins its lanes on a conflict; an explicit barrier is always safe."""
         self.barrier()
 
     def track_dispatch(self, reads, writes) -> None:
-        pass
+        """src/graph.rs:1532-1560.  A no-op for the same reason: every operation registers its buffers with the
+        encoder's conflict tracking when it is encoded."""
 
     def barrier_count(self) -> int:
         return self._barriers

@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmlxn_b200.so")
-SOURCES = ["runtime.cu", "qmv.cu", "qmv_tc.cu", "qmm.cu", "moe.cu"]
+SOURCES = ["runtime.cu", "qmv.cu", "qmv_tc.cu", "qmv_mma.cu", "qmm.cu", "moe.cu"]
 HEADERS = ["common.cuh", "ptx.cuh", "tensor_map.cuh", os.path.join("..", "..", "include", "mlxn_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",

@@ -51,14 +51,15 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     return t;
 }
 
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // Bounded wait.  Returns false if the wait gave up (or another thread already raised `abort`).
 // `abort` is a CTA-shared word; `status` the device status word the host reads after the launch.
-// A legitimate wait lasts microseconds; the limit is two seconds of wall time.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// A legitimate wait lasts microseconds; the default limit is two seconds of wall time (`limit_ns` shortens it
+// for the kernel that exists to exercise this path).
 // `sleep_ns` > 0 spaces the polls out (for warps that are not on the critical path: each poll costs issue
 // slots that working warps could use).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort, uint32_t *status,
-                                          uint32_t code, uint32_t sleep_ns = 0) {
+                                          uint32_t code, uint32_t sleep_ns = 0, uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     // The wall clock is only looked at every 64 polls, and for the first time after 64 polls: reading it costs
     // hundreds of cycles, which a wait that is about to succeed must not pay.
@@ -74,7 +75,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
             if (*abort) return false;
             const uint64_t now = global_timer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) break;
+            else if (now - t0 > limit_ns) break;
         }
     }
     *abort = 1;

@@ -1,0 +1,612 @@
+// Register-level mat-vec for 1..8 activation rows (decode): y[m, n] = x[m, k] . W[n, k]^T with W in GGML blocks.
+//
+// Replaces upstream kernel_mul_mv_{q4_0,q8_0,q6_K}_f32 (src/shaders/quantized_matmul_ggml.metal:104-330).
+// The operation is bound by the weight stream, so the kernel is organised around three things:
+//
+//  * One launch, no scratch memory, no atomics.  The activations are split into f16 hi + lo halves inside the
+//    kernel (per block of 32 / scale group of 16, pre-scaled by a power of two so that both halves stay f16
+//    normals whatever the magnitudes), and every output element is written exactly once by one CTA, so results
+//    are bit-reproducible and there is nothing to zero or to combine afterwards.
+//  * The multiply-adds run on the tensor cores from registers (mma.sync m16n8k16, f16 x f16 -> f32).  The
+//    weights enter as *exact integers*: the raw 4/6/8-bit codes written as f16 subnormals (n * 2^-24; one or two
+//    bit operations per pair of codes, no conversion instruction).  A 16-row weight tile is the A operand, the
+//    (up to 8) activation rows are the 8 columns of B.  Every block of 32 (Q6_K: scale group of 16) gets its own
+//    accumulator, started at -offset * sum(x) so that the unsigned codes need no subtraction, and is folded into
+//    the running sum with the block's f16 scale: four multiply-adds per 512 weights.
+//  * The weights arrive through a shared-memory ring filled by one 2-D tensor-map copy (TMA) per stage of
+//    R rows x 256 (Q6_K: 512) K values.  A CTA is small (8 consumer warps + a producer warp, about 100 KB of
+//    shared memory) so that two are resident per SM: launched as a programmatic dependent, the next mat-vec in
+//    the stream fills its ring with weights while the one ahead is still running, and starts computing the
+//    moment its activations are final.
+//
+// Work split: an item is R = 16 * TPW weight rows over all of K; CTA c takes items c, c + grid, ...  Inside a
+// CTA the eight consumer warps split every stage along K (warp w owns block w of the stage's eight; Q6_K: one
+// (super-block, half, 16-column strip) of the stage's two super-blocks), each keeping TPW accumulator tiles; at
+// the end of an item the eight partial sums per output are added in a fixed order through shared memory.
+//
+// Supported: Q4_0 / Q8_0 with k % 256 == 0, Q6_K with k % 512 == 0; weight rows that start on 16-byte boundaries;
+// dense form.  Everything else takes the other mat-vec kernels.
+#include "tensor_map.cuh"
+
+#include <cstdio>
+#include <cstdlib>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace mlxn {
+
+constexpr int kMwWarps = 8;                         // consumer warps
+constexpr int kMwThreads = (kMwWarps + 1) * 32;     // + producer warp
+constexpr int kMwMaxSlots = 12;
+
+// A "unit" is what one warp multiplies per tile and K step: one block of 32 (Q4_0 / Q8_0: two MMAs, one scale)
+// or one quarter of a Q6_K super-block (one half nh, one 16-column strip js: four MMAs, four scale groups).
+// UBYTES: bytes of a stage per row and per unit-of-every-warp (8 blocks, or 2 super-blocks).  OFFSET: code bias.
+// NG: scale groups (accumulator starts) per unit.  NM: MMAs per unit (each wants 4 activation values per lane).
+template <int T> struct MwTraits;
+template <> struct MwTraits<GT_Q4_0> { static constexpr int UK = 256, UBYTES = 144, OFFSET = 8, NG = 1, NM = 2; };
+template <> struct MwTraits<GT_Q8_0> { static constexpr int UK = 256, UBYTES = 272, OFFSET = 128, NG = 1, NM = 2; };
+template <> struct MwTraits<GT_Q6_K> { static constexpr int UK = 512, UBYTES = 420, OFFSET = 32, NG = 4, NM = 4; };
+
+// Shared-memory bytes per row of a stage of KB units per warp: the stage's bytes plus the up to 12 bytes between
+// the 16-byte boundary the copy starts at and the stage's first byte (Q6_K), rounded up to an ODD multiple of 16,
+// so that the 32-bit reads of eight consecutive rows fall into distinct banks.
+__host__ __device__ constexpr uint32_t mw_pitch(int ggml_type, int kb) {
+    const uint32_t raw = (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : 420u) * (uint32_t)kb;
+    const uint32_t lead = ggml_type == GT_Q6_K ? (kb == 1 ? 12u : kb == 2 ? 8u : 0u) : 0u;
+    const uint32_t c = (raw + lead + 15u) / 16u;
+    return 16u * (c | 1u);
+}
+
+struct MwCfg {
+    uint32_t items;       // row groups of R rows
+    uint32_t spi;         // stages per item = k / (KB * UK)
+    uint32_t nslots;      // ring depth
+    uint32_t xst_off;     // shared-memory offsets behind the ring
+    uint32_t ptab_off;
+    uint32_t red_off;
+};
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
+    asm volatile("st.shared.v2.b32 [%0], {%1,%2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
+}
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t a) {
+    asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(a) : "memory");
+}
+
+// D = A (16 x 16, row) * B (16 x 8, col) + C, f16 operands, f32 accumulate.  Lane (g = lane / 4, t = lane % 4):
+// a0 = A[g][2t, 2t+1], a1 = A[g+8][2t, 2t+1], a2 = A[g][2t+8, 2t+9], a3 = A[g+8][2t+8, 2t+9];
+// b0 = B[2t, 2t+1][g], b1 = B[2t+8, 2t+9][g]; c0 = C[g][2t], c1 = C[g][2t+1], c2 = C[g+8][2t], c3 = C[g+8][2t+1].
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1, const float (&c)[4]) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
+}
+
+__device__ __forceinline__ uint32_t h2_bits(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// Four activation values (scaled) -> the B registers of one MMA: hi halves (e0, e2), (e1, e3) and the f16 residues.
+// The pairing follows the code extraction: a 32-bit word of four codes (c0..c3) becomes the A registers (c0, c2)
+// and (c1, c3).
+__device__ __forceinline__ void split4(float e0, float e1, float e2, float e3, uint32_t &bh0, uint32_t &bh1, uint32_t &bl0,
+                                       uint32_t &bl1) {
+    const __half2 h02 = __floats2half2_rn(e0, e2), h13 = __floats2half2_rn(e1, e3);
+    const float2 f02 = __half22float2(h02), f13 = __half22float2(h13);
+    bh0 = *reinterpret_cast<const uint32_t *>(&h02);
+    bh1 = *reinterpret_cast<const uint32_t *>(&h13);
+    bl0 = h2_bits(e0 - f02.x, e2 - f02.y);
+    bl1 = h2_bits(e1 - f13.x, e3 - f13.y);
+}
+
+// Power of two that brings `amax` into [2^13, 2^14), and its inverse; 1 for an all-zero or non-finite run.
+__device__ __forceinline__ void pow2_scale(float amax, float &s, float &inv) {
+    s = 1.f;
+    inv = 1.f;
+    if (amax > 0.f && amax < 3.0e38f) {
+        int e = 13 + 127 - (int)((__float_as_uint(amax) >> 23) & 0xffu);
+        e = max(-100, min(100, e));
+        s = __uint_as_float((uint32_t)(e + 127) << 23);
+        inv = __uint_as_float((uint32_t)(127 - e) << 23);
+    }
+}
+
+// Which elements of its block (Q4_0 / Q8_0) lane t multiplies in MMA `h` (0, 1) of the block, as two pairs of
+// consecutive elements.  Blocks with an even index inside the stage start on a 4-byte boundary, so their codes
+// (2 bytes in) straddle the 32-bit words: lanes t = 0..2 take whole words, lane t = 3 the two half words at either
+// end.  `mis` = that case.
+__device__ __forceinline__ void mw_pairs(int ggml_type, bool mis, uint32_t t, uint32_t h, uint32_t &p0, uint32_t &p1) {
+    if (ggml_type == GT_Q8_0) {
+        if (!mis) { p0 = 16 * h + 4 * t; p1 = p0 + 2; }
+        else if (h == 0) { p0 = 2 + 4 * t; p1 = 4 + 4 * t; }
+        else { p0 = t < 3 ? 18 + 4 * t : 0; p1 = t < 3 ? 20 + 4 * t : 30; }
+    } else {  // Q4_0: byte c holds element c (low nibble, MMA 0) and 16 + c (high nibble, MMA 1)
+        if (!mis) { p0 = 4 * t; p1 = 4 * t + 2; }
+        else { p0 = t < 3 ? 2 + 4 * t : 0; p1 = t < 3 ? 4 + 4 * t : 14; }
+        p0 += 16 * h;
+        p1 += 16 * h;
+    }
+}
+
+// TPW: 16-row tiles per warp.  KB: units per warp and stage.  MP: activation rows carried (1, 2, 4 or 8, >= m).
+template <int T, int TPW, int KB, int MP>
+__global__ void __launch_bounds__(kMwThreads, 2)
+    qmv_mma_kernel(const QmvArgs a, const MwCfg c, const __grid_constant__ CUtensorMap wmap) {
+    using TR = MwTraits<T>;
+    constexpr int R = 16 * TPW, NG = TR::NG, NM = TR::NM;
+    constexpr uint32_t PITCH = mw_pitch(T, KB);
+    constexpr uint32_t SBYTES = (uint32_t)TR::UBYTES * KB;   // bytes of a stage per row
+    constexpr uint32_t SK = (uint32_t)TR::UK * KB;           // K values per stage
+    constexpr uint32_t STAGE = (uint32_t)R * PITCH;          // bytes per ring slot (a multiple of 256)
+    // activation conversion: one "piece" = the four values a lane feeds to one MMA; a warp has KB * MP * NM * 4 of
+    // them per stage, spread over its 32 lanes in NPASS passes
+    constexpr int PIECES = KB * MP * NM * 4;
+    constexpr int NPASS = (PIECES + 31) / 32;
+    constexpr uint32_t XCC = (uint32_t)PIECES * 16;          // offset of the (ci, cs) table behind the pieces
+    constexpr uint32_t XST = (XCC + (uint32_t)KB * MP * NG * 8 + 15u) & ~15u;   // the pieces are read 16 bytes at a time
+    constexpr float kOff = -(float)TR::OFFSET / 16777216.0f;
+
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    __shared__ __align__(8) uint64_t full[kMwMaxSlots], empty[kMwMaxSlots], fin[2];
+    __shared__ volatile uint32_t abort_flag;
+
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t grid = gridDim.x, cta = blockIdx.x;
+
+    if (tid == 0) {
+        abort_flag = 0;
+        for (uint32_t s = 0; s < c.nslots; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kMwWarps);
+        }
+        mbar_init(&fin[0], kMwWarps);
+        mbar_init(&fin[1], kMwWarps);
+        mbar_init_fence();
+    }
+    __syncthreads();
+    allow_dependents();   // the next overlapped launch may become resident and fetch its weights
+
+    const uint32_t smem_base = smem_u32(smem);
+
+    if (warp == kMwWarps) {
+        // ======================= producer: one tensor copy (R rows x one stage) per ring slot =======================
+        if (lane == 0) {
+            if (!a.early_weights) grid_dependency_wait();
+            uint32_t slot = 0, ph = 0, cidx = 0;
+            bool ok = true;
+            for (uint32_t item = cta; ok && item < c.items; item += grid) {
+                for (uint32_t s = 0; s < c.spi; s++, cidx++) {
+                    if (cidx >= c.nslots && !mbar_wait(&empty[slot], ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, 64u)) {
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(&full[slot], STAGE);
+                    // coordinates in 8-byte elements; rows past n and bytes past the end of a row arrive as zeros
+                    const uint32_t x0 = ((s * SBYTES) & ~15u) >> 3;
+                    asm volatile(
+                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                        ::"r"(smem_base + slot * STAGE), "l"(&wmap), "r"(x0), "r"(item * (uint32_t)R), "r"(smem_u32(&full[slot]))
+                        : "memory");
+                    if (++slot == c.nslots) { slot = 0; ph ^= 1u; }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ======================= consumers =======================
+        const uint32_t g = lane >> 2, t = lane & 3u, w = warp;
+        const uint32_t xst = smem_base + c.xst_off + w * XST;   // this warp's converted activations
+        const uint32_t xcc = xst + XCC;
+        const uint32_t ptab = smem_base + c.ptab_off + w * (R * 16 * KB);
+        const uint32_t red = smem_base + c.red_off;
+
+        // ---- geometry of the warp's units inside a stage ----
+        // Q4_0 / Q8_0: blocks KB w .. KB w + KB - 1 of the stage's 8 KB; block b starts BB * b bytes into the row
+        constexpr uint32_t BB = T == GT_Q8_0 ? 34u : 18u;
+        // Q6_K: quarter (nh, js) of the super-blocks sp, sp + 2, ...; super-block sb starts lead + 210 sb bytes in
+        const uint32_t sp = w >> 2, nh = (w >> 1) & 1u, js = w & 1u;
+        const uint32_t q6A = 64 * nh + 16 * js + 4 * t, q6H = 128 + 32 * nh + 16 * js + 4 * t, q6S = 192 + 8 * nh + js;
+
+        // ---- activation pieces this lane converts: piece index pc = lane + 32 pass ----
+        // Q4_0 / Q8_0: pc = ((i MP + r) NM + h) 4 + tt (unit i, activation row r, MMA h, quad lane tt);
+        // Q6_K:        pc = ((i MP + r) 4 + q) 4 + tt (scale group q)
+        const float *xsrc0[NPASS], *xsrc1[NPASS];
+        bool xok[NPASS];
+#pragma unroll
+        for (int p = 0; p < NPASS; p++) {
+            const uint32_t pc = lane + 32 * p, tt = pc & 3u, hq = (pc >> 2) % NM, ir = (pc >> 2) / NM;
+            const uint32_t r = ir % MP, i = ir / MP;
+            xok[p] = pc < (uint32_t)PIECES && r < a.m;
+            const float *row = a.x + (size_t)(xok[p] ? r : 0) * a.k;
+            if constexpr (T == GT_Q6_K) {
+                const uint32_t sb = sp + 2 * i;
+                xsrc0[p] = row + 256 * sb + 128 * nh + 32 * hq + 16 * js + 4 * tt;
+                xsrc1[p] = xsrc0[p] + 2;
+            } else {
+                const uint32_t b = KB * w + i;
+                uint32_t p0, p1;
+                mw_pairs(T, (b & 1u) == 0, tt, hq, p0, p1);
+                xsrc0[p] = row + 32 * b + p0;
+                xsrc1[p] = row + 32 * b + p1;
+            }
+        }
+        float xr[NPASS][4];
+        auto load_x = [&](uint32_t ks) {
+#pragma unroll
+            for (int p = 0; p < NPASS; p++) {
+                float2 v0 = make_float2(0.f, 0.f), v1 = v0;
+                if (xok[p]) {
+                    v0 = __ldcg(reinterpret_cast<const float2 *>(xsrc0[p] + (size_t)ks * SK));
+                    v1 = __ldcg(reinterpret_cast<const float2 *>(xsrc1[p] + (size_t)ks * SK));
+                }
+                xr[p][0] = v0.x; xr[p][1] = v0.y; xr[p][2] = v1.x; xr[p][3] = v1.y;
+            }
+        };
+        // Splits the loaded values into f16 hi + lo and stores the lane's piece; per scale group (the 8 lanes of a
+        // block, the 4 of a Q6_K group) also the accumulator start ci = -offset 2^-24 s sum(x) and cs = 1 / s, where
+        // s is the power of two that brings the group's largest magnitude into [2^13, 2^14).
+        auto convert_x = [&]() {
+#pragma unroll
+            for (int p = 0; p < NPASS; p++) {
+                const uint32_t pc = lane + 32 * p;
+                float am = fmaxf(fmaxf(fabsf(xr[p][0]), fabsf(xr[p][1])), fmaxf(fabsf(xr[p][2]), fabsf(xr[p][3])));
+                float sum = (xr[p][0] + xr[p][1]) + (xr[p][2] + xr[p][3]);
+                constexpr int RED = T == GT_Q6_K ? 2 : 4;   // xor distances 1, 2 (, 4)
+#pragma unroll
+                for (int o = 1; o <= RED; o <<= 1) {
+                    am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+                    sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                }
+                float s, inv;
+                pow2_scale(am, s, inv);
+                // Q4_0: the high nibbles stay where they are in their byte (16 x the code): their activations / 16
+                const float sv = (T == GT_Q4_0 && ((pc >> 2) & 1u)) ? s * 0.0625f : s;
+                uint32_t f0, f1, f2, f3;
+                split4(xr[p][0] * sv, xr[p][1] * sv, xr[p][2] * sv, xr[p][3] * sv, f0, f1, f2, f3);
+                if (pc < (uint32_t)PIECES) {
+                    sts128(xst + pc * 16, f0, f1, f2, f3);
+                    if constexpr (T == GT_Q6_K) {
+                        if ((pc & 3u) == 0) sts64(xcc + (pc >> 2) * 8, __float_as_uint(kOff * (s * sum)), __float_as_uint(inv));
+                    } else {
+                        if ((pc & 7u) == 0) sts64(xcc + (pc >> 3) * 8, __float_as_uint(kOff * (s * sum)), __float_as_uint(inv));
+                    }
+                }
+            }
+        };
+
+        float acc[TPW][4];
+#pragma unroll
+        for (int j = 0; j < TPW; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+        grid_dependency_wait();   // the activations belong to the kernels ahead until they are done
+        load_x(0);
+
+        uint32_t slot = 0, ph = 0, fin_ph = 0;
+        bool ok = true, first_item = true;
+        for (uint32_t item = cta; ok && item < c.items; item += grid) {
+            for (uint32_t s = 0; ok && s < c.spi; s++) {
+                __syncwarp();           // the previous stage's pieces have all been fetched
+                convert_x();
+                __syncwarp();
+                load_x(s + 1 < c.spi ? s + 1 : 0);   // the next stage's values (every item starts at K = 0 again)
+
+                if (!mbar_wait(&full[slot], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, 0xFFFFFFFFu)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t stage = smem_base + slot * STAGE;
+                uint32_t lead = 0;
+                if constexpr (T == GT_Q6_K) {
+                    lead = (s * SBYTES) & 15u;   // a multiple of 4
+                    // d * sub-scale of the warp's scale groups, for every row of the stage (lanes split the rows)
+#pragma unroll
+                    for (int i = 0; i < KB; i++) {
+#pragma unroll
+                        for (int rr = 0; rr < (R + 31) / 32; rr++) {
+                            const uint32_t r = lane + 32 * rr;
+                            if (r < (uint32_t)R) {
+                                const uint32_t rb = stage + r * PITCH + lead + 210 * (sp + 2 * i);
+                                const float d = half_bits_to_float(lds_u16(rb + 208));
+                                float p[4];
+#pragma unroll
+                                for (int q = 0; q < 4; q++) p[q] = d * (float)lds_s8(rb + q6S + 2 * q);
+                                sts128(ptab + (i * R + r) * 16, __float_as_uint(p[0]), __float_as_uint(p[1]), __float_as_uint(p[2]),
+                                       __float_as_uint(p[3]));
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+
+#pragma unroll
+                for (int i = 0; i < KB; i++) {
+                    // ---- the unit's B registers (lanes g < MP hold activation row g) and accumulator starts ----
+                    uint32_t bf[NM][4];
+#pragma unroll
+                    for (int h = 0; h < NM; h++) {
+                        bf[h][0] = bf[h][1] = bf[h][2] = bf[h][3] = 0u;
+                        if (g < (uint32_t)MP) lds128(xst + ((((i * MP + g) * NM + h) * 4 + t) * 16), bf[h][0], bf[h][1], bf[h][2], bf[h][3]);
+                    }
+                    float ci0[NG], cs0[NG], ci1[NG], cs1[NG];
+#pragma unroll
+                    for (int q = 0; q < NG; q++) {
+                        ci0[q] = cs0[q] = ci1[q] = cs1[q] = 0.f;
+                        if (2 * t < (uint32_t)MP) {
+                            uint32_t u0, u1;
+                            lds64(xcc + ((i * MP + 2 * t) * NG + q) * 8, u0, u1);
+                            ci0[q] = __uint_as_float(u0);
+                            cs0[q] = __uint_as_float(u1);
+                        }
+                        if (2 * t + 1 < (uint32_t)MP) {
+                            uint32_t u0, u1;
+                            lds64(xcc + ((i * MP + 2 * t + 1) * NG + q) * 8, u0, u1);
+                            ci1[q] = __uint_as_float(u0);
+                            cs1[q] = __uint_as_float(u1);
+                        }
+                    }
+
+                    if constexpr (T == GT_Q6_K) {
+                        const uint32_t sb = sp + 2 * i;
+#pragma unroll
+                        for (int j = 0; j < TPW; j++) {
+                            uint32_t qv[2][4];   // [row g / g + 8][q1..q4]: four 6-bit codes each, one per byte
+                            uint32_t pv[2][4];
+#pragma unroll
+                            for (int h = 0; h < 2; h++) {
+                                const uint32_t rb = stage + (16 * j + g + 8 * h) * PITCH + lead + 210 * sb;
+                                uint32_t A, B, H;
+                                if (sp == 0) {
+                                    A = lds32(rb + q6A);
+                                    B = lds32(rb + q6A + 32);
+                                    H = lds32(rb + q6H);
+                                } else {   // odd super-blocks start 2 bytes past a 4-byte boundary
+                                    A = __byte_perm(lds32(rb + q6A - 2), lds32(rb + q6A + 2), 0x5432);
+                                    B = __byte_perm(lds32(rb + q6A + 30), lds32(rb + q6A + 34), 0x5432);
+                                    H = __byte_perm(lds32(rb + q6H - 2), lds32(rb + q6H + 2), 0x5432);
+                                }
+                                qv[h][0] = (A & 0x0F0F0F0Fu) | ((H & 0x03030303u) << 4);
+                                qv[h][1] = (B & 0x0F0F0F0Fu) | ((H & 0x0C0C0C0Cu) << 2);
+                                qv[h][2] = ((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u);
+                                qv[h][3] = ((B >> 4) & 0x0F0F0F0Fu) | ((H & 0xC0C0C0C0u) >> 2);
+                                lds128(ptab + (i * R + 16 * j + g + 8 * h) * 16, pv[h][0], pv[h][1], pv[h][2], pv[h][3]);
+                            }
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                const uint32_t a0 = qv[0][q] & 0x00FF00FFu, a2 = (qv[0][q] >> 8) & 0x00FF00FFu;
+                                const uint32_t a1 = qv[1][q] & 0x00FF00FFu, a3 = (qv[1][q] >> 8) & 0x00FF00FFu;
+                                float d[4] = {ci0[q], ci1[q], ci0[q], ci1[q]};
+                                mma16816(d, a0, a1, a2, a3, bf[q][0], bf[q][1], d);
+                                mma16816(d, a0, a1, a2, a3, bf[q][2], bf[q][3], d);
+                                const float pa = __uint_as_float(pv[0][q]), pb = __uint_as_float(pv[1][q]);
+                                acc[j][0] = fmaf(pa * cs0[q], d[0], acc[j][0]);
+                                acc[j][1] = fmaf(pa * cs1[q], d[1], acc[j][1]);
+                                acc[j][2] = fmaf(pb * cs0[q], d[2], acc[j][2]);
+                                acc[j][3] = fmaf(pb * cs1[q], d[3], acc[j][3]);
+                            }
+                        }
+                    } else {
+                        const uint32_t b = KB * w + i, boff = BB * b;
+                        const bool mis = (b & 1u) == 0;
+#pragma unroll
+                        for (int j = 0; j < TPW; j++) {
+                            uint32_t wa[2], wb[2];
+                            float dd[2];
+#pragma unroll
+                            for (int h = 0; h < 2; h++) {
+                                const uint32_t rb = stage + (16 * j + g + 8 * h) * PITCH + boff;
+                                dd[h] = half_bits_to_float(lds_u16(rb));
+                                if constexpr (T == GT_Q8_0) {
+                                    if (!mis) {
+                                        wa[h] = lds32(rb + 2 + 4 * t);
+                                        wb[h] = lds32(rb + 18 + 4 * t);
+                                    } else {
+                                        wa[h] = lds32(rb + 4 + 4 * t);
+                                        // lanes 0..2: the whole word; lane 3: the half words at either end of the block
+                                        wb[h] = __byte_perm(lds32(rb + (t < 3 ? 20 + 4 * t : 0)), lds32(rb + (t < 3 ? 20 + 4 * t : 32)),
+                                                            t < 3 ? 0x3210 : 0x5432);
+                                    }
+                                    wa[h] ^= 0x80808080u;   // signed byte -> byte + 128
+                                    wb[h] ^= 0x80808080u;
+                                } else {
+                                    if (!mis) wa[h] = lds32(rb + 2 + 4 * t);
+                                    else wa[h] = __byte_perm(lds32(rb + (t < 3 ? 4 + 4 * t : 0)), lds32(rb + (t < 3 ? 4 + 4 * t : 16)),
+                                                             t < 3 ? 0x3210 : 0x5432);
+                                    wb[h] = 0;
+                                }
+                            }
+                            float d[4] = {ci0[0], ci1[0], ci0[0], ci1[0]};
+                            if constexpr (T == GT_Q8_0) {
+                                uint32_t a0 = wa[0] & 0x00FF00FFu, a2 = (wa[0] >> 8) & 0x00FF00FFu;
+                                uint32_t a1 = wa[1] & 0x00FF00FFu, a3 = (wa[1] >> 8) & 0x00FF00FFu;
+                                mma16816(d, a0, a1, a2, a3, bf[0][0], bf[0][1], d);
+                                mma16816(d, a0, a1, a2, a3, bf[0][2], bf[0][3], d);
+                                a0 = wb[0] & 0x00FF00FFu; a2 = (wb[0] >> 8) & 0x00FF00FFu;
+                                a1 = wb[1] & 0x00FF00FFu; a3 = (wb[1] >> 8) & 0x00FF00FFu;
+                                mma16816(d, a0, a1, a2, a3, bf[1][0], bf[1][1], d);
+                                mma16816(d, a0, a1, a2, a3, bf[1][2], bf[1][3], d);
+                            } else {
+                                // low nibbles: elements c0..c3 of the word's four bytes; high nibbles (x 16): 16 + c
+                                uint32_t a0 = wa[0] & 0x000F000Fu, a2 = (wa[0] >> 8) & 0x000F000Fu;
+                                uint32_t a1 = wa[1] & 0x000F000Fu, a3 = (wa[1] >> 8) & 0x000F000Fu;
+                                mma16816(d, a0, a1, a2, a3, bf[0][0], bf[0][1], d);
+                                mma16816(d, a0, a1, a2, a3, bf[0][2], bf[0][3], d);
+                                a0 = wa[0] & 0x00F000F0u; a2 = (wa[0] >> 8) & 0x00F000F0u;
+                                a1 = wa[1] & 0x00F000F0u; a3 = (wa[1] >> 8) & 0x00F000F0u;
+                                mma16816(d, a0, a1, a2, a3, bf[1][0], bf[1][1], d);
+                                mma16816(d, a0, a1, a2, a3, bf[1][2], bf[1][3], d);
+                            }
+                            acc[j][0] = fmaf(dd[0] * cs0[0], d[0], acc[j][0]);
+                            acc[j][1] = fmaf(dd[0] * cs1[0], d[1], acc[j][1]);
+                            acc[j][2] = fmaf(dd[1] * cs0[0], d[2], acc[j][2]);
+                            acc[j][3] = fmaf(dd[1] * cs1[0], d[3], acc[j][3]);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[slot]);
+                if (++slot == c.nslots) { slot = 0; ph ^= 1u; }
+            }
+            if (!ok) break;
+
+            // ---- end of the item: add the eight warps' partial sums in a fixed order and write the rows out ----
+            if (!first_item) {   // the previous item's sums have all been read
+                if (!mbar_wait(&fin[1], fin_ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, 0xFFFFFFFFu)) break;
+            }
+#pragma unroll
+            for (int j = 0; j < TPW; j++) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const uint32_t col = 2 * t + (i & 1), row = 16 * j + g + 8 * (i >> 1);
+                    if (col < (uint32_t)MP) sts32(red + ((w * MP + col) * R + row) * 4, __float_as_uint(acc[j][i] * 16777216.0f));
+                    acc[j][i] = 0.f;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&fin[0]);
+            if (!mbar_wait(&fin[0], fin_ph, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, 0xFFFFFFFFu)) break;
+            {
+                const uint32_t ld = qmv_ld(a);
+                for (uint32_t idx = tid; idx < (uint32_t)R * a.m; idx += kMwWarps * 32) {
+                    const uint32_t col = idx / R, row = idx % R;
+                    float sum = 0.f;
+#pragma unroll
+                    for (int ww = 0; ww < kMwWarps; ww++) sum += __uint_as_float(lds32(red + ((ww * MP + col) * R + row) * 4));
+                    const uint32_t grow = item * R + row;
+                    if (grow < a.n) {
+                        const size_t off = (size_t)col * ld + a.y_col0 + grow;
+                        a.y[off] = sum;
+                        for (uint32_t pr = 0; pr < a.n_peer; pr++) a.y_peer[pr][off] = sum;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&fin[1]);
+            fin_ph ^= 1u;
+            first_item = false;
+        }
+    }
+    if (abort_flag) {  // let copies in flight land before the CTA's shared memory is released
+        for (int i = 0; i < 200; i++) __nanosleep(5000);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+static uint32_t mw_uk(int t) { return t == GT_Q6_K ? 512u : 256u; }
+
+bool qmv_mma_supported(int ggml_type, const QmvArgs &a) {
+    if (ggml_type != GT_Q4_0 && ggml_type != GT_Q8_0 && ggml_type != GT_Q6_K) return false;
+    if (a.ids || a.nprob != 1 || a.m < 1 || a.m > 8) return false;
+    if (a.k == 0 || a.n == 0 || a.k % mw_uk(ggml_type) != 0) return false;
+    const uint64_t row_bytes = (uint64_t)(a.k / ggml_qk(ggml_type)) * ggml_block_bytes(ggml_type);
+    if (row_bytes % 16 != 0 || row_bytes >= (1ull << 32)) return false;
+    if (((uintptr_t)a.w & 15u) || ((uintptr_t)a.x & 15u)) return false;
+    if ((uint64_t)a.m * a.n >= (1ull << 32)) return false;
+    return encode_tiled_fn() != nullptr;
+}
+
+static inline size_t mw_align(size_t v, size_t al) { return (v + al - 1) / al * al; }
+
+template <int T, int TPW, int KB, int MP>
+static cudaError_t launch_mw(const QmvArgs &a, int sm_count, int ctas_per_sm, cudaStream_t st) {
+    using TR = MwTraits<T>;
+    constexpr uint32_t R = 16 * TPW, PITCH = mw_pitch(T, KB), STAGE = R * PITCH;
+    constexpr uint32_t PIECES = KB * MP * TR::NM * 4, XST = (PIECES * 16 + KB * MP * TR::NG * 8 + 15u) & ~15u;
+    MwCfg c{};
+    c.items = (a.n + R - 1) / R;
+    c.spi = a.k / (TR::UK * KB);
+    const size_t xst_bytes = mw_align((size_t)kMwWarps * XST, 128);
+    const size_t ptab_bytes = T == GT_Q6_K ? (size_t)kMwWarps * R * 16 * KB : 0;
+    const size_t red_bytes = (size_t)kMwWarps * MP * R * 4;
+    const size_t tail = xst_bytes + ptab_bytes + red_bytes;
+    const size_t budget = 110 * 1024;   // two CTAs per SM
+    uint32_t nslots = (uint32_t)((budget - tail - 1024) / STAGE);
+    if (nslots > (uint32_t)kMwMaxSlots) nslots = kMwMaxSlots;
+    if (nslots < 2) return cudaErrorInvalidConfiguration;
+    c.nslots = nslots;
+    c.xst_off = nslots * STAGE;
+    c.ptab_off = c.xst_off + (uint32_t)xst_bytes;
+    c.red_off = c.ptab_off + (uint32_t)ptab_bytes;
+    const size_t smem = (size_t)c.red_off + red_bytes + 1024;
+
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return cudaErrorNotSupported;
+    const uint32_t row_bytes = (a.k / BlockTraits<T>::QK) * BlockTraits<T>::BYTES;
+    alignas(64) CUtensorMap wmap;
+    {
+        // the weight matrix as [n rows][row_bytes / 8] 8-byte elements; box = R rows x PITCH bytes
+        const cuuint64_t gdim[2] = {row_bytes / 8, a.n};
+        const cuuint64_t gstride[1] = {row_bytes};
+        const cuuint32_t box[2] = {(cuuint32_t)(PITCH / 8), (cuuint32_t)R};
+        const cuuint32_t estr[2] = {1, 1};
+        if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(a.w), gdim, gstride, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    static size_t attr_smem[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    if (smem > attr_smem[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(qmv_mma_kernel<T, TPW, KB, MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        attr_smem[dev] = smem;
+    }
+    uint32_t grid = (uint32_t)(sm_count * ctas_per_sm);
+    if (grid > c.items) grid = c.items;
+    return launch_overlapped(qmv_mma_kernel<T, TPW, KB, MP>, dim3(grid), dim3(kMwThreads), smem, st, a, c, wmap);
+}
+
+// (TPW, KB): a warp works on TPW x KB tile-units per stage.  Few weight rows -> narrow row groups and long K stages.
+// The activation split costs MP x KB per stage and warp whatever TPW is, so many activation rows want KB = 1.
+template <int T, int MP>
+static cudaError_t launch_mw_m(const QmvArgs &a, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
+    const uint32_t kb_ok = a.k / MwTraits<T>::UK;   // KB must divide the number of K units
+    if (tpw >= 4 || MP == 8 || kb_ok % 2 != 0) return launch_mw<T, 4, 1, MP>(a, sm_count, ctas_per_sm, st);
+    if constexpr (MP <= 4) {
+        if (tpw >= 2 || MP == 4 || kb_ok % 4 != 0) return launch_mw<T, 2, 2, MP>(a, sm_count, ctas_per_sm, st);
+    }
+    if constexpr (MP <= 2) return launch_mw<T, 1, 4, MP>(a, sm_count, ctas_per_sm, st);
+    return cudaErrorInvalidConfiguration;
+}
+
+template <int T>
+static cudaError_t launch_mw_t(const QmvArgs &a, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
+    if (a.m <= 1) return launch_mw_m<T, 1>(a, sm_count, ctas_per_sm, tpw, st);
+    if (a.m <= 2) return launch_mw_m<T, 2>(a, sm_count, ctas_per_sm, tpw, st);
+    if (a.m <= 4) return launch_mw_m<T, 4>(a, sm_count, ctas_per_sm, tpw, st);
+    return launch_mw_m<T, 8>(a, sm_count, ctas_per_sm, tpw, st);
+}
+
+// `ctas_per_sm` (1 or 2) and `tpw` (0: chosen from n; 1, 2, 4) are tuning knobs of the caller.
+cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs &a, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
+    if (ctas_per_sm < 1) ctas_per_sm = 1;
+    if (ctas_per_sm > 2) ctas_per_sm = 2;
+    if (tpw <= 0) {
+        // the largest row group that still gives every SM an item
+        tpw = a.n >= 64u * (uint32_t)sm_count ? 4 : a.n >= 32u * (uint32_t)sm_count ? 2 : 1;
+    }
+    switch (ggml_type) {
+    case GT_Q4_0: return launch_mw_t<GT_Q4_0>(a, sm_count, ctas_per_sm, tpw, st);
+    case GT_Q8_0: return launch_mw_t<GT_Q8_0>(a, sm_count, ctas_per_sm, tpw, st);
+    case GT_Q6_K: return launch_mw_t<GT_Q6_K>(a, sm_count, ctas_per_sm, tpw, st);
+    default: return cudaErrorInvalidValue;
+    }
+}
+
+}  // namespace mlxn

@@ -4,6 +4,7 @@
 // The dispatchers mirror upstream src/ops/quantized_matmul_ggml.rs and
 // src/ops/quantized_matmul_id_ggml.rs: same validation order, same messages, same routing rules.
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 
 #include <atomic>
 #include <cstdarg>
@@ -18,6 +19,7 @@
 
 #include "../../include/mlxn_b200.h"
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace mlxn {
 cudaError_t launch_qmv(int ggml_type, const QmvArgs &a, bool want_stream, int sm_count, cudaStream_t st,
@@ -26,6 +28,8 @@ bool qmv_tc_supported(int ggml_type, const QmvArgs &a);
 size_t qmv_tc_scratch_bytes(const QmvArgs &a);
 cudaError_t launch_qmv_tc(int ggml_type, const QmvArgs &a, uint8_t *scratch, uint32_t *flags, int sm_count, cudaStream_t st,
                           cudaStream_t pub_st, cudaEvent_t pub_ev, int *launches);
+bool qmv_mma_supported(int ggml_type, const QmvArgs &a);
+cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs &a, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st);
 cudaError_t launch_qmm_tc(int ggml_type, const QmmArgs &a, bool routed, uint32_t nt, uint8_t *scratch, cudaStream_t st,
                           int *launches);
 cudaError_t launch_qmm_simt(int ggml_type, const QmmArgs &a, bool routed, uint32_t max_rows, cudaStream_t st);
@@ -83,12 +87,14 @@ void mlxn_detail_count_launches(int launches) {
     g_last_kernel = "qmm_tc";
 }
 
-static std::atomic<int> g_opt_qmv{-1}, g_opt_qmm{-1};  // -1 unset; qmv: 0 simple, 1 stream, 2 tc, 3 auto; qmm: 0 simt, 1 tc
+static std::atomic<int> g_opt_qmv{-1}, g_opt_qmm{-1};  // -1 unset; qmv: 0 simple, 1 stream, 2 tc, 3 auto, 4 mma; qmm: 0 simt, 1 tc
+static std::atomic<int> g_opt_mma_ctas{2}, g_opt_mma_tpw{0};   // tuning knobs of the register-level mat-vec
 static int opt_qmv() {
     int v = g_opt_qmv.load();
     if (v < 0) {
         const char *e = getenv("MLXN_QMV");
-        v = (e && strcmp(e, "simple") == 0) ? 0 : (e && strcmp(e, "stream") == 0) ? 1 : (e && strcmp(e, "tc") == 0) ? 2 : 3;
+        v = (e && strcmp(e, "simple") == 0) ? 0 : (e && strcmp(e, "stream") == 0) ? 1 : (e && strcmp(e, "tc") == 0) ? 2
+            : (e && strcmp(e, "mma") == 0) ? 4 : 3;
         g_opt_qmv = v;
     }
     return v;
@@ -159,6 +165,24 @@ struct mlxn_registry {
     std::set<std::string> cached;
 };
 
+// Device status words (see ST_* in common.cuh).  Ref-counted: the kernels of a captured graph keep writing to the
+// block of the encoder that recorded them, so the block must outlive that encoder for as long as the graph exists.
+struct StatusBlock {
+    std::atomic<int> refs{1};
+    int ordinal = 0;
+    uint32_t *dev = nullptr;
+};
+static void status_block_release(StatusBlock *sb) {
+    if (sb && sb->refs.fetch_sub(1) == 1) {
+        int prev = 0;
+        cudaGetDevice(&prev);
+        cudaSetDevice(sb->ordinal);
+        cudaFree(sb->dev);
+        cudaSetDevice(prev);
+        delete sb;
+    }
+}
+
 struct mlxn_graph {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
@@ -169,6 +193,11 @@ struct mlxn_graph {
     std::vector<mlxn_buffer *> uploads, outputs;  // hold a reference each
     std::vector<bool> fetched;                    // per output: the graph copies it back to its host shadow itself
     std::vector<bool> covered;                    // per output: its storage is fetched by one of the graph's copies
+    // What the recorded kernels address besides the caller's buffers belongs to the graph: the scratch arenas that
+    // were in use while it was recorded (freed when the graph is destroyed) and the recording encoder's status block.
+    int ordinal = 0;
+    std::vector<std::pair<void *, size_t>> scratch;
+    StatusBlock *sb = nullptr;
 };
 
 // Scratch arenas outlive their encoder: short-lived encoders (one per command buffer, as upstream uses them) would
@@ -232,7 +261,12 @@ struct mlxn_encoder {
     size_t scratch_lane_bytes[kLanes] = {};
     std::vector<std::pair<void *, size_t>> retired;  // outgrown scratch arenas, handed back after the next wait
     std::vector<mlxn_buffer *> cap_uploads, cap_outputs;  // see mlxn_graph; filled while a capture is open
-    uint32_t *status_dev = nullptr;
+    // arenas set aside while a capture is open (the capture draws fresh ones, which the graph then owns)
+    uint8_t *saved_scratch[kLanes] = {};
+    size_t saved_scratch_bytes[kLanes] = {};
+    std::vector<std::pair<void *, size_t>> cap_retired;   // arenas outgrown during the capture: also the graph's
+    StatusBlock *sb = nullptr;
+    uint32_t *status_dev = nullptr;   // == sb->dev
     uint32_t *status_host = nullptr;  // pinned
 };
 
@@ -288,7 +322,16 @@ extern "C" int mlxn_set_option(const char *key, const char *value) {
         else if (strcmp(value, "tc") == 0) g_opt_qmv = 2;
         else if (strcmp(value, "stream") == 0) g_opt_qmv = 1;
         else if (strcmp(value, "simple") == 0) g_opt_qmv = 0;
-        else return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: qmv must be 'auto', 'tc', 'stream' or 'simple'");
+        else if (strcmp(value, "mma") == 0) g_opt_qmv = 4;
+        else return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: qmv must be 'auto', 'mma', 'tc', 'stream' or 'simple'");
+        return MLXN_OK;
+    }
+    if (strcmp(key, "qmv_mma_ctas") == 0 || strcmp(key, "qmv_mma_tpw") == 0) {
+        const int v = atoi(value);
+        const bool ctas = key[8] == 'c';
+        if (ctas ? (v < 1 || v > 2) : !(v == 0 || v == 1 || v == 2 || v == 4))
+            return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: value '%s' out of range", key, value);
+        (ctas ? g_opt_mma_ctas : g_opt_mma_tpw) = v;
         return MLXN_OK;
     }
     if (strcmp(key, "qmm") == 0) {
@@ -554,6 +597,34 @@ extern "C" int mlxn_pool_release(mlxn_pool *pool, mlxn_buffer *buf) {
     mlxn_buffer_release(buf);
     return MLXN_OK;
 }
+extern "C" int mlxn_pool_alloc_batch(mlxn_pool *pool, mlxn_device *dev, size_t count, const size_t *byte_lens,
+                                     const int *dtypes, const size_t *shapes, const size_t *ranks, mlxn_buffer **out) {
+    if (!pool || !dev || !out || (count && (!byte_lens || !dtypes)))
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: pool, device, sizes, dtypes and out must not be null");
+    size_t shape_at = 0;
+    for (size_t i = 0; i < count; i++) {
+        const size_t rank = (shapes && ranks) ? ranks[i] : 0;
+        const int rc = mlxn_pool_alloc(pool, dev, byte_lens[i], dtypes[i], rank ? shapes + shape_at : nullptr, rank, &out[i]);
+        shape_at += rank;
+        if (rc) {
+            // all or nothing: what this call handed out goes back to the free lists (the error message stays)
+            const std::string msg = g_last_error;
+            for (size_t j = 0; j < i; j++) {
+                for (size_t u = pool->in_use.size(); u-- > 0;)
+                    if (pool->in_use[u].second == out[j]->st) {
+                        storage_release(pool->in_use[u].second);
+                        pool->in_use.erase(pool->in_use.begin() + u);
+                        break;
+                    }
+                mlxn_pool_release(pool, out[j]);
+                out[j] = nullptr;
+            }
+            g_last_error = msg;
+            return rc;
+        }
+    }
+    return MLXN_OK;
+}
 extern "C" void mlxn_pool_reset(mlxn_pool *pool) {
     if (!pool) return;
     for (auto &p : pool->in_use) pool->free_list[p.first].push_back(p.second);
@@ -661,6 +732,11 @@ extern "C" int mlxn_encoder_create(mlxn_device *dev, mlxn_encoder **out) {
     // status word, then (256 bytes in) the zero-initialised flag words the tensor-core mat-vec's CTAs hand work over with
     if (err == cudaSuccess) err = cudaMalloc((void **)&e->status_dev, kStatusBlockBytes);
     if (err == cudaSuccess) err = cudaMemset(e->status_dev, 0, kStatusBlockBytes);
+    if (err == cudaSuccess) {
+        e->sb = new StatusBlock();
+        e->sb->ordinal = dev->ordinal;
+        e->sb->dev = e->status_dev;
+    }
     if (err == cudaSuccess) err = cudaHostAlloc((void **)&e->status_host, 4, cudaHostAllocDefault);
     if (err != cudaSuccess) {
         for (int l = 0; l < kLanes; l++) {
@@ -673,7 +749,8 @@ extern "C" int mlxn_encoder_create(mlxn_device *dev, mlxn_encoder **out) {
         if (e->ev_aux_join) cudaEventDestroy(e->ev_aux_join);
         if (e->ev_start) cudaEventDestroy(e->ev_start);
         if (e->ev_end) cudaEventDestroy(e->ev_end);
-        if (e->status_dev) cudaFree(e->status_dev);
+        if (e->sb) status_block_release(e->sb);
+        else if (e->status_dev) cudaFree(e->status_dev);
         delete e;
         return cuda_fail(err, "encoder creation");
     }
@@ -729,9 +806,12 @@ extern "C" void mlxn_encoder_destroy(mlxn_encoder *enc) {
         }
     }
     (void)cudaGetLastError();
-    for (int l = 0; l < kLanes; l++)
+    for (int l = 0; l < kLanes; l++) {
         if (enc->scratch_lane[l]) scratch_give(enc->ordinal, enc->scratch_lane[l], enc->scratch_lane_bytes[l]);
-    cudaFree(enc->status_dev);
+        if (enc->saved_scratch[l]) scratch_give(enc->ordinal, enc->saved_scratch[l], enc->saved_scratch_bytes[l]);
+    }
+    for (auto &pr : enc->cap_retired) scratch_give(enc->ordinal, pr.first, pr.second);
+    status_block_release(enc->sb);
     cudaFreeHost(enc->status_host);
     cudaEventDestroy(enc->ev_start);
     cudaEventDestroy(enc->ev_end);
@@ -746,7 +826,15 @@ extern "C" void mlxn_encoder_destroy(mlxn_encoder *enc) {
     delete enc;
 }
 
-extern "C" void *mlxn_encoder_stream(mlxn_encoder *enc) { return enc ? (void *)enc->lanes[0] : nullptr; }
+static int encoder_join_lanes(mlxn_encoder *e);
+// Lane 0, after it has been made to wait for the other lane: work the caller enqueues on the returned stream runs
+// behind everything encoded so far.
+extern "C" void *mlxn_encoder_stream(mlxn_encoder *enc) {
+    if (!enc) return nullptr;
+    cudaSetDevice(enc->ordinal);
+    if (!enc->capturing && encoder_join_lanes(enc) != MLXN_OK) return nullptr;
+    return (void *)enc->lanes[0];
+}
 
 // Ends the current concurrent group: lane 0 waits for every other lane that has work of the group; the next
 // operation starts a new group on lane 0.
@@ -866,6 +954,57 @@ extern "C" int mlxn_encoder_commit_wait_with_gpu_time(mlxn_encoder *enc, double 
     return MLXN_OK;
 }
 
+// Per-command-buffer profile (upstream kernel_profile, enabled by MLX_PROFILE_CB=1): device time per label.
+static std::mutex g_prof_mu;
+static std::map<std::string, std::pair<uint64_t, uint64_t>> g_prof;   // label -> (command buffers, nanoseconds)
+static bool profile_cb_enabled() {
+    static const bool on = [] { const char *e = getenv("MLX_PROFILE_CB"); return e && *e && strcmp(e, "0") != 0; }();
+    return on;
+}
+extern "C" int mlxn_encoder_commit_and_wait_labeled(mlxn_encoder *enc, const char *label) {
+    if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
+    const char *name = label ? label : "";
+    nvtxRangePushA(name);   // visible to a profiler that is attached; a no-op otherwise
+    int rc;
+    if (profile_cb_enabled()) {
+        double s = 0.0;
+        rc = mlxn_encoder_commit_wait_with_gpu_time(enc, &s);
+        if (rc == MLXN_OK) {
+            const uint64_t ns = (uint64_t)(s * 1e9);
+            {
+                std::lock_guard<std::mutex> lk(g_prof_mu);
+                auto &e = g_prof[name];
+                e.first++;
+                e.second += ns;
+            }
+            fprintf(stderr, "[mlx-native] cb %s: %.3f us\n", name, s * 1e6);
+        }
+    } else {
+        rc = mlxn_encoder_commit_and_wait(enc);
+    }
+    nvtxRangePop();
+    return rc;
+}
+// Profile mode turns the asynchronous commit into a synchronous one to get the device time, as upstream does.
+extern "C" int mlxn_encoder_commit_labeled(mlxn_encoder *enc, const char *label) {
+    if (profile_cb_enabled()) return mlxn_encoder_commit_and_wait_labeled(enc, label);
+    nvtxRangePushA(label ? label : "");
+    const int rc = mlxn_encoder_commit(enc);
+    nvtxRangePop();
+    return rc;
+}
+extern "C" int mlxn_profile_cb_get(const char *label, uint64_t *count, uint64_t *nanoseconds) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    auto it = g_prof.find(label ? label : "");
+    if (count) *count = it == g_prof.end() ? 0 : it->second.first;
+    if (nanoseconds) *nanoseconds = it == g_prof.end() ? 0 : it->second.second;
+    return MLXN_OK;
+}
+extern "C" void mlxn_profile_cb_reset(void) {
+    std::lock_guard<std::mutex> lk(g_prof_mu);
+    g_prof.clear();
+}
+
 extern "C" int mlxn_encoder_begin_capture(mlxn_encoder *enc) {
     if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
     if (enc->capturing) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: a capture is already open");
@@ -874,6 +1013,14 @@ extern "C" int mlxn_encoder_begin_capture(mlxn_encoder *enc) {
     if (jrc) return jrc;
     CUDA_TRY(cudaStreamBeginCapture(enc->lanes[0], cudaStreamCaptureModeRelaxed), "begin capture");
     enc->capturing = true;
+    // the recorded kernels must not address arenas that later eager work may outgrow and hand back: the capture
+    // draws arenas of its own, which the graph keeps
+    for (int l = 0; l < kLanes; l++) {
+        enc->saved_scratch[l] = enc->scratch_lane[l];
+        enc->saved_scratch_bytes[l] = enc->scratch_lane_bytes[l];
+        enc->scratch_lane[l] = nullptr;
+        enc->scratch_lane_bytes[l] = 0;
+    }
     enc->cap_launch0 = g_launches.load();
     enc->cap_dispatch0 = g_dispatch.load();
     return MLXN_OK;
@@ -885,6 +1032,18 @@ extern "C" int mlxn_encoder_end_capture(mlxn_encoder *enc, mlxn_graph **out) {
     int jrc = encoder_join_lanes(enc);  // every forked lane rejoins lane 0 before the capture ends
     enc->capturing = false;
     auto *g = new mlxn_graph();
+    g->ordinal = enc->ordinal;
+    for (int l = 0; l < kLanes; l++) {
+        if (enc->scratch_lane[l]) g->scratch.push_back({enc->scratch_lane[l], enc->scratch_lane_bytes[l]});
+        enc->scratch_lane[l] = enc->saved_scratch[l];
+        enc->scratch_lane_bytes[l] = enc->saved_scratch_bytes[l];
+        enc->saved_scratch[l] = nullptr;
+        enc->saved_scratch_bytes[l] = 0;
+    }
+    for (auto &pr : enc->cap_retired) g->scratch.push_back(pr);
+    enc->cap_retired.clear();
+    g->sb = enc->sb;
+    g->sb->refs.fetch_add(1);
     // Results the host already has a view of are fetched back by the graph itself (copy nodes behind all the work),
     // so that a replay costs no device-to-host call per result at commit time.
     if (!jrc) {
@@ -913,6 +1072,8 @@ extern "C" int mlxn_encoder_end_capture(mlxn_encoder *enc, mlxn_graph **out) {
     if (e == cudaSuccess) e = cudaGraphInstantiate(&g->exec, g->graph, 0);
     if (e != cudaSuccess) {
         if (g->graph) cudaGraphDestroy(g->graph);
+        for (auto &pr : g->scratch) scratch_give(g->ordinal, pr.first, pr.second);   // nothing was launched
+        status_block_release(g->sb);
         delete g;
         for (mlxn_buffer *b : enc->cap_uploads) mlxn_buffer_release(b);
         for (mlxn_buffer *b : enc->cap_outputs) mlxn_buffer_release(b);
@@ -932,13 +1093,24 @@ extern "C" int mlxn_encoder_end_capture(mlxn_encoder *enc, mlxn_graph **out) {
 }
 extern "C" int mlxn_graph_launch(mlxn_graph *graph, mlxn_encoder *enc) {
     if (!graph || !enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: graph and encoder must not be null");
+    if (enc->capturing) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: graph launch while a capture is open");
+    // the recorded kernels report through the status block of the encoder that recorded them
+    if (graph->sb != enc->sb)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: a captured graph replays on the encoder that recorded it");
     int rc = encoder_begin_work(enc);
     if (rc) return rc;
     if ((rc = encoder_join_lanes(enc))) return rc;  // the graph's buffers are unknown here: it is its own group
     CUDA_TRY(cudaGraphLaunch(graph->exec, enc->lanes[0]), "graph launch");
     for (mlxn_buffer *b : graph->uploads) {
-        std::lock_guard<std::mutex> lk(b->st->mu);
-        b->st->host_newer = false;  // the replay has just read the shadow
+        {
+            std::lock_guard<std::mutex> lk(b->st->mu);
+            // the replay's copy node reads the pinned shadow when lane 0 gets there: a host write has to wait for it
+            b->st->host_newer = false;
+            b->st->last_stream = enc->lanes[0];
+            b->st->has_last = true;
+        }
+        b->refs.fetch_add(1);
+        enc->retained.push_back(b);
     }
     for (size_t oi = 0; oi < graph->outputs.size(); oi++) {
         mlxn_buffer *b = graph->outputs[oi];
@@ -959,6 +1131,16 @@ extern "C" int mlxn_graph_launch(mlxn_graph *graph, mlxn_encoder *enc) {
 }
 extern "C" void mlxn_graph_destroy(mlxn_graph *graph) {
     if (!graph) return;
+    if (!graph->scratch.empty()) {
+        // a replay may still be running on some stream: wait before the arenas go back
+        int prev = 0;
+        cudaGetDevice(&prev);
+        cudaSetDevice(graph->ordinal);
+        cudaDeviceSynchronize();
+        for (auto &pr : graph->scratch) scratch_give(graph->ordinal, pr.first, pr.second);
+        cudaSetDevice(prev);
+    }
+    status_block_release(graph->sb);
     for (mlxn_buffer *b : graph->uploads) mlxn_buffer_release(b);
     for (mlxn_buffer *b : graph->outputs) mlxn_buffer_release(b);
     if (graph->exec) cudaGraphExecDestroy(graph->exec);
@@ -980,7 +1162,7 @@ static int encoder_scratch(mlxn_encoder *e, size_t bytes, uint8_t **out) {
                 return fail(MLXN_BUFFER_ALLOCATION_ERROR, "Failed to allocate device buffer of %zu bytes", want);
             }
         }
-        if (scratch) e->retired.push_back({scratch, scratch_bytes});
+        if (scratch) (e->capturing ? e->cap_retired : e->retired).push_back({scratch, scratch_bytes});
         scratch = static_cast<uint8_t *>(p);
         scratch_bytes = want;
     }
@@ -1076,6 +1258,37 @@ static int op_begin(mlxn_encoder *e, std::initializer_list<OpBuf> bufs) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// the give-up path of the kernels' bounded waits, made reachable for a test
+// ------------------------------------------------------------------------------------------------
+// One CTA waits, with the given limit, on a shared-memory barrier that nothing ever arrives at.  The wait runs out,
+// the kernel records ST_WAIT_FULL_TIMEOUT in the encoder's status word and returns normally: the context stays
+// usable and the next commit reports CommandBufferError, exactly as a production kernel's expired wait would.
+__global__ void wait_probe_kernel(uint32_t *status, uint64_t limit_ns) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ volatile uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mlxn::mbar_init(&bar, 1);
+        mlxn::mbar_init_fence();
+    }
+    __syncthreads();
+    (void)mlxn::mbar_wait(&bar, 0u, &abort_flag, status, mlxn::ST_WAIT_FULL_TIMEOUT, 0u, limit_ns);
+}
+
+extern "C" int mlxn_debug_wait_probe(mlxn_encoder *enc, uint32_t limit_us) {
+    if (!enc) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder must not be null");
+    if (limit_us == 0 || limit_us > 100000)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: wait probe limit (%u us) must be in 1..100000", limit_us);
+    int rc = encoder_begin_work(enc);
+    if (rc) return rc;
+    if ((rc = encoder_join_lanes(enc))) return rc;
+    wait_probe_kernel<<<1, 32, 0, enc->lanes[0]>>>(enc->status_dev, (uint64_t)limit_us * 1000ull);
+    CUDA_TRY(cudaGetLastError(), "wait probe launch");
+    g_launches.fetch_add(1);
+    return MLXN_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
 // quantized_matmul_ggml
 // ------------------------------------------------------------------------------------------------
 static const char *mv_kernel_name(int t) {
@@ -1138,6 +1351,14 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
         static const int min_m_q6k = [] { const char *e = getenv("MLXN_QMV_TC_MIN_M_Q6K"); return e ? atoi(e) : 1; }();
         const int need_m = (int)p->ggml_type == GT_Q6_K ? (a.k >= 8192 ? (min_m_q6k < 2 ? min_m_q6k : 2) : min_m_q6k) : min_m;
         const bool want_tc = mode == 2 || (mode == 3 && (int)a.m >= need_m);
+        if (mode == 4 && qmv_mma_supported((int)p->ggml_type, a)) {
+            // register-level tensor-core mat-vec: one launch, no scratch, every output written once
+            CUDA_TRY(launch_qmv_mma((int)p->ggml_type, a, dev->sm_count, g_opt_mma_ctas.load(), g_opt_mma_tpw.load(), enc->stream),
+                     "mat-vec launch");
+            g_launches.fetch_add(1);
+            g_last_kernel = "qmv_mma";
+            continue;
+        }
         if (want_tc && qmv_tc_supported((int)p->ggml_type, a)) {
             // tensor-core path: packed activations, block sums and split-K partial sums live in the encoder's arena
             uint8_t *scratch = nullptr;

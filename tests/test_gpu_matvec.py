@@ -15,15 +15,15 @@ def ctx():
     return Ctx()
 
 
-@pytest.fixture(params=["tc", "stream", "simple"])
+@pytest.fixture(params=["mma", "tc", "stream", "simple"])
 def variant(request):
-    # "tc" is the library default; shapes the tensor-core kernel does not take fall through to "stream"
+    # shapes the tensor-core kernels ("mma", "tc") do not take fall through to "stream"
     mx.set_option("qmv", request.param)
     yield request.param
     mx.set_option("qmv", "auto")
 
 
-KERNEL_OF = {"tc": "qmv_tc", "stream": "qmv_stream", "simple": "qmv_simple"}
+KERNEL_OF = {"mma": "qmv_mma", "tc": "qmv_tc", "stream": "qmv_stream", "simple": "qmv_simple"}
 
 
 def check(ctx, tname, wq, x, n, k, abs_tol=None, tol=MV_TOL):
@@ -88,7 +88,7 @@ def test_all_m(ctx, variant, tname, m):
 @pytest.mark.parametrize("tname", ["Q8_0", "Q6_K"])
 @pytest.mark.parametrize("n,k", [(4096, 4096), (12288, 4096), (4096, 12288)])
 @pytest.mark.parametrize("m", [1, 8])
-@pytest.mark.parametrize("kernel", ["tc", "stream"])
+@pytest.mark.parametrize("kernel", ["mma", "tc", "stream"])
 def test_decode_sweep_shapes(ctx, tname, n, k, m, kernel):
     mx.set_option("qmv", kernel)
     wq = normal_weights(11, n, k, TYPES[tname][1])
@@ -140,7 +140,7 @@ def test_zero_weights_and_zero_scale(ctx, variant):
 
 
 def test_kernels_agree_closely(ctx):
-    """The three mat-vec kernels agree to within summation-order rounding."""
+    """The four mat-vec kernels agree to within summation-order rounding."""
     n, k = 512, 4096
     for tname in ("Q4_0", "Q8_0", "Q6_K"):
         gtype, otype = TYPES[tname]
@@ -153,10 +153,14 @@ def test_kernels_agree_closely(ctx):
         mx.set_option("qmv", "tc")
         c = ctx.matmul(gtype, wq, x, n, k)
         assert mx.last_kernel_name() == "qmv_tc"
+        mx.set_option("qmv", "mma")
+        e = ctx.matmul(gtype, wq, x, n, k)
+        assert mx.last_kernel_name() == "qmv_mma"
         _, ad = orc.qmatmul(otype, wq, x, n, k, nthreads=8)
         mx.set_option("qmv", "auto")
         assert norm_err(a, b, ad) <= MV_TOL
         assert norm_err(a, c, ad) <= MV_TOL
+        assert norm_err(a, e, ad) <= MV_TOL
 
 
 # ---- error behaviour (src/ops/quantized_matmul_ggml.rs:283-334)

@@ -224,3 +224,128 @@ def test_graph_replay_with_host_views(ctx):
         enc.commit_and_wait()
         y_ref, ad = orc.qmatmul(otype, wq, x, n, k, nthreads=8)
         assert norm_err(yb.as_slice(np.float32).reshape(m, n), y_ref, ad) <= MV_TOL
+
+
+def test_graph_outlives_eager_growth_of_the_encoder_scratch(ctx):
+    """A captured graph owns the scratch arenas its kernels address: a larger eager operation on the same encoder
+    afterwards (which outgrows and hands back the encoder's own arena) must not disturb a later replay."""
+    mx.set_option("qmv", "tc")                               # the mat-vec kernel that uses scratch memory
+    d = ctx.device
+    gtype, otype = TYPES["Q8_0"]
+    n, k, m = 512, 1024, 4
+    wq = normal_weights(51, n, k, otype)
+    x = normal_acts(51, m, k)
+    w, xb = ctx.buf(wq, mx.DType.U8), ctx.buf(x, mx.DType.F32)
+    yb = d.alloc_buffer(m * n * 4, mx.DType.F32)
+    p = mx.GgmlQuantizedMatmulParams(m, n, k, gtype)
+    enc = d.command_encoder()
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, w, yb, p)
+    enc.commit_and_wait()
+    enc.begin_capture()
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, w, yb, p)
+    g = enc.end_capture()
+    assert mx.last_kernel_name() == "qmv_tc"
+    # a prefill-sized mat-mat on the same encoder: its packed activations need a much larger arena
+    n2, k2, m2 = 256, 4096, 512
+    w2q = normal_weights(52, n2, k2, otype)
+    x2 = normal_acts(52, m2, k2)
+    y2 = ctx.matmul(gtype, w2q, x2, n2, k2)
+    w2, x2b = ctx.buf(w2q, mx.DType.U8), ctx.buf(x2, mx.DType.F32)
+    y2b = d.alloc_buffer(m2 * n2 * 4, mx.DType.F32)
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, x2b, w2, y2b, mx.GgmlQuantizedMatmulParams(m2, n2, k2, gtype))
+    enc.commit_and_wait()
+    assert np.array_equal(y2b.as_slice(np.float32).reshape(m2, n2), y2)
+    yb.as_mut_slice(np.float32)[:] = 0
+    g.launch(enc)
+    enc.commit_and_wait()
+    y_ref, ad = orc.qmatmul(otype, wq, x, n, k, nthreads=8)
+    assert norm_err(yb.as_slice(np.float32).reshape(m, n), y_ref, ad) <= MV_TOL
+    # a graph replays on the encoder that recorded it
+    other = d.command_encoder()
+    other_is_same = False
+    try:
+        g.launch(other)
+        other_is_same = True     # a pooled encoder may hand the recording encoder's resources out again
+    except mx.InvalidArgument as e:
+        assert "encoder that recorded it" in str(e)
+    if other_is_same:
+        other.commit_and_wait()
+
+
+def test_host_view_rewritten_right_after_a_replay(ctx):
+    """The replay's upload node reads the pinned host view when the stream gets there; a host write issued straight
+    after graph_launch (no wait) has to wait for that read instead of changing what the replay sees."""
+    d = ctx.device
+    gtype, otype = TYPES["Q8_0"]
+    n, k, m = 2048, 4096, 1
+    wq = normal_weights(61, n, k, otype)
+    w = ctx.buf(wq, mx.DType.U8)
+    xb = d.alloc_buffer(m * k * 4, mx.DType.F32)
+    ys = [d.alloc_buffer(m * n * 4, mx.DType.F32) for _ in range(2)]
+    p = mx.GgmlQuantizedMatmulParams(m, n, k, gtype)
+    enc = d.command_encoder()
+    xs = [normal_acts(61 + i, m, k) for i in range(3)]
+    graphs = []
+    for yb in ys:
+        xb.as_mut_slice(np.float32)[:] = xs[0].reshape(-1)
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, w, yb, p)
+        enc.commit_and_wait()
+        xb.as_mut_slice(np.float32)[:] = xs[0].reshape(-1)
+        enc.begin_capture()
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, w, yb, p)
+        graphs.append(enc.end_capture())
+    xb.as_mut_slice(np.float32)[:] = xs[1].reshape(-1)
+    graphs[0].launch(enc)
+    xb.as_mut_slice(np.float32)[:] = xs[2].reshape(-1)       # no wait in between
+    graphs[1].launch(enc)
+    enc.commit_and_wait()
+    for yb, x in zip(ys, xs[1:]):
+        y_ref, ad = orc.qmatmul(otype, wq, x, n, k, nthreads=8)
+        assert norm_err(yb.as_slice(np.float32).reshape(m, n), y_ref, ad) <= MV_TOL
+
+
+def test_bounded_wait_that_runs_out_is_reported_and_recoverable(ctx):
+    """src/encoder.rs:1867-1878, src/error.rs:87-89: a failed command buffer surfaces as CommandBufferError at the wait
+    and is transient.  Here the failure is a kernel wait that gives up after its limit; nothing faults or hangs, the
+    kernel returns normally with a status word, and the same encoder computes correctly afterwards."""
+    d = ctx.device
+    gtype, otype = TYPES["Q8_0"]
+    n, k, m = 256, 1024, 2
+    wq = normal_weights(71, n, k, otype)
+    x = normal_acts(71, m, k)
+    enc = d.command_encoder()
+    enc.debug_wait_probe(1000)
+    with pytest.raises(mx.CommandBufferError, match="gave up waiting for data") as ei:
+        enc.commit_and_wait()
+    assert ei.value.is_transient()
+    w, xb = ctx.buf(wq, mx.DType.U8), ctx.buf(x, mx.DType.F32)
+    yb = d.alloc_buffer(m * n * 4, mx.DType.F32)
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, w, yb, mx.GgmlQuantizedMatmulParams(m, n, k, gtype))
+    enc.commit_and_wait()                                    # the status word was cleared: no stale error
+    y_ref, ad = orc.qmatmul(otype, wq, x, n, k, nthreads=8)
+    assert norm_err(yb.as_slice(np.float32).reshape(m, n), y_ref, ad) <= MV_TOL
+    with pytest.raises(mx.InvalidArgument):
+        enc.debug_wait_probe(0)
+
+
+def test_pool_alloc_batch_and_labeled_commits(ctx):
+    d = ctx.device
+    pool = mx.MlxBufferPool()
+    bufs = pool.alloc_batch(d, [(3000, mx.DType.U8, [3000]), (64, mx.DType.F32, [4, 4]), (5000, mx.DType.F32, None)])
+    assert [b.byte_len() for b in bufs] == [4096, 64, 8192] and bufs[1].shape() == [4, 4]
+    assert pool.in_use_count() == 3
+    with pytest.raises(mx.InvalidArgument):
+        pool.alloc_batch(d, [(128, mx.DType.U8, None), (0, mx.DType.U8, None)])
+    assert pool.in_use_count() == 3                          # all or nothing: the first request of the failed batch went back
+    enc = d.command_encoder()
+    gtype, otype = TYPES["Q4_0"]
+    wq = normal_weights(81, 64, 256, otype)
+    w, xb = ctx.buf(wq, mx.DType.U8), ctx.buf(normal_acts(81, 1, 256), mx.DType.F32)
+    yb = d.alloc_buffer(64 * 4, mx.DType.F32)
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, w, yb, mx.GgmlQuantizedMatmulParams(1, 64, 256, gtype))
+    enc.commit_labeled("layer.test")
+    enc.wait_until_completed()
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, w, yb, mx.GgmlQuantizedMatmulParams(1, 64, 256, gtype))
+    enc.commit_and_wait_labeled("layer.test")
+    n_cb, ns = mx.profile_cb_get("layer.test")
+    assert (n_cb, ns) == (0, 0) or ns > 0                    # the table fills only under MLX_PROFILE_CB=1
