@@ -6,12 +6,20 @@ Headline (`value`): weight GB/s of the decode mat-vec sweep — Qwen3-8B-shaped 
 step, every launch on its own weight buffer (915 MB per step, so each launch finds its weights cold in L2).
 One step = one pass over the sweep, replayed from a CUDA graph; timed with CUDA events on the launching stream.
 
+The 32 mat-vecs of a step are independent, so the encoder may overlap them, and mat-vecs of one block type and
+activation-row class that follow one another leave as one kernel; the sweep is therefore encoded row count by row
+count.  The same sweep is also timed as a DEPENDENT CHAIN (all 32 write one shared result buffer, so each waits for
+the one ahead, as the projections of a decoder layer do): that figure is the one in `roofline`; the independent one
+is `value` and `roofline_independent`.
+
 Also reported on the same JSON line: `e2e` (same sweep through the public API with host buffers: activations
-written on the host, uploaded, results read back), `roofline` (mat-vec kernel vs measured HBM copy peak),
-`cpu_baseline` (the CPU oracle on a bounded sample), `clocks`, `gpu_launches`, and under `extra` the prefill
-mat-mat TFLOP/s and the MoE expert-routed tokens/s.
+written on the host, uploaded, results read back), `cpu_baseline` (the CPU oracle on a bounded sample, all host
+threads and one thread), `clocks`, `gpu_launches`, and `roofline_by_config`: one entry per benchmark configuration
+(Q4_0 4096x4096 mat-vec; the sweep; the twelve prefill mat-mat cells in TFLOP/s against the measured bf16 burst and the
+nominal 2250; the MoE FFN layer in tokens/s and expert-weight GB/s; the lm_head at m = 1 and m = 256).
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+  python bench.py --case mv|mm|moe|moe_layer|cmp [args]     small fixed workloads for profiler captures (see run_case)
 For N > 1 launch with torch.distributed.run; weights are sharded along N (rows) and every rank's mat-vec kernels
 store their columns of the result straight into all ranks' result buffers (peer memory over NVLink, allocated as
 torch symmetric memory), with one cross-rank barrier per step ("strong" scaling: the total work is fixed).  If
@@ -52,6 +60,32 @@ def measured_peaks():
         return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
     except Exception:
         return 6650.0, 1590.0, "fallback"
+
+
+def traffic_ratio(launches):
+    """DRAM bytes per algorithmic byte of the mat-vec kernels, from the ncu captures summarised in
+    profiles/matvec_dram_traffic.md (rows `| kernel | type | shape | m | algorithmic MB | dram MB | ratio |`),
+    weighted by the sweep's bytes per block type."""
+    table = {}
+    try:
+        with open(os.path.join(ROOT, "profiles", "matvec_dram_traffic.md")) as f:
+            for line in f:
+                cells = [c.strip() for c in line.strip().strip("|").split("|")]
+                if len(cells) >= 7 and cells[0].startswith("qmv_"):
+                    table.setdefault(cells[1], []).append(float(cells[6]))
+    except Exception:
+        return None, "profiles/matvec_dram_traffic.md not found"
+    tot = num = 0.0
+    for L in launches:
+        b = weight_bytes(L["t"], L["n_loc"], L["k"])
+        rs = table.get(L["t"])
+        if rs:
+            tot += b
+            num += b * (sum(rs) / len(rs))
+    if tot == 0:
+        return None, "no capture for these block types in profiles/matvec_dram_traffic.md"
+    return num / tot, ("dram__bytes_read+write per algorithmic byte from profiles/matvec_dram_traffic.md (mean per block "
+                       "type over the captured shapes), scaled to the step")
 
 
 class ClockSampler:
@@ -122,36 +156,16 @@ def run_reference(args, rank, world):
     on a bounded sample of the sweep: every (type, shape) at m = 1, a slice of the weight rows each."""
     if rank != 0:
         return
-    from oracle import oracle as orc
-
-    otype = {"Q8_0": orc.Q8_0, "Q6_K": orc.Q6_K}
     cores = os.cpu_count() or 1
-    rng = np.random.default_rng(0)
-    sample_rows = 512
-    items = []
-    for t in TYPE_NAMES:
-        for (n, k) in SHAPES:
-            rows = min(n, sample_rows)
-            wf = (rng.standard_normal((rows, k), dtype=np.float32) * np.float32(0.02))
-            items.append((t, rows, k, orc.quantize(otype[t], wf, rule="ggml"), rng.standard_normal((1, k)).astype(np.float32)))
-    step_bytes = sum(w.size for (_, _, _, w, _) in items)
-
-    def step():
-        for (t, rows, k, w, x) in items:
-            orc.qmatmul(otype[t], w, x, rows, k, nthreads=cores, want_absdot=False)
-
-    for _ in range(args.warmup):
-        step()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step()
-    dt = (time.perf_counter() - t0) / args.steps
+    items, step_bytes, sample_rows = reference_sample()
+    dt = time_oracle(items, cores, steps=args.steps, warmup=args.warmup)
     gbs = step_bytes / dt / 1e9
-    sample = f"{sample_rows} weight rows of each of the 8 (type, shape) pairs at m=1, {cores} threads"
+    sample = (f"the whole sweep cut to {sample_rows} weight rows per mat-vec ({step_bytes / 1e6:.1f} MB of weights per pass), "
+              f"{cores} threads")
     line = {"impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "decode mat-vec sweep (Qwen3-8B shapes, Q8_0+Q6_K), CPU scalar oracle, bounded sample"},
+            "config": sweep_config(args.gpus),
             "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -197,12 +211,13 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- resident data: one weight buffer per launch (sharded by rows across ranks), activations, outputs
     launches = []
-    for t in TYPE_NAMES:
+    # encoded row count by row count, type by type: neighbours in the sweep can then leave as one kernel
+    for (m, t) in [(m, t) for m in MS for t in TYPE_NAMES]:
         for (n, k) in SHAPES:
             wq = weights[(t, n, k)]
             n_loc = n // world
             w_loc = sharding.shard_weight_bytes(wq, int(gt[t]), n, k, rank, world)
-            for m in MS:
+            for _once in (0,):
                 wbuf = dev.alloc_buffer(w_loc.size, mx.DType.U8)
                 wbuf.upload(w_loc)
                 x = rng.standard_normal((m, k)).astype(np.float32)
@@ -245,6 +260,7 @@ def run_ours(args, rank, world, local_rank):
         for L in launches:
             encode_op(enc, L)
             if world > 1 and symm is None:
+                enc.memory_barrier()          # the mat-vec may sit on the encoder's other lane (or still be pending)
                 with torch.cuda.stream(ext_stream):
                     dist.all_gather_into_tensor(L["y_all"], L["y_loc"])
 
@@ -303,6 +319,25 @@ def run_ours(args, rank, world, local_rank):
             raise RuntimeError(f"rank {rank}: sharded result differs from the unsharded mat-vec: {diff}")
         del wfull, ychk
 
+    if world > 1:
+        # every rank's assembled results against the CPU oracle, on rows around every shard boundary and the last rows
+        from oracle import oracle as orc
+        otype = {"Q8_0": orc.Q8_0, "Q6_K": orc.Q6_K}
+        for L in launches[::5]:
+            t, n, k, m, n_loc = L["t"], L["n"], L["k"], L["m"], L["n_loc"]
+            rows = sorted({r for b in range(world) for r in (b * n_loc, b * n_loc + 1, (b + 1) * n_loc - 1)} | {n - 1})
+            rb = weight_bytes(t, 1, k)
+            wq = weights[(t, n, k)]
+            wsel = np.concatenate([wq[r * rb:(r + 1) * rb] for r in rows])
+            ref, ad = orc.qmatmul(otype[t], wsel, L["x_host"], len(rows), k, nthreads=4)
+            if L["y_full"] is not None:
+                got = L["y_full"].cpu().numpy()[:, rows]
+            else:   # NCCL fallback: [world * m, n_loc] gathered blocks
+                ya = L["y_all"].cpu().numpy().reshape(world, m, n_loc)
+                got = np.stack([ya[r // n_loc, :, r % n_loc] for r in rows], axis=1)
+            err = float(np.max(np.abs(got.astype(np.float64) - ref) / np.maximum(ad, 1e-30)))
+            if not err <= 1e-5:
+                raise RuntimeError(f"rank {rank}: sharded {t} {n}x{k} m={m} differs from the oracle: normalised error {err:.3e}")
     del weights
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -327,6 +362,38 @@ def run_ours(args, rank, world, local_rank):
     ms_step = ms_total / args.steps
     value = step_weight_bytes / (ms_step * 1e-3) / 1e9
 
+    # ---- the same sweep as a dependent chain: every mat-vec writes the one shared result buffer, so each waits for
+    # ---- the one ahead (write-after-write), as the projections of a decoder layer wait for one another
+    ms_chain = None
+    chain_launches = None
+    if world == 1:
+        shared = dev.alloc_buffer(max(L["m"] * L["n_loc"] for L in launches) * 4, mx.DType.F32)
+
+        def encode_chain():
+            for L in launches:
+                yv = shared.slice_view(0, L["m"] * L["n_loc"])
+                mx.quantized_matmul_ggml(enc, reg, dev, L["x"], L["w"], yv, L["params"])
+
+        encode_chain()
+        enc.commit_and_wait()
+        enc.begin_capture()
+        encode_chain()
+        cgraph = enc.end_capture()
+        for _ in range(3):
+            cgraph.launch(enc)
+        enc.commit_and_wait()
+        mx.reset_counters()
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(ext_stream):
+            c0.record()
+        for _ in range(args.steps):
+            cgraph.launch(enc)
+        with torch.cuda.stream(ext_stream):
+            c1.record()
+        enc.commit_and_wait()
+        ms_chain = c0.elapsed_time(c1) / args.steps
+        chain_launches = mx.kernel_launch_count()
+
     # ---- e2e: the same sweep through the public API with host buffers, copies inside the timed region
     e2e_steps = max(3, min(args.steps, 20))
     h2d = sum(L["m"] * L["k"] * 4 for L in launches)
@@ -346,6 +413,7 @@ def run_ours(args, rank, world, local_rank):
         for L in launches:
             encode_op(e2e_enc, L)
             if world > 1 and symm is None:
+                e2e_enc.memory_barrier()
                 with torch.cuda.stream(e2e_stream):
                     dist.all_gather_into_tensor(L["y_all"], L["y_loc"])
 
@@ -404,26 +472,33 @@ def run_ours(args, rank, world, local_rank):
         return
 
     hbm_peak, tf_peak, peak_kind = measured_peaks()
-    achieved = step_algo_bytes / (ms_step * 1e-3) / 1e9
+    ratio, ratio_note = traffic_ratio(launches)
+
+    def roofline_of(ms, variant):
+        ach = step_algo_bytes / (ms * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak,
+                "traffic": step_algo_bytes * ratio if ratio else None, "traffic_note": ratio_note, "peak_kind": f"{peak_kind} copy bandwidth",
+                "kernel": "qmv_mma_kernel (m <= 4 and the narrow shapes), qmv_tc_kernel + qmv_tc_pack_kernel, qmv_stream_kernel",
+                "variant": variant, "ms_per_step": ms,
+                "note": "achieved = (weight + activation + output bytes of the 32 mat-vecs) / event-timed step"}
+
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "decode mat-vec sweep: Qwen3-8B projections (4096->4096, 4096->1024, 4096->12288, "
-                               "12288->4096) x {Q8_0,Q6_K} x m in {1,2,4,8}; 32 mat-vecs per step",
-                   "weight_bytes_per_step": step_weight_bytes, "l2": "each launch has its own weight buffer: 915 MB of "
-                   "distinct weights per step, larger than L2", "launch": "CUDA graph replay" if graph is not None else
-                   "direct launches + NCCL all-gather per mat-vec",
-                   "exchange": "none" if world == 1 else ("peer stores from the mat-vec kernels into every rank's result "
-                   "buffer (symmetric memory) + one cross-rank barrier per step" if symm is not None else
-                   "NCCL all-gather per mat-vec"), "parallelism": f"n-shard x{world}"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                     "traffic": step_algo_bytes * 1.01, "traffic_note": "ncu dram__bytes_read+write of qmv_tc_kernel is 1.008x (Q8_0) "
-                     "and 1.011x (Q6_K) its algorithmic bytes (profiles/qmv_tc_*_full.md); scaled to the step", "peak_kind": f"{peak_kind} copy bandwidth", "kernel": "qmv_tc_kernel (+ qmv_tc_pack_kernel)",
-                     "note": "achieved = (weight + activation + output bytes of the 32 launches) / event-timed step"},
+        "config": sweep_config(world),
+        "run": {"launch": "CUDA graph replay" if graph is not None else "direct launches + NCCL all-gather per mat-vec",
+                "exchange": "none" if world == 1 else ("peer stores from the mat-vec kernels into every rank's result "
+                "buffer (symmetric memory) + one cross-rank barrier per step" if symm is not None else
+                "NCCL all-gather per mat-vec")},
+        "roofline": roofline_of(ms_chain if ms_chain is not None else ms_step,
+                                "dependent chain: all 32 mat-vecs write one shared result buffer, each waits for the one ahead"
+                                if ms_chain is not None else "independent launches (no chain variant on more than one GPU)"),
+        "roofline_independent": roofline_of(ms_step, "independent launches: conflict-free neighbours overlap or leave as one kernel"),
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": e2e_s * 1e3},
         "gpu_launches": int(n_launch),
+        "gpu_launches_chain": int(chain_launches) if chain_launches is not None else None,
         "clocks": clocks,
     }
 
@@ -432,6 +507,8 @@ def run_ours(args, rank, world, local_rank):
         if not args.no_extra:
             try:
                 line["extra"] = extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak)
+                line["roofline_by_config"] = by_config(line["extra"], line["roofline_independent"],
+                                                       line["roofline"] if ms_chain is not None else None, hbm_peak, tf_peak)
             except Exception as ex:  # the headline stands on its own
                 line["extra"] = {"error": repr(ex)}
     if sharded is not None:
@@ -447,7 +524,7 @@ def sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream):
     [T, hidden] partial sums as the combine) and the N-sharded Q6_K lm_head mat-vec (151936 x 5120, m = 1, peer
     stores into every rank's logits + one cross-rank barrier)."""
     from mlx_native_b200 import sharding
-    from mlx_native_b200.profile_case import random_blocks
+    from mlx_native_b200.ggml_pack import random_blocks
 
     out = {}
     rng = np.random.default_rng(11)          # same seed on every rank: replicated activations and logits
@@ -565,26 +642,59 @@ def sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream):
     return out
 
 
-def cpu_baseline():
+def reference_sample(sample_rows=128):
+    """The bounded sample both CPU legs use: the whole sweep (8 (type, shape) pairs x m in {1, 2, 4, 8}) cut to
+    `sample_rows` weight rows per mat-vec."""
     from oracle import oracle as orc
 
-    cores = os.cpu_count() or 1
+    otype = {"Q8_0": orc.Q8_0, "Q6_K": orc.Q6_K}
     rng = np.random.default_rng(0)
-    n, k = 2048, 4096
-    wf = (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02))
-    x = rng.standard_normal((1, k)).astype(np.float32)
-    total_b, total_t = 0, 0.0
-    for t, ot in (("Q8_0", orc.Q8_0), ("Q6_K", orc.Q6_K)):
-        w = orc.quantize(ot, wf, rule="ggml")
-        orc.qmatmul(ot, w, x, n, k, nthreads=cores, want_absdot=False)
-        reps = 5
-        t0 = time.perf_counter()
-        for _ in range(reps):
-            orc.qmatmul(ot, w, x, n, k, nthreads=cores, want_absdot=False)
-        total_t += time.perf_counter() - t0
-        total_b += reps * w.size
-    return {"value": total_b / total_t / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
-            "sample": f"2048x4096 Q8_0 and Q6_K weights, m=1, 5 repetitions each, {cores} host threads"}
+    items = []
+    for t in TYPE_NAMES:
+        for (n, k) in SHAPES:
+            rows = min(n, sample_rows)
+            wf = (rng.standard_normal((rows, k), dtype=np.float32) * np.float32(0.02))
+            wq = orc.quantize(otype[t], wf, rule="ggml")
+            for m in MS:
+                items.append((otype[t], rows, k, wq, rng.standard_normal((m, k)).astype(np.float32)))
+    return items, sum(w.size for (_, _, _, w, _) in items), sample_rows
+
+
+def sweep_config(world=1, graph=True, symm=False):
+    """`config` of the JSON line; the same for both arms."""
+    return {"workload": "decode mat-vec sweep: Qwen3-8B projections (4096->4096, 4096->1024, 4096->12288, "
+                        "12288->4096) x {Q8_0,Q6_K} x m in {1,2,4,8}; 32 mat-vecs per step",
+            "weight_bytes_per_step": sum(weight_bytes(t, n, k) for t in TYPE_NAMES for (n, k) in SHAPES for _ in MS),
+            "l2": "each launch has its own weight buffer: 915 MB of distinct weights per step, larger than L2",
+            "parallelism": f"n-shard x{world}"}
+
+
+def time_oracle(items, nthreads, steps, warmup=1):
+    from oracle import oracle as orc
+
+    def step():
+        for (ot, rows, k, w, x) in items:
+            orc.qmatmul(ot, w, x, rows, k, nthreads=nthreads, want_absdot=False)
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    return (time.perf_counter() - t0) / steps
+
+
+def cpu_baseline():
+    """The CPU oracle (kind "port": the upstream scalar path restated in C; the Rust reference cannot be built here) on
+    the reference arm's sample, with all host threads and with one."""
+    cores = os.cpu_count() or 1
+    items, step_bytes, rows = reference_sample()
+    t_all = time_oracle(items, cores, steps=20)
+    t_one = time_oracle(items, 1, steps=3)
+    return {"value": step_bytes / t_all / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+            "one_thread": {"value": step_bytes / t_one / 1e9, "unit": "GB/s", "cores": 1},
+            "sample": f"the whole sweep cut to {rows} weight rows per mat-vec ({step_bytes / 1e6:.1f} MB of weights per "
+                      f"pass); 20 passes on {cores} threads, 3 passes on 1 thread"}
 
 
 def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
@@ -617,7 +727,7 @@ def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
         return statistics.median(ts)
 
     mm = {}
-    for (n, k, ms) in ((4096, 4096, (512, 2048)), (12288, 4096, (2048,)), (4096, 12288, (2048,))):
+    for (n, k, ms) in ((4096, 4096, (512, 2048)), (12288, 4096, (512, 2048)), (4096, 12288, (512, 2048))):
         wf = (rng.standard_normal((512, k), dtype=np.float32) * np.float32(0.02))
         for t in ("Q4_0", "Q6_K"):
             wq = np.tile(gp.pack(otype[t], wf), n // 512)   # timing does not depend on the values
@@ -631,7 +741,8 @@ def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
                 p = mx.GgmlQuantizedMatmulParams(m, n, k, gt[t])
                 sec = timed(lambda e: mx.quantized_matmul_ggml(e, reg, dev, xb, wb, yb, p))
                 tf = 2.0 * m * n * k / sec / 1e12
-                mm[f"{t}_m{m}_n{n}_k{k}"] = {"tflops": tf, "ms": sec * 1e3, "frac_of_measured_bf16_peak": tf / tf_peak}
+                mm[f"{t}_m{m}_n{n}_k{k}"] = {"tflops": tf, "ms": sec * 1e3, "frac_of_measured_bf16_peak": tf / tf_peak,
+                                             "frac_of_nominal_2250": tf / 2250.0}
             del wb
     out["qmm"] = mm
 
@@ -680,7 +791,7 @@ def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
     out["moe_ffn_layer"] = moe
 
     # lm_head: Q6_K 151936 x 5120 (638 MB), m = 1 (mat-vec, HBM-bound) and m = 256 (mat-mat)
-    from mlx_native_b200.profile_case import random_blocks
+    from mlx_native_b200.ggml_pack import random_blocks
     n, k = 151936, 5120
     blk = random_blocks(rng, "Q6_K", n, k)
     wb = dev.alloc_buffer(blk.size, mx.DType.U8)
@@ -696,7 +807,183 @@ def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
         lm[f"m{m}"] = {"us": sec * 1e6, "weight_GBps": blk.size / sec / 1e9, "frac_of_measured_hbm_peak": blk.size / sec / 1e9 / hbm_peak,
                        "tflops": 2.0 * m * n * k / sec / 1e12}
     out["lm_head_q6k"] = lm
+
+    # configuration 1: Q4_0 4096 x 4096, m = 1; 16 weight copies (151 MB, more than L2) per replayed graph, once with
+    # 16 result buffers (independent calls) and once with one (each call waits for the one ahead)
+    n, k, copies = 4096, 4096, 16
+    wq = gp.pack(gp.Q4_0, (rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)))
+    wbs = []
+    for _ in range(copies):
+        b = dev.alloc_buffer(wq.size, mx.DType.U8)
+        b.upload(wq)
+        wbs.append(b)
+    x = rng.standard_normal((1, k)).astype(np.float32)
+    xb = dev.alloc_buffer(x.nbytes, mx.DType.F32)
+    xb.upload(x)
+    ys = [dev.alloc_buffer(n * 4, mx.DType.F32) for _ in range(copies)]
+    p1 = mx.GgmlQuantizedMatmulParams(1, n, k, mx.GgmlType.Q4_0)
+    c1 = {}
+    for name, outs in (("independent", ys), ("chain", [ys[0]] * copies)):
+        def seq(e, outs=outs):
+            for wb_, yb_ in zip(wbs, outs):
+                mx.quantized_matmul_ggml(e, reg, dev, xb, wb_, yb_, p1)
+        sec = timed(seq, inner=1) / copies
+        c1[name] = {"us": sec * 1e6, "weight_GBps": wq.size / sec / 1e9, "frac_of_measured_hbm_peak": wq.size / sec / 1e9 / hbm_peak}
+    out["q4_0_4096x4096_m1"] = c1
     return out
+
+
+def by_config(extra, sweep_indep, sweep_chain, hbm_peak, tf_peak):
+    """One {bound, achieved, peak, frac, unit} entry per benchmark configuration and cell."""
+    r = {}
+    if "q4_0_4096x4096_m1" in extra:
+        for name, v in extra["q4_0_4096x4096_m1"].items():
+            r[f"config1 Q4_0 4096x4096 m=1 ({name})"] = {"bound": "hbm", "achieved": v["weight_GBps"], "peak": hbm_peak,
+                                                       "frac": v["frac_of_measured_hbm_peak"], "unit": "GB/s", "us": v["us"]}
+    r["config2 decode sweep (independent)"] = {k: sweep_indep[k] for k in ("bound", "achieved", "peak", "frac", "unit")}
+    if sweep_chain is not None:
+        r["config2 decode sweep (dependent chain)"] = {k: sweep_chain[k] for k in ("bound", "achieved", "peak", "frac", "unit")}
+    for name, v in extra.get("qmm", {}).items():
+        r[f"config3 {name}"] = {"bound": "tensor", "achieved": v["tflops"], "peak": tf_peak, "frac": v["frac_of_measured_bf16_peak"],
+                                "frac_of_nominal_2250": v["frac_of_nominal_2250"], "unit": "TFLOP/s"}
+    for name, v in extra.get("moe_ffn_layer", {}).items():
+        r[f"config4 MoE FFN layer {name}"] = {"bound": "hbm", "achieved": v["expert_weight_GBps"], "peak": hbm_peak,
+                                             "frac": v["frac_of_measured_hbm_peak"], "unit": "GB/s",
+                                             "tokens_per_s": v["tokens_per_s"], "ms_per_layer": v["ms_per_layer"]}
+    lm = extra.get("lm_head_q6k", {})
+    if "m1" in lm:
+        r["config5 lm_head Q6_K m=1"] = {"bound": "hbm", "achieved": lm["m1"]["weight_GBps"], "peak": hbm_peak,
+                                        "frac": lm["m1"]["frac_of_measured_hbm_peak"], "unit": "GB/s", "us": lm["m1"]["us"]}
+    if "m256" in lm:
+        r["config5 lm_head Q6_K m=256"] = {"bound": "tensor", "achieved": lm["m256"]["tflops"], "peak": tf_peak,
+                                          "frac": lm["m256"]["tflops"] / tf_peak, "frac_of_nominal_2250": lm["m256"]["tflops"] / 2250.0,
+                                          "unit": "TFLOP/s", "us": lm["m256"]["us"]}
+    return r
+
+
+# --------------------------------------------------------------------------------------------- profiler workloads
+def run_case(argv):
+    """Small fixed workloads for profiler captures (a few hundred MB on the device, a handful of launches).
+
+      --case mv  [Q8_0|Q6_K|Q4_0] [m]   decode mat-vec, n=12288 k=4096, 4 weight copies (> L2), two passes
+      --case mvs [Q8_0|Q6_K|Q4_0] [m]   the same on the narrow shape n=1024 k=4096, 40 weight copies (> L2)
+      --case mm  [Q4_0|Q6_K|Q8_0] [m]   prefill mat-mat, n=4096 k=4096, m=512 by default
+      --case moe [m]                    expert-routed gate projection, 128 experts, top-8
+      --case moe_layer [m] [reps]       whole MoE FFN layer (route, gate, up, SwiGLU, down, reduce), 128 experts, top-8
+      --case cmp [types] [ms]           the mat-vec kernels side by side, microseconds per call, independent and chained
+                                        (CUDA-graph replay over rotating weight copies > L2)
+    The kernel variant follows the MLXN_QMV / MLXN_QMM environment variables.  Weights are random bytes with finite
+    f16 scales: the kernels' timing and memory traffic do not depend on the values."""
+    import mlx_native_b200 as mx
+    from mlx_native_b200.ggml_pack import random_blocks
+
+    gt = {"Q4_0": mx.GgmlType.Q4_0, "Q8_0": mx.GgmlType.Q8_0, "Q6_K": mx.GgmlType.Q6_K}
+    mode = argv[0] if argv else "mv"
+    dev = mx.MlxDevice.new(0)
+    reg = mx.KernelRegistry.new()
+    rng = np.random.default_rng(0)
+
+    def upload(a, dt=mx.DType.U8):
+        b = dev.alloc_buffer(a.nbytes, dt)
+        b.upload(a)
+        return b
+
+    if mode == "cmp":
+        types = (argv[1] if len(argv) > 1 else "Q8_0,Q6_K,Q4_0").split(",")
+        ms = [int(v) for v in (argv[2] if len(argv) > 2 else "1,2,4,8").split(",")]
+
+        def timed(t, n, k, m, variant, chain, reps=10):
+            wbytes = weight_bytes(t, n, k)
+            ncopies = int(max(4, min(48, (300e6 // wbytes) + 1)))
+            w = random_blocks(rng, t, n, k)
+            ws = [upload(w) for _ in range(ncopies)]
+            xb = upload(rng.standard_normal((m, k)).astype(np.float32), mx.DType.F32)
+            ys = [dev.alloc_buffer(m * n * 4, mx.DType.F32) for _ in range(1 if chain else ncopies)] * (ncopies if chain else 1)
+            p = mx.GgmlQuantizedMatmulParams(m, n, k, gt[t])
+            mx.set_option("qmv", variant)
+            enc = dev.command_encoder()
+            for wb, yb in zip(ws[:2], ys[:2]):
+                mx.quantized_matmul_ggml(enc, reg, dev, xb, wb, yb, p)
+            enc.commit_and_wait()
+            enc.begin_capture()
+            for wb, yb in zip(ws, ys):
+                mx.quantized_matmul_ggml(enc, reg, dev, xb, wb, yb, p)
+            g = enc.end_capture()
+            for _ in range(2):
+                g.launch(enc)
+            enc.commit_and_wait()
+            for _ in range(reps):
+                g.launch(enc)
+            return enc.commit_wait_with_gpu_time() / (reps * ncopies) * 1e6
+
+        for t in types:
+            for (n, k) in SHAPES:
+                for m in ms:
+                    ideal = weight_bytes(t, n, k) / (measured_peaks()[0] * 1e3)
+                    cells = [f"{v}{'/chain' if ch else ''} {timed(t, n, k, m, v, ch):6.2f}"
+                             for ch in (False, True) for v in ("auto", "mma", "tc", "stream") if not (v == "stream" and m > 2)]
+                    print(f"{t} {n:6d}x{k:<6d} m={m} ideal {ideal:5.2f} us | " + " ".join(cells), flush=True)
+        mx.set_option("qmv", "auto")
+        return
+    enc = dev.command_encoder()
+    E, top_k, hidden, ffn = 128, 8, 2048, 768
+    if mode == "moe_layer":
+        T = int(argv[1]) if len(argv) > 1 else 512
+        reps = int(argv[2]) if len(argv) > 2 else 3
+        bufs = {}
+        for name, t, rows, cols in (("gate", "Q4_0", E * ffn, hidden), ("up", "Q4_0", E * ffn, hidden), ("down", "Q6_K", E * hidden, ffn)):
+            w = random_blocks(rng, t, rows, cols)
+            bufs[name] = upload(w)
+            bufs[name + "_stride"] = w.size // E
+        lg = upload(rng.standard_normal((T, E)).astype(np.float32), mx.DType.F32)
+        xb = upload(rng.standard_normal((T, hidden)).astype(np.float32), mx.DType.F32)
+        ids = dev.alloc_buffer(T * top_k * 4, mx.DType.U32)
+        rw = dev.alloc_buffer(T * top_k * 4, mx.DType.F32)
+        yg, yu, act = (dev.alloc_buffer(T * top_k * ffn * 4, mx.DType.F32) for _ in range(3))
+        yd = dev.alloc_buffer(T * top_k * hidden * 4, mx.DType.F32)
+        outb = dev.alloc_buffer(T * hidden * 4, mx.DType.F32)
+        pg = mx.GgmlQuantizedMatmulIdParams(T, top_k, ffn, hidden, E, bufs["gate_stride"], mx.GgmlType.Q4_0)
+        pd = mx.GgmlQuantizedMatmulIdParams(T * top_k, 1, hidden, ffn, E, bufs["down_stride"], mx.GgmlType.Q6_K)
+        for _ in range(reps):
+            mx.moe_softmax_topk(enc, reg, dev, lg, ids, rw, T, E, top_k)
+            mx.quantized_matmul_id_ggml(enc, reg, dev, xb, bufs["gate"], ids, yg, pg)
+            mx.quantized_matmul_id_ggml(enc, reg, dev, xb, bufs["up"], ids, yu, pg)
+            mx.silu_mul(enc, reg, dev, yg, yu, act, T * top_k * ffn)
+            mx.quantized_matmul_id_ggml(enc, reg, dev, act, bufs["down"], ids, yd, pd)
+            mx.moe_weighted_reduce(enc, reg, dev, rw, yd, outb, T, top_k, hidden)
+            enc.commit_and_wait()
+        print("ok", mx.last_kernel_name())
+        return
+    if mode == "moe":
+        m = int(argv[1]) if len(argv) > 1 else 512
+        w = random_blocks(rng, "Q4_0", E * ffn, hidden)
+        wb = upload(w)
+        xb = upload(rng.standard_normal((m, hidden)).astype(np.float32), mx.DType.F32)
+        ib = upload(np.stack([rng.permutation(E)[:top_k] for _ in range(m)]).astype(np.uint32), mx.DType.U32)
+        yb = dev.alloc_buffer(m * top_k * ffn * 4, mx.DType.F32)
+        p = mx.GgmlQuantizedMatmulIdParams(m, top_k, ffn, hidden, E, w.size // E, mx.GgmlType.Q4_0)
+        for _ in range(3):
+            mx.quantized_matmul_id_ggml(enc, reg, dev, xb, wb, ib, yb, p)
+        enc.commit_and_wait()
+        print("ok", mx.last_kernel_name())
+        return
+    t = argv[1] if len(argv) > 1 else ("Q4_0" if mode == "mm" else "Q8_0")
+    if mode == "mv":
+        n, k, m, copies = 12288, 4096, int(argv[2]) if len(argv) > 2 else 1, 4
+    elif mode == "mvs":
+        n, k, m, copies = 1024, 4096, int(argv[2]) if len(argv) > 2 else 1, 40
+    else:
+        n, k, m, copies = 4096, 4096, int(argv[2]) if len(argv) > 2 else 512, 1
+    w = random_blocks(rng, t, n, k)
+    ws = [upload(w) for _ in range(copies)]
+    xb = upload(rng.standard_normal((m, k)).astype(np.float32), mx.DType.F32)
+    ys = [dev.alloc_buffer(m * n * 4, mx.DType.F32) for _ in range(copies)]
+    p = mx.GgmlQuantizedMatmulParams(m, n, k, gt[t])
+    for _ in range(2):
+        for wbuf, yb in zip(ws, ys):
+            mx.quantized_matmul_ggml(enc, reg, dev, xb, wbuf, yb, p)
+        enc.commit_and_wait()
+    print("ok", mx.last_kernel_name(), "launches", mx.kernel_launch_count())
 
 
 def main():
@@ -706,7 +993,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the secondary mat-mat / MoE figures")
+    ap.add_argument("--case", nargs=argparse.REMAINDER, help="run one profiler workload instead of the benchmark (see run_case)")
     args = ap.parse_args()
+    if args.case is not None:
+        run_case(args.case)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

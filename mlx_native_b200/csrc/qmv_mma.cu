@@ -59,9 +59,37 @@ __host__ __device__ constexpr uint32_t mw_pitch(int ggml_type, int kb) {
     return 16u * (c | 1u);
 }
 
-struct MwCfg {
-    uint32_t items;       // row groups of R rows
+constexpr int kMwMaxProbs = 8;     // mat-vecs one launch can carry
+constexpr int kMwMaxGrid = 320;    // CTAs of a launch (two per SM)
+
+// One mat-vec of a launch.  A launch carries up to kMwMaxProbs mat-vecs that have no buffer conflicts with one
+// another (same block type and kernel configuration); their row groups form one list of work items.
+struct MwProb {
+    const float *x;
+    float *y;
+    uint32_t n, k, m;
     uint32_t spi;         // stages per item = k / (KB * UK)
+    uint32_t item0;       // index of the problem's first item in the launch's item list
+    uint32_t y_ld, y_col0;
+};
+struct MwBatch {
+    MwProb p[kMwMaxProbs];
+    uint32_t nprob;
+    uint32_t early_weights;   // no problem's weights were written by a kernel of this process (see QmvArgs)
+    uint32_t n_peer;          // row-sharded form, single problem only (see QmvArgs)
+    float *y_peer[kMaxPeers];
+    uint32_t *status;
+    // CTA c works on items [cta_begin[c], cta_begin[c + 1]): contiguous chunks of (nearly) equal numbers of stages
+    uint32_t cta_begin[kMwMaxGrid + 1];
+};
+struct MwMaps {
+    CUtensorMap m[kMwMaxProbs];
+};
+
+struct MwCfg {
+#ifdef MLXN_EXPERIMENTS
+    uint32_t debug;       // 1: consumers only wait and release (no arithmetic); 2: no copies (arithmetic on stale data)
+#endif
     uint32_t nslots;      // ring depth
     uint32_t xst_off;     // shared-memory offsets behind the ring
     uint32_t ptab_off;
@@ -140,10 +168,65 @@ __device__ __forceinline__ void mw_pairs(int ggml_type, bool mis, uint32_t t, ui
     }
 }
 
+// One block of 32 (Q4_0 / Q8_0) against the warp's TPW tiles.  `pd`: shared address of the block in row g of the
+// stage (its f16 scale); `pa`: this lane's first code word; Q8_0: `pb0` its second code word.  MIS (the codes
+// straddle the 32-bit words): the last word of lane 3 is byte_perm(word at pb0, word at pb1, sel); the other lanes pass
+// pb0 == pb1 and the identity selector.  All other rows are compile-time offsets from these addresses.
+template <int T, int TPW, int MP, uint32_t PITCH, bool MIS>
+__device__ __forceinline__ void mw_block_tiles(uint32_t pd, uint32_t pa, uint32_t pb0, uint32_t pb1, uint32_t sel,
+                                               const uint32_t (&bf)[2][4], const float (&cq)[4], float cs0, float cs1,
+                                               float (&acc)[TPW][4]) {
+#pragma unroll
+    for (int j = 0; j < TPW; j++) {
+        uint32_t wa[2], wb[2];
+        float dd[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const uint32_t off = (16 * j + 8 * h) * PITCH;
+            dd[h] = half_bits_to_float(lds_u16(pd + off));
+            if constexpr (T == GT_Q8_0) {
+                wa[h] = lds32(pa + off);
+                wb[h] = MIS ? __byte_perm(lds32(pb0 + off), lds32(pb1 + off), sel) : lds32(pb0 + off);
+            } else {
+                wa[h] = MIS ? __byte_perm(lds32(pb0 + off), lds32(pb1 + off), sel) : lds32(pa + off);
+                wb[h] = 0;
+            }
+        }
+        float d[4];
+        if constexpr (T == GT_Q8_0) {
+            // (w ^ 0x80..) & 0x00FF00FF: the even bytes (+128) as two f16 subnormals; the odd bytes likewise
+            uint32_t a0 = (wa[0] ^ 0x80808080u) & 0x00FF00FFu, a2 = ((wa[0] >> 8) ^ 0x00800080u) & 0x00FF00FFu;
+            uint32_t a1 = (wa[1] ^ 0x80808080u) & 0x00FF00FFu, a3 = ((wa[1] >> 8) ^ 0x00800080u) & 0x00FF00FFu;
+            mma16816(d, a0, a1, a2, a3, bf[0][0], bf[0][1], cq);
+            mma16816(d, a0, a1, a2, a3, bf[0][2], bf[0][3], d);
+            a0 = (wb[0] ^ 0x80808080u) & 0x00FF00FFu; a2 = ((wb[0] >> 8) ^ 0x00800080u) & 0x00FF00FFu;
+            a1 = (wb[1] ^ 0x80808080u) & 0x00FF00FFu; a3 = ((wb[1] >> 8) ^ 0x00800080u) & 0x00FF00FFu;
+            mma16816(d, a0, a1, a2, a3, bf[1][0], bf[1][1], d);
+            mma16816(d, a0, a1, a2, a3, bf[1][2], bf[1][3], d);
+        } else {
+            // low nibbles: elements c0..c3 of the word's four bytes; high nibbles (x 16): 16 + c
+            uint32_t a0 = wa[0] & 0x000F000Fu, a2 = (wa[0] >> 8) & 0x000F000Fu;
+            uint32_t a1 = wa[1] & 0x000F000Fu, a3 = (wa[1] >> 8) & 0x000F000Fu;
+            mma16816(d, a0, a1, a2, a3, bf[0][0], bf[0][1], cq);
+            mma16816(d, a0, a1, a2, a3, bf[0][2], bf[0][3], d);
+            a0 = wa[0] & 0x00F000F0u; a2 = (wa[0] >> 8) & 0x00F000F0u;
+            a1 = wa[1] & 0x00F000F0u; a3 = (wa[1] >> 8) & 0x00F000F0u;
+            mma16816(d, a0, a1, a2, a3, bf[1][0], bf[1][1], d);
+            mma16816(d, a0, a1, a2, a3, bf[1][2], bf[1][3], d);
+        }
+        acc[j][0] = fmaf(dd[0] * cs0, d[0], acc[j][0]);
+        acc[j][2] = fmaf(dd[1] * cs0, d[2], acc[j][2]);
+        if constexpr (MP > 1) {
+            acc[j][1] = fmaf(dd[0] * cs1, d[1], acc[j][1]);
+            acc[j][3] = fmaf(dd[1] * cs1, d[3], acc[j][3]);
+        }
+    }
+}
+
 // TPW: 16-row tiles per warp.  KB: units per warp and stage.  MP: activation rows carried (1, 2, 4 or 8, >= m).
 template <int T, int TPW, int KB, int MP>
 __global__ void __launch_bounds__(kMwThreads, 2)
-    qmv_mma_kernel(const QmvArgs a, const MwCfg c, const __grid_constant__ CUtensorMap wmap) {
+    qmv_mma_kernel(const __grid_constant__ MwBatch bt, const MwCfg c, const __grid_constant__ MwMaps maps) {
     using TR = MwTraits<T>;
     constexpr int R = 16 * TPW, NG = TR::NG, NM = TR::NM;
     constexpr uint32_t PITCH = mw_pitch(T, KB);
@@ -153,9 +236,12 @@ __global__ void __launch_bounds__(kMwThreads, 2)
     // activation conversion: one "piece" = the four values a lane feeds to one MMA; a warp has KB * MP * NM * 4 of
     // them per stage, spread over its 32 lanes in NPASS passes
     constexpr int PIECES = KB * MP * NM * 4;
-    constexpr int NPASS = (PIECES + 31) / 32;
-    constexpr uint32_t XCC = (uint32_t)PIECES * 16;          // offset of the (ci, cs) table behind the pieces
-    constexpr uint32_t XST = (XCC + (uint32_t)KB * MP * NG * 8 + 15u) & ~15u;   // the pieces are read 16 bytes at a time
+    // ... a stage with fewer than 32 pieces shares a conversion pass with the stages after it (NB stages per batch)
+    constexpr int NB = PIECES >= 32 ? 1 : 32 / PIECES;
+    constexpr int NPASS = (NB * PIECES + 31) / 32;
+    constexpr int CCN = KB * MP * NG;                        // (ci, cs) pairs per stage
+    constexpr uint32_t XCC = (uint32_t)NB * PIECES * 16;     // offset of the (ci, cs) table behind the pieces
+    constexpr uint32_t XST = (XCC + (uint32_t)NB * CCN * 8 + 15u) & ~15u;   // the pieces are read 16 bytes at a time
     constexpr float kOff = -(float)TR::OFFSET / 16777216.0f;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -164,7 +250,7 @@ __global__ void __launch_bounds__(kMwThreads, 2)
     __shared__ volatile uint32_t abort_flag;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t grid = gridDim.x, cta = blockIdx.x;
+    const uint32_t g0 = bt.cta_begin[blockIdx.x], g1 = bt.cta_begin[blockIdx.x + 1];   // this CTA's items
 
     if (tid == 0) {
         abort_flag = 0;
@@ -184,21 +270,30 @@ __global__ void __launch_bounds__(kMwThreads, 2)
     if (warp == kMwWarps) {
         // ======================= producer: one tensor copy (R rows x one stage) per ring slot =======================
         if (lane == 0) {
-            if (!a.early_weights) grid_dependency_wait();
-            uint32_t slot = 0, ph = 0, cidx = 0;
+            if (!bt.early_weights) grid_dependency_wait();
+            uint32_t slot = 0, ph = 0, cidx = 0, p = 0;
             bool ok = true;
-            for (uint32_t item = cta; ok && item < c.items; item += grid) {
-                for (uint32_t s = 0; s < c.spi; s++, cidx++) {
-                    if (cidx >= c.nslots && !mbar_wait(&empty[slot], ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, 64u)) {
+            for (uint32_t gi = g0; ok && gi < g1; gi++) {
+                while (p + 1 < bt.nprob && gi >= bt.p[p + 1].item0) p++;
+                const uint32_t item = gi - bt.p[p].item0, spi = bt.p[p].spi;
+                for (uint32_t s = 0; s < spi; s++, cidx++) {
+                    if (cidx >= c.nslots && !mbar_wait(&empty[slot], ph ^ 1u, &abort_flag, bt.status, ST_WAIT_EMPTY_TIMEOUT, 0u)) {
                         ok = false;
                         break;
                     }
+#ifdef MLXN_EXPERIMENTS
+                    if (c.debug & 2u) {
+                        mbar_arrive(&full[slot]);
+                        if (++slot == c.nslots) { slot = 0; ph ^= 1u; }
+                        continue;
+                    }
+#endif
                     mbar_expect_tx(&full[slot], STAGE);
                     // coordinates in 8-byte elements; rows past n and bytes past the end of a row arrive as zeros
                     const uint32_t x0 = ((s * SBYTES) & ~15u) >> 3;
                     asm volatile(
                         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                        ::"r"(smem_base + slot * STAGE), "l"(&wmap), "r"(x0), "r"(item * (uint32_t)R), "r"(smem_u32(&full[slot]))
+                        ::"r"(smem_base + slot * STAGE), "l"(&maps.m[p]), "r"(x0), "r"(item * (uint32_t)R), "r"(smem_u32(&full[slot]))
                         : "memory");
                     if (++slot == c.nslots) { slot = 0; ph ^= 1u; }
                 }
@@ -216,37 +311,63 @@ __global__ void __launch_bounds__(kMwThreads, 2)
         // ---- geometry of the warp's units inside a stage ----
         // Q4_0 / Q8_0: blocks KB w .. KB w + KB - 1 of the stage's 8 KB; block b starts BB * b bytes into the row
         constexpr uint32_t BB = T == GT_Q8_0 ? 34u : 18u;
+        // blocks whose codes straddle the words (see mw_pairs): lanes 0..2 read one whole word, lane 3 the half words at
+        // either end of the block, joined by a byte permute
+        const uint32_t mhi = T == GT_Q8_0 ? 20u : 4u, mend = T == GT_Q8_0 ? 32u : 16u;
+        const uint32_t mo0 = t < 3 ? mhi + 4 * t : 0u, mo1 = t < 3 ? mhi + 4 * t : mend, msel = t < 3 ? 0x3210u : 0x5432u;
         // Q6_K: quarter (nh, js) of the super-blocks sp, sp + 2, ...; super-block sb starts lead + 210 sb bytes in
         const uint32_t sp = w >> 2, nh = (w >> 1) & 1u, js = w & 1u;
         const uint32_t q6A = 64 * nh + 16 * js + 4 * t, q6H = 128 + 32 * nh + 16 * js + 4 * t, q6S = 192 + 8 * nh + js;
 
-        // ---- activation pieces this lane converts: piece index pc = lane + 32 pass ----
+        // ---- activation pieces this lane converts: batch piece bp = lane + 32 pass = so PIECES + pc ----
+        // (so: stage of the batch)
         // Q4_0 / Q8_0: pc = ((i MP + r) NM + h) 4 + tt (unit i, activation row r, MMA h, quad lane tt);
         // Q6_K:        pc = ((i MP + r) 4 + q) 4 + tt (scale group q)
-        const float *xsrc0[NPASS], *xsrc1[NPASS];
-        bool xok[NPASS];
+        uint32_t xrel0[NPASS], xrel1[NPASS], xrow[NPASS], xso[NPASS];   // element offsets inside a stage; activation row
+        bool xin[NPASS];
 #pragma unroll
         for (int p = 0; p < NPASS; p++) {
-            const uint32_t pc = lane + 32 * p, tt = pc & 3u, hq = (pc >> 2) % NM, ir = (pc >> 2) / NM;
-            const uint32_t r = ir % MP, i = ir / MP;
-            xok[p] = pc < (uint32_t)PIECES && r < a.m;
-            const float *row = a.x + (size_t)(xok[p] ? r : 0) * a.k;
+            const uint32_t bp = lane + 32 * p, pc = bp % PIECES;
+            xso[p] = bp / PIECES;
+            const uint32_t tt = pc & 3u, hq = (pc >> 2) % NM, ir = (pc >> 2) / NM;
+            const uint32_t i = ir / MP;
+            xrow[p] = ir % MP;
+            xin[p] = bp < (uint32_t)(NB * PIECES);
             if constexpr (T == GT_Q6_K) {
                 const uint32_t sb = sp + 2 * i;
-                xsrc0[p] = row + 256 * sb + 128 * nh + 32 * hq + 16 * js + 4 * tt;
-                xsrc1[p] = xsrc0[p] + 2;
+                xrel0[p] = 256 * sb + 128 * nh + 32 * hq + 16 * js + 4 * tt;
+                xrel1[p] = xrel0[p] + 2;
             } else {
                 const uint32_t b = KB * w + i;
                 uint32_t p0, p1;
                 mw_pairs(T, (b & 1u) == 0, tt, hq, p0, p1);
-                xsrc0[p] = row + 32 * b + p0;
-                xsrc1[p] = row + 32 * b + p1;
+                xrel0[p] = 32 * b + p0;
+                xrel1[p] = 32 * b + p1;
             }
         }
+        // the problem being worked on
+        uint32_t cur = 0xFFFFFFFFu, spi = 1, pm = 0;
+        const float *xsrc0[NPASS], *xsrc1[NPASS];
+        bool xok[NPASS];
+        auto set_problem = [&](uint32_t p) {
+            cur = p;
+            spi = bt.p[p].spi;
+            pm = bt.p[p].m;
+#pragma unroll
+            for (int q = 0; q < NPASS; q++) {
+                xok[q] = xin[q] && xrow[q] < pm;
+                const float *row = bt.p[p].x + (size_t)(xok[q] ? xrow[q] : 0) * bt.p[p].k;
+                xsrc0[q] = row + xrel0[q];
+                xsrc1[q] = row + xrel1[q];
+            }
+        };
         float xr[NPASS][4];
-        auto load_x = [&](uint32_t ks) {
+        // `s0` = K stage (inside the item) of the batch's first stage; every item starts at K = 0 again
+        auto load_x = [&](uint32_t s0) {
 #pragma unroll
             for (int p = 0; p < NPASS; p++) {
+                uint32_t ks = s0 + xso[p];
+                while (ks >= spi) ks -= spi;
                 float2 v0 = make_float2(0.f, 0.f), v1 = v0;
                 if (xok[p]) {
                     v0 = __ldcg(reinterpret_cast<const float2 *>(xsrc0[p] + (size_t)ks * SK));
@@ -261,7 +382,7 @@ __global__ void __launch_bounds__(kMwThreads, 2)
         auto convert_x = [&]() {
 #pragma unroll
             for (int p = 0; p < NPASS; p++) {
-                const uint32_t pc = lane + 32 * p;
+                const uint32_t bp = lane + 32 * p;
                 float am = fmaxf(fmaxf(fabsf(xr[p][0]), fabsf(xr[p][1])), fmaxf(fabsf(xr[p][2]), fabsf(xr[p][3])));
                 float sum = (xr[p][0] + xr[p][1]) + (xr[p][2] + xr[p][3]);
                 constexpr int RED = T == GT_Q6_K ? 2 : 4;   // xor distances 1, 2 (, 4)
@@ -273,15 +394,17 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                 float s, inv;
                 pow2_scale(am, s, inv);
                 // Q4_0: the high nibbles stay where they are in their byte (16 x the code): their activations / 16
-                const float sv = (T == GT_Q4_0 && ((pc >> 2) & 1u)) ? s * 0.0625f : s;
+                const float sv = (T == GT_Q4_0 && ((bp >> 2) & 1u)) ? s * 0.0625f : s;
                 uint32_t f0, f1, f2, f3;
                 split4(xr[p][0] * sv, xr[p][1] * sv, xr[p][2] * sv, xr[p][3] * sv, f0, f1, f2, f3);
-                if (pc < (uint32_t)PIECES) {
-                    sts128(xst + pc * 16, f0, f1, f2, f3);
+                if (bp < (uint32_t)(NB * PIECES)) {
+                    sts128(xst + bp * 16, f0, f1, f2, f3);
+                    // (the pieces of a scale group are consecutive, and PIECES is a multiple of the group size, so
+                    //  bp / group size = so CCN + the group's index inside its stage)
                     if constexpr (T == GT_Q6_K) {
-                        if ((pc & 3u) == 0) sts64(xcc + (pc >> 2) * 8, __float_as_uint(kOff * (s * sum)), __float_as_uint(inv));
+                        if ((bp & 3u) == 0) sts64(xcc + (bp >> 2) * 8, __float_as_uint(kOff * (s * sum)), __float_as_uint(inv));
                     } else {
-                        if ((pc & 7u) == 0) sts64(xcc + (pc >> 3) * 8, __float_as_uint(kOff * (s * sum)), __float_as_uint(inv));
+                        if ((bp & 7u) == 0) sts64(xcc + (bp >> 3) * 8, __float_as_uint(kOff * (s * sum)), __float_as_uint(inv));
                     }
                 }
             }
@@ -292,22 +415,41 @@ __global__ void __launch_bounds__(kMwThreads, 2)
         for (int j = 0; j < TPW; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
         grid_dependency_wait();   // the activations belong to the kernels ahead until they are done
-        load_x(0);
 
-        uint32_t slot = 0, ph = 0, fin_ph = 0;
+        uint32_t slot = 0, ph = 0, fin_ph = 0, bi = 0;   // bi: stage inside the conversion batch
+        uint32_t p = 0;
         bool ok = true, first_item = true;
-        for (uint32_t item = cta; ok && item < c.items; item += grid) {
-            for (uint32_t s = 0; ok && s < c.spi; s++) {
-                __syncwarp();           // the previous stage's pieces have all been fetched
-                convert_x();
-                __syncwarp();
-                load_x(s + 1 < c.spi ? s + 1 : 0);   // the next stage's values (every item starts at K = 0 again)
+        for (uint32_t gi = g0; ok && gi < g1; gi++) {
+            while (p + 1 < bt.nprob && gi >= bt.p[p + 1].item0) p++;
+            if (p != cur) {   // first item, or the next mat-vec of the launch: its activations from K = 0
+                set_problem(p);
+                load_x(0);
+                bi = 0;
+            }
+            const uint32_t item = gi - bt.p[p].item0;
+            for (uint32_t s = 0; ok && s < spi; s++) {
+                if (bi == 0) {
+                    __syncwarp();           // the previous batch's pieces have all been fetched
+                    convert_x();
+                    __syncwarp();
+                    load_x(s + NB);         // the next batch's values, consumed NB stages from now
+                }
+                const uint32_t xsb = xst + bi * (PIECES * 16), xcb = xcc + bi * (CCN * 8);
+                bi = bi + 1 == (uint32_t)NB ? 0u : bi + 1;
 
-                if (!mbar_wait(&full[slot], ph, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, 0xFFFFFFFFu)) {
+                if (!mbar_wait(&full[slot], ph, &abort_flag, bt.status, ST_WAIT_FULL_TIMEOUT, 0u)) {
                     ok = false;
                     break;
                 }
                 const uint32_t stage = smem_base + slot * STAGE;
+#ifdef MLXN_EXPERIMENTS
+                if (c.debug & 1u) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&empty[slot]);
+                    if (++slot == c.nslots) { slot = 0; ph ^= 1u; }
+                    continue;
+                }
+#endif
                 uint32_t lead = 0;
                 if constexpr (T == GT_Q6_K) {
                     lead = (s * SBYTES) & 15u;   // a multiple of 4
@@ -338,121 +480,86 @@ __global__ void __launch_bounds__(kMwThreads, 2)
 #pragma unroll
                     for (int h = 0; h < NM; h++) {
                         bf[h][0] = bf[h][1] = bf[h][2] = bf[h][3] = 0u;
-                        if (g < (uint32_t)MP) lds128(xst + ((((i * MP + g) * NM + h) * 4 + t) * 16), bf[h][0], bf[h][1], bf[h][2], bf[h][3]);
+                        if (g < (uint32_t)MP) lds128(xsb + ((((i * MP + g) * NM + h) * 4 + t) * 16), bf[h][0], bf[h][1], bf[h][2], bf[h][3]);
                     }
-                    float ci0[NG], cs0[NG], ci1[NG], cs1[NG];
+                    // cq: what the accumulators of a scale group start from, columns 2t and 2t + 1 (-offset sum(x));
+                    // cs0 / cs1: the columns' inverse pre-scales.  Columns past m hold zeros throughout, so with one
+                    // activation row the second column's scale is never looked at.
+                    float cq[NG][4], cs0[NG], cs1[NG];
 #pragma unroll
                     for (int q = 0; q < NG; q++) {
-                        ci0[q] = cs0[q] = ci1[q] = cs1[q] = 0.f;
+                        float c0 = 0.f, c1 = 0.f;
+                        cs0[q] = cs1[q] = 0.f;
                         if (2 * t < (uint32_t)MP) {
                             uint32_t u0, u1;
-                            lds64(xcc + ((i * MP + 2 * t) * NG + q) * 8, u0, u1);
-                            ci0[q] = __uint_as_float(u0);
+                            lds64(xcb + ((i * MP + 2 * t) * NG + q) * 8, u0, u1);
+                            c0 = __uint_as_float(u0);
                             cs0[q] = __uint_as_float(u1);
                         }
-                        if (2 * t + 1 < (uint32_t)MP) {
+                        if (MP > 1 && 2 * t + 1 < (uint32_t)MP) {
                             uint32_t u0, u1;
-                            lds64(xcc + ((i * MP + 2 * t + 1) * NG + q) * 8, u0, u1);
-                            ci1[q] = __uint_as_float(u0);
+                            lds64(xcb + ((i * MP + 2 * t + 1) * NG + q) * 8, u0, u1);
+                            c1 = __uint_as_float(u0);
                             cs1[q] = __uint_as_float(u1);
                         }
+                        cq[q][0] = c0; cq[q][1] = c1; cq[q][2] = c0; cq[q][3] = c1;
                     }
 
                     if constexpr (T == GT_Q6_K) {
-                        const uint32_t sb = sp + 2 * i;
+                        // row g of the stage, this unit's super-block; odd super-blocks start 2 bytes past a 4-byte boundary:
+                        // their words are read from the 4-byte boundary below and shifted by a byte permute
+                        const uint32_t u6 = stage + g * PITCH + lead + 210 * (sp + 2 * i) - 2 * sp;
+                        const uint32_t pA = u6 + q6A, pH = u6 + q6H, pP = ptab + (i * R + g) * 16;
 #pragma unroll
                         for (int j = 0; j < TPW; j++) {
                             uint32_t qv[2][4];   // [row g / g + 8][q1..q4]: four 6-bit codes each, one per byte
                             uint32_t pv[2][4];
 #pragma unroll
                             for (int h = 0; h < 2; h++) {
-                                const uint32_t rb = stage + (16 * j + g + 8 * h) * PITCH + lead + 210 * sb;
+                                const uint32_t off = (16 * j + 8 * h) * PITCH;
                                 uint32_t A, B, H;
                                 if (sp == 0) {
-                                    A = lds32(rb + q6A);
-                                    B = lds32(rb + q6A + 32);
-                                    H = lds32(rb + q6H);
-                                } else {   // odd super-blocks start 2 bytes past a 4-byte boundary
-                                    A = __byte_perm(lds32(rb + q6A - 2), lds32(rb + q6A + 2), 0x5432);
-                                    B = __byte_perm(lds32(rb + q6A + 30), lds32(rb + q6A + 34), 0x5432);
-                                    H = __byte_perm(lds32(rb + q6H - 2), lds32(rb + q6H + 2), 0x5432);
+                                    A = lds32(pA + off);
+                                    B = lds32(pA + off + 32);
+                                    H = lds32(pH + off);
+                                } else {
+                                    A = __byte_perm(lds32(pA + off), lds32(pA + off + 4), 0x5432);
+                                    B = __byte_perm(lds32(pA + off + 32), lds32(pA + off + 36), 0x5432);
+                                    H = __byte_perm(lds32(pH + off), lds32(pH + off + 4), 0x5432);
                                 }
                                 qv[h][0] = (A & 0x0F0F0F0Fu) | ((H & 0x03030303u) << 4);
                                 qv[h][1] = (B & 0x0F0F0F0Fu) | ((H & 0x0C0C0C0Cu) << 2);
                                 qv[h][2] = ((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u);
                                 qv[h][3] = ((B >> 4) & 0x0F0F0F0Fu) | ((H & 0xC0C0C0C0u) >> 2);
-                                lds128(ptab + (i * R + 16 * j + g + 8 * h) * 16, pv[h][0], pv[h][1], pv[h][2], pv[h][3]);
+                                lds128(pP + (16 * j + 8 * h) * 16, pv[h][0], pv[h][1], pv[h][2], pv[h][3]);
                             }
 #pragma unroll
                             for (int q = 0; q < 4; q++) {
-                                const uint32_t a0 = qv[0][q] & 0x00FF00FFu, a2 = (qv[0][q] >> 8) & 0x00FF00FFu;
-                                const uint32_t a1 = qv[1][q] & 0x00FF00FFu, a3 = (qv[1][q] >> 8) & 0x00FF00FFu;
-                                float d[4] = {ci0[q], ci1[q], ci0[q], ci1[q]};
-                                mma16816(d, a0, a1, a2, a3, bf[q][0], bf[q][1], d);
+                                const uint32_t a0 = __byte_perm(qv[0][q], 0u, 0x4240), a2 = __byte_perm(qv[0][q], 0u, 0x4341);
+                                const uint32_t a1 = __byte_perm(qv[1][q], 0u, 0x4240), a3 = __byte_perm(qv[1][q], 0u, 0x4341);
+                                float d[4];
+                                mma16816(d, a0, a1, a2, a3, bf[q][0], bf[q][1], cq[q]);
                                 mma16816(d, a0, a1, a2, a3, bf[q][2], bf[q][3], d);
                                 const float pa = __uint_as_float(pv[0][q]), pb = __uint_as_float(pv[1][q]);
-                                acc[j][0] = fmaf(pa * cs0[q], d[0], acc[j][0]);
-                                acc[j][1] = fmaf(pa * cs1[q], d[1], acc[j][1]);
-                                acc[j][2] = fmaf(pb * cs0[q], d[2], acc[j][2]);
-                                acc[j][3] = fmaf(pb * cs1[q], d[3], acc[j][3]);
+                                if constexpr (MP == 1) {
+                                    const float fa = pa * cs0[q], fb = pb * cs0[q];
+                                    acc[j][0] = fmaf(fa, d[0], acc[j][0]);
+                                    acc[j][2] = fmaf(fb, d[2], acc[j][2]);
+                                } else {
+                                    acc[j][0] = fmaf(pa * cs0[q], d[0], acc[j][0]);
+                                    acc[j][1] = fmaf(pa * cs1[q], d[1], acc[j][1]);
+                                    acc[j][2] = fmaf(pb * cs0[q], d[2], acc[j][2]);
+                                    acc[j][3] = fmaf(pb * cs1[q], d[3], acc[j][3]);
+                                }
                             }
                         }
                     } else {
-                        const uint32_t b = KB * w + i, boff = BB * b;
-                        const bool mis = (b & 1u) == 0;
-#pragma unroll
-                        for (int j = 0; j < TPW; j++) {
-                            uint32_t wa[2], wb[2];
-                            float dd[2];
-#pragma unroll
-                            for (int h = 0; h < 2; h++) {
-                                const uint32_t rb = stage + (16 * j + g + 8 * h) * PITCH + boff;
-                                dd[h] = half_bits_to_float(lds_u16(rb));
-                                if constexpr (T == GT_Q8_0) {
-                                    if (!mis) {
-                                        wa[h] = lds32(rb + 2 + 4 * t);
-                                        wb[h] = lds32(rb + 18 + 4 * t);
-                                    } else {
-                                        wa[h] = lds32(rb + 4 + 4 * t);
-                                        // lanes 0..2: the whole word; lane 3: the half words at either end of the block
-                                        wb[h] = __byte_perm(lds32(rb + (t < 3 ? 20 + 4 * t : 0)), lds32(rb + (t < 3 ? 20 + 4 * t : 32)),
-                                                            t < 3 ? 0x3210 : 0x5432);
-                                    }
-                                    wa[h] ^= 0x80808080u;   // signed byte -> byte + 128
-                                    wb[h] ^= 0x80808080u;
-                                } else {
-                                    if (!mis) wa[h] = lds32(rb + 2 + 4 * t);
-                                    else wa[h] = __byte_perm(lds32(rb + (t < 3 ? 4 + 4 * t : 0)), lds32(rb + (t < 3 ? 4 + 4 * t : 16)),
-                                                             t < 3 ? 0x3210 : 0x5432);
-                                    wb[h] = 0;
-                                }
-                            }
-                            float d[4] = {ci0[0], ci1[0], ci0[0], ci1[0]};
-                            if constexpr (T == GT_Q8_0) {
-                                uint32_t a0 = wa[0] & 0x00FF00FFu, a2 = (wa[0] >> 8) & 0x00FF00FFu;
-                                uint32_t a1 = wa[1] & 0x00FF00FFu, a3 = (wa[1] >> 8) & 0x00FF00FFu;
-                                mma16816(d, a0, a1, a2, a3, bf[0][0], bf[0][1], d);
-                                mma16816(d, a0, a1, a2, a3, bf[0][2], bf[0][3], d);
-                                a0 = wb[0] & 0x00FF00FFu; a2 = (wb[0] >> 8) & 0x00FF00FFu;
-                                a1 = wb[1] & 0x00FF00FFu; a3 = (wb[1] >> 8) & 0x00FF00FFu;
-                                mma16816(d, a0, a1, a2, a3, bf[1][0], bf[1][1], d);
-                                mma16816(d, a0, a1, a2, a3, bf[1][2], bf[1][3], d);
-                            } else {
-                                // low nibbles: elements c0..c3 of the word's four bytes; high nibbles (x 16): 16 + c
-                                uint32_t a0 = wa[0] & 0x000F000Fu, a2 = (wa[0] >> 8) & 0x000F000Fu;
-                                uint32_t a1 = wa[1] & 0x000F000Fu, a3 = (wa[1] >> 8) & 0x000F000Fu;
-                                mma16816(d, a0, a1, a2, a3, bf[0][0], bf[0][1], d);
-                                mma16816(d, a0, a1, a2, a3, bf[0][2], bf[0][3], d);
-                                a0 = wa[0] & 0x00F000F0u; a2 = (wa[0] >> 8) & 0x00F000F0u;
-                                a1 = wa[1] & 0x00F000F0u; a3 = (wa[1] >> 8) & 0x00F000F0u;
-                                mma16816(d, a0, a1, a2, a3, bf[1][0], bf[1][1], d);
-                                mma16816(d, a0, a1, a2, a3, bf[1][2], bf[1][3], d);
-                            }
-                            acc[j][0] = fmaf(dd[0] * cs0[0], d[0], acc[j][0]);
-                            acc[j][1] = fmaf(dd[0] * cs1[0], d[1], acc[j][1]);
-                            acc[j][2] = fmaf(dd[1] * cs0[0], d[2], acc[j][2]);
-                            acc[j][3] = fmaf(dd[1] * cs1[0], d[3], acc[j][3]);
-                        }
+                        // rows g and g + 8 of tile j sit (16 j + 8 h) PITCH bytes past row g of the stage
+                        const uint32_t b = KB * w + i, rb0 = stage + g * PITCH + BB * b;
+                        if ((b & 1u) == 0)
+                            mw_block_tiles<T, TPW, MP, PITCH, true>(rb0, rb0 + 4 + 4 * t, rb0 + mo0, rb0 + mo1, msel, bf, cq[0], cs0[0], cs1[0], acc);
+                        else
+                            mw_block_tiles<T, TPW, MP, PITCH, false>(rb0, rb0 + 2 + 4 * t, rb0 + 18 + 4 * t, 0u, 0u, bf, cq[0], cs0[0], cs1[0], acc);
                     }
                 }
                 __syncwarp();
@@ -463,7 +570,7 @@ __global__ void __launch_bounds__(kMwThreads, 2)
 
             // ---- end of the item: add the eight warps' partial sums in a fixed order and write the rows out ----
             if (!first_item) {   // the previous item's sums have all been read
-                if (!mbar_wait(&fin[1], fin_ph ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, 0xFFFFFFFFu)) break;
+                if (!mbar_wait(&fin[1], fin_ph ^ 1u, &abort_flag, bt.status, ST_WAIT_EMPTY_TIMEOUT, 0u)) break;
             }
 #pragma unroll
             for (int j = 0; j < TPW; j++) {
@@ -476,19 +583,20 @@ __global__ void __launch_bounds__(kMwThreads, 2)
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&fin[0]);
-            if (!mbar_wait(&fin[0], fin_ph, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, 0xFFFFFFFFu)) break;
+            if (!mbar_wait(&fin[0], fin_ph, &abort_flag, bt.status, ST_WAIT_EMPTY_TIMEOUT, 0u)) break;
             {
-                const uint32_t ld = qmv_ld(a);
-                for (uint32_t idx = tid; idx < (uint32_t)R * a.m; idx += kMwWarps * 32) {
+                const MwProb &P = bt.p[p];
+                const uint32_t ld = P.y_ld ? P.y_ld : P.n;
+                for (uint32_t idx = tid; idx < (uint32_t)R * pm; idx += kMwWarps * 32) {
                     const uint32_t col = idx / R, row = idx % R;
                     float sum = 0.f;
 #pragma unroll
                     for (int ww = 0; ww < kMwWarps; ww++) sum += __uint_as_float(lds32(red + ((ww * MP + col) * R + row) * 4));
                     const uint32_t grow = item * R + row;
-                    if (grow < a.n) {
-                        const size_t off = (size_t)col * ld + a.y_col0 + grow;
-                        a.y[off] = sum;
-                        for (uint32_t pr = 0; pr < a.n_peer; pr++) a.y_peer[pr][off] = sum;
+                    if (grow < P.n) {
+                        const size_t off = (size_t)col * ld + P.y_col0 + grow;
+                        P.y[off] = sum;
+                        for (uint32_t pr = 0; pr < bt.n_peer; pr++) bt.y_peer[pr][off] = sum;
                     }
                 }
             }
@@ -522,13 +630,15 @@ bool qmv_mma_supported(int ggml_type, const QmvArgs &a) {
 static inline size_t mw_align(size_t v, size_t al) { return (v + al - 1) / al * al; }
 
 template <int T, int TPW, int KB, int MP>
-static cudaError_t launch_mw(const QmvArgs &a, int sm_count, int ctas_per_sm, cudaStream_t st) {
+static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, cudaStream_t st) {
     using TR = MwTraits<T>;
     constexpr uint32_t R = 16 * TPW, PITCH = mw_pitch(T, KB), STAGE = R * PITCH;
-    constexpr uint32_t PIECES = KB * MP * TR::NM * 4, XST = (PIECES * 16 + KB * MP * TR::NG * 8 + 15u) & ~15u;
+    constexpr uint32_t PIECES = KB * MP * TR::NM * 4, NB = PIECES >= 32 ? 1 : 32 / PIECES;
+    constexpr uint32_t XST = (NB * PIECES * 16 + NB * KB * MP * TR::NG * 8 + 15u) & ~15u;   // as in the kernel
     MwCfg c{};
-    c.items = (a.n + R - 1) / R;
-    c.spi = a.k / (TR::UK * KB);
+#ifdef MLXN_EXPERIMENTS
+    if (const char *e = getenv("MLXN_MW_DEBUG")) c.debug = (uint32_t)atoi(e);
+#endif
     const size_t xst_bytes = mw_align((size_t)kMwWarps * XST, 128);
     const size_t ptab_bytes = T == GT_Q6_K ? (size_t)kMwWarps * R * 16 * KB : 0;
     const size_t red_bytes = (size_t)kMwWarps * MP * R * 4;
@@ -545,18 +655,72 @@ static cudaError_t launch_mw(const QmvArgs &a, int sm_count, int ctas_per_sm, cu
 
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return cudaErrorNotSupported;
-    const uint32_t row_bytes = (a.k / BlockTraits<T>::QK) * BlockTraits<T>::BYTES;
-    alignas(64) CUtensorMap wmap;
-    {
+    if (nops < 1 || nops > kMwMaxProbs) return cudaErrorInvalidValue;
+    static thread_local MwBatch bt;      // too large for the stack of a deep call chain; one launch at a time per thread
+    alignas(64) static thread_local MwMaps maps;
+    bt.nprob = (uint32_t)nops;
+    bt.early_weights = 1;
+    bt.n_peer = nops == 1 ? ops[0].n_peer : 0;
+    for (uint32_t i = 0; i < bt.n_peer; i++) bt.y_peer[i] = ops[0].y_peer[i];
+    bt.status = ops[0].status;
+    uint64_t total_stages = 0;
+    uint32_t items = 0;
+    for (int i = 0; i < nops; i++) {
+        const QmvArgs &a = ops[i];
+        MwProb &P = bt.p[i];
+        P.x = a.x;
+        P.y = a.y;
+        P.n = a.n;
+        P.k = a.k;
+        P.m = a.m;
+        P.spi = a.k / (TR::UK * KB);
+        P.item0 = items;
+        P.y_ld = a.y_ld;
+        P.y_col0 = a.y_col0;
+        const uint32_t its = (a.n + R - 1) / R;
+        items += its;
+        total_stages += (uint64_t)its * P.spi;
+        if (!a.early_weights) bt.early_weights = 0;
+        const uint32_t row_bytes = (a.k / BlockTraits<T>::QK) * BlockTraits<T>::BYTES;
         // the weight matrix as [n rows][row_bytes / 8] 8-byte elements; box = R rows x PITCH bytes
         const cuuint64_t gdim[2] = {row_bytes / 8, a.n};
         const cuuint64_t gstride[1] = {row_bytes};
         const cuuint32_t box[2] = {(cuuint32_t)(PITCH / 8), (cuuint32_t)R};
         const cuuint32_t estr[2] = {1, 1};
-        if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(a.w), gdim, gstride, box, estr,
+        if (enc(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(a.w), gdim, gstride, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
+    }
+    for (int i = nops; i < kMwMaxProbs; i++) {
+        bt.p[i] = MwProb{};
+        bt.p[i].item0 = items;
+        maps.m[i] = maps.m[0];
+    }
+    uint32_t grid = (uint32_t)(sm_count * ctas_per_sm);
+    if (grid > (uint32_t)kMwMaxGrid) grid = kMwMaxGrid;
+    if (grid > items) grid = items;
+    // contiguous chunks of items holding (nearly) the same number of stages each: CTA c starts at the first item whose
+    // stages begin at or after c / grid of all the launch's stages
+    {
+        uint32_t pi = 0;
+        uint64_t before = 0;   // stages of the problems ahead of pi
+        for (uint32_t cta = 0; cta <= grid; cta++) {
+            const uint64_t target = total_stages * cta / grid;
+            while (pi + 1 < (uint32_t)nops) {
+                const uint64_t its = bt.p[pi + 1].item0 - bt.p[pi].item0;
+                if (before + its * bt.p[pi].spi > target) break;
+                before += its * bt.p[pi].spi;
+                pi++;
+            }
+            const uint64_t its_p = (pi + 1 < (uint32_t)nops ? bt.p[pi + 1].item0 : items) - bt.p[pi].item0;
+            uint64_t in = (target - before + bt.p[pi].spi - 1) / bt.p[pi].spi;
+            if (in > its_p) in = its_p;
+            bt.cta_begin[cta] = bt.p[pi].item0 + (uint32_t)in;
+        }
+        bt.cta_begin[0] = 0;
+        bt.cta_begin[grid] = items;
+        for (uint32_t cta = grid + 1; cta <= (uint32_t)kMwMaxGrid; cta++) bt.cta_begin[cta] = items;
     }
     static size_t attr_smem[64] = {};
     int dev = 0;
@@ -567,44 +731,54 @@ static cudaError_t launch_mw(const QmvArgs &a, int sm_count, int ctas_per_sm, cu
         if (e != cudaSuccess) return e;
         attr_smem[dev] = smem;
     }
-    uint32_t grid = (uint32_t)(sm_count * ctas_per_sm);
-    if (grid > c.items) grid = c.items;
-    return launch_overlapped(qmv_mma_kernel<T, TPW, KB, MP>, dim3(grid), dim3(kMwThreads), smem, st, a, c, wmap);
+    return launch_overlapped(qmv_mma_kernel<T, TPW, KB, MP>, dim3(grid), dim3(kMwThreads), smem, st, bt, c, maps);
 }
 
 // (TPW, KB): a warp works on TPW x KB tile-units per stage.  Few weight rows -> narrow row groups and long K stages.
 // The activation split costs MP x KB per stage and warp whatever TPW is, so many activation rows want KB = 1.
 template <int T, int MP>
-static cudaError_t launch_mw_m(const QmvArgs &a, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
-    const uint32_t kb_ok = a.k / MwTraits<T>::UK;   // KB must divide the number of K units
-    if (tpw >= 4 || MP == 8 || kb_ok % 2 != 0) return launch_mw<T, 4, 1, MP>(a, sm_count, ctas_per_sm, st);
-    if constexpr (MP <= 4) {
-        if (tpw >= 2 || MP == 4 || kb_ok % 4 != 0) return launch_mw<T, 2, 2, MP>(a, sm_count, ctas_per_sm, st);
+static cudaError_t launch_mw_m(const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
+    uint32_t units_gcd = 4;   // KB must divide every problem's number of K units
+    for (int i = 0; i < nops; i++) {
+        const uint32_t u = ops[i].k / MwTraits<T>::UK;
+        if (u % 4 != 0) units_gcd = u % 2 == 0 ? (units_gcd < 2 ? units_gcd : 2) : 1;
     }
-    if constexpr (MP <= 2) return launch_mw<T, 1, 4, MP>(a, sm_count, ctas_per_sm, st);
+    if (tpw >= 4 || MP == 8 || units_gcd < 2) return launch_mw<T, 4, 1, MP>(ops, nops, sm_count, ctas_per_sm, st);
+    if constexpr (MP <= 4) {
+        if (tpw >= 2 || MP == 4 || units_gcd < 4) return launch_mw<T, 2, 2, MP>(ops, nops, sm_count, ctas_per_sm, st);
+    }
+    if constexpr (MP <= 2) return launch_mw<T, 1, 4, MP>(ops, nops, sm_count, ctas_per_sm, st);
     return cudaErrorInvalidConfiguration;
 }
 
 template <int T>
-static cudaError_t launch_mw_t(const QmvArgs &a, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
-    if (a.m <= 1) return launch_mw_m<T, 1>(a, sm_count, ctas_per_sm, tpw, st);
-    if (a.m <= 2) return launch_mw_m<T, 2>(a, sm_count, ctas_per_sm, tpw, st);
-    if (a.m <= 4) return launch_mw_m<T, 4>(a, sm_count, ctas_per_sm, tpw, st);
-    return launch_mw_m<T, 8>(a, sm_count, ctas_per_sm, tpw, st);
+static cudaError_t launch_mw_t(const QmvArgs *ops, int nops, uint32_t mmax, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
+    if (mmax <= 1) return launch_mw_m<T, 1>(ops, nops, sm_count, ctas_per_sm, tpw, st);
+    if (mmax <= 2) return launch_mw_m<T, 2>(ops, nops, sm_count, ctas_per_sm, tpw, st);
+    if (mmax <= 4) return launch_mw_m<T, 4>(ops, nops, sm_count, ctas_per_sm, tpw, st);
+    return launch_mw_m<T, 8>(ops, nops, sm_count, ctas_per_sm, tpw, st);
 }
 
-// `ctas_per_sm` (1 or 2) and `tpw` (0: chosen from n; 1, 2, 4) are tuning knobs of the caller.
-cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs &a, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
+// Launches `nops` (1..8) mat-vecs of one block type as ONE kernel.  The caller guarantees that no operation reads or
+// writes what another one writes.  `ctas_per_sm` (1 or 2) and `tpw` (0: chosen from the row count; 1, 2, 4) are tuning
+// knobs of the caller.
+cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
     if (ctas_per_sm < 1) ctas_per_sm = 1;
     if (ctas_per_sm > 2) ctas_per_sm = 2;
+    uint64_t rows = 0;
+    uint32_t mmax = 1;
+    for (int i = 0; i < nops; i++) {
+        rows += ops[i].n;
+        if (ops[i].m > mmax) mmax = ops[i].m;
+    }
     if (tpw <= 0) {
-        // the largest row group that still gives every SM an item
-        tpw = a.n >= 64u * (uint32_t)sm_count ? 4 : a.n >= 32u * (uint32_t)sm_count ? 2 : 1;
+        // the largest row group that still gives every CTA slot an item
+        tpw = rows >= 64ull * 2 * (uint32_t)sm_count ? 4 : rows >= 32ull * 2 * (uint32_t)sm_count ? 2 : 1;
     }
     switch (ggml_type) {
-    case GT_Q4_0: return launch_mw_t<GT_Q4_0>(a, sm_count, ctas_per_sm, tpw, st);
-    case GT_Q8_0: return launch_mw_t<GT_Q8_0>(a, sm_count, ctas_per_sm, tpw, st);
-    case GT_Q6_K: return launch_mw_t<GT_Q6_K>(a, sm_count, ctas_per_sm, tpw, st);
+    case GT_Q4_0: return launch_mw_t<GT_Q4_0>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
+    case GT_Q8_0: return launch_mw_t<GT_Q8_0>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
+    case GT_Q6_K: return launch_mw_t<GT_Q6_K>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -29,7 +29,7 @@ size_t qmv_tc_scratch_bytes(const QmvArgs &a);
 cudaError_t launch_qmv_tc(int ggml_type, const QmvArgs &a, uint8_t *scratch, uint32_t *flags, int sm_count, cudaStream_t st,
                           cudaStream_t pub_st, cudaEvent_t pub_ev, int *launches);
 bool qmv_mma_supported(int ggml_type, const QmvArgs &a);
-cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs &a, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st);
+cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st);
 cudaError_t launch_qmm_tc(int ggml_type, const QmmArgs &a, bool routed, uint32_t nt, uint8_t *scratch, cudaStream_t st,
                           int *launches);
 cudaError_t launch_qmm_simt(int ggml_type, const QmmArgs &a, bool routed, uint32_t max_rows, cudaStream_t st);
@@ -89,6 +89,7 @@ void mlxn_detail_count_launches(int launches) {
 
 static std::atomic<int> g_opt_qmv{-1}, g_opt_qmm{-1};  // -1 unset; qmv: 0 simple, 1 stream, 2 tc, 3 auto, 4 mma; qmm: 0 simt, 1 tc
 static std::atomic<int> g_opt_mma_ctas{2}, g_opt_mma_tpw{0};   // tuning knobs of the register-level mat-vec
+static std::atomic<int> g_opt_mv_batch{1};                     // coalesce conflict-free mat-vecs into one launch
 static int opt_qmv() {
     int v = g_opt_qmv.load();
     if (v < 0) {
@@ -131,6 +132,7 @@ struct Storage {
     cudaStream_t last_stream = nullptr;  // stream of the last operation that touched the storage
     bool has_last = false;
     bool kernel_written = false;  // some operation of this library has used the storage as an output
+    struct mlxn_encoder *pend_enc = nullptr;  // encoder holding a not-yet-launched mat-vec that uses the storage
     std::mutex mu;
 };
 
@@ -267,6 +269,12 @@ struct mlxn_encoder {
     std::vector<std::pair<void *, size_t>> cap_retired;   // arenas outgrown during the capture: also the graph's
     StatusBlock *sb = nullptr;
     uint32_t *status_dev = nullptr;   // == sb->dev
+    // Mat-vecs of the current concurrent group that have been encoded but not launched: the reference dispatches the
+    // operations of a group concurrently; here up to 8 of them (same block type, same activation-row class) leave as
+    // ONE kernel whose CTAs share the work of all of them.  Launched by the first thing that ends the group.
+    std::vector<QmvArgs> pend;
+    int pend_type = 0, pend_lane = 0;
+    uint32_t pend_mp = 0;
     uint32_t *status_host = nullptr;  // pinned
 };
 
@@ -324,6 +332,12 @@ extern "C" int mlxn_set_option(const char *key, const char *value) {
         else if (strcmp(value, "simple") == 0) g_opt_qmv = 0;
         else if (strcmp(value, "mma") == 0) g_opt_qmv = 4;
         else return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: qmv must be 'auto', 'mma', 'tc', 'stream' or 'simple'");
+        return MLXN_OK;
+    }
+    if (strcmp(key, "qmv_batch") == 0) {
+        if (strcmp(value, "0") != 0 && strcmp(value, "1") != 0)
+            return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: qmv_batch must be '0' or '1'");
+        g_opt_mv_batch = value[0] == '1';
         return MLXN_OK;
     }
     if (strcmp(key, "qmv_mma_ctas") == 0 || strcmp(key, "qmv_mma_tpw") == 0) {
@@ -481,7 +495,15 @@ extern "C" uint64_t mlxn_buffer_byte_offset(const mlxn_buffer *buf) { return buf
 extern "C" void *mlxn_buffer_device_ptr(const mlxn_buffer *buf) { return buf->dev(); }
 
 // wait for whatever touched the storage last (device work or an upload still reading the shadow)
+static int encoder_flush_pending(struct mlxn_encoder *e);
 static int storage_quiesce(Storage *s) {
+    if (s->pend_enc) {   // a mat-vec that uses the storage is still waiting to be launched
+        struct mlxn_encoder *pe = s->pend_enc;
+        s->mu.unlock();   // the flush takes the storages' locks itself
+        const int rc = encoder_flush_pending(pe);
+        s->mu.lock();
+        if (rc) return rc;
+    }
     if (s->has_last) {
         CUDA_TRY(cudaStreamSynchronize(s->last_stream), "stream synchronize");
         s->has_last = false;
@@ -779,6 +801,7 @@ static void encoder_release_retained(mlxn_encoder *e) {
 extern "C" void mlxn_encoder_destroy(mlxn_encoder *enc) {
     if (!enc) return;
     cudaSetDevice(enc->ordinal);
+    (void)encoder_flush_pending(enc);
     cudaError_t serr = cudaStreamSynchronize(enc->aux);
     for (int l = 0; l < kLanes; l++) {
         cudaError_t e1 = cudaStreamSynchronize(enc->lanes[l]);
@@ -827,6 +850,7 @@ extern "C" void mlxn_encoder_destroy(mlxn_encoder *enc) {
 }
 
 static int encoder_join_lanes(mlxn_encoder *e);
+static int encoder_flush_pending(mlxn_encoder *e);
 // Lane 0, after it has been made to wait for the other lane: work the caller enqueues on the returned stream runs
 // behind everything encoded so far.
 extern "C" void *mlxn_encoder_stream(mlxn_encoder *enc) {
@@ -838,7 +862,50 @@ extern "C" void *mlxn_encoder_stream(mlxn_encoder *enc) {
 
 // Ends the current concurrent group: lane 0 waits for every other lane that has work of the group; the next
 // operation starts a new group on lane 0.
+static uint32_t mv_row_class(uint32_t m) { return m <= 1 ? 1u : m <= 2 ? 2u : m <= 4 ? 4u : 8u; }
+static int encoder_scratch_on(mlxn_encoder *e, int lane, size_t bytes, uint8_t **out);
+static int encoder_flush_pending(mlxn_encoder *e) {
+    if (e->pend.empty()) return MLXN_OK;
+    cudaSetDevice(e->ordinal);
+    cudaStream_t st = e->lanes[e->pend_lane];
+    cudaError_t err = cudaSuccess;
+    int launches = 1, rc = MLXN_OK;
+    // A mat-vec that ended up alone (the next operation depended on it, or nothing followed) gains nothing from the
+    // batched kernel's shared work list; with "auto" it takes the kernel that is fastest for a lone call of its kind.
+    const QmvArgs &a0 = e->pend[0];
+    const bool lone_other = e->pend.size() == 1 && opt_qmv() == 3 && a0.n_peer == 0 &&
+                            (e->pend_type == GT_Q6_K || a0.m > 2);
+    if (lone_other) {
+        if (!(e->pend_type == GT_Q6_K && a0.m == 1) && qmv_tc_supported(e->pend_type, a0)) {
+            uint8_t *scratch = nullptr;
+            if ((rc = encoder_scratch_on(e, e->pend_lane, qmv_tc_scratch_bytes(a0), &scratch)) == MLXN_OK) {
+                launches = 0;
+                err = launch_qmv_tc(e->pend_type, a0, scratch, e->status_dev + 64, e->dev->sm_count, st, nullptr, nullptr, &launches);
+                g_last_kernel = "qmv_tc";
+            }
+        } else {
+            err = launch_qmv(e->pend_type, a0, true, e->dev->sm_count, st, &g_last_kernel);
+        }
+    } else {
+        err = launch_qmv_mma(e->pend_type, e->pend.data(), (int)e->pend.size(), e->dev->sm_count, g_opt_mma_ctas.load(),
+                             g_opt_mma_tpw.load(), st);
+    }
+    e->pend.clear();
+    for (mlxn_buffer *b : e->retained) {
+        std::lock_guard<std::mutex> lk(b->st->mu);
+        if (b->st->pend_enc == e) b->st->pend_enc = nullptr;
+    }
+    if (rc) return rc;
+    if (err != cudaSuccess) return cuda_fail(err, "mat-vec launch");
+    g_launches.fetch_add((uint64_t)launches);
+    return MLXN_OK;
+}
+
 static int encoder_join_lanes(mlxn_encoder *e) {
+    {
+        const int frc = encoder_flush_pending(e);
+        if (frc) return frc;
+    }
     for (int l = 1; l < kLanes; l++) {
         if (!e->lane_busy[l]) continue;
         CUDA_TRY(cudaEventRecord(e->ev_join[l], e->lanes[l]), "event record");
@@ -921,6 +988,7 @@ extern "C" int mlxn_encoder_wait_until_completed(mlxn_encoder *enc) {
     if (enc->committed) {
         e = cudaEventSynchronize(enc->ev_end);
     } else {
+        (void)encoder_flush_pending(enc);
         e = cudaStreamSynchronize(enc->aux);
         for (int l = 0; l < kLanes && e == cudaSuccess; l++) e = cudaStreamSynchronize(enc->lanes[l]);
     }
@@ -1149,9 +1217,10 @@ extern "C" void mlxn_graph_destroy(mlxn_graph *graph) {
 }
 
 // Grows the encoder's scratch arena (kept for its lifetime; an outgrown arena is freed at the next wait).
-static int encoder_scratch(mlxn_encoder *e, size_t bytes, uint8_t **out) {
-    uint8_t *&scratch = e->scratch_lane[e->cur_lane];  // operations on different lanes may run at the same time
-    size_t &scratch_bytes = e->scratch_lane_bytes[e->cur_lane];
+static int encoder_scratch(mlxn_encoder *e, size_t bytes, uint8_t **out) { return encoder_scratch_on(e, e->cur_lane, bytes, out); }
+static int encoder_scratch_on(mlxn_encoder *e, int lane, size_t bytes, uint8_t **out) {
+    uint8_t *&scratch = e->scratch_lane[lane];  // operations on different lanes may run at the same time
+    size_t &scratch_bytes = e->scratch_lane_bytes[lane];
     if (bytes > scratch_bytes) {
         size_t want = bucket_size(bytes < (1u << 20) ? (1u << 20) : bytes);
         void *p = scratch_take(e->ordinal, want, &want);
@@ -1210,7 +1279,7 @@ struct OpBuf {
     mlxn_buffer *b;
     bool out;
 };
-static int op_begin(mlxn_encoder *e, std::initializer_list<OpBuf> bufs) {
+static int op_begin(mlxn_encoder *e, std::initializer_list<OpBuf> bufs, bool joins_batch = false) {
     int rc = encoder_begin_work(e);
     if (rc) return rc;
     auto has = [](const std::vector<const void *> &v, const void *p) {
@@ -1232,7 +1301,8 @@ static int op_begin(mlxn_encoder *e, std::initializer_list<OpBuf> bufs) {
     }
     if (conflict && (rc = encoder_join_lanes(e))) return rc;
     const bool first = e->grp_reads.empty() && e->grp_writes.empty();
-    const int lane = first ? 0 : (e->cur_lane + 1) % kLanes;
+    // a mat-vec that leaves with the pending batch shares that batch's lane; everything else alternates
+    const int lane = first ? 0 : (joins_batch && !e->pend.empty()) ? e->pend_lane : (e->cur_lane + 1) % kLanes;
     if (!e->grp_open) {
         CUDA_TRY(cudaEventRecord(e->ev_fork, e->lanes[0]), "event record");  // everything before this group
         e->grp_open = true;
@@ -1319,10 +1389,20 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
                        mlxn_buffer *output, const mlxn_qmm_params *p, const ShardOut *sh = nullptr) {
     int rc = touch_kernel(reg, dev, mv_kernel_name((int)p->ggml_type));
     if (rc) return rc;
-    if ((rc = op_begin(enc, {{input, false}, {weight, false}, {output, true}}))) return rc;
-    const bool stream = opt_qmv_stream();
-    // rows are processed in groups of at most 8 (the reference launches one grid row per input row)
-    for (uint32_t m0 = 0; m0 < p->m; m0 += 8) {
+    const int mode = opt_qmv();
+    // "auto": the register-level kernel where it measured fastest (few activation rows: its cost grows with m, the
+    // tensor-memory kernel's does not), the tensor-memory kernel for the rest
+    auto wants_mma = [&](const QmvArgs &a) {
+        if (mode == 4) return true;
+        if (mode != 3) return false;
+        // measured: batched, the register-level kernel is the faster one except for many activation rows on the
+        // long-K and the widest Q6_K shapes
+        const bool q6 = (int)p->ggml_type == GT_Q6_K;
+        if (a.m >= 4 && a.k >= 8192) return false;
+        if (q6 && a.m > 4 && a.n >= 8192) return false;
+        return true;
+    };
+    auto make_args = [&](uint32_t m0) {
         QmvArgs a{};
         a.w = weight->dev();
         a.x = reinterpret_cast<const float *>(input->dev()) + (size_t)m0 * p->k;
@@ -1343,24 +1423,56 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
         a.expert_stride = 0;
         a.status = enc->status_dev;
         a.early_weights = weight->st->kernel_written ? 0u : 1u;
-        // The tensor-core kernel's time does not grow with the number of rows, the streaming SIMT kernel's does.
-        // Alone, the streaming kernel is a little faster for one row; in a sequence of mat-vecs the tensor-core
-        // kernel's calls overlap better, and the whole decode sweep is fastest with it everywhere ("auto").
-        const int mode = opt_qmv();
+        return a;
+    };
+    // A mat-vec for the register-level kernel is not launched at once: it waits for the operations that follow, and
+    // conflict-free mat-vecs of the same block type leave as one kernel (upstream dispatches the operations between
+    // two barriers concurrently, src/encoder.rs:837-853).  The group ends, and the kernel is launched, at the first
+    // conflict, barrier, commit or capture boundary, or when the next mat-vec does not fit the batch.
+    if (p->m <= 8) {
+        const QmvArgs a0 = make_args(0);
+        if (wants_mma(a0) && qmv_mma_supported((int)p->ggml_type, a0)) {
+            const bool batch = g_opt_mv_batch.load() != 0 && !sh;
+            const bool fits = batch && !enc->pend.empty() && enc->pend_type == (int)p->ggml_type &&
+                              enc->pend_mp == mv_row_class(a0.m) && enc->pend.size() < 8;
+            if (!enc->pend.empty() && !fits && (rc = encoder_flush_pending(enc))) return rc;
+            if ((rc = op_begin(enc, {{input, false}, {weight, false}, {output, true}}, true))) return rc;
+            // (a conflict found by op_begin has launched the batch and started a new group)
+            if (enc->pend.empty()) {
+                enc->pend_type = (int)p->ggml_type;
+                enc->pend_mp = mv_row_class(a0.m);
+                enc->pend_lane = enc->cur_lane;
+            }
+            enc->pend.push_back(a0);
+            for (mlxn_buffer *b : {input, weight, output}) {
+                std::lock_guard<std::mutex> lk(b->st->mu);
+                b->st->pend_enc = enc;
+            }
+            g_last_kernel = "qmv_mma";
+            g_dispatch.fetch_add(1);
+            if (!batch) return encoder_flush_pending(enc);
+            return MLXN_OK;
+        }
+    }
+    if ((rc = op_begin(enc, {{input, false}, {weight, false}, {output, true}}))) return rc;
+    const bool stream = opt_qmv_stream();
+    // rows are processed in groups of at most 8 (the reference launches one grid row per input row)
+    for (uint32_t m0 = 0; m0 < p->m; m0 += 8) {
+        const QmvArgs a = make_args(m0);
+        // The tensor-memory kernel's time does not grow with the number of rows, the streaming SIMT kernel's does.
         static const int min_m = [] { const char *e = getenv("MLXN_QMV_TC_MIN_M"); return e ? atoi(e) : 1; }();         // experiment switches
         static const int min_m_q6k = [] { const char *e = getenv("MLXN_QMV_TC_MIN_M_Q6K"); return e ? atoi(e) : 1; }();
         const int need_m = (int)p->ggml_type == GT_Q6_K ? (a.k >= 8192 ? (min_m_q6k < 2 ? min_m_q6k : 2) : min_m_q6k) : min_m;
-        const bool want_tc = mode == 2 || (mode == 3 && (int)a.m >= need_m);
-        if (mode == 4 && qmv_mma_supported((int)p->ggml_type, a)) {
-            // register-level tensor-core mat-vec: one launch, no scratch, every output written once
-            CUDA_TRY(launch_qmv_mma((int)p->ggml_type, a, dev->sm_count, g_opt_mma_ctas.load(), g_opt_mma_tpw.load(), enc->stream),
+        const bool want_tc = mode == 2 || ((mode == 3 || mode == 4) && (int)a.m >= need_m);
+        if (mode == 4 && p->m > 8 && qmv_mma_supported((int)p->ggml_type, a)) {
+            CUDA_TRY(launch_qmv_mma((int)p->ggml_type, &a, 1, dev->sm_count, g_opt_mma_ctas.load(), g_opt_mma_tpw.load(), enc->stream),
                      "mat-vec launch");
             g_launches.fetch_add(1);
             g_last_kernel = "qmv_mma";
             continue;
         }
-        if (want_tc && qmv_tc_supported((int)p->ggml_type, a)) {
-            // tensor-core path: packed activations, block sums and split-K partial sums live in the encoder's arena
+        if (want_tc && mode != 4 && qmv_tc_supported((int)p->ggml_type, a)) {
+            // tensor-memory path: packed activations, block sums and split-K partial sums live in the encoder's arena
             uint8_t *scratch = nullptr;
             if ((rc = encoder_scratch(enc, qmv_tc_scratch_bytes(a), &scratch))) return rc;
             int launches = 0;

@@ -85,3 +85,16 @@ def pack(ggml_type: int, values: np.ndarray) -> np.ndarray:
     if values.size % BLOCK_VALUES[t] != 0:
         raise ValueError(f"{values.size} values is not a multiple of the block length {BLOCK_VALUES[t]}")
     return {Q4_0: pack_q4_0, Q8_0: pack_q8_0, Q6_K: pack_q6_k}[t](values)
+
+
+# Block geometry by type name: (values per block, bytes per block, byte offset of the f16 scale d)
+BLOCK_GEOMETRY = {"Q4_0": (32, 18, 0), "Q8_0": (32, 34, 0), "Q6_K": (256, 210, 208)}
+
+
+def random_blocks(rng, type_name: str, n: int, k: int) -> np.ndarray:
+    """n x k weights as random block bytes with finite f16 scales in a small range.  For timing and memory-traffic
+    runs only: the kernels' speed does not depend on the values, and packing 600 MB of real weights takes minutes."""
+    qk, bb, dpos = BLOCK_GEOMETRY[type_name]
+    raw = rng.integers(0, 256, size=(n * (k // qk), bb), dtype=np.uint8)
+    raw[:, dpos + 1] = (raw[:, dpos + 1] & 0x83) | 0x20   # f16 scale exponent in a small finite range
+    return raw.reshape(-1)
