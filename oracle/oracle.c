@@ -14,9 +14,10 @@
  * whose expected values are literal numbers in tests/test_oracle.py, (2) an
  * independent numpy restatement of the upstream production dequantizers
  * (src/gguf/mod.rs) that must agree bit for bit with this file, which follows
- * the upstream test-suite dequantizers, and (3) the committed fixtures under
- * tests/golden/.  Against outputs of the upstream code itself parity is
- * unpinned.
+ * the upstream test-suite dequantizers, and (3) the vectors under tests/golden/,
+ * which this oracle produced itself (tests/golden/make_golden.py): they freeze
+ * its answers against later edits, they do not tie it to upstream.  Against
+ * outputs of the upstream code itself parity is unpinned.
  *
  * Build: gcc -O2 -ffp-contract=off -fPIC -shared (no FMA contraction, so the
  * f32 accumulation order and rounding are those of the upstream scalar loop).

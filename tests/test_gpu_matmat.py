@@ -83,6 +83,64 @@ def test_short_and_odd_k(ctx, variant, tname, k):
     check(ctx, tname, wq, normal_acts(k, m, k), n, k, force=True)
 
 
+def sampled_rows(n, count, rng_seed=0):
+    """A sample of weight rows that always includes the first and last rows of the first, a middle and the last
+    128-row tile (the tensor-core kernel's work items)."""
+    fixed = {0, 127, 128, n // 2, n - 129 if n > 129 else 0, n - 128 if n > 128 else 0, n - 1}
+    rest = np.random.default_rng(rng_seed).choice(n, size=max(0, count - len(fixed)), replace=False)
+    return np.array(sorted(fixed | set(int(r) for r in rest)))
+
+
+# every prefill cell of the benchmark: m in {512, 2048} x {(4096, 4096), (12288, 4096), (4096, 12288)} x {Q4_0, Q6_K}
+@pytest.mark.parametrize("tname", ["Q4_0", "Q6_K"])
+@pytest.mark.parametrize("m,n,k", [(2048, 4096, 4096), (512, 12288, 4096), (2048, 12288, 4096), (512, 4096, 12288),
+                                   (2048, 4096, 12288)])
+def test_benchmark_prefill_cells_sampled(ctx, tname, m, n, k):
+    """The benchmark's own prefill shapes at full size (256-wide activation tiles, no K split, 1.7 waves of the
+    persistent walk) against the oracle on a sample of weight rows x a sample of activation rows."""
+    mx.set_option("qmm", "tc")
+    gtype, otype = TYPES[tname]
+    rb = orc.row_bytes(otype, k)
+    base = normal_weights(31, 512, k, otype).reshape(512, rb)
+    # distinct rows everywhere, quick to build: the 512 seeded rows rolled by a different amount per block of 512
+    wq = np.concatenate([np.roll(base, 7 * i, axis=0) for i in range(n // 512)]).reshape(-1)
+    x = normal_acts(31, m, k)
+    y = ctx.matmul(gtype, wq, x, n, k)
+    assert mx.last_kernel_name() == "qmm_tc"
+    assert np.isfinite(y).all()
+    rows = sampled_rows(n, 40)
+    xr = np.array(sorted({0, 1, 63, 64, 127, 128, 255, 256, m // 2, m - 257, m - 256, m - 65, m - 1}))
+    wsub = np.concatenate([wq[r * rb:(r + 1) * rb] for r in rows])
+    y_ref, ad = orc.qmatmul(otype, wsub, x[xr], len(rows), k, nthreads=8)
+    assert norm_err(y[np.ix_(xr, rows)], y_ref, ad) <= MM_TOL
+    y16, _ = orc.qmatmul(otype, wsub, x[xr], len(rows), k, f16_operands=True, nthreads=8)
+    assert norm_err(y[np.ix_(xr, rows)], y16, ad) <= F16_ORACLE_TOL
+
+
+# the large-vocabulary lm_head: Q6_K, k = 5120 (210-byte blocks x 20: rows start on 16-byte boundaries only every
+# other row, so the mat-mat fetches them with the generic 16-byte copies), m = 256
+@pytest.mark.parametrize("n", [16384 + 64, 151936])
+def test_lm_head_q6k_m256_sampled(ctx, n):
+    mx.set_option("qmm", "tc")
+    gtype, otype = TYPES["Q6_K"]
+    k, m = 5120, 256
+    rb = orc.row_bytes(otype, k)
+    base = normal_weights(41, 512, k, otype).reshape(512, rb)
+    reps = (n + 511) // 512
+    wq = np.concatenate([np.roll(base, 11 * i, axis=0) for i in range(reps)])[:n].reshape(-1)
+    x = normal_acts(41, m, k)
+    y = ctx.matmul(gtype, wq, x, n, k)
+    assert mx.last_kernel_name() == "qmm_tc"
+    assert np.isfinite(y).all()
+    rows = sampled_rows(n, 48)
+    xr = np.array([0, 1, 63, 64, 127, 128, 200, 255])
+    wsub = np.concatenate([wq[r * rb:(r + 1) * rb] for r in rows])
+    y_ref, ad = orc.qmatmul(otype, wsub, x[xr], len(rows), k, nthreads=8)
+    assert norm_err(y[np.ix_(xr, rows)], y_ref, ad) <= MM_TOL
+    y16, _ = orc.qmatmul(otype, wsub, x[xr], len(rows), k, f16_operands=True, nthreads=8)
+    assert norm_err(y[np.ix_(xr, rows)], y16, ad) <= F16_ORACLE_TOL
+
+
 @pytest.mark.parametrize("tname", ["Q4_0", "Q6_K"])
 @pytest.mark.parametrize("m,n,k", [(512, 4096, 4096), (512, 1024, 12288)])
 def test_prefill_shapes_sampled(ctx, tname, m, n, k):

@@ -206,3 +206,68 @@ def test_q6k_row_pairs(ctx, n, k, m):
         assert mx.last_kernel_name() != "qmv_tc"
     finally:
         mx.set_option("qmv", "auto")
+
+
+# ---- the large-vocabulary lm_head at full size: Q6_K 151936 x 5120, m = 1 (638 MB of weights), a sample of rows
+# ---- including the first and last tiles
+@pytest.mark.parametrize("kernel", ["auto", "tc", "stream"])
+def test_lm_head_q6k_full_size_sampled(ctx, kernel):
+    mx.set_option("qmv", kernel)
+    try:
+        gtype, otype = TYPES["Q6_K"]
+        n, k = 151936, 5120
+        rb = orc.row_bytes(otype, k)
+        base = normal_weights(51, 512, k, otype).reshape(512, rb)
+        wq = np.concatenate([np.roll(base, 13 * i, axis=0) for i in range((n + 511) // 512)])[:n].reshape(-1)
+        x = normal_acts(51, 1, k)
+        y = ctx.matmul(gtype, wq, x, n, k)
+        assert np.isfinite(y).all() and np.count_nonzero(y) > 0.99 * n
+        rows = np.array(sorted({0, 1, 127, 128, n // 2, n - 129, n - 128, n - 2, n - 1} |
+                               set(int(r) for r in np.random.default_rng(1).choice(n, size=55, replace=False))))
+        wsub = np.concatenate([wq[r * rb:(r + 1) * rb] for r in rows])
+        y_ref, ad = orc.qmatmul(otype, wsub, x, len(rows), k, nthreads=8)
+        assert norm_err(y[:, rows], y_ref, ad) <= MV_TOL
+    finally:
+        mx.set_option("qmv", "auto")
+
+
+# ---- several conflict-free mat-vecs in one encoder leave as one kernel; a mat-vec that reads another one's result
+# ---- ends the group first (upstream: concurrent dispatch between barriers, src/encoder.rs:837-853)
+@pytest.mark.parametrize("tname", ["Q4_0", "Q8_0", "Q6_K"])
+def test_batched_launch_of_independent_matvecs(ctx, tname):
+    gtype, otype = TYPES[tname]
+    d = ctx.device
+    k = 4096
+    shapes = [(4096, 1), (1024, 1), (12288, 1), (512, 1), (4096, 2), (64, 1), (1030, 1), (2048, 1), (4096, 1), (256, 1)]
+    ws, xs, wbs, xbs, ybs = [], [], [], [], []
+    for i, (n, m) in enumerate(shapes):
+        ws.append(normal_weights(60 + i, n, k, otype))
+        xs.append(normal_acts(60 + i, m, k))
+        wbs.append(ctx.buf(ws[-1], mx.DType.U8))
+        xbs.append(ctx.buf(xs[-1], mx.DType.F32))
+        ybs.append(d.alloc_buffer(m * n * 4, mx.DType.F32))
+    mx.reset_counters()
+    enc = d.command_encoder()
+    for (n, m), wb, xb, yb in zip(shapes, wbs, xbs, ybs):
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, xb, wb, yb, mx.GgmlQuantizedMatmulParams(m, n, k, gtype))
+    assert mx.kernel_launch_count() <= 3          # nothing has been launched for the open batch yet
+    enc.commit_and_wait()
+    assert mx.dispatch_count() == len(shapes) and mx.kernel_launch_count() < len(shapes)
+    for (n, m), w, x, yb in zip(shapes, ws, xs, ybs):
+        y_ref, ad = orc.qmatmul(otype, w, x, n, k, nthreads=8)
+        assert norm_err(yb.as_slice(np.float32).reshape(m, n), y_ref, ad) <= MV_TOL, (tname, n, m)
+    # a dependent pair: the second reads the first one's result, so the first is launched before the second is queued
+    n1, n2 = 4096, 512
+    w1, w2 = normal_weights(81, n1, k, otype), normal_weights(82, n2, n1, otype)
+    x = normal_acts(81, 1, k)
+    y1, y2 = d.alloc_buffer(n1 * 4, mx.DType.F32), d.alloc_buffer(n2 * 4, mx.DType.F32)
+    enc = d.command_encoder()
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, ctx.buf(x, mx.DType.F32), ctx.buf(w1, mx.DType.U8), y1,
+                             mx.GgmlQuantizedMatmulParams(1, n1, k, gtype))
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, y1, ctx.buf(w2, mx.DType.U8), y2, mx.GgmlQuantizedMatmulParams(1, n2, n1, gtype))
+    enc.commit_and_wait()
+    r1, ad1 = orc.qmatmul(otype, w1, x, n1, k, nthreads=8)
+    got1 = y1.as_slice(np.float32).reshape(1, n1)
+    assert norm_err(got1, r1, ad1) <= MV_TOL
+    r2, ad2 = orc.qmatmul(otype, w2, got1.copy(), n2, n1, nthreads=8)
+    assert norm_err(y2.as_slice(np.float32).reshape(1, n2), r2, ad2) <= MV_TOL

@@ -172,3 +172,44 @@ def test_moe_ffn_layer_full_size_sampled(ctx):
     toks = np.unique(pairs // top_k)[:16]
     want = orc.moe_weighted_reduce(yd.reshape(T, top_k, hidden)[toks].reshape(-1, hidden), rw[toks], len(toks), top_k, hidden)
     assert np.allclose(got[toks], want, rtol=1e-5, atol=1e-6)
+
+
+def test_moe_ffn_layer_full_size_decode(ctx):
+    """The MoE configuration at its full size for one token (128 experts, top-8, hidden 2048, ffn 768; the routed
+    mat-vec form, n_tokens = 1 for gate / up and n_tokens = 8, top_k = 1 for down): every output against the oracle."""
+    d = ctx.device
+    E, top_k, hidden, ffn, T = 128, 8, 2048, 768, 1
+    g4, o4 = TYPES["Q4_0"]
+    g6, o6 = TYPES["Q6_K"]
+    base_g = normal_weights(71, ffn, hidden, o4).reshape(ffn, -1)
+    base_u = normal_weights(72, ffn, hidden, o4).reshape(ffn, -1)
+    base_d = normal_weights(73, hidden, ffn, o6).reshape(hidden, -1)
+    wg = np.concatenate([np.roll(base_g, e, axis=0) for e in range(E)]).reshape(-1)
+    wu = np.concatenate([np.roll(base_u, 3 * e, axis=0) for e in range(E)]).reshape(-1)
+    wd = np.concatenate([np.roll(base_d, 5 * e, axis=0) for e in range(E)]).reshape(-1)
+    x = normal_acts(74, T, hidden)
+    logits = np.random.default_rng(75).standard_normal((T, E)).astype(np.float32)
+    ids, rw = route(ctx, logits, top_k)
+    o_ids, o_rw = orc.moe_softmax_topk(logits, top_k)
+    assert np.array_equal(ids, o_ids)
+    flat = ids.reshape(-1)
+    yg, _ = ctx.matmul_id(g4, wg, wg.size // E, x, flat, top_k, ffn, hidden, E)
+    assert mx.last_kernel_name().startswith("qmv")
+    yu, _ = ctx.matmul_id(g4, wu, wu.size // E, x, flat, top_k, ffn, hidden, E)
+    rg, adg = orc.qmatmul_id(o4, wg, wg.size // E, x, flat, top_k, ffn, hidden, E, nthreads=8)
+    ru, adu = orc.qmatmul_id(o4, wu, wu.size // E, x, flat, top_k, ffn, hidden, E, nthreads=8)
+    assert norm_err(yg, rg, adg) <= 1e-5 and norm_err(yu, ru, adu) <= 1e-5
+    act = d.alloc_buffer(yg.nbytes, mx.DType.F32)
+    enc = d.command_encoder()
+    mx.silu_mul(enc, ctx.registry, d, ctx.buf(yg, mx.DType.F32), ctx.buf(yu, mx.DType.F32), act, yg.size)
+    enc.commit_and_wait()
+    a = act.as_slice(np.float32).reshape(T * top_k, ffn).copy()
+    yd, _ = ctx.matmul_id(g6, wd, wd.size // E, a, flat, 1, hidden, ffn, E)
+    rd, add = orc.qmatmul_id(o6, wd, wd.size // E, a, flat, 1, hidden, ffn, E, nthreads=8)
+    assert norm_err(yd, rd, add) <= 1e-5
+    out = d.alloc_buffer(T * hidden * 4, mx.DType.F32)
+    enc = d.command_encoder()
+    mx.moe_weighted_reduce(enc, ctx.registry, d, ctx.buf(rw, mx.DType.F32), ctx.buf(yd, mx.DType.F32), out, T, top_k, hidden)
+    enc.commit_and_wait()
+    want = orc.moe_weighted_reduce(yd, o_rw, T, top_k, hidden)
+    assert np.allclose(out.as_slice(np.float32).reshape(T, hidden), want, rtol=1e-5, atol=1e-6)

@@ -18,7 +18,7 @@ def ctx():
     return Ctx()
 
 
-@pytest.mark.parametrize("qmv", ["auto", "tc", "stream", "simple"])
+@pytest.mark.parametrize("qmv", ["auto", "mma", "tc", "stream", "simple"])
 @pytest.mark.parametrize("tname,n,k,m,world", [("Q8_0", 1024, 4096, 1, 2), ("Q8_0", 1024, 4096, 8, 4), ("Q6_K", 2048, 2048, 4, 2),
                                                ("Q4_0", 768, 1024, 3, 3), ("Q6_K", 512, 768, 2, 2), ("Q8_0", 1536, 12288, 2, 2)])
 def test_sharded_equals_unsharded(ctx, qmv, tname, n, k, m, world):
@@ -46,7 +46,9 @@ def test_sharded_equals_unsharded(ctx, qmv, tname, n, k, m, world):
         assert norm_err(got, y_ref, ad) <= MV_TOL
         # the peer copy is written by the same kernels; download it through a fresh host view
         got_peer = peer.download(np.float32).reshape(m, n)
-        assert np.array_equal(got_peer.view(np.uint32), got.view(np.uint32)) or norm_err(got_peer, y_ref, ad) <= MV_TOL
+        assert norm_err(got_peer, y_ref, ad) <= MV_TOL
+        if mx.last_kernel_name() != "qmv_tc":     # every kernel but the one that adds split tiles up with atomics
+            assert np.array_equal(got_peer.view(np.uint32), got.view(np.uint32))
     finally:
         mx.set_option("qmv", "auto")
 
