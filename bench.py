@@ -272,10 +272,12 @@ def run_ours(args, rank, world, local_rank):
         encode_step()
         graph = enc.end_capture()
 
-    def rank_barrier_on_stream(stream):
-        """All ranks' kernels of the step have finished (their peer stores have landed) before anyone goes on."""
-        with torch.cuda.stream(stream):
-            symm["hdl"].barrier()
+    pbar = sharding.PeerBarrier(local_rank) if symm is not None else None
+
+    def rank_barrier_on_stream(stream, e=None):
+        """All ranks' kernels of the step have finished (their peer stores have landed) before anyone goes on: the
+        library's own barrier kernel over a flag array in symmetric memory (bounded wait, plain peer stores)."""
+        pbar.wait(e if e is not None else enc)
 
     def run_step():
         if graph is not None:
@@ -436,7 +438,7 @@ def run_ours(args, rank, world, local_rank):
         else:
             e2e_encode()
         if symm is not None:
-            rank_barrier_on_stream(e2e_stream)
+            rank_barrier_on_stream(e2e_stream, e2e_enc)
         e2e_enc.commit_and_wait()
         acc = 0.0
         for L in launches:
@@ -463,7 +465,7 @@ def run_ours(args, rank, world, local_rank):
     sharded = None
     if world > 1 and not args.no_extra:
         try:
-            sharded = sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream)
+            sharded = sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream, pbar)
         except Exception as ex:  # the headline stands on its own
             sharded = {"error": repr(ex)}
     if rank != 0:
@@ -518,7 +520,7 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-def sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream):
+def sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream, pbar=None):
     """Secondary multi-GPU figures, every rank taking part:
     the expert-sharded MoE FFN layer (128 experts / world per rank, local routing filter, one all-reduce of the
     [T, hidden] partial sums as the combine) and the N-sharded Q6_K lm_head mat-vec (151936 x 5120, m = 1, peer
@@ -606,39 +608,164 @@ def sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream):
                         "combine": "NCCL all-reduce of the [T, hidden] partial sums"}
     out["moe_ffn_layer_expert_sharded"] = moe
 
-    # ---- N-sharded lm_head, Q6_K 151936 x 5120, m = 1
-    n, k, m = 151936, 5120, 1
+    # ---- the same layer with tokens sharded too and all-to-all dispatch / combine (sharding.MoeAllToAll over NCCL):
+    # ---- rank r owns T / world tokens and E / world experts; every (token, slot) row travels to its expert's rank,
+    # ---- is computed there, and travels back unreduced, so the output is bit-identical to the one-GPU layer
     try:
+        a2a = sharding.MoeAllToAll(E, top_k)
+        moe2 = {}
+        for T in (512, 1):
+            logits = rng.standard_normal((T, E)).astype(np.float32)          # same on every rank
+            xfull = rng.standard_normal((T, hidden)).astype(np.float32)
+            t_lo, t_hi = T * rank // world, T * (rank + 1) // world
+            Tl = t_hi - t_lo
+            cap = T * top_k                                                   # every pair could land on one rank
+            tz = lambda *shape, dt=torch.float32: torch.zeros(shape, dtype=dt, device="cuda")
+            wrap = lambda t, dt: dev.wrap_device_memory(t.data_ptr(), max(t.numel(), 1) * t.element_size(), dt)
+            x_t = torch.from_numpy(xfull[t_lo:t_hi].copy()).cuda() if Tl else tz(1, hidden)
+            lg_t = torch.from_numpy(logits[t_lo:t_hi].copy()).cuda() if Tl else tz(1, E)
+            ids_t, rw_t = tz(max(Tl, 1) * top_k, dt=torch.int32), tz(max(Tl, 1) * top_k)
+            rows_t, lids_t = tz(cap, hidden), tz(cap, dt=torch.int32)
+            yg_t, yu_t, act_t, yd_t = tz(cap, ffn), tz(cap, ffn), tz(cap, ffn), tz(cap, hidden)
+            pairs_t, out_t = tz(max(Tl, 1) * top_k, hidden), tz(max(Tl, 1), hidden)
+            lg_b, ids_b, rw_b = wrap(lg_t, mx.DType.F32), wrap(ids_t, mx.DType.U32), wrap(rw_t, mx.DType.F32)
+            rows_b, lids_b = wrap(rows_t, mx.DType.F32), wrap(lids_t, mx.DType.U32)
+            yg_b, yu_b, act_b, yd_b = (wrap(t, mx.DType.F32) for t in (yg_t, yu_t, act_t, yd_t))
+            pairs_b, out_b = wrap(pairs_t, mx.DType.F32), wrap(out_t, mx.DType.F32)
+            scratch = mx.IdMmScratch.alloc(dev, cnt, cap)
+
+            def layer_a2a():
+                if Tl:
+                    mx.moe_softmax_topk(enc, reg, dev, lg_b, ids_b, rw_b, Tl, E, top_k)
+                with torch.cuda.stream(torch.cuda.ExternalStream(enc.stream())):      # joins the encoder's lanes
+                    plan = a2a.plan(ids_t[:Tl * top_k])
+                    rows, lids = a2a.dispatch(plan, x_t[:Tl], rows_t, lids_t)
+                P = rows.shape[0]
+                if P:
+                    pg2 = mx.GgmlQuantizedMatmulIdParams(P, 1, ffn, hidden, cnt, w["gate_stride"], mx.GgmlType.Q4_0)
+                    pd2 = mx.GgmlQuantizedMatmulIdParams(P, 1, hidden, ffn, cnt, w["down_stride"], mx.GgmlType.Q6_K)
+                    mx.quantized_matmul_id_ggml_pooled(enc, reg, dev, rows_b, w["gate"], lids_b, yg_b, scratch, pg2)
+                    mx.quantized_matmul_id_ggml_pooled(enc, reg, dev, rows_b, w["up"], lids_b, yu_b, scratch, pg2)
+                    mx.silu_mul(enc, reg, dev, yg_b, yu_b, act_b, P * ffn)
+                    mx.quantized_matmul_id_ggml_pooled(enc, reg, dev, act_b, w["down"], lids_b, yd_b, scratch, pd2)
+                with torch.cuda.stream(torch.cuda.ExternalStream(enc.stream())):
+                    a2a.combine(plan, yd_t[:P], pairs_t[:Tl * top_k])
+                if Tl:
+                    mx.moe_weighted_reduce(enc, reg, dev, rw_b, pairs_b, out_b, Tl, top_k, hidden)
+
+            sec = timed(layer_a2a)
+            # bit-identity with the one-GPU layer: rank 0 holds every rank's experts and runs the whole layer alone
+            gathered = [torch.empty((T * (r + 1) // world - T * r // world, hidden), dtype=torch.float32, device="cuda")
+                        for r in range(world)]
+            enc.commit_and_wait()
+            torch.cuda.synchronize()
+            dist.all_gather(gathered, out_t[:Tl].contiguous())
+            identical = None
+            if rank == 0:
+                full = {}
+                parts = {"gate": [], "up": [], "down": []}
+                for r in range(world):
+                    rr = np.random.default_rng(100 + r)               # same draw order as when the shards were made
+                    for nm, tt, rws, cls in (("gate", "Q4_0", cnt * ffn, hidden), ("up", "Q4_0", cnt * ffn, hidden),
+                                             ("down", "Q6_K", cnt * hidden, ffn)):
+                        parts[nm].append(random_blocks(rr, tt, rws, cls))
+                for name in parts:
+                    allw = np.concatenate(parts[name])
+                    full[name] = dev.alloc_buffer(allw.size, mx.DType.U8)
+                    full[name].upload(allw)
+                    full[name + "_stride"] = allw.size // E
+                del parts
+                e1 = dev.command_encoder()
+                lg1, x1 = dev.alloc_buffer(logits.nbytes, mx.DType.F32), dev.alloc_buffer(xfull.nbytes, mx.DType.F32)
+                lg1.upload(logits)
+                x1.upload(xfull)
+                ids1, rw1 = dev.alloc_buffer(T * top_k * 4, mx.DType.U32), dev.alloc_buffer(T * top_k * 4, mx.DType.F32)
+                g1, u1, a1 = (dev.alloc_buffer(T * top_k * ffn * 4, mx.DType.F32) for _ in range(3))
+                d1, o1 = dev.alloc_buffer(T * top_k * hidden * 4, mx.DType.F32), dev.alloc_buffer(T * hidden * 4, mx.DType.F32)
+                pg1 = mx.GgmlQuantizedMatmulIdParams(T, top_k, ffn, hidden, E, full["gate_stride"], mx.GgmlType.Q4_0)
+                pd1 = mx.GgmlQuantizedMatmulIdParams(T * top_k, 1, hidden, ffn, E, full["down_stride"], mx.GgmlType.Q6_K)
+                mx.moe_softmax_topk(e1, reg, dev, lg1, ids1, rw1, T, E, top_k)
+                mx.quantized_matmul_id_ggml(e1, reg, dev, x1, full["gate"], ids1, g1, pg1)
+                mx.quantized_matmul_id_ggml(e1, reg, dev, x1, full["up"], ids1, u1, pg1)
+                mx.silu_mul(e1, reg, dev, g1, u1, a1, T * top_k * ffn)
+                mx.quantized_matmul_id_ggml(e1, reg, dev, a1, full["down"], ids1, d1, pd1)
+                mx.moe_weighted_reduce(e1, reg, dev, rw1, d1, o1, T, top_k, hidden)
+                e1.commit_and_wait()
+                want = o1.download(np.float32).reshape(T, hidden)
+                got = torch.cat(gathered, dim=0).cpu().numpy()
+                identical = bool(np.array_equal(got.view(np.uint32), want.view(np.uint32)))
+                if not identical:
+                    raise RuntimeError(f"all-to-all MoE layer (T={T}) is not bit-identical to the one-GPU layer: "
+                                       f"max diff {float(np.max(np.abs(got - want)))}")
+                del full
+            moe2[f"m{T}"] = {"tokens_per_s": T / sec, "ms_per_layer": sec * 1e3, "experts_per_rank": cnt,
+                             "exchange": "NCCL all-to-all dispatch of (row, local expert id) per (token, slot) pair + all-to-all "
+                                         "combine of the unreduced result rows", "bit_identical_to_one_gpu": identical}
+        out["moe_ffn_layer_all_to_all"] = moe2
+    except Exception as ex:
+        out["moe_ffn_layer_all_to_all"] = {"error": repr(ex)}
+        if "bit-identical" in repr(ex):
+            raise
+
+    # ---- N-sharded lm_head, Q6_K 151936 x 5120: m = 1 (mat-vec) and m = 256 (mat-mat); every rank's kernels store their
+    # ---- columns into all ranks' logits (peer stores from the kernels' epilogues) + one cross-rank barrier
+    n, k = 151936, 5120
+    try:
+        from oracle import oracle as orc
+
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm_mem
 
         n_loc = n // world
+        rb = k // 256 * 210
         blk = random_blocks(wrng, "Q6_K", n_loc, k)
         wb = dev.alloc_buffer(blk.size, mx.DType.U8)
         wb.upload(blk)
-        x = rng.standard_normal((m, k)).astype(np.float32)
-        xb = dev.alloc_buffer(x.nbytes, mx.DType.F32, [m, k])
-        xb.upload(x)
-        buf = symm_mem.empty(m * n, dtype=torch.float32, device=f"cuda:{torch.cuda.current_device()}")
-        hdl = symm_mem.rendezvous(buf, dist.group.WORLD)
-        buf.zero_()
-        ptrs = [int(p) for p in hdl.buffer_ptrs]
-        yb = dev.wrap_device_memory(ptrs[rank], m * n * 4, mx.DType.F32, [m, n])
-        peers = [ptrs[r] for r in range(world) if r != rank]
-        prm = mx.GgmlQuantizedMatmulParams(m, n_loc, k, mx.GgmlType.Q6_K)
+        # rows of this rank that the oracle re-computes: first, second and last of the shard
+        mine_rows = [0, 1, n_loc // 2, n_loc - 1]
+        my_w = np.concatenate([blk[r * rb:(r + 1) * rb] for r in mine_rows])
+        all_w = [None] * world
+        dist.all_gather_object(all_w, my_w)
+        chk_rows = [r * n_loc + i for r in range(world) for i in mine_rows]
+        chk_w = np.concatenate(all_w)
+        for m in (1, 256):
+            x = rng.standard_normal((m, k)).astype(np.float32)              # same on every rank
+            xb = dev.alloc_buffer(x.nbytes, mx.DType.F32, [m, k])
+            xb.upload(x)
+            buf = symm_mem.empty(m * n, dtype=torch.float32, device=f"cuda:{torch.cuda.current_device()}")
+            hdl = symm_mem.rendezvous(buf, dist.group.WORLD)
+            buf.zero_()
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            yb = dev.wrap_device_memory(ptrs[rank], m * n * 4, mx.DType.F32, [m, n])
+            peers = [ptrs[r] for r in range(world) if r != rank]
+            prm = mx.GgmlQuantizedMatmulParams(m, n_loc, k, mx.GgmlType.Q6_K)
 
-        def step():
-            mx.quantized_matmul_ggml_sharded(enc, reg, dev, xb, wb, yb, prm, n, rank * n_loc, peers)
-            with torch.cuda.stream(ext_stream):
-                hdl.barrier()
+            if pbar is None:
+                pbar = sharding.PeerBarrier(torch.cuda.current_device())
 
-        sec = timed(step)
-        nz = int((buf != 0).sum().item())
-        out["lm_head_q6k_m1_n_sharded"] = {"us": sec * 1e6, "weight_GBps_all_ranks": n * (k // 256) * 210 / sec / 1e9,
-                                           "logits_filled": nz, "of": m * n,
-                                           "exchange": "peer stores from the mat-vec kernel + one barrier"}
+            def step():
+                mx.quantized_matmul_ggml_sharded(enc, reg, dev, xb, wb, yb, prm, n, rank * n_loc, peers)
+                pbar.wait(enc)
+
+            sec = timed(step)
+            got = buf.view(m, n)[:, chk_rows].cpu().numpy()
+            ref, ad = orc.qmatmul(orc.Q6_K, chk_w, x, len(chk_rows), k, nthreads=4)
+            err = float(np.max(np.abs(got.astype(np.float64) - ref) / np.maximum(ad, 1e-30)))
+            tol = 1e-5 if m <= 8 else 2e-3
+            if not err <= tol:
+                raise RuntimeError(f"rank {rank}: sharded lm_head m={m} differs from the oracle: normalised error {err:.3e}")
+            sent = m * n_loc * 4 * (world - 1)                                # bytes this rank stores to its peers
+            out[f"lm_head_q6k_m{m}_n_sharded"] = {
+                "us": sec * 1e6, "weight_GBps_all_ranks": n * rb / sec / 1e9, "tflops_all_ranks": 2.0 * m * n * k / sec / 1e12,
+                "kernel": mx.last_kernel_name(), "oracle_norm_err": err,
+                "nvlink_out_GBps_per_gpu": sent / sec / 1e9, "nvlink_frac_of_measured_770": sent / sec / 1e9 / 770.0,
+                "nvlink_frac_of_nominal_900": sent / sec / 1e9 / 900.0,
+                "exchange": "peer stores from the kernel epilogues + one barrier"}
+            del buf, hdl
     except Exception as ex:
-        out["lm_head_q6k_m1_n_sharded"] = {"error": repr(ex)}
+        out["lm_head_q6k_n_sharded"] = {"error": repr(ex)}
+        if "differs from the oracle" in repr(ex):
+            raise
     return out
 
 

@@ -290,16 +290,28 @@ size_t mlxn_noalloc_scratch_limit(void);
 int mlxn_quantized_matmul_ggml_mm_noalloc(void *cuda_stream, const void *input_dev, const void *weight_dev,
                                           void *output_dev, const mlxn_qmm_params *params);
 
-/* Row-sharded mat-vec for tensor parallelism (m <= 8; no upstream counterpart: upstream is single-GPU).  This
- * rank holds params->n of the n_total weight rows, rows [col0, col0 + n) of the full matrix.  `output` is this
- * rank's full result buffer, f32 [m, n_total]; the kernel stores its columns there AND at the same place in the
- * other ranks' result buffers (`peer_outputs`: device addresses mapped into this process, e.g. CUDA IPC or
- * symmetric memory; at most 7), so that every rank holds the whole result once all ranks' kernels have finished,
- * without a collective launch.  The caller orders ranks (a barrier between this call and the first use of the
- * full result, and between that use and the next call that writes the buffers). */
+/* Row-sharded matmul for tensor parallelism (no upstream counterpart: upstream is single-GPU).  This rank holds
+ * params->n of the n_total weight rows, rows [col0, col0 + n) of the full matrix.  `output` is this rank's full
+ * result buffer, f32 [m, n_total]; the kernels store their columns there AND at the same place in the other ranks'
+ * result buffers (`peer_outputs`: device addresses mapped into this process, e.g. CUDA IPC or symmetric memory; at
+ * most 7), so that every rank holds the whole result once all ranks' kernels have finished, without a collective
+ * launch.  m <= 8 takes the mat-vec kernels (the register-level one stores to the peers from its own epilogue: one
+ * launch per call), larger m the tensor-core mat-mat, whose epilogue sends each finished tile to the peers while the
+ * other tiles are still being computed.  The caller orders ranks (a barrier between this call and the first use of
+ * the full result, and between that use and the next call that writes the buffers). */
 int mlxn_quantized_matmul_ggml_sharded(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
                                        mlxn_buffer *weight, mlxn_buffer *output, const mlxn_qmm_params *params,
                                        uint32_t n_total, uint32_t col0, void *const *peer_outputs, uint32_t n_peers);
+
+/* Cross-rank barrier for the row-sharded and expert-sharded forms (one process per GPU; no upstream counterpart).
+ * Every rank owns a zero-initialised flag array uint32[world] in memory its peers can store to (symmetric or IPC
+ * memory); flag_ptrs[r] is rank r's array as mapped into this process.  The call enqueues, behind everything encoded
+ * so far, a kernel that publishes `epoch` (which the caller raises by one per barrier) to every rank and waits until
+ * every rank's epoch has arrived here: what the ranks stored to one another before the barrier is visible after it.
+ * The wait is bounded by `limit_us` (1..10000000): when it runs out the next commit reports MLXN_COMMAND_BUFFER_ERROR
+ * ("gave up waiting for another rank") and the GPU stays usable.  world <= 32.  Plain peer loads and stores only. */
+int mlxn_peer_barrier(mlxn_encoder *enc, uint32_t rank, uint32_t world, void *const *flag_ptrs, uint32_t epoch,
+                      uint32_t limit_us);
 
 /* ---- tuning and introspection (no upstream counterpart) -------------------------------------- */
 /* Selects kernel variants for cross-checks: key/value pairs

@@ -110,6 +110,7 @@ SIGNATURES = {
     "mlxn_moe_expert_shard_route": (i32, [vp, vp, vp, vp, vp, u32, u32, u32]),
     "mlxn_noalloc_scratch_limit": (sz, []),
     "mlxn_quantized_matmul_ggml_mm_noalloc": (i32, [vp, vp, vp, vp, C.POINTER(QmmParams)]),
+    "mlxn_peer_barrier": (i32, [vp, u32, u32, C.POINTER(C.c_void_p), u32, u32]),
     "mlxn_set_option": (i32, [C.c_char_p, C.c_char_p]),
     "mlxn_debug_wait_probe": (i32, [vp, u32]),
     "mlxn_last_kernel_name": (C.c_char_p, []),

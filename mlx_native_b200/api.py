@@ -475,6 +475,13 @@ def last_kernel_name() -> str:
     return _native.lib().mlxn_last_kernel_name().decode()
 
 
+def peer_barrier(encoder: "CommandEncoder", rank: int, world: int, flag_ptrs, epoch: int, limit_us: int = 2000000) -> None:
+    """Cross-rank barrier over peer memory (see mlxn_peer_barrier): flag_ptrs[r] = device address of rank r's flag array
+    (uint32[world], zero-initialised) as mapped into this process; `epoch` grows by one per barrier."""
+    arr = (C.c_void_p * world)(*[C.c_void_p(int(p)) for p in flag_ptrs])
+    _check(_native.lib().mlxn_peer_barrier(encoder._h, rank, world, arr, epoch & 0xFFFFFFFF, limit_us))
+
+
 def profile_cb_get(label: str) -> tuple[int, int]:
     """(command buffers, device nanoseconds) recorded under `label` while MLX_PROFILE_CB=1 (src/kernel_profile.rs)."""
     n, ns = C.c_uint64(), C.c_uint64()

@@ -50,7 +50,7 @@ __host__ __device__ inline uint32_t ggml_block_bytes(int t) {
 
 // Device status word written by kernels whose bounded waits gave up.  0 = ok.
 enum : uint32_t { ST_OK = 0, ST_WAIT_FULL_TIMEOUT = 1, ST_WAIT_EMPTY_TIMEOUT = 2, ST_WAIT_MMA_TIMEOUT = 3,
-                  ST_WAIT_TMEM_TIMEOUT = 4, ST_BAD_ARGUMENT = 5 };
+                  ST_WAIT_TMEM_TIMEOUT = 4, ST_BAD_ARGUMENT = 5, ST_WAIT_PEER_TIMEOUT = 6 };
 
 // Arguments shared by the mat-vec kernels (dense and expert-routed).
 struct QmvArgs {
@@ -94,7 +94,13 @@ struct QmmArgs {
     uint64_t expert_stride;
     const uint32_t *tiles;   // optional compact tile list built by the bucketing kernel
     uint32_t *status;
+    // Row-sharded dense form (tensor-core kernel only): this rank holds n of the y_ld weight rows; output row o lives
+    // at y[o * y_ld + y_col0 ..] and every finished tile is also stored to the same place in the other ranks' result
+    // buffers (peer memory), as for the mat-vec (see QmvArgs).  y_ld == 0: a plain [m, n] result.
+    uint32_t y_ld, y_col0, n_peer;
+    float *y_peer[7];
 };
+__host__ __device__ inline uint32_t qmm_ld(const QmmArgs &a) { return a.y_ld ? a.y_ld : a.n; }
 
 // ---- overlapped launches -------------------------------------------------------------------------
 // A kernel launched with launch_overlapped may be scheduled while the kernel ahead of it in the stream is still

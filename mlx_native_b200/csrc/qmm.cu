@@ -1004,13 +1004,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                         const int32_t o = tab[r];
                         if (o < 0) continue;
                         const float4 val = *reinterpret_cast<const float4 *>(stg + r * kPitch + 4 * lane);
-                        float *dst = a.y + (size_t)o * a.n + c4;
+                        const size_t off = (size_t)o * qmm_ld(a) + a.y_col0 + c4;
+                        float *dst = a.y + off;
                         if (c4 + 3 < a.n) {
                             *reinterpret_cast<float4 *>(dst) = val;
+                            for (uint32_t pr = 0; pr < a.n_peer; pr++) *reinterpret_cast<float4 *>(a.y_peer[pr] + off) = val;
                         } else {
                             if (c4 < a.n) dst[0] = val.x;
                             if (c4 + 1 < a.n) dst[1] = val.y;
                             if (c4 + 2 < a.n) dst[2] = val.z;
+                            for (uint32_t pr = 0; pr < a.n_peer; pr++) {
+                                float *pd = a.y_peer[pr] + off;
+                                if (c4 < a.n) pd[0] = val.x;
+                                if (c4 + 1 < a.n) pd[1] = val.y;
+                                if (c4 + 2 < a.n) pd[2] = val.z;
+                            }
                         }
                     }
                 }
@@ -1035,7 +1043,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                         const int32_t o = tab[col + j];
                         if (o >= 0) {
                             if (c.ksplit > 1) atomicAdd(&a.y[(size_t)o * a.n + wrow], __uint_as_float(v[j]));
-                            else a.y[(size_t)o * a.n + wrow] = __uint_as_float(v[j]);
+                            else {
+                                const size_t off = (size_t)o * qmm_ld(a) + a.y_col0 + wrow;
+                                a.y[off] = __uint_as_float(v[j]);
+                                for (uint32_t pr = 0; pr < a.n_peer; pr++) a.y_peer[pr][off] = __uint_as_float(v[j]);
+                            }
                         }
                     }
                 }
@@ -1172,8 +1184,11 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     uint32_t limit = 222 * 1024;  // + 1 KB alignment slack + ~3 KB of static shared memory <= 227 KB
     // narrow tiles stage their result in shared memory (two tiles of NT x 132 floats) and write whole output rows
     const uint32_t stage_bytes = 2u * NT * (kTcRowsW + 4) * 4u;
-    const bool staged = NT == 64 && qmm_tc_ksplit(NT, a.m, a.n, a.k, sm_count_of_device(), routed) == 1 &&
-                        ((((uintptr_t)a.y) | ((uintptr_t)a.n * 4u)) & 15u) == 0 && !getenv("MLXN_TC_NO_STAGED_OUT");
+    // (the row-sharded form never splits K: its tiles go straight to every rank's buffer)
+    const bool sharded = a.y_ld != 0 || a.n_peer != 0;
+    const bool staged = NT == 64 && (sharded || qmm_tc_ksplit(NT, a.m, a.n, a.k, sm_count_of_device(), routed) == 1) &&
+                        ((((uintptr_t)a.y) | ((uintptr_t)qmm_ld(a) * 4u) | ((uintptr_t)a.y_col0 * 4u)) & 15u) == 0 && a.n_peer == 0 &&
+                        !getenv("MLXN_TC_NO_STAGED_OUT");
     if (staged) limit -= stage_bytes;
     // activation ring first (at least two raw slots kept back), the rest goes to the raw weight ring
     uint32_t b_stages = (limit - 2 * raw_slot) / b_bytes;
@@ -1197,7 +1212,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     if (staged) c.stage_off = c.raw_off + raw_bytes;
     const size_t smem = (size_t)c.raw_off + raw_bytes + (staged ? stage_bytes : 0u) + 1024;  // + slack for manual 1024-byte alignment
 
-    const uint32_t ksplit = qmm_tc_ksplit(NT, a.m, a.n, a.k, sm_count_of_device(), routed);
+    const uint32_t ksplit = sharded ? 1u : qmm_tc_ksplit(NT, a.m, a.n, a.k, sm_count_of_device(), routed);
     size_t tiles;
     uint8_t *xpack = scratch;
     if (routed) {

@@ -54,7 +54,7 @@ template <> struct MwTraits<GT_Q6_K> { static constexpr int UK = 512, UBYTES = 4
 // so that the 32-bit reads of eight consecutive rows fall into distinct banks.
 __host__ __device__ constexpr uint32_t mw_pitch(int ggml_type, int kb) {
     const uint32_t raw = (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : 420u) * (uint32_t)kb;
-    const uint32_t lead = ggml_type == GT_Q6_K ? (kb == 1 ? 12u : kb == 2 ? 8u : 0u) : 0u;
+    const uint32_t lead = ggml_type == GT_Q6_K ? (kb == 1 ? 12u : 8u) : 0u;
     const uint32_t c = (raw + lead + 15u) / 16u;
     return 16u * (c | 1u);
 }
@@ -71,13 +71,13 @@ struct MwProb {
     uint32_t spi;         // stages per item = k / (KB * UK)
     uint32_t item0;       // index of the problem's first item in the launch's item list
     uint32_t y_ld, y_col0;
+    uint32_t n_peer;      // row-sharded form (see QmvArgs): the other ranks' result buffers
+    float *y_peer[kMaxPeers];
 };
 struct MwBatch {
     MwProb p[kMwMaxProbs];
     uint32_t nprob;
     uint32_t early_weights;   // no problem's weights were written by a kernel of this process (see QmvArgs)
-    uint32_t n_peer;          // row-sharded form, single problem only (see QmvArgs)
-    float *y_peer[kMaxPeers];
     uint32_t *status;
     // CTA c works on items [cta_begin[c], cta_begin[c + 1]): contiguous chunks of (nearly) equal numbers of stages
     uint32_t cta_begin[kMwMaxGrid + 1];
@@ -224,7 +224,11 @@ __device__ __forceinline__ void mw_block_tiles(uint32_t pd, uint32_t pa, uint32_
 }
 
 // TPW: 16-row tiles per warp.  KB: units per warp and stage.  MP: activation rows carried (1, 2, 4 or 8, >= m).
-template <int T, int TPW, int KB, int MP>
+// PAIR (Q6_K rows of 16 j + 8 bytes, e.g. k = 5120: only every other row starts on a 16-byte boundary): the tensor
+// map's rows are PAIRS of weight rows; a stage is two copies of R / 2 map rows, the even weight rows into stage rows
+// [0, R / 2) and the odd ones into [R / 2, R), each from the 16-byte boundary below its first byte (the odd rows'
+// data therefore starts 8 bytes further into its chunk than the even rows').
+template <int T, int TPW, int KB, int MP, bool PAIR>
 __global__ void __launch_bounds__(kMwThreads, 2)
     qmv_mma_kernel(const __grid_constant__ MwBatch bt, const MwCfg c, const __grid_constant__ MwMaps maps) {
     using TR = MwTraits<T>;
@@ -290,11 +294,25 @@ __global__ void __launch_bounds__(kMwThreads, 2)
 #endif
                     mbar_expect_tx(&full[slot], STAGE);
                     // coordinates in 8-byte elements; rows past n and bytes past the end of a row arrive as zeros
-                    const uint32_t x0 = ((s * SBYTES) & ~15u) >> 3;
-                    asm volatile(
-                        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                        ::"r"(smem_base + slot * STAGE), "l"(&maps.m[p]), "r"(x0), "r"(item * (uint32_t)R), "r"(smem_u32(&full[slot]))
-                        : "memory");
+                    if constexpr (PAIR) {
+                        const uint32_t row_bytes = (bt.p[p].k / 256u) * 210u;
+                        const uint32_t xe = ((s * SBYTES) & ~15u) >> 3, xo = ((row_bytes + s * SBYTES) & ~15u) >> 3;
+                        asm volatile(
+                            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                            ::"r"(smem_base + slot * STAGE), "l"(&maps.m[p]), "r"(xe), "r"(item * (uint32_t)(R / 2)), "r"(smem_u32(&full[slot]))
+                            : "memory");
+                        asm volatile(
+                            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                            ::"r"(smem_base + slot * STAGE + (R / 2) * PITCH), "l"(&maps.m[p]), "r"(xo), "r"(item * (uint32_t)(R / 2)),
+                              "r"(smem_u32(&full[slot]))
+                            : "memory");
+                    } else {
+                        const uint32_t x0 = ((s * SBYTES) & ~15u) >> 3;
+                        asm volatile(
+                            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                            ::"r"(smem_base + slot * STAGE), "l"(&maps.m[p]), "r"(x0), "r"(item * (uint32_t)R), "r"(smem_u32(&full[slot]))
+                            : "memory");
+                    }
                     if (++slot == c.nslots) { slot = 0; ph ^= 1u; }
                 }
             }
@@ -460,7 +478,9 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                         for (int rr = 0; rr < (R + 31) / 32; rr++) {
                             const uint32_t r = lane + 32 * rr;
                             if (r < (uint32_t)R) {
-                                const uint32_t rb = stage + r * PITCH + lead + 210 * (sp + 2 * i);
+                                // (pair mode: logical row r sits in stage row (r & 1) R / 2 + r / 2, odd rows 8 bytes further in)
+                                const uint32_t rb = PAIR ? stage + ((r & 1u) * (R / 2) + (r >> 1)) * PITCH + (lead ^ (8u * (r & 1u))) + 210 * (sp + 2 * i)
+                                                         : stage + r * PITCH + lead + 210 * (sp + 2 * i);
                                 const float d = half_bits_to_float(lds_u16(rb + 208));
                                 float p[4];
 #pragma unroll
@@ -508,7 +528,8 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                     if constexpr (T == GT_Q6_K) {
                         // row g of the stage, this unit's super-block; odd super-blocks start 2 bytes past a 4-byte boundary:
                         // their words are read from the 4-byte boundary below and shifted by a byte permute
-                        const uint32_t u6 = stage + g * PITCH + lead + 210 * (sp + 2 * i) - 2 * sp;
+                        const uint32_t u6 = (PAIR ? stage + ((g & 1u) * (R / 2) + (g >> 1)) * PITCH + (lead ^ (8u * (g & 1u)))
+                                                  : stage + g * PITCH + lead) + 210 * (sp + 2 * i) - 2 * sp;
                         const uint32_t pA = u6 + q6A, pH = u6 + q6H, pP = ptab + (i * R + g) * 16;
 #pragma unroll
                         for (int j = 0; j < TPW; j++) {
@@ -516,7 +537,7 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                             uint32_t pv[2][4];
 #pragma unroll
                             for (int h = 0; h < 2; h++) {
-                                const uint32_t off = (16 * j + 8 * h) * PITCH;
+                                const uint32_t off = (PAIR ? 8 * j + 4 * h : 16 * j + 8 * h) * PITCH;   // rows g, g + 8 of tile j
                                 uint32_t A, B, H;
                                 if (sp == 0) {
                                     A = lds32(pA + off);
@@ -596,7 +617,7 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                     if (grow < P.n) {
                         const size_t off = (size_t)col * ld + P.y_col0 + grow;
                         P.y[off] = sum;
-                        for (uint32_t pr = 0; pr < bt.n_peer; pr++) bt.y_peer[pr][off] = sum;
+                        for (uint32_t pr = 0; pr < P.n_peer; pr++) P.y_peer[pr][off] = sum;
                     }
                 }
             }
@@ -616,12 +637,19 @@ __global__ void __launch_bounds__(kMwThreads, 2)
 // ------------------------------------------------------------------------------------------------
 static uint32_t mw_uk(int t) { return t == GT_Q6_K ? 512u : 256u; }
 
+// Q6_K rows of 16 j + 8 bytes with an even row count: pairs of rows start on 16-byte boundaries (see PAIR above)
+bool qmv_mma_pair_mode(int ggml_type, const QmvArgs &a) {
+    if (ggml_type != GT_Q6_K || a.k % 256 != 0) return false;
+    const uint64_t row_bytes = (uint64_t)(a.k / 256) * 210;
+    return row_bytes % 16 == 8 && a.n % 2 == 0;
+}
+
 bool qmv_mma_supported(int ggml_type, const QmvArgs &a) {
     if (ggml_type != GT_Q4_0 && ggml_type != GT_Q8_0 && ggml_type != GT_Q6_K) return false;
     if (a.ids || a.nprob != 1 || a.m < 1 || a.m > 8) return false;
     if (a.k == 0 || a.n == 0 || a.k % mw_uk(ggml_type) != 0) return false;
     const uint64_t row_bytes = (uint64_t)(a.k / ggml_qk(ggml_type)) * ggml_block_bytes(ggml_type);
-    if (row_bytes % 16 != 0 || row_bytes >= (1ull << 32)) return false;
+    if ((row_bytes % 16 != 0 && !qmv_mma_pair_mode(ggml_type, a)) || row_bytes >= (1ull << 31)) return false;
     if (((uintptr_t)a.w & 15u) || ((uintptr_t)a.x & 15u)) return false;
     if ((uint64_t)a.m * a.n >= (1ull << 32)) return false;
     return encode_tiled_fn() != nullptr;
@@ -629,7 +657,7 @@ bool qmv_mma_supported(int ggml_type, const QmvArgs &a) {
 
 static inline size_t mw_align(size_t v, size_t al) { return (v + al - 1) / al * al; }
 
-template <int T, int TPW, int KB, int MP>
+template <int T, int TPW, int KB, int MP, bool PAIR>
 static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, cudaStream_t st) {
     using TR = MwTraits<T>;
     constexpr uint32_t R = 16 * TPW, PITCH = mw_pitch(T, KB), STAGE = R * PITCH;
@@ -660,8 +688,6 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
     alignas(64) static thread_local MwMaps maps;
     bt.nprob = (uint32_t)nops;
     bt.early_weights = 1;
-    bt.n_peer = nops == 1 ? ops[0].n_peer : 0;
-    for (uint32_t i = 0; i < bt.n_peer; i++) bt.y_peer[i] = ops[0].y_peer[i];
     bt.status = ops[0].status;
     uint64_t total_stages = 0;
     uint32_t items = 0;
@@ -677,15 +703,18 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
         P.item0 = items;
         P.y_ld = a.y_ld;
         P.y_col0 = a.y_col0;
+        P.n_peer = a.n_peer;
+        for (uint32_t q = 0; q < (uint32_t)kMaxPeers; q++) P.y_peer[q] = q < a.n_peer ? a.y_peer[q] : nullptr;
         const uint32_t its = (a.n + R - 1) / R;
         items += its;
         total_stages += (uint64_t)its * P.spi;
         if (!a.early_weights) bt.early_weights = 0;
         const uint32_t row_bytes = (a.k / BlockTraits<T>::QK) * BlockTraits<T>::BYTES;
         // the weight matrix as [n rows][row_bytes / 8] 8-byte elements; box = R rows x PITCH bytes
-        const cuuint64_t gdim[2] = {row_bytes / 8, a.n};
-        const cuuint64_t gstride[1] = {row_bytes};
-        const cuuint32_t box[2] = {(cuuint32_t)(PITCH / 8), (cuuint32_t)R};
+        // (pair mode: [n / 2 row pairs][2 row_bytes / 8], box = R / 2 pairs x PITCH bytes)
+        const cuuint64_t gdim[2] = {PAIR ? row_bytes / 4 : row_bytes / 8, PAIR ? a.n / 2 : a.n};
+        const cuuint64_t gstride[1] = {PAIR ? 2ull * row_bytes : row_bytes};
+        const cuuint32_t box[2] = {(cuuint32_t)(PITCH / 8), (cuuint32_t)(PAIR ? R / 2 : R)};
         const cuuint32_t estr[2] = {1, 1};
         if (enc(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(a.w), gdim, gstride, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -727,36 +756,48 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (smem > attr_smem[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(qmv_mma_kernel<T, TPW, KB, MP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(qmv_mma_kernel<T, TPW, KB, MP, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         attr_smem[dev] = smem;
     }
-    return launch_overlapped(qmv_mma_kernel<T, TPW, KB, MP>, dim3(grid), dim3(kMwThreads), smem, st, bt, c, maps);
+    return launch_overlapped(qmv_mma_kernel<T, TPW, KB, MP, PAIR>, dim3(grid), dim3(kMwThreads), smem, st, bt, c, maps);
 }
 
 // (TPW, KB): a warp works on TPW x KB tile-units per stage.  Few weight rows -> narrow row groups and long K stages.
 // The activation split costs MP x KB per stage and warp whatever TPW is, so many activation rows want KB = 1.
-template <int T, int MP>
+template <int T, int MP, bool PAIR>
 static cudaError_t launch_mw_m(const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
     uint32_t units_gcd = 4;   // KB must divide every problem's number of K units
     for (int i = 0; i < nops; i++) {
         const uint32_t u = ops[i].k / MwTraits<T>::UK;
         if (u % 4 != 0) units_gcd = u % 2 == 0 ? (units_gcd < 2 ? units_gcd : 2) : 1;
     }
-    if (tpw >= 4 || MP == 8 || units_gcd < 2) return launch_mw<T, 4, 1, MP>(ops, nops, sm_count, ctas_per_sm, st);
+    if (tpw >= 4 || MP == 8 || units_gcd < 2) return launch_mw<T, 4, 1, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
     if constexpr (MP <= 4) {
-        if (tpw >= 2 || MP == 4 || units_gcd < 4) return launch_mw<T, 2, 2, MP>(ops, nops, sm_count, ctas_per_sm, st);
+        if (tpw >= 2 || MP == 4 || units_gcd < 4) return launch_mw<T, 2, 2, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
     }
-    if constexpr (MP <= 2) return launch_mw<T, 1, 4, MP>(ops, nops, sm_count, ctas_per_sm, st);
+    if constexpr (MP <= 2) return launch_mw<T, 1, 4, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
     return cudaErrorInvalidConfiguration;
+}
+
+template <int T, bool PAIR>
+static cudaError_t launch_mw_p(const QmvArgs *ops, int nops, uint32_t mmax, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
+    if (mmax <= 1) return launch_mw_m<T, 1, PAIR>(ops, nops, sm_count, ctas_per_sm, tpw, st);
+    if (mmax <= 2) return launch_mw_m<T, 2, PAIR>(ops, nops, sm_count, ctas_per_sm, tpw, st);
+    if (mmax <= 4) return launch_mw_m<T, 4, PAIR>(ops, nops, sm_count, ctas_per_sm, tpw, st);
+    return launch_mw_m<T, 8, PAIR>(ops, nops, sm_count, ctas_per_sm, tpw, st);
 }
 
 template <int T>
 static cudaError_t launch_mw_t(const QmvArgs *ops, int nops, uint32_t mmax, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
-    if (mmax <= 1) return launch_mw_m<T, 1>(ops, nops, sm_count, ctas_per_sm, tpw, st);
-    if (mmax <= 2) return launch_mw_m<T, 2>(ops, nops, sm_count, ctas_per_sm, tpw, st);
-    if (mmax <= 4) return launch_mw_m<T, 4>(ops, nops, sm_count, ctas_per_sm, tpw, st);
-    return launch_mw_m<T, 8>(ops, nops, sm_count, ctas_per_sm, tpw, st);
+    if constexpr (T == GT_Q6_K) {
+        // all or none of a launch's mat-vecs are in pair mode (the caller batches accordingly)
+        const bool pair = qmv_mma_pair_mode(T, ops[0]);
+        for (int i = 1; i < nops; i++)
+            if (qmv_mma_pair_mode(T, ops[i]) != pair) return cudaErrorInvalidValue;
+        if (pair) return launch_mw_p<T, true>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
+    }
+    return launch_mw_p<T, false>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
 }
 
 // Launches `nops` (1..8) mat-vecs of one block type as ONE kernel.  The caller guarantees that no operation reads or

@@ -29,6 +29,7 @@ size_t qmv_tc_scratch_bytes(const QmvArgs &a);
 cudaError_t launch_qmv_tc(int ggml_type, const QmvArgs &a, uint8_t *scratch, uint32_t *flags, int sm_count, cudaStream_t st,
                           cudaStream_t pub_st, cudaEvent_t pub_ev, int *launches);
 bool qmv_mma_supported(int ggml_type, const QmvArgs &a);
+bool qmv_mma_pair_mode(int ggml_type, const QmvArgs &a);
 cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st);
 cudaError_t launch_qmm_tc(int ggml_type, const QmmArgs &a, bool routed, uint32_t nt, uint8_t *scratch, cudaStream_t st,
                           int *launches);
@@ -275,6 +276,7 @@ struct mlxn_encoder {
     std::vector<QmvArgs> pend;
     int pend_type = 0, pend_lane = 0;
     uint32_t pend_mp = 0;
+    bool pend_pair = false;
     uint32_t *status_host = nullptr;  // pinned
 };
 
@@ -876,7 +878,12 @@ static int encoder_flush_pending(mlxn_encoder *e) {
     const bool lone_other = e->pend.size() == 1 && opt_qmv() == 3 && a0.n_peer == 0 &&
                             (e->pend_type == GT_Q6_K || a0.m > 2);
     if (lone_other) {
-        if (!(e->pend_type == GT_Q6_K && a0.m == 1) && qmv_tc_supported(e->pend_type, a0)) {
+        // (one Q6_K row: the streaming kernel, except on matrices so large that the launch overhead no longer shows)
+        const bool q6_one_row_small = e->pend_type == GT_Q6_K && a0.m == 1 && (uint64_t)a0.n * a0.k < (1ull << 27);
+        const bool q6_one_row_large = e->pend_type == GT_Q6_K && a0.m == 1 && !q6_one_row_small;
+        if (q6_one_row_large) {
+            err = launch_qmv_mma(e->pend_type, &a0, 1, e->dev->sm_count, g_opt_mma_ctas.load(), g_opt_mma_tpw.load(), st);
+        } else if (!q6_one_row_small && qmv_tc_supported(e->pend_type, a0)) {
             uint8_t *scratch = nullptr;
             if ((rc = encoder_scratch_on(e, e->pend_lane, qmv_tc_scratch_bytes(a0), &scratch)) == MLXN_OK) {
                 launches = 0;
@@ -976,6 +983,7 @@ static const char *status_text(uint32_t s) {
     case ST_WAIT_EMPTY_TIMEOUT: return "a kernel gave up waiting for a pipeline stage to be released";
     case ST_WAIT_MMA_TIMEOUT: return "a kernel gave up waiting for the tensor cores";
     case ST_WAIT_TMEM_TIMEOUT: return "a kernel gave up waiting for tensor memory";
+    case ST_WAIT_PEER_TIMEOUT: return "a kernel gave up waiting for another rank at a barrier";
     default: return "a kernel reported an error";
     }
 }
@@ -1359,6 +1367,63 @@ extern "C" int mlxn_debug_wait_probe(mlxn_encoder *enc, uint32_t limit_us) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// cross-rank barrier over peer memory (one process per GPU; no counterpart in the reference)
+// ------------------------------------------------------------------------------------------------
+// Every rank owns a flag array uint32[world] that the other ranks can store to (symmetric / IPC memory).  Thread r of
+// the one-CTA kernel publishes this rank's epoch in rank r's array (slot = this rank) behind a system-wide fence, so
+// that everything this GPU stored to its peers before the barrier is visible to whoever sees the flag, and then waits
+// until rank r's epoch has arrived in its own array.  The wait is bounded: when it runs out the kernel records
+// ST_WAIT_PEER_TIMEOUT and returns, and the next commit reports CommandBufferError (a rank that never arrives must not
+// hang the others' GPUs).  Plain loads and stores only: no multicast, so a rank that dies leaves nothing bound.
+struct PeerFlags {
+    uint32_t *p[32];
+};
+__global__ void peer_barrier_kernel(uint32_t rank, uint32_t world, const PeerFlags flags, uint32_t epoch, uint64_t limit_ns,
+                                    uint32_t *status) {
+    const uint32_t r = threadIdx.x;
+    if (r >= world) return;
+    __threadfence_system();
+    volatile uint32_t *theirs = flags.p[r] + rank;
+    *theirs = epoch;
+    __threadfence_system();
+    volatile uint32_t *mine = flags.p[rank] + r;
+    const uint64_t t0 = mlxn::global_timer_ns();
+    for (uint32_t polls = 0;; polls++) {
+        // epochs only grow; a difference in the upper half of the range means "not yet" (wrap-around safe)
+        if ((int32_t)(*mine - epoch) >= 0) break;
+        if ((polls & 63u) == 63u && mlxn::global_timer_ns() - t0 > limit_ns) {
+            if (status) atomicCAS(status, 0u, (uint32_t)mlxn::ST_WAIT_PEER_TIMEOUT);
+            break;
+        }
+        __nanosleep(100);
+    }
+    __threadfence_system();
+}
+
+// `flag_ptrs`: host array of `world` device addresses, entry r = rank r's flag array as mapped into this process.
+extern "C" int mlxn_peer_barrier(mlxn_encoder *enc, uint32_t rank, uint32_t world, void *const *flag_ptrs, uint32_t epoch,
+                                 uint32_t limit_us) {
+    if (!enc || !flag_ptrs) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: encoder and flag pointers must not be null");
+    if (world == 0 || world > 32 || rank >= world)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: peer barrier: rank %u of %u ranks (1..32)", rank, world);
+    if (limit_us == 0 || limit_us > 10000000)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: peer barrier: wait limit (%u us) must be in 1..10000000", limit_us);
+    for (uint32_t r = 0; r < world; r++)
+        if (!flag_ptrs[r] || ((uintptr_t)flag_ptrs[r] & 3u))
+            return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: peer barrier: flag array %u is null or misaligned", r);
+    int rc = encoder_begin_work(enc);
+    if (rc) return rc;
+    if ((rc = encoder_join_lanes(enc))) return rc;   // everything encoded so far is ahead of the barrier
+    PeerFlags table{};
+    for (uint32_t r = 0; r < world; r++) table.p[r] = static_cast<uint32_t *>(flag_ptrs[r]);
+    peer_barrier_kernel<<<1, 32, 0, enc->lanes[0]>>>(rank, world, table, epoch, (uint64_t)limit_us * 1000ull, enc->status_dev);
+    CUDA_TRY(cudaGetLastError(), "peer barrier launch");
+    g_launches.fetch_add(1);
+    g_barrier.fetch_add(1);
+    return MLXN_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
 // quantized_matmul_ggml
 // ------------------------------------------------------------------------------------------------
 static const char *mv_kernel_name(int t) {
@@ -1432,15 +1497,17 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
     if (p->m <= 8) {
         const QmvArgs a0 = make_args(0);
         if (wants_mma(a0) && qmv_mma_supported((int)p->ggml_type, a0)) {
-            const bool batch = g_opt_mv_batch.load() != 0 && !sh;
+            const bool batch = g_opt_mv_batch.load() != 0;
+            const bool pair = qmv_mma_pair_mode((int)p->ggml_type, a0);
             const bool fits = batch && !enc->pend.empty() && enc->pend_type == (int)p->ggml_type &&
-                              enc->pend_mp == mv_row_class(a0.m) && enc->pend.size() < 8;
+                              enc->pend_mp == mv_row_class(a0.m) && enc->pend_pair == pair && enc->pend.size() < 8;
             if (!enc->pend.empty() && !fits && (rc = encoder_flush_pending(enc))) return rc;
             if ((rc = op_begin(enc, {{input, false}, {weight, false}, {output, true}}, true))) return rc;
             // (a conflict found by op_begin has launched the batch and started a new group)
             if (enc->pend.empty()) {
                 enc->pend_type = (int)p->ggml_type;
                 enc->pend_mp = mv_row_class(a0.m);
+                enc->pend_pair = pair;
                 enc->pend_lane = enc->cur_lane;
             }
             enc->pend.push_back(a0);
@@ -1491,7 +1558,7 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
 }
 
 static int dispatch_mm(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input, mlxn_buffer *weight,
-                       mlxn_buffer *output, const mlxn_qmm_params *p) {
+                       mlxn_buffer *output, const mlxn_qmm_params *p, const ShardOut *sh = nullptr) {
     int rc = touch_kernel(reg, dev, mm_kernel_name((int)p->ggml_type));
     if (rc) return rc;
     if ((rc = op_begin(enc, {{input, false}, {weight, false}, {output, true}}))) return rc;
@@ -1506,7 +1573,15 @@ static int dispatch_mm(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
     a.n_experts = 1;
     a.total_rows = p->m;
     a.status = enc->status_dev;
-    if (opt_qmm_tc() && qmm_tc_supported(a)) {
+    if (sh) {
+        a.y_ld = sh->y_ld;
+        a.y_col0 = sh->y_col0;
+        a.n_peer = sh->n_peer;
+        for (uint32_t i = 0; i < sh->n_peer; i++) a.y_peer[i] = sh->peer[i];
+        if (!qmm_tc_supported(a))
+            return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_sharded: the mat-mat form needs K to be a multiple of 32");
+    }
+    if ((sh || opt_qmm_tc()) && qmm_tc_supported(a)) {
         const uint32_t nt = qmm_tc_pick_nt((int)p->ggml_type, p->m, p->n, dev->sm_count, false);
         uint8_t *scratch = nullptr;
         if ((rc = encoder_scratch(enc, qmm_tc_scratch_bytes(a, nt, false), &scratch))) return rc;
@@ -1574,9 +1649,9 @@ extern "C" int mlxn_quantized_matmul_ggml_sharded(mlxn_encoder *enc, mlxn_regist
                                                   uint32_t n_total, uint32_t col0, void *const *peer_outputs, uint32_t n_peers) {
     int rc = check_handles(enc, dev, {input, weight, output, params});
     if (rc) return rc;
-    if (params->m == 0 || params->m > MLXN_MM_ROUTING_THRESHOLD)
-        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_sharded: m (%u) must be in 1..%u", params->m,
-                    (unsigned)MLXN_MM_ROUTING_THRESHOLD);
+    if (params->m == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_sharded: m must be > 0");
+    if (params->m > MLXN_MM_ROUTING_THRESHOLD && (int)params->ggml_type == GT_Q4_K)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_sharded: Q4_K has no mat-mat form");
     if (n_peers > (uint32_t)kMaxPeers || (n_peers && !peer_outputs))
         return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_sharded: at most %d peer outputs", kMaxPeers);
     if ((uint64_t)col0 + params->n > n_total)
@@ -1597,6 +1672,7 @@ extern "C" int mlxn_quantized_matmul_ggml_sharded(mlxn_encoder *enc, mlxn_regist
             return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_ggml_sharded: peer output %u is null or misaligned", i);
         sh.peer[i] = static_cast<float *>(peer_outputs[i]);
     }
+    if (params->m > MLXN_MM_ROUTING_THRESHOLD) return dispatch_mm(enc, reg, dev, input, weight, output, params, &sh);
     return dispatch_mv(enc, reg, dev, input, weight, output, params, &sh);
 }
 

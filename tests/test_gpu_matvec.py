@@ -208,9 +208,25 @@ def test_q6k_row_pairs(ctx, n, k, m):
         mx.set_option("qmv", "auto")
 
 
+@pytest.mark.parametrize("n,k,m", [(2, 1024, 1), (66, 5120, 2), (128, 1024, 8), (130, 3072, 3), (1000, 5120, 1), (4748, 5120, 4),
+                                   (18992, 5120, 1)])
+def test_q6k_row_pairs_register_kernel(ctx, n, k, m):
+    """The same row geometry on the register-level kernel (its tensor map's rows are pairs of weight rows too)."""
+    mx.set_option("qmv", "mma")
+    try:
+        wq = normal_weights(n + k, min(n, 1024), k, orc.Q6_K)
+        if n > 1024:
+            rb = orc.row_bytes(orc.Q6_K, k)
+            wq = np.concatenate([np.roll(wq.reshape(1024, rb), 3 * i, axis=0) for i in range((n + 1023) // 1024)])[:n].reshape(-1)
+        check(ctx, "Q6_K", wq, normal_acts(m, m, k), n, k)
+        assert mx.last_kernel_name() == "qmv_mma"
+    finally:
+        mx.set_option("qmv", "auto")
+
+
 # ---- the large-vocabulary lm_head at full size: Q6_K 151936 x 5120, m = 1 (638 MB of weights), a sample of rows
 # ---- including the first and last tiles
-@pytest.mark.parametrize("kernel", ["auto", "tc", "stream"])
+@pytest.mark.parametrize("kernel", ["auto", "mma", "tc", "stream"])
 def test_lm_head_q6k_full_size_sampled(ctx, kernel):
     mx.set_option("qmv", kernel)
     try:

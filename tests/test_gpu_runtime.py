@@ -349,3 +349,31 @@ def test_pool_alloc_batch_and_labeled_commits(ctx):
     enc.commit_and_wait_labeled("layer.test")
     n_cb, ns = mx.profile_cb_get("layer.test")
     assert (n_cb, ns) == (0, 0) or ns > 0                    # the table fills only under MLX_PROFILE_CB=1
+
+
+def test_peer_barrier_passes_when_everyone_arrived_and_gives_up_otherwise(ctx):
+    """The library's cross-rank barrier on one GPU: two "ranks" whose flag arrays are ordinary buffers here.  With the
+    other rank's arrival already in place the barrier passes; without it the bounded wait runs out, the commit reports
+    CommandBufferError (transient) and the encoder keeps working.  Nothing hangs: the kernel returns by itself."""
+    d = ctx.device
+    mine = d.alloc_buffer(32 * 4, mx.DType.U32)
+    theirs = d.alloc_buffer(32 * 4, mx.DType.U32)
+    ptrs = [mine.contents_ptr(), theirs.contents_ptr()]          # rank 0 = this process
+    enc = d.command_encoder()
+    # rank 1 "arrived" at epoch 1: its flag in rank 0's array (slot 1) is set
+    flags = np.zeros(32, np.uint32)
+    flags[1] = 1
+    mine.upload(flags)
+    mx.peer_barrier(enc, 0, 2, ptrs, 1, limit_us=200000)
+    enc.commit_and_wait()
+    assert theirs.download(np.uint32)[0] == 1                    # this rank's arrival was published to the other one
+    assert mine.download(np.uint32)[0] == 1                      # and to itself
+    # epoch 2: nobody else arrives
+    mx.peer_barrier(enc, 0, 2, ptrs, 2, limit_us=2000)
+    with pytest.raises(mx.CommandBufferError, match="another rank") as ei:
+        enc.commit_and_wait()
+    assert ei.value.is_transient()
+    mx.peer_barrier(enc, 0, 1, ptrs[:1], 3, limit_us=2000)       # a one-rank group never waits
+    enc.commit_and_wait()
+    with pytest.raises(mx.InvalidArgument):
+        mx.peer_barrier(enc, 2, 2, ptrs, 1)

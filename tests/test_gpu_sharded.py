@@ -53,6 +53,38 @@ def test_sharded_equals_unsharded(ctx, qmv, tname, n, k, m, world):
         mx.set_option("qmv", "auto")
 
 
+@pytest.mark.parametrize("tname,n,k,m,world", [("Q6_K", 2048, 5120, 256, 2), ("Q4_0", 1536, 1024, 64, 4), ("Q8_0", 1024, 2048, 33, 2)])
+def test_sharded_mat_mat_equals_oracle(ctx, tname, n, k, m, world):
+    """The tensor-core mat-mat in the row-sharded form (prefill / lm_head with many rows): every rank's tiles land in
+    the full-width result and in the buffer that stands in for a peer."""
+    from tests.gpu_util import MM_TOL
+
+    d = ctx.device
+    gtype, otype = TYPES[tname]
+    wq = normal_weights(33, n, k, otype)
+    x = normal_acts(33, m, k)
+    xb = ctx.buf(x, mx.DType.F32)
+    full = d.alloc_buffer(m * n * 4, mx.DType.F32)
+    peer = d.alloc_buffer(m * n * 4, mx.DType.F32)
+    full.upload(np.full(m * n, np.nan, np.float32))
+    peer.upload(np.full(m * n, np.nan, np.float32))
+    enc = d.command_encoder()
+    n_loc = n // world
+    for rank in range(world):
+        wb = ctx.buf(sharding.shard_weight_bytes(wq, int(gtype), n, k, rank, world), mx.DType.U8)
+        mx.quantized_matmul_ggml_sharded(enc, ctx.registry, d, xb, wb, full, mx.GgmlQuantizedMatmulParams(m, n_loc, k, gtype),
+                                         n, rank * n_loc, [peer.contents_ptr()])
+        assert mx.last_kernel_name() == "qmm_tc"
+    enc.commit_and_wait()
+    got = full.as_slice(np.float32).reshape(m, n)
+    got_peer = peer.download(np.float32).reshape(m, n)
+    y_ref, ad = orc.qmatmul(otype, wq, x, n, k, nthreads=8)
+    assert norm_err(got, y_ref, ad) <= MM_TOL
+    y16, _ = orc.qmatmul(otype, wq, x, n, k, f16_operands=True, nthreads=8)
+    assert norm_err(got, y16, ad) <= 2e-5
+    assert np.array_equal(got_peer.view(np.uint32), got.view(np.uint32))
+
+
 def test_sharded_argument_errors(ctx):
     d = ctx.device
     gtype, otype = TYPES["Q8_0"]
@@ -61,8 +93,8 @@ def test_sharded_argument_errors(ctx):
     xb, wb = ctx.buf(normal_acts(1, 9, k), mx.DType.F32), ctx.buf(wq, mx.DType.U8)
     out = d.alloc_buffer(9 * 2 * n * 4, mx.DType.F32)
     enc = d.command_encoder()
-    with pytest.raises(mx.InvalidArgument):   # mat-vec route only
-        mx.quantized_matmul_ggml_sharded(enc, ctx.registry, d, xb, wb, out, mx.GgmlQuantizedMatmulParams(9, n, k, gtype), 2 * n, 0)
+    with pytest.raises(mx.InvalidArgument):   # m = 0
+        mx.quantized_matmul_ggml_sharded(enc, ctx.registry, d, xb, wb, out, mx.GgmlQuantizedMatmulParams(0, n, k, gtype), 2 * n, 0)
     with pytest.raises(mx.InvalidArgument):   # columns outside the full width
         mx.quantized_matmul_ggml_sharded(enc, ctx.registry, d, xb, wb, out, mx.GgmlQuantizedMatmulParams(1, n, k, gtype), 2 * n, n + 1)
     small = d.alloc_buffer(n * 4, mx.DType.F32)

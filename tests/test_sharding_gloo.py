@@ -41,6 +41,17 @@ def test_two_rank_expert_sharding_matches_single_rank(tmp_path, T, E, top_k):
     assert bool(np.load(tmp_path / "ok.npy")[0])
 
 
+@pytest.mark.parametrize("T,E,top_k,world", [(5, 8, 2, 2), (12, 16, 8, 2), (1, 8, 4, 2), (9, 12, 3, 3)])
+def test_all_to_all_dispatch_combine_is_bit_identical_to_one_rank(tmp_path, T, E, top_k, world):
+    port = _free_port()
+    worker = os.path.join(ROOT, "tests", "shard_worker.py")
+    procs = [subprocess.Popen([sys.executable, worker, str(r), str(world), str(port), "moe_a2a", str(T), str(E), str(top_k),
+                               str(tmp_path)]) for r in range(world)]
+    for p in procs:
+        assert p.wait(timeout=300) == 0
+    assert bool(np.load(tmp_path / "ok.npy")[0])
+
+
 def test_sharding_helpers_errors():
     sys.path.insert(0, ROOT)
     from mlx_native_b200 import sharding
