@@ -6,7 +6,20 @@
 
 #include <utility>
 
+#include <cstdlib>
+
 namespace mlxn {
+
+// Experiment switches — environment variables that re-configure a kernel or switch parts of it off, for ablations —
+// exist only in builds made with -DMLXN_EXPERIMENTS.  The shipped library does not look at them, and the kernels'
+// debug masks are the constant 0 there, so their tests compile away.
+#ifdef MLXN_EXPERIMENTS
+inline const char *exp_env(const char *name) { return getenv(name); }
+#define MLXN_DBG(c) ((c).debug)
+#else
+inline const char *exp_env(const char *) { return nullptr; }
+#define MLXN_DBG(c) 0u
+#endif
 
 // GGML type codes (same numbering as mlxn_ggml_type in include/mlxn_b200.h).
 enum : int { GT_F32 = 0, GT_F16 = 1, GT_Q4_0 = 2, GT_Q8_0 = 3, GT_Q4_K = 4, GT_Q5_K = 5, GT_Q6_K = 6, GT_I16 = 7 };
@@ -17,6 +30,7 @@ template <> struct BlockTraits<GT_Q4_0> { static constexpr int QK = 32, BYTES = 
 template <> struct BlockTraits<GT_Q8_0> { static constexpr int QK = 32, BYTES = 34; };
 template <> struct BlockTraits<GT_Q6_K> { static constexpr int QK = 256, BYTES = 210; };
 template <> struct BlockTraits<GT_Q4_K> { static constexpr int QK = 256, BYTES = 144; };
+template <> struct BlockTraits<GT_Q5_K> { static constexpr int QK = 256, BYTES = 176; };
 
 // Q4_K (src/gguf/mod.rs:440-452): the 6-bit (scale, min) pair of sub-block j from the block's 12 packed bytes.
 __host__ __device__ inline void q4k_scale_min(uint32_t j, const uint8_t *scales, uint32_t &sc, uint32_t &mn) {

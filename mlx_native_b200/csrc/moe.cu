@@ -19,9 +19,13 @@ constexpr uint32_t kNotLocal = 0xFFFFFFFFu;   // id of a (token, slot) pair whos
 // counts gives each warp its first position, pass 2 writes the entries (ballot + popcount inside the warp), so the
 // list order is the scan order.  grid n_experts, 256 threads.
 constexpr uint32_t kMap0Entries = 4096;   // id entries staged per chunk (8 KB + padding)
+// An id >= n_experts belongs to no bucket (it is staged as 0xFFFF, which is no expert because n_experts <= 65535).  So
+// that the grouped route agrees with the mat-vec route, which writes a zero row for such a pair, CTA 0 zeroes the
+// pair's output row (`y`, n floats; optional) -- except for the id 0xFFFFFFFF, the "expert of another rank" mark of the
+// expert-sharded form, whose rows nobody reads and which is far too frequent there to pay for.
 __global__ void __launch_bounds__(256) moe_map0_kernel(const uint32_t *ids, uint32_t n_tokens, uint32_t top_k,
                                                        uint32_t n_experts, uint32_t hids_stride, uint32_t *htpe,
-                                                       int32_t *hids) {
+                                                       int32_t *hids, float *y, uint32_t n) {
     __shared__ uint16_t stage[kMap0Entries + 2 * 64 + 64];
     __shared__ uint32_t warp_hits[8];
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -37,7 +41,7 @@ __global__ void __launch_bounds__(256) moe_map0_kernel(const uint32_t *ids, uint
             int sel = 0;
             if (t < n_tokens)
                 for (uint32_t sl = 0; sl < top_k; sl++)
-                    sel += ((ids[(size_t)t * top_k + sl] & 0xFFFFu) == e16) ? (int)(sl + 1) : 0;
+                    sel += (ids[(size_t)t * top_k + sl] == e) ? (int)(sl + 1) : 0;
             const uint32_t hit = __ballot_sync(0xffffffffu, sel > 0);
             if (sel > 0) {
                 const uint32_t pos = n_all + __popc(hit & ((1u << lane) - 1u));
@@ -57,7 +61,12 @@ __global__ void __launch_bounds__(256) moe_map0_kernel(const uint32_t *ids, uint
         __syncthreads();   // the previous chunk has been scanned, warp_hits consumed
         for (uint32_t i = threadIdx.x; i < ct * top_k; i += 256) {
             const uint32_t t = i / top_k, sl = i - t * top_k;
-            stage[sl * pitch + t] = (uint16_t)(ids[(size_t)c0 * top_k + i] & 0xFFFFu);
+            const uint32_t id = ids[(size_t)c0 * top_k + i];
+            stage[sl * pitch + t] = id < n_experts ? (uint16_t)id : (uint16_t)0xFFFFu;
+            if (e == 0 && y && id >= n_experts && id != 0xFFFFFFFFu) {
+                float *yr = y + ((size_t)c0 * top_k + i) * n;
+                for (uint32_t j = 0; j < n; j++) yr[j] = 0.f;
+            }
         }
         __syncthreads();
         // warp w scans the 32-token groups [g_lo, g_hi) of the chunk
@@ -94,8 +103,8 @@ __global__ void __launch_bounds__(256) moe_map0_kernel(const uint32_t *ids, uint
 }
 
 cudaError_t launch_moe_map0(const uint32_t *ids, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts,
-                            uint32_t hids_stride, uint32_t *htpe, int32_t *hids, cudaStream_t st) {
-    moe_map0_kernel<<<n_experts, 256, 0, st>>>(ids, n_tokens, top_k, n_experts, hids_stride, htpe, hids);
+                            uint32_t hids_stride, uint32_t *htpe, int32_t *hids, float *y, uint32_t n, cudaStream_t st) {
+    moe_map0_kernel<<<n_experts, 256, 0, st>>>(ids, n_tokens, top_k, n_experts, hids_stride, htpe, hids, y, n);
     return cudaGetLastError();
 }
 

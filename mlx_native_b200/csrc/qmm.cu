@@ -627,13 +627,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     const uint32_t raw_stage_bytes = kTcRowsW * c.seg_stride;
     // wait styles: the single producer / MMA warps spin (they are the critical path and cost one warp's issue
     // slots); the dequantising warps space their polls out
-    const uint32_t wmode_cr = (c.debug & 32u) ? 0u : 0xFFFFFFFFu;
-    const uint32_t wmode_dq = (c.debug & 16u) ? 0xFFFFFFFFu : 0u;
+    const uint32_t wmode_cr = (MLXN_DBG(c) & 32u) ? 0u : 0xFFFFFFFFu;
+    const uint32_t wmode_dq = (MLXN_DBG(c) & 16u) ? 0xFFFFFFFFu : 0u;
 #ifdef MLXN_TC_TRACE
     // experiment: CTA 0 logs (event, clock) pairs into y (use with debug 256, which keeps the epilogue from writing y)
     uint32_t trace_n = 0;
     auto TRACE = [&](uint32_t role, uint32_t code, uint32_t x) {
-        if ((c.debug & 512u) && blockIdx.x == 0 && lane == 0 && trace_n < 500) {
+        if ((MLXN_DBG(c) & 512u) && blockIdx.x == 0 && lane == 0 && trace_n < 500) {
             uint32_t *t = reinterpret_cast<uint32_t *>(a.y) + role * 1024 + 2 * trace_n;
             t[0] = (code << 16) | (x & 0xFFFFu);
             t[1] = (uint32_t)clock64();
@@ -665,7 +665,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                             break;
                         }
                     }
-                    if (kc >= it.nck || (c.debug & 8u)) {
+                    if (kc >= it.nck || (MLXN_DBG(c) & 8u)) {
                         mbar_arrive(&b_full[s]);
                     } else {
                         mbar_expect_tx(&b_full[s], b_bytes);
@@ -719,7 +719,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             constexpr uint32_t idesc = umma_idesc_f16(kTcRowsW, NT);
             const uint64_t bd0 = umma_desc_k_sw128(smem_base + c.b_off);
             const uint64_t b_step = b_bytes >> 4;  // descriptor address field is in 16-byte units
-            const bool do_mma = !(c.debug & 4u);
+            const bool do_mma = !(MLXN_DBG(c) & 4u);
             const uint32_t d_col = tmem_d + w * NT;
             uint32_t sa = 0, aph = 0, sb = 0, bph = 0, nitem = 0;   // ring positions of the stage being looked at
             bool ok = true;
@@ -827,7 +827,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
             for (int i = 0; i < kRawSlots; i++) {
                 const uint8_t *src = slot_src[i] + koff;
                 const uint32_t pre_b = (uint32_t)((uintptr_t)src & 15u);
-                if (slot_cc[i] != 0xFFFFFFFFu && slot_cc[i] * 16u < pre_b + seg_bytes && !(c.debug & 2u))
+                if (slot_cc[i] != 0xFFFFFFFFu && slot_cc[i] * 16u < pre_b + seg_bytes && !(MLXN_DBG(c) & 2u))
                     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + slot_dst[i]),
                                  "l"(src - pre_b + slot_cc[i] * 16u)
                                  : "memory");
@@ -897,7 +897,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                     const uint32_t pre = (row_lo4 + ((r_abs * KR) / QK) * BB) & 15u;
                     const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
                 uint32_t regs[32];
-                if (c.aligned && row_ok && !(c.debug & 1u)) {
+                if (c.aligned && row_ok && !(MLXN_DBG(c) & 1u)) {
                     const uint32_t stage_row = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride;
                     if constexpr (T == GT_Q6_K) {
                         dequant32_q6k_aligned_p(r_abs & 7u, stage_row, set, 2 * half, regs);
@@ -915,7 +915,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                     for (uint32_t hh = 0; hh < 2; hh++) {
                         uint4 v[4];
                         const uint32_t e0 = 128 * set + 64 * half + 32 * hh;  // element offset inside the raw stage
-                        if (row_ok && r_abs * KR + e0 < a.k && !(c.debug & 1u)) {
+                        if (row_ok && r_abs * KR + e0 < a.k && !(MLXN_DBG(c) & 1u)) {
                             dequant32<T>(seg, e0, v);
                         } else {
 #pragma unroll
@@ -998,7 +998,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                     mbar_arrive(&stage_ready[nitem & 1u]);        // this warp's part of the staged tile is written
                 }
                 if (!mbar_wait(&stage_ready[nitem & 1u], (nitem >> 1) & 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) break;
-                if (!(c.debug & 256u)) {
+                if (!(MLXN_DBG(c) & 256u)) {
                     const uint32_t c4 = n0 + 4 * lane;
                     for (uint32_t r = dw; r < NT; r += kTcDequantWarps) {
                         const int32_t o = tab[r];
@@ -1037,7 +1037,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                     for (int j = 0; j < 32; j++) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(v1[j]));
                 }
                 tmem_ld_wait();
-                if (wrow < a.n && !(c.debug & 256u)) {
+                if (wrow < a.n && !(MLXN_DBG(c) & 256u)) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
                         const int32_t o = tab[col + j];
@@ -1104,7 +1104,7 @@ size_t qmm_tc_scratch_bytes(const QmmArgs &a, uint32_t nt, bool routed) {
 // Split-K factor for a dense call: 2 when the tile grid alone would fill at most ~half of the SMs and K is long
 // enough to share (two halves added onto a zeroed y give the same sum in either order).
 uint32_t qmm_tc_ksplit(uint32_t nt, uint32_t rows, uint32_t n, uint32_t k, int sm_count, bool routed) {
-    if (routed || getenv("MLXN_TC_NO_SPLITK")) return 1;
+    if (routed || exp_env("MLXN_TC_NO_SPLITK")) return 1;
     const uint64_t tiles = (uint64_t)((n + kTcRowsW - 1) / kTcRowsW) * ((rows + nt - 1) / nt);
     return (tiles * 2 <= (uint64_t)sm_count + sm_count / 8 && k >= 2048) ? 2u : 1u;
 }
@@ -1144,13 +1144,13 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES, KR = TcTraits<T>::KR;
     TcCfg c{};
     {
-        const char *dbg = getenv("MLXN_TC_DEBUG");
+        const char *dbg = exp_env("MLXN_TC_DEBUG");
         c.debug = dbg ? (uint32_t)atoi(dbg) : 0u;
     }
     {
         const uint32_t row_bytes = (a.k / QK) * BB;
         c.aligned = ((((uintptr_t)a.w | a.expert_stride) & 15u) == 0 && row_bytes % 16 == 0 && a.k % 256 == 0) ? 1u : 0u;
-        if (getenv("MLXN_TC_NO_ALIGNED")) c.aligned = 0;  // experiment switch
+        if (exp_env("MLXN_TC_NO_ALIGNED")) c.aligned = 0;  // experiment switch
     }
     c.nchunks = (a.k + 63) / 64;
     c.seg_stride = round_up_u((KR / QK) * BB + 15, 16) + 16;
@@ -1160,7 +1160,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     // pitch an odd multiple of 16).  A 3-D map [expert][row][words]; dense calls are one expert.
     alignas(64) CUtensorMap wmap;
     memset(&wmap, 0, sizeof(wmap));
-    if (c.aligned && !getenv("MLXN_TC_NO_TMA")) {
+    if (c.aligned && !exp_env("MLXN_TC_NO_TMA")) {
         EncodeTiledFn enc = encode_tiled_fn();
         const uint32_t row_bytes = (a.k / QK) * BB;
         const uint32_t box_bytes = T == GT_Q6_K ? 240u : (uint32_t)((KR / QK) * BB);
@@ -1188,19 +1188,19 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     const bool sharded = a.y_ld != 0 || a.n_peer != 0;
     const bool staged = NT == 64 && (sharded || qmm_tc_ksplit(NT, a.m, a.n, a.k, sm_count_of_device(), routed) == 1) &&
                         ((((uintptr_t)a.y) | ((uintptr_t)qmm_ld(a) * 4u) | ((uintptr_t)a.y_col0 * 4u)) & 15u) == 0 && a.n_peer == 0 &&
-                        !getenv("MLXN_TC_NO_STAGED_OUT");
+                        !exp_env("MLXN_TC_NO_STAGED_OUT");
     if (staged) limit -= stage_bytes;
     // activation ring first (at least two raw slots kept back), the rest goes to the raw weight ring
     uint32_t b_stages = (limit - 2 * raw_slot) / b_bytes;
     if (b_stages > 6) b_stages = 6;
-    if (const char *e = getenv("MLXN_TC_STAGES")) {  // experiment switch
+    if (const char *e = exp_env("MLXN_TC_STAGES")) {  // experiment switch
         const uint32_t v = (uint32_t)atoi(e);
         if (v >= 2 && v <= b_stages) b_stages = v;
     }
     if (b_stages < 2) return cudaErrorInvalidConfiguration;
     uint32_t raw_slots = (limit - b_stages * b_bytes) / raw_slot;
     if (raw_slots > 6) raw_slots = 6;
-    if (const char *e = getenv("MLXN_TC_RAW")) {  // experiment switch
+    if (const char *e = exp_env("MLXN_TC_RAW")) {  // experiment switch
         const uint32_t v = (uint32_t)atoi(e);
         if (v >= 2 && v <= raw_slots) raw_slots = v;
     }
@@ -1254,7 +1254,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     // persistent CTAs, one per SM, each walking its share of the (weight tile, K split, activation tile) items
     const uint64_t items = (uint64_t)c.n_wt * tiles * ksplit;
     uint32_t ctas = (uint32_t)sm_count_of_device();
-    if (const char *e = getenv("MLXN_TC_CTAS")) {  // experiment switch
+    if (const char *e = exp_env("MLXN_TC_CTAS")) {  // experiment switch
         const int v = atoi(e);
         if (v >= 1 && v <= 4096) ctas = (uint32_t)v;
     }

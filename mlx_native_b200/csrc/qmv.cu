@@ -103,6 +103,39 @@ __device__ __forceinline__ void dot_row_simple(const uint8_t *wrow, const float 
                 }
             }
         }
+    } else if constexpr (T == GT_Q5_K) {
+        // src/gguf/mod.rs:469-540: f16 d, f16 dmin, scales[12] (as Q4_K), qh[32] (one high bit per value), qs[128].
+        // task = 8 consecutive bytes of one pair of sub-blocks (low nibbles + bit 2p of qh: sub-block 2p; high nibbles
+        // + bit 2p+1: sub-block 2p+1); value = (d*sc)*q - dmin*m with every product and the difference rounded in f32
+        const uint32_t ntask = (k / 256) * 16;
+        for (uint32_t tk = lane; tk < ntask; tk += 32) {
+            const uint32_t b = tk >> 4, p = (tk >> 2) & 3u, l0 = 8 * (tk & 3u);
+            const uint8_t *blk = wrow + 176u * b;
+            uint32_t sc1, m1, sc2, m2;
+            q4k_scale_min(2 * p, blk + 4, sc1, m1);
+            q4k_scale_min(2 * p + 1, blk + 4, sc2, m2);
+            const float d = half_bits_to_float(ld_u16(blk)), dmin = half_bits_to_float(ld_u16(blk + 2));
+            const float d1 = __fmul_rn(d, (float)sc1), min1 = __fmul_rn(dmin, (float)m1);
+            const float d2 = __fmul_rn(d, (float)sc2), min2 = __fmul_rn(dmin, (float)m2);
+            const uint8_t *q = blk + 48 + 32 * p + l0, *qh = blk + 16 + l0;
+            const float *xb = x + 256u * b + 64u * p + l0;
+#pragma unroll
+            for (int i = 0; i < 8; i += 2) {
+                const uint32_t qq = ld_u16(q + i), hh = ld_u16(qh + i) >> (2 * p);
+                const float w0 = __fsub_rn(__fmul_rn(d1, (float)((qq & 15u) + ((hh & 1u) << 4))), min1);
+                const float w1 = __fsub_rn(__fmul_rn(d1, (float)(((qq >> 8) & 15u) + (((hh >> 8) & 1u) << 4))), min1);
+                const float w2 = __fsub_rn(__fmul_rn(d2, (float)(((qq >> 4) & 15u) + (((hh >> 1) & 1u) << 4))), min2);
+                const float w3 = __fsub_rn(__fmul_rn(d2, (float)((qq >> 12) + (((hh >> 9) & 1u) << 4))), min2);
+#pragma unroll
+                for (int t = 0; t < M; t++) {
+                    const float *xt = xb + (size_t)t * k;
+                    acc[t] = fmaf(w0, __ldg(xt + i), acc[t]);
+                    acc[t] = fmaf(w1, __ldg(xt + i + 1), acc[t]);
+                    acc[t] = fmaf(w2, __ldg(xt + 32 + i), acc[t]);
+                    acc[t] = fmaf(w3, __ldg(xt + 32 + i + 1), acc[t]);
+                }
+            }
+        }
     } else {  // Q6_K: 16 strips of 4 (x4 groups) per block
         const uint32_t ntask = (k / 256) * 16;
         for (uint32_t tk = lane; tk < ntask; tk += 32) {
@@ -511,7 +544,7 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
         const uint32_t seg_bytes = (kb / QK) * BB;
         const uint8_t *src = wb + (size_t)(row0 + lane) * row_bytes + (size_t)w.s * slice_bytes;
         const uint32_t pre = (uint32_t)((uintptr_t)src & 15u);
-        const uint32_t bytes = (valid && lane < nrows && !(c.debug & 2u)) ? ((pre + seg_bytes + 15u) & ~15u) : 0u;
+        const uint32_t bytes = (valid && lane < nrows && !(MLXN_DBG(c) & 2u)) ? ((pre + seg_bytes + 15u) & ~15u) : 0u;
         uint32_t total = bytes;
         total += __shfl_xor_sync(0xffffffffu, total, 1);
         total += __shfl_xor_sync(0xffffffffu, total, 2);
@@ -627,7 +660,7 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
 #pragma unroll
                 for (int t = 0; t < M; t++) acc[r][t] = 0.0f;
             const bool landed = !abort_flag && mbar_wait(&full_bar[slot], (it >> c.lg_stages) & 1u, &abort_flag, a.status, ST_WAIT_FULL_TIMEOUT, 100);
-            if (valid && landed && !(c.debug & 1u)) {
+            if (valid && landed && !(MLXN_DBG(c) & 1u)) {
                 for (uint32_t task = wig * 32 + lane; task < ntasks; task += 32 * c.wpg) {
                     if constexpr (T == GT_Q4_0) task_q4_0<M>(seg, task, xs, xsum, c.ks, acc);
                     else if constexpr (T == GT_Q8_0) task_q8_0<M>(seg, task, xs, xsum, c.ks, acc);
@@ -753,7 +786,7 @@ static bool stream_config(const QmvArgs &a, int sm_count, size_t smem_limit, uin
     c.lg_stages = lg;
     c.lg_wpg = lg_wpg;
     {
-        const char *dbg = getenv("MLXN_MV_DEBUG");
+        const char *dbg = exp_env("MLXN_MV_DEBUG");
         c.debug = dbg ? (uint32_t)atoi(dbg) : 0u;
     }
     c.ks = ks;
@@ -851,6 +884,10 @@ cudaError_t launch_qmv(int ggml_type, const QmvArgs &a, bool want_stream, int sm
         default: return cudaErrorInvalidValue;
         }
     }
+    case GT_Q5_K:   // the expert-routed mat-vec only, as upstream (src/shaders/quantized_matmul_id_ggml.metal:401-509)
+        *kname = "qmv_simple";
+        if (a.m != 1) return cudaErrorInvalidValue;
+        return launch_simple_tm<GT_Q5_K, 1>(a, st);
     default: return cudaErrorInvalidValue;
     }
 }

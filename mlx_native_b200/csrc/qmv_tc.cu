@@ -368,7 +368,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
         }
         for (int s = 0; s < 2; s++) mbar_init(&fin_all[s], kVtCvtWarps);
         mbar_init_fence();
-        if (!(c.debug & 2u)) {
+        if (!(MLXN_DBG(c) & 2u)) {
             VtWalk st;
             st.init(u0, u1, c.upt, c.cu, c.nslots);
             mbar_expect_tx(&raw_full[0], kVtRows * c.row_stride + st.cnt * (4 * 2048 + AUX));
@@ -385,8 +385,8 @@ __global__ void __launch_bounds__(kVtThreads, 1)
     const uint32_t tmem = tmem_base_s;
     const uint32_t smem_base = smem_u32(smem);
     allow_dependents();  // the next overlapped launch in the stream (its blocks wait for this grid before reading anything)
-    const uint32_t wspin = (c.debug & 64u) ? 0u : ((c.debug & 128u) ? 40u : 0xFFFFFFFFu);   // MMA warps poll back to back (experiments: suspend / sleep)
-    const uint32_t wdq = (c.debug & 16u) ? 0xFFFFFFFFu : ((c.debug & 32u) ? 20u : 0u);  // convert warps: suspend / spin / short sleeps
+    const uint32_t wspin = (MLXN_DBG(c) & 64u) ? 0u : ((MLXN_DBG(c) & 128u) ? 40u : 0xFFFFFFFFu);   // MMA warps poll back to back (experiments: suspend / sleep)
+    const uint32_t wdq = (MLXN_DBG(c) & 16u) ? 0xFFFFFFFFu : ((MLXN_DBG(c) & 32u) ? 20u : 0u);  // convert warps: suspend / spin / short sleeps
 
     if (warp == kVtCvtWarps) {
         // ======================= producer warp: one tensor copy of weights per stage + the packed activations =======================
@@ -397,7 +397,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                 break;
             uint8_t *sl = smem + slot * c.slot_bytes;
             if (lane == 0) {
-                if (c.debug & 2u) {
+                if (MLXN_DBG(c) & 2u) {
                     mbar_arrive(&raw_full[slot]);  // experiment: no copies
                 } else {
                     // one tensor copy brings the stage's 128 rows (rows past n arrive as zeros); the box is always
@@ -439,7 +439,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
                             }
                             tc_fence_after();
                             const uint32_t acol = tmem + sl * kVtSlotCols, dcol = acol + 32;
-                            if (!(c.debug & 4u)) {
+                            if (!(MLXN_DBG(c) & 4u)) {
                                 if constexpr (T == GT_Q6_K) {
                                     // sub-step ss = 4 n + g: 32 K = half of 64-wide chunk ss / 2; one MMA per scale group
                                     const uint32_t ss = 4 * n + g;
@@ -491,7 +491,7 @@ __global__ void __launch_bounds__(kVtThreads, 1)
             uint32_t d[32];
             tmem_ld_32x32(lane_base + pv_sl * kVtSlotCols + 32, d);
             tmem_ld_wait();
-            if (c.debug & 1u) return;
+            if (MLXN_DBG(c) & 1u) return;
             const uint64_t dd0 = pack2(pv_d0 * 16777216.0f, pv_d0 * 16777216.0f), dn0 = pack2(-kOff * pv_d0, -kOff * pv_d0);
             const uint64_t dd1 = pack2(pv_d1 * 16777216.0f, pv_d1 * 16777216.0f), dn1 = pack2(-kOff * pv_d1, -kOff * pv_d1);
 #pragma unroll
@@ -646,7 +646,7 @@ bool qmv_tc_supported(int ggml_type, const QmvArgs &a) {
         // rows of 210-byte super-blocks: every row on a 16-byte boundary (k % 2048 == 0), or every other row with the
         // rows between 8 bytes past one (k % 2048 == 1024: pairs of rows become the tensor map's rows; n even)
         const uint32_t rem = a.k % 2048;
-        if (!(rem == 0 || (rem == 1024 && a.n % 2 == 0 && !getenv("MLXN_VT_NO_PAIRS")))) return false;
+        if (!(rem == 0 || (rem == 1024 && a.n % 2 == 0 && !exp_env("MLXN_VT_NO_PAIRS")))) return false;
     }
     if (a.ids || a.nprob != 1 || a.m < 1 || a.m > 8) return false;
     if (a.k % kVtUnitK != 0 || a.k == 0 || a.n == 0 || a.k / kVtUnitK > (uint32_t)kVtMaxUnits) return false;
@@ -697,7 +697,7 @@ static cudaError_t launch_vt_t(const QmvArgs &a, uint8_t *scratch, uint32_t *fla
     constexpr int UB = VtTraits<T>::UB;
     VtCfg c{};
     {
-        const char *dbg = getenv("MLXN_VT_DEBUG");
+        const char *dbg = exp_env("MLXN_VT_DEBUG");
         c.debug = dbg ? (uint32_t)atoi(dbg) : 0u;
     }
     c.tiles = (a.n + kVtRows - 1) / kVtRows;
@@ -706,7 +706,7 @@ static cudaError_t launch_vt_t(const QmvArgs &a, uint8_t *scratch, uint32_t *fla
     // cu odd: the rows of a stage sit cu * UB bytes apart, an odd multiple of 16 bytes, so that the 16-byte reads
     // of eight consecutive rows fall into eight different bank groups
     c.cu = T == GT_Q4_0 ? 3u : 1u;
-    if (const char *e = getenv("MLXN_VT_CU")) {  // experiment switch
+    if (const char *e = exp_env("MLXN_VT_CU")) {  // experiment switch
         const uint32_t v = (uint32_t)atoi(e);
         if (T != GT_Q6_K && v >= 1 && v <= 5 && v * UB / 4 <= 256) c.cu = v;
     }
@@ -717,7 +717,7 @@ static cudaError_t launch_vt_t(const QmvArgs &a, uint8_t *scratch, uint32_t *fla
     const uint32_t limit = 208 * 1024;
     c.nslots = limit / c.slot_bytes;
     if (c.nslots > (uint32_t)kVtMaxSlots) c.nslots = kVtMaxSlots;
-    if (const char *e = getenv("MLXN_VT_SLOTS")) {  // experiment switch
+    if (const char *e = exp_env("MLXN_VT_SLOTS")) {  // experiment switch
         const uint32_t v = (uint32_t)atoi(e);
         if (v >= 2 && v <= c.nslots) c.nslots = v;
     }

@@ -38,7 +38,7 @@ size_t qmm_tc_scratch_bytes(const QmmArgs &a, uint32_t nt, bool routed);
 uint32_t qmm_tc_pick_nt(int ggml_type, uint32_t rows, uint32_t n, int sm_count, bool routed);
 bool qmm_tc_supported(const QmmArgs &a);
 cudaError_t launch_moe_map0(const uint32_t *ids, uint32_t n_tokens, uint32_t top_k, uint32_t n_experts,
-                            uint32_t hids_stride, uint32_t *htpe, int32_t *hids, cudaStream_t st);
+                            uint32_t hids_stride, uint32_t *htpe, int32_t *hids, float *y, uint32_t n, cudaStream_t st);
 cudaError_t launch_moe_softmax_topk(const float *logits, uint32_t n_tokens, uint32_t n_experts, uint32_t top_k,
                                     uint32_t *out_ids, float *out_w, cudaStream_t st);
 cudaError_t launch_silu_mul(const float *gate, const float *up, float *out, uint32_t n, cudaStream_t st);
@@ -681,8 +681,13 @@ static const char *const kKernelNames[] = {
     "kernel_mul_mm_q4_0_tensor_f32", "kernel_mul_mm_q8_0_tensor_f32", "kernel_mul_mm_q6_K_tensor_f32",
     "kernel_mul_mv_id_q4_0_f32", "kernel_mul_mv_id_q8_0_f32", "kernel_mul_mv_id_q6_K_f32",
     "kernel_mul_mm_id_map0_ne20_1", "kernel_mul_mm_id_map0_ne20_8",
+    // the bucketing kernel takes any top_k; the values upstream's audit lists as uncovered there
+    // (docs/moe-q-perf-audit-2026-04-27.md:79-84) have names of the same pattern here
+    "kernel_mul_mm_id_map0_ne20_2", "kernel_mul_mm_id_map0_ne20_4", "kernel_mul_mm_id_map0_ne20_5", "kernel_mul_mm_id_map0_ne20_6",
+    "kernel_mul_mm_id_map0_ne20_10", "kernel_mul_mm_id_map0_ne20_16", "kernel_mul_mm_id_map0_ne20_22", "kernel_mul_mm_id_map0_ne20_n",
     "kernel_mul_mm_id_q4_0_f32", "kernel_mul_mm_id_q8_0_f32", "kernel_mul_mm_id_q6_K_f32",
     "kernel_mul_mm_id_q4_0_tensor_f32", "kernel_mul_mm_id_q8_0_tensor_f32", "kernel_mul_mm_id_q6_K_tensor_f32",
+    "kernel_mul_mv_id_q5_K_f32",
     "kernel_mul_mv_q4_K_f32", "kernel_mul_mv_id_q4_K_f32", "kernel_mul_mm_id_q4_K_f32", "kernel_mul_mm_id_q4_K_tensor_f32",
     "moe_softmax_topk_f32", "moe_weighted_reduce_f32", "silu_mul_f32",
 };
@@ -1433,7 +1438,8 @@ static const char *mm_kernel_name(int t) {
     return t == GT_Q4_0 ? "kernel_mul_mm_q4_0_tensor_f32" : t == GT_Q8_0 ? "kernel_mul_mm_q8_0_tensor_f32" : "kernel_mul_mm_q6_K_tensor_f32";
 }
 static const char *mv_id_kernel_name(int t) {
-    return t == GT_Q4_0 ? "kernel_mul_mv_id_q4_0_f32" : t == GT_Q8_0 ? "kernel_mul_mv_id_q8_0_f32" : t == GT_Q4_K ? "kernel_mul_mv_id_q4_K_f32" : "kernel_mul_mv_id_q6_K_f32";
+    return t == GT_Q4_0 ? "kernel_mul_mv_id_q4_0_f32" : t == GT_Q8_0 ? "kernel_mul_mv_id_q8_0_f32" : t == GT_Q4_K ? "kernel_mul_mv_id_q4_K_f32"
+         : t == GT_Q5_K ? "kernel_mul_mv_id_q5_K_f32" : "kernel_mul_mv_id_q6_K_f32";
 }
 static const char *mm_id_kernel_name(int t) {
     return t == GT_Q4_0 ? "kernel_mul_mm_id_q4_0_tensor_f32" : t == GT_Q8_0 ? "kernel_mul_mm_id_q8_0_tensor_f32" : t == GT_Q4_K ? "kernel_mul_mm_id_q4_K_tensor_f32" : "kernel_mul_mm_id_q6_K_tensor_f32";
@@ -1527,8 +1533,8 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
     for (uint32_t m0 = 0; m0 < p->m; m0 += 8) {
         const QmvArgs a = make_args(m0);
         // The tensor-memory kernel's time does not grow with the number of rows, the streaming SIMT kernel's does.
-        static const int min_m = [] { const char *e = getenv("MLXN_QMV_TC_MIN_M"); return e ? atoi(e) : 1; }();         // experiment switches
-        static const int min_m_q6k = [] { const char *e = getenv("MLXN_QMV_TC_MIN_M_Q6K"); return e ? atoi(e) : 1; }();
+        static const int min_m = [] { const char *e = exp_env("MLXN_QMV_TC_MIN_M"); return e ? atoi(e) : 1; }();         // experiment switches
+        static const int min_m_q6k = [] { const char *e = exp_env("MLXN_QMV_TC_MIN_M_Q6K"); return e ? atoi(e) : 1; }();
         const int need_m = (int)p->ggml_type == GT_Q6_K ? (a.k >= 8192 ? (min_m_q6k < 2 ? min_m_q6k : 2) : min_m_q6k) : min_m;
         const bool want_tc = mode == 2 || ((mode == 3 || mode == 4) && (int)a.m >= need_m);
         if (mode == 4 && p->m > 8 && qmv_mma_supported((int)p->ggml_type, a)) {
@@ -1694,6 +1700,8 @@ static int validate_id(const char *who, mlxn_buffer *input, mlxn_buffer *weight,
     if (p->n_tokens == 0 || p->k == 0 || p->n == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: n_tokens, K, and N must all be > 0", who);
     if (p->top_k == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: top_k must be > 0", who);
     if (p->n_experts == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: n_experts must be > 0", who);
+    if (p->n_experts > 65535u)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: n_experts (%u) must be <= 65535", who, p->n_experts);
     if (t < 0 || t > MLXN_GGML_I16) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: unknown ggml_type %d", who, t);
     const uint32_t qk = ggml_qk(t);
     if (p->k % qk != 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: K (%u) must be divisible by block QK (%u)", who, p->k, qk);
@@ -1721,7 +1729,7 @@ static int validate_id(const char *who, mlxn_buffer *input, mlxn_buffer *weight,
     if (output->len < expected_out)
         return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: output buffer too small: expected %zu bytes for [%zu x %u] f32, got %zu",
                     who, expected_out, total_rows, p->n, output->len);
-    if (t != GT_Q4_0 && t != GT_Q8_0 && t != GT_Q6_K && t != GT_Q4_K)
+    if (t != GT_Q4_0 && t != GT_Q8_0 && t != GT_Q6_K && t != GT_Q4_K && t != GT_Q5_K)
         return fail(MLXN_KERNEL_NOT_FOUND, "Kernel not found: expert-routed kernels for %s are not built into this library yet", ggml_name(t));
     if (total_rows > 0x7FFFFFFFull / 1) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: %s: n_tokens * top_k is too large", who);
     return MLXN_OK;
@@ -1755,11 +1763,13 @@ static int dispatch_id_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *de
 static int dispatch_id_mm_stages(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
                                  mlxn_buffer *weight, mlxn_buffer *ids, mlxn_buffer *output, uint32_t *htpe, int32_t *hids,
                                  uint32_t hids_stride, size_t scratch_used, const mlxn_qmm_id_params *p) {
-    int rc = touch_kernel(reg, dev, p->top_k == 1 ? "kernel_mul_mm_id_map0_ne20_1" : "kernel_mul_mm_id_map0_ne20_8");
+    char map0_name[48];
+    snprintf(map0_name, sizeof(map0_name), "kernel_mul_mm_id_map0_ne20_%u", p->top_k);
+    int rc = touch_kernel(reg, dev, known_kernel(map0_name) ? map0_name : "kernel_mul_mm_id_map0_ne20_n");
     if (rc) return rc;
     if ((rc = touch_kernel(reg, dev, mm_id_kernel_name((int)p->ggml_type)))) return rc;
     CUDA_TRY(launch_moe_map0(reinterpret_cast<const uint32_t *>(ids->dev()), p->n_tokens, p->top_k, p->n_experts,
-                             hids_stride, htpe, hids, enc->stream),
+                             hids_stride, htpe, hids, reinterpret_cast<float *>(output->dev()), p->n, enc->stream),
              "map0 launch");
     g_launches.fetch_add(1);
     g_dispatch.fetch_add(1);
@@ -1797,9 +1807,11 @@ static int dispatch_id_mm_stages(mlxn_encoder *enc, mlxn_registry *reg, mlxn_dev
     return MLXN_OK;
 }
 
+// Upstream routes to the grouped mat-mat only for top_k in {1, 8} (the two instantiations of its bucketing kernel,
+// src/ops/quantized_matmul_id_ggml.rs:265-273) and names the other values as a gap
+// (docs/moe-q-perf-audit-2026-04-27.md:79-84); the bucketing kernel here takes any top_k, so every top_k takes the route.
 static bool id_routes_to_mm(const mlxn_qmm_id_params *p) {
-    return p->n_tokens > mlxn_mm_id_routing_threshold() && (p->top_k == 1 || p->top_k == 8) && p->k >= 32 &&
-           (int)p->ggml_type != GT_Q5_K;
+    return p->n_tokens > mlxn_mm_id_routing_threshold() && p->k >= 32 && (int)p->ggml_type != GT_Q5_K;
 }
 
 extern "C" size_t mlxn_id_mm_htpe_bytes(const mlxn_qmm_id_params *p) { return p ? (size_t)p->n_experts * 4 : 0; }

@@ -261,6 +261,20 @@ def dequantize_to_f32(data: np.ndarray, ggml_type: GgmlType) -> np.ndarray:
         dj = (d * sc.astype(f32)).astype(f32)[:, :, None]
         mj = (dmin * mn.astype(f32)).astype(f32)[:, :, None]
         return ((dj * q).astype(f32) - mj).astype(f32).reshape(-1)
+    if ggml_type == GgmlType.Q5_K:
+        b = d8.reshape(-1, 176)                                        # src/gguf/mod.rs:469-541
+        d, dmin = _f16(b[:, 0:2]), _f16(b[:, 2:4])
+        s = b[:, 4:16].astype(np.uint32)
+        sc = np.concatenate([s[:, 0:4] & 63, (s[:, 8:12] & 0x0F) | ((s[:, 0:4] >> 6) << 4)], axis=1)     # [nb, 8]
+        mn = np.concatenate([s[:, 4:8] & 63, (s[:, 8:12] >> 4) | ((s[:, 4:8] >> 6) << 4)], axis=1)
+        qh = b[:, 16:48]                                                                                 # [nb, 32]
+        qs = b[:, 48:].reshape(-1, 4, 32)
+        lo = np.stack([qs & 0x0F, qs >> 4], axis=2).reshape(-1, 8, 32)
+        hi = (qh[:, None, :] >> np.arange(8, dtype=np.uint8)[None, :, None]) & 1                         # sub-block j: bit j
+        q = (lo + 16 * hi).astype(f32)
+        dj = (d * sc.astype(f32)).astype(f32)[:, :, None]
+        mj = (dmin * mn.astype(f32)).astype(f32)[:, :, None]
+        return ((dj * q).astype(f32) - mj).astype(f32).reshape(-1)
     if ggml_type == GgmlType.Q6_K:
         b = d8.reshape(-1, 210)
         nb = b.shape[0]
@@ -360,7 +374,17 @@ def load_tensor_experts(self: GgufFile, name: str, device: MlxDevice, rank: int,
     return _to_device(device, raw, info.ggml_type, (per, n, k))
 
 
+def load_tensor_into_pool(self: GgufFile, name: str, device: MlxDevice, pool) -> MlxBuffer:
+    """src/gguf/mod.rs:1127-1137: `load_tensor`, then the buffer is registered with the pool so that the pool's residency
+    accounting covers the weights (on this device every allocation is already resident: the registration only records
+    it).  Errors: those of `load_tensor`, plus InvalidArgument from `register_existing`."""
+    buf = load_tensor(self, name, device)
+    pool.register_existing(device, buf)
+    return buf
+
+
 GgufFile.load_tensor = load_tensor
+GgufFile.load_tensor_into_pool = load_tensor_into_pool
 GgufFile.load_tensor_f32 = load_tensor_f32
 GgufFile.load_tensor_rows = load_tensor_rows
 GgufFile.load_tensor_experts = load_tensor_experts

@@ -35,6 +35,7 @@
  *   src/shaders/quantized_matmul_id_mm.metal:242-283  map0 bucketing
  *   src/shaders/moe_softmax_topk.metal:27-148    router softmax + top-k
  *   src/gguf/mod.rs:440-452, 582-644             Q4_K scale/min unpacking and dequantize
+ *   src/gguf/mod.rs:469-540                      Q5_K dequantize (known answers: tests/test_q5_k_dequant.rs:121-262)
  *   tests/test_q4_k_kernels.rs:58-76, 108-180    Q4_K scale packing and the test packer
  *   src/shaders/moe_weighted_reduce.metal:33-66  weighted combine
  *   src/shaders/silu_mul.metal:17-30             SwiGLU
@@ -53,6 +54,7 @@
 #define BYTES_Q8_0 34
 #define BYTES_Q6_K 210
 #define BYTES_Q4_K 144
+#define BYTES_Q5_K 176
 
 /* ggml_type codes shared with include/mlxn_b200.h */
 enum { T_F32 = 0, T_F16 = 1, T_Q4_0 = 2, T_Q8_0 = 3, T_Q4_K = 4, T_Q5_K = 5, T_Q6_K = 6, T_I16 = 7 };
@@ -223,9 +225,38 @@ void orc_dequant_q4_k(const uint8_t *data, size_t nblocks, float *out) {
     }
 }
 
-static int type_qk(int t) { return (t == T_Q6_K || t == T_Q4_K) ? QK_K : 32; }
+/* src/gguf/mod.rs:469-540 (tests/test_q5_k_dequant.rs:55-98 holds the same formula as the specification).
+ * Block: f16 d, f16 dmin, scales[12] (as Q4_K), qh[32], qs[128].  Pair p of sub-blocks: bytes [32p, 32p+32) of qs,
+ * low nibbles + bit 2p of qh[l] -> sub-block 2p, high nibbles + bit 2p+1 -> sub-block 2p+1;
+ * value = (d * sc) * q - (dmin * m), q = nibble + 16 * bit, each product and the difference rounded in f32. */
+void orc_dequant_q5_k(const uint8_t *data, size_t nblocks, float *out) {
+    for (size_t b = 0; b < nblocks; b++) {
+        const uint8_t *blk = data + b * BYTES_Q5_K;
+        const float d = orc_f16_to_f32(rd_u16(blk));
+        const float dmin = orc_f16_to_f32(rd_u16(blk + 2));
+        const uint8_t *scales = blk + 4, *qh = blk + 16, *qs = blk + 48;
+        float *o = out + b * QK_K;
+        for (int p = 0; p < 4; p++) {
+            uint8_t sc1, m1, sc2, m2;
+            orc_q4k_scale_min(2 * p, scales, &sc1, &m1);
+            orc_q4k_scale_min(2 * p + 1, scales, &sc2, &m2);
+            const float d1 = d * (float)sc1, min1 = dmin * (float)m1;
+            const float d2 = d * (float)sc2, min2 = dmin * (float)m2;
+            for (int l = 0; l < 32; l++) {
+                const unsigned q1 = (qs[32 * p + l] & 0x0Fu) + (((qh[l] >> (2 * p)) & 1u) ? 16u : 0u);
+                const unsigned q2 = (qs[32 * p + l] >> 4) + (((qh[l] >> (2 * p + 1)) & 1u) ? 16u : 0u);
+                volatile float a = d1 * (float)q1;   /* no fused multiply-subtract */
+                volatile float c = d2 * (float)q2;
+                o[64 * p + l] = a - min1;
+                o[64 * p + 32 + l] = c - min2;
+            }
+        }
+    }
+}
+
+static int type_qk(int t) { return (t == T_Q6_K || t == T_Q4_K || t == T_Q5_K) ? QK_K : 32; }
 static int type_bytes(int t) {
-    return t == T_Q4_0 ? BYTES_Q4_0 : t == T_Q8_0 ? BYTES_Q8_0 : t == T_Q4_K ? BYTES_Q4_K : BYTES_Q6_K;
+    return t == T_Q4_0 ? BYTES_Q4_0 : t == T_Q8_0 ? BYTES_Q8_0 : t == T_Q4_K ? BYTES_Q4_K : t == T_Q5_K ? BYTES_Q5_K : BYTES_Q6_K;
 }
 
 int orc_dequant(int ggml_type, const uint8_t *data, size_t nblocks, float *out) {
@@ -234,6 +265,7 @@ int orc_dequant(int ggml_type, const uint8_t *data, size_t nblocks, float *out) 
     case T_Q8_0: orc_dequant_q8_0(data, nblocks, out); return 0;
     case T_Q6_K: orc_dequant_q6_k(data, nblocks, out); return 0;
     case T_Q4_K: orc_dequant_q4_k(data, nblocks, out); return 0;
+    case T_Q5_K: orc_dequant_q5_k(data, nblocks, out); return 0;
     default: return -1;
     }
 }
@@ -493,7 +525,7 @@ static void *mm_worker(void *arg) {
  * staging, quantized_matmul_mm_tensor.metal:92-158 and :280-287) and still accumulates in f32. */
 int orc_qmatmul(int ggml_type, const uint8_t *w, const float *x, int m, size_t n, size_t k,
                 size_t row0, size_t row1, float *y, double *absdot, int f16_operands, int nthreads) {
-    if (ggml_type != T_Q4_0 && ggml_type != T_Q8_0 && ggml_type != T_Q6_K && ggml_type != T_Q4_K) return -1;
+    if (ggml_type != T_Q4_0 && ggml_type != T_Q8_0 && ggml_type != T_Q6_K && ggml_type != T_Q4_K && ggml_type != T_Q5_K) return -1;
     if (k % (size_t)type_qk(ggml_type)) return -2;
     if (nthreads < 1) nthreads = 1;
     if (nthreads > 256) nthreads = 256;

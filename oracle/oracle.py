@@ -17,8 +17,8 @@ _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 
 # ggml_type codes (same numbering as include/mlxn_b200.h)
 F32, F16, Q4_0, Q8_0, Q4_K, Q5_K, Q6_K, I16 = range(8)
-BLOCK_VALUES = {Q4_0: 32, Q8_0: 32, Q6_K: 256, Q4_K: 256}
-BLOCK_BYTES = {Q4_0: 18, Q8_0: 34, Q6_K: 210, Q4_K: 144}
+BLOCK_VALUES = {Q4_0: 32, Q8_0: 32, Q6_K: 256, Q4_K: 256, Q5_K: 256}
+BLOCK_BYTES = {Q4_0: 18, Q8_0: 34, Q6_K: 210, Q4_K: 144, Q5_K: 176}
 
 
 def build(force: bool = False) -> str:

@@ -61,8 +61,15 @@ def test_q4_0_and_float_dequantizers():
     assert np.array_equal(gguf.dequantize_to_f32(w, GgmlType.Q4_0), orc.dequantize(orc.Q4_0, w))
     h = rng.standard_normal(9).astype(np.float16)
     assert np.array_equal(gguf.dequantize_to_f32(h.view(np.uint8), GgmlType.F16), h.astype(np.float32))
-    with pytest.raises(gguf.GgufParseError):
-        gguf.dequantize_to_f32(np.zeros(176, np.uint8), GgmlType.Q5_K)
+
+
+def test_q5_k_host_dequantizer_matches_the_oracle():
+    rng = np.random.default_rng(5)
+    blk = rng.integers(0, 256, (24, 176), dtype=np.uint8)
+    blk[:, 0:2] = (rng.standard_normal(24) * 0.01).astype(np.float16).view(np.uint8).reshape(24, 2)
+    blk[:, 2:4] = (rng.standard_normal(24) * 0.01).astype(np.float16).view(np.uint8).reshape(24, 2)
+    got = gguf.dequantize_to_f32(blk.reshape(-1), GgmlType.Q5_K)
+    assert np.array_equal(got, orc.dequantize(orc.Q5_K, blk.reshape(-1)))
 
 
 def test_rejects_bad_files(tmp_path):

@@ -48,6 +48,12 @@ def test_load_tensor_and_matvec(ctx, model):
         assert np.array_equal(fb.as_slice(np.float32), orc.dequantize(orc.Q6_K, t["w6"]))
         with pytest.raises(gguf.GgufParseError, match="not found"):
             g.load_tensor("missing", ctx.device)
+        # src/gguf/mod.rs:1127-1137: the loaded buffer is also registered with the pool
+        pool = mx.MlxBufferPool()
+        pb = g.load_tensor_into_pool("output.weight", ctx.device, pool)
+        assert np.array_equal(pb.as_slice(np.uint8), t["w6"])
+        with pytest.raises(gguf.GgufParseError, match="not found"):
+            g.load_tensor_into_pool("missing", ctx.device, pool)
 
 
 def test_sharded_loads(ctx, model):

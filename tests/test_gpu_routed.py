@@ -119,7 +119,7 @@ def test_mm_id_matches_mv_id(ctx, qmm, tname, n_tokens, n_experts, n, k, tol):
 
 @pytest.mark.parametrize("mode", ["auto", "pooled"])
 def test_routing_threshold_and_pooled(ctx, mode):
-    """n_tokens > 32 with top_k in {1, 8} takes the grouped mat-mat; the pooled form leaves the bucketing
+    """n_tokens > 32 takes the grouped mat-mat (any top_k); the pooled form leaves the bucketing
     in the caller's scratch; top_k = 1 is the down-projection convention (n_tokens = T*top_k rows, flat ids)."""
     gtype, otype = TYPES["Q6_K"]
     n_experts, n, k = 16, 96, 768
@@ -142,12 +142,25 @@ def test_routing_threshold_and_pooled(ctx, mode):
     assert mx.last_kernel_name() == "qmm_tc_id"
     yd_ref, add = orc.qmatmul_id(otype, stacked, stride, xd, ids, 1, n, k, n_experts, nthreads=8)
     assert norm_err(yd, yd_ref, add) <= MM_TOL
-    # top_k = 2 has no grouped route upstream: falls back to mv_id at any n_tokens
-    ids2 = ids.reshape(T, top_k)[:, :2].reshape(-1)
-    y2, _ = ctx.matmul_id(gtype, stacked, stride, x, ids2, 2, n, k, n_experts, mode=mode)
-    assert mx.last_kernel_name().startswith("qmv")
-    y2_ref, ad2 = orc.qmatmul_id(otype, stacked, stride, x, ids2, 2, n, k, n_experts, nthreads=8)
-    assert norm_err(y2, y2_ref, ad2) <= MV_TOL
+    # other top_k values (upstream falls back to mv_id for them and lists that as a gap,
+    # docs/moe-q-perf-audit-2026-04-27.md:79-84): the bucketing takes any top_k, so they take the grouped route too
+    for tk in (2, 3, 5):
+        idsk = ids.reshape(T, top_k)[:, :tk].reshape(-1)
+        yk, _ = ctx.matmul_id(gtype, stacked, stride, x, idsk, tk, n, k, n_experts, mode=mode)
+        assert mx.last_kernel_name() == "qmm_tc_id"
+        yk_ref, adk = orc.qmatmul_id(otype, stacked, stride, x, idsk, tk, n, k, n_experts, nthreads=8)
+        assert norm_err(yk, yk_ref, adk) <= MM_TOL
+        yk16, _ = orc.qmatmul_id(otype, stacked, stride, x, idsk, tk, n, k, n_experts, f16_operands=True, nthreads=8)
+        assert norm_err(yk, yk16, adk) <= 2e-5
+    # an id past n_experts gives a zero row on the grouped route, as on the mat-vec route
+    bad = ids.copy()
+    bad[5] = n_experts + 3
+    bad[77] = 0x10005                        # its low 16 bits name a real expert: must not be mistaken for it
+    yb, _ = ctx.matmul_id(gtype, stacked, stride, x, bad, top_k, n, k, n_experts, mode=mode)
+    assert np.all(yb[5] == 0) and np.all(yb[77] == 0)
+    keep = np.ones(T * top_k, bool)
+    keep[[5, 77]] = False
+    assert norm_err(yb[keep], y_ref[keep], ad[keep]) <= MM_TOL
 
 
 def test_pooled_capacity_errors(ctx):
