@@ -64,7 +64,7 @@ __host__ __device__ inline uint32_t ggml_block_bytes(int t) {
 
 // Device status word written by kernels whose bounded waits gave up.  0 = ok.
 enum : uint32_t { ST_OK = 0, ST_WAIT_FULL_TIMEOUT = 1, ST_WAIT_EMPTY_TIMEOUT = 2, ST_WAIT_MMA_TIMEOUT = 3,
-                  ST_WAIT_TMEM_TIMEOUT = 4, ST_BAD_ARGUMENT = 5, ST_WAIT_PEER_TIMEOUT = 6 };
+                  ST_WAIT_TMEM_TIMEOUT = 4, ST_BAD_ARGUMENT = 5, ST_WAIT_PEER_TIMEOUT = 6, ST_WAIT_GRID_TIMEOUT = 7 };
 
 // Arguments shared by the mat-vec kernels (dense and expert-routed).
 struct QmvArgs {
@@ -88,6 +88,10 @@ struct QmvArgs {
     uint32_t y_col0;        // first output column of this rank
     uint32_t n_peer;        // other ranks' buffers in y_peer
     float *y_peer[7];
+    // Batched launches of the register-level kernel only: this mat-vec reads or overwrites what a mat-vec earlier in
+    // the same launch writes, so it starts after all of them have finished (a barrier across the grid).
+    uint32_t after_earlier;
+    uint32_t *grid_bar;     // 32 zeroed words of device memory for those barriers (one launch at a time uses them)
 };
 constexpr int kMaxPeers = 7;
 __host__ __device__ inline uint32_t qmv_ld(const QmvArgs &a) { return a.y_ld ? a.y_ld : a.n; }
@@ -137,6 +141,24 @@ inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 b
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+// The same for a kernel whose blocks wait on one another: all blocks of the grid are resident at the same time
+// (the launch fails with cudaErrorCooperativeLaunchTooLarge if they cannot be).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_cooperative(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                      Args &&...args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);

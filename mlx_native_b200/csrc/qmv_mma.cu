@@ -30,6 +30,7 @@
 
 #include <cstdio>
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -37,7 +38,7 @@
 namespace mlxn {
 
 constexpr int kMwWarps = 8;                         // consumer warps
-constexpr int kMwThreads = (kMwWarps + 1) * 32;     // + producer warp
+constexpr int kMwThreads = kMwWarps * 32;
 constexpr int kMwMaxSlots = 12;
 
 // A "unit" is what one warp multiplies per tile and K step: one block of 32 (Q4_0 / Q8_0: two MMAs, one scale)
@@ -52,8 +53,13 @@ template <> struct MwTraits<GT_Q6_K> { static constexpr int UK = 512, UBYTES = 4
 // Shared-memory bytes per row of a stage of KB units per warp: the stage's bytes plus the up to 12 bytes between
 // the 16-byte boundary the copy starts at and the stage's first byte (Q6_K), rounded up to an ODD multiple of 16,
 // so that the 32-bit reads of eight consecutive rows fall into distinct banks.
+// A tensor copy is at most 256 elements (2048 bytes) wide: a longer stage row arrives as two copies, the first half of
+// the stage's K range for warps 0..3 and the second for warps 4..7, each into its own R x PITCH region of the slot.
+__host__ __device__ constexpr uint32_t mw_halves(int ggml_type, int kb) {
+    return (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : 420u) * (uint32_t)kb + 12u > 2048u ? 2u : 1u;
+}
 __host__ __device__ constexpr uint32_t mw_pitch(int ggml_type, int kb) {
-    const uint32_t raw = (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : 420u) * (uint32_t)kb;
+    const uint32_t raw = (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : 420u) * (uint32_t)kb / mw_halves(ggml_type, kb);
     const uint32_t lead = ggml_type == GT_Q6_K ? (kb == 1 ? 12u : 8u) : 0u;
     const uint32_t c = (raw + lead + 15u) / 16u;
     return 16u * (c | 1u);
@@ -79,6 +85,14 @@ struct MwBatch {
     uint32_t nprob;
     uint32_t early_weights;   // no problem's weights were written by a kernel of this process (see QmvArgs)
     uint32_t *status;
+    uint32_t nitems;          // items of all problems
+    // Dependent form (dep_mask != 0; a cooperative launch): bit p set = problem p starts only after every CTA has
+    // finished all the problems before it.  Every problem's items are then spread over all CTAs (CTA c takes
+    // items [c I / G, (c + 1) I / G) of a problem with I items), and the weights of the problems ahead keep streaming
+    // into the ring while a CTA waits.  bar[p] counts the CTAs that are done with the problems before p; bar[31] the
+    // CTAs that have left (the last one zeroes the block for the next launch).
+    uint32_t dep_mask;
+    uint32_t *bar;
     // CTA c works on items [cta_begin[c], cta_begin[c + 1]): contiguous chunks of (nearly) equal numbers of stages
     uint32_t cta_begin[kMwMaxGrid + 1];
 };
@@ -88,7 +102,8 @@ struct MwMaps {
 
 struct MwCfg {
 #ifdef MLXN_EXPERIMENTS
-    uint32_t debug;       // 1: consumers only wait and release (no arithmetic); 2: no copies (arithmetic on stale data)
+    uint32_t debug;       // 1: consumers only wait and release (no arithmetic); 2: no copies (arithmetic on stale data);
+                          // 4: no activation conversion; 8: no Q6_K scale table
 #endif
     uint32_t nslots;      // ring depth
     uint32_t xst_off;     // shared-memory offsets behind the ring
@@ -101,6 +116,42 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
     asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
+// Loads at a compile-time offset from a register address (the offset travels in the instruction: no address arithmetic)
+template <uint32_t OFF> __device__ __forceinline__ uint32_t lds32i(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.b32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(OFF));
+    return v;
+}
+template <uint32_t OFF> __device__ __forceinline__ uint32_t lds_u16i(uint32_t addr) {
+    uint32_t v;
+    asm volatile("{ .reg .u16 t; ld.shared.u16 t, [%1+%2]; cvt.u32.u16 %0, t; }" : "=r"(v) : "r"(addr), "n"(OFF));
+    return v;
+}
+template <uint32_t OFF> __device__ __forceinline__ void lds64i(uint32_t addr, uint32_t &a, uint32_t &b) {
+    asm volatile("ld.shared.v2.b32 {%0,%1}, [%2+%3];" : "=r"(a), "=r"(b) : "r"(addr), "n"(OFF));
+}
+template <uint32_t OFF> __device__ __forceinline__ void lds128i(uint32_t addr, uint32_t &a, uint32_t &b, uint32_t &c, uint32_t &d) {
+    asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4+%5];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr), "n"(OFF));
+}
+// The f16 in the low / high half of a 32-bit word, as f32
+__device__ __forceinline__ float f16lo_to_float(uint32_t w) {
+    float f;
+    asm("{ .reg .f16 l, h; mov.b32 {l, h}, %1; cvt.f32.f16 %0, l; }" : "=f"(f) : "r"(w));
+    return f;
+}
+__device__ __forceinline__ float f16hi_to_float(uint32_t w) {
+    float f;
+    asm("{ .reg .f16 l, h; mov.b32 {l, h}, %1; cvt.f32.f16 %0, h; }" : "=f"(f) : "r"(w));
+    return f;
+}
+// f(integral_constant<int, I>) for I = 0 .. N - 1: loop bodies whose shared-memory offsets must be compile-time constants
+template <int I, int N, class F> __device__ __forceinline__ void static_for(F &&f) {
+    if constexpr (I < N) {
+        f(std::integral_constant<int, I>{});
+        static_for<I + 1, N>(f);
+    }
+}
+
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -152,75 +203,106 @@ __device__ __forceinline__ void pow2_scale(float amax, float &s, float &inv) {
 }
 
 // Which elements of its block (Q4_0 / Q8_0) lane t multiplies in MMA `h` (0, 1) of the block, as two pairs of
-// consecutive elements.  Blocks with an even index inside the stage start on a 4-byte boundary, so their codes
-// (2 bytes in) straddle the 32-bit words: lanes t = 0..2 take whole words, lane t = 3 the two half words at either
-// end.  `mis` = that case.
+// consecutive elements.  The blocks of a row are worked on in pairs (even, odd index inside the stage): the even
+// block starts on a 4-byte boundary, so its codes (2 bytes in) straddle the 32-bit words.  There lanes t = 1..3 take
+// whole words and lane 0 the two half words at either end of the codes (which sit in the words that also hold the
+// pair's two f16 scales).  The odd block's codes are word-aligned.  `mis` = the even block.
 __device__ __forceinline__ void mw_pairs(int ggml_type, bool mis, uint32_t t, uint32_t h, uint32_t &p0, uint32_t &p1) {
     if (ggml_type == GT_Q8_0) {
         if (!mis) { p0 = 16 * h + 4 * t; p1 = p0 + 2; }
-        else if (h == 0) { p0 = 2 + 4 * t; p1 = 4 + 4 * t; }
-        else { p0 = t < 3 ? 18 + 4 * t : 0; p1 = t < 3 ? 20 + 4 * t : 30; }
+        else if (h == 0) { p0 = t ? 4 * t - 2 : 0; p1 = t ? 4 * t : 30; }
+        else { p0 = 14 + 4 * t; p1 = 16 + 4 * t; }
     } else {  // Q4_0: byte c holds element c (low nibble, MMA 0) and 16 + c (high nibble, MMA 1)
         if (!mis) { p0 = 4 * t; p1 = 4 * t + 2; }
-        else { p0 = t < 3 ? 2 + 4 * t : 0; p1 = t < 3 ? 4 + 4 * t : 14; }
+        else { p0 = t ? 4 * t - 2 : 0; p1 = t ? 4 * t : 14; }
         p0 += 16 * h;
         p1 += 16 * h;
     }
 }
 
-// One block of 32 (Q4_0 / Q8_0) against the warp's TPW tiles.  `pd`: shared address of the block in row g of the
-// stage (its f16 scale); `pa`: this lane's first code word; Q8_0: `pb0` its second code word.  MIS (the codes
-// straddle the 32-bit words): the last word of lane 3 is byte_perm(word at pb0, word at pb1, sel); the other lanes pass
-// pb0 == pb1 and the identity selector.  All other rows are compile-time offsets from these addresses.
-template <int T, int TPW, int MP, uint32_t PITCH, bool MIS>
-__device__ __forceinline__ void mw_block_tiles(uint32_t pd, uint32_t pa, uint32_t pb0, uint32_t pb1, uint32_t sel,
-                                               const uint32_t (&bf)[2][4], const float (&cq)[4], float cs0, float cs1,
-                                               float (&acc)[TPW][4]) {
-#pragma unroll
-    for (int j = 0; j < TPW; j++) {
-        uint32_t wa[2], wb[2];
-        float dd[2];
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const uint32_t off = (16 * j + 8 * h) * PITCH;
-            dd[h] = half_bits_to_float(lds_u16(pd + off));
+// A pair of blocks (even, odd index inside the stage; 2 x 32 values) against the warp's TPW tiles.
+// `base` = shared address of the pair in row g of the stage + 4 t; `base2`: lanes 1..3 the same, lane 0 the word that
+// holds the last two codes of the even block (and the odd block's scale); `sel`: the byte permute that joins lane 0's
+// two half words (identity in the other lanes); `rbs`: the pair's address in row g (scales, more than one activation
+// row only: with one, the scales are needed in lane 0 alone, which has them in the words it reads anyway).
+//
+// The 8 columns of an MMA are (activation row, f16 half): column 2 r holds the hi halves of activation row r (of the
+// set's four), column 2 r + 1 the lo halves, so ONE multiply gives both partial sums and lane t ends up with those of
+// activation row t: (hi, lo) for weight row g and (hi, lo) for weight row g + 8.  NS = 2 sets for 5..8 activation rows.
+// bf0 / bf1: the B registers of the two blocks' MMAs [set][MMA of the block][2]; cc: -offset sum(x), cs: inverse
+// activation pre-scale of this lane's activation row [set][block] (the codes enter unsigned, so every block owes
+// scale x cc).  All other rows are compile-time offsets from these addresses.
+template <int T, int TPW, int MP, int NS, uint32_t PITCH, uint32_t IOFF>
+__device__ __forceinline__ void mw_pair_tiles(uint32_t base, uint32_t base2, uint32_t rbs, uint32_t sel,
+                                              const uint32_t (&bf0)[NS][2][2], const uint32_t (&bf1)[NS][2][2],
+                                              const float (&cc)[NS][2], const float (&cs)[NS][2], float (&acc)[TPW][NS][4]) {
+    const float zz[4] = {0.f, 0.f, 0.f, 0.f};
+    constexpr uint32_t BB = T == GT_Q8_0 ? 34u : 18u;
+    static_for<0, TPW>([&](auto J) {
+        constexpr uint32_t j = decltype(J)::value;
+        uint32_t w0[2], w1[2], w2[2], w3[2];   // [row g, row g + 8]
+        float d0[2], d1[2];
+        static_for<0, 2>([&](auto H) {
+            constexpr uint32_t h = decltype(H)::value, OFF = (16 * j + 8 * h) * PITCH + IOFF;
+            const uint32_t s0 = lds32i<OFF>(base), s1 = lds32i<OFF>(base2);
+            w0[h] = __byte_perm(s0, s1, sel);
             if constexpr (T == GT_Q8_0) {
-                wa[h] = lds32(pa + off);
-                wb[h] = MIS ? __byte_perm(lds32(pb0 + off), lds32(pb1 + off), sel) : lds32(pb0 + off);
+                w1[h] = lds32i<OFF + 16>(base);
+                w2[h] = lds32i<OFF + 36>(base);
+                w3[h] = lds32i<OFF + 52>(base);
             } else {
-                wa[h] = MIS ? __byte_perm(lds32(pb0 + off), lds32(pb1 + off), sel) : lds32(pa + off);
-                wb[h] = 0;
+                w1[h] = lds32i<OFF + 20>(base);
+                w2[h] = w3[h] = 0;
             }
-        }
-        float d[4];
+            if constexpr (MP == 1) {
+                d0[h] = f16lo_to_float(s0);
+                d1[h] = f16hi_to_float(s1);
+            } else {
+                d0[h] = f16lo_to_float(lds_u16i<OFF>(rbs));
+                d1[h] = f16lo_to_float(lds_u16i<OFF + BB>(rbs));
+            }
+        });
+        uint32_t a[4][4];   // the A registers of the pair's four MMAs
         if constexpr (T == GT_Q8_0) {
-            // (w ^ 0x80..) & 0x00FF00FF: the even bytes (+128) as two f16 subnormals; the odd bytes likewise
-            uint32_t a0 = (wa[0] ^ 0x80808080u) & 0x00FF00FFu, a2 = ((wa[0] >> 8) ^ 0x00800080u) & 0x00FF00FFu;
-            uint32_t a1 = (wa[1] ^ 0x80808080u) & 0x00FF00FFu, a3 = ((wa[1] >> 8) ^ 0x00800080u) & 0x00FF00FFu;
-            mma16816(d, a0, a1, a2, a3, bf[0][0], bf[0][1], cq);
-            mma16816(d, a0, a1, a2, a3, bf[0][2], bf[0][3], d);
-            a0 = (wb[0] ^ 0x80808080u) & 0x00FF00FFu; a2 = ((wb[0] >> 8) ^ 0x00800080u) & 0x00FF00FFu;
-            a1 = (wb[1] ^ 0x80808080u) & 0x00FF00FFu; a3 = ((wb[1] >> 8) ^ 0x00800080u) & 0x00FF00FFu;
-            mma16816(d, a0, a1, a2, a3, bf[1][0], bf[1][1], d);
-            mma16816(d, a0, a1, a2, a3, bf[1][2], bf[1][3], d);
+            // codes + 128 as f16 subnormals: bytes 0, 2 and bytes 1, 3 of the word, each into the low byte of a half
+            auto un = [&](uint32_t (&r)[4], uint32_t wg, uint32_t wg8) {
+                const uint32_t x0 = wg ^ 0x80808080u, x1 = wg8 ^ 0x80808080u;
+                r[0] = __byte_perm(x0, 0u, 0x4240); r[1] = __byte_perm(x1, 0u, 0x4240);
+                r[2] = __byte_perm(x0, 0u, 0x4341); r[3] = __byte_perm(x1, 0u, 0x4341);
+            };
+            un(a[0], w0[0], w0[1]);
+            un(a[1], w1[0], w1[1]);
+            un(a[2], w2[0], w2[1]);
+            un(a[3], w3[0], w3[1]);
         } else {
             // low nibbles: elements c0..c3 of the word's four bytes; high nibbles (x 16): 16 + c
-            uint32_t a0 = wa[0] & 0x000F000Fu, a2 = (wa[0] >> 8) & 0x000F000Fu;
-            uint32_t a1 = wa[1] & 0x000F000Fu, a3 = (wa[1] >> 8) & 0x000F000Fu;
-            mma16816(d, a0, a1, a2, a3, bf[0][0], bf[0][1], cq);
-            mma16816(d, a0, a1, a2, a3, bf[0][2], bf[0][3], d);
-            a0 = wa[0] & 0x00F000F0u; a2 = (wa[0] >> 8) & 0x00F000F0u;
-            a1 = wa[1] & 0x00F000F0u; a3 = (wa[1] >> 8) & 0x00F000F0u;
-            mma16816(d, a0, a1, a2, a3, bf[1][0], bf[1][1], d);
-            mma16816(d, a0, a1, a2, a3, bf[1][2], bf[1][3], d);
+            auto un = [&](uint32_t (&lo)[4], uint32_t (&hi)[4], uint32_t wg, uint32_t wg8) {
+                lo[0] = wg & 0x000F000Fu; lo[2] = (wg >> 8) & 0x000F000Fu;
+                lo[1] = wg8 & 0x000F000Fu; lo[3] = (wg8 >> 8) & 0x000F000Fu;
+                hi[0] = wg & 0x00F000F0u; hi[2] = (wg >> 8) & 0x00F000F0u;
+                hi[1] = wg8 & 0x00F000F0u; hi[3] = (wg8 >> 8) & 0x00F000F0u;
+            };
+            un(a[0], a[1], w0[0], w0[1]);
+            un(a[2], a[3], w1[0], w1[1]);
         }
-        acc[j][0] = fmaf(dd[0] * cs0, d[0], acc[j][0]);
-        acc[j][2] = fmaf(dd[1] * cs0, d[2], acc[j][2]);
-        if constexpr (MP > 1) {
-            acc[j][1] = fmaf(dd[0] * cs1, d[1], acc[j][1]);
-            acc[j][3] = fmaf(dd[1] * cs1, d[3], acc[j][3]);
+#pragma unroll
+        for (int ns = 0; ns < NS; ns++) {
+            float e0[4], e1[4];
+            mma16816(e0, a[0][0], a[0][1], a[0][2], a[0][3], bf0[ns][0][0], bf0[ns][0][1], zz);
+            mma16816(e1, a[2][0], a[2][1], a[2][2], a[2][3], bf1[ns][0][0], bf1[ns][0][1], zz);
+            mma16816(e0, a[1][0], a[1][1], a[1][2], a[1][3], bf0[ns][1][0], bf0[ns][1][1], e0);
+            mma16816(e1, a[3][0], a[3][1], a[3][2], a[3][3], bf1[ns][1][0], bf1[ns][1][1], e1);
+            const float t00 = d0[0] * cs[ns][0], t01 = d0[1] * cs[ns][0], t10 = d1[0] * cs[ns][1], t11 = d1[1] * cs[ns][1];
+            acc[j][ns][0] = fmaf(t00, e0[0], fmaf(d0[0], cc[ns][0], acc[j][ns][0]));
+            acc[j][ns][1] = fmaf(t00, e0[1], acc[j][ns][1]);
+            acc[j][ns][2] = fmaf(t01, e0[2], fmaf(d0[1], cc[ns][0], acc[j][ns][2]));
+            acc[j][ns][3] = fmaf(t01, e0[3], acc[j][ns][3]);
+            acc[j][ns][0] = fmaf(t10, e1[0], fmaf(d1[0], cc[ns][1], acc[j][ns][0]));
+            acc[j][ns][1] = fmaf(t10, e1[1], acc[j][ns][1]);
+            acc[j][ns][2] = fmaf(t11, e1[2], fmaf(d1[1], cc[ns][1], acc[j][ns][2]));
+            acc[j][ns][3] = fmaf(t11, e1[3], acc[j][ns][3]);
         }
-    }
+    });
 }
 
 // TPW: 16-row tiles per warp.  KB: units per warp and stage.  MP: activation rows carried (1, 2, 4 or 8, >= m).
@@ -233,10 +315,13 @@ __global__ void __launch_bounds__(kMwThreads, 2)
     qmv_mma_kernel(const __grid_constant__ MwBatch bt, const MwCfg c, const __grid_constant__ MwMaps maps) {
     using TR = MwTraits<T>;
     constexpr int R = 16 * TPW, NG = TR::NG, NM = TR::NM;
+    constexpr int NS = MP > 4 ? 2 : 1;                       // sets of four activation rows
     constexpr uint32_t PITCH = mw_pitch(T, KB);
     constexpr uint32_t SBYTES = (uint32_t)TR::UBYTES * KB;   // bytes of a stage per row
     constexpr uint32_t SK = (uint32_t)TR::UK * KB;           // K values per stage
-    constexpr uint32_t STAGE = (uint32_t)R * PITCH;          // bytes per ring slot (a multiple of 256)
+    constexpr uint32_t HV = mw_halves(T, KB);                // copies (K halves) per stage
+    static_assert(HV == 1 || T != GT_Q6_K, "a Q6_K stage row fits one copy");
+    constexpr uint32_t STAGE = HV * (uint32_t)R * PITCH;     // bytes per ring slot (a multiple of 256)
     // activation conversion: one "piece" = the four values a lane feeds to one MMA; a warp has KB * MP * NM * 4 of
     // them per stage, spread over its 32 lanes in NPASS passes
     constexpr int PIECES = KB * MP * NM * 4;
@@ -248,9 +333,14 @@ __global__ void __launch_bounds__(kMwThreads, 2)
     constexpr uint32_t XST = (XCC + (uint32_t)NB * CCN * 8 + 15u) & ~15u;   // the pieces are read 16 bytes at a time
     constexpr float kOff = -(float)TR::OFFSET / 16777216.0f;
 
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    __shared__ __align__(8) uint64_t full[kMwMaxSlots], empty[kMwMaxSlots], fin[2];
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    uint8_t *smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);   // (tensor copies land on 128-byte boundaries)
+    __shared__ __align__(8) uint64_t full[kMwMaxSlots], fin[2];
+    __shared__ uint32_t rel[kMwMaxSlots];   // warps that have released the slot (counts up; a round is over at a multiple of 8)
+    // this CTA's items [s_lo, s_hi) of every problem (counted from the problem's first item) and the number of the
+    // CTA's first stage of the problem (s_q0[nprob]: all its stages)
+    __shared__ uint32_t s_lo[kMwMaxProbs], s_hi[kMwMaxProbs], s_q0[kMwMaxProbs + 1];
+    __shared__ __align__(8) uint64_t gbar;  // dependent launches: warp 0 tells the others that the grid barrier is through
     __shared__ volatile uint32_t abort_flag;
 
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -260,65 +350,89 @@ __global__ void __launch_bounds__(kMwThreads, 2)
         abort_flag = 0;
         for (uint32_t s = 0; s < c.nslots; s++) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kMwWarps);
+            rel[s] = 0;
         }
         mbar_init(&fin[0], kMwWarps);
         mbar_init(&fin[1], kMwWarps);
+        mbar_init(&gbar, 1);
         mbar_init_fence();
+    }
+    if (tid >= 32 && tid < 32 + bt.nprob) {
+        const uint32_t p2 = tid - 32;
+        const uint32_t b = bt.p[p2].item0, e = p2 + 1 < bt.nprob ? bt.p[p2 + 1].item0 : bt.nitems;
+        if (bt.dep_mask) {   // every problem's items spread over all CTAs
+            s_lo[p2] = (uint32_t)(((uint64_t)blockIdx.x * (e - b)) / gridDim.x);
+            s_hi[p2] = (uint32_t)(((uint64_t)(blockIdx.x + 1) * (e - b)) / gridDim.x);
+        } else {             // one contiguous chunk of the launch's item list
+            s_lo[p2] = max(g0, b) - b;
+            s_hi[p2] = max(min(g1, e), max(g0, b)) - b;
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t q = 0;
+        for (uint32_t p2 = 0; p2 < bt.nprob; p2++) {
+            s_q0[p2] = q;
+            q += (s_hi[p2] - s_lo[p2]) * bt.p[p2].spi;
+        }
+        s_q0[bt.nprob] = q;
     }
     __syncthreads();
     allow_dependents();   // the next overlapped launch may become resident and fetch its weights
 
     const uint32_t smem_base = smem_u32(smem);
+    // L2: the weights pass through once (first to go); the activations are read again by every item (last to go)
+    uint64_t pol_w, pol_x;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_w));
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_x));
 
-    if (warp == kMwWarps) {
-        // ======================= producer: one tensor copy (R rows x one stage) per ring slot =======================
-        if (lane == 0) {
-            if (!bt.early_weights) grid_dependency_wait();
-            uint32_t slot = 0, ph = 0, cidx = 0, p = 0;
-            bool ok = true;
-            for (uint32_t gi = g0; ok && gi < g1; gi++) {
-                while (p + 1 < bt.nprob && gi >= bt.p[p + 1].item0) p++;
-                const uint32_t item = gi - bt.p[p].item0, spi = bt.p[p].spi;
-                for (uint32_t s = 0; s < spi; s++, cidx++) {
-                    if (cidx >= c.nslots && !mbar_wait(&empty[slot], ph ^ 1u, &abort_flag, bt.status, ST_WAIT_EMPTY_TIMEOUT, 0u)) {
-                        ok = false;
-                        break;
-                    }
+    // The tensor copy (R rows x one stage) of the CTA's stage number q into ring slot `slot`.  There is no producer
+    // warp: thread 0 fills the ring at the start, and afterwards the warp that is the last to release a slot starts
+    // the copy of the stage that uses the slot next.
+    auto issue = [&](uint32_t q, uint32_t slot) {
+        if (q >= s_q0[bt.nprob]) return;
+        uint32_t p = 0;
+        while (q >= s_q0[p + 1]) p++;
+        const uint32_t spi = bt.p[p].spi, qq = q - s_q0[p];
+        const uint32_t item = s_lo[p] + qq / spi, s = qq % spi;
 #ifdef MLXN_EXPERIMENTS
-                    if (c.debug & 2u) {
-                        mbar_arrive(&full[slot]);
-                        if (++slot == c.nslots) { slot = 0; ph ^= 1u; }
-                        continue;
-                    }
+        if (c.debug & 2u) {
+            mbar_arrive(&full[slot]);
+            return;
+        }
 #endif
-                    mbar_expect_tx(&full[slot], STAGE);
-                    // coordinates in 8-byte elements; rows past n and bytes past the end of a row arrive as zeros
-                    if constexpr (PAIR) {
-                        const uint32_t row_bytes = (bt.p[p].k / 256u) * 210u;
-                        const uint32_t xe = ((s * SBYTES) & ~15u) >> 3, xo = ((row_bytes + s * SBYTES) & ~15u) >> 3;
-                        asm volatile(
-                            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                            ::"r"(smem_base + slot * STAGE), "l"(&maps.m[p]), "r"(xe), "r"(item * (uint32_t)(R / 2)), "r"(smem_u32(&full[slot]))
-                            : "memory");
-                        asm volatile(
-                            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                            ::"r"(smem_base + slot * STAGE + (R / 2) * PITCH), "l"(&maps.m[p]), "r"(xo), "r"(item * (uint32_t)(R / 2)),
-                              "r"(smem_u32(&full[slot]))
-                            : "memory");
-                    } else {
-                        const uint32_t x0 = ((s * SBYTES) & ~15u) >> 3;
-                        asm volatile(
-                            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                            ::"r"(smem_base + slot * STAGE), "l"(&maps.m[p]), "r"(x0), "r"(item * (uint32_t)R), "r"(smem_u32(&full[slot]))
-                            : "memory");
-                    }
-                    if (++slot == c.nslots) { slot = 0; ph ^= 1u; }
-                }
+        mbar_expect_tx(&full[slot], STAGE);
+        // coordinates in 8-byte elements; rows past n and bytes past the end of a row arrive as zeros
+        if constexpr (PAIR) {
+            const uint32_t row_bytes = (bt.p[p].k / 256u) * 210u;
+            const uint32_t xe = ((s * SBYTES) & ~15u) >> 3, xo = ((row_bytes + s * SBYTES) & ~15u) >> 3;
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+                ::"r"(smem_base + slot * STAGE), "l"(&maps.m[p]), "r"(xe), "r"(item * (uint32_t)(R / 2)), "r"(smem_u32(&full[slot])), "l"(pol_w)
+                : "memory");
+            asm volatile(
+                "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+                ::"r"(smem_base + slot * STAGE + (R / 2) * PITCH), "l"(&maps.m[p]), "r"(xo), "r"(item * (uint32_t)(R / 2)),
+                  "r"(smem_u32(&full[slot])), "l"(pol_w)
+                : "memory");
+        } else {
+#pragma unroll
+            for (uint32_t hv = 0; hv < HV; hv++) {
+                const uint32_t x0 = ((s * SBYTES + hv * (SBYTES / HV)) & ~15u) >> 3;
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
+                    ::"r"(smem_base + slot * STAGE + hv * (uint32_t)R * PITCH), "l"(&maps.m[p]), "r"(x0), "r"(item * (uint32_t)R),
+                      "r"(smem_u32(&full[slot])), "l"(pol_w)
+                    : "memory");
             }
         }
-        __syncwarp();
-    } else {
+    };
+    if (tid == 0) {
+        if (!bt.early_weights) grid_dependency_wait();
+        for (uint32_t q = 0; q < c.nslots; q++) issue(q, q);
+    }
+
+    {
         // ======================= consumers =======================
         const uint32_t g = lane >> 2, t = lane & 3u, w = warp;
         const uint32_t xst = smem_base + c.xst_off + w * XST;   // this warp's converted activations
@@ -329,10 +443,6 @@ __global__ void __launch_bounds__(kMwThreads, 2)
         // ---- geometry of the warp's units inside a stage ----
         // Q4_0 / Q8_0: blocks KB w .. KB w + KB - 1 of the stage's 8 KB; block b starts BB * b bytes into the row
         constexpr uint32_t BB = T == GT_Q8_0 ? 34u : 18u;
-        // blocks whose codes straddle the words (see mw_pairs): lanes 0..2 read one whole word, lane 3 the half words at
-        // either end of the block, joined by a byte permute
-        const uint32_t mhi = T == GT_Q8_0 ? 20u : 4u, mend = T == GT_Q8_0 ? 32u : 16u;
-        const uint32_t mo0 = t < 3 ? mhi + 4 * t : 0u, mo1 = t < 3 ? mhi + 4 * t : mend, msel = t < 3 ? 0x3210u : 0x5432u;
         // Q6_K: quarter (nh, js) of the super-blocks sp, sp + 2, ...; super-block sb starts lead + 210 sb bytes in
         const uint32_t sp = w >> 2, nh = (w >> 1) & 1u, js = w & 1u;
         const uint32_t q6A = 64 * nh + 16 * js + 4 * t, q6H = 128 + 32 * nh + 16 * js + 4 * t, q6S = 192 + 8 * nh + js;
@@ -364,13 +474,14 @@ __global__ void __launch_bounds__(kMwThreads, 2)
             }
         }
         // the problem being worked on
-        uint32_t cur = 0xFFFFFFFFu, spi = 1, pm = 0;
+        uint32_t cur = 0xFFFFFFFFu, spi = 1, pm = 0, pk = 0;
         const float *xsrc0[NPASS], *xsrc1[NPASS];
         bool xok[NPASS];
         auto set_problem = [&](uint32_t p) {
             cur = p;
             spi = bt.p[p].spi;
             pm = bt.p[p].m;
+            pk = bt.p[p].k;
 #pragma unroll
             for (int q = 0; q < NPASS; q++) {
                 xok[q] = xin[q] && xrow[q] < pm;
@@ -387,9 +498,9 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                 uint32_t ks = s0 + xso[p];
                 while (ks >= spi) ks -= spi;
                 float2 v0 = make_float2(0.f, 0.f), v1 = v0;
-                if (xok[p]) {
-                    v0 = __ldcg(reinterpret_cast<const float2 *>(xsrc0[p] + (size_t)ks * SK));
-                    v1 = __ldcg(reinterpret_cast<const float2 *>(xsrc1[p] + (size_t)ks * SK));
+                if (xok[p] && ks * SK + xrel0[p] < pk) {   // (the last stage of a row may reach past K: zeros there)
+                    asm volatile("ld.global.cg.L2::cache_hint.v2.f32 {%0, %1}, [%2], %3;" : "=f"(v0.x), "=f"(v0.y) : "l"(xsrc0[p] + (size_t)ks * SK), "l"(pol_x));
+                    asm volatile("ld.global.cg.L2::cache_hint.v2.f32 {%0, %1}, [%2], %3;" : "=f"(v1.x), "=f"(v1.y) : "l"(xsrc1[p] + (size_t)ks * SK), "l"(pol_x));
                 }
                 xr[p][0] = v0.x; xr[p][1] = v0.y; xr[p][2] = v1.x; xr[p][3] = v1.y;
             }
@@ -420,33 +531,76 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                     // (the pieces of a scale group are consecutive, and PIECES is a multiple of the group size, so
                     //  bp / group size = so CCN + the group's index inside its stage)
                     if constexpr (T == GT_Q6_K) {
-                        if ((bp & 3u) == 0) sts64(xcc + (bp >> 2) * 8, __float_as_uint(kOff * (s * sum)), __float_as_uint(inv));
+                        if ((bp & 3u) == 0) sts64(xcc + (bp >> 2) * 8, __float_as_uint(kOff * sum), __float_as_uint(inv));
                     } else {
-                        if ((bp & 7u) == 0) sts64(xcc + (bp >> 3) * 8, __float_as_uint(kOff * (s * sum)), __float_as_uint(inv));
+                        if ((bp & 7u) == 0) sts64(xcc + (bp >> 3) * 8, __float_as_uint(kOff * sum), __float_as_uint(inv));
                     }
                 }
             }
         };
 
-        float acc[TPW][4];
+        // [tile][set][hi and lo partial sums of weight row g, of weight row g + 8] for activation row t + 4 set
+        float acc[TPW][NS][4];
 #pragma unroll
-        for (int j = 0; j < TPW; j++) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        for (int j = 0; j < TPW; j++)
+#pragma unroll
+            for (int ns = 0; ns < NS; ns++) acc[j][ns][0] = acc[j][ns][1] = acc[j][ns][2] = acc[j][ns][3] = 0.f;
 
         grid_dependency_wait();   // the activations belong to the kernels ahead until they are done
 
         uint32_t slot = 0, ph = 0, fin_ph = 0, bi = 0;   // bi: stage inside the conversion batch
-        uint32_t p = 0;
+        uint32_t qn = 0;                                 // the CTA's stages so far
+        uint32_t gb_ph = 0;
         bool ok = true, first_item = true;
-        for (uint32_t gi = g0; ok && gi < g1; gi++) {
-            while (p + 1 < bt.nprob && gi >= bt.p[p + 1].item0) p++;
+        for (uint32_t p = 0; ok && p < bt.nprob; p++) {
+        const uint32_t item_lo = s_lo[p], item_hi = s_hi[p];
+        if ((bt.dep_mask >> p) & 1u) {
+            // The problem reads or overwrites results of the problems before it.  Every CTA reports, once, that its
+            // share of those is written (also the CTAs that have no items here), then waits for all the others.
+            if (warp == 0) {
+                if (!first_item && !mbar_wait(&fin[1], fin_ph ^ 1u, &abort_flag, bt.status, ST_WAIT_EMPTY_TIMEOUT, 0u)) ok = false;
+                if (ok && lane == 0) {
+                    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(bt.bar + p) : "memory");
+                    if (item_hi > item_lo) {   // one thread per CTA watches the counter; the other warps wait in shared memory
+                        uint64_t t0 = 0;
+                        for (uint32_t polls = 1;; polls++) {
+                            uint32_t v;
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(bt.bar + p) : "memory");
+                            if (v >= gridDim.x) break;
+                            __nanosleep(40);
+                            if ((polls & 63u) == 0) {
+                                if (abort_flag) break;
+                                const uint64_t now = global_timer_ns();
+                                if (t0 == 0) t0 = now;
+                                else if (now - t0 > kWaitLimitNs) {
+                                    abort_flag = 1;
+                                    if (bt.status) atomicCAS(bt.status, 0u, (uint32_t)ST_WAIT_GRID_TIMEOUT);
+                                    break;
+                                }
+                            }
+                        }
+                        mbar_arrive(&gbar);
+                    }
+                }
+                __syncwarp();
+            }
+            if (item_hi > item_lo) {
+                if (!mbar_wait(&gbar, gb_ph, &abort_flag, bt.status, ST_WAIT_GRID_TIMEOUT, 0u) || abort_flag) ok = false;
+                gb_ph ^= 1u;
+            }
+        }
+        for (uint32_t item = item_lo; ok && item < item_hi; item++) {
             if (p != cur) {   // first item, or the next mat-vec of the launch: its activations from K = 0
                 set_problem(p);
                 load_x(0);
                 bi = 0;
             }
-            const uint32_t item = gi - bt.p[p].item0;
             for (uint32_t s = 0; ok && s < spi; s++) {
+#ifdef MLXN_EXPERIMENTS
+                if (bi == 0 && !(c.debug & 4u)) {
+#else
                 if (bi == 0) {
+#endif
                     __syncwarp();           // the previous batch's pieces have all been fetched
                     convert_x();
                     __syncwarp();
@@ -463,7 +617,12 @@ __global__ void __launch_bounds__(kMwThreads, 2)
 #ifdef MLXN_EXPERIMENTS
                 if (c.debug & 1u) {
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&empty[slot]);
+                    if (lane == 0) {   // the last of the eight warps to let go of the slot starts the copy of the stage that gets it next
+                        uint32_t old;
+                        asm volatile("atom.acq_rel.cta.shared.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(smem_u32(&rel[slot])) : "memory");
+                        if ((old & (uint32_t)(kMwWarps - 1)) == (uint32_t)(kMwWarps - 1)) issue(qn + c.nslots, slot);
+                    }
+                    qn++;
                     if (++slot == c.nslots) { slot = 0; ph ^= 1u; }
                     continue;
                 }
@@ -472,6 +631,9 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                 if constexpr (T == GT_Q6_K) {
                     lead = (s * SBYTES) & 15u;   // a multiple of 4
                     // d * sub-scale of the warp's scale groups, for every row of the stage (lanes split the rows)
+#ifdef MLXN_EXPERIMENTS
+                    if (!(c.debug & 8u))
+#endif
 #pragma unroll
                     for (int i = 0; i < KB; i++) {
 #pragma unroll
@@ -493,118 +655,145 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                     __syncwarp();
                 }
 
-#pragma unroll
-                for (int i = 0; i < KB; i++) {
-                    // ---- the unit's B registers (lanes g < MP hold activation row g) and accumulator starts ----
-                    uint32_t bf[NM][4];
-#pragma unroll
-                    for (int h = 0; h < NM; h++) {
-                        bf[h][0] = bf[h][1] = bf[h][2] = bf[h][3] = 0u;
-                        if (g < (uint32_t)MP) lds128(xsb + ((((i * MP + g) * NM + h) * 4 + t) * 16), bf[h][0], bf[h][1], bf[h][2], bf[h][3]);
-                    }
-                    // cq: what the accumulators of a scale group start from, columns 2t and 2t + 1 (-offset sum(x));
-                    // cs0 / cs1: the columns' inverse pre-scales.  Columns past m hold zeros throughout, so with one
-                    // activation row the second column's scale is never looked at.
-                    float cq[NG][4], cs0[NG], cs1[NG];
-#pragma unroll
-                    for (int q = 0; q < NG; q++) {
-                        float c0 = 0.f, c1 = 0.f;
-                        cs0[q] = cs1[q] = 0.f;
-                        if (2 * t < (uint32_t)MP) {
-                            uint32_t u0, u1;
-                            lds64(xcb + ((i * MP + 2 * t) * NG + q) * 8, u0, u1);
-                            c0 = __uint_as_float(u0);
-                            cs0[q] = __uint_as_float(u1);
-                        }
-                        if (MP > 1 && 2 * t + 1 < (uint32_t)MP) {
-                            uint32_t u0, u1;
-                            lds64(xcb + ((i * MP + 2 * t + 1) * NG + q) * 8, u0, u1);
-                            c1 = __uint_as_float(u0);
-                            cs1[q] = __uint_as_float(u1);
-                        }
-                        cq[q][0] = c0; cq[q][1] = c1; cq[q][2] = c0; cq[q][3] = c1;
-                    }
-
-                    if constexpr (T == GT_Q6_K) {
-                        // row g of the stage, this unit's super-block; odd super-blocks start 2 bytes past a 4-byte boundary:
-                        // their words are read from the 4-byte boundary below and shifted by a byte permute
+                // this lane's converted activations: column g of an MMA = (activation row g / 2, hi or lo half); the rows are
+                // wrapped, the columns past 2 m are never looked at.  Its outputs belong to activation row t (+ 4 per set).
+                const uint32_t xlane = xsb + ((((g >> 1) & (uint32_t)(MP - 1)) * NM * 4 + t) * 16) + (g & 1u) * 8;
+                const uint32_t clane = xcb + (t & (uint32_t)(MP - 1)) * (NG * 8);
+                if constexpr (T == GT_Q6_K) {
+                    // odd super-blocks start 2 bytes past a 4-byte boundary: their words are read from the boundary below
+                    // and shifted by a byte permute (ODD).  The parity is the warp's, so the branch sits outside the loops.
+                    auto body = [&](auto ODDC) {
+                        constexpr bool ODD = decltype(ODDC)::value;
+                        const float zz[4] = {0.f, 0.f, 0.f, 0.f};
+                        // row g of the stage, the warp's first super-block
                         const uint32_t u6 = (PAIR ? stage + ((g & 1u) * (R / 2) + (g >> 1)) * PITCH + (lead ^ (8u * (g & 1u)))
-                                                  : stage + g * PITCH + lead) + 210 * (sp + 2 * i) - 2 * sp;
-                        const uint32_t pA = u6 + q6A, pH = u6 + q6H, pP = ptab + (i * R + g) * 16;
+                                                  : stage + g * PITCH + lead) + 208 * sp;
+                        const uint32_t pA = u6 + q6A, pH = u6 + q6H, pP = ptab + g * 16;
+                        static_for<0, KB>([&](auto IC) {
+                            constexpr uint32_t i = decltype(IC)::value;
+                            uint32_t bf[NS][4][2];
+                            float cc[NS][4], cs[NS][4];
+                            static_for<0, NS>([&](auto SC) {
+                                constexpr uint32_t ns = decltype(SC)::value;
+                                static_for<0, 4>([&](auto QC) {
+                                    constexpr uint32_t q = decltype(QC)::value;
+                                    lds64i<(((i * MP + 4 * ns) * 4 + q) * 64)>(xlane, bf[ns][q][0], bf[ns][q][1]);
+                                    uint32_t u0, u1;
+                                    lds64i<(((i * MP + 4 * ns) * 4 + q) * 8)>(clane, u0, u1);
+                                    cc[ns][q] = __uint_as_float(u0);
+                                    cs[ns][q] = __uint_as_float(u1);
+                                });
+                            });
+                            static_for<0, TPW>([&](auto JC) {
+                                constexpr uint32_t j = decltype(JC)::value;
+                                uint32_t qv[2][4];   // [row g / g + 8][q1..q4]: four 6-bit codes each, one per byte
+                                uint32_t pv[2][4];
+                                static_for<0, 2>([&](auto HC) {
+                                    constexpr uint32_t h = decltype(HC)::value;
+                                    constexpr uint32_t off = (PAIR ? 8 * j + 4 * h : 16 * j + 8 * h) * PITCH + 420 * i;   // rows g, g + 8 of tile j
+                                    uint32_t A, B, H;
+                                    if constexpr (!ODD) {
+                                        A = lds32i<off>(pA);
+                                        B = lds32i<off + 32>(pA);
+                                        H = lds32i<off>(pH);
+                                    } else {
+                                        A = __byte_perm(lds32i<off>(pA), lds32i<off + 4>(pA), 0x5432);
+                                        B = __byte_perm(lds32i<off + 32>(pA), lds32i<off + 36>(pA), 0x5432);
+                                        H = __byte_perm(lds32i<off>(pH), lds32i<off + 4>(pH), 0x5432);
+                                    }
+                                    qv[h][0] = (A & 0x0F0F0F0Fu) | ((H & 0x03030303u) << 4);
+                                    qv[h][1] = (B & 0x0F0F0F0Fu) | ((H & 0x0C0C0C0Cu) << 2);
+                                    qv[h][2] = ((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u);
+                                    qv[h][3] = ((B >> 4) & 0x0F0F0F0Fu) | ((H & 0xC0C0C0C0u) >> 2);
+                                    lds128i<((i * R) + 16 * j + 8 * h) * 16>(pP, pv[h][0], pv[h][1], pv[h][2], pv[h][3]);
+                                });
 #pragma unroll
-                        for (int j = 0; j < TPW; j++) {
-                            uint32_t qv[2][4];   // [row g / g + 8][q1..q4]: four 6-bit codes each, one per byte
-                            uint32_t pv[2][4];
+                                for (int q = 0; q < 4; q++) {
+                                    const uint32_t a0 = __byte_perm(qv[0][q], 0u, 0x4240), a2 = __byte_perm(qv[0][q], 0u, 0x4341);
+                                    const uint32_t a1 = __byte_perm(qv[1][q], 0u, 0x4240), a3 = __byte_perm(qv[1][q], 0u, 0x4341);
+                                    const float pa = __uint_as_float(pv[0][q]), pb = __uint_as_float(pv[1][q]);
 #pragma unroll
-                            for (int h = 0; h < 2; h++) {
-                                const uint32_t off = (PAIR ? 8 * j + 4 * h : 16 * j + 8 * h) * PITCH;   // rows g, g + 8 of tile j
-                                uint32_t A, B, H;
-                                if (sp == 0) {
-                                    A = lds32(pA + off);
-                                    B = lds32(pA + off + 32);
-                                    H = lds32(pH + off);
-                                } else {
-                                    A = __byte_perm(lds32(pA + off), lds32(pA + off + 4), 0x5432);
-                                    B = __byte_perm(lds32(pA + off + 32), lds32(pA + off + 36), 0x5432);
-                                    H = __byte_perm(lds32(pH + off), lds32(pH + off + 4), 0x5432);
+                                    for (int ns = 0; ns < NS; ns++) {
+                                        float d[4];
+                                        mma16816(d, a0, a1, a2, a3, bf[ns][q][0], bf[ns][q][1], zz);
+                                        const float ta = pa * cs[ns][q], tb = pb * cs[ns][q];
+                                        acc[j][ns][0] = fmaf(ta, d[0], fmaf(pa, cc[ns][q], acc[j][ns][0]));
+                                        acc[j][ns][1] = fmaf(ta, d[1], acc[j][ns][1]);
+                                        acc[j][ns][2] = fmaf(tb, d[2], fmaf(pb, cc[ns][q], acc[j][ns][2]));
+                                        acc[j][ns][3] = fmaf(tb, d[3], acc[j][ns][3]);
+                                    }
                                 }
-                                qv[h][0] = (A & 0x0F0F0F0Fu) | ((H & 0x03030303u) << 4);
-                                qv[h][1] = (B & 0x0F0F0F0Fu) | ((H & 0x0C0C0C0Cu) << 2);
-                                qv[h][2] = ((A >> 4) & 0x0F0F0F0Fu) | (H & 0x30303030u);
-                                qv[h][3] = ((B >> 4) & 0x0F0F0F0Fu) | ((H & 0xC0C0C0C0u) >> 2);
-                                lds128(pP + (16 * j + 8 * h) * 16, pv[h][0], pv[h][1], pv[h][2], pv[h][3]);
-                            }
-#pragma unroll
-                            for (int q = 0; q < 4; q++) {
-                                const uint32_t a0 = __byte_perm(qv[0][q], 0u, 0x4240), a2 = __byte_perm(qv[0][q], 0u, 0x4341);
-                                const uint32_t a1 = __byte_perm(qv[1][q], 0u, 0x4240), a3 = __byte_perm(qv[1][q], 0u, 0x4341);
-                                float d[4];
-                                mma16816(d, a0, a1, a2, a3, bf[q][0], bf[q][1], cq[q]);
-                                mma16816(d, a0, a1, a2, a3, bf[q][2], bf[q][3], d);
-                                const float pa = __uint_as_float(pv[0][q]), pb = __uint_as_float(pv[1][q]);
-                                if constexpr (MP == 1) {
-                                    const float fa = pa * cs0[q], fb = pb * cs0[q];
-                                    acc[j][0] = fmaf(fa, d[0], acc[j][0]);
-                                    acc[j][2] = fmaf(fb, d[2], acc[j][2]);
-                                } else {
-                                    acc[j][0] = fmaf(pa * cs0[q], d[0], acc[j][0]);
-                                    acc[j][1] = fmaf(pa * cs1[q], d[1], acc[j][1]);
-                                    acc[j][2] = fmaf(pb * cs0[q], d[2], acc[j][2]);
-                                    acc[j][3] = fmaf(pb * cs1[q], d[3], acc[j][3]);
-                                }
-                            }
-                        }
-                    } else {
-                        // rows g and g + 8 of tile j sit (16 j + 8 h) PITCH bytes past row g of the stage
-                        const uint32_t b = KB * w + i, rb0 = stage + g * PITCH + BB * b;
-                        if ((b & 1u) == 0)
-                            mw_block_tiles<T, TPW, MP, PITCH, true>(rb0, rb0 + 4 + 4 * t, rb0 + mo0, rb0 + mo1, msel, bf, cq[0], cs0[0], cs1[0], acc);
-                        else
-                            mw_block_tiles<T, TPW, MP, PITCH, false>(rb0, rb0 + 2 + 4 * t, rb0 + 18 + 4 * t, 0u, 0u, bf, cq[0], cs0[0], cs1[0], acc);
-                    }
+                            });
+                        });
+                    };
+                    if (sp) body(std::true_type{});
+                    else body(std::false_type{});
+                } else {
+                    // the warp's blocks KB w .. KB w + KB - 1 of the stage, two at a time (KB is even: the first of a pair
+                    // starts on a 4-byte boundary); rows g and g + 8 of tile j sit (16 j + 8 h) PITCH bytes further on
+                    const uint32_t rb = stage + (HV == 2 ? (w >> 2) * ((uint32_t)R * PITCH) : 0u) + g * PITCH + BB * KB * (HV == 2 ? (w & 3u) : w);
+                    const uint32_t base = rb + 4 * t, base2 = rb + (t ? 4 * t : (T == GT_Q8_0 ? 32u : 16u));
+                    const uint32_t sel = t ? 0x3210u : 0x5432u;
+                    static_for<0, KB / 2>([&](auto IC) {
+                        constexpr uint32_t i = 2 * decltype(IC)::value;
+                        uint32_t bf0[NS][2][2], bf1[NS][2][2];
+                        float cc[NS][2], cs[NS][2];
+                        static_for<0, NS>([&](auto SC) {
+                            constexpr uint32_t ns = decltype(SC)::value;
+                            static_for<0, 2>([&](auto HC) {
+                                constexpr uint32_t h = decltype(HC)::value;
+                                lds64i<((i * MP + 4 * ns) * 2 + h) * 64>(xlane, bf0[ns][h][0], bf0[ns][h][1]);
+                                lds64i<(((i + 1) * MP + 4 * ns) * 2 + h) * 64>(xlane, bf1[ns][h][0], bf1[ns][h][1]);
+                            });
+                            uint32_t u0, u1, v0, v1;
+                            lds64i<(i * MP + 4 * ns) * 8>(clane, u0, u1);
+                            lds64i<((i + 1) * MP + 4 * ns) * 8>(clane, v0, v1);
+                            cc[ns][0] = __uint_as_float(u0);
+                            cs[ns][0] = __uint_as_float(u1);
+                            cc[ns][1] = __uint_as_float(v0);
+                            cs[ns][1] = __uint_as_float(v1);
+                        });
+                        mw_pair_tiles<T, TPW, MP, NS, PITCH, BB * i>(base, base2, rb, sel, bf0, bf1, cc, cs, acc);
+                    });
                 }
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[slot]);
+                if (lane == 0) {   // the last of the eight warps to let go of the slot starts the copy of the stage that gets it next
+                    uint32_t old;
+                    asm volatile("atom.acq_rel.cta.shared.add.u32 %0, [%1], 1;" : "=r"(old) : "r"(smem_u32(&rel[slot])) : "memory");
+                    if ((old & (uint32_t)(kMwWarps - 1)) == (uint32_t)(kMwWarps - 1)) issue(qn + c.nslots, slot);
+                }
+                qn++;
                 if (++slot == c.nslots) { slot = 0; ph ^= 1u; }
             }
             if (!ok) break;
 
             // ---- end of the item: add the eight warps' partial sums in a fixed order and write the rows out ----
             if (!first_item) {   // the previous item's sums have all been read
-                if (!mbar_wait(&fin[1], fin_ph ^ 1u, &abort_flag, bt.status, ST_WAIT_EMPTY_TIMEOUT, 0u)) break;
+                if (!mbar_wait(&fin[1], fin_ph ^ 1u, &abort_flag, bt.status, ST_WAIT_EMPTY_TIMEOUT, 0u)) {
+                    ok = false;
+                    break;
+                }
             }
 #pragma unroll
             for (int j = 0; j < TPW; j++) {
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const uint32_t col = 2 * t + (i & 1), row = 16 * j + g + 8 * (i >> 1);
-                    if (col < (uint32_t)MP) sts32(red + ((w * MP + col) * R + row) * 4, __float_as_uint(acc[j][i] * 16777216.0f));
-                    acc[j][i] = 0.f;
+                for (int ns = 0; ns < NS; ns++) {
+                    const uint32_t col = t + 4 * ns;
+#pragma unroll
+                    for (int i = 0; i < 2; i++) {
+                        const uint32_t row = 16 * j + g + 8 * i;
+                        if (col < (uint32_t)MP)
+                            sts32(red + ((w * MP + col) * R + row) * 4, __float_as_uint((acc[j][ns][2 * i] + acc[j][ns][2 * i + 1]) * 16777216.0f));
+                        acc[j][ns][2 * i] = acc[j][ns][2 * i + 1] = 0.f;
+                    }
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&fin[0]);
-            if (!mbar_wait(&fin[0], fin_ph, &abort_flag, bt.status, ST_WAIT_EMPTY_TIMEOUT, 0u)) break;
+            if (!mbar_wait(&fin[0], fin_ph, &abort_flag, bt.status, ST_WAIT_EMPTY_TIMEOUT, 0u)) {
+                ok = false;
+                break;
+            }
             {
                 const MwProb &P = bt.p[p];
                 const uint32_t ld = P.y_ld ? P.y_ld : P.n;
@@ -626,9 +815,22 @@ __global__ void __launch_bounds__(kMwThreads, 2)
             fin_ph ^= 1u;
             first_item = false;
         }
+        }
     }
     if (abort_flag) {  // let copies in flight land before the CTA's shared memory is released
         for (int i = 0; i < 200; i++) __nanosleep(5000);
+    }
+    if (bt.dep_mask) {
+        // the last CTA to leave clears the barrier words for the next launch that uses them (launches that share
+        // them are ordered by their stream)
+        __syncthreads();
+        if (tid == 0) {
+            const uint32_t old = atomicAdd(bt.bar + 31, 1u);
+            if (old == gridDim.x - 1) {
+                for (uint32_t i = 0; i < 32; i++) bt.bar[i] = 0;
+                __threadfence();
+            }
+        }
     }
 }
 
@@ -660,7 +862,7 @@ static inline size_t mw_align(size_t v, size_t al) { return (v + al - 1) / al * 
 template <int T, int TPW, int KB, int MP, bool PAIR>
 static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, cudaStream_t st) {
     using TR = MwTraits<T>;
-    constexpr uint32_t R = 16 * TPW, PITCH = mw_pitch(T, KB), STAGE = R * PITCH;
+    constexpr uint32_t R = 16 * TPW, PITCH = mw_pitch(T, KB), STAGE = mw_halves(T, KB) * R * PITCH;
     constexpr uint32_t PIECES = KB * MP * TR::NM * 4, NB = PIECES >= 32 ? 1 : 32 / PIECES;
     constexpr uint32_t XST = (NB * PIECES * 16 + NB * KB * MP * TR::NG * 8 + 15u) & ~15u;   // as in the kernel
     MwCfg c{};
@@ -671,15 +873,16 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
     const size_t ptab_bytes = T == GT_Q6_K ? (size_t)kMwWarps * R * 16 * KB : 0;
     const size_t red_bytes = (size_t)kMwWarps * MP * R * 4;
     const size_t tail = xst_bytes + ptab_bytes + red_bytes;
-    const size_t budget = 110 * 1024;   // two CTAs per SM
-    uint32_t nslots = (uint32_t)((budget - tail - 1024) / STAGE);
+    // two CTAs per SM: 228 KB, less 1 KB per CTA for the system and the kernel's few hundred bytes of static storage
+    const size_t budget = 115200;
+    uint32_t nslots = (uint32_t)((budget - tail - 128) / STAGE);
     if (nslots > (uint32_t)kMwMaxSlots) nslots = kMwMaxSlots;
     if (nslots < 2) return cudaErrorInvalidConfiguration;
     c.nslots = nslots;
     c.xst_off = nslots * STAGE;
     c.ptab_off = c.xst_off + (uint32_t)xst_bytes;
     c.red_off = c.ptab_off + (uint32_t)ptab_bytes;
-    const size_t smem = (size_t)c.red_off + red_bytes + 1024;
+    const size_t smem = (size_t)c.red_off + red_bytes + 128;
 
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return cudaErrorNotSupported;
@@ -699,7 +902,7 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
         P.n = a.n;
         P.k = a.k;
         P.m = a.m;
-        P.spi = a.k / (TR::UK * KB);
+        P.spi = (a.k + TR::UK * KB - 1) / (TR::UK * KB);   // the last stage may reach past K: the copy fills zeros
         P.item0 = items;
         P.y_ld = a.y_ld;
         P.y_col0 = a.y_col0;
@@ -721,6 +924,16 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
+    bt.nitems = items;
+    bt.dep_mask = 0;
+    bt.bar = ops[0].grid_bar;
+    uint32_t max_items = 0;
+    for (int i = 0; i < nops; i++) {
+        if (i > 0 && ops[i].after_earlier) bt.dep_mask |= 1u << i;
+        const uint32_t its = (ops[i].n + R - 1) / R;
+        if (its > max_items) max_items = its;
+    }
+    if (bt.dep_mask && !bt.bar) return cudaErrorInvalidValue;
     for (int i = nops; i < kMwMaxProbs; i++) {
         bt.p[i] = MwProb{};
         bt.p[i].item0 = items;
@@ -728,7 +941,7 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
     }
     uint32_t grid = (uint32_t)(sm_count * ctas_per_sm);
     if (grid > (uint32_t)kMwMaxGrid) grid = kMwMaxGrid;
-    if (grid > items) grid = items;
+    if (grid > (bt.dep_mask ? max_items : items)) grid = bt.dep_mask ? max_items : items;
     // contiguous chunks of items holding (nearly) the same number of stages each: CTA c starts at the first item whose
     // stages begin at or after c / grid of all the launch's stages
     {
@@ -760,23 +973,31 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
         if (e != cudaSuccess) return e;
         attr_smem[dev] = smem;
     }
+    if (bt.dep_mask)   // its CTAs wait on one another: all of them resident at once, or the launch is refused
+        return launch_cooperative(qmv_mma_kernel<T, TPW, KB, MP, PAIR>, dim3(grid), dim3(kMwThreads), smem, st, bt, c, maps);
     return launch_overlapped(qmv_mma_kernel<T, TPW, KB, MP, PAIR>, dim3(grid), dim3(kMwThreads), smem, st, bt, c, maps);
 }
 
 // (TPW, KB): a warp works on TPW x KB tile-units per stage.  Few weight rows -> narrow row groups and long K stages.
-// The activation split costs MP x KB per stage and warp whatever TPW is, so many activation rows want KB = 1.
+// Q4_0 / Q8_0 blocks are worked on in pairs (KB even).  The activation split costs MP x KB per stage and warp whatever
+// TPW is, so many activation rows want a small KB.
 template <int T, int MP, bool PAIR>
 static cudaError_t launch_mw_m(const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
-    uint32_t units_gcd = 4;   // KB must divide every problem's number of K units
-    for (int i = 0; i < nops; i++) {
-        const uint32_t u = ops[i].k / MwTraits<T>::UK;
-        if (u % 4 != 0) units_gcd = u % 2 == 0 ? (units_gcd < 2 ? units_gcd : 2) : 1;
+    if constexpr (T == GT_Q6_K) {
+        if (tpw >= 4 || MP == 8) return launch_mw<T, 4, 1, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
+        if constexpr (MP <= 4) {
+            if (tpw >= 2 || MP == 4) return launch_mw<T, 2, 2, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
+        }
+        if constexpr (MP <= 2) return launch_mw<T, 1, 4, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
+    } else {
+        if constexpr (MP == 8) return launch_mw<T, 2, 2, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
+        if constexpr (MP <= 4) {
+            if (tpw >= 4) return launch_mw<T, 4, 2, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
+            if (tpw >= 2) return launch_mw<T, 2, 4, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
+        }
+        if constexpr (MP == 4) return launch_mw<T, 1, 4, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
+        if constexpr (MP <= 2) return launch_mw<T, 1, 8, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
     }
-    if (tpw >= 4 || MP == 8 || units_gcd < 2) return launch_mw<T, 4, 1, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
-    if constexpr (MP <= 4) {
-        if (tpw >= 2 || MP == 4 || units_gcd < 4) return launch_mw<T, 2, 2, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
-    }
-    if constexpr (MP <= 2) return launch_mw<T, 1, 4, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
     return cudaErrorInvalidConfiguration;
 }
 
@@ -806,15 +1027,19 @@ static cudaError_t launch_mw_t(const QmvArgs *ops, int nops, uint32_t mmax, int 
 cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
     if (ctas_per_sm < 1) ctas_per_sm = 1;
     if (ctas_per_sm > 2) ctas_per_sm = 2;
-    uint64_t rows = 0;
+    uint64_t rows = 0, rows_min = ~0ull;
     uint32_t mmax = 1;
+    bool dep = false;
     for (int i = 0; i < nops; i++) {
         rows += ops[i].n;
+        if (ops[i].n < rows_min) rows_min = ops[i].n;
         if (ops[i].m > mmax) mmax = ops[i].m;
+        if (i > 0 && ops[i].after_earlier) dep = true;
     }
+    if (dep) rows = rows_min;   // every mat-vec of a dependent launch has the whole grid to itself
     if (tpw <= 0) {
-        // the largest row group that still gives every CTA slot an item
-        tpw = rows >= 64ull * 2 * (uint32_t)sm_count ? 4 : rows >= 32ull * 2 * (uint32_t)sm_count ? 2 : 1;
+        // measured: 64-row groups from 8192 rows on (every other CTA slot still gets one), 16-row groups below
+        tpw = rows >= 8192 ? 4 : 1;
     }
     switch (ggml_type) {
     case GT_Q4_0: return launch_mw_t<GT_Q4_0>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);

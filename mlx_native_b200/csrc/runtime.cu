@@ -91,6 +91,9 @@ void mlxn_detail_count_launches(int launches) {
 static std::atomic<int> g_opt_qmv{-1}, g_opt_qmm{-1};  // -1 unset; qmv: 0 simple, 1 stream, 2 tc, 3 auto, 4 mma; qmm: 0 simt, 1 tc
 static std::atomic<int> g_opt_mma_ctas{2}, g_opt_mma_tpw{0};   // tuning knobs of the register-level mat-vec
 static std::atomic<int> g_opt_mv_batch{1};                     // coalesce conflict-free mat-vecs into one launch
+// ... and mat-vecs that depend on one another (barriers inside the launch).  Off by default: measured on B200 a barrier
+// across the grid costs about a microsecond more than the overlapped launch of a separate kernel.
+static std::atomic<int> g_opt_mv_chain{0};
 static int opt_qmv() {
     int v = g_opt_qmv.load();
     if (v < 0) {
@@ -277,6 +280,7 @@ struct mlxn_encoder {
     int pend_type = 0, pend_lane = 0;
     uint32_t pend_mp = 0;
     bool pend_pair = false;
+    bool grp_pend_only = false;       // every operation of the current group is in `pend` (none has been launched yet)
     uint32_t *status_host = nullptr;  // pinned
 };
 
@@ -340,6 +344,12 @@ extern "C" int mlxn_set_option(const char *key, const char *value) {
         if (strcmp(value, "0") != 0 && strcmp(value, "1") != 0)
             return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: qmv_batch must be '0' or '1'");
         g_opt_mv_batch = value[0] == '1';
+        return MLXN_OK;
+    }
+    if (strcmp(key, "qmv_chain") == 0) {
+        if (strcmp(value, "0") != 0 && strcmp(value, "1") != 0)
+            return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: qmv_chain must be '0' or '1'");
+        g_opt_mv_chain = value[0] == '1';
         return MLXN_OK;
     }
     if (strcmp(key, "qmv_mma_ctas") == 0 || strcmp(key, "qmv_mma_tpw") == 0) {
@@ -879,16 +889,16 @@ static int encoder_flush_pending(mlxn_encoder *e) {
     int launches = 1, rc = MLXN_OK;
     // A mat-vec that ended up alone (the next operation depended on it, or nothing followed) gains nothing from the
     // batched kernel's shared work list; with "auto" it takes the kernel that is fastest for a lone call of its kind.
+    e->grp_pend_only = false;   // (what is launched here stays part of the group until the lanes are joined)
+    // barrier words of a launch whose mat-vecs depend on one another: one set per lane (launches of a lane are ordered)
+    for (QmvArgs &a : e->pend) a.grid_bar = e->status_dev + 1024 + 32 * e->pend_lane;
     const QmvArgs &a0 = e->pend[0];
-    const bool lone_other = e->pend.size() == 1 && opt_qmv() == 3 && a0.n_peer == 0 &&
-                            (e->pend_type == GT_Q6_K || a0.m > 2);
+    // (measured: one or two activation rows stay with this kernel, except one Q6_K row on a small matrix, where the
+    //  streaming kernel's short start wins; more rows take the tensor-memory kernel, whose time does not grow with m)
+    const bool q6_one_row_small = e->pend_type == GT_Q6_K && a0.m == 1 && (uint64_t)a0.n * a0.k < (1ull << 23);
+    const bool lone_other = e->pend.size() == 1 && opt_qmv() == 3 && a0.n_peer == 0 && (q6_one_row_small || a0.m > 2);
     if (lone_other) {
-        // (one Q6_K row: the streaming kernel, except on matrices so large that the launch overhead no longer shows)
-        const bool q6_one_row_small = e->pend_type == GT_Q6_K && a0.m == 1 && (uint64_t)a0.n * a0.k < (1ull << 27);
-        const bool q6_one_row_large = e->pend_type == GT_Q6_K && a0.m == 1 && !q6_one_row_small;
-        if (q6_one_row_large) {
-            err = launch_qmv_mma(e->pend_type, &a0, 1, e->dev->sm_count, g_opt_mma_ctas.load(), g_opt_mma_tpw.load(), st);
-        } else if (!q6_one_row_small && qmv_tc_supported(e->pend_type, a0)) {
+        if (!q6_one_row_small && qmv_tc_supported(e->pend_type, a0)) {
             uint8_t *scratch = nullptr;
             if ((rc = encoder_scratch_on(e, e->pend_lane, qmv_tc_scratch_bytes(a0), &scratch)) == MLXN_OK) {
                 launches = 0;
@@ -901,6 +911,18 @@ static int encoder_flush_pending(mlxn_encoder *e) {
     } else {
         err = launch_qmv_mma(e->pend_type, e->pend.data(), (int)e->pend.size(), e->dev->sm_count, g_opt_mma_ctas.load(),
                              g_opt_mma_tpw.load(), st);
+        if (err == cudaErrorCooperativeLaunchTooLarge) {
+            // the device cannot hold the whole grid at once (it is shared): the chained mat-vecs leave one by one
+            (void)cudaGetLastError();
+            err = cudaSuccess;
+            launches = 0;
+            for (QmvArgs &a : e->pend) {
+                a.after_earlier = 0;
+                if (err == cudaSuccess)
+                    err = launch_qmv_mma(e->pend_type, &a, 1, e->dev->sm_count, g_opt_mma_ctas.load(), g_opt_mma_tpw.load(), st);
+                launches++;
+            }
+        }
     }
     e->pend.clear();
     for (mlxn_buffer *b : e->retained) {
@@ -989,6 +1011,7 @@ static const char *status_text(uint32_t s) {
     case ST_WAIT_MMA_TIMEOUT: return "a kernel gave up waiting for the tensor cores";
     case ST_WAIT_TMEM_TIMEOUT: return "a kernel gave up waiting for tensor memory";
     case ST_WAIT_PEER_TIMEOUT: return "a kernel gave up waiting for another rank at a barrier";
+    case ST_WAIT_GRID_TIMEOUT: return "a kernel gave up waiting for its other blocks at a barrier";
     default: return "a kernel reported an error";
     }
 }
@@ -1292,7 +1315,29 @@ struct OpBuf {
     mlxn_buffer *b;
     bool out;
 };
-static int op_begin(mlxn_encoder *e, std::initializer_list<OpBuf> bufs, bool joins_batch = false) {
+static bool op_conflicts(mlxn_encoder *e, std::initializer_list<OpBuf> bufs) {
+    auto has = [](const std::vector<const void *> &v, const void *p) {
+        for (const void *q : v)
+            if (q == p) return true;
+        return false;
+    };
+    bool conflict = false;
+    for (const OpBuf &ob : bufs) {
+        if (!ob.b) continue;
+        Storage *st = ob.b->st;
+        bool writes = ob.out;
+        {
+            std::lock_guard<std::mutex> lk(st->mu);
+            writes = writes || st->host_newer;
+        }
+        if (writes) conflict = conflict || has(e->grp_reads, st) || has(e->grp_writes, st);
+        else conflict = conflict || has(e->grp_writes, st);
+    }
+    return conflict;
+}
+// `ordered_in_batch`: the operation joins the pending batch as a dependent mat-vec (the batch's kernel orders it after
+// the ones it conflicts with), so a conflict does not end the group.
+static int op_begin(mlxn_encoder *e, std::initializer_list<OpBuf> bufs, bool joins_batch = false, bool ordered_in_batch = false) {
     int rc = encoder_begin_work(e);
     if (rc) return rc;
     auto has = [](const std::vector<const void *> &v, const void *p) {
@@ -1312,8 +1357,9 @@ static int op_begin(mlxn_encoder *e, std::initializer_list<OpBuf> bufs, bool joi
         if (writes) conflict = conflict || has(e->grp_reads, st) || has(e->grp_writes, st);
         else conflict = conflict || has(e->grp_writes, st);
     }
-    if (conflict && (rc = encoder_join_lanes(e))) return rc;
+    if (conflict && !ordered_in_batch && (rc = encoder_join_lanes(e))) return rc;
     const bool first = e->grp_reads.empty() && e->grp_writes.empty();
+    e->grp_pend_only = joins_batch && (first || e->grp_pend_only);
     // a mat-vec that leaves with the pending batch shares that batch's lane; everything else alternates
     const int lane = first ? 0 : (joins_batch && !e->pend.empty()) ? e->pend_lane : (e->cur_lane + 1) % kLanes;
     if (!e->grp_open) {
@@ -1468,9 +1514,8 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
         if (mode != 3) return false;
         // measured: batched, the register-level kernel is the faster one except for many activation rows on the
         // long-K and the widest Q6_K shapes
-        const bool q6 = (int)p->ggml_type == GT_Q6_K;
-        if (a.m >= 4 && a.k >= 8192) return false;
-        if (q6 && a.m > 4 && a.n >= 8192) return false;
+        if (a.m > 4) return false;
+        if (a.m == 4 && a.k >= 8192) return false;
         return true;
     };
     auto make_args = [&](uint32_t m0) {
@@ -1508,7 +1553,14 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
             const bool fits = batch && !enc->pend.empty() && enc->pend_type == (int)p->ggml_type &&
                               enc->pend_mp == mv_row_class(a0.m) && enc->pend_pair == pair && enc->pend.size() < 8;
             if (!enc->pend.empty() && !fits && (rc = encoder_flush_pending(enc))) return rc;
-            if ((rc = op_begin(enc, {{input, false}, {weight, false}, {output, true}}, true))) return rc;
+            // A mat-vec that depends on the batch it would join (it reads a result of the batch, or writes over one)
+            // still joins it when the group holds nothing but that batch: the kernel then starts it after the
+            // mat-vecs ahead of it (a barrier across its grid) while the weights keep streaming.
+            bool chained = false;
+            if (fits && g_opt_mv_chain.load() && enc->grp_pend_only && a0.n_peer == 0 && enc->pend[0].n_peer == 0 &&
+                op_conflicts(enc, {{input, false}, {weight, false}, {output, true}}))
+                chained = true;
+            if ((rc = op_begin(enc, {{input, false}, {weight, false}, {output, true}}, true, chained))) return rc;
             // (a conflict found by op_begin has launched the batch and started a new group)
             if (enc->pend.empty()) {
                 enc->pend_type = (int)p->ggml_type;
@@ -1517,6 +1569,7 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
                 enc->pend_lane = enc->cur_lane;
             }
             enc->pend.push_back(a0);
+            enc->pend.back().after_earlier = chained && enc->pend.size() > 1 ? 1u : 0u;
             for (mlxn_buffer *b : {input, weight, output}) {
                 std::lock_guard<std::mutex> lk(b->st->mu);
                 b->st->pend_enc = enc;

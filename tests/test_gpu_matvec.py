@@ -247,8 +247,8 @@ def test_lm_head_q6k_full_size_sampled(ctx, kernel):
         mx.set_option("qmv", "auto")
 
 
-# ---- several conflict-free mat-vecs in one encoder leave as one kernel; a mat-vec that reads another one's result
-# ---- ends the group first (upstream: concurrent dispatch between barriers, src/encoder.rs:837-853)
+# ---- several conflict-free mat-vecs in one encoder leave as one kernel (upstream: concurrent dispatch between
+# ---- barriers, src/encoder.rs:837-853); see also test_chained_matvecs_in_one_launch below
 @pytest.mark.parametrize("tname", ["Q4_0", "Q8_0", "Q6_K"])
 def test_batched_launch_of_independent_matvecs(ctx, tname):
     gtype, otype = TYPES[tname]
@@ -272,7 +272,7 @@ def test_batched_launch_of_independent_matvecs(ctx, tname):
     for (n, m), w, x, yb in zip(shapes, ws, xs, ybs):
         y_ref, ad = orc.qmatmul(otype, w, x, n, k, nthreads=8)
         assert norm_err(yb.as_slice(np.float32).reshape(m, n), y_ref, ad) <= MV_TOL, (tname, n, m)
-    # a dependent pair: the second reads the first one's result, so the first is launched before the second is queued
+    # a dependent pair: the second reads the first one's result
     n1, n2 = 4096, 512
     w1, w2 = normal_weights(81, n1, k, otype), normal_weights(82, n2, n1, otype)
     x = normal_acts(81, 1, k)
@@ -287,3 +287,50 @@ def test_batched_launch_of_independent_matvecs(ctx, tname):
     assert norm_err(got1, r1, ad1) <= MV_TOL
     r2, ad2 = orc.qmatmul(otype, w2, got1.copy(), n2, n1, nthreads=8)
     assert norm_err(y2.as_slice(np.float32).reshape(1, n2), r2, ad2) <= MV_TOL
+
+
+# ---- option qmv_chain=1: mat-vecs that depend on one another (each reads the result of the one before, or writes over
+# ---- it) also leave as ONE kernel: its blocks meet at a barrier between them while the next one's weights keep streaming
+@pytest.mark.parametrize("tname", ["Q4_0", "Q8_0", "Q6_K"])
+@pytest.mark.parametrize("m", [1, 2, 4])
+def test_chained_matvecs_in_one_launch(ctx, tname, m):
+    gtype, otype = TYPES[tname]
+    d = ctx.device
+    dims = [2048, 4096, 512, 1024, 3072, 512]        # x0 [m, 2048] -> 4096 -> 512 -> 1024 -> 3072 -> 512
+    ws = [normal_weights(300 + i, dims[i + 1], dims[i], otype) for i in range(len(dims) - 1)]
+    wbs = [ctx.buf(w, mx.DType.U8) for w in ws]
+    x0 = normal_acts(300, m, dims[0])
+    results = {}
+    for chain in ("1", "0"):
+        mx.set_option("qmv_chain", chain)
+        mx.set_option("qmv", "mma")            # the same kernel and tiling with and without chaining
+        mx.set_option("qmv_mma_tpw", "1")
+        try:
+            bufs = [ctx.buf(x0, mx.DType.F32)] + [d.alloc_buffer(m * n * 4, mx.DType.F32) for n in dims[1:]]
+            side = d.alloc_buffer(m * dims[3] * 4, mx.DType.F32)
+            mx.reset_counters()
+            enc = d.command_encoder()
+            for i in range(len(ws)):
+                mx.quantized_matmul_ggml(enc, ctx.registry, d, bufs[i], wbs[i], bufs[i + 1],
+                                         mx.GgmlQuantizedMatmulParams(m, dims[i + 1], dims[i], gtype))
+            # ... and one that overwrites the last result's neighbour twice (write after write)
+            for i in (1, 1):
+                mx.quantized_matmul_ggml(enc, ctx.registry, d, bufs[2], wbs[2], side, mx.GgmlQuantizedMatmulParams(m, dims[3], dims[2], gtype))
+            enc.commit_and_wait()
+            launches = mx.kernel_launch_count()
+            results[chain] = ([b.as_slice(np.float32).copy() for b in bufs[1:]], side.as_slice(np.float32).copy(), launches)
+        finally:
+            mx.set_option("qmv_chain", "0")
+            mx.set_option("qmv", "auto")
+            mx.set_option("qmv_mma_tpw", "0")
+    got, side1, launches1 = results["1"]
+    ref, side0, launches0 = results["0"]
+    assert launches1 == 1 and launches0 >= len(ws)    # (unchained, only conflict-free neighbours share a launch)
+    x = x0
+    for i, w in enumerate(ws):
+        y_ref, ad = orc.qmatmul(otype, w, x, dims[i + 1], dims[i], nthreads=8)
+        y = got[i].reshape(m, dims[i + 1])
+        assert norm_err(y, y_ref, ad) <= MV_TOL, (tname, m, i)
+        assert np.array_equal(got[i], ref[i])          # the same kernel either way: bit-identical to separate launches
+        x = y.copy()
+    assert np.array_equal(side1, side0) and np.array_equal(side1.reshape(m, dims[3]), got[2].reshape(m, dims[3]))
