@@ -906,8 +906,13 @@ def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
             mx.moe_softmax_topk(e, reg, dev, lg, ids, rw, T, E, top_k)
             mx.quantized_matmul_id_ggml(e, reg, dev, xb, wg, ids, yg, pg)
             mx.quantized_matmul_id_ggml(e, reg, dev, xb, wu, ids, yu, pg)
-            mx.silu_mul(e, reg, dev, yg, yu, act, T * top_k * ffn)
-            mx.quantized_matmul_id_ggml(e, reg, dev, act, wd, ids, yd, pd)
+            if T * top_k <= mx.MM_ID_ROUTING_THRESHOLD:
+                # decode: SwiGLU is formed on the down projection's activation load, as upstream's fused
+                # quantized_matmul_id_swiglu_q4_0 does at decode (src/ops/quantized_matmul_id_ggml.rs:551-670)
+                mx.quantized_matmul_id_swiglu(e, reg, dev, yg, yu, wd, ids, yd, pd)
+            else:
+                mx.silu_mul(e, reg, dev, yg, yu, act, T * top_k * ffn)
+                mx.quantized_matmul_id_ggml(e, reg, dev, act, wd, ids, yd, pd)
             mx.moe_weighted_reduce(e, reg, dev, rw, yd, outb, T, top_k, hidden)
 
         sec = timed(layer)
@@ -1075,8 +1080,11 @@ def run_case(argv):
             mx.moe_softmax_topk(enc, reg, dev, lg, ids, rw, T, E, top_k)
             mx.quantized_matmul_id_ggml(enc, reg, dev, xb, bufs["gate"], ids, yg, pg)
             mx.quantized_matmul_id_ggml(enc, reg, dev, xb, bufs["up"], ids, yu, pg)
-            mx.silu_mul(enc, reg, dev, yg, yu, act, T * top_k * ffn)
-            mx.quantized_matmul_id_ggml(enc, reg, dev, act, bufs["down"], ids, yd, pd)
+            if T * top_k <= mx.MM_ID_ROUTING_THRESHOLD:
+                mx.quantized_matmul_id_swiglu(enc, reg, dev, yg, yu, bufs["down"], ids, yd, pd)
+            else:
+                mx.silu_mul(enc, reg, dev, yg, yu, act, T * top_k * ffn)
+                mx.quantized_matmul_id_ggml(enc, reg, dev, act, bufs["down"], ids, yd, pd)
             mx.moe_weighted_reduce(enc, reg, dev, rw, yd, outb, T, top_k, hidden)
             enc.commit_and_wait()
         print("ok", mx.last_kernel_name())

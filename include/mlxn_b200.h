@@ -222,6 +222,14 @@ int mlxn_dispatch_mm_for_test(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device
 int mlxn_quantized_matmul_id_ggml(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
                                   mlxn_buffer *weight, mlxn_buffer *ids, mlxn_buffer *output,
                                   const mlxn_qmm_id_params *params);
+/* quantized_matmul_id_swiglu_q4_0 (src/ops/quantized_matmul_id_ggml.rs:551-670; kernel
+ * src/shaders/quantized_matmul_id_ggml.metal:231-319), here for Q4_0, Q8_0 and Q6_K: the fused SwiGLU + expert-routed
+ * mat-vec of the MoE down projection.  gate, up: f32 [n_tokens * top_k, k], one row per (token, slot) pair;
+ * output[r, :] = W[ids[r]] . (silu(gate[r, :]) * up[r, :]).  The activations are formed while they are loaded: there
+ * is no separate SwiGLU launch and no [rows, k] intermediate in memory. */
+int mlxn_quantized_matmul_id_swiglu(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *gate,
+                                    mlxn_buffer *up, mlxn_buffer *weight, mlxn_buffer *ids, mlxn_buffer *output,
+                                    const mlxn_qmm_id_params *params);
 /* quantized_matmul_id_ggml_pooled (src/ops/quantized_matmul_id_ggml.rs:288-389) with the caller-owned
  * IdMmScratch {htpe, hids} (:672-719) and its capacities (check_capacity :704-718). */
 int mlxn_quantized_matmul_id_ggml_pooled(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev,

@@ -98,6 +98,7 @@ SIGNATURES = {
                                                  C.POINTER(C.c_void_p), C.c_uint32]),
     "mlxn_dispatch_mm_for_test": (i32, [vp, vp, vp, vp, vp, vp, C.POINTER(QmmParams)]),
     "mlxn_quantized_matmul_id_ggml": (i32, [vp, vp, vp, vp, vp, vp, vp, C.POINTER(QmmIdParams)]),
+    "mlxn_quantized_matmul_id_swiglu": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, C.POINTER(QmmIdParams)]),
     "mlxn_quantized_matmul_id_ggml_pooled": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32,
                                                    C.POINTER(QmmIdParams)]),
     "mlxn_dispatch_id_mm_for_test": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, C.POINTER(QmmIdParams)]),

@@ -549,6 +549,22 @@ def quantized_matmul_id_ggml(encoder, registry, device, input, weight, ids, outp
                                                        _h(ids), _h(output), C.byref(params._c())))
 
 
+def quantized_matmul_id_swiglu(encoder, registry, device, gate, up, weight, ids, output,
+                               params: GgmlQuantizedMatmulIdParams) -> None:
+    """Fused SwiGLU + expert-routed mat-vec for Q4_0, Q8_0 and Q6_K: output[r] = W[ids[r]] . (silu(gate[r]) * up[r]),
+    gate / up f32 [n_tokens * top_k, k] (src/shaders/quantized_matmul_id_ggml.metal:231-319)."""
+    _check(_native.lib().mlxn_quantized_matmul_id_swiglu(encoder._h, _h(registry), device._h, _h(gate), _h(up), _h(weight),
+                                                         _h(ids), _h(output), C.byref(params._c())))
+
+
+def quantized_matmul_id_swiglu_q4_0(encoder, registry, device, gate, up, weight, ids, output,
+                                    params: GgmlQuantizedMatmulIdParams) -> None:
+    """src/ops/quantized_matmul_id_ggml.rs:551-670 (Q4_0 only, as upstream)."""
+    if params.ggml_type != GgmlType.Q4_0:
+        raise InvalidArgument(f"Invalid argument: quantized_matmul_id_swiglu_q4_0: expected Q4_0, got {GgmlType(params.ggml_type).name}")
+    quantized_matmul_id_swiglu(encoder, registry, device, gate, up, weight, ids, output, params)
+
+
 class IdMmScratch:
     """src/ops/quantized_matmul_id_ggml.rs:672-719."""
 

@@ -92,6 +92,11 @@ struct QmvArgs {
     // the same launch writes, so it starts after all of them have finished (a barrier across the grid).
     uint32_t after_earlier;
     uint32_t *grid_bar;     // 32 zeroed words of device memory for those barriers (one launch at a time uses them)
+    // Register-level kernel, expert-routed form: one QmvArgs per (token, slot) row with m = 1, `ids` set and the
+    // row's expert read from ids[id_index]; `x` / `y` already point at the row's activations and results.
+    uint32_t id_index;
+    // ... and its fused SwiGLU form: the activations are silu(x) * x2 (src/shaders/quantized_matmul_id_ggml.metal:231-319)
+    const float *x2;
 };
 constexpr int kMaxPeers = 7;
 __host__ __device__ inline uint32_t qmv_ld(const QmvArgs &a) { return a.y_ld ? a.y_ld : a.n; }

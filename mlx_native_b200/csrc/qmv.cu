@@ -597,7 +597,16 @@ __global__ void __launch_bounds__(NW * 32, 1) qmv_stream_kernel(const QmvArgs a,
                     v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (idx < M * ks4) {
                         const uint32_t t = idx / ks4, f = idx - t * ks4;
-                        if (k0 + 4 * f < a.k) v[u] = __ldg(reinterpret_cast<const float4 *>(xg + (size_t)t * a.k + k0) + f);
+                        if (k0 + 4 * f < a.k) {
+                            v[u] = __ldg(reinterpret_cast<const float4 *>(xg + (size_t)t * a.k + k0) + f);
+                            if (a.x2) {   // fused SwiGLU: silu(gate) * up (src/shaders/quantized_matmul_id_ggml.metal:231-319)
+                                const float4 up = __ldg(reinterpret_cast<const float4 *>(xg + (a.x2 - a.x) + (size_t)t * a.k + k0) + f);
+                                v[u].x = v[u].x / (1.0f + expf(-v[u].x)) * up.x;
+                                v[u].y = v[u].y / (1.0f + expf(-v[u].y)) * up.y;
+                                v[u].z = v[u].z / (1.0f + expf(-v[u].z)) * up.z;
+                                v[u].w = v[u].w / (1.0f + expf(-v[u].w)) * up.w;
+                            }
+                        }
                     }
                 }
 #pragma unroll
@@ -861,6 +870,21 @@ template <int T> static cudaError_t launch_t(const QmvArgs &a, bool want_stream,
         return cudaErrorInvalidValue;
     }
 #undef MLXN_CASE
+}
+
+// Whether launch_qmv would run the streaming kernel for these arguments (the only one of the two that knows the fused
+// SwiGLU form, QmvArgs::x2).
+bool qmv_stream_available(int ggml_type, const QmvArgs &a, int sm_count) {
+    StreamCfg c{};
+    uint32_t grid = 0;
+    size_t smem = 0;
+    const uint32_t nw = a.m <= 2 ? 16 : 8;
+    switch (ggml_type) {
+    case GT_Q4_0: return stream_config<GT_Q4_0>(a, sm_count, 227 * 1024 - 2048, nw, c, grid, smem);
+    case GT_Q8_0: return stream_config<GT_Q8_0>(a, sm_count, 227 * 1024 - 2048, nw, c, grid, smem);
+    case GT_Q6_K: return stream_config<GT_Q6_K>(a, sm_count, 227 * 1024 - 2048, nw, c, grid, smem);
+    default: return false;
+    }
 }
 
 // Launches the mat-vec for a.m in [1,8] (dense) or the routed form (a.ids != nullptr, a.m == 1).

@@ -65,13 +65,16 @@ __host__ __device__ constexpr uint32_t mw_pitch(int ggml_type, int kb) {
     return 16u * (c | 1u);
 }
 
-constexpr int kMwMaxProbs = 8;     // mat-vecs one launch can carry
+constexpr int kMwMaxProbs = 16;    // mat-vecs one launch can carry
 constexpr int kMwMaxGrid = 320;    // CTAs of a launch (two per SM)
 
 // One mat-vec of a launch.  A launch carries up to kMwMaxProbs mat-vecs that have no buffer conflicts with one
 // another (same block type and kernel configuration); their row groups form one list of work items.
 struct MwProb {
     const float *x;
+    const float *x2;      // fused SwiGLU: the activations are silu(x) * x2 (nullptr: x as it is)
+    const uint32_t *ids;  // expert-routed: the weights are those of expert ids[id_idx] of the stacked tensor (3-D map)
+    uint32_t id_idx;
     float *y;
     uint32_t n, k, m;
     uint32_t spi;         // stages per item = k / (KB * UK)
@@ -93,6 +96,7 @@ struct MwBatch {
     // CTAs that have left (the last one zeroes the block for the next launch).
     uint32_t dep_mask;
     uint32_t *bar;
+    uint32_t routed;          // some problem is expert-routed: the expert ids are read once the kernels ahead are done
     // CTA c works on items [cta_begin[c], cta_begin[c + 1]): contiguous chunks of (nearly) equal numbers of stages
     uint32_t cta_begin[kMwMaxGrid + 1];
 };
@@ -340,6 +344,7 @@ __global__ void __launch_bounds__(kMwThreads, 2)
     // this CTA's items [s_lo, s_hi) of every problem (counted from the problem's first item) and the number of the
     // CTA's first stage of the problem (s_q0[nprob]: all its stages)
     __shared__ uint32_t s_lo[kMwMaxProbs], s_hi[kMwMaxProbs], s_q0[kMwMaxProbs + 1];
+    __shared__ uint32_t s_exp[kMwMaxProbs];   // expert of every routed problem
     __shared__ __align__(8) uint64_t gbar;  // dependent launches: warp 0 tells the others that the grid barrier is through
     __shared__ volatile uint32_t abort_flag;
 
@@ -419,6 +424,14 @@ __global__ void __launch_bounds__(kMwThreads, 2)
 #pragma unroll
             for (uint32_t hv = 0; hv < HV; hv++) {
                 const uint32_t x0 = ((s * SBYTES + hv * (SBYTES / HV)) & ~15u) >> 3;
+                if (bt.p[p].ids) {   // [expert][row][bytes]: an expert id past the table reads as zeros
+                    asm volatile(
+                        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+                        ::"r"(smem_base + slot * STAGE + hv * (uint32_t)R * PITCH), "l"(&maps.m[p]), "r"(x0), "r"(item * (uint32_t)R),
+                          "r"(s_exp[p]), "r"(smem_u32(&full[slot])), "l"(pol_w)
+                        : "memory");
+                    continue;
+                }
                 asm volatile(
                     "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;"
                     ::"r"(smem_base + slot * STAGE + hv * (uint32_t)R * PITCH), "l"(&maps.m[p]), "r"(x0), "r"(item * (uint32_t)R),
@@ -427,6 +440,11 @@ __global__ void __launch_bounds__(kMwThreads, 2)
             }
         }
     };
+    if (bt.routed) {
+        grid_dependency_wait();   // the expert ids belong to the kernels ahead
+        if (tid < bt.nprob) s_exp[tid] = bt.p[tid].ids ? __ldcg(bt.p[tid].ids + bt.p[tid].id_idx) : 0u;
+        __syncthreads();
+    }
     if (tid == 0) {
         if (!bt.early_weights) grid_dependency_wait();
         for (uint32_t q = 0; q < c.nslots; q++) issue(q, q);
@@ -477,11 +495,15 @@ __global__ void __launch_bounds__(kMwThreads, 2)
         uint32_t cur = 0xFFFFFFFFu, spi = 1, pm = 0, pk = 0;
         const float *xsrc0[NPASS], *xsrc1[NPASS];
         bool xok[NPASS];
+        ptrdiff_t x2d = 0;   // fused SwiGLU: where the second operand sits relative to the first (elements)
+        bool has2 = false;
         auto set_problem = [&](uint32_t p) {
             cur = p;
             spi = bt.p[p].spi;
             pm = bt.p[p].m;
             pk = bt.p[p].k;
+            has2 = bt.p[p].x2 != nullptr;
+            x2d = has2 ? bt.p[p].x2 - bt.p[p].x : 0;
 #pragma unroll
             for (int q = 0; q < NPASS; q++) {
                 xok[q] = xin[q] && xrow[q] < pm;
@@ -501,6 +523,15 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                 if (xok[p] && ks * SK + xrel0[p] < pk) {   // (the last stage of a row may reach past K: zeros there)
                     asm volatile("ld.global.cg.L2::cache_hint.v2.f32 {%0, %1}, [%2], %3;" : "=f"(v0.x), "=f"(v0.y) : "l"(xsrc0[p] + (size_t)ks * SK), "l"(pol_x));
                     asm volatile("ld.global.cg.L2::cache_hint.v2.f32 {%0, %1}, [%2], %3;" : "=f"(v1.x), "=f"(v1.y) : "l"(xsrc1[p] + (size_t)ks * SK), "l"(pol_x));
+                }
+                if (has2 && xok[p] && ks * SK + xrel0[p] < pk) {   // silu(gate) * up, as src/shaders/silu_mul.metal:17-30
+                    float2 u0, u1;
+                    asm volatile("ld.global.cg.L2::cache_hint.v2.f32 {%0, %1}, [%2], %3;" : "=f"(u0.x), "=f"(u0.y) : "l"(xsrc0[p] + (size_t)ks * SK + x2d), "l"(pol_x));
+                    asm volatile("ld.global.cg.L2::cache_hint.v2.f32 {%0, %1}, [%2], %3;" : "=f"(u1.x), "=f"(u1.y) : "l"(xsrc1[p] + (size_t)ks * SK + x2d), "l"(pol_x));
+                    v0.x = v0.x / (1.0f + expf(-v0.x)) * u0.x;
+                    v0.y = v0.y / (1.0f + expf(-v0.y)) * u0.y;
+                    v1.x = v1.x / (1.0f + expf(-v1.x)) * u1.x;
+                    v1.y = v1.y / (1.0f + expf(-v1.y)) * u1.y;
                 }
                 xr[p][0] = v0.x; xr[p][1] = v0.y; xr[p][2] = v1.x; xr[p][3] = v1.y;
             }
@@ -857,6 +888,17 @@ bool qmv_mma_supported(int ggml_type, const QmvArgs &a) {
     return encode_tiled_fn() != nullptr;
 }
 
+// The expert-routed form: one problem per (token, slot) row (m = 1, `ids` and `id_index` set).  The stacked weights are
+// addressed through a 3-D map [expert][row][bytes], so rows and experts must start on 16-byte boundaries.
+bool qmv_mma_supported_routed(int ggml_type, const QmvArgs &a) {
+    if (ggml_type != GT_Q4_0 && ggml_type != GT_Q8_0 && ggml_type != GT_Q6_K) return false;
+    if (!a.ids || a.m != 1 || a.k == 0 || a.n == 0 || a.n_experts == 0 || a.k % mw_uk(ggml_type) != 0) return false;
+    const uint64_t row_bytes = (uint64_t)(a.k / ggml_qk(ggml_type)) * ggml_block_bytes(ggml_type);
+    if (row_bytes % 16 != 0 || row_bytes >= (1ull << 31) || a.expert_stride % 16 != 0 || a.expert_stride < row_bytes * a.n) return false;
+    if (((uintptr_t)a.w & 15u) || ((uintptr_t)a.x & 15u) || ((uintptr_t)a.x2 & 15u)) return false;
+    return encode_tiled_fn() != nullptr;
+}
+
 static inline size_t mw_align(size_t v, size_t al) { return (v + al - 1) / al * al; }
 
 template <int T, int TPW, int KB, int MP, bool PAIR>
@@ -891,6 +933,7 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
     alignas(64) static thread_local MwMaps maps;
     bt.nprob = (uint32_t)nops;
     bt.early_weights = 1;
+    bt.routed = 0;
     bt.status = ops[0].status;
     uint64_t total_stages = 0;
     uint32_t items = 0;
@@ -898,6 +941,10 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
         const QmvArgs &a = ops[i];
         MwProb &P = bt.p[i];
         P.x = a.x;
+        P.x2 = a.x2;
+        P.ids = a.ids;
+        P.id_idx = a.id_index;
+        if (a.ids) bt.routed = 1;
         P.y = a.y;
         P.n = a.n;
         P.k = a.k;
@@ -911,7 +958,7 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
         const uint32_t its = (a.n + R - 1) / R;
         items += its;
         total_stages += (uint64_t)its * P.spi;
-        if (!a.early_weights) bt.early_weights = 0;
+        if (!a.early_weights || a.ids) bt.early_weights = 0;
         const uint32_t row_bytes = (a.k / BlockTraits<T>::QK) * BlockTraits<T>::BYTES;
         // the weight matrix as [n rows][row_bytes / 8] 8-byte elements; box = R rows x PITCH bytes
         // (pair mode: [n / 2 row pairs][2 row_bytes / 8], box = R / 2 pairs x PITCH bytes)
@@ -919,6 +966,19 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
         const cuuint64_t gstride[1] = {PAIR ? 2ull * row_bytes : row_bytes};
         const cuuint32_t box[2] = {(cuuint32_t)(PITCH / 8), (cuuint32_t)(PAIR ? R / 2 : R)};
         const cuuint32_t estr[2] = {1, 1};
+        if (a.ids) {
+            // the stacked experts as [n_experts][n rows][row_bytes / 8]; box = 1 expert x R rows x PITCH bytes
+            if (PAIR) return cudaErrorInvalidValue;
+            const cuuint64_t gdim3[3] = {row_bytes / 8, a.n, a.n_experts};
+            const cuuint64_t gstride3[2] = {row_bytes, a.expert_stride};
+            const cuuint32_t box3[3] = {(cuuint32_t)(PITCH / 8), (cuuint32_t)R, 1};
+            const cuuint32_t estr3[3] = {1, 1, 1};
+            if (enc(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT64, 3, const_cast<uint8_t *>(a.w), gdim3, gstride3, box3, estr3,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+                return cudaErrorInvalidValue;
+            continue;
+        }
         if (enc(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, const_cast<uint8_t *>(a.w), gdim, gstride, box, estr,
                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -1027,16 +1087,12 @@ static cudaError_t launch_mw_t(const QmvArgs *ops, int nops, uint32_t mmax, int 
 cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
     if (ctas_per_sm < 1) ctas_per_sm = 1;
     if (ctas_per_sm > 2) ctas_per_sm = 2;
-    uint64_t rows = 0, rows_min = ~0ull;
+    uint64_t rows = 0;   // of the launch's largest mat-vec
     uint32_t mmax = 1;
-    bool dep = false;
     for (int i = 0; i < nops; i++) {
-        rows += ops[i].n;
-        if (ops[i].n < rows_min) rows_min = ops[i].n;
+        if (ops[i].n > rows) rows = ops[i].n;
         if (ops[i].m > mmax) mmax = ops[i].m;
-        if (i > 0 && ops[i].after_earlier) dep = true;
     }
-    if (dep) rows = rows_min;   // every mat-vec of a dependent launch has the whole grid to itself
     if (tpw <= 0) {
         // measured: 64-row groups from 8192 rows on (every other CTA slot still gets one), 16-row groups below
         tpw = rows >= 8192 ? 4 : 1;

@@ -29,6 +29,9 @@ size_t qmv_tc_scratch_bytes(const QmvArgs &a);
 cudaError_t launch_qmv_tc(int ggml_type, const QmvArgs &a, uint8_t *scratch, uint32_t *flags, int sm_count, cudaStream_t st,
                           cudaStream_t pub_st, cudaEvent_t pub_ev, int *launches);
 bool qmv_mma_supported(int ggml_type, const QmvArgs &a);
+bool qmv_mma_supported_routed(int ggml_type, const QmvArgs &a);
+bool qmv_stream_available(int ggml_type, const QmvArgs &a, int sm_count);
+constexpr size_t kMvBatchMax = 16;   // mat-vecs one launch of the register-level kernel carries (kMwMaxProbs)
 bool qmv_mma_pair_mode(int ggml_type, const QmvArgs &a);
 cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st);
 cudaError_t launch_qmm_tc(int ggml_type, const QmmArgs &a, bool routed, uint32_t nt, uint8_t *scratch, cudaStream_t st,
@@ -258,6 +261,9 @@ struct mlxn_encoder {
     cudaEvent_t ev_aux = nullptr, ev_aux_join = nullptr;
     bool aux_busy = false;
     std::vector<const void *> grp_reads, grp_writes;  // storages the current group reads / writes
+    // inputs whose host shadow was uploaded inside the group, with the lane the copy went to: a write for the other
+    // lanes, but an operation that runs on the same lane comes after the copy anyway
+    std::vector<std::pair<const void *, int>> grp_uploads;
     bool grp_open = false;           // ev_fork marks the start of the current group
     cudaEvent_t ev_start = nullptr, ev_end = nullptr;
     bool started = false, committed = false, capturing = false;
@@ -689,7 +695,7 @@ static const char *const kKernelNames[] = {
     "kernel_mul_mv_q4_0_f32", "kernel_mul_mv_q8_0_f32", "kernel_mul_mv_q6_K_f32",
     "kernel_mul_mm_q4_0_f32", "kernel_mul_mm_q8_0_f32", "kernel_mul_mm_q6_K_f32",
     "kernel_mul_mm_q4_0_tensor_f32", "kernel_mul_mm_q8_0_tensor_f32", "kernel_mul_mm_q6_K_tensor_f32",
-    "kernel_mul_mv_id_q4_0_f32", "kernel_mul_mv_id_q8_0_f32", "kernel_mul_mv_id_q6_K_f32",
+    "kernel_mul_mv_id_q4_0_f32", "kernel_mul_mv_id_q8_0_f32", "kernel_mul_mv_id_q6_K_f32", "kernel_mul_mv_id_q4_0_f32_swiglu",
     "kernel_mul_mm_id_map0_ne20_1", "kernel_mul_mm_id_map0_ne20_8",
     // the bucketing kernel takes any top_k; the values upstream's audit lists as uncovered there
     // (docs/moe-q-perf-audit-2026-04-27.md:79-84) have names of the same pattern here
@@ -834,6 +840,7 @@ extern "C" void mlxn_encoder_destroy(mlxn_encoder *enc) {
         enc->aux_busy = false;
         enc->grp_reads.clear();
         enc->grp_writes.clear();
+        enc->grp_uploads.clear();
         enc->grp_open = false;
         if (*enc->status_host != 0) {
             *enc->status_host = 0;
@@ -896,7 +903,7 @@ static int encoder_flush_pending(mlxn_encoder *e) {
     // (measured: one or two activation rows stay with this kernel, except one Q6_K row on a small matrix, where the
     //  streaming kernel's short start wins; more rows take the tensor-memory kernel, whose time does not grow with m)
     const bool q6_one_row_small = e->pend_type == GT_Q6_K && a0.m == 1 && (uint64_t)a0.n * a0.k < (1ull << 23);
-    const bool lone_other = e->pend.size() == 1 && opt_qmv() == 3 && a0.n_peer == 0 && (q6_one_row_small || a0.m > 2);
+    const bool lone_other = e->pend.size() == 1 && opt_qmv() == 3 && a0.n_peer == 0 && !a0.ids && (q6_one_row_small || a0.m > 2);
     if (lone_other) {
         if (!q6_one_row_small && qmv_tc_supported(e->pend_type, a0)) {
             uint8_t *scratch = nullptr;
@@ -953,6 +960,7 @@ static int encoder_join_lanes(mlxn_encoder *e) {
     }
     e->grp_reads.clear();
     e->grp_writes.clear();
+    e->grp_uploads.clear();
     e->grp_open = false;
     e->cur_lane = 0;
     e->stream = e->lanes[0];
@@ -1315,7 +1323,8 @@ struct OpBuf {
     mlxn_buffer *b;
     bool out;
 };
-static bool op_conflicts(mlxn_encoder *e, std::initializer_list<OpBuf> bufs) {
+// `lane`: the lane the operation would run on.
+static bool op_conflicts(mlxn_encoder *e, std::initializer_list<OpBuf> bufs, int lane) {
     auto has = [](const std::vector<const void *> &v, const void *p) {
         for (const void *q : v)
             if (q == p) return true;
@@ -1332,36 +1341,27 @@ static bool op_conflicts(mlxn_encoder *e, std::initializer_list<OpBuf> bufs) {
         }
         if (writes) conflict = conflict || has(e->grp_reads, st) || has(e->grp_writes, st);
         else conflict = conflict || has(e->grp_writes, st);
+        for (const auto &u : e->grp_uploads)
+            if (u.first == st && (writes || u.second != lane)) conflict = true;
     }
     return conflict;
+}
+// The lane an operation that does not conflict with the group gets: a mat-vec that leaves with the pending batch shares
+// that batch's lane; everything else alternates.
+static int op_lane(const mlxn_encoder *e, bool joins_batch) {
+    const bool first = e->grp_reads.empty() && e->grp_writes.empty();
+    return first ? 0 : (joins_batch && !e->pend.empty()) ? e->pend_lane : (e->cur_lane + 1) % kLanes;
 }
 // `ordered_in_batch`: the operation joins the pending batch as a dependent mat-vec (the batch's kernel orders it after
 // the ones it conflicts with), so a conflict does not end the group.
 static int op_begin(mlxn_encoder *e, std::initializer_list<OpBuf> bufs, bool joins_batch = false, bool ordered_in_batch = false) {
     int rc = encoder_begin_work(e);
     if (rc) return rc;
-    auto has = [](const std::vector<const void *> &v, const void *p) {
-        for (const void *q : v)
-            if (q == p) return true;
-        return false;
-    };
-    bool conflict = false;
-    for (const OpBuf &ob : bufs) {
-        if (!ob.b) continue;
-        Storage *st = ob.b->st;
-        bool writes = ob.out;
-        {
-            std::lock_guard<std::mutex> lk(st->mu);
-            writes = writes || st->host_newer;
-        }
-        if (writes) conflict = conflict || has(e->grp_reads, st) || has(e->grp_writes, st);
-        else conflict = conflict || has(e->grp_writes, st);
-    }
+    const bool conflict = op_conflicts(e, bufs, op_lane(e, joins_batch));
     if (conflict && !ordered_in_batch && (rc = encoder_join_lanes(e))) return rc;
     const bool first = e->grp_reads.empty() && e->grp_writes.empty();
     e->grp_pend_only = joins_batch && (first || e->grp_pend_only);
-    // a mat-vec that leaves with the pending batch shares that batch's lane; everything else alternates
-    const int lane = first ? 0 : (joins_batch && !e->pend.empty()) ? e->pend_lane : (e->cur_lane + 1) % kLanes;
+    const int lane = op_lane(e, joins_batch);
     if (!e->grp_open) {
         CUDA_TRY(cudaEventRecord(e->ev_fork, e->lanes[0]), "event record");  // everything before this group
         e->grp_open = true;
@@ -1380,7 +1380,11 @@ static int op_begin(mlxn_encoder *e, std::initializer_list<OpBuf> bufs, bool joi
             std::lock_guard<std::mutex> lk(st->mu);
             writes = writes || st->host_newer;
         }
-        (writes ? e->grp_writes : e->grp_reads).push_back(st);
+        if (ob.out) e->grp_writes.push_back(st);
+        else {
+            e->grp_reads.push_back(st);
+            if (writes) e->grp_uploads.push_back({st, lane});   // its host shadow is copied in by bind() below, on this lane
+        }
         if ((rc = bind(e, ob.b, ob.out))) return rc;
     }
     return MLXN_OK;
@@ -1551,14 +1555,14 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
             const bool batch = g_opt_mv_batch.load() != 0;
             const bool pair = qmv_mma_pair_mode((int)p->ggml_type, a0);
             const bool fits = batch && !enc->pend.empty() && enc->pend_type == (int)p->ggml_type &&
-                              enc->pend_mp == mv_row_class(a0.m) && enc->pend_pair == pair && enc->pend.size() < 8;
+                              enc->pend_mp == mv_row_class(a0.m) && enc->pend_pair == pair && enc->pend.size() < kMvBatchMax;
             if (!enc->pend.empty() && !fits && (rc = encoder_flush_pending(enc))) return rc;
             // A mat-vec that depends on the batch it would join (it reads a result of the batch, or writes over one)
             // still joins it when the group holds nothing but that batch: the kernel then starts it after the
             // mat-vecs ahead of it (a barrier across its grid) while the weights keep streaming.
             bool chained = false;
             if (fits && g_opt_mv_chain.load() && enc->grp_pend_only && a0.n_peer == 0 && enc->pend[0].n_peer == 0 &&
-                op_conflicts(enc, {{input, false}, {weight, false}, {output, true}}))
+                op_conflicts(enc, {{input, false}, {weight, false}, {output, true}}, enc->pend_lane))
                 chained = true;
             if ((rc = op_begin(enc, {{input, false}, {weight, false}, {output, true}}, true, chained))) return rc;
             // (a conflict found by op_begin has launched the batch and started a new group)
@@ -1788,26 +1792,76 @@ static int validate_id(const char *who, mlxn_buffer *input, mlxn_buffer *weight,
     return MLXN_OK;
 }
 
+// `up` != nullptr: the fused SwiGLU form (src/ops/quantized_matmul_id_ggml.rs:551-670): `input` is the gate, both are
+// [n_tokens * top_k, k] with one row per OUTPUT row, and the activations are silu(gate) * up.
 static int dispatch_id_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input, mlxn_buffer *weight,
-                          mlxn_buffer *ids, mlxn_buffer *output, const mlxn_qmm_id_params *p) {
-    int rc = touch_kernel(reg, dev, mv_id_kernel_name((int)p->ggml_type));
+                          mlxn_buffer *ids, mlxn_buffer *output, const mlxn_qmm_id_params *p, mlxn_buffer *up = nullptr) {
+    const int t = (int)p->ggml_type;
+    int rc = touch_kernel(reg, dev, up ? "kernel_mul_mv_id_q4_0_f32_swiglu" : mv_id_kernel_name(t));
     if (rc) return rc;
-    if ((rc = op_begin(enc, {{input, false}, {weight, false}, {ids, false}, {output, true}}))) return rc;
+    const uint32_t rows = p->n_tokens * p->top_k;
     QmvArgs a{};
     a.w = weight->dev();
     a.x = reinterpret_cast<const float *>(input->dev());
+    a.x2 = up ? reinterpret_cast<const float *>(up->dev()) : nullptr;
     a.y = reinterpret_cast<float *>(output->dev());
     a.ids = reinterpret_cast<const uint32_t *>(ids->dev());
     a.n = p->n;
     a.k = p->k;
     a.m = 1;
-    a.nprob = p->n_tokens * p->top_k;
-    a.top_k = p->top_k;
+    a.nprob = rows;
+    a.top_k = up ? 1 : p->top_k;   // (fused: every output row has its own input row)
     a.n_experts = p->n_experts;
     a.expert_stride = p->expert_stride;
     a.status = enc->status_dev;
-    CUDA_TRY(launch_qmv((int)p->ggml_type, a, opt_qmv_stream(), dev->sm_count, enc->stream, &g_last_kernel), "mat-vec launch");
-    g_launches.fetch_add(1);
+    // Few rows (decode): every (token, slot) row is one mat-vec of the register-level kernel, and the rows of this call,
+    // and of the calls around it that do not depend on it (gate and up of one layer), leave as one launch.
+    const int mode = opt_qmv();
+    if ((mode == 3 || mode == 4) && rows <= kMvBatchMax && qmv_mma_supported_routed(t, a)) {
+        const bool batch = g_opt_mv_batch.load() != 0;
+        const bool fits = batch && !enc->pend.empty() && enc->pend_type == t && enc->pend_mp == 1 && !enc->pend_pair &&
+                          enc->pend.size() + rows <= kMvBatchMax;
+        if (!enc->pend.empty() && !fits && (rc = encoder_flush_pending(enc))) return rc;
+        if ((rc = op_begin(enc, {{input, false}, {up, false}, {weight, false}, {ids, false}, {output, true}}, true))) return rc;
+        if (enc->pend.empty()) {
+            enc->pend_type = t;
+            enc->pend_mp = 1;
+            enc->pend_pair = false;
+            enc->pend_lane = enc->cur_lane;
+        }
+        for (uint32_t r = 0; r < rows; r++) {
+            QmvArgs ar = a;
+            ar.nprob = 1;
+            ar.id_index = r;
+            ar.x = a.x + (size_t)(r / a.top_k) * p->k;
+            ar.x2 = a.x2 ? a.x2 + (size_t)r * p->k : nullptr;
+            ar.y = a.y + (size_t)r * p->n;
+            ar.early_weights = 0;
+            enc->pend.push_back(ar);
+        }
+        for (mlxn_buffer *b : {input, up, weight, ids, output}) {
+            if (!b) continue;
+            std::lock_guard<std::mutex> lk(b->st->mu);
+            b->st->pend_enc = enc;
+        }
+        g_last_kernel = "qmv_mma";
+        g_dispatch.fetch_add(1);
+        if (!batch) return encoder_flush_pending(enc);
+        return MLXN_OK;
+    }
+    if ((rc = op_begin(enc, {{input, false}, {up, false}, {weight, false}, {ids, false}, {output, true}}))) return rc;
+    int launches = 1;
+    if (up && !(opt_qmv_stream() && qmv_stream_available(t, a, dev->sm_count))) {
+        // no fused form for this shape: SwiGLU into the encoder's scratch, then the plain routed mat-vec
+        uint8_t *scratch = nullptr;
+        if ((rc = encoder_scratch(enc, (size_t)rows * p->k * 4, &scratch))) return rc;
+        CUDA_TRY(launch_silu_mul(a.x, a.x2, reinterpret_cast<float *>(scratch), rows * p->k, enc->stream), "silu_mul launch");
+        a.x = reinterpret_cast<const float *>(scratch);
+        a.x2 = nullptr;
+        launches = 2;
+    }
+    CUDA_TRY(launch_qmv(t, a, opt_qmv_stream(), dev->sm_count, enc->stream, &g_last_kernel), "mat-vec launch");
+    g_launches.fetch_add((uint64_t)launches);
     g_dispatch.fetch_add(1);
     return MLXN_OK;
 }
@@ -1891,6 +1945,34 @@ extern "C" int mlxn_quantized_matmul_id_ggml(mlxn_encoder *enc, mlxn_registry *r
     if ((rc = encoder_scratch(enc, htpe_b + hids_b + tc_b, &scratch))) return rc;
     return dispatch_id_mm_stages(enc, reg, dev, input, weight, ids, output, reinterpret_cast<uint32_t *>(scratch),
                                  reinterpret_cast<int32_t *>(scratch + htpe_b), params->n_tokens, htpe_b + hids_b, params);
+}
+
+// quantized_matmul_id_swiglu_q4_0 (src/ops/quantized_matmul_id_ggml.rs:551-670), for Q4_0, Q8_0 and Q6_K:
+// output[r, :] = W[ids[r]] . (silu(gate[r, :]) * up[r, :]) for the n_tokens * top_k rows r.
+extern "C" int mlxn_quantized_matmul_id_swiglu(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *gate,
+                                               mlxn_buffer *up, mlxn_buffer *weight, mlxn_buffer *ids, mlxn_buffer *output,
+                                               const mlxn_qmm_id_params *params) {
+    int rc = check_handles(enc, dev, {gate, up, weight, ids, output, params});
+    if (rc) return rc;
+    const int t = (int)params->ggml_type;
+    if (t != GT_Q4_0 && t != GT_Q8_0 && t != GT_Q6_K)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_id_swiglu: expected Q4_0, Q8_0 or Q6_K, got %s", ggml_name(t));
+    if (params->n_tokens == 0 || params->k == 0 || params->n == 0)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_id_swiglu: n_tokens, K, and N must all be > 0");
+    if (params->top_k == 0) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_id_swiglu: top_k must be > 0");
+    // gate and up hold one row per (token, slot) pair: validate the rest as the routed mat-vec over n_tokens * top_k "tokens"
+    mlxn_qmm_id_params q = *params;
+    const uint64_t rows = (uint64_t)params->n_tokens * params->top_k;
+    if (rows > 0x7FFFFFFFull) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_id_swiglu: n_tokens * top_k is too large");
+    q.n_tokens = (uint32_t)rows;
+    q.top_k = 1;
+    if ((rc = validate_id("quantized_matmul_id_swiglu", gate, weight, ids, output, &q))) return rc;
+    if (up->len < (size_t)rows * params->k * 4)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_id_swiglu: up buffer too small: expected %zu bytes, got %zu",
+                    (size_t)rows * params->k * 4, up->len);
+    if ((rc = check_alignment(gate, weight, output))) return rc;
+    if ((uintptr_t)up->dev() & 3u) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: f32 buffers must be 4-byte aligned");
+    return dispatch_id_mv(enc, reg, dev, gate, weight, ids, output, &q, up);
 }
 
 static int check_scratch_buffers(mlxn_buffer *htpe, mlxn_buffer *hids, const mlxn_qmm_id_params *p) {

@@ -296,7 +296,8 @@ def test_batched_launch_of_independent_matvecs(ctx, tname):
 def test_chained_matvecs_in_one_launch(ctx, tname, m):
     gtype, otype = TYPES[tname]
     d = ctx.device
-    dims = [2048, 4096, 512, 1024, 3072, 512]        # x0 [m, 2048] -> 4096 -> 512 -> 1024 -> 3072 -> 512
+    # x0 [m, 2048] -> 4096 -> 2048 -> 6144 -> 2048 -> 4096 (every K a multiple of 2048: Q6_K rows on 16-byte boundaries)
+    dims = [2048, 4096, 2048, 6144, 2048, 4096]
     ws = [normal_weights(300 + i, dims[i + 1], dims[i], otype) for i in range(len(dims) - 1)]
     wbs = [ctx.buf(w, mx.DType.U8) for w in ws]
     x0 = normal_acts(300, m, dims[0])
