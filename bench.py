@@ -1004,6 +1004,7 @@ def run_case(argv):
       --case moe_layer [m] [reps]       whole MoE FFN layer (route, gate, up, SwiGLU, down, reduce), 128 experts, top-8
       --case cmp [types] [ms]           the mat-vec kernels side by side, microseconds per call, independent and chained
                                         (CUDA-graph replay over rotating weight copies > L2)
+      --case gap                        microseconds per launch of a chain of dependent trivial kernels
     The kernel variant follows the MLXN_QMV / MLXN_QMM environment variables.  Weights are random bytes with finite
     f16 scales: the kernels' timing and memory traffic do not depend on the values."""
     import mlx_native_b200 as mx
@@ -1055,6 +1056,41 @@ def run_case(argv):
                     cells = [f"{v}{'/chain' if ch else ''} {timed(t, n, k, m, v, ch):6.2f}"
                              for ch in (False, True) for v in ("auto", "mma", "tc", "stream") if not (v == "stream" and m > 2)]
                     print(f"{t} {n:6d}x{k:<6d} m={m} ideal {ideal:5.2f} us | " + " ".join(cells), flush=True)
+        mx.set_option("qmv", "auto")
+        return
+    if mode == "gap":
+        # what a dependent launch costs on this device whatever it computes: chains of kernels that each wait for the
+        # one before (CUDA-graph replay, device-timed) -- a 64-element SwiGLU (ordinary launches) and a 16 x 256 mat-vec
+        # of the register-level kernel (programmatic dependent launches)
+        n_el, reps, chain_len = 64, 10, 200
+        a = upload(rng.standard_normal(n_el).astype(np.float32), mx.DType.F32)
+        b = upload(rng.standard_normal(n_el).astype(np.float32), mx.DType.F32)
+        w = upload(random_blocks(rng, "Q8_0", 16, 256))
+        xs = [upload(rng.standard_normal(256).astype(np.float32), mx.DType.F32)]
+        y = dev.alloc_buffer(16 * 4, mx.DType.F32)
+        p = mx.GgmlQuantizedMatmulParams(1, 16, 256, mx.GgmlType.Q8_0)
+        mx.set_option("qmv", "mma")
+
+        def chain(kind, e):
+            for _ in range(chain_len):
+                if kind == "plain":
+                    mx.silu_mul(e, reg, dev, a, b, a, n_el)
+                else:
+                    mx.quantized_matmul_ggml(e, reg, dev, xs[0], w, y, p)   # the same result buffer: write after write
+
+        for kind in ("plain", "overlapped"):
+            enc = dev.command_encoder()
+            chain(kind, enc)
+            enc.commit_and_wait()
+            enc.begin_capture()
+            chain(kind, enc)
+            g = enc.end_capture()
+            g.launch(enc)
+            enc.commit_and_wait()
+            for _ in range(reps):
+                g.launch(enc)
+            us = enc.commit_wait_with_gpu_time() / (reps * chain_len) * 1e6
+            print(f"dependent launch, {kind}: {us:.2f} us per kernel")
         mx.set_option("qmv", "auto")
         return
     enc = dev.command_encoder()

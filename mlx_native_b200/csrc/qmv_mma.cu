@@ -1,31 +1,40 @@
 // Register-level mat-vec for 1..8 activation rows (decode): y[m, n] = x[m, k] . W[n, k]^T with W in GGML blocks.
 //
-// Replaces upstream kernel_mul_mv_{q4_0,q8_0,q6_K}_f32 (src/shaders/quantized_matmul_ggml.metal:104-330).
-// The operation is bound by the weight stream, so the kernel is organised around three things:
+// Replaces upstream kernel_mul_mv_{q4_0,q8_0,q6_K}_f32 (src/shaders/quantized_matmul_ggml.metal:104-330), and for a
+// handful of (token, slot) rows kernel_mul_mv_id_* and its fused SwiGLU form (src/shaders/quantized_matmul_id_ggml.metal).
+// The operation is bound by the weight stream, so the kernel is organised around these things:
 //
-//  * One launch, no scratch memory, no atomics.  The activations are split into f16 hi + lo halves inside the
-//    kernel (per block of 32 / scale group of 16, pre-scaled by a power of two so that both halves stay f16
-//    normals whatever the magnitudes), and every output element is written exactly once by one CTA, so results
-//    are bit-reproducible and there is nothing to zero or to combine afterwards.
-//  * The multiply-adds run on the tensor cores from registers (mma.sync m16n8k16, f16 x f16 -> f32).  The
-//    weights enter as *exact integers*: the raw 4/6/8-bit codes written as f16 subnormals (n * 2^-24; one or two
-//    bit operations per pair of codes, no conversion instruction).  A 16-row weight tile is the A operand, the
-//    (up to 8) activation rows are the 8 columns of B.  Every block of 32 (Q6_K: scale group of 16) gets its own
-//    accumulator, started at -offset * sum(x) so that the unsigned codes need no subtraction, and is folded into
-//    the running sum with the block's f16 scale: four multiply-adds per 512 weights.
-//  * The weights arrive through a shared-memory ring filled by one 2-D tensor-map copy (TMA) per stage of
-//    R rows x 256 (Q6_K: 512) K values.  A CTA is small (8 consumer warps + a producer warp, about 100 KB of
-//    shared memory) so that two are resident per SM: launched as a programmatic dependent, the next mat-vec in
-//    the stream fills its ring with weights while the one ahead is still running, and starts computing the
-//    moment its activations are final.
+//  * One launch, no scratch memory, no atomics on results.  The activations are split into f16 hi + lo halves inside
+//    the kernel (per block of 32 / scale group of 16, pre-scaled by a power of two so that both halves stay f16
+//    normals whatever the magnitudes), and every output element is written exactly once by one CTA, so results are
+//    bit-reproducible and there is nothing to zero or to combine afterwards.
+//  * The multiply-adds run on the tensor cores from registers (mma.sync m16n8k16, f16 x f16 -> f32).  The weights
+//    enter as *exact integers*: the raw 4/6/8-bit codes written as f16 subnormals (n * 2^-24; about one bit operation
+//    per pair of codes, no conversion instruction).  A 16-row weight tile is the A operand.  The 8 columns of B are
+//    (activation row, f16 half): column 2 r holds the hi halves of activation row r, column 2 r + 1 the lo halves, so
+//    one multiply yields both partial sums of up to four activation rows (two "sets" for five to eight).  The codes
+//    are unsigned; the bias (8, 32, 128) times the block's activation sum is added with the block's scale.
+//  * The weights arrive through a shared-memory ring filled by 2-D tensor-map copies (TMA) of R rows x one K stage,
+//    with an L2 evict-first hint (they pass once); the activations are re-read by every item and carry evict-last.
+//    There is no producer warp: thread 0 fills the ring at the start and afterwards the warp that is the last of the
+//    eight to release a slot issues the copy of the stage that gets the slot next.  A CTA is 8 warps, 128 registers
+//    and about 112 KB of shared memory, two per SM.  Launched as a programmatic dependent, the next mat-vec in the
+//    stream fills its ring with weights while the one ahead is still running.
+//  * Q4_0 / Q8_0 blocks are worked on in pairs: the even block of a pair starts on a 4-byte boundary, lanes 1..3 read
+//    whole words of its codes and lane 0 the two half words at either end, which sit in the words that also hold the
+//    pair's two f16 scales (so with one activation row the scales cost no load).  All shared-memory offsets inside a
+//    stage are compile-time constants of the instructions.
+//  * One launch carries up to 16 mat-vecs of the same block type (MwBatch): conflict-free neighbours of an encoder
+//    share one work list cut into chunks of equal numbers of stages.  Optionally (dep_mask) mat-vecs that depend on one
+//    another ride in one cooperative launch with a bounded barrier across the grid between them.
 //
-// Work split: an item is R = 16 * TPW weight rows over all of K; CTA c takes items c, c + grid, ...  Inside a
-// CTA the eight consumer warps split every stage along K (warp w owns block w of the stage's eight; Q6_K: one
-// (super-block, half, 16-column strip) of the stage's two super-blocks), each keeping TPW accumulator tiles; at
-// the end of an item the eight partial sums per output are added in a fixed order through shared memory.
+// Work split: an item is R = 16 * TPW weight rows over all of K; inside a CTA the eight warps split every stage along
+// K (Q4_0 / Q8_0: warp w owns blocks KB w .. KB w + KB - 1 of the stage's 8 KB; Q6_K: one (super-block parity, half,
+// 16-column strip) of the stage's 2 KB super-blocks), each keeping TPW accumulator tiles; at the end of an item the
+// eight partial sums per output are added in a fixed order through shared memory.
 //
-// Supported: Q4_0 / Q8_0 with k % 256 == 0, Q6_K with k % 512 == 0; weight rows that start on 16-byte boundaries;
-// dense form.  Everything else takes the other mat-vec kernels.
+// Supported: Q4_0 / Q8_0 with k % 256 == 0, Q6_K with k % 512 == 0; weight rows that start on 16-byte boundaries
+// (Q6_K also rows of 16 j + 8 bytes, in pairs).  Everything else takes the other mat-vec kernels.
 #include "tensor_map.cuh"
 
 #include <cstdio>
@@ -1087,15 +1096,21 @@ static cudaError_t launch_mw_t(const QmvArgs *ops, int nops, uint32_t mmax, int 
 cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
     if (ctas_per_sm < 1) ctas_per_sm = 1;
     if (ctas_per_sm > 2) ctas_per_sm = 2;
-    uint64_t rows = 0;   // of the launch's largest mat-vec
     uint32_t mmax = 1;
-    for (int i = 0; i < nops; i++) {
-        if (ops[i].n > rows) rows = ops[i].n;
+    for (int i = 0; i < nops; i++)
         if (ops[i].m > mmax) mmax = ops[i].m;
-    }
     if (tpw <= 0) {
-        // measured: 64-row groups from 8192 rows on (every other CTA slot still gets one), 16-row groups below
-        tpw = rows >= 8192 ? 4 : 1;
+        // measured: the largest row group (the activation split is paid once per group) that still gives at least every
+        // other CTA slot an item; 16-row groups when even 32-row groups do not
+        tpw = 1;
+        for (int cand = 4; cand >= 2; cand >>= 1) {
+            uint64_t items = 0;
+            for (int i = 0; i < nops; i++) items += (ops[i].n + 16u * cand - 1) / (16u * cand);
+            if (items >= (uint64_t)sm_count) {
+                tpw = cand;
+                break;
+            }
+        }
     }
     switch (ggml_type) {
     case GT_Q4_0: return launch_mw_t<GT_Q4_0>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
