@@ -212,6 +212,19 @@ typedef struct mlxn_qmm_id_params {
  * m <= 8 (or k < 32) runs the fused dequant-dot mat-vec kernels, larger m the tensor-core mat-mat. */
 int mlxn_quantized_matmul_ggml(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
                                mlxn_buffer *weight, mlxn_buffer *output, const mlxn_qmm_params *params);
+/* GgmlQuantizedMatmulPerm021Params (src/ops/quantized_matmul_ggml.rs:612-625). */
+typedef struct mlxn_qmm_perm021_params {
+    uint32_t m, n, k;      /* k = n_heads * head_dim */
+    uint32_t head_dim;     /* a positive multiple of 32 */
+    uint32_t ggml_type;    /* MLXN_GGML_Q4_0 or MLXN_GGML_Q6_K */
+} mlxn_qmm_perm021_params;
+/* quantized_matmul_mm_tensor_perm021 (src/ops/quantized_matmul_ggml.rs:640-742; kernel
+ * src/shaders/quantized_matmul_mm_tensor.metal:411-598): the tensor-core mat-mat whose activations are the
+ * attention output where it lies, bf16 [n_heads, seq_len = m, head_dim], cast bf16 -> f32 -> f16 as upstream does
+ * (:520-539).  weight: [n, k] blocks; output: f32 [m, n].  Always the mat-mat route, at any m. */
+int mlxn_quantized_matmul_mm_tensor_perm021(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev,
+                                            mlxn_buffer *input_bf16, mlxn_buffer *weight, mlxn_buffer *output,
+                                            const mlxn_qmm_perm021_params *params);
 /* dispatch_mm_for_test (src/ops/quantized_matmul_ggml.rs:371-402): force the mat-mat path at any m. */
 int mlxn_dispatch_mm_for_test(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
                               mlxn_buffer *weight, mlxn_buffer *output, const mlxn_qmm_params *params);

@@ -20,6 +20,10 @@ class QmmParams(C.Structure):
     _fields_ = [("m", u32), ("n", u32), ("k", u32), ("ggml_type", u32)]
 
 
+class QmmPerm021Params(C.Structure):
+    _fields_ = [("m", u32), ("n", u32), ("k", u32), ("head_dim", u32), ("ggml_type", u32)]
+
+
 class QmmIdParams(C.Structure):
     _fields_ = [("n_tokens", u32), ("top_k", u32), ("n", u32), ("k", u32), ("n_experts", u32),
                 ("ggml_type", u32), ("expert_stride", u64)]
@@ -96,6 +100,7 @@ SIGNATURES = {
     "mlxn_quantized_matmul_ggml": (i32, [vp, vp, vp, vp, vp, vp, C.POINTER(QmmParams)]),
     "mlxn_quantized_matmul_ggml_sharded": (i32, [vp, vp, vp, vp, vp, vp, C.POINTER(QmmParams), C.c_uint32, C.c_uint32,
                                                  C.POINTER(C.c_void_p), C.c_uint32]),
+    "mlxn_quantized_matmul_mm_tensor_perm021": (i32, [vp, vp, vp, vp, vp, vp, C.POINTER(QmmPerm021Params)]),
     "mlxn_dispatch_mm_for_test": (i32, [vp, vp, vp, vp, vp, vp, C.POINTER(QmmParams)]),
     "mlxn_quantized_matmul_id_ggml": (i32, [vp, vp, vp, vp, vp, vp, vp, C.POINTER(QmmIdParams)]),
     "mlxn_quantized_matmul_id_swiglu": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, C.POINTER(QmmIdParams)]),

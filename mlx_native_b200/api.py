@@ -14,7 +14,7 @@ from dataclasses import dataclass
 import numpy as np
 
 from . import _native
-from ._native import QmmIdParams, QmmParams
+from ._native import QmmIdParams, QmmParams, QmmPerm021Params
 
 
 # ---------------------------------------------------------------- errors (src/error.rs:21-89)
@@ -115,6 +115,18 @@ class GgmlQuantizedMatmulParams:      # src/ops/quantized_matmul_ggml.rs:183-194
 
     def _c(self) -> QmmParams:
         return QmmParams(self.m, self.n, self.k, int(self.ggml_type))
+
+
+@dataclass(frozen=True)
+class GgmlQuantizedMatmulPerm021Params:   # src/ops/quantized_matmul_ggml.rs:612-625
+    m: int
+    n: int
+    k: int
+    head_dim: int
+    ggml_type: GgmlType
+
+    def _c(self):
+        return _native.QmmPerm021Params(self.m, self.n, self.k, self.head_dim, int(self.ggml_type))
 
 
 @dataclass(frozen=True)
@@ -525,6 +537,13 @@ def dispatch_mm_for_test(encoder, registry, device, input, weight, output, param
     """src/ops/quantized_matmul_ggml.rs:371-402."""
     _check(_native.lib().mlxn_dispatch_mm_for_test(encoder._h, _h(registry), device._h, _h(input), _h(weight),
                                                    _h(output), C.byref(params._c())))
+
+
+def quantized_matmul_mm_tensor_perm021(encoder, registry, device, input_bf16, weight, output,
+                                       params: GgmlQuantizedMatmulPerm021Params) -> None:
+    """src/ops/quantized_matmul_ggml.rs:640-742: the mat-mat on bf16 activations laid out [n_heads, seq_len, head_dim]."""
+    _check(_native.lib().mlxn_quantized_matmul_mm_tensor_perm021(encoder._h, _h(registry), device._h, _h(input_bf16),
+                                                                 _h(weight), _h(output), C.byref(params._c())))
 
 
 def noalloc_scratch_limit() -> int:

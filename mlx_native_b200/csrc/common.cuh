@@ -122,6 +122,11 @@ struct QmmArgs {
     // buffers (peer memory), as for the mat-vec (see QmvArgs).  y_ld == 0: a plain [m, n] result.
     uint32_t y_ld, y_col0, n_peer;
     float *y_peer[7];
+    // bf16 "perm021" activations (dense tensor-core form only; src/ops/quantized_matmul_ggml.rs:573-742): x[row][kk] is
+    // read from a bf16 array laid out [k / head_dim heads][m rows][head_dim] — the attention output before its permute —
+    // and cast bf16 -> f32 -> f16 while it is packed.  nullptr: the f32 array `x`.
+    const uint16_t *x_bf16;
+    uint32_t head_dim;
 };
 __host__ __device__ inline uint32_t qmm_ld(const QmmArgs &a) { return a.y_ld ? a.y_ld : a.n; }
 

@@ -222,7 +222,8 @@ __global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *x
                 const int32_t id = a.hids[(size_t)e * a.hids_stride + row];
                 src = (id >= 0 && (uint32_t)id < a.total_rows) ? id / (int32_t)a.top_k : -1;
             }
-            if (src >= 0) src_row[i] = a.x + (size_t)src * a.k;
+            // (perm021 form: the pointer only marks the row as present; the element addresses are formed per chunk)
+            if (src >= 0) src_row[i] = a.x_bf16 ? reinterpret_cast<const float *>(a.x_bf16) : a.x + (size_t)src * a.k;
         }
     }
     for (uint32_t kc = blockIdx.x; kc < nchunks; kc += gridDim.x) {
@@ -237,7 +238,17 @@ __global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *x
             if (src_row[i] && k0 < a.k) {
                 const float *xp = src_row[i] + k0;
                 float v[8];
-                if (k0 + 8 <= a.k && (((uintptr_t)xp) & 15u) == 0) {
+                if (a.x_bf16) {
+                    // eight consecutive K values lie inside one head (head_dim is a multiple of 32): 16 bytes of bf16
+                    const uint32_t h = k0 / a.head_dim, d0 = k0 - h * a.head_dim, row = mt * NT + r;
+                    const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(a.x_bf16 + ((size_t)h * a.m + row) * a.head_dim + d0));
+                    const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {   // bf16 -> f32 is exact; f32 -> f16 rounds to nearest even below
+                        v[2 * u] = __uint_as_float(w4[u] << 16);
+                        v[2 * u + 1] = __uint_as_float(w4[u] & 0xFFFF0000u);
+                    }
+                } else if (k0 + 8 <= a.k && (((uintptr_t)xp) & 15u) == 0) {
                     const float4 lo = __ldg(reinterpret_cast<const float4 *>(xp));
                     const float4 hi = __ldg(reinterpret_cast<const float4 *>(xp) + 1);
                     v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;

@@ -695,6 +695,7 @@ static const char *const kKernelNames[] = {
     "kernel_mul_mv_q4_0_f32", "kernel_mul_mv_q8_0_f32", "kernel_mul_mv_q6_K_f32",
     "kernel_mul_mm_q4_0_f32", "kernel_mul_mm_q8_0_f32", "kernel_mul_mm_q6_K_f32",
     "kernel_mul_mm_q4_0_tensor_f32", "kernel_mul_mm_q8_0_tensor_f32", "kernel_mul_mm_q6_K_tensor_f32",
+    "kernel_mul_mm_q4_0_tensor_bf16_perm021", "kernel_mul_mm_q6_K_tensor_bf16_perm021",
     "kernel_mul_mv_id_q4_0_f32", "kernel_mul_mv_id_q8_0_f32", "kernel_mul_mv_id_q6_K_f32", "kernel_mul_mv_id_q4_0_f32_swiglu",
     "kernel_mul_mm_id_map0_ne20_1", "kernel_mul_mm_id_map0_ne20_8",
     // the bucketing kernel takes any top_k; the values upstream's audit lists as uncovered there
@@ -1737,6 +1738,65 @@ extern "C" int mlxn_quantized_matmul_ggml_sharded(mlxn_encoder *enc, mlxn_regist
     }
     if (params->m > MLXN_MM_ROUTING_THRESHOLD) return dispatch_mm(enc, reg, dev, input, weight, output, params, &sh);
     return dispatch_mv(enc, reg, dev, input, weight, output, params, &sh);
+}
+
+// quantized_matmul_mm_tensor_perm021 (src/ops/quantized_matmul_ggml.rs:640-742): the O-projection reads the attention
+// output where it lies — bf16 [n_heads, seq_len, head_dim] — instead of a permuted f32 copy.
+extern "C" int mlxn_quantized_matmul_mm_tensor_perm021(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev,
+                                                       mlxn_buffer *input_bf16, mlxn_buffer *weight, mlxn_buffer *output,
+                                                       const mlxn_qmm_perm021_params *p) {
+    int rc = check_handles(enc, dev, {input_bf16, weight, output, p});
+    if (rc) return rc;
+    const int t = (int)p->ggml_type;
+    if (t != GT_Q4_0 && t != GT_Q6_K)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_mm_tensor_perm021: unsupported ggml_type %s (only Q4_0 and Q6_K are instantiated)",
+                    ggml_name(t));
+    if (p->head_dim == 0 || p->head_dim % 32 != 0)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_mm_tensor_perm021: head_dim %u must be a positive multiple of 32 (NK tile width)",
+                    p->head_dim);
+    if (p->m == 0 || p->n == 0 || p->k == 0)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_mm_tensor_perm021: M, K, and N must all be > 0");
+    if (p->k % p->head_dim != 0)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_mm_tensor_perm021: k (%u) must be divisible by head_dim (%u)", p->k,
+                    p->head_dim);
+    const uint32_t qk = ggml_qk(t);
+    if (p->k % qk != 0)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_mm_tensor_perm021: K (%u) must be divisible by block QK (%u)", p->k, qk);
+    const size_t need_in = (size_t)p->k * p->m * 2;   // n_heads * seq_len * head_dim bf16
+    if (input_bf16->len < need_in)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_mm_tensor_perm021: input_bf16 buffer too small (have %zu, need %zu)",
+                    input_bf16->len, need_in);
+    const size_t need_w = (size_t)p->n * (p->k / qk) * ggml_block_bytes(t), need_out = (size_t)p->m * p->n * 4;
+    if (weight->len < need_w)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_mm_tensor_perm021: weight buffer too small (have %zu, need %zu)", weight->len, need_w);
+    if (output->len < need_out)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_mm_tensor_perm021: output buffer too small (have %zu, need %zu)", output->len, need_out);
+    if (((uintptr_t)weight->dev() & 1u) || ((uintptr_t)output->dev() & 3u) || ((uintptr_t)input_bf16->dev() & 15u))
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: quantized_matmul_mm_tensor_perm021: weight data must be 2-byte, output 4-byte, input_bf16 16-byte aligned");
+    if ((rc = touch_kernel(reg, dev, t == GT_Q4_0 ? "kernel_mul_mm_q4_0_tensor_bf16_perm021" : "kernel_mul_mm_q6_K_tensor_bf16_perm021"))) return rc;
+    if ((rc = op_begin(enc, {{input_bf16, false}, {weight, false}, {output, true}}))) return rc;
+    QmmArgs a{};
+    a.w = weight->dev();
+    a.x = nullptr;
+    a.x_bf16 = reinterpret_cast<const uint16_t *>(input_bf16->dev());
+    a.head_dim = p->head_dim;
+    a.y = reinterpret_cast<float *>(output->dev());
+    a.m = p->m;
+    a.n = p->n;
+    a.k = p->k;
+    a.top_k = 1;
+    a.n_experts = 1;
+    a.total_rows = p->m;
+    a.status = enc->status_dev;
+    const uint32_t nt = qmm_tc_pick_nt(t, p->m, p->n, dev->sm_count, false);
+    uint8_t *scratch = nullptr;
+    if ((rc = encoder_scratch(enc, qmm_tc_scratch_bytes(a, nt, false), &scratch))) return rc;
+    int launches = 0;
+    CUDA_TRY(launch_qmm_tc(t, a, false, nt, scratch, enc->stream, &launches), "mat-mat launch");
+    g_launches.fetch_add(launches);
+    g_last_kernel = "qmm_tc";
+    g_dispatch.fetch_add(1);
+    return MLXN_OK;
 }
 
 extern "C" int mlxn_dispatch_mm_for_test(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *input,
