@@ -44,7 +44,7 @@ sys.path.insert(0, ROOT)
 SHAPES = [(4096, 4096), (1024, 4096), (12288, 4096), (4096, 12288)]  # (n, k)
 MS = [1, 2, 4, 8]
 TYPE_NAMES = ["Q8_0", "Q6_K"]
-BLOCK = {"Q4_0": (32, 18), "Q8_0": (32, 34), "Q6_K": (256, 210)}
+BLOCK = {"Q4_0": (32, 18), "Q8_0": (32, 34), "Q6_K": (256, 210), "Q4_K": (256, 144)}
 METRIC = "q-matvec weight GB/s"
 
 
@@ -1010,7 +1010,7 @@ def run_case(argv):
     import mlx_native_b200 as mx
     from mlx_native_b200.ggml_pack import random_blocks
 
-    gt = {"Q4_0": mx.GgmlType.Q4_0, "Q8_0": mx.GgmlType.Q8_0, "Q6_K": mx.GgmlType.Q6_K}
+    gt = {"Q4_0": mx.GgmlType.Q4_0, "Q8_0": mx.GgmlType.Q8_0, "Q6_K": mx.GgmlType.Q6_K, "Q4_K": mx.GgmlType.Q4_K}
     mode = argv[0] if argv else "mv"
     dev = mx.MlxDevice.new(0)
     reg = mx.KernelRegistry.new()
@@ -1053,8 +1053,9 @@ def run_case(argv):
             for (n, k) in SHAPES:
                 for m in ms:
                     ideal = weight_bytes(t, n, k) / (measured_peaks()[0] * 1e3)
+                    variants = ("auto", "simple") if t == "Q4_K" else ("auto", "mma", "tc", "stream")
                     cells = [f"{v}{'/chain' if ch else ''} {timed(t, n, k, m, v, ch):6.2f}"
-                             for ch in (False, True) for v in ("auto", "mma", "tc", "stream") if not (v == "stream" and m > 2)]
+                             for ch in (False, True) for v in variants if not (v in ("stream", "simple") and m > 2)]
                     print(f"{t} {n:6d}x{k:<6d} m={m} ideal {ideal:5.2f} us | " + " ".join(cells), flush=True)
         mx.set_option("qmv", "auto")
         return

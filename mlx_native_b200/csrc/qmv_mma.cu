@@ -58,6 +58,10 @@ template <int T> struct MwTraits;
 template <> struct MwTraits<GT_Q4_0> { static constexpr int UK = 256, UBYTES = 144, OFFSET = 8, NG = 1, NM = 2; };
 template <> struct MwTraits<GT_Q8_0> { static constexpr int UK = 256, UBYTES = 272, OFFSET = 128, NG = 1, NM = 2; };
 template <> struct MwTraits<GT_Q6_K> { static constexpr int UK = 512, UBYTES = 420, OFFSET = 32, NG = 4, NM = 4; };
+// Q4_K: a unit is one PAIR of 32-value sub-blocks of a super-block (32 bytes: low nibbles = the first sub-block, high
+// nibbles = the second; four MMAs, two scale groups).  The codes carry no bias; the sub-block's minimum dmin * m is
+// subtracted through the activation sum (OFFSET 1 is the weight of that sum).
+template <> struct MwTraits<GT_Q4_K> { static constexpr int UK = 512, UBYTES = 288, OFFSET = 1, NG = 2, NM = 4; };
 
 // Shared-memory bytes per row of a stage of KB units per warp: the stage's bytes plus the up to 12 bytes between
 // the 16-byte boundary the copy starts at and the stage's first byte (Q6_K), rounded up to an ODD multiple of 16,
@@ -65,10 +69,10 @@ template <> struct MwTraits<GT_Q6_K> { static constexpr int UK = 512, UBYTES = 4
 // A tensor copy is at most 256 elements (2048 bytes) wide: a longer stage row arrives as two copies, the first half of
 // the stage's K range for warps 0..3 and the second for warps 4..7, each into its own R x PITCH region of the slot.
 __host__ __device__ constexpr uint32_t mw_halves(int ggml_type, int kb) {
-    return (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : 420u) * (uint32_t)kb + 12u > 2048u ? 2u : 1u;
+    return (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : ggml_type == GT_Q4_K ? 288u : 420u) * (uint32_t)kb + 12u > 2048u ? 2u : 1u;
 }
 __host__ __device__ constexpr uint32_t mw_pitch(int ggml_type, int kb) {
-    const uint32_t raw = (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : 420u) * (uint32_t)kb / mw_halves(ggml_type, kb);
+    const uint32_t raw = (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : ggml_type == GT_Q4_K ? 288u : 420u) * (uint32_t)kb / mw_halves(ggml_type, kb);
     const uint32_t lead = ggml_type == GT_Q6_K ? (kb == 1 ? 12u : 8u) : 0u;
     const uint32_t c = (raw + lead + 15u) / 16u;
     return 16u * (c | 1u);
@@ -492,6 +496,11 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                 const uint32_t sb = sp + 2 * i;
                 xrel0[p] = 256 * sb + 128 * nh + 32 * hq + 16 * js + 4 * tt;
                 xrel1[p] = xrel0[p] + 2;
+            } else if constexpr (T == GT_Q4_K) {
+                // MMA hq of the unit: sub-block hq / 2 of the pair (low / high nibbles), its elements 16 (hq % 2) + 4 tt ...
+                const uint32_t sb = sp + 2 * i;
+                xrel0[p] = 256 * sb + 64 * (w & 3u) + 32 * (hq >> 1) + 16 * (hq & 1u) + 4 * tt;
+                xrel1[p] = xrel0[p] + 2;
             } else {
                 const uint32_t b = KB * w + i;
                 uint32_t p0, p1;
@@ -563,7 +572,7 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                 float s, inv;
                 pow2_scale(am, s, inv);
                 // Q4_0: the high nibbles stay where they are in their byte (16 x the code): their activations / 16
-                const float sv = (T == GT_Q4_0 && ((bp >> 2) & 1u)) ? s * 0.0625f : s;
+                const float sv = ((T == GT_Q4_0 && ((bp >> 2) & 1u)) || (T == GT_Q4_K && ((bp >> 3) & 1u))) ? s * 0.0625f : s;
                 uint32_t f0, f1, f2, f3;
                 split4(xr[p][0] * sv, xr[p][1] * sv, xr[p][2] * sv, xr[p][3] * sv, f0, f1, f2, f3);
                 if (bp < (uint32_t)(NB * PIECES)) {
@@ -668,6 +677,40 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                 }
 #endif
                 uint32_t lead = 0;
+                if constexpr (T == GT_Q4_K) {
+                    // (d * sc, d * sc', dmin * m, dmin * m') of the warp's sub-block pair, for every row of the stage (lanes
+                    // split the rows); the 6-bit scales and minima are unpacked as in src/gguf/mod.rs:440-452
+                    const uint32_t pu = w & 3u;
+#pragma unroll
+                    for (int i = 0; i < KB; i++) {
+#pragma unroll
+                        for (int rr = 0; rr < (R + 31) / 32; rr++) {
+                            const uint32_t r = lane + 32 * rr;
+                            if (r < (uint32_t)R) {
+                                const uint32_t rb = stage + r * PITCH + 144 * (sp + 2 * i);
+                                const uint32_t dd = lds32(rb);
+                                const float d = f16lo_to_float(dd), dmin = f16hi_to_float(dd);
+                                const uint32_t s0 = lds32(rb + 4), s1 = lds32(rb + 8), s2 = lds32(rb + 12);   // scales[0..11]
+                                uint32_t sc0, sc1, m0, m1;
+                                if (pu < 2) {          // sub-blocks j = 2 pu, 2 pu + 1 < 4: sc = s[j] & 63, m = s[j + 4] & 63
+                                    const uint32_t a = s0 >> (16 * pu), b = s1 >> (16 * pu);
+                                    sc0 = a & 63u; sc1 = (a >> 8) & 63u;
+                                    m0 = b & 63u; m1 = (b >> 8) & 63u;
+                                } else {               // j >= 4: sc = (s[j + 4] & 15) | (s[j - 4] >> 6) << 4, m = (s[j + 4] >> 4) | (s[j] >> 6) << 4
+                                    const uint32_t sh = 16 * (pu - 2);
+                                    const uint32_t a = s2 >> sh, lo = s0 >> sh, hi = s1 >> sh;
+                                    sc0 = (a & 15u) | (((lo >> 6) & 3u) << 4);
+                                    sc1 = ((a >> 8) & 15u) | (((lo >> 14) & 3u) << 4);
+                                    m0 = ((a >> 4) & 15u) | (((hi >> 6) & 3u) << 4);
+                                    m1 = ((a >> 12) & 15u) | (((hi >> 14) & 3u) << 4);
+                                }
+                                sts128(ptab + (i * R + r) * 16, __float_as_uint(d * (float)sc0), __float_as_uint(d * (float)sc1),
+                                       __float_as_uint(dmin * (float)m0), __float_as_uint(dmin * (float)m1));
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
                 if constexpr (T == GT_Q6_K) {
                     lead = (s * SBYTES) & 15u;   // a multiple of 4
                     // d * sub-scale of the warp's scale groups, for every row of the stage (lanes split the rows)
@@ -699,7 +742,72 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                 // wrapped, the columns past 2 m are never looked at.  Its outputs belong to activation row t (+ 4 per set).
                 const uint32_t xlane = xsb + ((((g >> 1) & (uint32_t)(MP - 1)) * NM * 4 + t) * 16) + (g & 1u) * 8;
                 const uint32_t clane = xcb + (t & (uint32_t)(MP - 1)) * (NG * 8);
-                if constexpr (T == GT_Q6_K) {
+                if constexpr (T == GT_Q4_K) {
+                    // row g of the stage, the warp's first super-block, its pair of sub-blocks: 32 bytes of nibbles 16 bytes in
+                    const uint32_t pQ = stage + g * PITCH + 144 * sp + 16 + 32 * (w & 3u) + 4 * t, pP = ptab + g * 16;
+                    const float zz[4] = {0.f, 0.f, 0.f, 0.f};
+                    static_for<0, KB>([&](auto IC) {
+                        constexpr uint32_t i = decltype(IC)::value;
+                        uint32_t bf[NS][4][2];
+                        float cc[NS][2], cs[NS][2];
+                        static_for<0, NS>([&](auto SC) {
+                            constexpr uint32_t ns = decltype(SC)::value;
+                            static_for<0, 4>([&](auto QC) {
+                                constexpr uint32_t q = decltype(QC)::value;
+                                lds64i<(((i * MP + 4 * ns) * 4 + q) * 64)>(xlane, bf[ns][q][0], bf[ns][q][1]);
+                            });
+                            static_for<0, 2>([&](auto QC) {
+                                constexpr uint32_t q = decltype(QC)::value;
+                                uint32_t u0, u1;
+                                lds64i<(((i * MP + 4 * ns) * 2 + q) * 8)>(clane, u0, u1);
+                                cc[ns][q] = __uint_as_float(u0);
+                                cs[ns][q] = __uint_as_float(u1);
+                            });
+                        });
+                        static_for<0, TPW>([&](auto JC) {
+                            constexpr uint32_t j = decltype(JC)::value;
+                            uint32_t w0[2], w1[2], pv[2][4];
+                            static_for<0, 2>([&](auto HC) {
+                                constexpr uint32_t h = decltype(HC)::value;
+                                constexpr uint32_t off = (16 * j + 8 * h) * PITCH + 288 * i;   // rows g, g + 8 of tile j
+                                w0[h] = lds32i<off>(pQ);
+                                w1[h] = lds32i<off + 16>(pQ);
+                                lds128i<((i * R) + 16 * j + 8 * h) * 16>(pP, pv[h][0], pv[h][1], pv[h][2], pv[h][3]);
+                            });
+                            // low nibbles: first sub-block, elements c0..c3 of the word's bytes; high nibbles (x 16): the second
+                            uint32_t a[4][4];
+                            a[0][0] = w0[0] & 0x000F000Fu; a[0][2] = (w0[0] >> 8) & 0x000F000Fu;
+                            a[0][1] = w0[1] & 0x000F000Fu; a[0][3] = (w0[1] >> 8) & 0x000F000Fu;
+                            a[1][0] = w1[0] & 0x000F000Fu; a[1][2] = (w1[0] >> 8) & 0x000F000Fu;
+                            a[1][1] = w1[1] & 0x000F000Fu; a[1][3] = (w1[1] >> 8) & 0x000F000Fu;
+                            a[2][0] = w0[0] & 0x00F000F0u; a[2][2] = (w0[0] >> 8) & 0x00F000F0u;
+                            a[2][1] = w0[1] & 0x00F000F0u; a[2][3] = (w0[1] >> 8) & 0x00F000F0u;
+                            a[3][0] = w1[0] & 0x00F000F0u; a[3][2] = (w1[0] >> 8) & 0x00F000F0u;
+                            a[3][1] = w1[1] & 0x00F000F0u; a[3][3] = (w1[1] >> 8) & 0x00F000F0u;
+                            const float pa0 = __uint_as_float(pv[0][0]), pa1 = __uint_as_float(pv[0][1]), ma0 = __uint_as_float(pv[0][2]),
+                                        ma1 = __uint_as_float(pv[0][3]);
+                            const float pb0 = __uint_as_float(pv[1][0]), pb1 = __uint_as_float(pv[1][1]), mb0 = __uint_as_float(pv[1][2]),
+                                        mb1 = __uint_as_float(pv[1][3]);
+#pragma unroll
+                            for (int ns = 0; ns < NS; ns++) {
+                                float e0[4], e1[4];
+                                mma16816(e0, a[0][0], a[0][1], a[0][2], a[0][3], bf[ns][0][0], bf[ns][0][1], zz);
+                                mma16816(e1, a[2][0], a[2][1], a[2][2], a[2][3], bf[ns][2][0], bf[ns][2][1], zz);
+                                mma16816(e0, a[1][0], a[1][1], a[1][2], a[1][3], bf[ns][1][0], bf[ns][1][1], e0);
+                                mma16816(e1, a[3][0], a[3][1], a[3][2], a[3][3], bf[ns][3][0], bf[ns][3][1], e1);
+                                const float ta0 = pa0 * cs[ns][0], ta1 = pa1 * cs[ns][1], tb0 = pb0 * cs[ns][0], tb1 = pb1 * cs[ns][1];
+                                acc[j][ns][0] = fmaf(ta0, e0[0], fmaf(ma0, cc[ns][0], acc[j][ns][0]));
+                                acc[j][ns][1] = fmaf(ta0, e0[1], acc[j][ns][1]);
+                                acc[j][ns][2] = fmaf(tb0, e0[2], fmaf(mb0, cc[ns][0], acc[j][ns][2]));
+                                acc[j][ns][3] = fmaf(tb0, e0[3], acc[j][ns][3]);
+                                acc[j][ns][0] = fmaf(ta1, e1[0], fmaf(ma1, cc[ns][1], acc[j][ns][0]));
+                                acc[j][ns][1] = fmaf(ta1, e1[1], acc[j][ns][1]);
+                                acc[j][ns][2] = fmaf(tb1, e1[2], fmaf(mb1, cc[ns][1], acc[j][ns][2]));
+                                acc[j][ns][3] = fmaf(tb1, e1[3], acc[j][ns][3]);
+                            }
+                        });
+                    });
+                } else if constexpr (T == GT_Q6_K) {
                     // odd super-blocks start 2 bytes past a 4-byte boundary: their words are read from the boundary below
                     // and shifted by a byte permute (ODD).  The parity is the warp's, so the branch sits outside the loops.
                     auto body = [&](auto ODDC) {
@@ -877,7 +985,7 @@ __global__ void __launch_bounds__(kMwThreads, 2)
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
-static uint32_t mw_uk(int t) { return t == GT_Q6_K ? 512u : 256u; }
+static uint32_t mw_uk(int t) { return t == GT_Q6_K ? 512u : 256u; }   // (Q4_K: a last stage of one super-block is fine)
 
 // Q6_K rows of 16 j + 8 bytes with an even row count: pairs of rows start on 16-byte boundaries (see PAIR above)
 bool qmv_mma_pair_mode(int ggml_type, const QmvArgs &a) {
@@ -887,7 +995,7 @@ bool qmv_mma_pair_mode(int ggml_type, const QmvArgs &a) {
 }
 
 bool qmv_mma_supported(int ggml_type, const QmvArgs &a) {
-    if (ggml_type != GT_Q4_0 && ggml_type != GT_Q8_0 && ggml_type != GT_Q6_K) return false;
+    if (ggml_type != GT_Q4_0 && ggml_type != GT_Q8_0 && ggml_type != GT_Q6_K && ggml_type != GT_Q4_K) return false;
     if (a.ids || a.nprob != 1 || a.m < 1 || a.m > 8) return false;
     if (a.k == 0 || a.n == 0 || a.k % mw_uk(ggml_type) != 0) return false;
     const uint64_t row_bytes = (uint64_t)(a.k / ggml_qk(ggml_type)) * ggml_block_bytes(ggml_type);
@@ -900,7 +1008,7 @@ bool qmv_mma_supported(int ggml_type, const QmvArgs &a) {
 // The expert-routed form: one problem per (token, slot) row (m = 1, `ids` and `id_index` set).  The stacked weights are
 // addressed through a 3-D map [expert][row][bytes], so rows and experts must start on 16-byte boundaries.
 bool qmv_mma_supported_routed(int ggml_type, const QmvArgs &a) {
-    if (ggml_type != GT_Q4_0 && ggml_type != GT_Q8_0 && ggml_type != GT_Q6_K) return false;
+    if (ggml_type != GT_Q4_0 && ggml_type != GT_Q8_0 && ggml_type != GT_Q6_K && ggml_type != GT_Q4_K) return false;
     if (!a.ids || a.m != 1 || a.k == 0 || a.n == 0 || a.n_experts == 0 || a.k % mw_uk(ggml_type) != 0) return false;
     const uint64_t row_bytes = (uint64_t)(a.k / ggml_qk(ggml_type)) * ggml_block_bytes(ggml_type);
     if (row_bytes % 16 != 0 || row_bytes >= (1ull << 31) || a.expert_stride % 16 != 0 || a.expert_stride < row_bytes * a.n) return false;
@@ -921,7 +1029,7 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
     if (const char *e = getenv("MLXN_MW_DEBUG")) c.debug = (uint32_t)atoi(e);
 #endif
     const size_t xst_bytes = mw_align((size_t)kMwWarps * XST, 128);
-    const size_t ptab_bytes = T == GT_Q6_K ? (size_t)kMwWarps * R * 16 * KB : 0;
+    const size_t ptab_bytes = (T == GT_Q6_K || T == GT_Q4_K) ? (size_t)kMwWarps * R * 16 * KB : 0;
     const size_t red_bytes = (size_t)kMwWarps * MP * R * 4;
     const size_t tail = xst_bytes + ptab_bytes + red_bytes;
     // two CTAs per SM: 228 KB, less 1 KB per CTA for the system and the kernel's few hundred bytes of static storage
@@ -1052,7 +1160,7 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
 // TPW is, so many activation rows want a small KB.
 template <int T, int MP, bool PAIR>
 static cudaError_t launch_mw_m(const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
-    if constexpr (T == GT_Q6_K) {
+    if constexpr (T == GT_Q6_K || T == GT_Q4_K) {
         if (tpw >= 4 || MP == 8) return launch_mw<T, 4, 1, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
         if constexpr (MP <= 4) {
             if (tpw >= 2 || MP == 4) return launch_mw<T, 2, 2, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
@@ -1116,6 +1224,7 @@ cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs *ops, int nops, int sm_c
     case GT_Q4_0: return launch_mw_t<GT_Q4_0>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
     case GT_Q8_0: return launch_mw_t<GT_Q8_0>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
     case GT_Q6_K: return launch_mw_t<GT_Q6_K>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
+    case GT_Q4_K: return launch_mw_t<GT_Q4_K>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
     default: return cudaErrorInvalidValue;
     }
 }

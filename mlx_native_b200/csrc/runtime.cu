@@ -904,7 +904,8 @@ static int encoder_flush_pending(mlxn_encoder *e) {
     // (measured: one or two activation rows stay with this kernel, except one Q6_K row on a small matrix, where the
     //  streaming kernel's short start wins; more rows take the tensor-memory kernel, whose time does not grow with m)
     const bool q6_one_row_small = e->pend_type == GT_Q6_K && a0.m == 1 && (uint64_t)a0.n * a0.k < (1ull << 23);
-    const bool lone_other = e->pend.size() == 1 && opt_qmv() == 3 && a0.n_peer == 0 && !a0.ids && (q6_one_row_small || a0.m > 2);
+    const bool lone_other = e->pend.size() == 1 && opt_qmv() == 3 && a0.n_peer == 0 && !a0.ids && e->pend_type != GT_Q4_K &&
+                            (q6_one_row_small || a0.m > 2);
     if (lone_other) {
         if (!q6_one_row_small && qmv_tc_supported(e->pend_type, a0)) {
             uint8_t *scratch = nullptr;
@@ -1519,6 +1520,7 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
         if (mode != 3) return false;
         // measured: batched, the register-level kernel is the faster one except for many activation rows on the
         // long-K and the widest Q6_K shapes
+        if ((int)p->ggml_type == GT_Q4_K) return true;   // (its only other kernel is the plain one)
         if (a.m > 4) return false;
         if (a.m == 4 && a.k >= 8192) return false;
         return true;
@@ -1595,7 +1597,7 @@ static int dispatch_mv(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, 
         static const int min_m_q6k = [] { const char *e = exp_env("MLXN_QMV_TC_MIN_M_Q6K"); return e ? atoi(e) : 1; }();
         const int need_m = (int)p->ggml_type == GT_Q6_K ? (a.k >= 8192 ? (min_m_q6k < 2 ? min_m_q6k : 2) : min_m_q6k) : min_m;
         const bool want_tc = mode == 2 || ((mode == 3 || mode == 4) && (int)a.m >= need_m);
-        if (mode == 4 && p->m > 8 && qmv_mma_supported((int)p->ggml_type, a)) {
+        if ((mode == 4 || (mode == 3 && (int)p->ggml_type == GT_Q4_K)) && p->m > 8 && qmv_mma_supported((int)p->ggml_type, a)) {
             CUDA_TRY(launch_qmv_mma((int)p->ggml_type, &a, 1, dev->sm_count, g_opt_mma_ctas.load(), g_opt_mma_tpw.load(), enc->stream),
                      "mat-vec launch");
             g_launches.fetch_add(1);

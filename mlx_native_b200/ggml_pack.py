@@ -88,7 +88,7 @@ def pack(ggml_type: int, values: np.ndarray) -> np.ndarray:
 
 
 # Block geometry by type name: (values per block, bytes per block, byte offset of the f16 scale d)
-BLOCK_GEOMETRY = {"Q4_0": (32, 18, 0), "Q8_0": (32, 34, 0), "Q6_K": (256, 210, 208)}
+BLOCK_GEOMETRY = {"Q4_0": (32, 18, 0), "Q8_0": (32, 34, 0), "Q6_K": (256, 210, 208), "Q4_K": (256, 144, 0)}
 
 
 def random_blocks(rng, type_name: str, n: int, k: int) -> np.ndarray:
@@ -97,4 +97,6 @@ def random_blocks(rng, type_name: str, n: int, k: int) -> np.ndarray:
     qk, bb, dpos = BLOCK_GEOMETRY[type_name]
     raw = rng.integers(0, 256, size=(n * (k // qk), bb), dtype=np.uint8)
     raw[:, dpos + 1] = (raw[:, dpos + 1] & 0x83) | 0x20   # f16 scale exponent in a small finite range
+    if type_name == "Q4_K":
+        raw[:, 3] = (raw[:, 3] & 0x83) | 0x20             # ... and the f16 dmin behind it
     return raw.reshape(-1)

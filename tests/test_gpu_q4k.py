@@ -24,8 +24,24 @@ def test_dense_matvec(ctx, n, k, m):
     wq = normal_weights(n + k, n, k, O)
     x = normal_acts(m, m, k)
     y = ctx.matmul(G, wq, x, n, k)
-    assert mx.last_kernel_name() == "qmv_simple"
+    assert mx.last_kernel_name() == "qmv_mma"            # the register-level tensor-core kernel (144-byte blocks: rows always 16-byte aligned)
     y_ref, ad = orc.qmatmul(O, wq, x, n, k, nthreads=4)
+    assert norm_err(y, y_ref, ad) <= MV_TOL
+    mx.set_option("qmv", "simple")
+    try:
+        y2 = ctx.matmul(G, wq, x, n, k)
+        assert mx.last_kernel_name() == "qmv_simple" and norm_err(y2, y_ref, ad) <= MV_TOL
+    finally:
+        mx.set_option("qmv", "auto")
+
+
+@pytest.mark.parametrize("n,k,m", [(4096, 4096, 1), (1024, 4096, 4), (12288, 4096, 2), (4096, 12288, 1), (2048, 5120, 8), (777, 2304, 3)])
+def test_dense_matvec_model_shapes(ctx, n, k, m):
+    wq = normal_weights(n + k + m, n, k, O)
+    x = normal_acts(m + 50, m, k)
+    y = ctx.matmul(G, wq, x, n, k)
+    assert mx.last_kernel_name() == "qmv_mma"
+    y_ref, ad = orc.qmatmul(O, wq, x, n, k, nthreads=8)
     assert norm_err(y, y_ref, ad) <= MV_TOL
 
 
