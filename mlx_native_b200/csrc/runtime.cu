@@ -260,9 +260,14 @@ struct mlxn_encoder {
     cudaStream_t aux = nullptr;      // side work that nothing in the group waits for (copies of results to peer GPUs)
     cudaEvent_t ev_aux = nullptr, ev_aux_join = nullptr;
     bool aux_busy = false;
-    std::vector<const void *> grp_reads, grp_writes;  // storages the current group reads / writes
-    // inputs whose host shadow was uploaded inside the group, with the lane the copy went to: a write for the other
-    // lanes, but an operation that runs on the same lane comes after the copy anyway
+    // byte ranges of storages the current group reads / writes (views of one storage that do not overlap are independent)
+    struct Span {
+        const void *st;
+        size_t lo, hi;
+    };
+    std::vector<Span> grp_reads, grp_writes;
+    // inputs whose host shadow was uploaded inside the group (the whole storage is copied), with the lane the copy went
+    // to: a write for the other lanes, but an operation that runs on the same lane comes after the copy anyway
     std::vector<std::pair<const void *, int>> grp_uploads;
     bool grp_open = false;           // ev_fork marks the start of the current group
     cudaEvent_t ev_start = nullptr, ev_end = nullptr;
@@ -1327,22 +1332,25 @@ struct OpBuf {
 };
 // `lane`: the lane the operation would run on.
 static bool op_conflicts(mlxn_encoder *e, std::initializer_list<OpBuf> bufs, int lane) {
-    auto has = [](const std::vector<const void *> &v, const void *p) {
-        for (const void *q : v)
-            if (q == p) return true;
-        return false;
-    };
     bool conflict = false;
     for (const OpBuf &ob : bufs) {
         if (!ob.b) continue;
         Storage *st = ob.b->st;
-        bool writes = ob.out;
+        bool uploads = false;
         {
             std::lock_guard<std::mutex> lk(st->mu);
-            writes = writes || st->host_newer;
+            uploads = st->host_newer;
         }
-        if (writes) conflict = conflict || has(e->grp_reads, st) || has(e->grp_writes, st);
-        else conflict = conflict || has(e->grp_writes, st);
+        // (an upload copies the whole storage: it counts as a write of all of it)
+        const size_t lo = uploads ? 0 : ob.b->offset, hi = uploads ? st->bytes : ob.b->offset + ob.b->len;
+        auto has = [&](const std::vector<mlxn_encoder::Span> &v) {
+            for (const auto &q : v)
+                if (q.st == st && q.lo < hi && lo < q.hi) return true;
+            return false;
+        };
+        const bool writes = ob.out || uploads;
+        if (writes) conflict = conflict || has(e->grp_reads) || has(e->grp_writes);
+        else conflict = conflict || has(e->grp_writes);
         for (const auto &u : e->grp_uploads)
             if (u.first == st && (writes || u.second != lane)) conflict = true;
     }
@@ -1377,16 +1385,15 @@ static int op_begin(mlxn_encoder *e, std::initializer_list<OpBuf> bufs, bool joi
     for (const OpBuf &ob : bufs) {
         if (!ob.b) continue;
         Storage *st = ob.b->st;
-        bool writes = ob.out;
+        bool uploads = false;
         {
             std::lock_guard<std::mutex> lk(st->mu);
-            writes = writes || st->host_newer;
+            uploads = st->host_newer;
         }
-        if (ob.out) e->grp_writes.push_back(st);
-        else {
-            e->grp_reads.push_back(st);
-            if (writes) e->grp_uploads.push_back({st, lane});   // its host shadow is copied in by bind() below, on this lane
-        }
+        const mlxn_encoder::Span span{st, ob.b->offset, ob.b->offset + ob.b->len};
+        if (ob.out) e->grp_writes.push_back(span);
+        else e->grp_reads.push_back(span);
+        if (uploads) e->grp_uploads.push_back({st, lane});   // its host shadow is copied in by bind() below, on this lane
         if ((rc = bind(e, ob.b, ob.out))) return rc;
     }
     return MLXN_OK;

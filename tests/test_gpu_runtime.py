@@ -270,6 +270,7 @@ def test_graph_outlives_eager_growth_of_the_encoder_scratch(ctx):
         assert "encoder that recorded it" in str(e)
     if other_is_same:
         other.commit_and_wait()
+    mx.set_option("qmv", "auto")
 
 
 def test_host_view_rewritten_right_after_a_replay(ctx):
@@ -377,3 +378,43 @@ def test_peer_barrier_passes_when_everyone_arrived_and_gives_up_otherwise(ctx):
     enc.commit_and_wait()
     with pytest.raises(mx.InvalidArgument):
         mx.peer_barrier(enc, 2, 2, ptrs, 1)
+
+
+# ---- conflict tracking is by byte range: operations on views of one storage that do not overlap are independent
+def test_views_of_one_arena_do_not_conflict(ctx):
+    from oracle import oracle as orc
+    from tests.gpu_util import MV_TOL, TYPES, norm_err, normal_acts, normal_weights
+    gtype, otype = TYPES["Q8_0"]
+    d = ctx.device
+    mx.set_option("qmv", "auto")
+    n, k, cnt = 512, 1024, 4
+    ws = [normal_weights(40 + i, n, k, otype) for i in range(cnt)]
+    xs = normal_acts(40, cnt, k)
+    xin = d.alloc_buffer(cnt * k * 4, mx.DType.F32)
+    yout = d.alloc_buffer(cnt * n * 4, mx.DType.F32)
+    xin.as_mut_slice(np.float32)[:] = xs.reshape(-1)              # one host write, one upload
+    xv = [xin.slice_view(i * k * 4, k) for i in range(cnt)]
+    yv = [yout.slice_view(i * n * 4, n) for i in range(cnt)]
+    p = mx.GgmlQuantizedMatmulParams(1, n, k, gtype)
+    wb = [ctx.buf(w, mx.DType.U8) for w in ws]
+    mx.reset_counters()
+    enc = d.command_encoder()
+    for i in range(cnt):
+        mx.quantized_matmul_ggml(enc, ctx.registry, d, xv[i], wb[i], yv[i], p)
+    enc.commit_and_wait()
+    assert mx.kernel_launch_count() == 1                           # four mat-vecs, disjoint views: one batched launch
+    y = yout.as_slice(np.float32).reshape(cnt, n)
+    for i in range(cnt):
+        y_ref, ad = orc.qmatmul(otype, ws[i], xs[i][None], n, k)
+        assert norm_err(y[i][None], y_ref, ad) <= MV_TOL
+    # overlapping views do conflict: the second call reads what the first one writes (its input view covers y row 0)
+    mx.reset_counters()
+    enc = d.command_encoder()
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, xv[0], wb[0], yv[0], p)
+    y0_as_input = yout.slice_view(0, k)                            # the first k floats of the arena = rows 0 and 1 of y
+    mx.quantized_matmul_ggml(enc, ctx.registry, d, y0_as_input, wb[1], yv[3], p)
+    enc.commit_and_wait()
+    assert mx.kernel_launch_count() == 2
+    x2 = yout.as_slice(np.float32)[:k].copy()
+    y_ref, ad = orc.qmatmul(otype, ws[1], x2[None], n, k)
+    assert norm_err(yout.as_slice(np.float32).reshape(cnt, n)[3][None], y_ref, ad) <= MV_TOL
