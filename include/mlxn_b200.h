@@ -302,6 +302,8 @@ int mlxn_moe_weighted_reduce_local(mlxn_encoder *enc, mlxn_registry *reg, mlxn_d
  *    mlxn_noalloc_scratch_limit() bytes (m*k up to about 8M elements); larger calls are refused with
  *    MLXN_INVALID_ARGUMENT and a message naming both sizes;
  *  - dense Q4_0 / Q8_0 / Q6_K only; K a multiple of 32;
+ *  - the call works on the CURRENT device: `cuda_stream` and the three pointers must belong to it (a stream of
+ *    another device is refused with MLXN_INVALID_ARGUMENT where the runtime can tell);
  *  - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
  *    current) — make that first call outside any stream capture;
  *  - all calls on a device share the one array: two calls whose kernels overlap on the GPU (different

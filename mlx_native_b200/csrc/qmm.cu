@@ -1285,7 +1285,8 @@ template <int T> static cudaError_t launch_tc_t(const QmmArgs &a, bool routed, u
     }
 }
 
-// tcgen05 mat-mat.  `scratch` must hold qmm_tc_scratch_bytes(a, nt, routed) bytes, 1024-byte aligned.
+// tcgen05 mat-mat.  `scratch` must hold qmm_tc_scratch_bytes(a, nt, routed) bytes and start on a 256-byte boundary (the packed
+// tiles in it are sources of bulk copies: 16-byte alignment is what the hardware needs; their offsets are multiples of 1024).
 cudaError_t launch_qmm_tc(int ggml_type, const QmmArgs &a, bool routed, uint32_t nt, uint8_t *scratch, cudaStream_t st,
                           int *launches) {
     switch (ggml_type) {
@@ -1359,6 +1360,20 @@ extern "C" int mlxn_quantized_matmul_ggml_mm_noalloc(void *cuda_stream, const vo
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
         return mlxn_detail_fail(MLXN_DEVICE_NOT_FOUND, "No usable current CUDA device for quantized_matmul_ggml_mm_noalloc");
+#if CUDART_VERSION >= 12080
+    {
+        // the kernels are launched on the CURRENT device: a stream of another device would be refused by the launch with an
+        // error that does not say why
+        int sdev = -1;
+        if (cudaStreamGetDevice(static_cast<cudaStream_t>(cuda_stream), &sdev) == cudaSuccess && sdev != dev) {
+            char msg[160];
+            snprintf(msg, sizeof(msg), "Invalid argument: quantized_matmul_ggml_mm_noalloc: the stream belongs to device %d but device %d is current",
+                     sdev, dev);
+            return mlxn_detail_fail(MLXN_INVALID_ARGUMENT, msg);
+        }
+        cudaGetLastError();
+    }
+#endif
     uint8_t *scratch = nullptr;
     int sms = 0;
     {
