@@ -588,6 +588,10 @@ __global__ void __launch_bounds__(kMwThreads, 2)
             }
         };
 
+        // Q6_K with one activation row: the bias term of the rows this lane builds the scale table for (row lane + 32 rr)
+        float corr[(R + 31) / 32];
+#pragma unroll
+        for (int rr = 0; rr < (R + 31) / 32; rr++) corr[rr] = 0.f;
         // [tile][set][hi and lo partial sums of weight row g, of weight row g + 8] for activation row t + 4 set
         float acc[TPW][NS][4];
 #pragma unroll
@@ -730,6 +734,17 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                                 float p[4];
 #pragma unroll
                                 for (int q = 0; q < 4; q++) p[q] = d * (float)lds_s8(rb + q6S + 2 * q);
+                                if constexpr (MP == 1) {
+                                    // one activation row: the groups' inverse pre-scales go into the table, and what the
+                                    // row owes for the codes' bias (scale x -32 sum(x), over all groups) into `corr`
+#pragma unroll
+                                    for (int q = 0; q < 4; q++) {
+                                        uint32_t u0, u1;
+                                        lds64(xcb + (i * 4 + q) * 8, u0, u1);
+                                        corr[rr] = fmaf(p[q], __uint_as_float(u0), corr[rr]);
+                                        p[q] *= __uint_as_float(u1);
+                                    }
+                                }
                                 sts128(ptab + (i * R + r) * 16, __float_as_uint(p[0]), __float_as_uint(p[1]), __float_as_uint(p[2]),
                                        __float_as_uint(p[3]));
                             }
@@ -826,10 +841,12 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                                 static_for<0, 4>([&](auto QC) {
                                     constexpr uint32_t q = decltype(QC)::value;
                                     lds64i<(((i * MP + 4 * ns) * 4 + q) * 64)>(xlane, bf[ns][q][0], bf[ns][q][1]);
-                                    uint32_t u0, u1;
-                                    lds64i<(((i * MP + 4 * ns) * 4 + q) * 8)>(clane, u0, u1);
-                                    cc[ns][q] = __uint_as_float(u0);
-                                    cs[ns][q] = __uint_as_float(u1);
+                                    if constexpr (MP > 1) {   // (one activation row: pre-scale and bias are in the scale table)
+                                        uint32_t u0, u1;
+                                        lds64i<(((i * MP + 4 * ns) * 4 + q) * 8)>(clane, u0, u1);
+                                        cc[ns][q] = __uint_as_float(u0);
+                                        cs[ns][q] = __uint_as_float(u1);
+                                    }
                                 });
                             });
                             static_for<0, TPW>([&](auto JC) {
@@ -864,6 +881,13 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                                     for (int ns = 0; ns < NS; ns++) {
                                         float d[4];
                                         mma16816(d, a0, a1, a2, a3, bf[ns][q][0], bf[ns][q][1], zz);
+                                        if constexpr (MP == 1) {
+                                            acc[j][ns][0] = fmaf(pa, d[0], acc[j][ns][0]);
+                                            acc[j][ns][1] = fmaf(pa, d[1], acc[j][ns][1]);
+                                            acc[j][ns][2] = fmaf(pb, d[2], acc[j][ns][2]);
+                                            acc[j][ns][3] = fmaf(pb, d[3], acc[j][ns][3]);
+                                            continue;
+                                        }
                                         const float ta = pa * cs[ns][q], tb = pb * cs[ns][q];
                                         acc[j][ns][0] = fmaf(ta, d[0], fmaf(pa, cc[ns][q], acc[j][ns][0]));
                                         acc[j][ns][1] = fmaf(ta, d[1], acc[j][ns][1]);
@@ -937,6 +961,19 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                 }
             }
             __syncwarp();
+            if constexpr (T == GT_Q6_K && MP == 1) {
+                // ... plus the bias term of the rows this lane kept the books for (this warp's share of K)
+#pragma unroll
+                for (int rr = 0; rr < (R + 31) / 32; rr++) {
+                    const uint32_t r = lane + 32 * rr;
+                    if (r < (uint32_t)R) {
+                        const uint32_t addr = red + (w * R + r) * 4;
+                        sts32(addr, __float_as_uint(__uint_as_float(lds32(addr)) + corr[rr] * 16777216.0f));
+                    }
+                    corr[rr] = 0.f;
+                }
+                __syncwarp();
+            }
             if (lane == 0) mbar_arrive(&fin[0]);
             if (!mbar_wait(&fin[0], fin_ph, &abort_flag, bt.status, ST_WAIT_EMPTY_TIMEOUT, 0u)) {
                 ok = false;
