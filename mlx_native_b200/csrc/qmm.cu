@@ -280,6 +280,7 @@ template <int T> struct TcTraits;
 template <> struct TcTraits<GT_Q4_0> { static constexpr int KR = 256; };  // raw-stage K extent
 template <> struct TcTraits<GT_Q8_0> { static constexpr int KR = 256; };
 template <> struct TcTraits<GT_Q6_K> { static constexpr int KR = 256; };
+template <> struct TcTraits<GT_Q4_K> { static constexpr int KR = 256; };
 
 __device__ __forceinline__ uint32_t lds32s(uint32_t addr) {
     uint32_t v;
@@ -352,6 +353,45 @@ template <int T> __device__ __forceinline__ void dequant32(uint32_t seg, uint32_
             out[j].y = h2_as_u32(__hmul2(__hsub2(b, off), d2));
             out[j].z = h2_as_u32(__hmul2(__hsub2(cc, off), d2));
             out[j].w = h2_as_u32(__hmul2(__hsub2(dd, off), d2));
+        }
+    } else if constexpr (T == GT_Q4_K) {
+        // sub-block j of the 144-byte super-block: 32 nibbles of the bytes 16 + 32 (j / 2) ..., low for even j;
+        // value = (d sc) q - (dmin m) (src/gguf/mod.rs:582-644), formed in f32 and rounded to f16 once
+        const uint32_t o = seg + 144u * (e >> 8);
+        const uint32_t j = (e & 255u) >> 5;
+        const uint32_t dd = lds16s(o) | (lds16s(o + 2) << 16);
+        uint32_t sw[3];
+        lds_words_n<3>(o + 4, sw);                      // scales[0..11]
+        uint32_t sc, mn;
+        if (j < 4) {
+            sc = (sw[0] >> (8 * j)) & 63u;
+            mn = (sw[1] >> (8 * j)) & 63u;
+        } else {
+            const uint32_t sh = 8 * (j - 4);
+            sc = ((sw[2] >> sh) & 15u) | ((((sw[0] >> sh) >> 6) & 3u) << 4);
+            mn = (((sw[2] >> sh) >> 4) & 15u) | ((((sw[1] >> sh) >> 6) & 3u) << 4);
+        }
+        const float ds = half_bits_to_float(dd & 0xFFFFu) * (float)sc;
+        const float dm = half_bits_to_float(dd >> 16) * (float)mn;
+        const float c = fmaf(-128.0f, ds, -dm);
+        uint32_t Q[8];
+        lds_words_n<8>(o + 16 + 32 * (j >> 1), Q);
+        const uint32_t ash = (j & 1u) ? 4u : 0u;
+#pragma unroll
+        for (int jj = 0; jj < 4; jj++) {
+            uint32_t res[4];
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const uint32_t u = (Q[2 * jj + i] >> ash) & 0x0F0F0F0Fu;
+                // 128 + u spliced into an f32 mantissa; fma(128 + u, ds, -128 ds - dm) = ds u - dm
+                const float f0 = fmaf(__uint_as_float(__byte_perm(u, 0x43000000u, 0x7044)), ds, c);
+                const float f1 = fmaf(__uint_as_float(__byte_perm(u, 0x43000000u, 0x7144)), ds, c);
+                const float f2 = fmaf(__uint_as_float(__byte_perm(u, 0x43000000u, 0x7244)), ds, c);
+                const float f3 = fmaf(__uint_as_float(__byte_perm(u, 0x43000000u, 0x7344)), ds, c);
+                res[2 * i] = h2_as_u32(__floats2half2_rn(f0, f1));
+                res[2 * i + 1] = h2_as_u32(__floats2half2_rn(f2, f3));
+            }
+            out[jj] = make_uint4(res[0], res[1], res[2], res[3]);
         }
     } else {
         const uint32_t o = seg + 210u * (e >> 8);
@@ -908,12 +948,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                     const uint32_t pre = (row_lo4 + ((r_abs * KR) / QK) * BB) & 15u;
                     const uint32_t seg = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride + pre;
                 uint32_t regs[32];
-                if (c.aligned && row_ok && !(MLXN_DBG(c) & 1u)) {
+                if (T != GT_Q4_K && c.aligned && row_ok && !(MLXN_DBG(c) & 1u)) {   // (Q4_K: the generic extraction below)
                     const uint32_t stage_row = smem_base + c.raw_off + rs * raw_stage_bytes + rr * c.seg_stride;
                     if constexpr (T == GT_Q6_K) {
                         dequant32_q6k_aligned_p(r_abs & 7u, stage_row, set, 2 * half, regs);
                         dequant32_q6k_aligned_p(r_abs & 7u, stage_row, set, 2 * half + 1, regs + 16);
-                    } else {
+                    } else if constexpr (T != GT_Q4_K) {
                         switch (2 * set + half) {  // uniform per warp
                         case 0: dequant64_aligned<T, 0>(stage_row, regs); break;
                         case 1: dequant64_aligned<T, 1>(stage_row, regs); break;
@@ -1293,6 +1333,7 @@ cudaError_t launch_qmm_tc(int ggml_type, const QmmArgs &a, bool routed, uint32_t
     case GT_Q4_0: return launch_tc_t<GT_Q4_0>(a, routed, nt, scratch, st, launches);
     case GT_Q8_0: return launch_tc_t<GT_Q8_0>(a, routed, nt, scratch, st, launches);
     case GT_Q6_K: return launch_tc_t<GT_Q6_K>(a, routed, nt, scratch, st, launches);
+    case GT_Q4_K: return launch_tc_t<GT_Q4_K>(a, routed, nt, scratch, st, launches);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -1965,7 +1965,7 @@ static int dispatch_id_mm_stages(mlxn_encoder *enc, mlxn_registry *reg, mlxn_dev
     a.total_rows = p->n_tokens * p->top_k;
     a.expert_stride = p->expert_stride;
     a.status = enc->status_dev;
-    if (opt_qmm_tc() && qmm_tc_supported(a) && (int)p->ggml_type != GT_Q4_K) {   // Q4_K: CUDA-core tiles for now
+    if (opt_qmm_tc() && qmm_tc_supported(a)) {
         const uint32_t nt = qmm_tc_pick_nt((int)p->ggml_type, p->n_tokens, p->n, dev->sm_count, true);
         uint8_t *scratch = nullptr;
         const size_t need = qmm_tc_scratch_bytes(a, nt, true);

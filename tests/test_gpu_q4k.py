@@ -65,19 +65,28 @@ def test_routed_matvec(ctx, T, E, top_k, n, k):
     assert norm_err(y, y_ref, ad) <= MV_TOL
 
 
-@pytest.mark.parametrize("T,E,top_k,n,k", [(16, 8, 8, 64, 512), (64, 4, 1, 96, 1024), (40, 16, 8, 128, 2048)])
+@pytest.mark.parametrize("T,E,top_k,n,k", [(16, 8, 8, 64, 512), (64, 4, 1, 96, 1024), (40, 16, 8, 128, 2048), (200, 32, 8, 768, 2048),
+                                           (70, 6, 3, 130, 768)])
 def test_routed_bucketed_matmat(ctx, T, E, top_k, n, k):
     wq = normal_weights(T + 3 * E, E * n, k, O)
     x = normal_acts(T + 1, T, k)
     rng = np.random.default_rng(T * 17 + E)
     ids = np.stack([rng.permutation(E)[:top_k] for _ in range(T)]).astype(np.uint32).reshape(-1)
     y, (htpe, hids) = ctx.matmul_id(G, wq, wq.size // E, x, ids, top_k, n, k, E, mode="force_mm")
-    assert mx.last_kernel_name() == "qmm_simt_id"
+    assert mx.last_kernel_name() == "qmm_tc_id"          # the tensor-core grouped mat-mat (weights dequantized into tensor memory)
+    mx.set_option("qmm", "simt")
+    try:
+        y_simt, _ = ctx.matmul_id(G, wq, wq.size // E, x, ids, top_k, n, k, E, mode="force_mm")
+        assert mx.last_kernel_name() == "qmm_simt_id"
+    finally:
+        mx.set_option("qmm", "tc")
     # bucketing: bit-exact against the oracle
     o_htpe, o_hids = orc.moe_map0(ids, T, top_k, E)
     assert np.array_equal(htpe.as_slice(np.uint32), o_htpe)
     y_ref, ad = orc.qmatmul_id(O, wq, wq.size // E, x, ids, top_k, n, k, E, f16_operands=True)
-    assert norm_err(y, y_ref, ad) <= MM_TOL
+    assert norm_err(y, y_ref, ad) <= MM_TOL and norm_err(y_simt, y_ref, ad) <= MM_TOL
+    y_f32, ad32 = orc.qmatmul_id(O, wq, wq.size // E, x, ids, top_k, n, k, E)
+    assert norm_err(y, y_f32, ad32) <= MM_TOL
 
 
 def test_dense_forced_matmat_is_refused(ctx):
