@@ -62,6 +62,9 @@ template <> struct MwTraits<GT_Q6_K> { static constexpr int UK = 512, UBYTES = 4
 // nibbles = the second; four MMAs, two scale groups).  The codes carry no bias; the sub-block's minimum dmin * m is
 // subtracted through the activation sum (OFFSET 1 is the weight of that sum).
 template <> struct MwTraits<GT_Q4_K> { static constexpr int UK = 512, UBYTES = 288, OFFSET = 1, NG = 2, NM = 4; };
+// Q5_K: as Q4_K with a fifth code bit per value from the super-block's 32 qh bytes (176-byte super-blocks); both
+// sub-blocks' codes are brought down to plain 5-bit values, so neither needs its activations rescaled.
+template <> struct MwTraits<GT_Q5_K> { static constexpr int UK = 512, UBYTES = 352, OFFSET = 1, NG = 2, NM = 4; };
 
 // Shared-memory bytes per row of a stage of KB units per warp: the stage's bytes plus the up to 12 bytes between
 // the 16-byte boundary the copy starts at and the stage's first byte (Q6_K), rounded up to an ODD multiple of 16,
@@ -69,10 +72,10 @@ template <> struct MwTraits<GT_Q4_K> { static constexpr int UK = 512, UBYTES = 2
 // A tensor copy is at most 256 elements (2048 bytes) wide: a longer stage row arrives as two copies, the first half of
 // the stage's K range for warps 0..3 and the second for warps 4..7, each into its own R x PITCH region of the slot.
 __host__ __device__ constexpr uint32_t mw_halves(int ggml_type, int kb) {
-    return (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : ggml_type == GT_Q4_K ? 288u : 420u) * (uint32_t)kb + 12u > 2048u ? 2u : 1u;
+    return (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : ggml_type == GT_Q4_K ? 288u : ggml_type == GT_Q5_K ? 352u : 420u) * (uint32_t)kb + 12u > 2048u ? 2u : 1u;
 }
 __host__ __device__ constexpr uint32_t mw_pitch(int ggml_type, int kb) {
-    const uint32_t raw = (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : ggml_type == GT_Q4_K ? 288u : 420u) * (uint32_t)kb / mw_halves(ggml_type, kb);
+    const uint32_t raw = (ggml_type == GT_Q4_0 ? 144u : ggml_type == GT_Q8_0 ? 272u : ggml_type == GT_Q4_K ? 288u : ggml_type == GT_Q5_K ? 352u : 420u) * (uint32_t)kb / mw_halves(ggml_type, kb);
     const uint32_t lead = ggml_type == GT_Q6_K ? (kb == 1 ? 12u : 8u) : 0u;
     const uint32_t c = (raw + lead + 15u) / 16u;
     return 16u * (c | 1u);
@@ -496,7 +499,7 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                 const uint32_t sb = sp + 2 * i;
                 xrel0[p] = 256 * sb + 128 * nh + 32 * hq + 16 * js + 4 * tt;
                 xrel1[p] = xrel0[p] + 2;
-            } else if constexpr (T == GT_Q4_K) {
+            } else if constexpr (T == GT_Q4_K || T == GT_Q5_K) {
                 // MMA hq of the unit: sub-block hq / 2 of the pair (low / high nibbles), its elements 16 (hq % 2) + 4 tt ...
                 const uint32_t sb = sp + 2 * i;
                 xrel0[p] = 256 * sb + 64 * (w & 3u) + 32 * (hq >> 1) + 16 * (hq & 1u) + 4 * tt;
@@ -681,7 +684,8 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                 }
 #endif
                 uint32_t lead = 0;
-                if constexpr (T == GT_Q4_K) {
+                if constexpr (T == GT_Q4_K || T == GT_Q5_K) {
+                    constexpr uint32_t SBB = T == GT_Q4_K ? 144u : 176u;   // super-block bytes
                     // (d * sc, d * sc', dmin * m, dmin * m') of the warp's sub-block pair, for every row of the stage (lanes
                     // split the rows); the 6-bit scales and minima are unpacked as in src/gguf/mod.rs:440-452
                     const uint32_t pu = w & 3u;
@@ -691,7 +695,7 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                         for (int rr = 0; rr < (R + 31) / 32; rr++) {
                             const uint32_t r = lane + 32 * rr;
                             if (r < (uint32_t)R) {
-                                const uint32_t rb = stage + r * PITCH + 144 * (sp + 2 * i);
+                                const uint32_t rb = stage + r * PITCH + SBB * (sp + 2 * i);
                                 const uint32_t dd = lds32(rb);
                                 const float d = f16lo_to_float(dd), dmin = f16hi_to_float(dd);
                                 const uint32_t s0 = lds32(rb + 4), s1 = lds32(rb + 8), s2 = lds32(rb + 12);   // scales[0..11]
@@ -757,9 +761,14 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                 // wrapped, the columns past 2 m are never looked at.  Its outputs belong to activation row t (+ 4 per set).
                 const uint32_t xlane = xsb + ((((g >> 1) & (uint32_t)(MP - 1)) * NM * 4 + t) * 16) + (g & 1u) * 8;
                 const uint32_t clane = xcb + (t & (uint32_t)(MP - 1)) * (NG * 8);
-                if constexpr (T == GT_Q4_K) {
-                    // row g of the stage, the warp's first super-block, its pair of sub-blocks: 32 bytes of nibbles 16 bytes in
-                    const uint32_t pQ = stage + g * PITCH + 144 * sp + 16 + 32 * (w & 3u) + 4 * t, pP = ptab + g * 16;
+                if constexpr (T == GT_Q4_K || T == GT_Q5_K) {
+                    constexpr bool Q5 = T == GT_Q5_K;
+                    constexpr uint32_t SBB = Q5 ? 176u : 144u, QS0 = Q5 ? 48u : 16u;   // super-block bytes; where its nibbles start
+                    // row g of the stage, the warp's first super-block, its pair of sub-blocks: 32 bytes of nibbles
+                    // (Q5_K: and the 32 bytes of fifth bits 16 bytes in, bits 2 pu and 2 pu + 1 for the pair's two sub-blocks)
+                    const uint32_t pu = w & 3u;
+                    const uint32_t pQ = stage + g * PITCH + SBB * sp + QS0 + 32 * pu + 4 * t, pP = ptab + g * 16;
+                    const uint32_t pH = stage + g * PITCH + SBB * sp + 16 + 4 * t;
                     const float zz[4] = {0.f, 0.f, 0.f, 0.f};
                     static_for<0, KB>([&](auto IC) {
                         constexpr uint32_t i = decltype(IC)::value;
@@ -781,16 +790,34 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                         });
                         static_for<0, TPW>([&](auto JC) {
                             constexpr uint32_t j = decltype(JC)::value;
-                            uint32_t w0[2], w1[2], pv[2][4];
+                            uint32_t w0[2], w1[2], hb0[2] = {0, 0}, hb1[2] = {0, 0}, pv[2][4];
                             static_for<0, 2>([&](auto HC) {
                                 constexpr uint32_t h = decltype(HC)::value;
-                                constexpr uint32_t off = (16 * j + 8 * h) * PITCH + 288 * i;   // rows g, g + 8 of tile j
+                                constexpr uint32_t off = (16 * j + 8 * h) * PITCH + 2 * SBB * i;   // rows g, g + 8 of tile j
                                 w0[h] = lds32i<off>(pQ);
                                 w1[h] = lds32i<off + 16>(pQ);
+                                if constexpr (Q5) {
+                                    hb0[h] = lds32i<off>(pH) >> (2 * pu);
+                                    hb1[h] = lds32i<off + 16>(pH) >> (2 * pu);
+                                }
                                 lds128i<((i * R) + 16 * j + 8 * h) * 16>(pP, pv[h][0], pv[h][1], pv[h][2], pv[h][3]);
                             });
-                            // low nibbles: first sub-block, elements c0..c3 of the word's bytes; high nibbles (x 16): the second
                             uint32_t a[4][4];
+                            if constexpr (Q5) {
+                                // five-bit codes, one per byte: nibble | fifth bit << 4; then bytes 0, 2 and 1, 3 into halves
+                                auto un5 = [&](uint32_t (&lo)[4], uint32_t (&hi)[4], int r0, uint32_t wg, uint32_t hg, uint32_t wg8, uint32_t hg8) {
+                                    const uint32_t cA = (wg & 0x0F0F0F0Fu) | ((hg & 0x01010101u) << 4), cB = ((wg >> 4) & 0x0F0F0F0Fu) | ((hg & 0x02020202u) << 3);
+                                    const uint32_t dA = (wg8 & 0x0F0F0F0Fu) | ((hg8 & 0x01010101u) << 4), dB = ((wg8 >> 4) & 0x0F0F0F0Fu) | ((hg8 & 0x02020202u) << 3);
+                                    (void)r0;
+                                    lo[0] = __byte_perm(cA, 0u, 0x4240); lo[2] = __byte_perm(cA, 0u, 0x4341);
+                                    lo[1] = __byte_perm(dA, 0u, 0x4240); lo[3] = __byte_perm(dA, 0u, 0x4341);
+                                    hi[0] = __byte_perm(cB, 0u, 0x4240); hi[2] = __byte_perm(cB, 0u, 0x4341);
+                                    hi[1] = __byte_perm(dB, 0u, 0x4240); hi[3] = __byte_perm(dB, 0u, 0x4341);
+                                };
+                                un5(a[0], a[2], 0, w0[0], hb0[0], w0[1], hb0[1]);
+                                un5(a[1], a[3], 0, w1[0], hb1[0], w1[1], hb1[1]);
+                            } else {
+                            // low nibbles: first sub-block, elements c0..c3 of the word's bytes; high nibbles (x 16): the second
                             a[0][0] = w0[0] & 0x000F000Fu; a[0][2] = (w0[0] >> 8) & 0x000F000Fu;
                             a[0][1] = w0[1] & 0x000F000Fu; a[0][3] = (w0[1] >> 8) & 0x000F000Fu;
                             a[1][0] = w1[0] & 0x000F000Fu; a[1][2] = (w1[0] >> 8) & 0x000F000Fu;
@@ -799,6 +826,7 @@ __global__ void __launch_bounds__(kMwThreads, 2)
                             a[2][1] = w0[1] & 0x00F000F0u; a[2][3] = (w0[1] >> 8) & 0x00F000F0u;
                             a[3][0] = w1[0] & 0x00F000F0u; a[3][2] = (w1[0] >> 8) & 0x00F000F0u;
                             a[3][1] = w1[1] & 0x00F000F0u; a[3][3] = (w1[1] >> 8) & 0x00F000F0u;
+                            }
                             const float pa0 = __uint_as_float(pv[0][0]), pa1 = __uint_as_float(pv[0][1]), ma0 = __uint_as_float(pv[0][2]),
                                         ma1 = __uint_as_float(pv[0][3]);
                             const float pb0 = __uint_as_float(pv[1][0]), pb1 = __uint_as_float(pv[1][1]), mb0 = __uint_as_float(pv[1][2]),
@@ -1045,7 +1073,7 @@ bool qmv_mma_supported(int ggml_type, const QmvArgs &a) {
 // The expert-routed form: one problem per (token, slot) row (m = 1, `ids` and `id_index` set).  The stacked weights are
 // addressed through a 3-D map [expert][row][bytes], so rows and experts must start on 16-byte boundaries.
 bool qmv_mma_supported_routed(int ggml_type, const QmvArgs &a) {
-    if (ggml_type != GT_Q4_0 && ggml_type != GT_Q8_0 && ggml_type != GT_Q6_K && ggml_type != GT_Q4_K) return false;
+    if (ggml_type != GT_Q4_0 && ggml_type != GT_Q8_0 && ggml_type != GT_Q6_K && ggml_type != GT_Q4_K && ggml_type != GT_Q5_K) return false;
     if (!a.ids || a.m != 1 || a.k == 0 || a.n == 0 || a.n_experts == 0 || a.k % mw_uk(ggml_type) != 0) return false;
     const uint64_t row_bytes = (uint64_t)(a.k / ggml_qk(ggml_type)) * ggml_block_bytes(ggml_type);
     if (row_bytes % 16 != 0 || row_bytes >= (1ull << 31) || a.expert_stride % 16 != 0 || a.expert_stride < row_bytes * a.n) return false;
@@ -1066,7 +1094,7 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
     if (const char *e = getenv("MLXN_MW_DEBUG")) c.debug = (uint32_t)atoi(e);
 #endif
     const size_t xst_bytes = mw_align((size_t)kMwWarps * XST, 128);
-    const size_t ptab_bytes = (T == GT_Q6_K || T == GT_Q4_K) ? (size_t)kMwWarps * R * 16 * KB : 0;
+    const size_t ptab_bytes = (T == GT_Q6_K || T == GT_Q4_K || T == GT_Q5_K) ? (size_t)kMwWarps * R * 16 * KB : 0;
     const size_t red_bytes = (size_t)kMwWarps * MP * R * 4;
     const size_t tail = xst_bytes + ptab_bytes + red_bytes;
     // two CTAs per SM: 228 KB, less 1 KB per CTA for the system and the kernel's few hundred bytes of static storage
@@ -1197,7 +1225,7 @@ static cudaError_t launch_mw(const QmvArgs *ops, int nops, int sm_count, int cta
 // TPW is, so many activation rows want a small KB.
 template <int T, int MP, bool PAIR>
 static cudaError_t launch_mw_m(const QmvArgs *ops, int nops, int sm_count, int ctas_per_sm, int tpw, cudaStream_t st) {
-    if constexpr (T == GT_Q6_K || T == GT_Q4_K) {
+    if constexpr (T == GT_Q6_K || T == GT_Q4_K || T == GT_Q5_K) {
         if (tpw >= 4 || MP == 8) return launch_mw<T, 4, 1, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
         if constexpr (MP <= 4) {
             if (tpw >= 2 || MP == 4) return launch_mw<T, 2, 2, MP, PAIR>(ops, nops, sm_count, ctas_per_sm, st);
@@ -1262,6 +1290,7 @@ cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs *ops, int nops, int sm_c
     case GT_Q8_0: return launch_mw_t<GT_Q8_0>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
     case GT_Q6_K: return launch_mw_t<GT_Q6_K>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
     case GT_Q4_K: return launch_mw_t<GT_Q4_K>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
+    case GT_Q5_K: return launch_mw_t<GT_Q5_K>(ops, nops, mmax, sm_count, ctas_per_sm, tpw, st);
     default: return cudaErrorInvalidValue;
     }
 }

@@ -16,14 +16,16 @@ def ctx():
     return Ctx()
 
 
-@pytest.mark.parametrize("T,top_k,E,n,k", [(1, 8, 16, 768, 2048), (5, 2, 4, 96, 512), (40, 8, 16, 64, 256), (3, 1, 2, 7, 768)])
+@pytest.mark.parametrize("T,top_k,E,n,k", [(1, 8, 16, 768, 2048), (5, 2, 4, 96, 512), (40, 8, 16, 64, 256), (3, 1, 2, 7, 768), (2, 8, 8, 2048, 1024),
+                                           (1, 4, 4, 33, 256)])
 def test_q5k_routed_matvec(ctx, T, top_k, E, n, k):
     rng = np.random.default_rng(T * 131 + n)
     w = random_q5k_blocks(rng, E * n * (k // 256))
     x = rng.standard_normal((T, k)).astype(np.float32)
     ids = np.stack([rng.permutation(E)[:top_k] for _ in range(T)]).astype(np.uint32).reshape(-1)
     y, _ = ctx.matmul_id(mx.GgmlType.Q5_K, w, w.size // E, x, ids, top_k, n, k, E)
-    assert mx.last_kernel_name().startswith("qmv")              # also for T > 32: Q5_K has no grouped mat-mat
+    # (also for T > 32: Q5_K has no grouped mat-mat) up to 16 rows: problems of the register-level tensor-core kernel
+    assert mx.last_kernel_name() == ("qmv_mma" if T * top_k <= 16 and k % 256 == 0 else "qmv_simple")
     y_ref, ad = orc.qmatmul_id(orc.Q5_K, w, w.size // E, x, ids, top_k, n, k, E, nthreads=8)
     assert norm_err(y, y_ref, ad) <= MV_TOL
 
