@@ -566,7 +566,7 @@ constexpr int kTcTmemCols = 512;
 //   ring in shared memory-->  f32 accumulator in tensor memory  --tcgen05.ld-->  y.
 // The dequantised weights never touch shared memory: its bandwidth is the scarce resource here (the tensor
 // core already reads the whole activation tile from it for every MMA).
-template <int T, int NT>
+template <int T, int NT, bool SH>
 __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, const TcCfg c, const uint8_t *xpack,
                                                                 const __grid_constant__ CUtensorMap wmap) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -580,6 +580,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile uint32_t abort_flag;
     __shared__ int32_t orow[2][NT];
+    // SH (row-sharded result): the peers' result buffers, copied out of the parameter block once.  The plain form is a
+    // separate instantiation: the peer stores' presence alone cost it 15 % (indexed reads of the parameter block).
+    __shared__ float *peer_y[SH ? 7 : 1];
 
     // Warps 0-3 are the four single-thread roles (one per scheduler partition, and the lowest warp numbers, so that
     // they are served before the dequantising warps whenever both have an instruction ready: these threads are the
@@ -593,6 +596,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     // ---- launched with programmatic stream serialisation), then the wait for them
     if (threadIdx.x == 0) {
         abort_flag = 0;
+        if constexpr (SH) {
+            peer_y[0] = a.y_peer[0]; peer_y[1] = a.y_peer[1]; peer_y[2] = a.y_peer[2]; peer_y[3] = a.y_peer[3];
+            peer_y[4] = a.y_peer[4]; peer_y[5] = a.y_peer[5]; peer_y[6] = a.y_peer[6];
+        }
         for (uint32_t s = 0; s < kTcAStages; s++) {
             mbar_init(&a_full[s], kTcDequantWarps / 2);  // the eight warps of one set
             mbar_init(&stage_done[s], 1);
@@ -1055,21 +1062,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                         const int32_t o = tab[r];
                         if (o < 0) continue;
                         const float4 val = *reinterpret_cast<const float4 *>(stg + r * kPitch + 4 * lane);
-                        const size_t off = (size_t)o * qmm_ld(a) + a.y_col0 + c4;
-                        float *dst = a.y + off;
+                        // (the staged form is never chosen for a call that also stores to peers)
+                        float *dst = SH ? a.y + ((size_t)o * qmm_ld(a) + a.y_col0 + c4) : a.y + ((size_t)o * a.n + c4);
                         if (c4 + 3 < a.n) {
                             *reinterpret_cast<float4 *>(dst) = val;
-                            for (uint32_t pr = 0; pr < a.n_peer; pr++) *reinterpret_cast<float4 *>(a.y_peer[pr] + off) = val;
                         } else {
                             if (c4 < a.n) dst[0] = val.x;
                             if (c4 + 1 < a.n) dst[1] = val.y;
                             if (c4 + 2 < a.n) dst[2] = val.z;
-                            for (uint32_t pr = 0; pr < a.n_peer; pr++) {
-                                float *pd = a.y_peer[pr] + off;
-                                if (c4 < a.n) pd[0] = val.x;
-                                if (c4 + 1 < a.n) pd[1] = val.y;
-                                if (c4 + 2 < a.n) pd[2] = val.z;
-                            }
                         }
                     }
                 }
@@ -1089,15 +1089,23 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                 }
                 tmem_ld_wait();
                 if (wrow < a.n && !(MLXN_DBG(c) & 256u)) {
+                    if constexpr (!SH) {   // a plain [m, n] result of this GPU: nothing between the 32 stores
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        const int32_t o = tab[col + j];
-                        if (o >= 0) {
-                            if (c.ksplit > 1) atomicAdd(&a.y[(size_t)o * a.n + wrow], __uint_as_float(v[j]));
-                            else {
+                        for (int j = 0; j < 32; j++) {
+                            const int32_t o = tab[col + j];
+                            if (o >= 0) {
+                                if (c.ksplit > 1) atomicAdd(&a.y[(size_t)o * a.n + wrow], __uint_as_float(v[j]));
+                                else a.y[(size_t)o * a.n + wrow] = __uint_as_float(v[j]);
+                            }
+                        }
+                    } else {           // row-sharded: leading dimension, column offset, the same tile to every peer
+#pragma unroll 4
+                        for (int j = 0; j < 32; j++) {
+                            const int32_t o = tab[col + j];
+                            if (o >= 0) {
                                 const size_t off = (size_t)o * qmm_ld(a) + a.y_col0 + wrow;
                                 a.y[off] = __uint_as_float(v[j]);
-                                for (uint32_t pr = 0; pr < a.n_peer; pr++) a.y_peer[pr][off] = __uint_as_float(v[j]);
+                                for (uint32_t pr = 0; pr < a.n_peer; pr++) peer_y[pr][off] = __uint_as_float(v[j]);
                             }
                         }
                     }
@@ -1190,7 +1198,7 @@ bool qmm_tc_supported(const QmmArgs &a) {
     return true;
 }
 
-template <int T, int NT>
+template <int T, int NT, bool SH>
 static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaStream_t st, int *launches) {
     constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES, KR = TcTraits<T>::KR;
     TcCfg c{};
@@ -1236,7 +1244,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     // narrow tiles stage their result in shared memory (two tiles of NT x 132 floats) and write whole output rows
     const uint32_t stage_bytes = 2u * NT * (kTcRowsW + 4) * 4u;
     // (the row-sharded form never splits K: its tiles go straight to every rank's buffer)
-    const bool sharded = a.y_ld != 0 || a.n_peer != 0;
+    constexpr bool sharded = SH;                         // a.y_ld != 0 || a.n_peer != 0
     const bool staged = NT == 64 && (sharded || qmm_tc_ksplit(NT, a.m, a.n, a.k, sm_count_of_device(), routed) == 1) &&
                         ((((uintptr_t)a.y) | ((uintptr_t)qmm_ld(a) * 4u) | ((uintptr_t)a.y_col0 * 4u)) & 15u) == 0 && a.n_peer == 0 &&
                         !exp_env("MLXN_TC_NO_STAGED_OUT");
@@ -1295,7 +1303,7 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
     if (smem > attr_smem[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(qmm_tc_kernel<T, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(qmm_tc_kernel<T, NT, SH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return e;
         attr_smem[dev] = smem;
     }
@@ -1312,15 +1320,23 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     if (items < ctas) ctas = (uint32_t)items;
     if (ctas == 0) return cudaSuccess;
     (*launches)++;
-    return launch_overlapped(qmm_tc_kernel<T, NT>, dim3(ctas), dim3(kTcThreads), smem, st, a, c, xpack, wmap);
+    return launch_overlapped(qmm_tc_kernel<T, NT, SH>, dim3(ctas), dim3(kTcThreads), smem, st, a, c, xpack, wmap);
 }
 
 template <int T> static cudaError_t launch_tc_t(const QmmArgs &a, bool routed, uint32_t nt, uint8_t *scratch, cudaStream_t st,
                                                 int *launches) {
+    if (a.y_ld != 0 || a.n_peer != 0) {   // row-sharded result: the instantiation with the peer stores
+        switch (nt) {
+        case 64: return launch_tc_tn<T, 64, true>(a, routed, scratch, st, launches);
+        case 128: return launch_tc_tn<T, 128, true>(a, routed, scratch, st, launches);
+        case 256: return launch_tc_tn<T, 256, true>(a, routed, scratch, st, launches);
+        default: return cudaErrorInvalidValue;
+        }
+    }
     switch (nt) {
-    case 64: return launch_tc_tn<T, 64>(a, routed, scratch, st, launches);
-    case 128: return launch_tc_tn<T, 128>(a, routed, scratch, st, launches);
-    case 256: return launch_tc_tn<T, 256>(a, routed, scratch, st, launches);
+    case 64: return launch_tc_tn<T, 64, false>(a, routed, scratch, st, launches);
+    case 128: return launch_tc_tn<T, 128, false>(a, routed, scratch, st, launches);
+    case 256: return launch_tc_tn<T, 256, false>(a, routed, scratch, st, launches);
     default: return cudaErrorInvalidValue;
     }
 }
