@@ -13,7 +13,8 @@ the one ahead, as the projections of a decoder layer do): that figure is the one
 is `value` and `roofline_independent`.
 
 Also reported on the same JSON line: `e2e` (same sweep through the public API with host buffers: activations
-written on the host, uploaded, results read back), `cpu_baseline` (the CPU oracle on a bounded sample, all host
+written on the host, uploaded, results read back; on one GPU four steps are in flight, commit / wait_until_completed
+on four encoders, so one step's copy back and host read overlap the next step's upload and kernels), `cpu_baseline` (the CPU oracle on a bounded sample, all host
 threads and one thread), `clocks`, `gpu_launches`, and `roofline_by_config`: one entry per benchmark configuration
 (Q4_0 4096x4096 mat-vec; the sweep; the twelve prefill mat-mat cells in TFLOP/s against the measured bf16 burst and the
 nominal 2250; the MoE FFN layer in tokens/s and expert-weight GB/s; the lm_head at m = 1 and m = 256).
@@ -397,7 +398,7 @@ def run_ours(args, rank, world, local_rank):
         chain_launches = mx.kernel_launch_count()
 
     # ---- e2e: the same sweep through the public API with host buffers, copies inside the timed region
-    e2e_steps = max(3, min(args.steps, 20))
+    e2e_steps = max(8, min(args.steps, 100))
     h2d = sum(L["m"] * L["k"] * 4 for L in launches)
     d2h = sum(L["m"] * (L["n"] if symm is not None else L["n_loc"]) * 4 for L in launches)
 
@@ -406,81 +407,115 @@ def run_ours(args, rank, world, local_rank):
     # activations on the host, replay, wait, read the results on the host".
     e2e_enc = dev.command_encoder()
     e2e_stream = torch.cuda.ExternalStream(e2e_enc.stream())
-    arena = None
+    e2e_in_flight = 1
     if world == 1:
-        # One arena for the step's activations and one for its results, the mat-vecs working on views of them
-        # (MlxBuffer::slice_view, src/buffer.rs:187-197): one host write and one upload, one copy back per step.
-        xa = dev.alloc_buffer(h2d, mx.DType.F32)
-        ya = dev.alloc_buffer(d2h, mx.DType.F32)
-        xo = yo = 0
-        for L in launches:
-            L["x_main"], L["y_main"] = L["x"], L["y"]
-            L["x"] = xa.slice_view(xo * 4, L["m"] * L["k"])
-            L["y"] = ya.slice_view(yo * 4, L["m"] * L["n_loc"])
-            L["y_off"] = yo
-            xo += L["m"] * L["k"]
-            yo += L["m"] * L["n_loc"]
-        arena = dict(x=xa, y=ya, x_host=np.concatenate([L["x_host"].reshape(-1) for L in launches]))
+        # Four steps in flight (upstream's commit / wait_until_completed pair, src/encoder.rs:2022-2050): four command
+        # encoders, each with one arena for the step's activations and one for its results, the mat-vecs working on
+        # views of them (MlxBuffer::slice_view, src/buffer.rs:187-197).  Step i is: wait for step i - 4 and read its
+        # results on the host; write the activations on the host (all 2.9 MB), replay the encoder's graph (one upload,
+        # 32 mat-vecs), commit (one copy back).  Every step uploads its own inputs and reads its own results; measured
+        # per step: 0.66 ms with one step in flight, 0.43 / 0.35 / 0.32 ms with two / three / four (the kernels alone
+        # take 0.33 ms).
+        e2e_in_flight = 4
+        x_host = np.concatenate([L["x_host"].reshape(-1) for L in launches])
+        sets = []
+        for s_i in range(e2e_in_flight):
+            xa = dev.alloc_buffer(h2d, mx.DType.F32)
+            ya = dev.alloc_buffer(d2h, mx.DType.F32)
+            ops, y_offs, xo, yo = [], [], 0, 0
+            for L in launches:
+                ops.append(dict(L, x=xa.slice_view(xo * 4, L["m"] * L["k"]), y=ya.slice_view(yo * 4, L["m"] * L["n_loc"])))
+                y_offs.append(yo)
+                xo += L["m"] * L["k"]
+                yo += L["m"] * L["n_loc"]
+            e = dev.command_encoder()
+            ya.as_slice(np.float32)                                           # create the pinned shadow up front
+            xa.as_mut_slice(np.float32)[:] = x_host
+            for op in ops:                                                    # first touch outside the capture
+                encode_op(e, op)
+            e.commit_and_wait()
+            xa.as_mut_slice(np.float32)[:] = x_host
+            e.begin_capture()
+            for op in ops:
+                encode_op(e, op)
+            sets.append(dict(x=xa, y=ya, enc=e, graph=e.end_capture(), y_offs=y_offs))
 
-    def write_inputs():
-        if arena is not None:
-            arena["x"].as_mut_slice(np.float32)[:] = arena["x_host"]          # host write -> upload at bind / replay
-            return
-        for L in launches:
-            L["x"].as_mut_slice(np.float32)[:] = L["x_host"].reshape(-1)      # host write -> upload at bind / replay
+        def submit(st):
+            st["x"].as_mut_slice(np.float32)[:] = x_host                      # host write -> upload at replay
+            st["graph"].launch(st["enc"])
+            st["enc"].commit()                                                # results with a host view are copied back
 
-    def e2e_encode():
-        for L in launches:
-            encode_op(e2e_enc, L)
-            if world > 1 and symm is None:
-                e2e_enc.memory_barrier()
-                with torch.cuda.stream(e2e_stream):
-                    dist.all_gather_into_tensor(L["y_all"], L["y_loc"])
+        def collect(st):
+            st["enc"].wait_until_completed()
+            res = st["y"].as_slice(np.float32)                                # host view, fetched back by the commit
+            return float(sum(res[o] for o in st["y_offs"]))
 
-    e2e_graph = None
-    if world == 1 or symm is not None:
-        if arena is not None:
-            arena["y"].as_slice(np.float32)
-        else:
+        def e2e_run(n):
+            acc = 0.0
+            D = e2e_in_flight
+            for i in range(n):
+                if i >= D:
+                    acc += collect(sets[(i - D) % D])                         # the set's previous step, before its reuse
+                submit(sets[i % D])
+            for i in range(max(0, n - D), n):
+                acc += collect(sets[i % D])
+            return acc
+
+        e2e_run(2 * e2e_in_flight)
+        barrier()
+        t0 = time.perf_counter()
+        e2e_run(e2e_steps)
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
+    else:
+        def write_inputs():
+            for L in launches:
+                L["x"].as_mut_slice(np.float32)[:] = L["x_host"].reshape(-1)      # host write -> upload at bind / replay
+
+        def e2e_encode():
+            for L in launches:
+                encode_op(e2e_enc, L)
+                if symm is None:
+                    e2e_enc.memory_barrier()
+                    with torch.cuda.stream(e2e_stream):
+                        dist.all_gather_into_tensor(L["y_all"], L["y_loc"])
+
+        e2e_graph = None
+        if symm is not None:
             for L in launches:                                                # create the pinned shadows up front
                 L["y"].as_slice(np.float32)
-        write_inputs()
-        e2e_encode()
-        e2e_enc.commit_and_wait()
-        write_inputs()
-        e2e_enc.begin_capture()
-        e2e_encode()
-        e2e_graph = e2e_enc.end_capture()
-
-    def e2e_step():
-        write_inputs()
-        if e2e_graph is not None:
-            e2e_graph.launch(e2e_enc)
-        else:
+            write_inputs()
             e2e_encode()
-        if symm is not None:
-            rank_barrier_on_stream(e2e_stream, e2e_enc)
-        e2e_enc.commit_and_wait()
-        acc = 0.0
-        if arena is not None:
-            res = arena["y"].as_slice(np.float32)                          # host view, fetched back by the commit
-            return float(sum(res[L["y_off"]] for L in launches))
-        for L in launches:
-            if world > 1 and symm is None:
-                acc += float(L["y_all"][0, 0].item())                      # device -> host read of the result
-            else:
-                acc += float(L["y"].as_slice(np.float32)[0])               # host view, fetched back by the commit
-        return acc
+            e2e_enc.commit_and_wait()
+            write_inputs()
+            e2e_enc.begin_capture()
+            e2e_encode()
+            e2e_graph = e2e_enc.end_capture()
 
-    for _ in range(2):
-        e2e_step()
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    barrier()
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
-    if dist is not None:
+        def e2e_step():
+            write_inputs()
+            if e2e_graph is not None:
+                e2e_graph.launch(e2e_enc)
+            else:
+                e2e_encode()
+            if symm is not None:
+                rank_barrier_on_stream(e2e_stream, e2e_enc)
+            e2e_enc.commit_and_wait()
+            acc = 0.0
+            for L in launches:
+                if symm is None:
+                    acc += float(L["y_all"][0, 0].item())                      # device -> host read of the result
+                else:
+                    acc += float(L["y"].as_slice(np.float32)[0])               # host view, fetched back by the commit
+            return acc
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
         tt = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e2e_s = float(tt.item())
@@ -522,7 +557,7 @@ def run_ours(args, rank, world, local_rank):
                                 if ms_chain is not None else "independent launches (no chain variant on more than one GPU)"),
         "roofline_independent": roofline_of(ms_step, "independent launches: conflict-free neighbours overlap or leave as one kernel"),
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_s * 1e3},
+                "ms_per_step": e2e_s * 1e3, "steps_in_flight": e2e_in_flight},
         "gpu_launches": int(n_launch),
         "gpu_launches_chain": int(chain_launches) if chain_launches is not None else None,
         "clocks": clocks,
