@@ -185,7 +185,9 @@ def run_ours(args, rank, world, local_rank):
         import torch.distributed as dist_
 
         dist = dist_
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        # (a lost rank ends the others' next collective with an error after three minutes instead of the default ten)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=datetime.timedelta(seconds=180))
     dev = mx.MlxDevice.new(local_rank)
     reg = mx.KernelRegistry.new()
     gt = {"Q8_0": mx.GgmlType.Q8_0, "Q6_K": mx.GgmlType.Q6_K, "Q4_0": mx.GgmlType.Q4_0}
@@ -577,6 +579,8 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+    if sharded is not None and sharded.get("failed_checks"):
+        raise SystemExit("multi-GPU correctness checks failed: " + "; ".join(sharded["failed_checks"]))
 
 
 def sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream, pbar=None):
@@ -588,6 +592,7 @@ def sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream, pbar=
     from mlx_native_b200.ggml_pack import random_blocks
 
     out = {}
+    failures = []                            # correctness checks that failed (reported at the end: every rank runs on)
     rng = np.random.default_rng(11)          # same seed on every rank: replicated activations and logits
 
     def timed(step, reps=10, warm=3):
@@ -753,18 +758,19 @@ def sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream, pbar=
                 want = o1.download(np.float32).reshape(T, hidden)
                 got = torch.cat(gathered, dim=0).cpu().numpy()
                 identical = bool(np.array_equal(got.view(np.uint32), want.view(np.uint32)))
+                rel = float(np.max(np.abs(got - want)) / max(float(np.max(np.abs(want))), 1e-30))
                 if not identical:
-                    raise RuntimeError(f"all-to-all MoE layer (T={T}) is not bit-identical to the one-GPU layer: "
-                                       f"max diff {float(np.max(np.abs(got - want)))}")
+                    # (recorded, not raised here: the other ranks are on their way into the next section's collectives)
+                    failures.append(f"all-to-all MoE layer (T={T}) is not bit-identical to the one-GPU layer: "
+                                    f"max |diff| / max |value| = {rel:.3e}")
                 del full
             moe2[f"m{T}"] = {"tokens_per_s": T / sec, "ms_per_layer": sec * 1e3, "experts_per_rank": cnt,
                              "exchange": "NCCL all-to-all dispatch of (row, local expert id) per (token, slot) pair + all-to-all "
-                                         "combine of the unreduced result rows", "bit_identical_to_one_gpu": identical}
+                                         "combine of the unreduced result rows", "bit_identical_to_one_gpu": identical,
+                             "max_rel_diff_to_one_gpu": rel if rank == 0 else None}
         out["moe_ffn_layer_all_to_all"] = moe2
     except Exception as ex:
         out["moe_ffn_layer_all_to_all"] = {"error": repr(ex)}
-        if "bit-identical" in repr(ex):
-            raise
 
     # ---- N-sharded lm_head, Q6_K 151936 x 5120: m = 1 (mat-vec) and m = 256 (mat-mat); every rank's kernels store their
     # ---- columns into all ranks' logits (peer stores from the kernels' epilogues) + one cross-rank barrier
@@ -824,7 +830,9 @@ def sharded_extra(mx, dev, reg, torch, dist, rank, world, enc, ext_stream, pbar=
     except Exception as ex:
         out["lm_head_q6k_n_sharded"] = {"error": repr(ex)}
         if "differs from the oracle" in repr(ex):
-            raise
+            failures.append(repr(ex))                  # (the last section: no collective follows on the other ranks)
+    if failures:
+        out["failed_checks"] = failures
     return out
 
 

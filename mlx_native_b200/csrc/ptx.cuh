@@ -58,6 +58,10 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 // for the kernel that exists to exercise this path).
 // `sleep_ns` > 0 spaces the polls out (for warps that are not on the critical path: each poll costs issue
 // slots that working warps could use).
+#ifndef MLXN_SUSPEND_HINT_NS
+#define MLXN_SUSPEND_HINT_NS 20000u
+#endif
+constexpr uint32_t kSuspendHintNs = MLXN_SUSPEND_HINT_NS;   // how long a pending try_wait may keep the thread suspended
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile uint32_t *abort, uint32_t *status,
                                           uint32_t code, uint32_t sleep_ns = 0, uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -69,7 +73,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
             if (mbar_try_wait(bar, parity)) return true;
         } else {
             if (sleep_ns) __nanosleep(sleep_ns);
-            if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
+            if (mbar_try_wait_suspend(bar, parity, kSuspendHintNs)) return true;
         }
         if ((polls & 63u) == 0) {
             if (*abort) return false;

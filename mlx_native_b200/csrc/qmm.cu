@@ -553,9 +553,14 @@ struct TcCfg {
     uint32_t raw_tma;     // raw weight stages arrive as one tensor copy each (needs `aligned`); otherwise 16-byte cp.async
 };
 
-constexpr int kTcAStages = 4;      // ring of dequantised weight stages held in tensor memory
+// ring of dequantised weight stages held in tensor memory: the columns the accumulators leave free.  Tiles of 64
+// activation rows (two 64-column accumulators) keep six stages in columns [128, 512), wider ones four in [256, 512):
+// the ring's depth over the latency of the loop dequantise -> MMA -> commit -> reuse is what bounds a narrow tile.
+template <int NT> struct TcRing {
+    static constexpr int kStages = NT <= 64 ? 6 : 4;
+    static constexpr int kColBase = NT <= 64 ? 128 : 256;
+};
 constexpr int kTcACols = 64;       // one stage: 128 K values as f16 pairs = 64 32-bit columns
-constexpr int kTcAColBase = 256;   // accumulator in columns [0, NT), weight ring in [256, 512)
 constexpr int kTcTmemCols = 512;
 
 // grid = min(work items, SMs) persistent CTAs; kTcThreads threads; 1 CTA per SM.
@@ -573,7 +578,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
     // tensor-core operand tiles need 1024-byte alignment (128-byte swizzle atoms): align by hand
     uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     constexpr int QK = BlockTraits<T>::QK, BB = BlockTraits<T>::BYTES, KR = TcTraits<T>::KR;
-    constexpr int kMaxB = 6, kMaxRaw = 6;
+    constexpr int kMaxB = 8, kMaxRaw = 6;
+    constexpr int kTcAStages = TcRing<NT>::kStages, kTcAColBase = TcRing<NT>::kColBase;
+    static_assert(kMaxB / 2 <= kTcAStages, "an activation chunk's place is freed by a stage_done phase the producer can still see");
     constexpr int kNumMma = NT <= 128 ? 2 : 1;   // issuing threads, each with its own accumulator
     __shared__ __align__(8) uint64_t a_full[kTcAStages], stage_done[kTcAStages], b_full[kMaxB];
     __shared__ __align__(8) uint64_t raw_full[kMaxRaw], raw_empty[kMaxRaw], acc_full, acc_empty, orow_ready[2], stage_ready[2];
@@ -717,7 +724,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                 for (uint32_t kc = 0; kc < 2 * it.nst; kc++, G++) {
                     if (G >= c.b_stages) {
                         const uint32_t j = (G - c.b_stages) >> 1;
-                        if (!mbar_wait(&stage_done[j & (kTcAStages - 1)], (j / kTcAStages) & 1u, &abort_flag, a.status,
+                        if (!mbar_wait(&stage_done[j % kTcAStages], (j / kTcAStages) & 1u, &abort_flag, a.status,
                                        ST_WAIT_EMPTY_TIMEOUT, wmode_cr)) {
                             ok = false;
                             break;
@@ -941,7 +948,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                 const uint32_t st = 2 * r + set;       // this set's K stage inside raw stage r
                 if (st < it.nst) {
                     const uint32_t J = J0 + st;        // its number in the CTA's whole run
-                    const uint32_t sa = J & (kTcAStages - 1);
+                    const uint32_t sa = J % kTcAStages;
                     // the MMAs that read this ring place's previous contents (K stage J - 4) have completed
                     if (J >= kTcAStages &&
                         !mbar_wait(&stage_done[sa], ((J / kTcAStages) & 1u) ^ 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT,
@@ -1251,12 +1258,15 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
     if (staged) limit -= stage_bytes;
     // activation ring first (at least two raw slots kept back), the rest goes to the raw weight ring
     uint32_t b_stages = (limit - 2 * raw_slot) / b_bytes;
-    if (b_stages > 6) b_stages = 6;
+    // (a 64-row tile's chunks are 8 KB: eight of them where four raw slots still fit beside them, the loop being
+    // bound by how far the copies run ahead of the MMAs)
+    const uint32_t b_cap = (NT == 64 && limit >= 8 * b_bytes + 4 * raw_slot) ? 8u : 6u;
+    if (b_stages > b_cap) b_stages = b_cap;
     if (const char *e = exp_env("MLXN_TC_STAGES")) {  // experiment switch
         const uint32_t v = (uint32_t)atoi(e);
-        if (v >= 2 && v <= b_stages) b_stages = v;
+        if (v >= 4 && v <= b_stages) b_stages = v;
     }
-    if (b_stages < 2) return cudaErrorInvalidConfiguration;
+    if (b_stages < 4) return cudaErrorInvalidConfiguration;   // (shallower rings are untested)
     uint32_t raw_slots = (limit - b_stages * b_bytes) / raw_slot;
     if (raw_slots > 6) raw_slots = 6;
     if (const char *e = exp_env("MLXN_TC_RAW")) {  // experiment switch

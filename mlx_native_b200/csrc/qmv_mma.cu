@@ -1272,6 +1272,15 @@ cudaError_t launch_qmv_mma(int ggml_type, const QmvArgs *ops, int nops, int sm_c
     uint32_t mmax = 1;
     for (int i = 0; i < nops; i++)
         if (ops[i].m > mmax) mmax = ops[i].m;
+    bool routed = false;
+    for (int i = 0; i < nops; i++) routed = routed || ops[i].ids != nullptr;
+    if (tpw <= 0 && routed) {
+        // Expert-routed rows: one geometry whatever else is in the launch (64-row groups: the smallest K stage of every
+        // row class), because the geometry fixes how K is shared among the warps and with it the rounding of a row's sum.
+        // A (token, slot) pair's result then does not depend on how many pairs travel with it, which is what makes an
+        // expert-parallel layer bit-identical to the single-GPU one.
+        tpw = 4;
+    }
     if (tpw <= 0) {
         // measured: the largest row group (the activation split is paid once per group) that still gives at least every
         // other CTA slot an item; 16-row groups when even 32-row groups do not

@@ -109,3 +109,26 @@ def test_gate_and_up_share_a_launch_and_bad_ids_give_zeros(ctx):
         y_ref, ad = orc.qmatmul_id(otype, w, stride, x, np.where(good, ids, 0).astype(np.uint32), top_k, n, k, n_experts, nthreads=8)
         assert norm_err(y[good], y_ref[good], ad[good]) <= MV_TOL
         assert np.all(y[~good] == 0.0)
+
+
+# ---- a (token, slot) pair's row does not depend on how many pairs share its launch: the all-to-all MoE layer sends
+# ---- each rank a different subset of the pairs and is still bit-identical to the one-GPU layer
+@pytest.mark.parametrize("tname,n,k", [("Q4_0", 768, 2048), ("Q8_0", 768, 2048), ("Q6_K", 512, 2048), ("Q4_K", 512, 2048)])
+def test_routed_rows_do_not_depend_on_the_launch_composition(ctx, tname, n, k):
+    gtype, otype = TYPES[tname] if tname in TYPES else (mx.GgmlType.Q4_K, orc.Q4_K)
+    n_experts = 8
+    w, stride = stacked(otype, n_experts, n, k, seed=800)
+    rows = normal_acts(21, 8, k)                                       # eight pairs, one activation row each (top_k = 1)
+    ids = np.array([5, 1, 7, 2, 2, 0, 6, 3], np.uint32)
+    whole, _ = ctx.matmul_id(gtype, w, stride, rows, ids, 1, n, k, n_experts)
+    assert mx.last_kernel_name() == "qmv_mma"
+    for parts in ((3, 5), (1, 7), (2, 2, 4)):
+        lo = 0
+        for cnt in parts:
+            part, _ = ctx.matmul_id(gtype, w, stride, rows[lo:lo + cnt], ids[lo:lo + cnt], 1, n, k, n_experts)
+            assert np.array_equal(part.view(np.uint32), whole[lo:lo + cnt].view(np.uint32)), (tname, parts, lo)
+            lo += cnt
+    # ... nor on whether the eight pairs belong to one token (top_k = 8, the row shared) or to eight
+    one_tok, _ = ctx.matmul_id(gtype, w, stride, rows[:1], ids, 8, n, k, n_experts)
+    eight, _ = ctx.matmul_id(gtype, w, stride, np.repeat(rows[:1], 8, axis=0), ids, 1, n, k, n_experts)
+    assert np.array_equal(one_tok.view(np.uint32), eight.view(np.uint32))
