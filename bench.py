@@ -1069,6 +1069,7 @@ def run_case(argv):
       --case mm  [Q4_0|Q6_K|Q8_0] [m]   prefill mat-mat, n=4096 k=4096, m=512 by default
       --case moe [m]                    expert-routed gate projection, 128 experts, top-8
       --case moe_layer [m] [reps]       whole MoE FFN layer (route, gate, up, SwiGLU, down, reduce), 128 experts, top-8
+      --case moe_trace [gate|down]      cycle trace of one CTA of the grouped mat-mat (experiment build only)
       --case cmp [types] [ms]           the mat-vec kernels side by side, microseconds per call, independent and chained
                                         (CUDA-graph replay over rotating weight copies > L2)
       --case gap                        microseconds per launch of a chain of dependent trivial kernels
@@ -1192,6 +1193,43 @@ def run_case(argv):
             mx.moe_weighted_reduce(enc, reg, dev, rw, yd, outb, T, top_k, hidden)
             enc.commit_and_wait()
         print("ok", mx.last_kernel_name())
+        return
+    if mode == "moe_trace":
+        # cycle trace of CTA 0 of the grouped mat-mat (gate: Q4_0 768 x 2048 per expert; down: Q6_K 2048 x 768), T = 512.
+        # Needs a library built with MLXN_NVCC_EXTRA="-DMLXN_EXPERIMENTS -DMLXN_TC_TRACE" and MLXN_TC_DEBUG=768 in the
+        # environment (the kernel then logs (event, clock) pairs into the result buffer instead of writing results).
+        # Prints "cycles role event index" lines: roles wprod (weight copies: 1 = stage requested), mma0 / mma1 (1 = item
+        # start, 2 = weights of a stage ready, 4 = activations ready, 5 = MMAs issued, 3 = committed), dq0 / dq1 (the two
+        # sets of dequantising warps: 1 = item start, 2 = raw stage arrived, 3 = ring place free, 8 = dequantised,
+        # 9 = stored to tensor memory, 4 = handed to the MMA warp, 10 = raw stage released, 5 / 6 / 7 = read-back).
+        which = argv[1] if len(argv) > 1 else "gate"
+        T = 512
+        t, n, k, m, tk = ("Q4_0", ffn, hidden, T, top_k) if which == "gate" else ("Q6_K", hidden, ffn, T * top_k, 1)
+        w = random_blocks(rng, t, E * n, k)
+        wb = upload(w)
+        xb = upload(rng.standard_normal((m, k)).astype(np.float32), mx.DType.F32)
+        ib = upload(np.stack([rng.permutation(E)[:top_k] for _ in range(T)]).astype(np.uint32).reshape(-1), mx.DType.U32)
+        yb = dev.alloc_buffer(m * tk * n * 4, mx.DType.F32)
+        p = mx.GgmlQuantizedMatmulIdParams(m, tk, n, k, E, w.size // E, gt[t])
+        for _ in range(2):
+            mx.quantized_matmul_id_ggml(enc, reg, dev, xb, wb, ib, yb, p)
+            enc.commit_and_wait()
+        yb.upload(np.zeros(m * tk * n, np.float32))
+        mx.quantized_matmul_id_ggml(enc, reg, dev, xb, wb, ib, yb, p)
+        enc.commit_and_wait()
+        tr = yb.download(np.float32).view(np.uint32)[:6 * 1024].reshape(6, 512, 2)
+        ev = []
+        for role, nm in {0: "wprod", 1: "mma0", 4: "mma1", 2: "dq0", 3: "dq1"}.items():
+            for code_x, clk in tr[role]:
+                if code_x == 0 and clk == 0:
+                    break
+                ev.append((int(clk), nm, int(code_x) >> 16, int(code_x) & 0xFFFF))
+        if not ev:
+            print("no trace events: the library was not built with -DMLXN_TC_TRACE, or MLXN_TC_DEBUG=768 is not set")
+            return
+        ev.sort(key=lambda e_: e_[0])
+        for clk, nm, code, idx in ev:
+            print(f"{(clk - ev[0][0]) & 0xFFFFFFFF:9d} {nm} {code} {idx}")
         return
     if mode == "moe":
         m = int(argv[1]) if len(argv) > 1 else 512

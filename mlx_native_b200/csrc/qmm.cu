@@ -759,6 +759,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                         ok = false;
                         break;
                     }
+                    TRACE(0, 1, requested);
                     const uint32_t kb = ((it.r_lo + r) * (KR / QK) * BB) & ~15u;   // byte offset of the stage in the row
                     mbar_expect_tx(&raw_full[slot], raw_stage_bytes);
                     asm volatile(
@@ -1006,6 +1007,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&raw_empty[rs]);  // this warp is done reading the raw stage
+                if (q4 == 0 && half == 0) TRACE(2 + set, 10, r);
                 consumed++;
                 if (++rs == R) { rs = 0; rph ^= 1u; }
             }
