@@ -410,26 +410,43 @@ def run_ours(args, rank, world, local_rank):
     e2e_enc = dev.command_encoder()
     e2e_stream = torch.cuda.ExternalStream(e2e_enc.stream())
     e2e_in_flight = 1
-    if world == 1:
+    if world == 1 or symm is not None:
         # Four steps in flight (upstream's commit / wait_until_completed pair, src/encoder.rs:2022-2050): four command
         # encoders, each with one arena for the step's activations and one for its results, the mat-vecs working on
         # views of them (MlxBuffer::slice_view, src/buffer.rs:187-197).  Step i is: wait for step i - 4 and read its
         # results on the host; write the activations on the host (all 2.9 MB), replay the encoder's graph (one upload,
         # 32 mat-vecs), commit (one copy back).  Every step uploads its own inputs and reads its own results; measured
-        # per step: 0.66 ms with one step in flight, 0.43 / 0.35 / 0.32 ms with two / three / four (the kernels alone
-        # take 0.33 ms).
+        # per step on one GPU: 0.66 ms with one step in flight, 0.43 / 0.35 / 0.32 ms with two / three / four (the kernels
+        # alone take 0.33 ms).
+        # On N GPUs every set's result arena is a symmetric-memory buffer of its own (the other ranks' kernels store their
+        # columns into it) with its own cross-rank barrier flags, and a step is bracketed by two barriers: one in front
+        # of the kernels (every rank has finished copying the set's previous results back, so they may be overwritten)
+        # and one behind them (every rank's columns have arrived, so the copy back may start).
         e2e_in_flight = 4
         x_host = np.concatenate([L["x_host"].reshape(-1) for L in launches])
+        n_res = sum(L["m"] * (L["n"] if symm is not None else L["n_loc"]) for L in launches)      # floats per result arena
         sets = []
         for s_i in range(e2e_in_flight):
             xa = dev.alloc_buffer(h2d, mx.DType.F32)
-            ya = dev.alloc_buffer(d2h, mx.DType.F32)
+            if symm is not None:
+                import torch.distributed._symmetric_memory as symm_mem
+                sbuf = symm_mem.empty(n_res, dtype=torch.float32, device=f"cuda:{local_rank}")
+                shdl = symm_mem.rendezvous(sbuf, dist.group.WORLD)
+                sbuf.zero_()
+                sptrs = [int(p_) for p_ in shdl.buffer_ptrs]
+                ya = dev.wrap_device_memory(sptrs[rank], n_res * 4, mx.DType.F32)
+                set_bar = sharding.PeerBarrier(local_rank)
+            else:
+                sbuf = shdl = sptrs = set_bar = None
+                ya = dev.alloc_buffer(d2h, mx.DType.F32)
             ops, y_offs, xo, yo = [], [], 0, 0
             for L in launches:
-                ops.append(dict(L, x=xa.slice_view(xo * 4, L["m"] * L["k"]), y=ya.slice_view(yo * 4, L["m"] * L["n_loc"])))
+                width = L["n"] if symm is not None else L["n_loc"]
+                peers_s = [sptrs[r] + yo * 4 for r in range(world) if r != rank] if symm is not None else None
+                ops.append(dict(L, x=xa.slice_view(xo * 4, L["m"] * L["k"]), y=ya.slice_view(yo * 4, L["m"] * width), peers=peers_s))
                 y_offs.append(yo)
                 xo += L["m"] * L["k"]
-                yo += L["m"] * L["n_loc"]
+                yo += L["m"] * width
             e = dev.command_encoder()
             ya.as_slice(np.float32)                                           # create the pinned shadow up front
             xa.as_mut_slice(np.float32)[:] = x_host
@@ -440,11 +457,16 @@ def run_ours(args, rank, world, local_rank):
             e.begin_capture()
             for op in ops:
                 encode_op(e, op)
-            sets.append(dict(x=xa, y=ya, enc=e, graph=e.end_capture(), y_offs=y_offs))
+            sets.append(dict(x=xa, y=ya, enc=e, graph=e.end_capture(), y_offs=y_offs, bar=set_bar, keep=(sbuf, shdl)))
+        barrier()
 
         def submit(st):
             st["x"].as_mut_slice(np.float32)[:] = x_host                      # host write -> upload at replay
+            if st["bar"] is not None:
+                st["bar"].wait(st["enc"])                                     # the set's previous results are read everywhere
             st["graph"].launch(st["enc"])
+            if st["bar"] is not None:
+                st["bar"].wait(st["enc"])                                     # every rank's columns have arrived
             st["enc"].commit()                                                # results with a host view are copied back
 
         def collect(st):
@@ -467,48 +489,34 @@ def run_ours(args, rank, world, local_rank):
         barrier()
         t0 = time.perf_counter()
         e2e_run(e2e_steps)
+        barrier()
         e2e_s = (time.perf_counter() - t0) / e2e_steps
+        if dist is not None:
+            tt = torch.tensor([e2e_s], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            e2e_s = float(tt.item())
+        # what came back to the host is what the device-timed sweep left in its own result buffers (same inputs)
+        for st in sets:
+            res = st["y"].as_slice(np.float32)
+            for L, o in zip(launches, st["y_offs"]):
+                want = (L["y_full"].cpu().numpy() if symm is not None else L["y"].download(np.float32)).reshape(-1)
+                got = res[o:o + want.size]
+                scale = max(float(np.max(np.abs(want))), 1e-30)
+                if not np.all(np.isfinite(got)) or float(np.max(np.abs(got - want))) > 1e-5 * scale:
+                    raise RuntimeError(f"rank {rank}: e2e result of {L['t']} {L['n']}x{L['k']} m={L['m']} differs from the "
+                                       f"device-timed sweep's: {float(np.max(np.abs(got - want))) / scale:.3e} of its scale")
     else:
-        def write_inputs():
+        # (no symmetric memory: direct launches and one NCCL all-gather per mat-vec, one step at a time)
+        def e2e_step():
             for L in launches:
-                L["x"].as_mut_slice(np.float32)[:] = L["x_host"].reshape(-1)      # host write -> upload at bind / replay
-
-        def e2e_encode():
+                L["x"].as_mut_slice(np.float32)[:] = L["x_host"].reshape(-1)      # host write -> upload at bind
             for L in launches:
                 encode_op(e2e_enc, L)
-                if symm is None:
-                    e2e_enc.memory_barrier()
-                    with torch.cuda.stream(e2e_stream):
-                        dist.all_gather_into_tensor(L["y_all"], L["y_loc"])
-
-        e2e_graph = None
-        if symm is not None:
-            for L in launches:                                                # create the pinned shadows up front
-                L["y"].as_slice(np.float32)
-            write_inputs()
-            e2e_encode()
+                e2e_enc.memory_barrier()
+                with torch.cuda.stream(e2e_stream):
+                    dist.all_gather_into_tensor(L["y_all"], L["y_loc"])
             e2e_enc.commit_and_wait()
-            write_inputs()
-            e2e_enc.begin_capture()
-            e2e_encode()
-            e2e_graph = e2e_enc.end_capture()
-
-        def e2e_step():
-            write_inputs()
-            if e2e_graph is not None:
-                e2e_graph.launch(e2e_enc)
-            else:
-                e2e_encode()
-            if symm is not None:
-                rank_barrier_on_stream(e2e_stream, e2e_enc)
-            e2e_enc.commit_and_wait()
-            acc = 0.0
-            for L in launches:
-                if symm is None:
-                    acc += float(L["y_all"][0, 0].item())                      # device -> host read of the result
-                else:
-                    acc += float(L["y"].as_slice(np.float32)[0])               # host view, fetched back by the commit
-            return acc
+            return sum(float(L["y_all"][0, 0].item()) for L in launches)       # device -> host read of the results
 
         for _ in range(2):
             e2e_step()
