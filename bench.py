@@ -977,24 +977,32 @@ def extra_numbers(mx, dev, reg, torch, tf_peak, hbm_peak):
         pg = mx.GgmlQuantizedMatmulIdParams(T, top_k, ffn, hidden, E, w1.size, mx.GgmlType.Q4_0)
         pd = mx.GgmlQuantizedMatmulIdParams(T * top_k, 1, hidden, ffn, E, w2.size, mx.GgmlType.Q6_K)
 
+        pl = mx.MoeFfnLayerParams(T, top_k, hidden, ffn, E, mx.GgmlType.Q4_0, mx.GgmlType.Q4_0, mx.GgmlType.Q6_K, w1.size, w1.size, w2.size)
+
         def layer(e):
+            # router, the expert half as one call (decode: routed mat-vecs for gate and up in one launch and the SwiGLU formed
+            # on the down projection's activation load, as upstream's fused quantized_matmul_id_swiglu_q4_0 does,
+            # src/ops/quantized_matmul_id_ggml.rs:551-670; prefill: one bucketing, one tile list and one activation pack
+            # for gate and up, the SwiGLU formed while the down projection's operand is packed), weighted reduce
+            mx.moe_softmax_topk(e, reg, dev, lg, ids, rw, T, E, top_k)
+            mx.moe_ffn_layer(e, reg, dev, xb, ids, wg, wu, wd, yg, yu, yd, pl)
+            mx.moe_weighted_reduce(e, reg, dev, rw, yd, outb, T, top_k, hidden)
+
+        def layer_calls(e):
+            # the same layer as the calls upstream's callers encode one by one
             mx.moe_softmax_topk(e, reg, dev, lg, ids, rw, T, E, top_k)
             mx.quantized_matmul_id_ggml(e, reg, dev, xb, wg, ids, yg, pg)
             mx.quantized_matmul_id_ggml(e, reg, dev, xb, wu, ids, yu, pg)
-            if T * top_k <= mx.MM_ID_ROUTING_THRESHOLD:
-                # decode: SwiGLU is formed on the down projection's activation load, as upstream's fused
-                # quantized_matmul_id_swiglu_q4_0 does at decode (src/ops/quantized_matmul_id_ggml.rs:551-670)
-                mx.quantized_matmul_id_swiglu(e, reg, dev, yg, yu, wd, ids, yd, pd)
-            else:
-                mx.silu_mul(e, reg, dev, yg, yu, act, T * top_k * ffn)
-                mx.quantized_matmul_id_ggml(e, reg, dev, act, wd, ids, yd, pd)
+            mx.silu_mul(e, reg, dev, yg, yu, act, T * top_k * ffn)
+            mx.quantized_matmul_id_ggml(e, reg, dev, act, wd, ids, yd, pd)
             mx.moe_weighted_reduce(e, reg, dev, rw, yd, outb, T, top_k, hidden)
 
         sec = timed(layer)
+        sec_calls = timed(layer_calls)
         active = min(E, T * top_k)
         wbytes = active * (2 * w1.size + w2.size) if T == 1 else E * (2 * w1.size + w2.size)
         moe[f"m{T}"] = {"tokens_per_s": T / sec, "ms_per_layer": sec * 1e3, "expert_weight_GBps": wbytes / sec / 1e9,
-                        "frac_of_measured_hbm_peak": wbytes / sec / 1e9 / hbm_peak}
+                        "frac_of_measured_hbm_peak": wbytes / sec / 1e9 / hbm_peak, "ms_per_layer_call_by_call": sec_calls * 1e3}
     out["moe_ffn_layer"] = moe
 
     # lm_head: Q6_K 151936 x 5120 (638 MB), m = 1 (mat-vec, HBM-bound) and m = 256 (mat-mat)

@@ -243,6 +243,26 @@ int mlxn_quantized_matmul_id_ggml(mlxn_encoder *enc, mlxn_registry *reg, mlxn_de
 int mlxn_quantized_matmul_id_swiglu(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *gate,
                                     mlxn_buffer *up, mlxn_buffer *weight, mlxn_buffer *ids, mlxn_buffer *output,
                                     const mlxn_qmm_id_params *params);
+/* The expert half of a MoE FFN layer as one call (no upstream counterpart; upstream's callers encode
+ * quantized_matmul_id_ggml for gate and up, silu_mul, and quantized_matmul_id_ggml with n_tokens * top_k rows and
+ * top_k = 1 for down, e.g. benches/bench_mul_mm_id_qwen36_ffn.rs).  Results are those of that chain, bit for bit.
+ *   x f32 [n_tokens, hidden]; ids u32 [n_tokens * top_k]; gate_w / up_w: stacked [n_experts][ffn][hidden / QK] blocks;
+ *   down_w: [n_experts][hidden][ffn / QK] blocks; gate_out, up_out f32 [n_tokens * top_k, ffn] (intermediates the caller
+ *   provides); down_out f32 [n_tokens * top_k, hidden], one row per (token, slot) pair, to be reduced with
+ *   mlxn_moe_weighted_reduce.
+ * More than HF2Q_MM_ID_ROUTING_THRESHOLD tokens: the pairs are bucketed once, the tile list is built once, x is packed
+ * once for gate and up, and silu(gate) * up is formed while the down projection's operand is packed (seven launches
+ * instead of thirteen).  Fewer tokens: the routed mat-vecs and the fused SwiGLU mat-vec.  What up_out holds afterwards
+ * depends on the route (the up projection, or silu(gate) * up where the stand-alone SwiGLU ran over it).
+ * A pair whose id names no expert gets a zero row in down_out; its rows of gate_out / up_out are unspecified. */
+typedef struct mlxn_moe_ffn_params {
+    uint32_t n_tokens, top_k, hidden, ffn, n_experts;
+    uint32_t gate_type, up_type, down_type;           /* mlxn_ggml_type */
+    uint64_t gate_stride, up_stride, down_stride;     /* bytes from one expert's matrix to the next */
+} mlxn_moe_ffn_params;
+int mlxn_moe_ffn_layer(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *x, mlxn_buffer *ids,
+                       mlxn_buffer *gate_w, mlxn_buffer *up_w, mlxn_buffer *down_w, mlxn_buffer *gate_out,
+                       mlxn_buffer *up_out, mlxn_buffer *down_out, const mlxn_moe_ffn_params *params);
 /* quantized_matmul_id_ggml_pooled (src/ops/quantized_matmul_id_ggml.rs:288-389) with the caller-owned
  * IdMmScratch {htpe, hids} (:672-719) and its capacities (check_capacity :704-718). */
 int mlxn_quantized_matmul_id_ggml_pooled(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev,

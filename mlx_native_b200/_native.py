@@ -29,6 +29,12 @@ class QmmIdParams(C.Structure):
                 ("ggml_type", u32), ("expert_stride", u64)]
 
 
+class MoeFfnParams(C.Structure):
+    _fields_ = [("n_tokens", u32), ("top_k", u32), ("hidden", u32), ("ffn", u32), ("n_experts", u32),
+                ("gate_type", u32), ("up_type", u32), ("down_type", u32),
+                ("gate_stride", u64), ("up_stride", u64), ("down_stride", u64)]
+
+
 # name -> (restype, argtypes); this table is also what tests check against the header
 SIGNATURES = {
     "mlxn_last_error_message": (C.c_char_p, []),
@@ -104,6 +110,7 @@ SIGNATURES = {
     "mlxn_dispatch_mm_for_test": (i32, [vp, vp, vp, vp, vp, vp, C.POINTER(QmmParams)]),
     "mlxn_quantized_matmul_id_ggml": (i32, [vp, vp, vp, vp, vp, vp, vp, C.POINTER(QmmIdParams)]),
     "mlxn_quantized_matmul_id_swiglu": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, C.POINTER(QmmIdParams)]),
+    "mlxn_moe_ffn_layer": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, C.POINTER(MoeFfnParams)]),
     "mlxn_quantized_matmul_id_ggml_pooled": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32,
                                                    C.POINTER(QmmIdParams)]),
     "mlxn_dispatch_id_mm_for_test": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, vp, C.POINTER(QmmIdParams)]),

@@ -584,6 +584,37 @@ def quantized_matmul_id_swiglu_q4_0(encoder, registry, device, gate, up, weight,
     quantized_matmul_id_swiglu(encoder, registry, device, gate, up, weight, ids, output, params)
 
 
+@dataclass(frozen=True)
+class MoeFfnLayerParams:
+    """Shapes of one MoE FFN layer's expert half: gate / up are [n_experts][ffn][hidden], down is [n_experts][hidden][ffn];
+    the strides are the bytes from one expert's matrix to the next."""
+    n_tokens: int
+    top_k: int
+    hidden: int
+    ffn: int
+    n_experts: int
+    gate_type: GgmlType
+    up_type: GgmlType
+    down_type: GgmlType
+    gate_stride: int
+    up_stride: int
+    down_stride: int
+
+    def _c(self) -> "_native.MoeFfnParams":
+        return _native.MoeFfnParams(self.n_tokens, self.top_k, self.hidden, self.ffn, self.n_experts, int(self.gate_type),
+                                    int(self.up_type), int(self.down_type), self.gate_stride, self.up_stride, self.down_stride)
+
+
+def moe_ffn_layer(encoder, registry, device, x, ids, gate_w, up_w, down_w, gate_out, up_out, down_out,
+                  params: MoeFfnLayerParams) -> None:
+    """Gate and up projections, SwiGLU and down projection of the routed experts as one call, with the results of the chain
+    quantized_matmul_id_ggml (gate), (up), silu_mul, quantized_matmul_id_ggml (down; n_tokens * top_k rows, top_k = 1) bit
+    for bit (upstream encodes that chain call by call: benches/bench_mul_mm_id_qwen36_ffn.rs).  down_out holds one row per
+    (token, slot) pair; gate_out and up_out are intermediates of [n_tokens * top_k, ffn] f32 each."""
+    _check(_native.lib().mlxn_moe_ffn_layer(encoder._h, _h(registry), device._h, _h(x), _h(ids), _h(gate_w), _h(up_w), _h(down_w),
+                                            _h(gate_out), _h(up_out), _h(down_out), C.byref(params._c())))
+
+
 class IdMmScratch:
     """src/ops/quantized_matmul_id_ggml.rs:672-719."""
 

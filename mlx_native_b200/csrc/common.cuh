@@ -127,6 +127,11 @@ struct QmmArgs {
     // and cast bf16 -> f32 -> f16 while it is packed.  nullptr: the f32 array `x`.
     const uint16_t *x_bf16;
     uint32_t head_dim;
+    // Fused MoE layer (routed tensor-core form): what an earlier call of the same layer has left in the scratch area and
+    // this call takes over instead of building it again (bit 0: the tile list, bit 1: the packed activations), and the
+    // second operand of a SwiGLU formed while packing: activations = silu(x) * x2 (src/shaders/silu_mul.metal:17-30).
+    uint32_t reuse;
+    const float *x2;
 };
 __host__ __device__ inline uint32_t qmm_ld(const QmmArgs &a) { return a.y_ld ? a.y_ld : a.n; }
 

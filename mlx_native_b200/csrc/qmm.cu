@@ -257,6 +257,14 @@ __global__ void __launch_bounds__(256) pack_x_kernel(const QmmArgs a, uint8_t *x
 #pragma unroll
                     for (int u = 0; u < 8; u++) v[u] = (k0 + u < a.k) ? xp[u] : 0.0f;
                 }
+                if (a.x2) {   // fused SwiGLU: the same expression as the stand-alone kernel, so the same f32 values
+                    const float *up = a.x2 + (xp - a.x);
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        const float uv = (k0 + u < a.k) ? __ldg(up + u) : 0.0f;
+                        v[u] = v[u] / (1.0f + expf(-v[u])) * uv;
+                    }
+                }
                 __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
                 __half2 h2 = __floats2half2_rn(v[4], v[5]), h3 = __floats2half2_rn(v[6], v[7]);
                 out.x = *reinterpret_cast<uint32_t *>(&h0);
@@ -1292,15 +1300,17 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
         if (tiles == 0) tiles = 1;
         const size_t header = ((1 + 2 * tiles) * 4 + 1023) / 1024 * 1024;
         uint32_t *tl = reinterpret_cast<uint32_t *>(scratch);
-        build_tiles_kernel<<<1, 256, 0, st>>>(a.htpe, a.n_experts, NT, (uint32_t)tiles, tl);
-        (*launches)++;
+        if (!(a.reuse & 1u)) {   // (an earlier call of the same layer built the list: same buckets, same NT)
+            build_tiles_kernel<<<1, 256, 0, st>>>(a.htpe, a.n_experts, NT, (uint32_t)tiles, tl);
+            (*launches)++;
+        }
         a.tiles = tl;
         xpack = scratch + header;
     } else {
         tiles = (a.m + NT - 1) / NT;
         a.tiles = nullptr;
     }
-    {
+    if (!(a.reuse & 2u)) {   // (... or packed the same activation rows already)
         // enough CTAs to fill the GPU a few times over, few enough that a tile's routing lookups are amortised
         uint32_t lanes = c.nchunks;
         while (lanes > 1 && (uint64_t)lanes * tiles > 2048) lanes = (lanes + 1) / 2;

@@ -2044,6 +2044,118 @@ extern "C" int mlxn_quantized_matmul_id_swiglu(mlxn_encoder *enc, mlxn_registry 
     return dispatch_id_mv(enc, reg, dev, gate, weight, ids, output, &q, up);
 }
 
+// ------------------------------------------------------------------------------------------------
+// The expert half of a MoE FFN layer as one call (no upstream counterpart: upstream encodes the three routed products and
+// the SwiGLU one by one, e.g. benches/bench_mul_mm_id_qwen36_ffn.rs).  Same results as that chain, bit for bit; what the
+// one call saves on the grouped route is preparation the three products share: the pairs are bucketed by expert once
+// (the down projection's rows are the same (token, slot) pairs in the same order), the tile list is built once, the
+// activations are packed once for gate and up, and the SwiGLU is formed while the down projection's operand is packed
+// (no stand-alone SwiGLU launch, no [pairs, ffn] intermediate).  Seven launches instead of thirteen.
+//   gate_out, up_out: f32 [n_tokens * top_k, ffn]; down_out: f32 [n_tokens * top_k, hidden], one row per pair.
+// Rows of pairs whose id names no expert: zeros in down_out, unspecified in gate_out / up_out on the grouped route.
+// Few tokens (n_tokens <= the routing threshold), Q5_K or shapes outside the tensor-core kernel take the chain itself.
+// ------------------------------------------------------------------------------------------------
+extern "C" int mlxn_moe_ffn_layer(mlxn_encoder *enc, mlxn_registry *reg, mlxn_device *dev, mlxn_buffer *x, mlxn_buffer *ids,
+                                  mlxn_buffer *gate_w, mlxn_buffer *up_w, mlxn_buffer *down_w, mlxn_buffer *gate_out,
+                                  mlxn_buffer *up_out, mlxn_buffer *down_out, const mlxn_moe_ffn_params *p) {
+    int rc = check_handles(enc, dev, {x, ids, gate_w, up_w, down_w, gate_out, up_out, down_out, p});
+    if (rc) return rc;
+    const uint64_t pairs = (uint64_t)p->n_tokens * p->top_k;
+    if (pairs == 0 || pairs > 0x7FFFFFFFull)
+        return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_ffn_layer: n_tokens * top_k must be in 1..2^31-1");
+    mlxn_qmm_id_params pg{p->n_tokens, p->top_k, p->ffn, p->hidden, p->n_experts, p->gate_type, p->gate_stride};
+    mlxn_qmm_id_params pu{p->n_tokens, p->top_k, p->ffn, p->hidden, p->n_experts, p->up_type, p->up_stride};
+    mlxn_qmm_id_params pd{(uint32_t)pairs, 1, p->hidden, p->ffn, p->n_experts, p->down_type, p->down_stride};
+    if ((rc = validate_id("moe_ffn_layer (gate)", x, gate_w, ids, gate_out, &pg))) return rc;
+    if ((rc = validate_id("moe_ffn_layer (up)", x, up_w, ids, up_out, &pu))) return rc;
+    if ((rc = validate_id("moe_ffn_layer (down)", gate_out, down_w, ids, down_out, &pd))) return rc;
+    if ((rc = check_alignment(x, gate_w, gate_out)) || (rc = check_alignment(x, up_w, up_out)) ||
+        (rc = check_alignment(gate_out, down_w, down_out)))
+        return rc;
+    auto probe = [&](const mlxn_qmm_id_params &q, mlxn_buffer *w) {
+        QmmArgs a{};
+        a.w = w->dev();
+        a.k = q.k;
+        a.expert_stride = q.expert_stride;
+        return qmm_tc_supported(a);
+    };
+    const bool grouped = id_routes_to_mm(&pg) && id_routes_to_mm(&pu) && id_routes_to_mm(&pd) && opt_qmm_tc() &&
+                         probe(pg, gate_w) && probe(pu, up_w) && probe(pd, down_w);
+    if (!grouped) {
+        // the chain itself: few tokens take the routed mat-vecs and the fused SwiGLU mat-vec; whatever else is left
+        // takes the calls one by one, with the SwiGLU written over up_out
+        if ((rc = mlxn_quantized_matmul_id_ggml(enc, reg, dev, x, gate_w, ids, gate_out, &pg))) return rc;
+        if ((rc = mlxn_quantized_matmul_id_ggml(enc, reg, dev, x, up_w, ids, up_out, &pu))) return rc;
+        const int td = (int)p->down_type;
+        if (!id_routes_to_mm(&pd) && (td == GT_Q4_0 || td == GT_Q8_0 || td == GT_Q6_K)) {
+            mlxn_qmm_id_params ps = pd;
+            return mlxn_quantized_matmul_id_swiglu(enc, reg, dev, gate_out, up_out, down_w, ids, down_out, &ps);
+        }
+        if (pairs * p->ffn > 0xFFFFFFFFull) return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: moe_ffn_layer: n_tokens * top_k * ffn is too large");
+        if ((rc = mlxn_silu_mul(enc, reg, dev, gate_out, up_out, up_out, (uint32_t)(pairs * p->ffn)))) return rc;
+        return mlxn_quantized_matmul_id_ggml(enc, reg, dev, up_out, down_w, ids, down_out, &pd);
+    }
+    if ((rc = op_begin(enc, {{x, false}, {ids, false}, {gate_w, false}, {up_w, false}, {down_w, false}, {gate_out, true},
+                             {up_out, true}, {down_out, true}})))
+        return rc;
+    char map0_name[48];
+    snprintf(map0_name, sizeof(map0_name), "kernel_mul_mm_id_map0_ne20_%u", p->top_k);
+    if ((rc = touch_kernel(reg, dev, known_kernel(map0_name) ? map0_name : "kernel_mul_mm_id_map0_ne20_n"))) return rc;
+    if ((rc = touch_kernel(reg, dev, mm_id_kernel_name((int)p->gate_type))) || (rc = touch_kernel(reg, dev, mm_id_kernel_name((int)p->up_type))) ||
+        (rc = touch_kernel(reg, dev, mm_id_kernel_name((int)p->down_type))))
+        return rc;
+    // scratch: bucket sizes, buckets ([experts, n_tokens]: a token holds an expert at most once, and the down projection's
+    // rows are the same pairs), then the tile list and the packed activations (sized for the longer of the two K)
+    const uint32_t nt = qmm_tc_pick_nt((int)p->gate_type, p->n_tokens, p->ffn, dev->sm_count, true);
+    const size_t htpe_b = ((size_t)p->n_experts * 4 + 1023) / 1024 * 1024;
+    const size_t hids_b = ((size_t)p->n_experts * p->n_tokens * 4 + 1023) / 1024 * 1024;
+    QmmArgs sz{};
+    sz.k = p->hidden > p->ffn ? p->hidden : p->ffn;
+    sz.n_experts = p->n_experts;
+    sz.total_rows = (uint32_t)pairs;
+    uint8_t *scratch = nullptr;
+    if ((rc = encoder_scratch(enc, htpe_b + hids_b + qmm_tc_scratch_bytes(sz, nt, true), &scratch))) return rc;
+    uint32_t *htpe = reinterpret_cast<uint32_t *>(scratch);
+    int32_t *hids = reinterpret_cast<int32_t *>(scratch + htpe_b);
+    uint8_t *tc = scratch + htpe_b + hids_b;
+    CUDA_TRY(launch_moe_map0(reinterpret_cast<const uint32_t *>(ids->dev()), p->n_tokens, p->top_k, p->n_experts, p->n_tokens,
+                             htpe, hids, reinterpret_cast<float *>(down_out->dev()), p->hidden, enc->stream),
+             "map0 launch");
+    g_launches.fetch_add(1);
+    g_barrier.fetch_add(1);
+    auto product = [&](const mlxn_qmm_id_params &q, mlxn_buffer *in, mlxn_buffer *in2, mlxn_buffer *w, mlxn_buffer *out,
+                       uint32_t reuse) -> int {
+        QmmArgs a{};
+        a.w = w->dev();
+        a.x = reinterpret_cast<const float *>(in->dev());
+        a.x2 = in2 ? reinterpret_cast<const float *>(in2->dev()) : nullptr;
+        a.y = reinterpret_cast<float *>(out->dev());
+        a.m = q.n_tokens;
+        a.n = q.n;
+        a.k = q.k;
+        a.htpe = htpe;
+        a.hids = hids;
+        a.hids_stride = p->n_tokens;
+        a.top_k = q.top_k;
+        a.n_experts = q.n_experts;
+        a.total_rows = (uint32_t)pairs;
+        a.expert_stride = q.expert_stride;
+        a.status = enc->status_dev;
+        a.reuse = reuse;
+        int launches = 0;
+        CUDA_TRY(launch_qmm_tc((int)q.ggml_type, a, true, nt, tc, enc->stream, &launches), "mat-mat launch");
+        g_launches.fetch_add(launches);
+        g_dispatch.fetch_add(1);
+        return MLXN_OK;
+    };
+    if ((rc = product(pg, x, nullptr, gate_w, gate_out, 0u))) return rc;          // builds the tile list, packs x
+    if ((rc = product(pu, x, nullptr, up_w, up_out, 3u))) return rc;              // takes both over
+    if ((rc = product(pd, gate_out, up_out, down_w, down_out, 1u))) return rc;    // same tiles; packs silu(gate) * up
+    g_last_kernel = "qmm_tc_id";
+    g_dispatch.fetch_add(1);
+    return MLXN_OK;
+}
+
 static int check_scratch_buffers(mlxn_buffer *htpe, mlxn_buffer *hids, const mlxn_qmm_id_params *p) {
     if (htpe->len < mlxn_id_mm_htpe_bytes(p))
         return fail(MLXN_INVALID_ARGUMENT, "Invalid argument: htpe buffer too small: expected %zu bytes, got %zu", mlxn_id_mm_htpe_bytes(p), htpe->len);
