@@ -1084,7 +1084,7 @@ def run_case(argv):
       --case mvs [Q8_0|Q6_K|Q4_0] [m]   the same on the narrow shape n=1024 k=4096, 40 weight copies (> L2)
       --case mm  [Q4_0|Q6_K|Q8_0] [m]   prefill mat-mat, n=4096 k=4096, m=512 by default
       --case moe [m]                    expert-routed gate projection, 128 experts, top-8
-      --case moe_layer [m] [reps]       whole MoE FFN layer (route, gate, up, SwiGLU, down, reduce), 128 experts, top-8
+      --case moe_layer [m] [reps] [calls]  whole MoE FFN layer (router, moe_ffn_layer, reduce; `calls`: the expert half call by call), 128 experts, top-8
       --case moe_trace [gate|down]      cycle trace of one CTA of the grouped mat-mat (experiment build only)
       --case cmp [types] [ms]           the mat-vec kernels side by side, microseconds per call, independent and chained
                                         (CUDA-graph replay over rotating weight copies > L2)
@@ -1197,13 +1197,16 @@ def run_case(argv):
         outb = dev.alloc_buffer(T * hidden * 4, mx.DType.F32)
         pg = mx.GgmlQuantizedMatmulIdParams(T, top_k, ffn, hidden, E, bufs["gate_stride"], mx.GgmlType.Q4_0)
         pd = mx.GgmlQuantizedMatmulIdParams(T * top_k, 1, hidden, ffn, E, bufs["down_stride"], mx.GgmlType.Q6_K)
+        calls = len(argv) > 3 and argv[3] == "calls"      # the layer call by call instead of as one moe_ffn_layer call
+        pl = mx.MoeFfnLayerParams(T, top_k, hidden, ffn, E, mx.GgmlType.Q4_0, mx.GgmlType.Q4_0, mx.GgmlType.Q6_K,
+                                  bufs["gate_stride"], bufs["up_stride"], bufs["down_stride"])
         for _ in range(reps):
             mx.moe_softmax_topk(enc, reg, dev, lg, ids, rw, T, E, top_k)
-            mx.quantized_matmul_id_ggml(enc, reg, dev, xb, bufs["gate"], ids, yg, pg)
-            mx.quantized_matmul_id_ggml(enc, reg, dev, xb, bufs["up"], ids, yu, pg)
-            if T * top_k <= mx.MM_ID_ROUTING_THRESHOLD:
-                mx.quantized_matmul_id_swiglu(enc, reg, dev, yg, yu, bufs["down"], ids, yd, pd)
+            if not calls:
+                mx.moe_ffn_layer(enc, reg, dev, xb, ids, bufs["gate"], bufs["up"], bufs["down"], yg, yu, yd, pl)
             else:
+                mx.quantized_matmul_id_ggml(enc, reg, dev, xb, bufs["gate"], ids, yg, pg)
+                mx.quantized_matmul_id_ggml(enc, reg, dev, xb, bufs["up"], ids, yu, pg)
                 mx.silu_mul(enc, reg, dev, yg, yu, act, T * top_k * ffn)
                 mx.quantized_matmul_id_ggml(enc, reg, dev, act, bufs["down"], ids, yd, pd)
             mx.moe_weighted_reduce(enc, reg, dev, rw, yd, outb, T, top_k, hidden)
