@@ -38,6 +38,16 @@ def test_header_compiles_as_c_and_cpp(tmp_path):
     subprocess.check_call(["g++", "-std=c++17", "-Wall", "-Werror", "-x", "c++", "-I", os.path.join(ROOT, "include"), "-c",
                            str(src), "-o", str(tmp_path / "t2.o")])
     assert ctypes.sizeof(_native.QmmParams) == 16 and ctypes.sizeof(_native.QmmIdParams) == 32
+    # the ctypes mirrors have the C structs' sizes and field offsets (printed by a program compiled against the header)
+    probe = tmp_path / "sizes.c"
+    probe.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "mlxn_b200.h"\nint main(void){ printf("%zu %zu %zu %zu %zu %zu\\n", '
+                     'sizeof(mlxn_qmm_params), sizeof(mlxn_qmm_id_params), offsetof(mlxn_qmm_id_params, expert_stride), '
+                     'sizeof(mlxn_moe_ffn_params), offsetof(mlxn_moe_ffn_params, gate_stride), sizeof(mlxn_qmm_perm021_params)); return 0; }\n')
+    exe = tmp_path / "sizes"
+    subprocess.check_call(["gcc", "-std=c99", "-I", os.path.join(ROOT, "include"), str(probe), "-o", str(exe)])
+    got = [int(v) for v in subprocess.check_output([str(exe)]).split()]
+    assert got == [ctypes.sizeof(_native.QmmParams), ctypes.sizeof(_native.QmmIdParams), _native.QmmIdParams.expert_stride.offset,
+                   ctypes.sizeof(_native.MoeFfnParams), _native.MoeFfnParams.gate_stride.offset, ctypes.sizeof(_native.QmmPerm021Params)]
 
 
 def test_block_geometry_and_dtypes():
