@@ -251,10 +251,9 @@ int mlxn_quantized_matmul_id_swiglu(mlxn_encoder *enc, mlxn_registry *reg, mlxn_
  *   provides); down_out f32 [n_tokens * top_k, hidden], one row per (token, slot) pair, to be reduced with
  *   mlxn_moe_weighted_reduce.
  * More than HF2Q_MM_ID_ROUTING_THRESHOLD tokens: the pairs are bucketed once, the tile list is built once, x is packed
- * once for gate and up, and silu(gate) * up is formed by the up projection's read-back, which writes the down
- * projection's packed operand directly (ffn a multiple of 128 and 16-byte aligned buffers; otherwise while that operand
- * is packed): six or seven launches instead of thirteen.  Fewer tokens: the routed mat-vecs and the fused SwiGLU
- * mat-vec.  What up_out holds afterwards depends on the route (nothing, the up projection, or silu(gate) * up).
+ * once for gate and up, and silu(gate) * up is formed while the down projection's operand is packed (seven launches
+ * instead of thirteen).  Fewer tokens: the routed mat-vecs and the fused SwiGLU mat-vec.  What up_out holds afterwards
+ * depends on the route (the up projection, or silu(gate) * up where the stand-alone SwiGLU ran over it).
  * A pair whose id names no expert gets a zero row in down_out; its rows of gate_out / up_out are unspecified. */
 typedef struct mlxn_moe_ffn_params {
     uint32_t n_tokens, top_k, hidden, ffn, n_experts;

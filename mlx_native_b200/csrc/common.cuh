@@ -132,13 +132,6 @@ struct QmmArgs {
     // second operand of a SwiGLU formed while packing: activations = silu(x) * x2 (src/shaders/silu_mul.metal:17-30).
     uint32_t reuse;
     const float *x2;
-    // ... the packed activations when they lie somewhere else than behind the tile list (bit 1 of `reuse` set) ...
-    const uint8_t *xpack_in;
-    // ... and the up projection of such a layer on 64-row tiles: instead of storing its result, the read-back forms
-    // silu(gate_in[o, c]) * result[o, c] (gate_in: the gate projection's result, f32 [pairs, n]) and writes it as f16 into
-    // the packed operand tiles of the down projection at act_out (same tile list, K = n; n a multiple of 128).
-    const float *gate_in;
-    uint8_t *act_out;
 };
 __host__ __device__ inline uint32_t qmm_ld(const QmmArgs &a) { return a.y_ld ? a.y_ld : a.n; }
 

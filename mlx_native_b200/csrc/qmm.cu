@@ -1073,29 +1073,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const QmmArgs a, 
                     mbar_arrive(&stage_ready[nitem & 1u]);        // this warp's part of the staged tile is written
                 }
                 if (!mbar_wait(&stage_ready[nitem & 1u], (nitem >> 1) & 1u, &abort_flag, a.status, ST_WAIT_EMPTY_TIMEOUT, wmode_dq)) break;
-                if (a.act_out) {
-                    // The up projection of a fused MoE layer: the tile's rows are the rows of the same tile of the down
-                    // projection's operand (same buckets), its 128 columns are two of that operand's 64-wide K chunks.
-                    // Every row is written, absent ones as zeros, as the activation pack would have left them.
-                    const uint32_t c4 = n0 + 4 * lane, kc = c4 >> 6, jc = (c4 & 63u) >> 3, hsel = (c4 >> 2) & 1u;
-                    const uint32_t chunks2 = (a.n + 63u) >> 6;
-                    uint8_t *tile = a.act_out + ((size_t)it.tt * chunks2 + kc) * (size_t)(NT * 128);
-                    for (uint32_t r = dw; r < NT; r += kTcDequantWarps) {
-                        const int32_t o = tab[r];
-                        uint2 out = make_uint2(0u, 0u);
-                        if (o >= 0 && c4 + 3 < a.n) {
-                            const float4 u = *reinterpret_cast<const float4 *>(stg + r * kPitch + 4 * lane);
-                            const float4 gt = __ldg(reinterpret_cast<const float4 *>(a.gate_in + (size_t)o * a.n + c4));
-                            // (the expression of the stand-alone SwiGLU kernel: the same f32 values, one rounding to f16)
-                            const __half2 h0 = __floats2half2_rn(gt.x / (1.0f + expf(-gt.x)) * u.x, gt.y / (1.0f + expf(-gt.y)) * u.y);
-                            const __half2 h1 = __floats2half2_rn(gt.z / (1.0f + expf(-gt.z)) * u.z, gt.w / (1.0f + expf(-gt.w)) * u.w);
-                            out.x = *reinterpret_cast<const uint32_t *>(&h0);
-                            out.y = *reinterpret_cast<const uint32_t *>(&h1);
-                        }
-                        if (kc < chunks2)
-                            *reinterpret_cast<uint2 *>(tile + (r >> 3) * 1024 + (r & 7u) * 128 + ((jc ^ (r & 7u)) << 4) + 8 * hsel) = out;
-                    }
-                } else if (!(MLXN_DBG(c) & 256u)) {
+                if (!(MLXN_DBG(c) & 256u)) {
                     const uint32_t c4 = n0 + 4 * lane;
                     for (uint32_t r = dw; r < NT; r += kTcDequantWarps) {
                         const int32_t o = tab[r];
@@ -1332,8 +1310,6 @@ static cudaError_t launch_tc_tn(QmmArgs a, bool routed, uint8_t *scratch, cudaSt
         tiles = (a.m + NT - 1) / NT;
         a.tiles = nullptr;
     }
-    if (a.xpack_in) xpack = const_cast<uint8_t *>(a.xpack_in);
-    if (a.act_out && (!staged || a.n % 128 != 0)) return cudaErrorInvalidValue;   // (the fused read-back is the staged one's)
     if (!(a.reuse & 2u)) {   // (... or packed the same activation rows already)
         // enough CTAs to fill the GPU a few times over, few enough that a tile's routing lookups are amortised
         uint32_t lanes = c.nchunks;

@@ -2050,8 +2050,7 @@ extern "C" int mlxn_quantized_matmul_id_swiglu(mlxn_encoder *enc, mlxn_registry 
 // one call saves on the grouped route is preparation the three products share: the pairs are bucketed by expert once
 // (the down projection's rows are the same (token, slot) pairs in the same order), the tile list is built once, the
 // activations are packed once for gate and up, and the SwiGLU is formed while the down projection's operand is packed
-// (no stand-alone SwiGLU launch, no [pairs, ffn] intermediate) -- or, where the shapes allow, by the up projection's read-back
-// itself, which then writes the down projection's packed operand instead of up_out.  Six or seven launches instead of thirteen.
+// (no stand-alone SwiGLU launch, no [pairs, ffn] intermediate).  Seven launches instead of thirteen.
 //   gate_out, up_out: f32 [n_tokens * top_k, ffn]; down_out: f32 [n_tokens * top_k, hidden], one row per pair.
 // Rows of pairs whose id names no expert: zeros in down_out, unspecified in gate_out / up_out on the grouped route.
 // Few tokens (n_tokens <= the routing threshold), Q5_K or shapes outside the tensor-core kernel take the chain itself.
@@ -2110,37 +2109,23 @@ extern "C" int mlxn_moe_ffn_layer(mlxn_encoder *enc, mlxn_registry *reg, mlxn_de
     const uint32_t nt = qmm_tc_pick_nt((int)p->gate_type, p->n_tokens, p->ffn, dev->sm_count, true);
     const size_t htpe_b = ((size_t)p->n_experts * 4 + 1023) / 1024 * 1024;
     const size_t hids_b = ((size_t)p->n_experts * p->n_tokens * 4 + 1023) / 1024 * 1024;
-    // Where the shapes allow (ffn a multiple of 128, 16-byte aligned rows: the staged read-back of 64-row tiles), the up
-    // projection's read-back forms silu(gate) * up itself and writes it as the down projection's packed operand into an
-    // area of its own: up_out is then not written, and the layer has no second activation pack.
-    const bool fuse_act = nt == 64 && p->ffn % 128 == 0 &&
-                          ((((uintptr_t)up_out->dev()) | ((uintptr_t)gate_out->dev()) | ((uintptr_t)p->ffn * 4u)) & 15u) == 0;
-    QmmArgs sz{}, sz2{};
-    sz.k = (fuse_act || p->hidden > p->ffn) ? p->hidden : p->ffn;
-    sz.n_experts = sz2.n_experts = p->n_experts;
-    sz.total_rows = sz2.total_rows = (uint32_t)pairs;
-    sz2.k = p->ffn;
-    const size_t x_area = qmm_tc_scratch_bytes(sz, nt, true), act_area = fuse_act ? qmm_tc_scratch_bytes(sz2, nt, true) : 0;
+    QmmArgs sz{};
+    sz.k = p->hidden > p->ffn ? p->hidden : p->ffn;
+    sz.n_experts = p->n_experts;
+    sz.total_rows = (uint32_t)pairs;
     uint8_t *scratch = nullptr;
-    if ((rc = encoder_scratch(enc, htpe_b + hids_b + x_area + act_area, &scratch))) return rc;
+    if ((rc = encoder_scratch(enc, htpe_b + hids_b + qmm_tc_scratch_bytes(sz, nt, true), &scratch))) return rc;
     uint32_t *htpe = reinterpret_cast<uint32_t *>(scratch);
     int32_t *hids = reinterpret_cast<int32_t *>(scratch + htpe_b);
     uint8_t *tc = scratch + htpe_b + hids_b;
-    uint8_t *act = tc + x_area;
     CUDA_TRY(launch_moe_map0(reinterpret_cast<const uint32_t *>(ids->dev()), p->n_tokens, p->top_k, p->n_experts, p->n_tokens,
                              htpe, hids, reinterpret_cast<float *>(down_out->dev()), p->hidden, enc->stream),
              "map0 launch");
     g_launches.fetch_add(1);
     g_barrier.fetch_add(1);
     auto product = [&](const mlxn_qmm_id_params &q, mlxn_buffer *in, mlxn_buffer *in2, mlxn_buffer *w, mlxn_buffer *out,
-                       uint32_t reuse, int fused = 0) -> int {
+                       uint32_t reuse) -> int {
         QmmArgs a{};
-        if (fused == 1) {          // the up projection writing the down projection's operand
-            a.gate_in = reinterpret_cast<const float *>(gate_out->dev());
-            a.act_out = act;
-        } else if (fused == 2) {   // the down projection reading it
-            a.xpack_in = act;
-        }
         a.w = w->dev();
         a.x = reinterpret_cast<const float *>(in->dev());
         a.x2 = in2 ? reinterpret_cast<const float *>(in2->dev()) : nullptr;
@@ -2164,13 +2149,8 @@ extern "C" int mlxn_moe_ffn_layer(mlxn_encoder *enc, mlxn_registry *reg, mlxn_de
         return MLXN_OK;
     };
     if ((rc = product(pg, x, nullptr, gate_w, gate_out, 0u))) return rc;          // builds the tile list, packs x
-    if (fuse_act) {
-        if ((rc = product(pu, x, nullptr, up_w, up_out, 3u, 1))) return rc;           // takes both over; writes silu(gate) * up, packed
-        if ((rc = product(pd, gate_out, nullptr, down_w, down_out, 3u, 2))) return rc; // same tiles, that operand
-    } else {
-        if ((rc = product(pu, x, nullptr, up_w, up_out, 3u))) return rc;              // takes both over
-        if ((rc = product(pd, gate_out, up_out, down_w, down_out, 1u))) return rc;    // same tiles; packs silu(gate) * up
-    }
+    if ((rc = product(pu, x, nullptr, up_w, up_out, 3u))) return rc;              // takes both over
+    if ((rc = product(pd, gate_out, up_out, down_w, down_out, 1u))) return rc;    // same tiles; packs silu(gate) * up
     g_last_kernel = "qmm_tc_id";
     g_dispatch.fetch_add(1);
     return MLXN_OK;
